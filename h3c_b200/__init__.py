@@ -1,0 +1,272 @@
+"""h3c_b200: host-side mirror of the reference's operator interface for the DiT denoiser block
+path, bound to libh3_b200.so (hand-written sm_100a kernels behind a C ABI).
+
+`Cuda` mirrors the reference's `h3_cuda` handle and its `h3_cuda_*` operators (same names minus
+the prefix, same argument meaning, errors raised as `H3Error` carrying the library's message);
+`Weight` mirrors `h3_cuda_w4a8_weight`.  torch tensors are used only as device buffers.
+"""
+from __future__ import annotations
+
+import ctypes as C
+
+from . import lib as _l
+from .lib import BF16, EPI_GATE, EPI_GELU, EPI_PLAIN, EPI_SWIGLU, F16, F32, I32, H3Error, call, load, ptr
+
+__all__ = ["Cuda", "Weight", "H3Error", "F32", "BF16", "F16", "I32", "EPI_PLAIN", "EPI_GATE", "EPI_SWIGLU",
+           "EPI_GELU", "load"]
+
+
+def _dt(t):
+    import torch
+    return {torch.float32: F32, torch.bfloat16: BF16, torch.float16: F16, torch.int32: I32}[t.dtype]
+
+
+class Weight:
+    """Resident INT8 [N,K] weight + per-channel scale (h3_cuda_w4a8_weight)."""
+
+    def __init__(self, cuda: "Cuda", handle: int):
+        self.cuda, self.h = cuda, handle
+
+    @property
+    def n(self):
+        return int(load().h3_cuda_w4a8_weight_n(self.h))
+
+    @property
+    def k(self):
+        return int(load().h3_cuda_w4a8_weight_k(self.h))
+
+    def download_int8(self):
+        import numpy as np
+        out = np.empty((self.n, self.k), np.int8)
+        call("h3_cuda_w4a8_weight_download_int8", self.h, out.ctypes.data)
+        return out
+
+    def download_scales(self):
+        import numpy as np
+        out = np.empty(self.n, np.float32)
+        call("h3b_w4a8_weight_download_scales", self.h, out.ctypes.data)
+        return out
+
+    def free(self):
+        if self.h:
+            load().h3_cuda_w4a8_weight_free(self.h)
+            self.h = None
+
+    def __del__(self):
+        try:
+            self.free()
+        except Exception:
+            pass
+
+
+class Cuda:
+    """One handle per device (h3_cuda).  Work is enqueued on torch's current stream."""
+
+    def __init__(self, device_index: int = 0):
+        import torch
+        load()
+        err = C.create_string_buffer(_l.ERR_LEN)
+        self.h = load().h3_cuda_create(device_index, err, _l.ERR_LEN)
+        if not self.h:
+            raise H3Error(f"h3_cuda_create: {err.value.decode(errors='replace')}")
+        self.device = torch.device("cuda", device_index)
+        self.use_stream(torch.cuda.current_stream(self.device))
+
+    def use_stream(self, stream):
+        call("h3_cuda_set_op_stream", self.h, stream.cuda_stream)
+
+    def close(self):
+        if self.h:
+            load().h3_cuda_free(self.h)
+            self.h = None
+
+    def check(self):
+        """Synchronises and raises if any kernel gave up a bounded wait."""
+        st = C.c_int(0)
+        call("h3b_cuda_check", self.h, C.byref(st))
+
+    def launch_count(self, reset=False) -> int:
+        return int(load().h3b_cuda_launch_count(self.h, int(reset)))
+
+    def set_quiet(self, on: bool):
+        load().h3_cuda_set_quiet(self.h, int(on))
+
+    # ---- weights
+    def weight_from_w4a8(self, packed, codebook, s_rel, s_channel, group_size=16) -> Weight:
+        import numpy as np
+        packed = np.ascontiguousarray(packed, np.int8)
+        h = C.c_void_p()
+        call("h3_cuda_w4a8_weight_create", self.h, packed.ctypes.data, packed.shape[0], packed.shape[1],
+             np.ascontiguousarray(codebook, np.float32).ctypes.data, np.ascontiguousarray(s_rel, np.uint8).ctypes.data,
+             np.ascontiguousarray(s_channel, np.float32).ctypes.data, group_size, C.byref(h), None, None)
+        return Weight(self, h.value)
+
+    def weight_from_i8(self, w_i8, s_channel) -> Weight:
+        import numpy as np
+        w_i8 = np.ascontiguousarray(w_i8, np.int8)
+        s_channel = np.ascontiguousarray(s_channel, np.float32)
+        h = C.c_void_p()
+        call("h3_cuda_w4a8_weight_create_from_i8", self.h, w_i8.ctypes.data, w_i8.shape[0], w_i8.shape[1],
+             s_channel.ctypes.data, C.byref(h), None, 1)
+        return Weight(self, h.value)
+
+    def weight_from_w4g(self, packed, scales_f16, group=128) -> Weight:
+        import numpy as np
+        packed = np.ascontiguousarray(packed, np.uint8)
+        scales_f16 = np.ascontiguousarray(scales_f16, np.uint16)
+        h = C.c_void_p()
+        call("h3b_w4g_weight_create", self.h, packed.ctypes.data, scales_f16.ctypes.data, packed.shape[0],
+             packed.shape[1] * 2, group, C.byref(h))
+        return Weight(self, h.value)
+
+    # ---- row-wise operators
+    def norm(self, x, *, branch=None, norm_w=None, modulation=None, row_map=None, slots=0, gate_slot=0, shift_slot=0,
+             scale_slot=0, eps=1e-5, identity=False, convrot_gs=0, gated=None, normed=None, rot=None, q=None,
+             scales=None):
+        a = _l.NormArgs(ptr(x), ptr(branch), ptr(norm_w), ptr(modulation), ptr(row_map), x.shape[0], x.shape[1],
+                        slots, gate_slot, shift_slot, scale_slot, eps, _dt(x), int(identity), convrot_gs, ptr(gated),
+                        ptr(normed), ptr(rot), ptr(q), ptr(scales))
+        call("h3b_norm_dev", self.h, C.byref(a))
+
+    def quantize_act_int8(self, x):
+        import torch
+        q = torch.empty(x.shape, dtype=torch.int8, device=x.device)
+        s = torch.empty(x.shape[0], dtype=torch.float32, device=x.device)
+        call("h3b_quantize_act_int8_dev", self.h, ptr(x), _dt(x), x.shape[0], x.shape[1], ptr(q), ptr(s))
+        return q, s
+
+    def adaln_f32_dev(self, x, norm_w, modulation, row_map, slots, shift_slot, scale_slot, eps=1e-5):
+        import torch
+        out = torch.empty_like(x)
+        call("h3_cuda_adaln_f32_dev", self.h, ptr(x), ptr(norm_w), ptr(modulation), ptr(row_map), x.shape[0],
+             x.shape[1], slots, shift_slot, scale_slot, eps, ptr(out), None)
+        return out
+
+    def rms_norm_f32_dev(self, x, w, eps=1e-5):
+        import torch
+        out = torch.empty_like(x)
+        call("h3_cuda_rms_norm_f32_dev", self.h, ptr(x), ptr(w), x.shape[0], x.shape[1], eps, ptr(out))
+        return out
+
+    def gate_f32_dev(self, residual, branch, modulation, row_map, slots, gate_slot):
+        import torch
+        out = torch.empty_like(residual)
+        call("h3_cuda_gate_f32_dev", self.h, ptr(residual), ptr(branch), ptr(modulation), ptr(row_map),
+             residual.shape[0], residual.shape[1], slots, gate_slot, ptr(out), None)
+        return out
+
+    def gate_adaln_f32_dev(self, residual, branch, norm_w, modulation, row_map, slots, gate_slot, shift_slot,
+                           scale_slot, eps=1e-5):
+        import torch
+        gated, normed = torch.empty_like(residual), torch.empty_like(residual)
+        call("h3_cuda_gate_adaln_f32_dev", self.h, ptr(residual), ptr(branch), ptr(norm_w), ptr(modulation),
+             ptr(row_map), residual.shape[0], residual.shape[1], slots, gate_slot, shift_slot, scale_slot, eps,
+             ptr(gated), ptr(normed), None)
+        return gated, normed
+
+    def swiglu_f32_dev(self, fused):
+        import torch
+        out = torch.empty((fused.shape[0], fused.shape[1] // 2), dtype=fused.dtype, device=fused.device)
+        call("h3_cuda_swiglu_f32_dev", self.h, ptr(fused), fused.shape[0], fused.shape[1] // 2, ptr(out), None)
+        return out
+
+    def convrot_act_f32_dd(self, x, gs):
+        import torch
+        y = torch.empty_like(x)
+        call("h3_cuda_convrot_act_f32_dd", self.h, ptr(x), x.shape[0], x.shape[1], gs, ptr(y))
+        return y
+
+    def qkv_rope(self, qkv, q_norm, k_norm, cos, sin, heads, head_dim, rope_half, eps=1e-5, grouped=0, split_half=1,
+                 out_dtype=None):
+        import torch
+        out_dtype = out_dtype or qkv.dtype
+        seq = qkv.shape[0]
+        q, k, v = (torch.empty((seq, heads, head_dim), dtype=out_dtype, device=qkv.device) for _ in range(3))
+        call("h3b_qkv_rope_dev", self.h, ptr(qkv), _dt(qkv), ptr(q_norm), ptr(k_norm), ptr(cos), ptr(sin), seq, heads,
+             head_dim, rope_half, eps, grouped, split_half, ptr(q), ptr(k), ptr(v), _dt(q))
+        return q, k, v
+
+    def cast(self, x, dtype):
+        import torch
+        out = torch.empty(x.shape, dtype=dtype, device=x.device)
+        call("h3b_cast_dev", self.h, ptr(x), _dt(x), ptr(out), _dt(out), x.numel())
+        return out
+
+    # ---- linears
+    def gemm_i8(self, weight: Weight, x_i8, act_scales, *, kind=EPI_PLAIN, out_dtype=None, residual=None,
+                modulation=None, row_map=None, slots=0, gate_slot=0, out=None):
+        import torch
+        out_dtype = out_dtype or torch.float32
+        m = x_i8.shape[0]
+        n_out = weight.n // 2 if kind == EPI_SWIGLU else weight.n
+        if out is None:
+            out = torch.empty((m, n_out), dtype=out_dtype, device=x_i8.device)
+        e = _l.GemmEpi(kind, _dt(out), ptr(residual), ptr(modulation), ptr(row_map), slots, gate_slot)
+        call("h3b_gemm_i8_dev", self.h, weight.h, ptr(x_i8), ptr(act_scales), m, ptr(out), C.byref(e))
+        return out
+
+    def gemm_i8_dequant_f32_w_act_dev(self, weight: Weight, x_f32, convrot_gs=0, epi: _l.DitGemmEpi | None = None):
+        import torch
+        m = x_f32.shape[0]
+        n_out = weight.n // 2 if (epi is not None and epi.swiglu) else weight.n
+        y = torch.empty((m, n_out), dtype=torch.float32, device=x_f32.device)
+        backend = C.create_string_buffer(32)
+        call("h3_cuda_gemm_i8_dequant_f32_w_act_dev_epi", self.h, weight.h, ptr(x_f32), convrot_gs, m, ptr(y), None,
+             None, backend, 32, C.byref(epi) if epi is not None else None)
+        return y
+
+    # ---- attention
+    def sdpa_bf16(self, q, k, v, scale=None, out=None):
+        """q [lq,H,128], k/v [lk,H,128] bf16 views whose last two dims are contiguous -> [lq, H*128] bf16."""
+        import torch
+        lq, heads, hd = q.shape
+        lk = k.shape[0]
+        scale = float(scale if scale is not None else hd ** -0.5)
+        if out is None:
+            out = torch.empty((lq, heads * hd), dtype=torch.bfloat16, device=q.device)
+        call("h3b_sdpa_bf16_dev", self.h, ptr(q), q.stride(0), ptr(k), k.stride(0), ptr(v), v.stride(0), lq, lk, heads,
+             hd, scale, ptr(out), out.stride(0))
+        return out
+
+    def sdpa_f16_dev(self, q, k, v, scale=None):
+        import torch
+        seq, heads, hd = q.shape
+        out = torch.empty((seq, heads * hd), dtype=torch.float32, device=q.device)
+        call("h3_cuda_sdpa_f16_dev", self.h, ptr(q), ptr(k), ptr(v), seq, heads, hd,
+             float(scale if scale is not None else hd ** -0.5), ptr(out), None)
+        return out
+
+    # ---- NVFP4
+    def quantize_act_nvfp4(self, x):
+        import torch
+        m, k = x.shape
+        packed = torch.zeros((m, k // 2), dtype=torch.uint8, device=x.device)
+        sf = torch.zeros(int(load().h3_cuda_nvfp4_sf_bytes(m, k)), dtype=torch.uint8, device=x.device)
+        call("h3_cuda_quantize_act_nvfp4_dev", self.h, ptr(x), m, k, ptr(packed), ptr(sf))
+        return packed, sf
+
+    # ---- host-buffer forms (numpy in, numpy out)
+    def adaln_f32(self, x, norm_w, modulation, row_map, slots, shift_slot, scale_slot, eps=1e-5):
+        import numpy as np
+        x = np.ascontiguousarray(x, np.float32)
+        modulation = np.ascontiguousarray(modulation, np.float32)
+        out = np.empty_like(x)
+        call("h3_cuda_adaln_f32", self.h, ptr(x), ptr(np.ascontiguousarray(norm_w, np.float32)), ptr(modulation),
+             ptr(row_map), x.shape[0], x.shape[1], slots, modulation.shape[0], shift_slot, scale_slot, eps, ptr(out),
+             None)
+        return out
+
+
+def ulysses_validate(heads, packed_align, tp, ulysses, ring):
+    """h3_ulysses_validate: returns (ok, message)."""
+    err = C.create_string_buffer(_l.ERR_LEN)
+    ok = load().h3_ulysses_validate(heads, packed_align, tp, ulysses, ring, err, _l.ERR_LEN)
+    return bool(ok), err.value.decode()
+
+
+def ulysses_pad_seq(seq, align=64):
+    return int(load().h3_ulysses_pad_seq(seq, align))
+
+
+def ulysses_local_rows(seq_pad, ulysses, rank):
+    return int(load().h3_ulysses_local_rows(seq_pad, ulysses, rank))

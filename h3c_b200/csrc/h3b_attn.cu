@@ -1,0 +1,394 @@
+// Flash-style attention for head_dim 128 on tcgen05: softmax(Q K^T * scale) V, bf16
+// operands, f32 scores / accumulation, non-causal, separate query and key counts
+// (self-attention and the rectangular cross-attention).  Same math as the
+// reference's h3_dit_w4a8_sdpa_f32 (h3_dit_w4a8.c:3073-3116) evaluated tile by tile
+// with a running maximum.
+//
+// One CTA per (128-query tile, head):
+//   warp 0     TMA: Q once, then K and V tiles of 128 keys into two-deep rings
+//   warp 1     MMA: S = Q K^T (128x128x128) into one of two TMEM score buffers,
+//              issued one tile ahead; O += P V (128x128x128) into a TMEM accumulator
+//   warps 2-5  softmax: one query row per thread.  Pass 1 reads the scores from TMEM
+//              for the row maximum, pass 2 re-reads them, exponentiates and writes P
+//              (bf16) to shared memory in the MMA's swizzled layout.  The accumulator
+//              is rescaled only when the running maximum grew by more than 2^8.
+#include <cuda_bf16.h>
+
+#include "h3b_internal.h"
+#include "h3b_ptx.cuh"
+
+namespace h3b {
+
+namespace attn {
+constexpr int BQ = 128, BKV = 128, HD = 128;
+constexpr int SLAB = BQ * 64 * 2;        // 128 rows x 64 bf16: one 128-byte-swizzled slab (16 KiB)
+constexpr int TILE = 2 * SLAB;           // 128 x 128 bf16 tile (32 KiB)
+constexpr int THREADS = 192;
+constexpr int TMEM_COLS = 512;
+constexpr uint32_t S_COL0 = 0, S_COL1 = 128, O_COL = 256;
+// shared memory: Q | K0 K1 | V0 V1 | P | barriers
+constexpr size_t SMEM_BYTES = 1024 + 6 * (size_t)TILE + 256;
+}  // namespace attn
+
+struct AttnParams {
+    CUtensorMap tmap_q, tmap_k, tmap_v;   // 3-D {d, head, row}, box {64, 1, 128}
+    __nv_bfloat16 *out;
+    size_t o_stride;                      // elements between output rows
+    int lq, lk, heads;
+    float scale_log2;                     // scale * log2(e)
+    int *status;
+};
+
+__device__ __forceinline__ float ex2_approx(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
+__global__ void __launch_bounds__(attn::THREADS, 1) k_attn_bf16(const __grid_constant__ AttnParams p) {
+    using namespace attn;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    uint8_t *sQ = smem, *sK = smem + TILE, *sV = smem + 3 * TILE, *sP = smem + 5 * TILE;
+    uint64_t *bars = reinterpret_cast<uint64_t *>(smem + 6 * TILE);
+    uint64_t *q_full = bars, *k_full = bars + 1, *v_full = bars + 3, *k_empty = bars + 5, *v_empty = bars + 7,
+             *s_full = bars + 9, *s_empty = bars + 11, *p_full = bars + 13, *pv_done = bars + 14;
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 15);
+    volatile int *abort_word = reinterpret_cast<volatile int *>(tmem_slot + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int q0 = blockIdx.x * BQ, head = blockIdx.y;
+    const int n_kv = (p.lk + BKV - 1) / BKV;
+
+    if (threadIdx.x == 0) {
+        mbar_init(q_full, 1);
+        for (int i = 0; i < 2; i++) {
+            mbar_init(&k_full[i], 1);
+            mbar_init(&v_full[i], 1);
+            mbar_init(&k_empty[i], 1);
+            mbar_init(&v_empty[i], 1);
+            mbar_init(&s_full[i], 1);
+            mbar_init(&s_empty[i], 4);
+        }
+        mbar_init(p_full, 4);
+        mbar_init(pv_done, 1);
+        *abort_word = 0;
+        mbar_fence_init();
+        tma_prefetch_desc(&p.tmap_q);
+        tma_prefetch_desc(&p.tmap_k);
+        tma_prefetch_desc(&p.tmap_v);
+    }
+    if (warp == 1) {
+        tmem_alloc(tmem_slot, TMEM_COLS);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            mbar_expect_tx(q_full, TILE);
+            tma_load_3d(sQ, &p.tmap_q, q_full, 0, head, q0);
+            tma_load_3d(sQ + SLAB, &p.tmap_q, q_full, 64, head, q0);
+            for (int j = 0; j < n_kv; j++) {
+                const int st = j & 1;
+                const uint32_t ph = ((j >> 1) & 1) ^ 1;
+                if (!mbar_wait(&k_empty[st], ph, abort_word, p.status, H3B_ST_TIMEOUT_EMPTY)) break;
+                mbar_expect_tx(&k_full[st], TILE);
+                tma_load_3d(sK + st * TILE, &p.tmap_k, &k_full[st], 0, head, j * BKV);
+                tma_load_3d(sK + st * TILE + SLAB, &p.tmap_k, &k_full[st], 64, head, j * BKV);
+                if (!mbar_wait(&v_empty[st], ph, abort_word, p.status, H3B_ST_TIMEOUT_EMPTY)) break;
+                mbar_expect_tx(&v_full[st], TILE);
+                tma_load_3d(sV + st * TILE, &p.tmap_v, &v_full[st], 0, head, j * BKV);
+                tma_load_3d(sV + st * TILE + SLAB, &p.tmap_v, &v_full[st], 64, head, j * BKV);
+            }
+        }
+        __syncwarp();
+    } else if (warp == 1) {
+        if (lane == 0) {
+            // S = Q K^T : both operands K-major (d contiguous).  O += P V : P K-major (keys contiguous),
+            // V as stored ([key][d], d contiguous) is the N-major form of the B operand.
+            constexpr uint32_t idesc_s = umma_idesc(1, 1, 1, BQ, BKV, 0, 0);
+            constexpr uint32_t idesc_o = umma_idesc(1, 1, 1, BQ, HD, 0, 1);
+            const uint32_t q_addr = smem_u32(sQ), p_addr = smem_u32(sP);
+            auto issue_s = [&](int j) -> bool {
+                const int st = j & 1;
+                if (!mbar_wait(&k_full[st], (j >> 1) & 1, abort_word, p.status, H3B_ST_TIMEOUT_FULL)) return false;
+                if (!mbar_wait(&s_empty[st], ((j >> 1) & 1) ^ 1, abort_word, p.status, H3B_ST_TIMEOUT_TMEM_EMPTY))
+                    return false;
+                tc_fence_after();
+                const uint32_t k_addr = smem_u32(sK + st * TILE);
+                const uint32_t d_tmem = tmem_base + (st ? S_COL1 : S_COL0);
+#pragma unroll
+                for (int k = 0; k < HD / 16; k++) {
+                    const uint32_t off = (uint32_t)(k >> 2) * SLAB + (uint32_t)(k & 3) * 32;
+                    umma_f16_ss(d_tmem, umma_desc_k_sw128(q_addr + off), umma_desc_k_sw128(k_addr + off), idesc_s,
+                                (uint32_t)(k != 0));
+                }
+                tc_commit(&s_full[st]);
+                tc_commit(&k_empty[st]);
+                return true;
+            };
+            bool ok = mbar_wait(q_full, 0, abort_word, p.status, H3B_ST_TIMEOUT_FULL);
+            if (ok) ok = issue_s(0);
+            for (int j = 0; ok && j < n_kv; j++) {
+                if (j + 1 < n_kv && !issue_s(j + 1)) break;
+                const int st = j & 1;
+                if (!mbar_wait(p_full, j & 1, abort_word, p.status, H3B_ST_TIMEOUT_OTHER)) break;
+                if (!mbar_wait(&v_full[st], (j >> 1) & 1, abort_word, p.status, H3B_ST_TIMEOUT_FULL)) break;
+                tc_fence_after();
+                const uint32_t v_addr = smem_u32(sV + st * TILE);
+#pragma unroll
+                for (int k = 0; k < BKV / 16; k++) {
+                    const uint32_t a_off = (uint32_t)(k >> 2) * SLAB + (uint32_t)(k & 3) * 32;
+                    umma_f16_ss(tmem_base + O_COL, umma_desc_k_sw128(p_addr + a_off),
+                                umma_desc_mn_sw128(v_addr + (uint32_t)k * 2048, SLAB, 1024), idesc_o,
+                                (uint32_t)((j | k) != 0));
+                }
+                tc_commit(&v_empty[st]);
+                tc_commit(pv_done);
+            }
+        }
+        __syncwarp();
+    } else {
+        // ------------------------------------------------------------ softmax
+        const int q = warp & 3;
+        const int r = q * 32 + lane;                       // query row inside the tile
+        const uint32_t lane_base = (uint32_t)(q * 32) << 16;
+        float m_run = -INFINITY, l_run = 0.0f;
+        bool ok = true;
+        for (int j = 0; j < n_kv && ok; j++) {
+            const int st = j & 1;
+            const uint32_t s_addr = tmem_base + lane_base + (st ? S_COL1 : S_COL0);
+            const int valid = min(BKV, p.lk - j * BKV);    // keys of this tile that exist
+            ok = mbar_wait(&s_full[st], (j >> 1) & 1, abort_word, p.status, H3B_ST_TIMEOUT_TMEM_FULL);
+            if (!ok) break;
+            tc_fence_after();
+            // pass 1: row maximum
+            float mx = -INFINITY;
+#pragma unroll 1
+            for (int ch = 0; ch < BKV / 32; ch++) {
+                uint32_t v[32];
+                tmem_ld_32x32b_x32(s_addr + ch * 32, v);
+                tmem_ld_wait();
+#pragma unroll
+                for (int i = 0; i < 32; i++)
+                    if (ch * 32 + i < valid) mx = fmaxf(mx, __uint_as_float(v[i]));
+            }
+            const float m_new = fmaxf(m_run, mx * p.scale_log2);
+            float alpha = 1.0f;
+            const bool grow_me = (m_new - m_run) > 8.0f;   // also true on the first tile (m_run = -inf)
+            if (grow_me) {
+                alpha = ex2_approx(m_run - m_new);         // 0 on the first tile
+                m_run = m_new;
+                l_run *= alpha;
+            }
+            // P's buffer and the accumulator are free once the previous P V product has completed
+            if (j > 0) {
+                ok = mbar_wait(pv_done, (j - 1) & 1, abort_word, p.status, H3B_ST_TIMEOUT_OTHER);
+                if (!ok) break;
+                tc_fence_after();
+                if (__any_sync(0xffffffffu, grow_me)) {
+#pragma unroll 1
+                    for (int ch = 0; ch < HD / 16; ch++) {
+                        uint32_t o[16];
+                        tmem_ld_32x32b_x16(tmem_base + lane_base + O_COL + ch * 16, o);
+                        tmem_ld_wait();
+#pragma unroll
+                        for (int i = 0; i < 16; i++) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+                        tmem_st_32x32b_x16(tmem_base + lane_base + O_COL + ch * 16, o);
+                    }
+                    tmem_st_wait();
+                }
+            }
+            // pass 2: probabilities -> bf16 -> shared memory (K-major, 128-byte swizzle, two 64-key slabs)
+            float l_add = 0.0f;
+#pragma unroll 1
+            for (int ch = 0; ch < BKV / 32; ch++) {
+                uint32_t v[32];
+                tmem_ld_32x32b_x32(s_addr + ch * 32, v);
+                tmem_ld_wait();
+                uint32_t packed[16];
+#pragma unroll
+                for (int i = 0; i < 32; i += 2) {
+                    float p0 = (ch * 32 + i < valid) ? ex2_approx(fmaf(__uint_as_float(v[i]), p.scale_log2, -m_run)) : 0.0f;
+                    float p1 = (ch * 32 + i + 1 < valid) ? ex2_approx(fmaf(__uint_as_float(v[i + 1]), p.scale_log2, -m_run)) : 0.0f;
+                    l_add += p0 + p1;
+                    __nv_bfloat162 h = __floats2bfloat162_rn(p0, p1);
+                    packed[i >> 1] = *reinterpret_cast<uint32_t *>(&h);
+                }
+                // 32 keys = four 16-byte chunks of this row
+                uint8_t *slab = sP + (ch >> 1) * SLAB + r * 128;
+#pragma unroll
+                for (int c = 0; c < 4; c++) {
+                    const int chunk = ((ch & 1) * 4 + c) ^ (r & 7);
+                    *reinterpret_cast<uint4 *>(slab + chunk * 16) =
+                        make_uint4(packed[4 * c], packed[4 * c + 1], packed[4 * c + 2], packed[4 * c + 3]);
+                }
+            }
+            l_run += l_add;
+            // scores consumed: the buffer may be overwritten by the tile after next
+            tc_fence_before();
+            fence_proxy_async_smem();
+            __syncwarp();
+            if (lane == 0) {
+                mbar_arrive(&s_empty[st]);
+                mbar_arrive(p_full);
+            }
+        }
+        // ---- final: O / l -> bf16 -> global
+        if (ok) ok = mbar_wait(pv_done, (n_kv - 1) & 1, abort_word, p.status, H3B_ST_TIMEOUT_OTHER);
+        tc_fence_after();
+        const int row = q0 + r;
+        const float inv_l = 1.0f / l_run;
+        __nv_bfloat16 *dst = p.out + (size_t)row * p.o_stride + (size_t)head * HD;
+#pragma unroll 1
+        for (int ch = 0; ch < HD / 32; ch++) {
+            uint32_t o[32];
+            tmem_ld_32x32b_x32(tmem_base + lane_base + O_COL + ch * 32, o);
+            tmem_ld_wait();
+            if (ok && row < p.lq) {
+#pragma unroll
+                for (int i = 0; i < 32; i += 8) {
+                    uint4 raw;
+                    __nv_bfloat162 *h = reinterpret_cast<__nv_bfloat162 *>(&raw);
+#pragma unroll
+                    for (int t = 0; t < 4; t++)
+                        h[t] = __floats2bfloat162_rn(__uint_as_float(o[i + 2 * t]) * inv_l,
+                                                     __uint_as_float(o[i + 2 * t + 1]) * inv_l);
+                    *reinterpret_cast<uint4 *>(dst + ch * 32 + i) = raw;
+                }
+            }
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, TMEM_COLS);
+    }
+}
+
+static int make_map(CUtensorMap *map, const void *base, size_t stride_elems, size_t rows, size_t heads, char *error,
+                    size_t error_size, const char *what) {
+    int rc = h3b_encode_tmap_3d(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, base, attn::HD, heads, rows,
+                                attn::HD * 2, stride_elems * 2, 64, 1, 128, CU_TENSOR_MAP_SWIZZLE_128B);
+    if (rc != 0) return fail(error, error_size, "sdpa: cuTensorMapEncodeTiled(%s) failed (%d)", what, rc);
+    return 1;
+}
+
+int launch_sdpa_bf16(h3_cuda *cuda, const void *q, size_t qs, const void *k, size_t ks, const void *v, size_t vs,
+                     size_t lq, size_t lk, size_t heads, size_t hd, float scale, void *out, size_t os, char *error,
+                     size_t error_size) {
+    if (!cuda || !q || !k || !v || !out || !lq || !lk || !heads) return fail(error, error_size, "invalid sdpa args");
+    if (hd != attn::HD) return fail(error, error_size, "sdpa: head_dim %zu unsupported (128 only)", hd);
+    if ((qs % 8) || (ks % 8) || (vs % 8) || (os % 8) || ((uintptr_t)q & 15) || ((uintptr_t)k & 15) ||
+        ((uintptr_t)v & 15) || ((uintptr_t)out & 15))
+        return fail(error, error_size, "sdpa: pointers must be 16-byte aligned and row strides multiples of 8 elements");
+    if (qs < heads * hd || ks < heads * hd || vs < heads * hd || os < heads * hd)
+        return fail(error, error_size, "sdpa: row stride smaller than heads*head_dim");
+    if (lq > 0x7fffff00u || lk > 0x7fffff00u || heads > 65535) return fail(error, error_size, "sdpa: shape too large");
+    if (!(scale > 0.0f)) return fail(error, error_size, "sdpa: scale must be positive");
+    AttnParams p;
+    memset(&p, 0, sizeof(p));
+    if (!make_map(&p.tmap_q, q, qs, lq, heads, error, error_size, "Q") ||
+        !make_map(&p.tmap_k, k, ks, lk, heads, error, error_size, "K") ||
+        !make_map(&p.tmap_v, v, vs, lk, heads, error, error_size, "V"))
+        return 0;
+    p.out = (__nv_bfloat16 *)out; p.o_stride = os; p.lq = (int)lq; p.lk = (int)lk; p.heads = (int)heads;
+    p.scale_log2 = scale * 1.4426950408889634f;
+    p.status = cuda->d_status;
+    H3B_CUDA_OK(cudaFuncSetAttribute(k_attn_bf16, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)attn::SMEM_BYTES),
+                "sdpa smem attribute");
+    dim3 grid((unsigned)ceil_div(lq, attn::BQ), (unsigned)heads);
+    k_attn_bf16<<<grid, attn::THREADS, attn::SMEM_BYTES, cuda->op_stream>>>(p);
+    cuda->launches++;
+    H3B_CUDA_OK(cudaGetLastError(), "k_attn_bf16 launch");
+    return 1;
+}
+
+}  // namespace h3b
+
+using namespace h3b;
+
+static const char *g_last_backend = "none";
+
+extern "C" {
+
+int h3b_sdpa_bf16_dev(h3_cuda *cuda, const void *d_q, size_t q_stride, const void *d_k, size_t k_stride,
+                      const void *d_v, size_t v_stride, size_t lq, size_t lk, size_t heads, size_t head_dim,
+                      float scale, void *d_out, size_t o_stride, char *error, size_t error_size) {
+    int ok = launch_sdpa_bf16(cuda, d_q, q_stride, d_k, k_stride, d_v, v_stride, lq, lk, heads, head_dim, scale, d_out,
+                              o_stride, error, error_size);
+    if (ok) g_last_backend = "tcgen05_flash_bf16";
+    return ok;
+}
+
+const char *h3_cuda_sdpa_backend_name(void) { return "tcgen05_flash_bf16"; }
+const char *h3_cuda_sdpa_last_backend_name(void) { return g_last_backend; }
+
+// F32 tensors in and out: cast to bf16 staging, run the bf16 kernel, cast back.
+int h3_cuda_sdpa_f16_dev_ex(h3_cuda *cuda, const float *d_query, const float *d_key, const float *d_value,
+                            size_t seq, size_t heads, size_t head_dim, float scale, int attn_window, float *d_out,
+                            double *sdpa_ms, char *backend_out, size_t backend_out_size, char *error,
+                            size_t error_size) {
+    if (!cuda || !d_query || !d_key || !d_value || !d_out || !seq || !heads || !head_dim)
+        return fail(error, error_size, "invalid sdpa args");
+    if (attn_window != 0) return fail(error, error_size, "sdpa: windowed attention (attn_window=%d) is not supported", attn_window);
+    const size_t n = seq * heads * head_dim;
+    if (!grow(cuda, &cuda->attn, &cuda->attn_bytes, 4 * n * 2, error, error_size)) return 0;
+    __nv_bfloat16 *q = (__nv_bfloat16 *)cuda->attn, *k = q + n, *v = k + n, *o = v + n;
+    Timer t(cuda, sdpa_ms);
+    int ok = h3b_cast_dev(cuda, d_query, H3B_F32, q, H3B_BF16, n, error, error_size) &&
+             h3b_cast_dev(cuda, d_key, H3B_F32, k, H3B_BF16, n, error, error_size) &&
+             h3b_cast_dev(cuda, d_value, H3B_F32, v, H3B_BF16, n, error, error_size) &&
+             h3b_sdpa_bf16_dev(cuda, q, heads * head_dim, k, heads * head_dim, v, heads * head_dim, seq, seq, heads,
+                               head_dim, scale, o, heads * head_dim, error, error_size) &&
+             h3b_cast_dev(cuda, o, H3B_BF16, d_out, H3B_F32, n, error, error_size);
+    t.stop();
+    if (backend_out && backend_out_size) snprintf(backend_out, backend_out_size, "tcgen05_flash_bf16");
+    return ok;
+}
+
+int h3_cuda_sdpa_f16_dev(h3_cuda *cuda, const float *d_query, const float *d_key, const float *d_value, size_t seq,
+                         size_t heads, size_t head_dim, float scale, float *d_out, double *sdpa_ms, char *error,
+                         size_t error_size) {
+    return h3_cuda_sdpa_f16_dev_ex(cuda, d_query, d_key, d_value, seq, heads, head_dim, scale, 0, d_out, sdpa_ms, NULL,
+                                   0, error, error_size);
+}
+
+int h3_cuda_sdpa_f32_dev(h3_cuda *cuda, const float *d_query, const float *d_key, const float *d_value, size_t seq,
+                         size_t heads, size_t head_dim, float scale, float *d_out, double *sdpa_ms, char *error,
+                         size_t error_size) {
+    return h3_cuda_sdpa_f16_dev_ex(cuda, d_query, d_key, d_value, seq, heads, head_dim, scale, 0, d_out, sdpa_ms, NULL,
+                                   0, error, error_size);
+}
+
+int h3_cuda_qkv_rope_sdpa_f16_dev(h3_cuda *cuda, const float *d_qkv, const float *d_q_norm, const float *d_k_norm,
+                                  const float *d_rope_cos, const float *d_rope_sin, size_t seq, size_t heads,
+                                  size_t head_dim, size_t rope_half, float epsilon, float scale, int attn_window,
+                                  float *d_attn_out, double *rope_ms, double *sdpa_ms, char *backend_out,
+                                  size_t backend_out_size, char *error, size_t error_size) {
+    if (!cuda || !d_qkv || !d_attn_out || !seq || !heads || !head_dim) return fail(error, error_size, "invalid qkv_rope_sdpa args");
+    if (attn_window != 0) return fail(error, error_size, "sdpa: windowed attention (attn_window=%d) is not supported", attn_window);
+    const size_t n = seq * heads * head_dim;
+    if (!grow(cuda, &cuda->attn, &cuda->attn_bytes, 4 * n * 2, error, error_size)) return 0;
+    __nv_bfloat16 *q = (__nv_bfloat16 *)cuda->attn, *k = q + n, *v = k + n, *o = v + n;
+    Timer tr(cuda, rope_ms);
+    if (!h3b_qkv_rope_dev(cuda, d_qkv, H3B_F32, d_q_norm, d_k_norm, d_rope_cos, d_rope_sin, seq, heads, head_dim,
+                          rope_half, epsilon, 0, 1, q, k, v, H3B_BF16, error, error_size))
+        return 0;
+    tr.stop();
+    Timer ts(cuda, sdpa_ms);
+    int ok = h3b_sdpa_bf16_dev(cuda, q, heads * head_dim, k, heads * head_dim, v, heads * head_dim, seq, seq, heads,
+                               head_dim, scale, o, heads * head_dim, error, error_size) &&
+             h3b_cast_dev(cuda, o, H3B_BF16, d_attn_out, H3B_F32, n, error, error_size);
+    ts.stop();
+    if (backend_out && backend_out_size) snprintf(backend_out, backend_out_size, "tcgen05_flash_bf16");
+    return ok;
+}
+
+}  // extern "C"

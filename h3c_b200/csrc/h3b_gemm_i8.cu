@@ -1,0 +1,370 @@
+// INT8 x INT8 -> INT32 GEMM on the 5th-generation tensor cores (tcgen05, kind::i8)
+// with the DiT epilogues fused:  Y = epi( a[m] * s[n] * sum_k X[m,k] W[n,k] ).
+//
+// Persistent kernel, one CTA per SM, 128 x 256 output tile, K in 128-byte blocks:
+//   warp 0     TMA producer: A (activation codes) and B (weight) tiles into a
+//              4-stage shared-memory ring, 128-byte swizzle
+//   warp 1     MMA issuer: four 128x256x32 tcgen05.mma per stage into one of two
+//              256-column TMEM accumulators; tcgen05.commit frees the stage
+//   warps 2-5  epilogue: tcgen05.ld the finished accumulator (one output row per
+//              thread), scale, apply gate+residual / SwiGLU / tanh-GELU, store.
+//              Runs while the MMA warp fills the other accumulator.
+// Accumulators are exact int32, so the integer part is bit-identical to
+// h3_w4a8_gemm_i8_dequant_f32 (h3_w4a8_dequant.c:692); the float part follows the
+// reference's operation order (a * s) * (float)acc and h3_dit_fused_epi.h:87-141.
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
+#include "h3b_internal.h"
+#include "h3b_ptx.cuh"
+
+namespace h3b {
+
+namespace gemm {
+constexpr int BM = 128;          // rows of X per tile
+constexpr int BN = 256;          // rows of W per tile (TMEM columns per accumulator)
+constexpr int BK = 128;          // int8 elements (= bytes) of K per stage
+constexpr int STAGES = 4;
+constexpr int A_BYTES = BM * BK;             // 16 KiB
+constexpr int B_BYTES = BN * BK;             // 32 KiB
+constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+constexpr int THREADS = 192;
+constexpr int TMEM_COLS = 512;
+constexpr int GROUP_M = 8;       // rasterisation: bands of 8 row-tiles share the weight tiles in L2
+constexpr size_t SMEM_BYTES = 1024 /*alignment slack*/ + (size_t)STAGES * STAGE_BYTES + 256;
+}  // namespace gemm
+
+struct GemmParams {
+    CUtensorMap tmap_a;   // X codes  [M, K] int8, box 128 (k) x 128 (m)
+    CUtensorMap tmap_b;   // W        [N, K] int8, box 128 (k) x 128 (n)
+    int M, N, K;          // N = rows of W
+    int n_out;            // columns of Y (N, or N/2 for SwiGLU)
+    int m_tiles, n_tiles, k_blocks;
+    int swiglu;
+    const float *act_scale;   // [M]
+    const float *s_channel;   // [N]
+    void *y;
+    const void *residual;     // gate: [M, n_out] in the output type
+    const float *mod;         // gate: [mod_rows, slots, n_out] or NULL
+    const uint32_t *row_map;  // gate: [M] or NULL
+    int slots, gate_slot;
+    int *status;
+};
+
+__device__ __forceinline__ void tile_coords(int tile, int m_tiles, int n_tiles, int &mt, int &nt) {
+    const int per_group = gemm::GROUP_M * n_tiles;
+    const int g = tile / per_group;
+    const int first_m = g * gemm::GROUP_M;
+    const int gm = min(gemm::GROUP_M, m_tiles - first_m);
+    const int local = tile - g * per_group;
+    mt = first_m + local % gm;
+    nt = local / gm;
+}
+
+__device__ __forceinline__ float gelu_tanh_dev(float v) {   // h3_vision_cuda.c:365-371
+    float inner = 0.7978845608028654f * (v + 0.044715f * v * v * v);
+    if (inner <= -10.0f) return 0.0f;
+    if (inner >= 10.0f) return v;
+    return 0.5f * v * (1.0f + tanhf(inner));
+}
+
+template <typename T> struct OutTraits;
+template <> struct OutTraits<float> {
+    static constexpr int VEC = 4;
+    __device__ static void store(float *p, const float *v) { *reinterpret_cast<float4 *>(p) = make_float4(v[0], v[1], v[2], v[3]); }
+    __device__ static void load(const float *p, float *v) {
+        float4 t = *reinterpret_cast<const float4 *>(p);
+        v[0] = t.x; v[1] = t.y; v[2] = t.z; v[3] = t.w;
+    }
+};
+template <> struct OutTraits<__nv_bfloat16> {
+    static constexpr int VEC = 8;
+    __device__ static void store(__nv_bfloat16 *p, const float *v) {
+        uint4 raw;
+        __nv_bfloat162 *h = reinterpret_cast<__nv_bfloat162 *>(&raw);
+#pragma unroll
+        for (int i = 0; i < 4; i++) h[i] = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
+        *reinterpret_cast<uint4 *>(p) = raw;
+    }
+    __device__ static void load(const __nv_bfloat16 *p, float *v) {
+        uint4 raw = *reinterpret_cast<const uint4 *>(p);
+        const __nv_bfloat162 *h = reinterpret_cast<const __nv_bfloat162 *>(&raw);
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            float2 f = __bfloat1622float2(h[i]);
+            v[2 * i] = f.x; v[2 * i + 1] = f.y;
+        }
+    }
+};
+template <> struct OutTraits<__half> {
+    static constexpr int VEC = 8;
+    __device__ static void store(__half *p, const float *v) {
+        uint4 raw;
+        __half2 *h = reinterpret_cast<__half2 *>(&raw);
+#pragma unroll
+        for (int i = 0; i < 4; i++) h[i] = __floats2half2_rn(v[2 * i], v[2 * i + 1]);
+        *reinterpret_cast<uint4 *>(p) = raw;
+    }
+    __device__ static void load(const __half *p, float *v) {
+        uint4 raw = *reinterpret_cast<const uint4 *>(p);
+        const __half2 *h = reinterpret_cast<const __half2 *>(&raw);
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            float2 f = __half22float2(h[i]);
+            v[2 * i] = f.x; v[2 * i + 1] = f.y;
+        }
+    }
+};
+template <> struct OutTraits<int32_t> {
+    static constexpr int VEC = 4;
+    __device__ static void store(int32_t *p, const float *v) { (void)p; (void)v; }
+    __device__ static void load(const int32_t *p, float *v) { (void)p; (void)v; }
+};
+
+template <int EPI, typename OutT>
+__global__ void __launch_bounds__(gemm::THREADS, 1) k_gemm_i8(const __grid_constant__ GemmParams p) {
+    using namespace gemm;
+    extern __shared__ uint8_t smem_raw[];
+    // 1024-byte alignment: required by the 128-byte swizzle pattern of TMA and the MMA descriptors
+    uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    uint64_t *bars = reinterpret_cast<uint64_t *>(smem + (size_t)STAGES * STAGE_BYTES);
+    uint64_t *full = bars, *empty = bars + STAGES, *tmem_full = bars + 2 * STAGES, *tmem_empty = bars + 2 * STAGES + 2;
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 2 * STAGES + 4);
+    volatile int *abort_word = reinterpret_cast<volatile int *>(tmem_slot + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int total_tiles = p.m_tiles * p.n_tiles;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; s++) {
+            mbar_init(&full[s], 1);
+            mbar_init(&empty[s], 1);
+        }
+        for (int b = 0; b < 2; b++) {
+            mbar_init(&tmem_full[b], 1);
+            mbar_init(&tmem_empty[b], 4);   // one arrival per epilogue warp
+        }
+        *abort_word = 0;
+        mbar_fence_init();
+        tma_prefetch_desc(&p.tmap_a);
+        tma_prefetch_desc(&p.tmap_b);
+    }
+    if (warp == 1) {
+        tmem_alloc(tmem_slot, TMEM_COLS);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        // ------------------------------------------------------- TMA producer
+        if (lane == 0) {
+            int s = 0;
+            uint32_t ph = 0;
+            for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
+                int mt, nt;
+                tile_coords(tile, p.m_tiles, p.n_tiles, mt, nt);
+                const int m0 = mt * BM;
+                const int n0 = p.swiglu ? nt * (BN / 2) : nt * BN;
+                const int n1 = p.swiglu ? p.N / 2 + n0 : n0 + BN / 2;
+                for (int kb = 0; kb < p.k_blocks; kb++) {
+                    if (!mbar_wait(&empty[s], ph ^ 1, abort_word, p.status, H3B_ST_TIMEOUT_EMPTY)) break;
+                    uint8_t *a_dst = smem + (size_t)s * STAGE_BYTES;
+                    uint8_t *b_dst = a_dst + A_BYTES;
+                    mbar_expect_tx(&full[s], STAGE_BYTES);
+                    tma_load_2d(a_dst, &p.tmap_a, &full[s], kb * BK, m0);
+                    tma_load_2d(b_dst, &p.tmap_b, &full[s], kb * BK, n0);
+                    tma_load_2d(b_dst + B_BYTES / 2, &p.tmap_b, &full[s], kb * BK, n1);
+                    if (++s == STAGES) { s = 0; ph ^= 1; }
+                }
+                if (*abort_word) break;
+            }
+        }
+        __syncwarp();
+    } else if (warp == 1) {
+        // --------------------------------------------------------- MMA issuer
+        if (lane == 0) {
+            constexpr uint32_t idesc = umma_idesc(2 /*s32*/, 1 /*s8*/, 1 /*s8*/, BM, BN, 0, 0);
+            int s = 0;
+            uint32_t ph = 0;
+            int it = 0;
+            for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, it++) {
+                const int buf = it & 1;
+                if (!mbar_wait(&tmem_empty[buf], ((it >> 1) & 1) ^ 1, abort_word, p.status, H3B_ST_TIMEOUT_TMEM_EMPTY))
+                    break;
+                tc_fence_after();
+                const uint32_t d_tmem = tmem_base + (uint32_t)buf * BN;
+                for (int kb = 0; kb < p.k_blocks; kb++) {
+                    if (!mbar_wait(&full[s], ph, abort_word, p.status, H3B_ST_TIMEOUT_FULL)) break;
+                    tc_fence_after();
+                    const uint32_t a_addr = smem_u32(smem + (size_t)s * STAGE_BYTES);
+                    const uint64_t a_desc = umma_desc_k_sw128(a_addr);
+                    const uint64_t b_desc = umma_desc_k_sw128(a_addr + A_BYTES);
+#pragma unroll
+                    for (int k = 0; k < BK / 32; k++)
+                        umma_i8_ss(d_tmem, a_desc + (uint64_t)(k * 2), b_desc + (uint64_t)(k * 2), idesc,
+                                   (uint32_t)((kb | k) != 0));
+                    tc_commit(&empty[s]);   // stage is free once these MMAs have read it
+                    if (++s == STAGES) { s = 0; ph ^= 1; }
+                }
+                if (*abort_word) break;
+                tc_commit(&tmem_full[buf]);
+            }
+        }
+        __syncwarp();
+    } else {
+        // ----------------------------------------------------------- epilogue
+        const int q = warp & 3;                 // TMEM lane quarter this warp may read
+        const uint32_t lane_base = (uint32_t)(q * 32) << 16;
+        OutT *y = reinterpret_cast<OutT *>(p.y);
+        const OutT *res = reinterpret_cast<const OutT *>(p.residual);
+        constexpr int VEC = OutTraits<OutT>::VEC;
+        int it = 0;
+        for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, it++) {
+            int mt, nt;
+            tile_coords(tile, p.m_tiles, p.n_tiles, mt, nt);
+            const int buf = it & 1;
+            const int row = mt * BM + q * 32 + lane;
+            const bool row_ok = row < p.M;
+            const int c0 = (EPI == H3B_EPI_SWIGLU) ? nt * (BN / 2) : nt * BN;   // first output column
+            const float a = row_ok ? p.act_scale[row] : 0.0f;
+            const float *gate = nullptr;
+            if (EPI == H3B_EPI_GATE && p.mod && row_ok) {
+                const size_t mrow = p.row_map ? p.row_map[row] : (size_t)row;
+                gate = p.mod + (mrow * p.slots + p.gate_slot) * (size_t)p.n_out;
+            }
+            bool ok = mbar_wait(&tmem_full[buf], (it >> 1) & 1, abort_word, p.status, H3B_ST_TIMEOUT_TMEM_FULL);
+            tc_fence_after();
+            const uint32_t t_addr = tmem_base + lane_base + (uint32_t)buf * BN;
+            constexpr int CHUNKS = (EPI == H3B_EPI_SWIGLU) ? (BN / 2) / 32 : BN / 32;
+            if (ok) {
+#pragma unroll 1
+                for (int ch = 0; ch < CHUNKS; ch++) {
+                    const int col = c0 + ch * 32;
+                    if (col >= p.n_out) break;   // uniform across the warp
+                    uint32_t r[32];
+                    tmem_ld_32x32b_x32(t_addr + ch * 32, r);
+                    uint32_t r2[32];
+                    if (EPI == H3B_EPI_SWIGLU) tmem_ld_32x32b_x32(t_addr + BN / 2 + ch * 32, r2);
+                    tmem_ld_wait();
+                    if (!row_ok) continue;
+                    if constexpr (std::is_same<OutT, int32_t>::value) {
+#pragma unroll
+                        for (int v = 0; v < 32; v += 4)
+                            if (col + v < p.n_out)
+                                *reinterpret_cast<uint4 *>(y + (size_t)row * p.n_out + col + v) =
+                                    make_uint4(r[v], r[v + 1], r[v + 2], r[v + 3]);
+                    } else {
+#pragma unroll
+                        for (int v = 0; v < 32; v += VEC) {
+                            if (col + v >= p.n_out) break;
+                            float out[VEC], resv[VEC];
+                            if (EPI == H3B_EPI_GATE) OutTraits<OutT>::load(res + (size_t)row * p.n_out + col + v, resv);
+#pragma unroll
+                            for (int i = 0; i < VEC; i++) {
+                                const int c = col + v + i;
+                                float val = __fmul_rn(__fmul_rn(a, __ldg(p.s_channel + c)), (float)(int32_t)r[v + i]);
+                                if (EPI == H3B_EPI_GATE) {
+                                    const float g = gate ? __ldg(gate + c) : 1.0f;
+                                    val = __fadd_rn(resv[i], __fmul_rn(val, g));
+                                } else if (EPI == H3B_EPI_GELU) {
+                                    val = gelu_tanh_dev(val);
+                                } else if (EPI == H3B_EPI_SWIGLU) {
+                                    const float u = __fmul_rn(__fmul_rn(a, __ldg(p.s_channel + p.n_out + c)),
+                                                              (float)(int32_t)r2[v + i]);
+                                    val = __fmul_rn(val / __fadd_rn(1.0f, expf(-val)), u);
+                                }
+                                out[i] = val;
+                            }
+                            OutTraits<OutT>::store(y + (size_t)row * p.n_out + col + v, out);
+                        }
+                    }
+                }
+            }
+            // hand the accumulator back to the MMA warp
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&tmem_empty[buf]);
+            if (*abort_word) break;
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, TMEM_COLS);
+    }
+}
+
+template <int EPI, typename OutT>
+static int gemm_launch_t(h3_cuda *cuda, const GemmParams &p, char *error, size_t error_size) {
+    auto kern = k_gemm_i8<EPI, OutT>;
+    H3B_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)gemm::SMEM_BYTES),
+                "gemm smem attribute");
+    int tiles = p.m_tiles * p.n_tiles;
+    int grid = tiles < cuda->sm_count ? tiles : cuda->sm_count;
+    kern<<<grid, gemm::THREADS, gemm::SMEM_BYTES, cuda->op_stream>>>(p);
+    cuda->launches++;
+    H3B_CUDA_OK(cudaGetLastError(), "k_gemm_i8 launch");
+    return 1;
+}
+
+template <int EPI>
+static int gemm_launch_e(h3_cuda *cuda, const GemmParams &p, int out_dtype, char *error, size_t error_size) {
+    switch (out_dtype) {
+    case H3B_F32: return gemm_launch_t<EPI, float>(cuda, p, error, error_size);
+    case H3B_BF16: return gemm_launch_t<EPI, __nv_bfloat16>(cuda, p, error, error_size);
+    case H3B_F16: return gemm_launch_t<EPI, __half>(cuda, p, error, error_size);
+    }
+    return fail(error, error_size, "gemm: unsupported output dtype %d", out_dtype);
+}
+
+int launch_gemm_i8(h3_cuda *cuda, const h3_cuda_w4a8_weight *w, const int8_t *x, const float *a, size_t m, void *y,
+                   const h3b_gemm_epi *epi, char *error, size_t error_size) {
+    using namespace gemm;
+    if (!cuda || !w || !x || !a || !y || !epi || m == 0) return fail(error, error_size, "gemm_i8: invalid arguments");
+    if (!w->tmap_ok) return fail(error, error_size, "gemm_i8: weight has no tensor map (K %% 16 != 0?)");
+    if (w->device != cuda->device) return fail(error, error_size, "gemm_i8: weight lives on device %d, handle on %d", w->device, cuda->device);
+    const size_t N = w->n, K = w->k;
+    if (K % 16 || (reinterpret_cast<uintptr_t>(x) & 15))
+        return fail(error, error_size, "gemm_i8: K must be a multiple of 16 and X 16-byte aligned (K=%zu)", K);
+    if (m > 0x7fffff00u || N > 0x7fffff00u) return fail(error, error_size, "gemm_i8: shape too large");
+    GemmParams p;
+    memset(&p, 0, sizeof(p));
+    p.swiglu = epi->kind == H3B_EPI_SWIGLU;
+    if (p.swiglu && (N % 2)) return fail(error, error_size, "gemm_i8: SwiGLU needs an even N");
+    p.M = (int)m; p.N = (int)N; p.K = (int)K;
+    p.n_out = p.swiglu ? (int)(N / 2) : (int)N;
+    if (p.n_out % 8) return fail(error, error_size, "gemm_i8: output width %d must be a multiple of 8", p.n_out);
+    if (reinterpret_cast<uintptr_t>(y) & 15) return fail(error, error_size, "gemm_i8: Y must be 16-byte aligned");
+    p.m_tiles = (int)ceil_div(m, BM);
+    p.n_tiles = p.swiglu ? (int)ceil_div((size_t)p.n_out, BN / 2) : (int)ceil_div(N, BN);
+    p.k_blocks = (int)ceil_div(K, BK);
+    p.act_scale = a; p.s_channel = w->d_s; p.y = y;
+    p.residual = epi->d_residual; p.mod = epi->d_modulation; p.row_map = epi->d_row_map;
+    p.slots = (int)epi->slots; p.gate_slot = (int)epi->gate_slot;
+    p.status = cuda->d_status;
+    p.tmap_b = w->tmap_b;
+    int rc = h3b_encode_tmap_2d(&p.tmap_a, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, x, K, m, K, BK, BM,
+                                CU_TENSOR_MAP_SWIZZLE_128B);
+    if (rc != 0) return fail(error, error_size, "gemm_i8: cuTensorMapEncodeTiled(A) failed (%d)", rc);
+    if (epi->kind == H3B_EPI_GATE) {
+        if (!epi->d_residual) return fail(error, error_size, "gemm_i8: gate epilogue needs a residual");
+        if (epi->d_modulation && epi->slots == 0) return fail(error, error_size, "gemm_i8: gate epilogue needs slots > 0");
+        if (reinterpret_cast<uintptr_t>(epi->d_residual) & 15) return fail(error, error_size, "gemm_i8: residual must be 16-byte aligned");
+    }
+    switch (epi->kind) {
+    case H3B_EPI_PLAIN:
+        if (epi->out_dtype == H3B_I32) return gemm_launch_t<H3B_EPI_PLAIN, int32_t>(cuda, p, error, error_size);
+        return gemm_launch_e<H3B_EPI_PLAIN>(cuda, p, epi->out_dtype, error, error_size);
+    case H3B_EPI_GATE: return gemm_launch_e<H3B_EPI_GATE>(cuda, p, epi->out_dtype, error, error_size);
+    case H3B_EPI_SWIGLU: return gemm_launch_e<H3B_EPI_SWIGLU>(cuda, p, epi->out_dtype, error, error_size);
+    case H3B_EPI_GELU: return gemm_launch_e<H3B_EPI_GELU>(cuda, p, epi->out_dtype, error, error_size);
+    }
+    return fail(error, error_size, "gemm_i8: unknown epilogue kind %d", epi->kind);
+}
+
+}  // namespace h3b

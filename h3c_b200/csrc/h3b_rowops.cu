@@ -1,0 +1,639 @@
+// HBM-bound row-wise kernels of the DiT block: gate / RMSNorm / adaLN modulate /
+// ConvRot / per-row INT8 quantisation fused in one launch, plus the elementwise
+// gate, SwiGLU, GELU, cast and QK-norm+RoPE kernels.
+//
+// Arithmetic follows the reference's CPU functions operation by operation
+// (explicit __fmul_rn / __fadd_rn so the compiler does not contract them into
+// FMAs); only the order of the row reductions differs.
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
+#include "h3b_internal.h"
+
+namespace h3b {
+
+template <typename T> __device__ __forceinline__ float to_f(T v);
+template <> __device__ __forceinline__ float to_f<float>(float v) { return v; }
+template <> __device__ __forceinline__ float to_f<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
+template <> __device__ __forceinline__ float to_f<__half>(__half v) { return __half2float(v); }
+template <typename T> __device__ __forceinline__ T from_f(float v);
+template <> __device__ __forceinline__ float from_f<float>(float v) { return v; }
+template <> __device__ __forceinline__ __nv_bfloat16 from_f<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
+template <> __device__ __forceinline__ __half from_f<__half>(float v) { return __float2half_rn(v); }
+
+// value as it reads back after being stored in T
+template <typename T> __device__ __forceinline__ float round_to(float v) { return to_f<T>(from_f<T>(v)); }
+
+template <typename T, int V> struct Vec { T v[V]; };
+
+template <typename T, int V>
+__device__ __forceinline__ void load_vec(const T *p, float (&out)[V]) {
+    if constexpr (V == 1) {
+        out[0] = to_f<T>(p[0]);
+    } else {
+        using VT = typename std::conditional<sizeof(T) * V == 16, uint4, uint2>::type;
+        VT raw = *reinterpret_cast<const VT *>(p);
+        const T *e = reinterpret_cast<const T *>(&raw);
+#pragma unroll
+        for (int i = 0; i < V; i++) out[i] = to_f<T>(e[i]);
+    }
+}
+template <typename T, int V>
+__device__ __forceinline__ void store_vec(T *p, const float (&in)[V]) {
+    if constexpr (V == 1) {
+        p[0] = from_f<T>(in[0]);
+    } else {
+        using VT = typename std::conditional<sizeof(T) * V == 16, uint4, uint2>::type;
+        VT raw;
+        T *e = reinterpret_cast<T *>(&raw);
+#pragma unroll
+        for (int i = 0; i < V; i++) e[i] = from_f<T>(in[i]);
+        *reinterpret_cast<VT *>(p) = raw;
+    }
+}
+
+__device__ __forceinline__ float block_sum(float v, float *red) {
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    __syncthreads();
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = v;
+    __syncthreads();
+    float t = 0.0f;
+    for (int i = 0; i < (int)(blockDim.x >> 5); i++) t += red[i];
+    return t;
+}
+__device__ __forceinline__ float block_max(float v, float *red) {
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    __syncthreads();
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = v;
+    __syncthreads();
+    float t = 0.0f;
+    for (int i = 0; i < (int)(blockDim.x >> 5); i++) t = fmaxf(t, red[i]);
+    return t;
+}
+
+__device__ __forceinline__ int8_t quant_code(float v, float inv) {
+    float q = roundf(__fmul_rn(v, inv));   // half away from zero, as the reference
+    q = fminf(fmaxf(q, -127.0f), 127.0f);
+    return (int8_t)(int)q;
+}
+
+struct NormParams {
+    const void *x, *branch;
+    const float *norm_w, *mod;
+    const uint32_t *row_map;
+    unsigned width, slots, gate_slot, shift_slot, scale_slot;
+    float eps;
+    int identity, gs;
+    void *gated, *normed;
+    float *rot;
+    int8_t *q;
+    float *scales;
+};
+
+// V = elements per vector access (4 when width % 4 == 0 and all pointers are
+// 16-byte aligned, else 1).  Dynamic shared memory: width floats.
+template <typename T, int V>
+__global__ void __launch_bounds__(256) k_norm(NormParams p) {
+    extern __shared__ float row[];
+    __shared__ float red[8];
+    const size_t r = blockIdx.x;
+    const unsigned W = p.width;
+    const size_t mrow = p.row_map ? p.row_map[r] : r;
+    const float *mod = p.mod ? p.mod + mrow * p.slots * W : nullptr;
+    const T *x = reinterpret_cast<const T *>(p.x) + r * W;
+    const T *br = p.branch ? reinterpret_cast<const T *>(p.branch) + r * W : nullptr;
+    T *gated = p.gated ? reinterpret_cast<T *>(p.gated) + r * W : nullptr;
+    T *normed = p.normed ? reinterpret_cast<T *>(p.normed) + r * W : nullptr;
+
+    // ---- stage the row (optionally residual + branch * gate), sum of squares
+    float ss = 0.0f;
+    for (unsigned c = threadIdx.x * V; c < W; c += blockDim.x * V) {
+        float v[V];
+        load_vec<T, V>(x + c, v);
+        if (br) {
+            float b[V];
+            load_vec<T, V>(br + c, b);
+#pragma unroll
+            for (int i = 0; i < V; i++) {
+                float g = mod ? mod[p.gate_slot * W + c + i] : 1.0f;
+                v[i] = round_to<T>(__fadd_rn(v[i], __fmul_rn(b[i], g)));
+            }
+            if (gated) store_vec<T, V>(gated + c, v);
+        }
+#pragma unroll
+        for (int i = 0; i < V; i++) {
+            row[c + i] = v[i];
+            ss = __fadd_rn(ss, __fmul_rn(v[i], v[i]));
+        }
+    }
+    float amax = 0.0f;
+    if (!p.identity) {
+        ss = block_sum(ss, red);
+        const float inv = 1.0f / sqrtf(ss / (float)W + p.eps);
+        for (unsigned c = threadIdx.x * V; c < W; c += blockDim.x * V) {
+            float y[V];
+#pragma unroll
+            for (int i = 0; i < V; i++) {
+                float w = p.norm_w ? p.norm_w[c + i] : 1.0f;
+                float n = __fmul_rn(__fmul_rn(row[c + i], inv), w);
+                if (mod)
+                    n = __fadd_rn(__fmul_rn(n, __fadd_rn(1.0f, mod[p.scale_slot * W + c + i])),
+                                  mod[p.shift_slot * W + c + i]);
+                y[i] = round_to<T>(n);
+                row[c + i] = y[i];
+                amax = fmaxf(amax, fabsf(y[i]));
+            }
+            if (normed) store_vec<T, V>(normed + c, y);
+        }
+    } else {
+        // same element ownership as the staging loop, so no barrier is needed here
+        for (unsigned c = threadIdx.x * V; c < W; c += blockDim.x * V)
+#pragma unroll
+            for (int i = 0; i < V; i++) amax = fmaxf(amax, fabsf(row[c + i]));
+    }
+
+    // ---- ConvRot: y = x * H per group, H = kron-power of the 4x4 regular Hadamard / sqrt(gs).
+    // H is symmetric, so this is a radix-4 butterfly network with strides 1, 4, 16, 64.
+    if (p.gs > 0) {
+        for (int stride = 1; stride < p.gs; stride <<= 2) {
+            __syncthreads();
+            for (unsigned b = threadIdx.x; b < W / 4; b += blockDim.x) {
+                unsigned lo = b % stride, hi = b / stride;
+                unsigned base = hi * stride * 4 + lo;
+                float a0 = row[base], a1 = row[base + stride], a2 = row[base + 2 * stride], a3 = row[base + 3 * stride];
+                float s = (a0 + a1) + (a2 + a3);
+                row[base] = s - 2.0f * a3;
+                row[base + stride] = s - 2.0f * a2;
+                row[base + 2 * stride] = s - 2.0f * a1;
+                row[base + 3 * stride] = s - 2.0f * a0;
+            }
+        }
+        __syncthreads();
+        const float norm = 1.0f / sqrtf((float)p.gs);   // exact: gs is a power of four
+        amax = 0.0f;
+        for (unsigned c = threadIdx.x; c < W; c += blockDim.x) {
+            float v = row[c] * norm;
+            row[c] = v;
+            amax = fmaxf(amax, fabsf(v));
+            if (p.rot) p.rot[r * W + c] = v;
+        }
+    }
+
+    // ---- per-row INT8 quantisation
+    if (p.q) {
+        amax = block_max(amax, red);
+        const float scale = amax > 0.0f ? amax / 127.0f : 1.0f;
+        const float inv = 1.0f / scale;
+        if (threadIdx.x == 0) p.scales[r] = scale;
+        int8_t *q = p.q + r * W;
+        if constexpr (V == 4) {
+            for (unsigned c = threadIdx.x * 4; c < W; c += blockDim.x * 4) {
+                char4 o;
+                o.x = quant_code(row[c], inv);
+                o.y = quant_code(row[c + 1], inv);
+                o.z = quant_code(row[c + 2], inv);
+                o.w = quant_code(row[c + 3], inv);
+                *reinterpret_cast<char4 *>(q + c) = o;
+            }
+        } else {
+            for (unsigned c = threadIdx.x; c < W; c += blockDim.x) q[c] = quant_code(row[c], inv);
+        }
+    }
+}
+
+template <typename T>
+static int norm_dispatch(h3_cuda *cuda, const NormParams &p, size_t rows, bool vec, char *error, size_t error_size) {
+    size_t smem = (size_t)p.width * sizeof(float);
+    if (smem > 200 * 1024) return fail(error, error_size, "row width %u too large for the row kernel", p.width);
+    auto kv = k_norm<T, 4>;
+    auto ks = k_norm<T, 1>;
+    if (smem > 48 * 1024) {
+        H3B_CUDA_OK(cudaFuncSetAttribute(kv, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem), "smem attr");
+        H3B_CUDA_OK(cudaFuncSetAttribute(ks, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem), "smem attr");
+    }
+    if (vec) kv<<<(unsigned)rows, 256, smem, cuda->op_stream>>>(p);
+    else ks<<<(unsigned)rows, 256, smem, cuda->op_stream>>>(p);
+    cuda->launches++;
+    H3B_CUDA_OK(cudaGetLastError(), "k_norm launch");
+    return 1;
+}
+
+int launch_norm(h3_cuda *cuda, const h3b_norm_args *a, char *error, size_t error_size) {
+    if (!cuda || !a || !a->d_x || !a->rows || !a->width) return fail(error, error_size, "norm: invalid arguments");
+    if (a->d_q && !a->d_scales) return fail(error, error_size, "norm: d_q without d_scales");
+    if (a->d_modulation && a->slots == 0) return fail(error, error_size, "norm: slots must be > 0");
+    if (a->convrot_gs != 0 && a->convrot_gs != 4 && a->convrot_gs != 16 && a->convrot_gs != 64 &&
+        a->convrot_gs != 256)
+        return fail(error, error_size, "norm: ConvRot group size %d unsupported (0, 4, 16, 64, 256)", a->convrot_gs);
+    if (a->convrot_gs && a->width % (size_t)a->convrot_gs)
+        return fail(error, error_size, "K=%zu not divisible by convrot_groupsize=%d", a->width, a->convrot_gs);
+    if (a->rows > 0x7fffffffu) return fail(error, error_size, "norm: too many rows");
+    NormParams p;
+    p.x = a->d_x; p.branch = a->d_branch; p.norm_w = a->d_norm_w; p.mod = a->d_modulation;
+    p.row_map = a->d_row_map; p.width = (unsigned)a->width; p.slots = (unsigned)a->slots;
+    p.gate_slot = (unsigned)a->gate_slot; p.shift_slot = (unsigned)a->shift_slot;
+    p.scale_slot = (unsigned)a->scale_slot; p.eps = a->epsilon; p.identity = a->identity;
+    p.gs = a->convrot_gs; p.gated = a->d_gated; p.normed = a->d_normed; p.rot = a->d_rot; p.q = a->d_q;
+    p.scales = a->d_scales;
+    // vector path: 4 elements per access (16 bytes of f32, 8 bytes of 16-bit types, 4 codes)
+    const uintptr_t amask = 4 * dtype_bytes(a->dtype) - 1;
+    auto al = [&](const void *q_, uintptr_t mask) { return !q_ || (reinterpret_cast<uintptr_t>(q_) & mask) == 0; };
+    bool vec = a->width % 4 == 0 && al(a->d_x, amask) && al(a->d_branch, amask) && al(a->d_gated, amask) &&
+               al(a->d_normed, amask) && al(a->d_q, 3);
+    switch (a->dtype) {
+    case H3B_F32: return norm_dispatch<float>(cuda, p, a->rows, vec, error, error_size);
+    case H3B_BF16: return norm_dispatch<__nv_bfloat16>(cuda, p, a->rows, vec, error, error_size);
+    case H3B_F16: return norm_dispatch<__half>(cuda, p, a->rows, vec, error, error_size);
+    }
+    return fail(error, error_size, "norm: unsupported dtype %d", a->dtype);
+}
+
+int launch_quant(h3_cuda *cuda, const void *x, int dtype, size_t m, size_t k, int8_t *q, float *scales, char *error,
+                 size_t error_size) {
+    h3b_norm_args a = {};
+    a.d_x = x; a.rows = m; a.width = k; a.dtype = dtype; a.identity = 1; a.d_q = q; a.d_scales = scales;
+    return launch_norm(cuda, &a, error, error_size);
+}
+
+int launch_convrot(h3_cuda *cuda, const float *x, size_t m, size_t k, int gs, float *y, char *error,
+                   size_t error_size) {
+    if (gs <= 0) {
+        if (x != y) H3B_CUDA_OK(cudaMemcpyAsync(y, x, m * k * sizeof(float), cudaMemcpyDeviceToDevice, cuda->op_stream), "convrot copy");
+        return 1;
+    }
+    h3b_norm_args a = {};
+    a.d_x = x; a.rows = m; a.width = k; a.dtype = H3B_F32; a.identity = 1; a.convrot_gs = gs; a.d_rot = y;
+    return launch_norm(cuda, &a, error, error_size);
+}
+
+// ------------------------------------------------------------- elementwise
+
+template <typename T>
+__global__ void k_gate(const T *res, const T *br, const float *mod, const uint32_t *row_map, size_t rows,
+                       unsigned width, unsigned slots, unsigned gate_slot, T *out) {
+    size_t n = rows * width;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
+        size_t r = i / width;
+        unsigned c = (unsigned)(i - r * width);
+        size_t mrow = row_map ? row_map[r] : r;
+        float g = mod[(mrow * slots + gate_slot) * width + c];
+        out[i] = from_f<T>(__fadd_rn(to_f<T>(res[i]), __fmul_rn(to_f<T>(br[i]), g)));
+    }
+}
+
+template <typename T>
+__global__ void k_swiglu(const T *fused, size_t rows, unsigned width, T *out) {
+    size_t n = rows * width;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
+        size_t r = i / width;
+        unsigned c = (unsigned)(i - r * width);
+        float g = to_f<T>(fused[r * 2 * width + c]), u = to_f<T>(fused[r * 2 * width + width + c]);
+        out[i] = from_f<T>(__fmul_rn(g / __fadd_rn(1.0f, expf(-g)), u));
+    }
+}
+
+__device__ __forceinline__ float gelu_tanh_f(float v) {
+    float inner = 0.7978845608028654f * (v + 0.044715f * v * v * v);
+    if (inner <= -10.0f) return 0.0f;
+    if (inner >= 10.0f) return v;
+    return 0.5f * v * (1.0f + tanhf(inner));
+}
+
+template <typename T>
+__global__ void k_gelu(const T *in, T *out, size_t n) {
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x)
+        out[i] = from_f<T>(gelu_tanh_f(to_f<T>(in[i])));
+}
+
+template <typename TI, typename TO>
+__global__ void k_cast(const TI *in, TO *out, size_t n) {
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x)
+        out[i] = from_f<TO>(to_f<TI>(in[i]));
+}
+
+static unsigned ew_grid(h3_cuda *cuda, size_t n) {
+    size_t g = ceil_div(n, 256);
+    size_t cap = (size_t)cuda->sm_count * 16;
+    return (unsigned)(g < 1 ? 1 : (g > cap ? cap : g));
+}
+
+int launch_gate(h3_cuda *cuda, const void *res, const void *branch, const float *mod, const uint32_t *row_map,
+                size_t rows, size_t width, size_t slots, size_t gate_slot, void *out, int dtype, char *error,
+                size_t error_size) {
+    if (!res || !branch || !mod || !out || !width || !slots) return fail(error, error_size, "gate: invalid arguments");
+    unsigned g = ew_grid(cuda, rows * width);
+    if (dtype == H3B_F32)
+        k_gate<float><<<g, 256, 0, cuda->op_stream>>>((const float *)res, (const float *)branch, mod, row_map, rows,
+                                                      (unsigned)width, (unsigned)slots, (unsigned)gate_slot, (float *)out);
+    else if (dtype == H3B_BF16)
+        k_gate<__nv_bfloat16><<<g, 256, 0, cuda->op_stream>>>((const __nv_bfloat16 *)res, (const __nv_bfloat16 *)branch,
+                                                              mod, row_map, rows, (unsigned)width, (unsigned)slots,
+                                                              (unsigned)gate_slot, (__nv_bfloat16 *)out);
+    else
+        return fail(error, error_size, "gate: unsupported dtype %d", dtype);
+    cuda->launches++;
+    H3B_CUDA_OK(cudaGetLastError(), "k_gate launch");
+    return 1;
+}
+
+int launch_swiglu(h3_cuda *cuda, const void *fused, size_t rows, size_t width, void *out, int dtype, char *error,
+                  size_t error_size) {
+    if (!fused || !out || !width) return fail(error, error_size, "swiglu: invalid arguments");
+    unsigned g = ew_grid(cuda, rows * width);
+    if (dtype == H3B_F32)
+        k_swiglu<float><<<g, 256, 0, cuda->op_stream>>>((const float *)fused, rows, (unsigned)width, (float *)out);
+    else if (dtype == H3B_BF16)
+        k_swiglu<__nv_bfloat16><<<g, 256, 0, cuda->op_stream>>>((const __nv_bfloat16 *)fused, rows, (unsigned)width,
+                                                                (__nv_bfloat16 *)out);
+    else
+        return fail(error, error_size, "swiglu: unsupported dtype %d", dtype);
+    cuda->launches++;
+    H3B_CUDA_OK(cudaGetLastError(), "k_swiglu launch");
+    return 1;
+}
+
+// ---------------------------------------------------------- QK-norm + RoPE
+//
+// One warp per (row, head); each lane owns EPL = head_dim / 32 consecutive
+// dimensions.  Split-half pairing (d, d + rope_half) lives rope_half / EPL lanes
+// apart; consecutive pairing (2d, 2d+1) lives inside one lane.
+template <typename TI, typename TO, int EPL>
+__global__ void __launch_bounds__(256) k_qkv_rope(const TI *qkv, const float *q_norm, const float *k_norm,
+                                                  const float *cosT, const float *sinT, size_t seq, unsigned heads,
+                                                  unsigned rope_half, float eps, int grouped, int split_half, TO *q,
+                                                  TO *k, TO *v) {
+    constexpr unsigned HD = EPL * 32;
+    const unsigned lane = threadIdx.x & 31;
+    const size_t item = (size_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (item >= seq * heads) return;
+    const size_t row = item / heads;
+    const unsigned head = (unsigned)(item - row * heads);
+    const size_t inner = (size_t)heads * HD;
+    const TI *base = qkv + row * inner * 3;
+    const TI *qb = grouped ? base + (size_t)head * HD * 3 : base + (size_t)head * HD;
+    const TI *kb = grouped ? qb + HD : qb + inner;
+    const TI *vb = grouped ? kb + HD : qb + 2 * inner;
+    const unsigned d0 = lane * EPL;
+    float qv[EPL], kv[EPL], vv[EPL];
+    load_vec<TI, EPL>(qb + d0, qv);
+    load_vec<TI, EPL>(kb + d0, kv);
+    load_vec<TI, EPL>(vb + d0, vv);
+    float qs = 0.0f, ks = 0.0f;
+#pragma unroll
+    for (int i = 0; i < EPL; i++) {
+        qs += qv[i] * qv[i];
+        ks += kv[i] * kv[i];
+    }
+    for (int o = 16; o > 0; o >>= 1) {
+        qs += __shfl_xor_sync(0xffffffffu, qs, o);
+        ks += __shfl_xor_sync(0xffffffffu, ks, o);
+    }
+    const float qi = 1.0f / sqrtf(qs / (float)HD + eps), ki = 1.0f / sqrtf(ks / (float)HD + eps);
+#pragma unroll
+    for (int i = 0; i < EPL; i++) {
+        qv[i] = __fmul_rn(__fmul_rn(qv[i], qi), q_norm[d0 + i]);
+        kv[i] = __fmul_rn(__fmul_rn(kv[i], ki), k_norm[d0 + i]);
+    }
+    if (rope_half) {
+        const float *cr = cosT + row * rope_half, *sr = sinT + row * rope_half;
+        if (split_half) {
+            const int lane_off = (int)(rope_half / EPL);
+            float qo[EPL], ko[EPL];
+#pragma unroll
+            for (int i = 0; i < EPL; i++) {
+                // partner values: from lane + off for the low half, lane - off for the high half
+                float q_up = __shfl_down_sync(0xffffffffu, qv[i], lane_off);
+                float q_dn = __shfl_up_sync(0xffffffffu, qv[i], lane_off);
+                float k_up = __shfl_down_sync(0xffffffffu, kv[i], lane_off);
+                float k_dn = __shfl_up_sync(0xffffffffu, kv[i], lane_off);
+                unsigned d = d0 + i;
+                if (d < rope_half) {
+                    float c = cr[d], s = sr[d];
+                    qo[i] = __fsub_rn(__fmul_rn(qv[i], c), __fmul_rn(q_up, s));
+                    ko[i] = __fsub_rn(__fmul_rn(kv[i], c), __fmul_rn(k_up, s));
+                } else if (d < 2 * rope_half) {
+                    float c = cr[d - rope_half], s = sr[d - rope_half];
+                    qo[i] = __fadd_rn(__fmul_rn(qv[i], c), __fmul_rn(q_dn, s));
+                    ko[i] = __fadd_rn(__fmul_rn(kv[i], c), __fmul_rn(k_dn, s));
+                } else {
+                    qo[i] = qv[i];
+                    ko[i] = kv[i];
+                }
+            }
+#pragma unroll
+            for (int i = 0; i < EPL; i++) {
+                qv[i] = qo[i];
+                kv[i] = ko[i];
+            }
+        } else if constexpr (EPL >= 2) {
+#pragma unroll
+            for (int i = 0; i < EPL; i += 2) {
+                unsigned pair = (d0 + i) >> 1;
+                if (pair < rope_half) {
+                    float c = cr[pair], s = sr[pair];
+                    float q0 = qv[i], q1 = qv[i + 1], k0 = kv[i], k1 = kv[i + 1];
+                    qv[i] = __fsub_rn(__fmul_rn(q0, c), __fmul_rn(q1, s));
+                    qv[i + 1] = __fadd_rn(__fmul_rn(q0, s), __fmul_rn(q1, c));
+                    kv[i] = __fsub_rn(__fmul_rn(k0, c), __fmul_rn(k1, s));
+                    kv[i + 1] = __fadd_rn(__fmul_rn(k0, s), __fmul_rn(k1, c));
+                }
+            }
+        }
+    }
+    const size_t o = (row * heads + head) * HD + d0;
+    store_vec<TO, EPL>(q + o, qv);
+    store_vec<TO, EPL>(k + o, kv);
+    store_vec<TO, EPL>(v + o, vv);
+}
+
+template <typename TI, typename TO>
+static int qkv_rope_dispatch(h3_cuda *cuda, const void *qkv, const float *qn, const float *kn, const float *c,
+                             const float *s, size_t seq, size_t heads, size_t hd, size_t rope_half, float eps,
+                             int grouped, int split_half, void *q, void *k, void *v, char *error, size_t error_size) {
+    size_t items = seq * heads;
+    unsigned grid = (unsigned)ceil_div(items, 8);
+#define H3B_ROPE(EPL)                                                                                          \
+    k_qkv_rope<TI, TO, EPL><<<grid, 256, 0, cuda->op_stream>>>((const TI *)qkv, qn, kn, c, s, seq, (unsigned)heads, \
+                                                               (unsigned)rope_half, eps, grouped, split_half,  \
+                                                               (TO *)q, (TO *)k, (TO *)v)
+    if (hd == 128) H3B_ROPE(4);
+    else if (hd == 64) H3B_ROPE(2);
+    else return fail(error, error_size, "qkv_rope: head_dim %zu unsupported (64 or 128)", hd);
+#undef H3B_ROPE
+    cuda->launches++;
+    H3B_CUDA_OK(cudaGetLastError(), "k_qkv_rope launch");
+    return 1;
+}
+
+}  // namespace h3b
+
+using namespace h3b;
+
+extern "C" {
+
+int h3b_norm_dev(h3_cuda *cuda, const h3b_norm_args *args, char *error, size_t error_size) {
+    return launch_norm(cuda, args, error, error_size);
+}
+
+int h3b_quantize_act_int8_dev(h3_cuda *cuda, const void *d_x, int dtype, size_t m, size_t k, int8_t *d_q,
+                              float *d_scales, char *error, size_t error_size) {
+    if (!cuda || !d_x || !d_q || !d_scales || !m || !k)
+        return fail(error, error_size, "invalid quantize_act_int8 arguments");
+    return launch_quant(cuda, d_x, dtype, m, k, d_q, d_scales, error, error_size);
+}
+
+int h3_cuda_convrot_act_f32_dd(h3_cuda *cuda, const float *d_x, size_t m, size_t k, int convrot_groupsize,
+                               float *d_y, char *error, size_t error_size) {
+    if (!cuda || !d_x || !d_y || !m || !k) return fail(error, error_size, "invalid convrot_act arguments");
+    if (d_x == d_y && convrot_groupsize > 0) return fail(error, error_size, "convrot_act: d_x and d_y must not alias");
+    return launch_convrot(cuda, d_x, m, k, convrot_groupsize, d_y, error, error_size);
+}
+
+int h3_cuda_adaln_f32_dev(h3_cuda *cuda, const float *d_x, const float *d_norm_w, const float *d_modulation,
+                          const uint32_t *d_row_map, size_t rows, size_t width, size_t slots, size_t shift_slot,
+                          size_t scale_slot, float epsilon, float *d_out, double *op_ms, char *error,
+                          size_t error_size) {
+    if (!cuda || !d_x || !d_norm_w || !d_modulation || !d_out || !width || !slots)
+        return fail(error, error_size, "invalid adaln arguments");
+    h3b_norm_args a = {};
+    a.d_x = d_x; a.d_norm_w = d_norm_w; a.d_modulation = d_modulation; a.d_row_map = d_row_map; a.rows = rows;
+    a.width = width; a.slots = slots; a.shift_slot = shift_slot; a.scale_slot = scale_slot; a.epsilon = epsilon;
+    a.dtype = H3B_F32; a.d_normed = d_out;
+    Timer t(cuda, op_ms);
+    int ok = launch_norm(cuda, &a, error, error_size);
+    t.stop();
+    return ok;
+}
+
+int h3_cuda_rms_norm_f32_dev(h3_cuda *cuda, const float *d_x, const float *d_w, size_t rows, size_t width,
+                             float eps, float *d_out, char *error, size_t error_size) {
+    if (!cuda || !d_x || !d_w || !d_out || !width) return fail(error, error_size, "invalid rms_norm arguments");
+    h3b_norm_args a = {};
+    a.d_x = d_x; a.d_norm_w = d_w; a.rows = rows; a.width = width; a.epsilon = eps; a.dtype = H3B_F32;
+    a.d_normed = d_out;
+    return launch_norm(cuda, &a, error, error_size);
+}
+
+int h3_cuda_gate_adaln_f32_dev(h3_cuda *cuda, const float *d_residual, const float *d_branch, const float *d_norm_w,
+                               const float *d_modulation, const uint32_t *d_row_map, size_t rows, size_t width,
+                               size_t slots, size_t gate_slot, size_t shift_slot, size_t scale_slot, float epsilon,
+                               float *d_gated, float *d_normed, double *op_ms, char *error, size_t error_size) {
+    if (!cuda || !d_residual || !d_branch || !d_norm_w || !d_modulation || !d_gated || !d_normed || !width || !slots)
+        return fail(error, error_size, "invalid gate_adaln arguments");
+    h3b_norm_args a = {};
+    a.d_x = d_residual; a.d_branch = d_branch; a.d_norm_w = d_norm_w; a.d_modulation = d_modulation;
+    a.d_row_map = d_row_map; a.rows = rows; a.width = width; a.slots = slots; a.gate_slot = gate_slot;
+    a.shift_slot = shift_slot; a.scale_slot = scale_slot; a.epsilon = epsilon; a.dtype = H3B_F32;
+    a.d_gated = d_gated; a.d_normed = d_normed;
+    Timer t(cuda, op_ms);
+    int ok = launch_norm(cuda, &a, error, error_size);
+    t.stop();
+    return ok;
+}
+
+int h3_cuda_gate_f32_dev(h3_cuda *cuda, const float *d_residual, const float *d_branch, const float *d_modulation,
+                         const uint32_t *d_row_map, size_t rows, size_t width, size_t slots, size_t gate_slot,
+                         float *d_out, double *op_ms, char *error, size_t error_size) {
+    if (!cuda) return fail(error, error_size, "gate: NULL handle");
+    Timer t(cuda, op_ms);
+    int ok = launch_gate(cuda, d_residual, d_branch, d_modulation, d_row_map, rows, width, slots, gate_slot, d_out,
+                         H3B_F32, error, error_size);
+    t.stop();
+    return ok;
+}
+
+int h3_cuda_swiglu_f32_dev(h3_cuda *cuda, const float *d_fused, size_t rows, size_t width, float *d_out,
+                           double *op_ms, char *error, size_t error_size) {
+    if (!cuda) return fail(error, error_size, "swiglu: NULL handle");
+    Timer t(cuda, op_ms);
+    int ok = launch_swiglu(cuda, d_fused, rows, width, d_out, H3B_F32, error, error_size);
+    t.stop();
+    return ok;
+}
+
+int h3b_qkv_rope_dev(h3_cuda *cuda, const void *d_qkv, int in_dtype, const float *d_q_norm, const float *d_k_norm,
+                     const float *d_rope_cos, const float *d_rope_sin, size_t seq, size_t heads, size_t head_dim,
+                     size_t rope_half, float epsilon, int grouped, int split_half, void *d_query, void *d_key,
+                     void *d_value, int out_dtype, char *error, size_t error_size) {
+    if (!cuda || !d_qkv || !d_q_norm || !d_k_norm || !d_query || !d_key || !d_value || !seq || !heads || !head_dim ||
+        (rope_half > 0 && (!d_rope_cos || !d_rope_sin)))
+        return fail(error, error_size, "invalid qkv_rope args");
+    if (rope_half * 2 > head_dim) return fail(error, error_size, "rope_half too large for head_dim");
+    if (split_half && rope_half % (head_dim / 32))
+        return fail(error, error_size, "qkv_rope: rope_half must be a multiple of head_dim/32");
+#define H3B_QR(TI, TO)                                                                                             \
+    return qkv_rope_dispatch<TI, TO>(cuda, d_qkv, d_q_norm, d_k_norm, d_rope_cos, d_rope_sin, seq, heads, head_dim, \
+                                     rope_half, epsilon, grouped, split_half, d_query, d_key, d_value, error,      \
+                                     error_size)
+    if (in_dtype == H3B_F32 && out_dtype == H3B_F32) H3B_QR(float, float);
+    if (in_dtype == H3B_F32 && out_dtype == H3B_BF16) H3B_QR(float, __nv_bfloat16);
+    if (in_dtype == H3B_BF16 && out_dtype == H3B_BF16) H3B_QR(__nv_bfloat16, __nv_bfloat16);
+    if (in_dtype == H3B_BF16 && out_dtype == H3B_F32) H3B_QR(__nv_bfloat16, float);
+#undef H3B_QR
+    return fail(error, error_size, "qkv_rope: unsupported dtype pair %d -> %d", in_dtype, out_dtype);
+}
+
+int h3_cuda_qkv_rope_f32_dev_layout(h3_cuda *cuda, const float *d_qkv, const float *d_q_norm, const float *d_k_norm,
+                                    const float *d_rope_cos, const float *d_rope_sin, size_t seq, size_t heads,
+                                    size_t head_dim, size_t rope_half, float epsilon, int grouped, int split_half,
+                                    float *d_query, float *d_key, float *d_value, double *op_ms, char *error,
+                                    size_t error_size) {
+    if (!cuda) return fail(error, error_size, "qkv_rope: NULL handle");
+    Timer t(cuda, op_ms);
+    int ok = h3b_qkv_rope_dev(cuda, d_qkv, H3B_F32, d_q_norm, d_k_norm, d_rope_cos, d_rope_sin, seq, heads, head_dim,
+                              rope_half, epsilon, grouped, split_half, d_query, d_key, d_value, H3B_F32, error,
+                              error_size);
+    t.stop();
+    return ok;
+}
+
+int h3_cuda_qkv_rope_f32_dev(h3_cuda *cuda, const float *d_qkv, const float *d_q_norm, const float *d_k_norm,
+                             const float *d_rope_cos, const float *d_rope_sin, size_t seq, size_t heads,
+                             size_t head_dim, size_t rope_half, float epsilon, float *d_query, float *d_key,
+                             float *d_value, double *op_ms, char *error, size_t error_size) {
+    // reference default: contiguous [Q|K|V] thirds, split-half pairing (h3_dit_w4a8.c:239-253)
+    return h3_cuda_qkv_rope_f32_dev_layout(cuda, d_qkv, d_q_norm, d_k_norm, d_rope_cos, d_rope_sin, seq, heads,
+                                           head_dim, rope_half, epsilon, 0, 1, d_query, d_key, d_value, op_ms, error,
+                                           error_size);
+}
+
+int h3b_cast_dev(h3_cuda *cuda, const void *d_in, int in_dtype, void *d_out, int out_dtype, size_t n, char *error,
+                 size_t error_size) {
+    if (!cuda || !d_in || !d_out) return fail(error, error_size, "cast: invalid arguments");
+    if (n == 0) return 1;
+    unsigned g = ew_grid(cuda, n);
+#define H3B_CAST(TI, TO) k_cast<TI, TO><<<g, 256, 0, cuda->op_stream>>>((const TI *)d_in, (TO *)d_out, n)
+    if (in_dtype == H3B_F32 && out_dtype == H3B_BF16) H3B_CAST(float, __nv_bfloat16);
+    else if (in_dtype == H3B_BF16 && out_dtype == H3B_F32) H3B_CAST(__nv_bfloat16, float);
+    else if (in_dtype == H3B_F32 && out_dtype == H3B_F16) H3B_CAST(float, __half);
+    else if (in_dtype == H3B_F16 && out_dtype == H3B_F32) H3B_CAST(__half, float);
+    else return fail(error, error_size, "cast: unsupported dtype pair %d -> %d", in_dtype, out_dtype);
+#undef H3B_CAST
+    cuda->launches++;
+    H3B_CUDA_OK(cudaGetLastError(), "k_cast launch");
+    return 1;
+}
+
+int h3_cuda_f32_to_f16_dev(h3_cuda *cuda, const float *d_in, void *d_out_half, size_t n, char *error,
+                           size_t error_size) {
+    return h3b_cast_dev(cuda, d_in, H3B_F32, d_out_half, H3B_F16, n, error, error_size);
+}
+int h3_cuda_f16_to_f32_dev(h3_cuda *cuda, const void *d_in_half, float *d_out, size_t n, char *error,
+                           size_t error_size) {
+    return h3b_cast_dev(cuda, d_in_half, H3B_F16, d_out, H3B_F32, n, error, error_size);
+}
+
+int h3b_gelu_tanh_dev(h3_cuda *cuda, const void *d_in, void *d_out, int dtype, size_t n, char *error,
+                      size_t error_size) {
+    if (!cuda || !d_in || !d_out) return fail(error, error_size, "gelu: invalid arguments");
+    unsigned g = ew_grid(cuda, n);
+    if (dtype == H3B_F32) k_gelu<float><<<g, 256, 0, cuda->op_stream>>>((const float *)d_in, (float *)d_out, n);
+    else if (dtype == H3B_BF16)
+        k_gelu<__nv_bfloat16><<<g, 256, 0, cuda->op_stream>>>((const __nv_bfloat16 *)d_in, (__nv_bfloat16 *)d_out, n);
+    else return fail(error, error_size, "gelu: unsupported dtype %d", dtype);
+    cuda->launches++;
+    H3B_CUDA_OK(cudaGetLastError(), "k_gelu launch");
+    return 1;
+}
+
+}  // extern "C"

@@ -1,0 +1,188 @@
+"""ctypes binding of libh3_b200.so -- the same C ABI a C caller of the reference links against.
+
+Nothing here computes: every function forwards raw device pointers (taken from torch tensors,
+which only provide device memory and streams) to the library.  Loading fails loudly when the
+library has not been built; there is no fallback.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from pathlib import Path
+
+HERE = Path(__file__).resolve().parent
+LIB_PATH = HERE / "libh3_b200.so"
+
+F32, BF16, F16, I32 = 0, 1, 2, 3
+EPI_PLAIN, EPI_GATE, EPI_SWIGLU, EPI_GELU = 0, 1, 2, 3
+ERR_LEN = 512
+
+vp = C.c_void_p
+sz = C.c_size_t
+i32 = C.c_int
+f32 = C.c_float
+cs = C.c_char_p
+dbl_p = C.POINTER(C.c_double)
+
+
+class H3Error(RuntimeError):
+    pass
+
+
+class DeviceInfo(C.Structure):
+    _fields_ = [("device_index", i32), ("name", C.c_char * 256), ("compute_major", i32), ("compute_minor", i32),
+                ("total_memory_bytes", sz), ("free_memory_bytes", sz), ("multiprocessor_count", i32),
+                ("driver_version", i32), ("runtime_version", i32)]
+
+
+class DitGemmEpi(C.Structure):  # h3_cuda_dit_gemm_epi, the reference's epilogue description
+    _fields_ = [("swiglu", i32), ("gate", i32), ("d_residual", vp), ("d_modulation", vp), ("d_row_map", vp),
+                ("d_lora", vp), ("lora_ready", vp), ("slots", sz), ("gate_slot", sz), ("requant_mode", i32),
+                ("requant_gs", i32), ("d_rq_x", vp), ("d_rq_act", vp), ("d_rq_pre", vp), ("requant_rows", sz),
+                ("y_f16", i32)]
+
+
+class GemmEpi(C.Structure):  # h3b_gemm_epi
+    _fields_ = [("kind", i32), ("out_dtype", i32), ("d_residual", vp), ("d_modulation", vp), ("d_row_map", vp),
+                ("slots", sz), ("gate_slot", sz)]
+
+
+class NormArgs(C.Structure):  # h3b_norm_args
+    _fields_ = [("d_x", vp), ("d_branch", vp), ("d_norm_w", vp), ("d_modulation", vp), ("d_row_map", vp),
+                ("rows", sz), ("width", sz), ("slots", sz), ("gate_slot", sz), ("shift_slot", sz),
+                ("scale_slot", sz), ("epsilon", f32), ("dtype", i32), ("identity", i32), ("convrot_gs", i32),
+                ("d_gated", vp), ("d_normed", vp), ("d_rot", vp), ("d_q", vp), ("d_scales", vp)]
+
+
+class UlyssesCfg(C.Structure):  # h3_ulysses_cfg
+    _fields_ = [("tp_size", i32), ("ulysses", i32), ("ring", i32), ("rank", i32), ("world_size", i32), ("comm", vp)]
+
+
+_ERR = (cs, sz)
+
+# name -> (restype, argtypes); `_ERR` marks the trailing (char *error, size_t error_size) pair
+_SIGS = {
+    "h3_cuda_create": (vp, (i32,) + _ERR),
+    "h3_cuda_free": (None, (vp,)),
+    "h3_cuda_release_heavy_workspace": (None, (vp,)),
+    "h3_cuda_pregrow_dit_scratch": (i32, (vp, sz, sz, sz, sz, sz) + _ERR),
+    "h3_cuda_pregrow_hadamard": (i32, (vp, i32) + _ERR),
+    "h3_cuda_dit_scratch_pregrown": (i32, (vp,)),
+    "h3_cuda_bind_device": (i32, (vp,) + _ERR),
+    "h3_cuda_device_count": (i32, _ERR),
+    "h3_cuda_probe": (i32, (i32, C.POINTER(DeviceInfo)) + _ERR),
+    "h3_cuda_get_info": (i32, (vp, C.POINTER(DeviceInfo))),
+    "h3_cuda_mem_info": (i32, (vp, C.POINTER(sz), C.POINTER(sz)) + _ERR),
+    "h3_cuda_set_graph_capture": (None, (vp, i32)),
+    "h3_cuda_graph_capture": (i32, (vp,)),
+    "h3_cuda_set_quiet": (None, (vp, i32)),
+    "h3_cuda_quiet": (i32, (vp,)),
+    "h3_cuda_set_op_stream": (i32, (vp, vp) + _ERR),
+    "h3_cuda_op_stream": (vp, (vp,)),
+    "h3_cuda_stream": (vp, (vp, i32)),
+    "h3_cuda_stream_count": (i32, ()),
+    "h3_cuda_event_record_default": (i32, (vp, C.POINTER(vp)) + _ERR),
+    "h3_cuda_event_record": (i32, (vp, vp) + _ERR),
+    "h3_cuda_stream_wait_event": (i32, (vp, vp) + _ERR),
+    "h3_cuda_event_destroy": (None, (vp,)),
+    "h3_cuda_host_alloc": (vp, (sz, C.POINTER(i32))),
+    "h3_cuda_host_free": (None, (vp, i32)),
+    "h3b_cuda_check": (i32, (vp, C.POINTER(i32)) + _ERR),
+    "h3b_cuda_launch_count": (C.c_ulonglong, (vp, i32)),
+    "h3_cuda_w4a8_weight_create": (i32, (vp, vp, sz, sz, vp, vp, vp, i32, C.POINTER(vp), dbl_p, dbl_p) + _ERR),
+    "h3_cuda_w4a8_weight_create_from_i8": (i32, (vp, vp, sz, sz, vp, C.POINTER(vp), dbl_p, i32) + _ERR),
+    "h3_cuda_w4a8_weight_upload_i8": (i32, (vp, vp, sz, sz, vp, i32) + _ERR),
+    "h3_cuda_w4a8_weight_ensure_ready": (i32, (vp,) + _ERR),
+    "h3_cuda_w4a8_weight_on_device": (i32, (vp, i32) + _ERR),
+    "h3_cuda_w4a8_weight_free": (None, (vp,)),
+    "h3_cuda_w4a8_weight_n": (sz, (vp,)),
+    "h3_cuda_w4a8_weight_k": (sz, (vp,)),
+    "h3_cuda_w4a8_weight_download_int8": (i32, (vp, vp) + _ERR),
+    "h3b_w4g_weight_create": (i32, (vp, vp, vp, sz, sz, i32, C.POINTER(vp)) + _ERR),
+    "h3b_w4a8_weight_data": (vp, (vp,)),
+    "h3b_w4a8_weight_scales": (vp, (vp,)),
+    "h3b_w4a8_weight_download_scales": (i32, (vp, vp) + _ERR),
+    "h3_cuda_gemm_i8_dequant_f32": (i32, (vp, vp, vp, vp, i32, vp, sz, sz, sz, vp, dbl_p, cs, sz) + _ERR),
+    "h3_cuda_gemm_i8_dequant_f32_w": (i32, (vp, vp, vp, vp, i32, sz, vp, dbl_p, cs, sz) + _ERR),
+    "h3_cuda_gemm_i8_dequant_f32_w_act": (i32, (vp, vp, vp, i32, sz, vp, dbl_p, dbl_p, cs, sz) + _ERR),
+    "h3_cuda_gemm_i8_dequant_f32_w_act_dev": (i32, (vp, vp, vp, i32, sz, vp, dbl_p, dbl_p, cs, sz) + _ERR),
+    "h3_cuda_gemm_i8_dequant_f32_w_act_dev_epi": (i32, (vp, vp, vp, i32, sz, vp, dbl_p, dbl_p, cs, sz,
+                                                        C.POINTER(DitGemmEpi)) + _ERR),
+    "h3_cuda_gemm_i8_dequant_f32_dev_pre_q": (i32, (vp, vp, vp, vp, sz, vp, dbl_p, dbl_p, cs, sz,
+                                                    C.POINTER(DitGemmEpi)) + _ERR),
+    "h3_cuda_convrot_act_f32_dd": (i32, (vp, vp, sz, sz, i32, vp) + _ERR),
+    "h3b_gemm_i8_dev": (i32, (vp, vp, vp, vp, sz, vp, C.POINTER(GemmEpi)) + _ERR),
+    "h3b_quantize_act_int8_dev": (i32, (vp, vp, i32, sz, sz, vp, vp) + _ERR),
+    "h3b_norm_dev": (i32, (vp, C.POINTER(NormArgs)) + _ERR),
+    "h3_cuda_adaln_f32_dev": (i32, (vp, vp, vp, vp, vp, sz, sz, sz, sz, sz, f32, vp, dbl_p) + _ERR),
+    "h3_cuda_gate_f32_dev": (i32, (vp, vp, vp, vp, vp, sz, sz, sz, sz, vp, dbl_p) + _ERR),
+    "h3_cuda_swiglu_f32_dev": (i32, (vp, vp, sz, sz, vp, dbl_p) + _ERR),
+    "h3_cuda_gate_adaln_f32_dev": (i32, (vp, vp, vp, vp, vp, vp, sz, sz, sz, sz, sz, sz, f32, vp, vp, dbl_p) + _ERR),
+    "h3_cuda_rms_norm_f32_dev": (i32, (vp, vp, vp, sz, sz, f32, vp) + _ERR),
+    "h3_cuda_qkv_rope_f32_dev": (i32, (vp, vp, vp, vp, vp, vp, sz, sz, sz, sz, f32, vp, vp, vp, dbl_p) + _ERR),
+    "h3_cuda_qkv_rope_f32_dev_layout": (i32, (vp, vp, vp, vp, vp, vp, sz, sz, sz, sz, f32, i32, i32, vp, vp, vp,
+                                              dbl_p) + _ERR),
+    "h3_cuda_f32_to_f16_dev": (i32, (vp, vp, vp, sz) + _ERR),
+    "h3_cuda_f16_to_f32_dev": (i32, (vp, vp, vp, sz) + _ERR),
+    "h3b_qkv_rope_dev": (i32, (vp, vp, i32, vp, vp, vp, vp, sz, sz, sz, sz, f32, i32, i32, vp, vp, vp, i32) + _ERR),
+    "h3b_cast_dev": (i32, (vp, vp, i32, vp, i32, sz) + _ERR),
+    "h3b_gelu_tanh_dev": (i32, (vp, vp, vp, i32, sz) + _ERR),
+    "h3_cuda_sdpa_f32_dev": (i32, (vp, vp, vp, vp, sz, sz, sz, f32, vp, dbl_p) + _ERR),
+    "h3_cuda_sdpa_f16_dev": (i32, (vp, vp, vp, vp, sz, sz, sz, f32, vp, dbl_p) + _ERR),
+    "h3_cuda_sdpa_f16_dev_ex": (i32, (vp, vp, vp, vp, sz, sz, sz, f32, i32, vp, dbl_p, cs, sz) + _ERR),
+    "h3_cuda_qkv_rope_sdpa_f16_dev": (i32, (vp, vp, vp, vp, vp, vp, sz, sz, sz, sz, f32, f32, i32, vp, dbl_p, dbl_p,
+                                            cs, sz) + _ERR),
+    "h3_cuda_sdpa_backend_name": (cs, ()),
+    "h3_cuda_sdpa_last_backend_name": (cs, ()),
+    "h3b_sdpa_bf16_dev": (i32, (vp, vp, sz, vp, sz, vp, sz, sz, sz, sz, sz, f32, vp, sz) + _ERR),
+    "h3_cuda_adaln_f32": (i32, (vp, vp, vp, vp, vp, sz, sz, sz, sz, sz, sz, f32, vp, dbl_p) + _ERR),
+    "h3_cuda_gate_f32": (i32, (vp, vp, vp, vp, vp, sz, sz, sz, sz, sz, vp, dbl_p) + _ERR),
+    "h3_cuda_swiglu_f32": (i32, (vp, vp, sz, sz, vp, dbl_p) + _ERR),
+    "h3_cuda_qkv_rope_f32": (i32, (vp, vp, vp, vp, vp, vp, sz, sz, sz, sz, f32, vp, vp, vp, dbl_p) + _ERR),
+    "h3_cuda_nvfp4_sf_bytes": (sz, (sz, sz)),
+    "h3_cuda_quantize_act_nvfp4_dev": (i32, (vp, vp, sz, sz, vp, vp) + _ERR),
+    "h3_ulysses_validate": (i32, (i32, i32, i32, i32, i32) + _ERR),
+    "h3_ulysses_pad_seq": (sz, (sz, i32)),
+    "h3_ulysses_local_rows": (sz, (sz, i32, i32)),
+}
+
+_lib = None
+
+
+def load() -> C.CDLL:
+    """Loads the library once; raises if it was not built."""
+    global _lib
+    if _lib is None:
+        if not LIB_PATH.exists():
+            raise H3Error(f"{LIB_PATH} is missing: run `python -m h3c_b200.build` (there is no fallback path)")
+        lib = C.CDLL(str(LIB_PATH))
+        for name, (res, args) in _SIGS.items():
+            fn = getattr(lib, name)
+            fn.restype = res
+            fn.argtypes = list(args)
+        _lib = lib
+    return _lib
+
+
+def declared_symbols():
+    return sorted(_SIGS)
+
+
+def ptr(t) -> int | None:
+    """Raw device (or host) address of a torch tensor / numpy array; None passes NULL."""
+    if t is None:
+        return None
+    if hasattr(t, "data_ptr"):
+        return t.data_ptr()
+    if hasattr(t, "ctypes"):
+        return t.ctypes.data
+    return int(t)
+
+
+def call(name: str, *args):
+    """Calls an entry point that ends in (error, error_size) and returns 1/0; raises H3Error on 0."""
+    lib = load()
+    err = C.create_string_buffer(ERR_LEN)
+    rc = getattr(lib, name)(*args, err, ERR_LEN)
+    if rc != 1:
+        raise H3Error(f"{name}: {err.value.decode(errors='replace') or 'failed'}")
+    return rc

@@ -1,0 +1,364 @@
+/* libh3_b200.so -- B200 (sm_100a) implementation of h3.c's DiT denoiser block path.
+ *
+ * C ABI only: plain pointers and sizes, no C++ or PyTorch types.  Entry points
+ * named h3_cuda_* / h3_ulysses_* keep the reference's name, argument order and
+ * meaning so a caller of the reference links against this library unchanged for
+ * this path; each one cites the reference declaration it replaces (file:line in
+ * the h3.c tree).  Entry points named h3b_* are additions (bf16 residual stream,
+ * the benchmark's block with cross-attention, one-process-per-GPU Ulysses) and
+ * say so.
+ *
+ * Conventions (as in the reference, h3_gpu_cuda.h / h3_ulysses.c:6-10):
+ *   - return int: 1 = ok, 0 = failure; message written to `error` (may be NULL)
+ *   - device pointers are raw; work is enqueued on h3_cuda_op_stream(cuda)
+ *     (NULL = legacy default stream); no implicit synchronisation in quiet mode
+ *   - `double *..._ms` outputs are optional; they are filled (with an event
+ *     synchronise) only when non-NULL and quiet mode is off
+ *   - one handle per device, one host thread per handle; handles are not
+ *     thread-safe
+ *   - there is no CPU fallback: every entry point fails if no sm_100 device or
+ *     kernel is available.
+ */
+#ifndef H3_B200_H
+#define H3_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ------------------------------------------------------------------ handle */
+
+typedef struct {                    /* h3_gpu_cuda.h:13-23 (same layout) */
+    int device_index;
+    char name[256];
+    int compute_major;
+    int compute_minor;
+    size_t total_memory_bytes;
+    size_t free_memory_bytes;
+    int multiprocessor_count;
+    int driver_version;
+    int runtime_version;
+} h3_cuda_device_info;
+
+typedef struct h3_cuda h3_cuda;     /* h3_gpu_cuda.h:25 */
+
+h3_cuda *h3_cuda_create(int device_index, char *error, size_t error_size);     /* h3_gpu_cuda.h:28 */
+void h3_cuda_free(h3_cuda *cuda);                                              /* :29 */
+void h3_cuda_release_heavy_workspace(h3_cuda *cuda);                           /* :33 */
+int h3_cuda_pregrow_dit_scratch(h3_cuda *cuda, size_t seq, size_t hidden, size_t heads,
+                                size_t head_dim, size_t ffn, char *error,
+                                size_t error_size);                            /* :40 */
+int h3_cuda_pregrow_hadamard(h3_cuda *cuda, int gs, char *error, size_t error_size); /* :47 */
+int h3_cuda_dit_scratch_pregrown(const h3_cuda *cuda);                         /* :53 */
+int h3_cuda_bind_device(h3_cuda *cuda, char *error, size_t error_size);        /* :57 */
+int h3_cuda_device_count(char *error, size_t error_size);                      /* :80 */
+int h3_cuda_probe(int device_index, h3_cuda_device_info *info, char *error,
+                  size_t error_size);                                          /* :81 */
+int h3_cuda_get_info(const h3_cuda *cuda, h3_cuda_device_info *info);          /* :83 */
+int h3_cuda_mem_info(h3_cuda *cuda, size_t *free_bytes, size_t *total_bytes, char *error,
+                     size_t error_size);                                       /* :86 */
+void h3_cuda_set_graph_capture(h3_cuda *cuda, int enabled);                    /* :209 */
+int h3_cuda_graph_capture(const h3_cuda *cuda);                                /* :210 */
+void h3_cuda_set_quiet(h3_cuda *cuda, int enabled);                            /* :212 */
+int h3_cuda_quiet(const h3_cuda *cuda);                                        /* :213 */
+int h3_cuda_set_op_stream(h3_cuda *cuda, void *stream, char *error, size_t error_size); /* :217 */
+void *h3_cuda_op_stream(const h3_cuda *cuda);                                  /* :219 */
+void *h3_cuda_stream(h3_cuda *cuda, int index);                                /* :227 */
+int h3_cuda_stream_count(void);                                                /* :228 */
+int h3_cuda_event_record_default(h3_cuda *cuda, void **out_event, char *error,
+                                 size_t error_size);                           /* :231 */
+int h3_cuda_event_record(void *stream, void *event, char *error, size_t error_size);      /* :234 */
+int h3_cuda_stream_wait_event(void *stream, void *event, char *error, size_t error_size); /* :237 */
+void h3_cuda_event_destroy(void *event);                                       /* :239 */
+void *h3_cuda_host_alloc(size_t bytes, int *pinned_out);                       /* :318 */
+void h3_cuda_host_free(void *p, int pinned);                                   /* :319 */
+
+/* Addition.  Synchronises the op stream and returns the device status word:
+ * 0 = every kernel launched through this handle ran to completion; non-zero =
+ * a kernel gave up a bounded wait (code in h3b_ptx.cuh) and its output is
+ * invalid.  Also reports sticky CUDA errors through `error`. */
+int h3b_cuda_check(h3_cuda *cuda, int *status_out, char *error, size_t error_size);
+/* Addition.  Kernel launches issued through this handle since the last call. */
+unsigned long long h3b_cuda_launch_count(h3_cuda *cuda, int reset);
+
+/* ----------------------------------------------------------------- weights */
+
+typedef struct h3_cuda_w4a8_weight h3_cuda_w4a8_weight;   /* h3_gpu_cuda.h:284 */
+
+/* Packed W4A8 (+ codebook / e4m3 group scales / per-channel scale) -> resident
+ * INT8 [N,K] + s_channel[N], decoded on the device.  h3_gpu_cuda.h:289-295 */
+int h3_cuda_w4a8_weight_create(h3_cuda *cuda, const int8_t *packed_host, size_t n, size_t k_half,
+                               const float *codebook16, const uint8_t *s_rel_f8,
+                               const float *s_channel, int group_size,
+                               h3_cuda_w4a8_weight **out, double *unpack_ms, double *h2d_ms,
+                               char *error, size_t error_size);
+/* Already-decoded INT8 [N,K] + weight_scale[N].  h3_gpu_cuda.h:304-308.  With
+ * borrow_host=0 the library takes ownership of both host buffers (allocated
+ * with malloc or h3_cuda_host_alloc) on success. */
+int h3_cuda_w4a8_weight_create_from_i8(h3_cuda *cuda, int8_t *w_i8, size_t n, size_t k,
+                                       float *s_channel, h3_cuda_w4a8_weight **out,
+                                       double *h2d_ms, int borrow_host, char *error,
+                                       size_t error_size);
+int h3_cuda_w4a8_weight_upload_i8(h3_cuda_w4a8_weight *weight, int8_t *w_i8, size_t n, size_t k,
+                                  float *s_channel, int borrow_host, char *error,
+                                  size_t error_size);                          /* :312 */
+int h3_cuda_w4a8_weight_ensure_ready(h3_cuda_w4a8_weight *weight, char *error,
+                                     size_t error_size);                       /* :326 */
+int h3_cuda_w4a8_weight_on_device(const h3_cuda_w4a8_weight *weight, int want_dev, char *error,
+                                  size_t error_size);                          /* :330 */
+void h3_cuda_w4a8_weight_free(h3_cuda_w4a8_weight *weight);                    /* :337 */
+size_t h3_cuda_w4a8_weight_n(const h3_cuda_w4a8_weight *weight);               /* :339 */
+size_t h3_cuda_w4a8_weight_k(const h3_cuda_w4a8_weight *weight);               /* :340 */
+int h3_cuda_w4a8_weight_download_int8(const h3_cuda_w4a8_weight *weight, int8_t *host_out,
+                                      char *error, size_t error_size);         /* :343 */
+/* Addition: symmetric int4 in groups of `group` along K with f16 scales (the
+ * benchmark's weight format): packed [N,K/2] (low nibble = even k, two's
+ * complement), scales_f16 [N,K/group].  Decoded on the device to the same
+ * resident INT8 + per-channel scale object: s_ch = max|s*q|/127,
+ * w_i8 = clamp(roundf(s*q / s_ch)). */
+int h3b_w4g_weight_create(h3_cuda *cuda, const uint8_t *packed_host, const uint16_t *scales_f16,
+                          size_t n, size_t k, int group, h3_cuda_w4a8_weight **out,
+                          char *error, size_t error_size);
+/* Addition: device pointers of the resident tensors. */
+const int8_t *h3b_w4a8_weight_data(const h3_cuda_w4a8_weight *weight);
+const float *h3b_w4a8_weight_scales(const h3_cuda_w4a8_weight *weight);
+int h3b_w4a8_weight_download_scales(const h3_cuda_w4a8_weight *weight, float *host_out, char *error,
+                                    size_t error_size);
+
+/* ------------------------------------------------------------------ linears */
+
+/* h3_gpu_cuda.h:378-401, same layout */
+typedef struct h3_cuda_dit_gemm_epi {
+    int swiglu;
+    int gate;
+    const float *d_residual;
+    const float *d_modulation;
+    const uint32_t *d_row_map;
+    const float *d_lora;
+    void *lora_ready;
+    size_t slots;
+    size_t gate_slot;
+    int requant_mode;
+    int requant_gs;
+    int8_t *d_rq_x;
+    float *d_rq_act;
+    float *d_rq_pre;
+    size_t requant_rows;
+    int y_f16;
+} h3_cuda_dit_gemm_epi;
+
+/* Host in / host out INT8 GEMM + dequant.  h3_gpu_cuda.h:274-280 */
+int h3_cuda_gemm_i8_dequant_f32(h3_cuda *cuda, const int8_t *x_i8, const int8_t *w_i8,
+                                const float *act_scales, int per_tensor_scale,
+                                const float *s_channel, size_t m, size_t n, size_t k, float *y_f32,
+                                double *gemm_ms, char *backend_out, size_t backend_out_size,
+                                char *error, size_t error_size);
+int h3_cuda_gemm_i8_dequant_f32_w(h3_cuda *cuda, const h3_cuda_w4a8_weight *weight,
+                                  const int8_t *x_i8, const float *act_scales, int per_tensor_scale,
+                                  size_t m, float *y_f32, double *gemm_ms, char *backend_out,
+                                  size_t backend_out_size, char *error, size_t error_size); /* :349 */
+int h3_cuda_gemm_i8_dequant_f32_w_act(h3_cuda *cuda, const h3_cuda_w4a8_weight *weight,
+                                      const float *x_f32, int convrot_groupsize, size_t m,
+                                      float *y_f32, double *prep_ms, double *gemm_ms,
+                                      char *backend_out, size_t backend_out_size, char *error,
+                                      size_t error_size);                      /* :360 */
+int h3_cuda_gemm_i8_dequant_f32_w_act_dev(h3_cuda *cuda, const h3_cuda_w4a8_weight *weight,
+                                          const float *d_x_f32, int convrot_groupsize, size_t m,
+                                          float *d_y_f32, double *prep_ms, double *gemm_ms,
+                                          char *backend_out, size_t backend_out_size, char *error,
+                                          size_t error_size);                  /* :368 */
+int h3_cuda_gemm_i8_dequant_f32_w_act_dev_epi(h3_cuda *cuda, const h3_cuda_w4a8_weight *weight,
+                                              const float *d_x_f32, int convrot_groupsize, size_t m,
+                                              float *d_y_f32, double *prep_ms, double *gemm_ms,
+                                              char *backend_out, size_t backend_out_size,
+                                              const h3_cuda_dit_gemm_epi *epi, char *error,
+                                              size_t error_size);              /* :403 */
+int h3_cuda_gemm_i8_dequant_f32_dev_pre_q(h3_cuda *cuda, const h3_cuda_w4a8_weight *weight,
+                                          const int8_t *d_x_i8, const float *d_act_in, size_t m,
+                                          float *d_y_f32, double *prep_ms, double *gemm_ms,
+                                          char *backend_out, size_t backend_out_size,
+                                          const h3_cuda_dit_gemm_epi *epi, char *error,
+                                          size_t error_size);                  /* :414 */
+int h3_cuda_convrot_act_f32_dd(h3_cuda *cuda, const float *d_x, size_t m, size_t k,
+                               int convrot_groupsize, float *d_y, char *error,
+                               size_t error_size);                             /* :137 */
+
+/* Additions: the general form every linear above is built on. */
+enum {            /* element types of activations / outputs */
+    H3B_F32 = 0,
+    H3B_BF16 = 1,
+    H3B_F16 = 2,
+    H3B_I32 = 3   /* raw int32 accumulators (parity checks) */
+};
+enum {            /* epilogue kinds */
+    H3B_EPI_PLAIN = 0,   /* y = a[m] s[n] acc                                         */
+    H3B_EPI_GATE = 1,    /* y = residual + (a s acc) * gate[row_map[m]][slot][n]; gate NULL -> 1 */
+    H3B_EPI_SWIGLU = 2,  /* y[m,c] = silu(g) * u, g = col c, u = col n/2 + c           */
+    H3B_EPI_GELU = 3     /* y = gelu_tanh(a s acc)                                     */
+};
+typedef struct h3b_gemm_epi {
+    int kind;                    /* H3B_EPI_* */
+    int out_dtype;               /* H3B_F32 / H3B_BF16 / H3B_F16 / H3B_I32 (plain only) */
+    const void *d_residual;      /* gate: [m,n] in out_dtype */
+    const float *d_modulation;   /* gate: [mod_rows, slots, n] or NULL */
+    const uint32_t *d_row_map;   /* gate: [m] or NULL (identity) */
+    size_t slots, gate_slot;
+} h3b_gemm_epi;
+/* d_x_i8 [m,k] codes, d_act_scales [m]; d_y is [m,n] ([m,n/2] for swiglu). */
+int h3b_gemm_i8_dev(h3_cuda *cuda, const h3_cuda_w4a8_weight *weight, const int8_t *d_x_i8,
+                    const float *d_act_scales, size_t m, void *d_y, const h3b_gemm_epi *epi,
+                    char *error, size_t error_size);
+/* Per-row absmax INT8 quantisation (reference rule, h3_w4a8_dequant.c:671):
+ * d_x [m,k] in `dtype`; writes codes [m,k] and scales [m]. */
+int h3b_quantize_act_int8_dev(h3_cuda *cuda, const void *d_x, int dtype, size_t m, size_t k,
+                              int8_t *d_q, float *d_scales, char *error, size_t error_size);
+/* One launch, one CTA per row:  (gate ->) RMSNorm * w (-> modulate) (-> round to dtype)
+ * (-> ConvRot per group) (-> per-row INT8 quant).  Optional parts are switched off by NULL
+ * pointers / zero values: d_branch (no gate stage), d_modulation (plain RMSNorm), identity=1
+ * (no normalisation at all: quantise / rotate d_x as it is), convrot_gs=0 (no rotation).
+ * Outputs that are NULL are not written. */
+typedef struct h3b_norm_args {
+    const void *d_x;             /* [rows,width] residual / input, `dtype` */
+    const void *d_branch;        /* optional [rows,width], `dtype` */
+    const float *d_norm_w;       /* [width] or NULL (ones) */
+    const float *d_modulation;   /* [mod_rows, slots, width] or NULL */
+    const uint32_t *d_row_map;   /* [rows] or NULL (identity) */
+    size_t rows, width, slots, gate_slot, shift_slot, scale_slot;
+    float epsilon;
+    int dtype;                   /* H3B_F32 / H3B_BF16 / H3B_F16: type of x, branch, gated, normed */
+    int identity;                /* 1: skip RMSNorm and modulation */
+    int convrot_gs;              /* 0, 4, 16, 64 or 256: Hadamard group size applied before the quant */
+    void *d_gated;               /* out: residual + branch*gate, `dtype` */
+    void *d_normed;              /* out: normalised (and modulated) row, `dtype` */
+    float *d_rot;                /* out: rotated row, f32 (h3_cuda_convrot_act_f32_dd) */
+    int8_t *d_q;                 /* out: INT8 codes */
+    float *d_scales;             /* out, with d_q: per-row scale */
+} h3b_norm_args;
+int h3b_norm_dev(h3_cuda *cuda, const h3b_norm_args *args, char *error, size_t error_size);
+
+/* -------------------------------------------------------------- elementwise */
+
+int h3_cuda_adaln_f32(h3_cuda *cuda, const float *x, const float *norm_w, const float *modulation,
+                      const uint32_t *row_map, size_t rows, size_t width, size_t slots,
+                      size_t mod_rows, size_t shift_slot, size_t scale_slot, float epsilon,
+                      float *out, double *op_ms, char *error, size_t error_size);   /* :694 */
+int h3_cuda_gate_f32(h3_cuda *cuda, const float *residual, const float *branch,
+                     const float *modulation, const uint32_t *row_map, size_t rows, size_t width,
+                     size_t slots, size_t mod_rows, size_t gate_slot, float *out, double *op_ms,
+                     char *error, size_t error_size);                               /* :700 */
+int h3_cuda_swiglu_f32(h3_cuda *cuda, const float *fused, size_t rows, size_t width, float *out,
+                       double *op_ms, char *error, size_t error_size);              /* :705 */
+int h3_cuda_qkv_rope_f32(h3_cuda *cuda, const float *qkv, const float *q_norm, const float *k_norm,
+                         const float *rope_cos, const float *rope_sin, size_t seq, size_t heads,
+                         size_t head_dim, size_t rope_half, float epsilon, float *query, float *key,
+                         float *value, double *op_ms, char *error, size_t error_size); /* :708 */
+int h3_cuda_adaln_f32_dev(h3_cuda *cuda, const float *d_x, const float *d_norm_w,
+                          const float *d_modulation, const uint32_t *d_row_map, size_t rows,
+                          size_t width, size_t slots, size_t shift_slot, size_t scale_slot,
+                          float epsilon, float *d_out, double *op_ms, char *error,
+                          size_t error_size);                                       /* :716 */
+int h3_cuda_gate_f32_dev(h3_cuda *cuda, const float *d_residual, const float *d_branch,
+                         const float *d_modulation, const uint32_t *d_row_map, size_t rows,
+                         size_t width, size_t slots, size_t gate_slot, float *d_out, double *op_ms,
+                         char *error, size_t error_size);                           /* :722 */
+int h3_cuda_swiglu_f32_dev(h3_cuda *cuda, const float *d_fused, size_t rows, size_t width,
+                           float *d_out, double *op_ms, char *error, size_t error_size); /* :727 */
+int h3_cuda_gate_adaln_f32_dev(h3_cuda *cuda, const float *d_residual, const float *d_branch,
+                               const float *d_norm_w, const float *d_modulation,
+                               const uint32_t *d_row_map, size_t rows, size_t width, size_t slots,
+                               size_t gate_slot, size_t shift_slot, size_t scale_slot, float epsilon,
+                               float *d_gated, float *d_normed, double *op_ms, char *error,
+                               size_t error_size);                                  /* :733 */
+int h3_cuda_rms_norm_f32_dev(h3_cuda *cuda, const float *d_x, const float *d_w, size_t rows,
+                             size_t width, float eps, float *d_out, char *error,
+                             size_t error_size);                                    /* :242 */
+int h3_cuda_qkv_rope_f32_dev(h3_cuda *cuda, const float *d_qkv, const float *d_q_norm,
+                             const float *d_k_norm, const float *d_rope_cos,
+                             const float *d_rope_sin, size_t seq, size_t heads, size_t head_dim,
+                             size_t rope_half, float epsilon, float *d_query, float *d_key,
+                             float *d_value, double *op_ms, char *error, size_t error_size); /* :748 */
+int h3_cuda_qkv_rope_f32_dev_layout(h3_cuda *cuda, const float *d_qkv, const float *d_q_norm,
+                                    const float *d_k_norm, const float *d_rope_cos,
+                                    const float *d_rope_sin, size_t seq, size_t heads,
+                                    size_t head_dim, size_t rope_half, float epsilon, int grouped,
+                                    int split_half, float *d_query, float *d_key, float *d_value,
+                                    double *op_ms, char *error, size_t error_size);  /* :755 */
+int h3_cuda_f32_to_f16_dev(h3_cuda *cuda, const float *d_in, void *d_out_half, size_t n, char *error,
+                           size_t error_size);                                      /* :196 */
+int h3_cuda_f16_to_f32_dev(h3_cuda *cuda, const void *d_in_half, float *d_out, size_t n, char *error,
+                           size_t error_size);                                      /* :198 */
+/* Additions: typed variants (dtype = H3B_F32 / H3B_BF16 for in and out). */
+int h3b_qkv_rope_dev(h3_cuda *cuda, const void *d_qkv, int in_dtype, const float *d_q_norm,
+                     const float *d_k_norm, const float *d_rope_cos, const float *d_rope_sin,
+                     size_t seq, size_t heads, size_t head_dim, size_t rope_half, float epsilon,
+                     int grouped, int split_half, void *d_query, void *d_key, void *d_value,
+                     int out_dtype, char *error, size_t error_size);
+int h3b_cast_dev(h3_cuda *cuda, const void *d_in, int in_dtype, void *d_out, int out_dtype, size_t n,
+                 char *error, size_t error_size);
+int h3b_gelu_tanh_dev(h3_cuda *cuda, const void *d_in, void *d_out, int dtype, size_t n, char *error,
+                      size_t error_size);
+
+/* ---------------------------------------------------------------- attention */
+
+/* F32 Q/K/V/out on the device, [seq, heads, head_dim]; computed in bf16 on the
+ * tensor cores with f32 softmax and accumulation.  h3_gpu_cuda.h:566, 579 */
+int h3_cuda_sdpa_f32_dev(h3_cuda *cuda, const float *d_query, const float *d_key,
+                         const float *d_value, size_t seq, size_t heads, size_t head_dim, float scale,
+                         float *d_out, double *sdpa_ms, char *error, size_t error_size);
+int h3_cuda_sdpa_f16_dev(h3_cuda *cuda, const float *d_query, const float *d_key,
+                         const float *d_value, size_t seq, size_t heads, size_t head_dim, float scale,
+                         float *d_out, double *sdpa_ms, char *error, size_t error_size);
+int h3_cuda_sdpa_f16_dev_ex(h3_cuda *cuda, const float *d_query, const float *d_key,
+                            const float *d_value, size_t seq, size_t heads, size_t head_dim,
+                            float scale, int attn_window, float *d_out, double *sdpa_ms,
+                            char *backend_out, size_t backend_out_size, char *error,
+                            size_t error_size);                                     /* :601 */
+/* QK-norm + RoPE into 16-bit staging, then attention.  h3_gpu_cuda.h:771 */
+int h3_cuda_qkv_rope_sdpa_f16_dev(h3_cuda *cuda, const float *d_qkv, const float *d_q_norm,
+                                  const float *d_k_norm, const float *d_rope_cos,
+                                  const float *d_rope_sin, size_t seq, size_t heads, size_t head_dim,
+                                  size_t rope_half, float epsilon, float scale, int attn_window,
+                                  float *d_attn_out, double *rope_ms, double *sdpa_ms,
+                                  char *backend_out, size_t backend_out_size, char *error,
+                                  size_t error_size);
+const char *h3_cuda_sdpa_backend_name(void);                                        /* :643 */
+const char *h3_cuda_sdpa_last_backend_name(void);                                   /* :680 */
+/* Addition: bf16 attention with explicit row strides (elements) and separate
+ * query / key counts (cross-attention).  q [lq, heads, 128] at q_stride per row,
+ * k/v [lk, heads, 128]; out [lq, heads*128] bf16 at o_stride.  Non-causal. */
+int h3b_sdpa_bf16_dev(h3_cuda *cuda, const void *d_q, size_t q_stride, const void *d_k,
+                      size_t k_stride, const void *d_v, size_t v_stride, size_t lq, size_t lk,
+                      size_t heads, size_t head_dim, float scale, void *d_out, size_t o_stride,
+                      char *error, size_t error_size);
+
+/* -------------------------------------------------------------------- NVFP4 */
+
+typedef struct h3_cuda_nvfp4_weight h3_cuda_nvfp4_weight;                           /* :445 */
+size_t h3_cuda_nvfp4_sf_bytes(size_t rows, size_t k);                               /* :450 */
+int h3_cuda_quantize_act_nvfp4_dev(h3_cuda *cuda, const float *d_x, size_t m, size_t k,
+                                   uint8_t *d_x_fp4, uint8_t *d_sf, char *error,
+                                   size_t error_size);                              /* :433 */
+
+/* ------------------------------------------------------------------ Ulysses */
+
+enum { H3_ULYSSES_PACKED_ALIGN = 64 };                                              /* h3_ulysses.h:10 */
+typedef struct h3_ulysses_cfg {                                                     /* h3_ulysses.h:12-19 */
+    int tp_size;
+    int ulysses;
+    int ring;
+    int rank;
+    int world_size;
+    void *comm;
+} h3_ulysses_cfg;
+int h3_ulysses_validate(int heads, int packed_align, int tp, int ulysses, int ring, char *err,
+                        size_t err_size);                                           /* h3_ulysses.h:21 */
+size_t h3_ulysses_pad_seq(size_t seq, int align);                                   /* :23 */
+size_t h3_ulysses_local_rows(size_t seq_pad, int ulysses, int rank);                /* :24 */
+
+#ifdef __cplusplus
+}
+#endif
+#endif

@@ -1,0 +1,342 @@
+"""Parity of the CUDA operators (called through the C ABI of libh3_b200.so) against the CPU oracle
+on the same seeded inputs.  Integer / byte results: bit-exact.  Float results: bit-exact where the
+kernel keeps the reference's operation order, otherwise within the tolerance written in the test."""
+import numpy as np
+import pytest
+
+from tests.conftest import rel_l2
+
+pytestmark = pytest.mark.gpu
+
+torch = pytest.importorskip("torch")
+
+
+@pytest.fixture(scope="module")
+def cuda():
+    import h3c_b200
+    c = h3c_b200.Cuda(0)
+    yield c
+    c.check()
+    c.close()
+
+
+def dev(a, dtype=None):
+    t = torch.from_numpy(np.ascontiguousarray(a)).cuda()
+    return t if dtype is None else t.to(dtype)
+
+
+def host(t):
+    return t.detach().float().cpu().numpy() if t.dtype in (torch.bfloat16, torch.float16) else t.detach().cpu().numpy()
+
+
+def acts(rng, m, k):
+    x = rng.normal(0, 1, (m, k)).astype(np.float32)
+    x[rng.random((m, k)) < 0.001] *= 20  # the benchmark's 0.1 % outliers
+    return x
+
+
+# ------------------------------------------------------------------ weights
+
+def test_w4a8_weight_decode_exact(cuda, oracle):
+    rng = np.random.default_rng(10)
+    n, k = 96, 512
+    packed = rng.integers(-128, 128, (n, k // 2), dtype=np.int8)
+    codebook = rng.normal(0, 50, 16).astype(np.float32)
+    s_rel = rng.integers(0x20, 0x50, (n, k // 16), dtype=np.uint8)
+    s_ch = rng.uniform(1e-3, 1e-2, n).astype(np.float32)
+    w = cuda.weight_from_w4a8(packed, codebook, s_rel, s_ch)
+    assert (w.n, w.k) == (n, k)
+    assert np.array_equal(w.download_int8(), oracle.w4a8_dequant_to_int8(packed, codebook, s_rel))
+    assert np.array_equal(w.download_scales(), s_ch)
+
+
+def test_w4g128_weight_decode_exact(cuda, oracle):
+    rng = np.random.default_rng(11)
+    wf = rng.normal(0, 0.02, (64, 512)).astype(np.float32)
+    packed, scales = oracle.w4g128_encode(wf, 128)
+    w = cuda.weight_from_w4g(packed, scales, 128)
+    w_i8, s = oracle.w4g128_decode_to_int8(packed, scales, 128)
+    assert np.array_equal(w.download_int8(), w_i8)
+    assert np.array_equal(w.download_scales(), s)
+    # the int4 -> int8 re-expression stays within half an int8 step of s*q
+    assert rel_l2(w_i8 * s[:, None], wf) < 0.12
+
+
+# ------------------------------------------------------------- row-wise ops
+
+@pytest.mark.parametrize("m,k", [(1, 64), (37, 3072), (5, 100)])
+def test_quantize_act_int8_exact(cuda, oracle, m, k):
+    rng = np.random.default_rng(12)
+    x = acts(rng, m, k)
+    x[0, : k // 2] = 0.0
+    if m > 2:
+        x[2] = 0.0  # zero row -> scale 1
+    q, s = cuda.quantize_act_int8(dev(x))
+    qo, so = oracle.quantize_act_int8(x)
+    assert np.array_equal(host(q), qo) and np.array_equal(host(s), so)
+    # bf16 input: same rule applied to the bf16 values
+    xb = dev(x, torch.bfloat16)
+    q, s = cuda.quantize_act_int8(xb)
+    qo, so = oracle.quantize_act_int8(host(xb))
+    assert np.array_equal(host(q), qo) and np.array_equal(host(s), so)
+
+
+def test_rowwise_f32_ops(cuda, oracle):
+    rng = np.random.default_rng(13)
+    rows, width, slots = 50, 3072, 6
+    x = rng.normal(0, 1.5, (rows, width)).astype(np.float32)
+    br = rng.normal(0, 1, (rows, width)).astype(np.float32)
+    nw = rng.normal(1, 0.1, width).astype(np.float32)
+    mod = rng.normal(0, 0.3, (3, slots, width)).astype(np.float32)
+    rmap = (np.arange(rows) % 3).astype(np.uint32)
+    dx, dbr, dnw, dmod, drm = dev(x), dev(br), dev(nw), dev(mod), dev(rmap.view(np.int32))
+    tol = 2e-6  # only the order of the row sum of squares differs
+    assert rel_l2(host(cuda.adaln_f32_dev(dx, dnw, dmod, drm, slots, 0, 1)), oracle.adaln(x, nw, mod, rmap, slots, 0, 1)) < tol
+    assert rel_l2(host(cuda.rms_norm_f32_dev(dx, dnw)), oracle.rms_norm(x, nw)) < tol
+    assert np.array_equal(host(cuda.gate_f32_dev(dx, dbr, dmod, drm, slots, 2)), oracle.gate(x, br, mod, rmap, slots, 2))
+    g, n = cuda.gate_adaln_f32_dev(dx, dbr, dnw, dmod, drm, slots, 2, 3, 4)
+    go, no = oracle.gate_adaln(x, br, nw, mod, rmap, slots, 2, 3, 4)
+    assert np.array_equal(host(g), go) and rel_l2(host(n), no) < tol
+    fused = rng.normal(0, 2, (rows, 2 * width)).astype(np.float32)
+    assert rel_l2(host(cuda.swiglu_f32_dev(dev(fused))), oracle.swiglu(fused)) < 1e-6
+    # identity row map (NULL): row r uses modulation row r
+    mod_id = rng.normal(0, 0.3, (rows, slots, width)).astype(np.float32)
+    assert rel_l2(host(cuda.adaln_f32_dev(dx, dnw, dev(mod_id), None, slots, 3, 4)),
+                  oracle.adaln(x, nw, mod_id, None, slots, 3, 4)) < tol
+
+
+def test_fused_adaln_quant_bf16(cuda, oracle):
+    """adaLN -> bf16 round -> INT8 codes in one launch.  The codes must be exactly the reference rule
+    applied to the kernel's own (bf16) normalised values; against the unfused CPU chain only the
+    reduction order differs, which may flip a few codes by one step."""
+    rng = np.random.default_rng(14)
+    rows, width = 64, 3072
+    x = dev(rng.normal(0, 1, (rows, width)).astype(np.float32), torch.bfloat16)
+    nw = rng.normal(1, 0.1, width).astype(np.float32)
+    mod = rng.normal(0, 0.3, (1, 6, width)).astype(np.float32)
+    rmap = np.zeros(rows, np.uint32)
+    normed = torch.empty_like(x)
+    q = torch.empty((rows, width), dtype=torch.int8, device="cuda")
+    s = torch.empty(rows, dtype=torch.float32, device="cuda")
+    cuda.norm(x, norm_w=dev(nw), modulation=dev(mod), row_map=dev(rmap.view(np.int32)), slots=6, shift_slot=0,
+              scale_slot=1, normed=normed, q=q, scales=s)
+    qo, so = oracle.quantize_act_int8(host(normed))
+    assert np.array_equal(host(q), qo) and np.array_equal(host(s), so)
+    cpu = oracle.bf16_round(oracle.adaln(host(x), nw, mod, rmap, 6, 0, 1))
+    qc, sc = oracle.quantize_act_int8(cpu)
+    diff = np.abs(host(q).astype(np.int32) - qc.astype(np.int32))
+    assert diff.max() <= 1 and (diff != 0).mean() < 5e-3
+    assert rel_l2(host(normed), cpu) < 2e-3
+
+
+@pytest.mark.parametrize("gs", [256, 16])
+def test_convrot(cuda, oracle, gs):
+    rng = np.random.default_rng(15)
+    x = acts(rng, 33, 1024)
+    y = host(cuda.convrot_act_f32_dd(dev(x), gs))
+    assert rel_l2(y, oracle.convrot(x, gs)) < 1e-6
+    # fused rotate + quantise: codes follow the reference rule on the kernel's rotated values
+    rot = torch.empty((33, 1024), dtype=torch.float32, device="cuda")
+    q = torch.empty((33, 1024), dtype=torch.int8, device="cuda")
+    s = torch.empty(33, dtype=torch.float32, device="cuda")
+    cuda.norm(dev(x), identity=True, convrot_gs=gs, rot=rot, q=q, scales=s)
+    qo, so = oracle.quantize_act_int8(host(rot))
+    assert np.array_equal(host(q), qo) and np.array_equal(host(s), so)
+
+
+def test_qkv_rope(cuda, oracle):
+    rng = np.random.default_rng(16)
+    heads, hd = 3, 128
+    pt, ph, pw = oracle.fill_video_pos(16, 3, 8, 12)
+    inv_freq = (1.0 / (10000.0 ** (np.arange(16) / 16.0))).astype(np.float32)
+    cos, sin = oracle.rope_tables(inv_freq, pt, ph, pw, 1.0)
+    seq = len(pt)
+    qkv = rng.normal(0, 1, (seq, 3 * heads * hd)).astype(np.float32)
+    qn, kn = rng.normal(1, 0.1, hd).astype(np.float32), rng.normal(1, 0.1, hd).astype(np.float32)
+    for grouped, split in ((0, 1), (0, 0), (1, 1)):
+        q, k, v = cuda.qkv_rope(dev(qkv), dev(qn), dev(kn), dev(cos), dev(sin), heads, hd, 48, grouped=grouped,
+                                split_half=split)
+        qo, ko, vo = oracle.qkv_rope(qkv, qn, kn, cos, sin, heads, hd, 48, grouped=grouped, split_half=split)
+        assert rel_l2(host(q), qo) < 1e-6 and rel_l2(host(k), ko) < 1e-6 and np.array_equal(host(v), vo)
+    q, k, v = cuda.qkv_rope(dev(qkv), dev(qn), dev(kn), None, None, heads, hd, 0)
+    qo, ko, vo = oracle.qkv_rope(qkv, qn, kn, None, None, heads, hd, 0)
+    assert rel_l2(host(q), qo) < 1e-6 and rel_l2(host(k), ko) < 1e-6
+
+
+# ---------------------------------------------------------------------- GEMM
+
+def make_weight(cuda, rng, n, k):
+    w_i8 = rng.integers(-127, 128, (n, k), dtype=np.int8)
+    s = rng.uniform(1e-3, 1e-2, n).astype(np.float32)
+    return cuda.weight_from_i8(w_i8, s), w_i8, s
+
+
+@pytest.mark.parametrize("m,n,k", [(1, 128, 128), (127, 256, 256), (129, 384, 512), (300, 640, 3072),
+                                   (16, 256, 144), (257, 24, 64)])
+def test_gemm_int32_accumulators_exact(cuda, m, n, k):
+    import h3c_b200
+    rng = np.random.default_rng(20 + m)
+    w, w_i8, _ = make_weight(cuda, rng, n, k)
+    x = rng.integers(-127, 128, (m, k), dtype=np.int8)
+    a = torch.ones(m, dtype=torch.float32, device="cuda")
+    acc = cuda.gemm_i8(w, dev(x), a, out_dtype=torch.int32)
+    cuda.check()
+    assert np.array_equal(host(acc), x.astype(np.int32) @ w_i8.astype(np.int32).T)
+
+
+def test_gemm_epilogues(cuda, oracle):
+    import h3c_b200
+    rng = np.random.default_rng(30)
+    m, n, k, slots = 200, 512, 256, 6
+    w, w_i8, s = make_weight(cuda, rng, n, k)
+    x = acts(rng, m, k)
+    xq, xs = oracle.quantize_act_int8(x)
+    dq, ds = dev(xq), dev(xs)
+    acc = oracle.gemm_i8_i32(xq, w_i8)
+    # plain, f32: same operation order as the reference -> identical bits
+    y = cuda.gemm_i8(w, dq, ds)
+    assert np.array_equal(host(y), oracle.gemm_i8_dequant(xq, w_i8, xs, s))
+    # gate + residual with a row map, f32
+    res = rng.normal(0, 1, (m, n)).astype(np.float32)
+    mod = rng.normal(0, 0.5, (3, slots, n)).astype(np.float32)
+    rmap = (np.arange(m) % 3).astype(np.uint32)
+    y = cuda.gemm_i8(w, dq, ds, kind=h3c_b200.EPI_GATE, residual=dev(res), modulation=dev(mod),
+                     row_map=dev(rmap.view(np.int32)), slots=slots, gate_slot=5)
+    assert np.array_equal(host(y), oracle.dequant_gate(acc, xs, s, res, mod, rmap, slots, 5))
+    # residual only (no modulation)
+    y = cuda.gemm_i8(w, dq, ds, kind=h3c_b200.EPI_GATE, residual=dev(res))
+    assert np.array_equal(host(y), res + oracle.gemm_i8_dequant(xq, w_i8, xs, s))
+    # SwiGLU (expf) and tanh-GELU (tanhf): device libm differs from glibc in the last ulps
+    y = cuda.gemm_i8(w, dq, ds, kind=h3c_b200.EPI_SWIGLU)
+    assert y.shape == (m, n // 2) and rel_l2(host(y), oracle.dequant_swiglu(acc, xs, s)) < 1e-6
+    y = cuda.gemm_i8(w, dq, ds, kind=h3c_b200.EPI_GELU)
+    assert rel_l2(host(y), oracle.dequant_gelu(acc, xs, s)) < 1e-6
+    # bf16 outputs are the f32 results rounded once
+    y = cuda.gemm_i8(w, dq, ds, out_dtype=torch.bfloat16)
+    assert np.array_equal(host(y), oracle.bf16_round(oracle.gemm_i8_dequant(xq, w_i8, xs, s)))
+    resb = dev(res, torch.bfloat16)
+    y = cuda.gemm_i8(w, dq, ds, kind=h3c_b200.EPI_GATE, out_dtype=torch.bfloat16, residual=resb, modulation=dev(mod),
+                     row_map=dev(rmap.view(np.int32)), slots=slots, gate_slot=2)
+    assert np.array_equal(host(y), oracle.bf16_round(oracle.dequant_gate(acc, xs, s, host(resb), mod, rmap, slots, 2)))
+    cuda.check()
+
+
+def test_reference_linear_entry_point(cuda, oracle):
+    """h3_cuda_gemm_i8_dequant_f32_w_act_dev(_epi): f32 activations in, ConvRot + quant + GEMM inside."""
+    from h3c_b200.lib import DitGemmEpi
+    rng = np.random.default_rng(31)
+    m, n, k = 70, 256, 512
+    w, w_i8, s = make_weight(cuda, rng, n, k)
+    x = acts(rng, m, k)
+    for gs in (0, 256):
+        y = cuda.gemm_i8_dequant_f32_w_act_dev(w, dev(x), gs)
+        xq, xs = oracle.quantize_act_int8(oracle.convrot(x, gs))
+        ref = oracle.gemm_i8_dequant(xq, w_i8, xs, s)
+        if gs == 0:
+            assert np.array_equal(host(y), ref)
+        else:
+            assert rel_l2(host(y), ref) < 2e-3  # butterfly vs dense rotation: a few codes move by one step
+    epi = DitGemmEpi()
+    epi.swiglu = 1
+    y = cuda.gemm_i8_dequant_f32_w_act_dev(w, dev(x), 0, epi)
+    xq, xs = oracle.quantize_act_int8(x)
+    assert rel_l2(host(y), oracle.dequant_swiglu(oracle.gemm_i8_i32(xq, w_i8), xs, s)) < 1e-6
+
+
+def test_gemm_full_size_sampled(cuda):
+    """Benchmark shape (M=6144, K=3072, N=9216): exact accumulators on sampled rows, every column."""
+    rng = np.random.default_rng(32)
+    m, n, k = 6144, 9216, 3072
+    w, w_i8, _ = make_weight(cuda, rng, n, k)
+    x = rng.integers(-127, 128, (m, k), dtype=np.int8)
+    a = torch.ones(m, dtype=torch.float32, device="cuda")
+    acc = cuda.gemm_i8(w, dev(x), a, out_dtype=torch.int32)
+    cuda.check()
+    rows = np.concatenate([[0, 127, 128, m - 1], rng.integers(0, m, 28)])
+    want = x[rows].astype(np.int32) @ w_i8.astype(np.int32).T
+    assert np.array_equal(host(acc[torch.from_numpy(rows).cuda()]), want)
+    # linearity in the activation scale (size-independent property of the dequant epilogue)
+    y1 = cuda.gemm_i8(w, dev(x), a)
+    y2 = cuda.gemm_i8(w, dev(x), 2 * a)
+    assert torch.equal(y2, 2 * y1)
+
+
+# ----------------------------------------------------------------- attention
+
+@pytest.mark.parametrize("lq,lk,heads", [(128, 128, 2), (200, 333, 3), (64, 1, 1), (384, 1024, 2)])
+def test_sdpa_bf16(cuda, oracle, lq, lk, heads):
+    rng = np.random.default_rng(40 + lq)
+    hd = 128
+    q = dev(rng.normal(0, 1, (lq, heads, hd)).astype(np.float32), torch.bfloat16)
+    k = dev(rng.normal(0, 1, (lk, heads, hd)).astype(np.float32), torch.bfloat16)
+    v = dev(rng.normal(0, 1, (lk, heads, hd)).astype(np.float32), torch.bfloat16)
+    out = cuda.sdpa_bf16(q, k, v)
+    cuda.check()
+    want = oracle.sdpa(host(q), host(k), host(v))
+    # bf16 probabilities and bf16 output: 2e-3 relative L2 against the f32 evaluation of the same inputs
+    assert rel_l2(host(out), want) < 4e-3
+
+
+def test_sdpa_cross_strided(cuda, oracle):
+    """Cross-attention: K and V are the two halves of one [T, 2*D] projection (row stride 2*D)."""
+    rng = np.random.default_rng(45)
+    lq, t, heads, hd = 300, 512, 2, 128
+    D = heads * hd
+    q = dev(rng.normal(0, 1, (lq, heads, hd)).astype(np.float32), torch.bfloat16)
+    kv = dev(rng.normal(0, 1, (t, 2 * D)).astype(np.float32), torch.bfloat16)
+    k = kv[:, :D].view(t, heads, hd)
+    v = kv[:, D:].view(t, heads, hd)
+    out = cuda.sdpa_bf16(q, k, v)
+    cuda.check()
+    want = oracle.sdpa(host(q), host(k.contiguous()), host(v.contiguous()))
+    assert rel_l2(host(out), want) < 4e-3
+
+
+def test_sdpa_full_size_sampled(cuda, oracle):
+    """Self-attention at the benchmark's 6,144 tokens (2 of 24 heads): sampled query rows against the oracle."""
+    rng = np.random.default_rng(46)
+    L, heads, hd = 6144, 2, 128
+    q = dev(rng.normal(0, 1, (L, heads, hd)).astype(np.float32), torch.bfloat16)
+    k = dev(rng.normal(0, 1, (L, heads, hd)).astype(np.float32), torch.bfloat16)
+    v = dev(rng.normal(0, 1, (L, heads, hd)).astype(np.float32), torch.bfloat16)
+    out = cuda.sdpa_bf16(q, k, v)
+    cuda.check()
+    rows = np.concatenate([[0, 127, 128, L - 1], rng.integers(0, L, 12)])
+    want = oracle.sdpa(host(q)[rows], host(k), host(v))
+    assert rel_l2(host(out)[rows], want) < 4e-3
+    # softmax rows sum to one: with V = 1 the output is exactly 1 up to bf16 rounding of P
+    ones = torch.ones_like(v)
+    o1 = cuda.sdpa_bf16(q, k, ones)
+    assert float((o1.float() - 1).abs().max()) < 2e-2
+
+
+def test_reference_sdpa_entry_point(cuda, oracle):
+    rng = np.random.default_rng(47)
+    seq, heads, hd = 150, 2, 128
+    q, k, v = (rng.normal(0, 1, (seq, heads, hd)).astype(np.float32) for _ in range(3))
+    out = cuda.sdpa_f16_dev(dev(q), dev(k), dev(v))
+    cuda.check()
+    assert rel_l2(host(out), oracle.sdpa(q, k, v)) < 1e-2  # inputs rounded to bf16 as well
+
+
+# --------------------------------------------------------------------- NVFP4
+
+@pytest.mark.parametrize("m,k", [(5, 64), (130, 256), (128, 3072)])
+def test_quantize_act_nvfp4_exact(cuda, oracle, m, k):
+    rng = np.random.default_rng(50 + m)
+    x = acts(rng, m, k)
+    x[0, :16] = 0.0          # all-zero block -> scale byte for 1.0
+    x[1 % m, 16:32] = 1e-9   # underflow -> clamped to byte 1
+    packed, sf = cuda.quantize_act_nvfp4(dev(x))
+    po, so = oracle.quantize_nvfp4(x)
+    assert np.array_equal(host(packed), po)
+    assert np.array_equal(host(sf), so)
+
+
+def test_host_buffer_adaln(cuda, oracle):
+    rng = np.random.default_rng(51)
+    x = rng.normal(0, 1, (9, 64)).astype(np.float32)
+    nw = rng.normal(1, 0.1, 64).astype(np.float32)
+    mod = rng.normal(0, 0.3, (3, 6, 64)).astype(np.float32)
+    rmap = (np.arange(9) % 3).astype(np.uint32)
+    assert rel_l2(cuda.adaln_f32(x, nw, mod, rmap, 6, 0, 1), oracle.adaln(x, nw, mod, rmap, 6, 0, 1)) < 2e-6
