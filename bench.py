@@ -1,0 +1,396 @@
+"""Benchmark of the DiT denoiser step (BASELINE.json's metric) on N GPUs of one node.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+
+N = 1 (default): the full 50-block W4A8 step at 6,144 video tokens (6x32x32 patch grid) + 512 text
+tokens, D = 3072, 24 x 128 heads, FFN 12288, bf16 residual stream, t = 0.5 -- BASELINE.json configs[3].
+N > 1 (under torchrun, one rank per GPU): the Ulysses sequence-parallel step at 50,220 tokens
+(31x30x54 grid) -- configs[4].
+`--impl reference` times the reference's CPU implementation of the same block on the host cores.
+
+Prints ONE JSON line (rank 0).  `value` is ms per step with every input resident in HBM; `e2e` is the
+same step through the host-buffer entry point (h3b_dit_layers_forward_f32) with pinned host arrays,
+host<->device copies inside the timed region.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import tempfile
+import time
+from concurrent.futures import ThreadPoolExecutor
+from pathlib import Path
+
+import numpy as np
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+METRIC = "dit_denoiser_ms_per_step_50_blocks"
+UNIT = "ms/step"
+
+GEO = dict(dim=3072, heads=24, head_dim=128, ffn=12288, n_blocks=50, text=512)
+GRID_1GPU = (6, 32, 32)      # 6,144 tokens
+GRID_ULYSSES = (31, 30, 54)  # 50,220 tokens
+
+
+def peaks():
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        d = json.loads(p.read_text())
+        return dict(hbm=d["hbm_gbs"], bf16=d["bf16_tflops"], bf16_sustained=d["bf16_tflops_sustained"], src="measured")
+    return dict(hbm=6650.0, bf16=1590.0, bf16_sustained=1400.0, src="fallback")
+
+
+def block_flops(m, text, dim, ffn):
+    """Algorithmic work of one block (FLOPs = 2MNK for linears, 4 Lq Lk H d for attention)."""
+    lin = 2.0 * m * (dim * (3 * dim + dim + dim + dim + ffn) + ffn * dim) + 2.0 * text * dim * 2 * dim
+    attn = 4.0 * m * m * dim + 4.0 * m * text * dim
+    return lin, attn
+
+
+class ClockSampler:
+    """nvidia-smi clock / throttle-reason samples while the timed region runs."""
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index = index
+        self.file = tempfile.NamedTemporaryFile("w+", suffix=".csv", delete=False)
+        self.proc = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.index), f"--query-gpu={self.Q}",
+                                          "--format=csv,noheader,nounits", "-lms", "100"], stdout=self.file,
+                                         stderr=subprocess.DEVNULL)
+        except OSError:
+            self.proc = None
+
+    def stop(self):
+        out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        if self.proc is None:
+            return out
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        self.file.flush()
+        self.file.seek(0)
+        sm, mx, reasons = [], [], set()
+        for line in self.file.read().splitlines():
+            f = [x.strip() for x in line.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1]))
+                mx.append(float(f[2]))
+            except ValueError:
+                continue
+            for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[5:9]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        os.unlink(self.file.name)
+        if sm:
+            # keep the samples taken under load (upper half), report their median
+            load = sorted(sm)[len(sm) // 2:]
+            out.update(sm_mhz=float(np.median(load)), sm_max_mhz=max(mx), reasons=sorted(reasons), samples=len(sm))
+        return out
+
+
+# ------------------------------------------------------------------------------- CPU baseline
+
+def cpu_block_sample(kind: str, threads: int, budget_s: float = 15.0):
+    """Times the reference's CPU block path on a bounded row sample of the N=1 workload.
+
+    kind "reference": the reference's own C functions (oracle/_ref/libh3_ref.so) driven over row slices
+    from `threads` host threads (its loops are serial); attention rows use the rectangular restatement of
+    the reference's loop (its own function only handles Lq == Lk).  kind "port": the CPU restatement.
+    Returns (ms_per_step_extrapolated, description)."""
+    from oracle.pyoracle import Oracle, Ref
+    dim, heads, hd, ffn, text_len = GEO["dim"], GEO["heads"], GEO["head_dim"], GEO["ffn"], GEO["text"]
+    m_full = GRID_1GPU[0] * GRID_1GPU[1] * GRID_1GPU[2]
+    oracle = Oracle(threads=1)
+    impl = Ref() if kind == "reference" else oracle
+    rng = np.random.default_rng(0)
+
+    def qweight(n, k):
+        w = rng.integers(-127, 128, (n, k), dtype=np.int8)
+        return w, rng.uniform(1e-4, 1e-3, n).astype(np.float32)
+
+    W = {k: qweight(*s) for k, s in dict(qkv=(3 * dim, dim), o=(dim, dim), cq=(dim, dim), ckv=(2 * dim, dim),
+                                         co=(dim, dim), up=(ffn, dim), down=(dim, ffn)).items()}
+    norm = rng.normal(1, 0.1, dim).astype(np.float32)
+    qn = rng.normal(1, 0.1, hd).astype(np.float32)
+    mod = rng.normal(0, 0.3, (1, 6, dim)).astype(np.float32)
+    inv_freq = (1.0 / (10000.0 ** (np.arange(16) / 16.0))).astype(np.float32)
+    pt, ph, pw = oracle.fill_video_pos(text_len, GRID_1GPU[0], 2 * GRID_1GPU[1], 2 * GRID_1GPU[2])
+    cos, sin = oracle.rope_tables(inv_freq, pt, ph, pw, 1.0)
+    k_all = rng.normal(0, 1, (m_full, heads, hd)).astype(np.float32)
+    v_all = rng.normal(0, 1, (m_full, heads, hd)).astype(np.float32)
+    ckv_all = rng.normal(0, 1, (text_len, 2 * dim)).astype(np.float32)
+    ck = np.ascontiguousarray(ckv_all[:, :dim]).reshape(text_len, heads, hd)
+    cv = np.ascontiguousarray(ckv_all[:, dim:]).reshape(text_len, heads, hd)
+
+    def linear(x, name):
+        q, s = impl.quantize_act_int8(impl.convrot(x, 0))
+        return impl.gemm_i8_dequant(q, W[name][0], s, W[name][1])
+
+    def rows_job(r0, r1):
+        n = r1 - r0
+        x = rng.normal(0, 1, (n, dim)).astype(np.float32)
+        rmap = np.zeros(n, np.uint32)
+        a = impl.adaln(x, norm, mod, rmap, 6, 0, 1)
+        q, _, _ = impl.qkv_rope(linear(a, "qkv"), qn, qn, cos[r0:r1], sin[r0:r1], heads, hd, 48)
+        att = oracle.sdpa(q, k_all, v_all)
+        x1 = impl.gate(x, linear(att, "o"), mod, rmap, 6, 2)
+        cq = linear(impl.rms_norm(x1, norm), "cq").reshape(n, heads, hd)
+        x2 = x1 + linear(oracle.sdpa(cq, ck, cv), "co")
+        up = linear(impl.adaln(x2, norm, mod, rmap, 6, 3, 4), "up")
+        h = (0.5 * up * (1.0 + np.tanh(0.7978845608028654 * (up + 0.044715 * up ** 3)))).astype(np.float32)
+        return impl.gate(x2, linear(h, "down"), mod, rmap, 6, 5)
+
+    def text_job(r0, r1):
+        return linear(rng.normal(0, 1, (r1 - r0, dim)).astype(np.float32), "ckv")
+
+    def run(rows_per_thread):
+        t0 = time.perf_counter()
+        with ThreadPoolExecutor(threads) as ex:
+            list(ex.map(lambda i: rows_job(i * rows_per_thread, (i + 1) * rows_per_thread), range(threads)))
+            list(ex.map(lambda i: text_job(i, i + 1), range(threads)))
+        return time.perf_counter() - t0
+
+    t1 = run(1)                                    # calibration: one row per thread
+    rpt = int(max(1, min(128, budget_s / max(t1, 1e-3))))
+    t = run(rpt) if rpt > 1 else t1
+    rows, trow = threads * rpt, threads
+    # the sample covered `rows` of m_full query rows and `trow` of text_len text rows of ONE block
+    frac = t / (rows / m_full + 0.0)               # crude: text rows are <1 % of the work, scale by query rows
+    ms_step = frac * GEO["n_blocks"] * 1e3
+    desc = (f"{rows} of {m_full} query rows (all linears, QK-norm+RoPE, self-attention against all {m_full} keys, "
+            f"cross-attention, FFN) + {trow} of {text_len} text rows of one block, {t:.1f} s on {threads} threads, "
+            f"scaled by rows x 50 blocks; attention rows via the rectangular form of the reference loop")
+    return ms_step, desc
+
+
+def reference_arm(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    from oracle.pyoracle import Ref
+    kind = "reference" if Ref.available() else "port"
+    cores = os.cpu_count() or 1
+    vals = []
+    desc = ""
+    for _ in range(max(1, min(args.steps, 2))):    # each "step" is one bounded sample; two are plenty on a CPU
+        v, desc = cpu_block_sample(kind, cores, budget_s=20.0)
+        vals.append(v)
+    value = float(np.median(vals))
+    line = {"impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": value, "higher_is_better": False,
+            "scaling": "weak", "vs_baseline": None, "dtype": "int8 linears + f32 attention (CPU)", "data": "synthetic",
+            "config": workload_config(1),
+            "cpu_baseline": {"value": value, "unit": UNIT, "cores": cores, "kind": kind, "sample": desc},
+            "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+            "gpu_launches": 0}
+    print(json.dumps(line))
+
+
+def workload_config(n_gpus):
+    grid = GRID_1GPU if n_gpus == 1 else GRID_ULYSSES
+    tokens = grid[0] * grid[1] * grid[2]
+    return {"workload": ("50-block W4A8 DiT denoiser step, 512x512x22 frames" if n_gpus == 1 else
+                         "Ulysses sequence-parallel 50-block W4A8 DiT step, 864x480x121 frames"),
+            "tokens": tokens, "patch_grid": list(grid), "text_tokens": GEO["text"], "dim": GEO["dim"],
+            "heads": GEO["heads"], "head_dim": GEO["head_dim"], "ffn": GEO["ffn"], "blocks": GEO["n_blocks"],
+            "weights": "int4 group-128 f16 scales, decoded once to resident int8 + per-channel scale",
+            "activations": "per-token absmax int8, bf16 residual stream", "timestep": 0.5,
+            "parallelism": "single GPU" if n_gpus == 1 else f"ulysses{n_gpus}",
+            "l2": "each step streams 3.4 GB of weights and >1 GB of activations, far above the 126 MB L2"}
+
+
+# -------------------------------------------------------------------------------------- GPU arm
+
+def gpu_arm(args):
+    import torch
+    import h3c_b200
+    from h3c_b200 import dit as D
+    from oracle.pyoracle import Oracle  # checker side only: positions / RoPE tables of the workload
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus:
+        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}: launch with torchrun --nproc-per-node {args.gpus}")
+    if world > 1:
+        raise SystemExit("the Ulysses multi-GPU step is not wired into bench.py yet")
+    torch.cuda.set_device(local)
+    cuda = h3c_b200.Cuda(local)
+    cuda.set_quiet(True)
+    geo = D.DitGeometry(dim=GEO["dim"], heads=GEO["heads"], head_dim=GEO["head_dim"], ffn=GEO["ffn"],
+                        n_blocks=GEO["n_blocks"], mod_rows=1, t_dim=256, kind=D.BLOCK_CROSS_GELU, stream_dtype=D.BF16)
+    dit = D.build_synthetic(cuda, geo, seed=0)
+    grid = GRID_1GPU
+    seq, text_len = grid[0] * grid[1] * grid[2], GEO["text"]
+    oracle = Oracle()
+    inv_freq = (1.0 / (10000.0 ** (np.arange(16) / 16.0))).astype(np.float32)
+    pt, ph, pw = oracle.fill_video_pos(text_len, grid[0], 2 * grid[1], 2 * grid[2])
+    cos_h, sin_h = oracle.rope_tables(inv_freq, pt, ph, pw, 1.0)
+    rng = np.random.default_rng(0)
+    # host (pinned) inputs of one step
+    x_h = torch.from_numpy(rng.normal(0, 1, (seq, geo.dim)).astype(np.float32)).pin_memory()
+    text_h = torch.from_numpy(rng.normal(0, 1, (text_len, geo.dim)).astype(np.float32)).pin_memory()
+    cos_p, sin_p = torch.from_numpy(cos_h).pin_memory(), torch.from_numpy(sin_h).pin_memory()
+    # timestep t = 0.5: sinusoidal feature of width t_dim (synthetic stand-in for the embedding table)
+    half = geo.t_dim // 2
+    freqs = np.exp(-np.log(10000.0) * np.arange(half) / half)
+    t_feat_h = torch.from_numpy(np.concatenate([np.cos(500.0 * freqs), np.sin(500.0 * freqs)]).astype(np.float32)).pin_memory()
+    y_h = torch.empty((seq, geo.dim), dtype=torch.float32).pin_memory()
+    # device-resident copies
+    x_d = x_h.cuda().to(torch.bfloat16)
+    text_d = text_h.cuda().to(torch.bfloat16)
+    cos_d, sin_d, t_d = cos_p.cuda(), sin_p.cuda(), t_feat_h.cuda()
+    rmap_d = torch.zeros(seq, dtype=torch.int32, device="cuda")
+    y_d = torch.empty_like(x_d)
+    dit.reserve(seq, text_len)
+
+    def step_resident():
+        dit.project_modulation(t_d)
+        dit.layers_forward(x_d, cos_d, sin_d, row_map=rmap_d, text=text_d, out=y_d)
+
+    def step_e2e():
+        dit.layers_forward_f32(t_feat_h, x_h, cos_p, sin_p, text=text_h, out=y_h)
+
+    for _ in range(args.warmup):
+        step_resident()
+    torch.cuda.synchronize()
+    cuda.check()
+
+    sampler = ClockSampler(local)
+    sampler.start()
+    time.sleep(0.3)
+    cuda.launch_count(reset=True)
+    ev = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps + 1)]
+    torch.cuda.synchronize()
+    ev[0].record()
+    for i in range(args.steps):
+        step_resident()
+        ev[i + 1].record()
+    torch.cuda.synchronize()
+    launches = cuda.launch_count(reset=True)
+    total_ms = ev[0].elapsed_time(ev[-1])
+    clocks = sampler.stop()
+    cuda.check()
+    ms_step = total_ms / args.steps
+
+    # per-kernel-class device time of one step (events around every launch of the class)
+    prof = profile_classes(cuda, dit, step_resident)
+
+    # end to end through the host-buffer entry point
+    e2e_ms = None
+    if not args.skip_e2e:
+        for _ in range(max(1, min(args.warmup, 2))):
+            step_e2e()
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(args.steps):
+            step_e2e()
+        e1.record()
+        torch.cuda.synchronize()
+        e2e_ms = max(e0.elapsed_time(e1), (time.perf_counter() - t0) * 1e3) / args.steps
+    h2d = x_h.numel() * 4 + text_h.numel() * 4 + cos_p.numel() * 8 + t_feat_h.numel() * 4
+    d2h = y_h.numel() * 4
+
+    pk = peaks()
+    lin_f, attn_f = block_flops(seq, text_len, geo.dim, geo.ffn)
+    roof = roofline(prof, lin_f, attn_f, geo.n_blocks, pk)
+    if args.skip_cpu_baseline:
+        cpu_ms, cpu_desc = None, "skipped (--skip-cpu-baseline)"
+    else:
+        cpu_ms, cpu_desc = cpu_block_sample("reference" if ref_available() else "port", os.cpu_count() or 1)
+
+    line = {"metric": METRIC, "value": ms_step, "unit": UNIT, "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": ms_step, "higher_is_better": False, "scaling": "weak", "vs_baseline": None,
+            "dtype": "int8 (linears, int32 accumulate) + bf16 (attention, f32 accumulate)", "data": "synthetic",
+            "config": workload_config(1),
+            "e2e": {"value": e2e_ms, "unit": UNIT, "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": int(d2h)},
+            "gpu_launches": int(launches), "clocks": clocks, "roofline": roof,
+            "cpu_baseline": {"value": cpu_ms, "unit": UNIT, "cores": os.cpu_count() or 1,
+                             "kind": "reference" if ref_available() else "port", "sample": cpu_desc},
+            "step_tflops": (lin_f + attn_f) * geo.n_blocks / (ms_step * 1e-3) / 1e12,
+            "kernel_classes": prof}
+    print(json.dumps(line))
+    dit.close()
+    cuda.close()
+
+
+def ref_available():
+    from oracle.pyoracle import Ref
+    return Ref.available()
+
+
+def profile_classes(cuda, dit, step):
+    """Runs one extra step with event pairs around every kernel launch (a library facility) and returns
+    {class: {"launches": n, "ms": total}} for the classes gemm_i8 / attention / rows / other."""
+    import ctypes as C
+    from h3c_b200.lib import load
+    lib = load()
+    lib.h3b_cuda_profile_begin(cuda.h)
+    step()
+    ms = (C.c_double * 8)()
+    cnt = (C.c_int * 8)()
+    n = lib.h3b_cuda_profile_end(cuda.h, ms, cnt, 8)
+    names = ["gemm_i8", "attention", "rows", "rope", "other"]
+    return {names[i]: {"launches": int(cnt[i]), "ms": float(ms[i])} for i in range(min(n, len(names))) if cnt[i]}
+
+
+def roofline(prof, lin_flops_block, attn_flops_block, n_blocks, pk):
+    """Roofline entry for the kernel class with the largest share of the step."""
+    if not prof:
+        return None
+    top = max(prof, key=lambda k: prof[k]["ms"])
+    p = prof[top]
+    per_launch_ms = p["ms"] / p["launches"]
+    if top == "gemm_i8":
+        flops = lin_flops_block * n_blocks / p["launches"]
+        # int8 tensor peak is not in MEASURED_PEAKS.json; the dense int8 rate of the part is twice its bf16
+        # rate, so the denominator is 2 x the measured sustained bf16 figure
+        peak = 2.0 * pk["bf16_sustained"]
+        note = f"2 x {pk['src']} sustained bf16 ({pk['bf16_sustained']} TFLOP/s): int8 runs at twice the bf16 rate"
+    elif top == "attention":
+        flops = attn_flops_block * n_blocks / p["launches"]
+        peak = pk["bf16_sustained"]
+        note = f"{pk['src']} sustained bf16"
+    else:
+        return {"bound": "hbm", "kernel": top, "achieved": None, "peak": pk["hbm"], "unit": "GB/s", "frac": None,
+                "traffic": None, "share_of_step": p["ms"] / sum(v["ms"] for v in prof.values())}
+    achieved = flops / (per_launch_ms * 1e-3) / 1e12
+    return {"bound": "tensor", "kernel": top, "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
+            "frac": achieved / peak, "traffic": None, "peak_note": note,
+            "share_of_step": p["ms"] / sum(v["ms"] for v in prof.values())}
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=5)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--skip-cpu-baseline", action="store_true", help="omit the CPU sample (profiling runs)")
+    ap.add_argument("--skip-e2e", action="store_true", help="omit the host-buffer measurement (profiling runs)")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        reference_arm(args)
+    else:
+        gpu_arm(args)
+
+
+if __name__ == "__main__":
+    main()

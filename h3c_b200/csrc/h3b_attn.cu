@@ -304,6 +304,7 @@ int launch_sdpa_bf16(h3_cuda *cuda, const void *q, size_t qs, const void *k, siz
     H3B_CUDA_OK(cudaFuncSetAttribute(k_attn_bf16, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)attn::SMEM_BYTES),
                 "sdpa smem attribute");
     dim3 grid((unsigned)ceil_div(lq, attn::BQ), (unsigned)heads);
+    ProfScope prof(cuda, PROF_ATTN);
     k_attn_bf16<<<grid, attn::THREADS, attn::SMEM_BYTES, cuda->op_stream>>>(p);
     cuda->launches++;
     H3B_CUDA_OK(cudaGetLastError(), "k_attn_bf16 launch");

@@ -1,0 +1,421 @@
+/* DiT block and block-chain host code, plain C on top of the C ABI of this library.
+ *
+ * One block is a fixed sequence of kernel launches on the handle's stream; nothing
+ * synchronises inside.  Two block shapes are supported:
+ *   H3B_BLOCK_REFERENCE   the reference's block (h3_dit_w4a8.c:3597-3830 device phases):
+ *                         adaLN -> QKV -> QK-norm/RoPE -> SDPA -> out (+gate, residual)
+ *                         -> adaLN -> fc1 (SwiGLU) -> fc2 (+gate, residual)
+ *   H3B_BLOCK_CROSS_GELU  the benchmark's block: the same self-attention part, then
+ *                         rms_norm -> cross-attention to the text tokens (+residual),
+ *                         then adaLN -> up (tanh-GELU) -> down (+gate, residual)
+ * Activations are kept in the configured stream type (f32 like the reference's CUDA
+ * path, or bf16); every quantised linear is "norm/rotate/quantise rows -> int8 GEMM
+ * with fused epilogue".
+ */
+#include <cuda_runtime_api.h>
+#include <stdarg.h>
+#include <stdio.h>
+#include <stdlib.h>
+#include <string.h>
+
+#include "../../include/h3_b200.h"
+
+typedef struct {
+    const h3_cuda_w4a8_weight *lin[H3B_LIN_COUNT];
+    float *norm1, *norm2, *q_norm, *k_norm, *norm_cross; /* device */
+    float *adaln_w, *adaln_b;                            /* device */
+    float *modulation;                                   /* device [mod_rows, 6, dim] */
+} h3b_block;
+
+struct h3b_dit {
+    h3_cuda *cuda;
+    h3b_dit_config cfg;
+    h3b_block *blocks;
+    /* workspace (device) */
+    size_t cap_seq, cap_text;
+    void *xa, *xb;          /* block-internal residuals x1 / x2, stream dtype [seq, dim] */
+    void *io;               /* chain input/output of the host-buffer entry point, stream dtype [seq, dim] */
+    void *qkv;              /* [seq, 3*inner] stream dtype */
+    void *wide;             /* [seq, ffn] stream dtype (FFN activation) */
+    void *q, *k, *v, *att;  /* bf16 [seq, inner] each */
+    void *cq;               /* bf16 [seq, inner] cross-attention queries */
+    void *ckv;              /* bf16 [text, 2*inner] */
+    int8_t *q8;             /* [seq, max(dim, ffn, inner)] activation codes */
+    float *s8;              /* [seq] activation scales */
+    int8_t *tq8;            /* [text, dim] */
+    float *ts8;             /* [text] */
+    /* staging for the host-buffer entry point */
+    float *st_x;            /* f32 [seq, dim] */
+    float *st_text;         /* f32 [text, dim] */
+    void *text_dev;         /* stream-dtype copy of the text tokens */
+    uint32_t *st_map;
+    float *st_cos, *st_sin, *st_t;
+};
+
+static int fail(char *error, size_t error_size, const char *fmt, ...) {
+    if (error && error_size) {
+        va_list ap;
+        va_start(ap, fmt);
+        vsnprintf(error, error_size, fmt, ap);
+        va_end(ap);
+    }
+    return 0;
+}
+
+static size_t elem(const h3b_dit *d) { return d->cfg.stream_dtype == H3B_F32 ? 4 : 2; }
+static size_t inner(const h3b_dit *d) { return d->cfg.heads * d->cfg.head_dim; }
+
+static int dmalloc(void **p, size_t bytes, char *error, size_t error_size) {
+    cudaError_t e = cudaMalloc(p, bytes ? bytes : 16);
+    if (e != cudaSuccess) return fail(error, error_size, "cudaMalloc(%zu): %s", bytes, cudaGetErrorString(e));
+    return 1;
+}
+
+static int upload(float **dst, const float *src, size_t count, char *error, size_t error_size) {
+    cudaError_t e;
+    if (!src) return 1;
+    if (!*dst && !dmalloc((void **)dst, count * sizeof(float), error, error_size)) return 0;
+    e = cudaMemcpy(*dst, src, count * sizeof(float), cudaMemcpyHostToDevice);
+    if (e != cudaSuccess) return fail(error, error_size, "cudaMemcpy(H2D): %s", cudaGetErrorString(e));
+    return 1;
+}
+
+h3b_dit *h3b_dit_create(h3_cuda *cuda, const h3b_dit_config *cfg, char *error, size_t error_size) {
+    h3b_dit *d;
+    if (!cuda || !cfg) {
+        fail(error, error_size, "h3b_dit_create: invalid arguments");
+        return NULL;
+    }
+    if (cfg->kind != H3B_BLOCK_REFERENCE && cfg->kind != H3B_BLOCK_CROSS_GELU) {
+        fail(error, error_size, "h3b_dit_create: unknown block kind %d", cfg->kind);
+        return NULL;
+    }
+    if (cfg->stream_dtype != H3B_F32 && cfg->stream_dtype != H3B_BF16) {
+        fail(error, error_size, "h3b_dit_create: stream dtype must be f32 or bf16");
+        return NULL;
+    }
+    if (!cfg->dim || !cfg->heads || cfg->head_dim != 128 || !cfg->ffn || !cfg->n_blocks || !cfg->mod_rows ||
+        cfg->rope_half * 2 > cfg->head_dim) {
+        fail(error, error_size, "h3b_dit_create: bad geometry (head_dim must be 128)");
+        return NULL;
+    }
+    if (cfg->kind == H3B_BLOCK_CROSS_GELU && cfg->heads * cfg->head_dim != cfg->dim) {
+        fail(error, error_size, "h3b_dit_create: cross block needs heads*head_dim == dim");
+        return NULL;
+    }
+    d = (h3b_dit *)calloc(1, sizeof(*d));
+    if (!d) {
+        fail(error, error_size, "h3b_dit_create: out of memory");
+        return NULL;
+    }
+    d->cuda = cuda;
+    d->cfg = *cfg;
+    d->blocks = (h3b_block *)calloc(cfg->n_blocks, sizeof(h3b_block));
+    if (!d->blocks) {
+        free(d);
+        fail(error, error_size, "h3b_dit_create: out of memory");
+        return NULL;
+    }
+    return d;
+}
+
+static void free_ws(h3b_dit *d) {
+    void **p[] = {&d->xa, &d->xb, &d->io, &d->qkv, &d->wide, &d->q, &d->k, &d->v, &d->att, &d->cq, &d->ckv, (void **)&d->q8,
+                  (void **)&d->s8, (void **)&d->tq8, (void **)&d->ts8, (void **)&d->st_x, (void **)&d->st_text,
+                  &d->text_dev, (void **)&d->st_map, (void **)&d->st_cos, (void **)&d->st_sin, (void **)&d->st_t};
+    size_t i;
+    for (i = 0; i < sizeof(p) / sizeof(p[0]); i++) {
+        if (*p[i]) cudaFree(*p[i]);
+        *p[i] = NULL;
+    }
+    d->cap_seq = d->cap_text = 0;
+}
+
+void h3b_dit_free(h3b_dit *d) {
+    size_t b;
+    if (!d) return;
+    cudaDeviceSynchronize();
+    free_ws(d);
+    for (b = 0; b < d->cfg.n_blocks; b++) {
+        h3b_block *k = &d->blocks[b];
+        float *p[] = {k->norm1, k->norm2, k->q_norm, k->k_norm, k->norm_cross, k->adaln_w, k->adaln_b, k->modulation};
+        size_t i;
+        for (i = 0; i < sizeof(p) / sizeof(p[0]); i++)
+            if (p[i]) cudaFree(p[i]);
+    }
+    free(d->blocks);
+    free(d);
+}
+
+int h3b_dit_set_linear(h3b_dit *d, unsigned block, int which, const h3_cuda_w4a8_weight *w, char *error,
+                       size_t error_size) {
+    size_t n, k, D, I, F;
+    if (!d || !w || block >= d->cfg.n_blocks || which < 0 || which >= H3B_LIN_COUNT)
+        return fail(error, error_size, "h3b_dit_set_linear: invalid arguments");
+    n = h3_cuda_w4a8_weight_n(w);
+    k = h3_cuda_w4a8_weight_k(w);
+    D = d->cfg.dim; I = inner(d); F = d->cfg.ffn;
+    {
+        const int swiglu = d->cfg.kind == H3B_BLOCK_REFERENCE;
+        const size_t want_n[H3B_LIN_COUNT] = {3 * I, D, swiglu ? 2 * F : F, D, I, 2 * I, D};
+        const size_t want_k[H3B_LIN_COUNT] = {D, I, D, F, D, D, I};
+        if (n != want_n[which] || k != want_k[which])
+            return fail(error, error_size, "h3b_dit_set_linear: linear %d is [%zu,%zu], expected [%zu,%zu]", which, n, k,
+                        want_n[which], want_k[which]);
+    }
+    d->blocks[block].lin[which] = w;
+    return 1;
+}
+
+int h3b_dit_set_block_aux(h3b_dit *d, unsigned block, const float *norm1, const float *norm2, const float *q_norm,
+                          const float *k_norm, const float *norm_cross, char *error, size_t error_size) {
+    h3b_block *b;
+    if (!d || block >= d->cfg.n_blocks || !norm1 || !norm2 || !q_norm || !k_norm)
+        return fail(error, error_size, "h3b_dit_set_block_aux: invalid arguments");
+    b = &d->blocks[block];
+    return upload(&b->norm1, norm1, d->cfg.dim, error, error_size) &&
+           upload(&b->norm2, norm2, d->cfg.dim, error, error_size) &&
+           upload(&b->q_norm, q_norm, d->cfg.head_dim, error, error_size) &&
+           upload(&b->k_norm, k_norm, d->cfg.head_dim, error, error_size) &&
+           upload(&b->norm_cross, norm_cross, d->cfg.dim, error, error_size);
+}
+
+static size_t mod_elems(const h3b_dit *d) { return d->cfg.mod_rows * 6 * d->cfg.dim; }
+
+int h3b_dit_set_adaln(h3b_dit *d, unsigned block, const float *w, const float *b, char *error, size_t error_size) {
+    h3b_block *k;
+    if (!d || block >= d->cfg.n_blocks || !w || !b || !d->cfg.t_dim)
+        return fail(error, error_size, "h3b_dit_set_adaln: invalid arguments");
+    k = &d->blocks[block];
+    if (!k->modulation && !dmalloc((void **)&k->modulation, mod_elems(d) * sizeof(float), error, error_size)) return 0;
+    return upload(&k->adaln_w, w, mod_elems(d) * d->cfg.t_dim, error, error_size) &&
+           upload(&k->adaln_b, b, mod_elems(d), error, error_size);
+}
+
+int h3b_dit_project_modulation(h3b_dit *d, const float *d_t_feat, char *error, size_t error_size) {
+    size_t b;
+    if (!d || !d_t_feat) return fail(error, error_size, "h3b_dit_project_modulation: invalid arguments");
+    for (b = 0; b < d->cfg.n_blocks; b++) {
+        h3b_block *k = &d->blocks[b];
+        if (!k->adaln_w) return fail(error, error_size, "block %zu has no adaLN projection", b);
+        if (!h3b_adaln_project_dev(d->cuda, k->adaln_w, k->adaln_b, mod_elems(d), d->cfg.t_dim, d_t_feat, k->modulation,
+                                   error, error_size))
+            return 0;
+    }
+    return 1;
+}
+
+const float *h3b_dit_modulation(h3b_dit *d, unsigned block) {
+    if (!d || block >= d->cfg.n_blocks) return NULL;
+    return d->blocks[block].modulation;
+}
+
+int h3b_dit_reserve(h3b_dit *d, size_t seq, size_t text_seq, char *error, size_t error_size) {
+    size_t D, I, F, widest, es;
+    if (!d || !seq) return fail(error, error_size, "h3b_dit_reserve: invalid arguments");
+    if (seq <= d->cap_seq && text_seq <= d->cap_text) return 1;
+    if (h3_cuda_graph_capture(d->cuda)) return fail(error, error_size, "workspace growth is forbidden during graph capture");
+    cudaStreamSynchronize((cudaStream_t)h3_cuda_op_stream(d->cuda));
+    free_ws(d);
+    D = d->cfg.dim; I = inner(d); F = d->cfg.ffn; es = elem(d);
+    widest = D > F ? D : F;
+    if (I > widest) widest = I;
+    if (!dmalloc(&d->xa, seq * D * es, error, error_size) || !dmalloc(&d->xb, seq * D * es, error, error_size) ||
+        !dmalloc(&d->io, seq * D * es, error, error_size) ||
+        !dmalloc(&d->qkv, seq * 3 * I * es, error, error_size) || !dmalloc(&d->wide, seq * F * es, error, error_size) ||
+        !dmalloc(&d->q, seq * I * 2, error, error_size) || !dmalloc(&d->k, seq * I * 2, error, error_size) ||
+        !dmalloc(&d->v, seq * I * 2, error, error_size) || !dmalloc(&d->att, seq * I * 2, error, error_size) ||
+        !dmalloc((void **)&d->q8, seq * widest, error, error_size) ||
+        !dmalloc((void **)&d->s8, seq * sizeof(float), error, error_size) ||
+        !dmalloc((void **)&d->st_x, seq * D * sizeof(float), error, error_size) ||
+        !dmalloc((void **)&d->st_map, seq * sizeof(uint32_t), error, error_size) ||
+        !dmalloc((void **)&d->st_cos, seq * (d->cfg.rope_half ? d->cfg.rope_half : 1) * sizeof(float), error, error_size) ||
+        !dmalloc((void **)&d->st_sin, seq * (d->cfg.rope_half ? d->cfg.rope_half : 1) * sizeof(float), error, error_size) ||
+        !dmalloc((void **)&d->st_t, (d->cfg.t_dim ? d->cfg.t_dim : 1) * sizeof(float), error, error_size))
+        return 0;
+    if (d->cfg.kind == H3B_BLOCK_CROSS_GELU) {
+        size_t t = text_seq ? text_seq : 1;
+        if (!dmalloc(&d->cq, seq * I * 2, error, error_size) || !dmalloc(&d->ckv, t * 2 * I * 2, error, error_size) ||
+            !dmalloc((void **)&d->tq8, t * D, error, error_size) ||
+            !dmalloc((void **)&d->ts8, t * sizeof(float), error, error_size) ||
+            !dmalloc((void **)&d->st_text, t * D * sizeof(float), error, error_size) ||
+            !dmalloc(&d->text_dev, t * D * es, error, error_size))
+            return 0;
+    }
+    d->cap_seq = seq;
+    d->cap_text = text_seq;
+    return 1;
+}
+
+int h3b_dit_launches_per_block(const h3b_dit *d) {
+    if (!d) return 0;
+    return d->cfg.kind == H3B_BLOCK_REFERENCE ? 10 : 17;
+}
+
+/* rows -> (gate) -> norm -> (modulate) -> (rotate) -> int8 codes in d->q8 / d->s8 */
+static int norm_quant(h3b_dit *d, const void *x, int dtype, size_t rows, size_t width, const float *norm_w,
+                      const float *mod, const uint32_t *row_map, size_t shift_slot, size_t scale_slot, int identity,
+                      int8_t *q, float *s, char *error, size_t error_size) {
+    h3b_norm_args a;
+    memset(&a, 0, sizeof(a));
+    a.d_x = x; a.d_norm_w = norm_w; a.d_modulation = mod; a.d_row_map = row_map; a.rows = rows; a.width = width;
+    a.slots = 6; a.shift_slot = shift_slot; a.scale_slot = scale_slot; a.epsilon = d->cfg.eps; a.dtype = dtype;
+    a.identity = identity; a.convrot_gs = d->cfg.convrot_gs; a.d_q = q; a.d_scales = s;
+    return h3b_norm_dev(d->cuda, &a, error, error_size);
+}
+
+static int gemm(h3b_dit *d, const h3_cuda_w4a8_weight *w, const int8_t *q, const float *s, size_t m, void *y, int kind,
+                int out_dtype, const void *residual, const float *mod, const uint32_t *row_map, size_t gate_slot,
+                char *error, size_t error_size) {
+    h3b_gemm_epi e;
+    memset(&e, 0, sizeof(e));
+    e.kind = kind; e.out_dtype = out_dtype; e.d_residual = residual; e.d_modulation = mod; e.d_row_map = row_map;
+    e.slots = 6; e.gate_slot = gate_slot;
+    return h3b_gemm_i8_dev(d->cuda, w, q, s, m, y, &e, error, error_size);
+}
+
+int h3b_dit_block_forward_dev(h3b_dit *d, unsigned block, const void *d_x, size_t seq, const float *d_modulation,
+                              const uint32_t *d_row_map, const float *d_cos, const float *d_sin, const void *d_text,
+                              size_t text_seq, void *d_y, char *error, size_t error_size) {
+    const h3b_block *b;
+    const float *mod;
+    size_t D, I, F;
+    int dt, i;
+    float scale;
+    if (!d || block >= d->cfg.n_blocks || !d_x || !d_y || !seq)
+        return fail(error, error_size, "h3b_dit_block_forward_dev: invalid arguments");
+    b = &d->blocks[block];
+    mod = d_modulation ? d_modulation : b->modulation;
+    if (!mod) return fail(error, error_size, "block %u: no modulation given or projected", block);
+    if (!b->norm1) return fail(error, error_size, "block %u: aux tensors not set", block);
+    for (i = 0; i < (d->cfg.kind == H3B_BLOCK_CROSS_GELU ? H3B_LIN_COUNT : 4); i++)
+        if (!b->lin[i]) return fail(error, error_size, "block %u: linear %d not set", block, i);
+    if (d->cfg.rope_half && (!d_cos || !d_sin)) return fail(error, error_size, "block %u: rope tables missing", block);
+    if (d->cfg.kind == H3B_BLOCK_CROSS_GELU && (!d_text || !text_seq))
+        return fail(error, error_size, "block %u: text tokens missing", block);
+    if (!h3b_dit_reserve(d, seq, text_seq, error, error_size)) return 0;
+    D = d->cfg.dim; I = inner(d); F = d->cfg.ffn; dt = d->cfg.stream_dtype;
+    scale = 1.0f / 11.313708498984761f; /* 1/sqrt(128) */
+
+    /* ---- self-attention: adaLN(0,1) -> QKV -> QK-norm + RoPE -> SDPA -> out * gate(2) + x */
+    if (!norm_quant(d, d_x, dt, seq, D, b->norm1, mod, d_row_map, 0, 1, 0, d->q8, d->s8, error, error_size)) return 0;
+    if (!gemm(d, b->lin[H3B_LIN_QKV], d->q8, d->s8, seq, d->qkv, H3B_EPI_PLAIN, dt, NULL, NULL, NULL, 0, error, error_size))
+        return 0;
+    if (!h3b_qkv_rope_dev(d->cuda, d->qkv, dt, b->q_norm, b->k_norm, d_cos, d_sin, seq, d->cfg.heads, d->cfg.head_dim,
+                          d->cfg.rope_half, d->cfg.eps, 0, 1, d->q, d->k, d->v, H3B_BF16, error, error_size))
+        return 0;
+    if (!h3b_sdpa_bf16_dev(d->cuda, d->q, I, d->k, I, d->v, I, seq, seq, d->cfg.heads, d->cfg.head_dim, scale, d->att, I,
+                           error, error_size))
+        return 0;
+    if (!norm_quant(d, d->att, H3B_BF16, seq, I, NULL, NULL, NULL, 0, 0, 1, d->q8, d->s8, error, error_size)) return 0;
+    /* x1 -> xa */
+    if (!gemm(d, b->lin[H3B_LIN_OUT], d->q8, d->s8, seq, d->xa, H3B_EPI_GATE, dt, d_x, mod, d_row_map, 2, error,
+              error_size))
+        return 0;
+
+    if (d->cfg.kind == H3B_BLOCK_REFERENCE) {
+        /* ---- MLP: adaLN(3,4) -> fc1 + SwiGLU -> fc2 * gate(5) + x1 */
+        if (!norm_quant(d, d->xa, dt, seq, D, b->norm2, mod, d_row_map, 3, 4, 0, d->q8, d->s8, error, error_size)) return 0;
+        if (!gemm(d, b->lin[H3B_LIN_FC1], d->q8, d->s8, seq, d->wide, H3B_EPI_SWIGLU, dt, NULL, NULL, NULL, 0, error,
+                  error_size))
+            return 0;
+        if (!norm_quant(d, d->wide, dt, seq, F, NULL, NULL, NULL, 0, 0, 1, d->q8, d->s8, error, error_size)) return 0;
+        return gemm(d, b->lin[H3B_LIN_FC2], d->q8, d->s8, seq, d_y, H3B_EPI_GATE, dt, d->xa, mod, d_row_map, 5, error,
+                    error_size);
+    }
+
+    /* ---- cross-attention: rms_norm -> q proj; text -> kv proj; SDPA(lq=seq, lk=text) -> out + x1 (no gate) */
+    if (!norm_quant(d, d->xa, dt, seq, D, b->norm_cross, NULL, NULL, 0, 0, 0, d->q8, d->s8, error, error_size)) return 0;
+    if (!gemm(d, b->lin[H3B_LIN_CROSS_Q], d->q8, d->s8, seq, d->cq, H3B_EPI_PLAIN, H3B_BF16, NULL, NULL, NULL, 0, error,
+              error_size))
+        return 0;
+    if (!norm_quant(d, d_text, dt, text_seq, D, NULL, NULL, NULL, 0, 0, 1, d->tq8, d->ts8, error, error_size)) return 0;
+    if (!gemm(d, b->lin[H3B_LIN_CROSS_KV], d->tq8, d->ts8, text_seq, d->ckv, H3B_EPI_PLAIN, H3B_BF16, NULL, NULL, NULL, 0,
+              error, error_size))
+        return 0;
+    if (!h3b_sdpa_bf16_dev(d->cuda, d->cq, I, d->ckv, 2 * I, (const char *)d->ckv + I * 2, 2 * I, seq, text_seq,
+                           d->cfg.heads, d->cfg.head_dim, scale, d->att, I, error, error_size))
+        return 0;
+    if (!norm_quant(d, d->att, H3B_BF16, seq, I, NULL, NULL, NULL, 0, 0, 1, d->q8, d->s8, error, error_size)) return 0;
+    /* x2 -> xb */
+    if (!gemm(d, b->lin[H3B_LIN_CROSS_OUT], d->q8, d->s8, seq, d->xb, H3B_EPI_GATE, dt, d->xa, NULL, NULL, 0, error,
+              error_size))
+        return 0;
+
+    /* ---- FFN: adaLN(3,4) -> up + tanh-GELU -> down * gate(5) + x2 */
+    if (!norm_quant(d, d->xb, dt, seq, D, b->norm2, mod, d_row_map, 3, 4, 0, d->q8, d->s8, error, error_size)) return 0;
+    if (!gemm(d, b->lin[H3B_LIN_FC1], d->q8, d->s8, seq, d->wide, H3B_EPI_GELU, dt, NULL, NULL, NULL, 0, error, error_size))
+        return 0;
+    if (!norm_quant(d, d->wide, dt, seq, F, NULL, NULL, NULL, 0, 0, 1, d->q8, d->s8, error, error_size)) return 0;
+    return gemm(d, b->lin[H3B_LIN_FC2], d->q8, d->s8, seq, d_y, H3B_EPI_GATE, dt, d->xb, mod, d_row_map, 5, error,
+                error_size);
+}
+
+int h3b_dit_layers_forward_dev(h3b_dit *d, unsigned first, unsigned n, const void *d_x, size_t seq,
+                               const uint32_t *d_row_map, const float *d_cos, const float *d_sin, const void *d_text,
+                               size_t text_seq, void *d_y, char *error, size_t error_size) {
+    unsigned i;
+    const void *cur = d_x;
+    if (!d || !n || first + n > d->cfg.n_blocks) return fail(error, error_size, "layers_forward: bad block range");
+    /* every block writes its result to d_y; inside a block the input is last read by the
+     * out-projection epilogue, before anything is written to d_y, so in-place chaining is safe */
+    for (i = 0; i < n; i++) {
+        if (!h3b_dit_block_forward_dev(d, first + i, cur, seq, NULL, d_row_map, d_cos, d_sin, d_text, text_seq, d_y, error,
+                                       error_size))
+            return 0;
+        cur = d_y;
+    }
+    return 1;
+}
+
+int h3b_dit_layers_forward_f32(h3b_dit *d, unsigned first, unsigned n, const float *t_feat, const float *x, size_t seq,
+                               const uint32_t *row_map, const float *rope_cos, const float *rope_sin, const float *text,
+                               size_t text_seq, float *y, char *error, size_t error_size) {
+    cudaStream_t st;
+    size_t D, rh;
+    void *dx;
+    const void *dtext = NULL;
+    cudaError_t e;
+    if (!d || !x || !y || !seq || !t_feat) return fail(error, error_size, "layers_forward_f32: invalid arguments");
+    if (!h3b_dit_reserve(d, seq, text_seq, error, error_size)) return 0;
+    st = (cudaStream_t)h3_cuda_op_stream(d->cuda);
+    D = d->cfg.dim; rh = d->cfg.rope_half;
+    cudaMemcpyAsync(d->st_x, x, seq * D * sizeof(float), cudaMemcpyHostToDevice, st);
+    cudaMemcpyAsync(d->st_t, t_feat, d->cfg.t_dim * sizeof(float), cudaMemcpyHostToDevice, st);
+    if (row_map) cudaMemcpyAsync(d->st_map, row_map, seq * sizeof(uint32_t), cudaMemcpyHostToDevice, st);
+    else cudaMemsetAsync(d->st_map, 0, seq * sizeof(uint32_t), st);
+    if (rh) {
+        if (!rope_cos || !rope_sin) return fail(error, error_size, "layers_forward_f32: rope tables missing");
+        cudaMemcpyAsync(d->st_cos, rope_cos, seq * rh * sizeof(float), cudaMemcpyHostToDevice, st);
+        cudaMemcpyAsync(d->st_sin, rope_sin, seq * rh * sizeof(float), cudaMemcpyHostToDevice, st);
+    }
+    if (d->cfg.kind == H3B_BLOCK_CROSS_GELU) {
+        if (!text || !text_seq) return fail(error, error_size, "layers_forward_f32: text tokens missing");
+        cudaMemcpyAsync(d->st_text, text, text_seq * D * sizeof(float), cudaMemcpyHostToDevice, st);
+        if (d->cfg.stream_dtype == H3B_F32) {
+            dtext = d->st_text;
+        } else {
+            if (!h3b_cast_dev(d->cuda, d->st_text, H3B_F32, d->text_dev, d->cfg.stream_dtype, text_seq * D, error, error_size))
+                return 0;
+            dtext = d->text_dev;
+        }
+    }
+    if (!h3b_dit_project_modulation(d, d->st_t, error, error_size)) return 0;
+    if (d->cfg.stream_dtype == H3B_F32) {
+        dx = d->st_x;
+    } else {
+        if (!h3b_cast_dev(d->cuda, d->st_x, H3B_F32, d->io, d->cfg.stream_dtype, seq * D, error, error_size)) return 0;
+        dx = d->io;
+    }
+    if (!h3b_dit_layers_forward_dev(d, first, n, dx, seq, d->st_map, d->st_cos, d->st_sin, dtext, text_seq, dx, error,
+                                    error_size))
+        return 0;
+    if (d->cfg.stream_dtype != H3B_F32) {
+        if (!h3b_cast_dev(d->cuda, dx, d->cfg.stream_dtype, d->st_x, H3B_F32, seq * D, error, error_size)) return 0;
+        dx = d->st_x;
+    }
+    e = cudaMemcpyAsync(y, dx, seq * D * sizeof(float), cudaMemcpyDeviceToHost, st);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(st);
+    if (e != cudaSuccess) return fail(error, error_size, "layers_forward_f32 download: %s", cudaGetErrorString(e));
+    return h3b_cuda_check(d->cuda, NULL, error, error_size);
+}

@@ -306,6 +306,7 @@ static int gemm_launch_t(h3_cuda *cuda, const GemmParams &p, char *error, size_t
                 "gemm smem attribute");
     int tiles = p.m_tiles * p.n_tiles;
     int grid = tiles < cuda->sm_count ? tiles : cuda->sm_count;
+    ProfScope prof(cuda, PROF_GEMM);
     kern<<<grid, gemm::THREADS, gemm::SMEM_BYTES, cuda->op_stream>>>(p);
     cuda->launches++;
     H3B_CUDA_OK(cudaGetLastError(), "k_gemm_i8 launch");

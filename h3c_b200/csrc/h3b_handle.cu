@@ -50,6 +50,29 @@ void Timer::stop() {
     on = false;
 }
 
+ProfScope::ProfScope(h3_cuda *c, int cls) : cuda(c), slot(-1) {
+    if (!c->prof_on || c->graph_capture) return;
+    if (c->prof_n == c->prof_cap) {
+        int cap = c->prof_cap ? c->prof_cap * 2 : 1024;
+        cudaEvent_t *ev = (cudaEvent_t *)realloc(c->prof_ev, sizeof(cudaEvent_t) * 2 * cap);
+        int *cl = (int *)realloc(c->prof_cls, sizeof(int) * cap);
+        if (!ev || !cl) return;
+        c->prof_ev = ev;
+        c->prof_cls = cl;
+        for (int i = c->prof_cap; i < cap; i++) {
+            cudaEventCreate(&ev[2 * i]);
+            cudaEventCreate(&ev[2 * i + 1]);
+        }
+        c->prof_cap = cap;
+    }
+    slot = c->prof_n++;
+    c->prof_cls[slot] = cls;
+    cudaEventRecord(c->prof_ev[2 * slot], c->op_stream);
+}
+ProfScope::~ProfScope() {
+    if (slot >= 0) cudaEventRecord(cuda->prof_ev[2 * slot + 1], cuda->op_stream);
+}
+
 // cuTensorMapEncodeTiled is reached through the runtime so that the library
 // needs no link-time dependency on libcuda.
 typedef CUresult (*encode_fn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
@@ -196,6 +219,9 @@ void h3_cuda_free(h3_cuda *cuda) {
     if (cuda->ev0) cudaEventDestroy(cuda->ev0);
     if (cuda->ev1) cudaEventDestroy(cuda->ev1);
     if (cuda->d_status) cudaFree(cuda->d_status);
+    for (int i = 0; i < 2 * cuda->prof_cap; i++) cudaEventDestroy(cuda->prof_ev[i]);
+    free(cuda->prof_ev);
+    free(cuda->prof_cls);
     free(cuda);
 }
 
@@ -323,6 +349,33 @@ int h3b_cuda_check(h3_cuda *cuda, int *status_out, char *error, size_t error_siz
         return fail(error, error_size, "a kernel gave up a bounded wait (status %d); its output is invalid", st);
     }
     return 1;
+}
+
+void h3b_cuda_profile_begin(h3_cuda *cuda) {
+    if (!cuda) return;
+    cuda->prof_n = 0;
+    cuda->prof_on = 1;
+}
+
+int h3b_cuda_profile_end(h3_cuda *cuda, double *ms_by_class, int *launches_by_class, int n_classes) {
+    if (!cuda || !ms_by_class || !launches_by_class) return 0;
+    cuda->prof_on = 0;
+    cudaStreamSynchronize(cuda->op_stream);
+    for (int i = 0; i < n_classes; i++) {
+        ms_by_class[i] = 0.0;
+        launches_by_class[i] = 0;
+    }
+    for (int i = 0; i < cuda->prof_n; i++) {
+        float t = 0.0f;
+        int c = cuda->prof_cls[i];
+        if (c < 0 || c >= n_classes) continue;
+        if (cudaEventElapsedTime(&t, cuda->prof_ev[2 * i], cuda->prof_ev[2 * i + 1]) == cudaSuccess) {
+            ms_by_class[c] += (double)t;
+            launches_by_class[c]++;
+        }
+    }
+    cuda->prof_n = 0;
+    return n_classes < PROF_CLASSES ? n_classes : PROF_CLASSES;
 }
 
 unsigned long long h3b_cuda_launch_count(h3_cuda *cuda, int reset) {

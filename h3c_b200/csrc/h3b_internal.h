@@ -26,6 +26,10 @@ struct h3_cuda {
     void *act_rot; size_t act_rot_bytes;   // ConvRot output (f32)
     void *attn;    size_t attn_bytes;      // 16-bit Q/K/V/O staging for the f32 attention entry points
     int pregrown;
+    // optional per-launch timing (h3b_cuda_profile_begin / _end)
+    int prof_on, prof_n, prof_cap;
+    cudaEvent_t *prof_ev;        // 2 events per recorded launch
+    int *prof_cls;
 };
 
 struct h3_cuda_w4a8_weight {
@@ -61,6 +65,16 @@ struct Timer {   // optional per-op timing, honouring quiet mode
     bool on;
     Timer(h3_cuda *c, double *out);
     void stop();
+};
+
+// kernel classes of the per-launch profile
+enum { PROF_GEMM = 0, PROF_ATTN = 1, PROF_ROWS = 2, PROF_ROPE = 3, PROF_OTHER = 4, PROF_CLASSES = 5 };
+// Brackets one kernel launch with an event pair while profiling is on.
+struct ProfScope {
+    h3_cuda *cuda;
+    int slot;
+    ProfScope(h3_cuda *c, int cls);
+    ~ProfScope();
 };
 
 static inline size_t ceil_div(size_t a, size_t b) { return (a + b - 1) / b; }

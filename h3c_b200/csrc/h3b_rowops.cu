@@ -211,6 +211,7 @@ static int norm_dispatch(h3_cuda *cuda, const NormParams &p, size_t rows, bool v
         H3B_CUDA_OK(cudaFuncSetAttribute(kv, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem), "smem attr");
         H3B_CUDA_OK(cudaFuncSetAttribute(ks, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem), "smem attr");
     }
+    ProfScope prof(cuda, PROF_ROWS);
     if (vec) kv<<<(unsigned)rows, 256, smem, cuda->op_stream>>>(p);
     else ks<<<(unsigned)rows, 256, smem, cuda->op_stream>>>(p);
     cuda->launches++;
@@ -309,6 +310,18 @@ template <typename TI, typename TO>
 __global__ void k_cast(const TI *in, TO *out, size_t n) {
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x)
         out[i] = from_f<TO>(to_f<TI>(in[i]));
+}
+
+// modulation[o] = b[o] + sum_i W[o,i] * t[i]; one warp per output (h3_dit_w4a8.c:2256-2261)
+__global__ void k_adaln_project(const float *w, const float *b, size_t out_dim, unsigned in_dim, const float *t,
+                                float *out) {
+    const size_t o = (size_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (o >= out_dim) return;
+    const unsigned lane = threadIdx.x & 31;
+    float acc = 0.0f;
+    for (unsigned i = lane; i < in_dim; i += 32) acc = fmaf(w[o * in_dim + i], t[i], acc);
+    for (int s = 16; s > 0; s >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, s);
+    if (lane == 0) out[o] = b[o] + acc;
 }
 
 static unsigned ew_grid(h3_cuda *cuda, size_t n) {
@@ -452,6 +465,7 @@ static int qkv_rope_dispatch(h3_cuda *cuda, const void *qkv, const float *qn, co
                              int grouped, int split_half, void *q, void *k, void *v, char *error, size_t error_size) {
     size_t items = seq * heads;
     unsigned grid = (unsigned)ceil_div(items, 8);
+    ProfScope prof(cuda, PROF_ROPE);
 #define H3B_ROPE(EPL)                                                                                          \
     k_qkv_rope<TI, TO, EPL><<<grid, 256, 0, cuda->op_stream>>>((const TI *)qkv, qn, kn, c, s, seq, (unsigned)heads, \
                                                                (unsigned)rope_half, eps, grouped, split_half,  \
@@ -621,6 +635,18 @@ int h3_cuda_f32_to_f16_dev(h3_cuda *cuda, const float *d_in, void *d_out_half, s
 int h3_cuda_f16_to_f32_dev(h3_cuda *cuda, const void *d_in_half, float *d_out, size_t n, char *error,
                            size_t error_size) {
     return h3b_cast_dev(cuda, d_in_half, H3B_F16, d_out, H3B_F32, n, error, error_size);
+}
+
+int h3b_adaln_project_dev(h3_cuda *cuda, const float *d_w, const float *d_b, size_t out_dim, size_t in_dim,
+                          const float *d_t_feat, float *d_out, char *error, size_t error_size) {
+    if (!cuda || !d_w || !d_b || !d_t_feat || !d_out || !out_dim || !in_dim)
+        return fail(error, error_size, "invalid adaln_project args");
+    ProfScope prof(cuda, PROF_OTHER);
+    k_adaln_project<<<(unsigned)ceil_div(out_dim, 8), 256, 0, cuda->op_stream>>>(d_w, d_b, out_dim, (unsigned)in_dim,
+                                                                                 d_t_feat, d_out);
+    cuda->launches++;
+    H3B_CUDA_OK(cudaGetLastError(), "k_adaln_project launch");
+    return 1;
 }
 
 int h3b_gelu_tanh_dev(h3_cuda *cuda, const void *d_in, void *d_out, int dtype, size_t n, char *error,

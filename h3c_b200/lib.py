@@ -53,6 +53,12 @@ class NormArgs(C.Structure):  # h3b_norm_args
                 ("d_gated", vp), ("d_normed", vp), ("d_rot", vp), ("d_q", vp), ("d_scales", vp)]
 
 
+class DitConfig(C.Structure):  # h3b_dit_config
+    _fields_ = [("kind", i32), ("stream_dtype", i32), ("convrot_gs", i32), ("dim", sz), ("heads", sz),
+                ("head_dim", sz), ("ffn", sz), ("rope_half", sz), ("n_blocks", sz), ("mod_rows", sz), ("t_dim", sz),
+                ("eps", f32)]
+
+
 class UlyssesCfg(C.Structure):  # h3_ulysses_cfg
     _fields_ = [("tp_size", i32), ("ulysses", i32), ("ring", i32), ("rank", i32), ("world_size", i32), ("comm", vp)]
 
@@ -88,6 +94,8 @@ _SIGS = {
     "h3_cuda_host_free": (None, (vp, i32)),
     "h3b_cuda_check": (i32, (vp, C.POINTER(i32)) + _ERR),
     "h3b_cuda_launch_count": (C.c_ulonglong, (vp, i32)),
+    "h3b_cuda_profile_begin": (None, (vp,)),
+    "h3b_cuda_profile_end": (i32, (vp, dbl_p, C.POINTER(i32), i32)),
     "h3_cuda_w4a8_weight_create": (i32, (vp, vp, sz, sz, vp, vp, vp, i32, C.POINTER(vp), dbl_p, dbl_p) + _ERR),
     "h3_cuda_w4a8_weight_create_from_i8": (i32, (vp, vp, sz, sz, vp, C.POINTER(vp), dbl_p, i32) + _ERR),
     "h3_cuda_w4a8_weight_upload_i8": (i32, (vp, vp, sz, sz, vp, i32) + _ERR),
@@ -140,6 +148,19 @@ _SIGS = {
     "h3_cuda_qkv_rope_f32": (i32, (vp, vp, vp, vp, vp, vp, sz, sz, sz, sz, f32, vp, vp, vp, dbl_p) + _ERR),
     "h3_cuda_nvfp4_sf_bytes": (sz, (sz, sz)),
     "h3_cuda_quantize_act_nvfp4_dev": (i32, (vp, vp, sz, sz, vp, vp) + _ERR),
+    "h3b_adaln_project_dev": (i32, (vp, vp, vp, sz, sz, vp, vp) + _ERR),
+    "h3b_dit_create": (vp, (vp, C.POINTER(DitConfig)) + _ERR),
+    "h3b_dit_free": (None, (vp,)),
+    "h3b_dit_set_linear": (i32, (vp, C.c_uint, i32, vp) + _ERR),
+    "h3b_dit_set_block_aux": (i32, (vp, C.c_uint, vp, vp, vp, vp, vp) + _ERR),
+    "h3b_dit_set_adaln": (i32, (vp, C.c_uint, vp, vp) + _ERR),
+    "h3b_dit_project_modulation": (i32, (vp, vp) + _ERR),
+    "h3b_dit_modulation": (vp, (vp, C.c_uint)),
+    "h3b_dit_reserve": (i32, (vp, sz, sz) + _ERR),
+    "h3b_dit_block_forward_dev": (i32, (vp, C.c_uint, vp, sz, vp, vp, vp, vp, vp, sz, vp) + _ERR),
+    "h3b_dit_layers_forward_dev": (i32, (vp, C.c_uint, C.c_uint, vp, sz, vp, vp, vp, vp, sz, vp) + _ERR),
+    "h3b_dit_layers_forward_f32": (i32, (vp, C.c_uint, C.c_uint, vp, vp, sz, vp, vp, vp, vp, sz, vp) + _ERR),
+    "h3b_dit_launches_per_block": (i32, (vp,)),
     "h3_ulysses_validate": (i32, (i32, i32, i32, i32, i32) + _ERR),
     "h3_ulysses_pad_seq": (sz, (sz, i32)),
     "h3_ulysses_local_rows": (sz, (sz, i32, i32)),

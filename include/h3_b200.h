@@ -81,6 +81,12 @@ void h3_cuda_host_free(void *p, int pinned);                                   /
  * a kernel gave up a bounded wait (code in h3b_ptx.cuh) and its output is
  * invalid.  Also reports sticky CUDA errors through `error`. */
 int h3b_cuda_check(h3_cuda *cuda, int *status_out, char *error, size_t error_size);
+/* Additions.  Per-launch device timing: between _begin and _end every kernel launch of the handle
+ * is bracketed by an event pair; _end synchronises and sums milliseconds and launches per kernel
+ * class (0 int8 GEMM, 1 attention, 2 row-wise norm/quant, 3 QK-norm+RoPE, 4 other) and returns the
+ * number of classes filled. */
+void h3b_cuda_profile_begin(h3_cuda *cuda);
+int h3b_cuda_profile_end(h3_cuda *cuda, double *ms_by_class, int *launches_by_class, int n_classes);
 /* Addition.  Kernel launches issued through this handle since the last call. */
 unsigned long long h3b_cuda_launch_count(h3_cuda *cuda, int reset);
 
@@ -298,6 +304,11 @@ int h3b_qkv_rope_dev(h3_cuda *cuda, const void *d_qkv, int in_dtype, const float
                      int out_dtype, char *error, size_t error_size);
 int h3b_cast_dev(h3_cuda *cuda, const void *d_in, int in_dtype, void *d_out, int out_dtype, size_t n,
                  char *error, size_t error_size);
+/* out[o] = b[o] + sum_i W[o,i] t[i] on the device (adaLN modulation projection,
+ * h3_dit_w4a8.c:2236 h3_dit_w4a8_adaln_project_f32 without the optional SiLU). */
+int h3b_adaln_project_dev(h3_cuda *cuda, const float *d_w, const float *d_b, size_t out_dim,
+                          size_t in_dim, const float *d_t_feat, float *d_out, char *error,
+                          size_t error_size);
 int h3b_gelu_tanh_dev(h3_cuda *cuda, const void *d_in, void *d_out, int dtype, size_t n, char *error,
                       size_t error_size);
 
@@ -341,6 +352,73 @@ size_t h3_cuda_nvfp4_sf_bytes(size_t rows, size_t k);                           
 int h3_cuda_quantize_act_nvfp4_dev(h3_cuda *cuda, const float *d_x, size_t m, size_t k,
                                    uint8_t *d_x_fp4, uint8_t *d_sf, char *error,
                                    size_t error_size);                              /* :433 */
+
+/* ---------------------------------------------------------- DiT block / chain */
+
+/* Additions.  The reference's block-level entry points (h3_dit_w4a8.h:527
+ * h3_dit_w4a8_block_forward_f32, :609 h3_dit_w4a8_layers_forward_f32) are bound
+ * to its checkpoint store and fixed geometry; these take the geometry and the
+ * weight objects explicitly and keep the same argument meaning otherwise
+ * (x/y [seq, dim], modulation [mod_rows, 6, dim], row_map [seq], rope tables
+ * [seq, rope_half]).  The host side is plain C (csrc/h3b_dit.c). */
+enum {
+    H3B_BLOCK_REFERENCE = 0, /* adaLN-QKV-RoPE-SDPA-out*gate | adaLN-fc1-SwiGLU-fc2*gate   (h3_dit_w4a8.c:4291) */
+    H3B_BLOCK_CROSS_GELU = 1 /* + rms_norm / cross-attention(text) / residual, FFN with tanh-GELU            */
+};
+enum { /* linear slots of a block */
+    H3B_LIN_QKV = 0, H3B_LIN_OUT = 1, H3B_LIN_FC1 = 2, H3B_LIN_FC2 = 3,
+    H3B_LIN_CROSS_Q = 4, H3B_LIN_CROSS_KV = 5, H3B_LIN_CROSS_OUT = 6, H3B_LIN_COUNT = 7
+};
+typedef struct h3b_dit_config {
+    int kind;          /* H3B_BLOCK_* */
+    int stream_dtype;  /* H3B_F32 (reference CUDA path) or H3B_BF16 residual stream */
+    int convrot_gs;    /* 0 or 256: activation rotation before every quantised linear */
+    size_t dim, heads, head_dim, ffn, rope_half, n_blocks, mod_rows, t_dim;
+    float eps;
+} h3b_dit_config;
+typedef struct h3b_dit h3b_dit;
+
+h3b_dit *h3b_dit_create(h3_cuda *cuda, const h3b_dit_config *cfg, char *error, size_t error_size);
+void h3b_dit_free(h3b_dit *dit);
+/* The context borrows the weight object (the caller frees it after h3b_dit_free). */
+int h3b_dit_set_linear(h3b_dit *dit, unsigned block, int which, const h3_cuda_w4a8_weight *weight,
+                       char *error, size_t error_size);
+/* Host f32 vectors, copied to the device: norm1/norm2 [dim], q_norm/k_norm [head_dim],
+ * norm_cross [dim] (cross block only, else NULL). */
+int h3b_dit_set_block_aux(h3b_dit *dit, unsigned block, const float *norm1, const float *norm2,
+                          const float *q_norm, const float *k_norm, const float *norm_cross,
+                          char *error, size_t error_size);
+/* adaLN projection of one block: W [mod_rows*6*dim, t_dim], b [mod_rows*6*dim] (host f32). */
+int h3b_dit_set_adaln(h3b_dit *dit, unsigned block, const float *w, const float *b, char *error,
+                      size_t error_size);
+/* modulation[block] = W t_feat + b for every block, on the device (the reference does this on the
+ * host per block and step, h3_dit_w4a8.c:2236).  d_t_feat: [t_dim] f32 on the device. */
+int h3b_dit_project_modulation(h3b_dit *dit, const float *d_t_feat, char *error, size_t error_size);
+/* Device pointer of the projected modulation of `block`: [mod_rows, 6, dim] f32. */
+const float *h3b_dit_modulation(h3b_dit *dit, unsigned block);
+/* Sizes the activation workspace for `seq` rows (+ `text_seq` text rows); afterwards the forward
+ * calls allocate nothing for sequences up to that size. */
+int h3b_dit_reserve(h3b_dit *dit, size_t seq, size_t text_seq, char *error, size_t error_size);
+/* One block, device tensors in the stream dtype.  d_modulation NULL = the projected one.
+ * d_text [text_seq, dim] (cross block only).  d_x and d_y may alias. */
+int h3b_dit_block_forward_dev(h3b_dit *dit, unsigned block, const void *d_x, size_t seq,
+                              const float *d_modulation, const uint32_t *d_row_map,
+                              const float *d_rope_cos, const float *d_rope_sin, const void *d_text,
+                              size_t text_seq, void *d_y, char *error, size_t error_size);
+/* Blocks [first, first+n) chained on the device; uses the projected modulation. */
+int h3b_dit_layers_forward_dev(h3b_dit *dit, unsigned first_block, unsigned n_blocks, const void *d_x,
+                               size_t seq, const uint32_t *d_row_map, const float *d_rope_cos,
+                               const float *d_rope_sin, const void *d_text, size_t text_seq, void *d_y,
+                               char *error, size_t error_size);
+/* Host f32 in / host f32 out, like h3_dit_w4a8_layers_forward_f32: uploads x (and text), the
+ * time feature, row map and rope tables, runs the chain, downloads y.  row_map NULL = all zeros. */
+int h3b_dit_layers_forward_f32(h3b_dit *dit, unsigned first_block, unsigned n_blocks,
+                               const float *t_feat, const float *x, size_t seq,
+                               const uint32_t *row_map, const float *rope_cos, const float *rope_sin,
+                               const float *text, size_t text_seq, float *y, char *error,
+                               size_t error_size);
+/* Kernel launches one block forward issues (for launch accounting). */
+int h3b_dit_launches_per_block(const h3b_dit *dit);
 
 /* ------------------------------------------------------------------ Ulysses */
 

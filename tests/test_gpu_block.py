@@ -1,0 +1,120 @@
+"""Whole-block and block-chain parity through the C ABI (h3b_dit_*) against the CPU oracle."""
+import numpy as np
+import pytest
+
+from tests.conftest import GOLDEN, rel_l2
+
+pytestmark = pytest.mark.gpu
+
+torch = pytest.importorskip("torch")
+
+
+@pytest.fixture(scope="module")
+def cuda():
+    import h3c_b200
+    c = h3c_b200.Cuda(0)
+    yield c
+    c.check()
+    c.close()
+
+
+def dev(a, dtype=None):
+    t = torch.from_numpy(np.ascontiguousarray(a)).cuda()
+    return t if dtype is None else t.to(dtype)
+
+
+def rope_for(oracle, text_len, t, h, w):
+    inv_freq = (1.0 / (10000.0 ** (np.arange(16) / 16.0))).astype(np.float32)
+    pt, ph, pw = oracle.fill_video_pos(text_len, t, 2 * h, 2 * w)
+    return oracle.rope_tables(inv_freq, pt, ph, pw, 1.0)
+
+
+def test_reference_block_f32_stream_against_reference_vectors(cuda, oracle):
+    """The reference's block (SwiGLU, row map with three modalities), f32 residual stream, against the
+    output the reference's own CPU functions produced (tests/golden/block_r.npz)."""
+    from h3c_b200 import dit as D
+    g = np.load(GOLDEN / "block_r.npz")
+    for gs in (0, 256):
+        geo = D.DitGeometry(dim=256, heads=2, head_dim=128, ffn=512, n_blocks=1, mod_rows=3, t_dim=8,
+                            kind=D.BLOCK_REFERENCE, stream_dtype=D.F32, convrot_gs=gs)
+        dit = D.Dit(cuda, geo)
+        for name, slot in D.LIN_NAMES_REF.items():
+            dit.set_linear(0, slot, cuda.weight_from_i8(g[f"w_{name}"], g[f"s_{name}"]))
+        dit.set_block_aux(0, g["norm1"], g["norm2"], g["q_norm"], g["k_norm"])
+        y = dit.block_forward(0, dev(g["x"]), dev(g["cos"]), dev(g["sin"]), modulation=dev(g["modulation"]),
+                              row_map=dev(g["row_map"].view(np.int32)))
+        cuda.check()
+        err = rel_l2(y.cpu().numpy(), g[f"y_gs{gs}"])
+        # attention runs in bf16 on the tensor cores; everything else is f32 / exact int32
+        assert err < 2e-3, (gs, err)
+        dit.close()
+
+
+def make_cross_case(cuda, oracle, seed, grid, text_len, dim, heads, ffn, n_blocks=1):
+    from h3c_b200 import dit as D
+    geo = D.DitGeometry(dim=dim, heads=heads, head_dim=128, ffn=ffn, n_blocks=n_blocks, mod_rows=1, t_dim=32,
+                        kind=D.BLOCK_CROSS_GELU, stream_dtype=D.BF16)
+    dit, host = D.build_synthetic(cuda, geo, seed=seed, keep_host=True)
+    rng = np.random.default_rng(seed + 100)
+    seq = grid[0] * grid[1] * grid[2]
+    x = rng.normal(0, 1, (seq, dim)).astype(np.float32)
+    text = rng.normal(0, 1, (text_len, dim)).astype(np.float32)
+    t_feat = rng.normal(0, 1, geo.t_dim).astype(np.float32)
+    cos, sin = rope_for(oracle, text_len, *grid)
+    return geo, dit, host, x, text, t_feat, cos, sin
+
+
+def oracle_weights(oracle, rec, t_feat, quantised):
+    W = {}
+    for name in ("qkv", "o", "cq", "ckv", "co", "up", "down"):
+        w_i8, s = oracle.w4g128_decode_to_int8(*rec[name])
+        W[name] = (w_i8, s) if quantised else (w_i8.astype(np.float32) * s[:, None])
+    for name in ("norm1", "norm_c", "norm2", "q_norm", "k_norm"):
+        W[name] = rec[name]
+    W["modulation"] = oracle.adaln_project(rec["adaln_w"], rec["adaln_b"], t_feat).reshape(6, -1)
+    return W
+
+
+def test_cross_gelu_block_bf16_stream(cuda, oracle):
+    """The benchmark's block on its own grid shape in miniature: (4,8,8) tokens, 64 text tokens."""
+    geo, dit, host, x, text, t_feat, cos, sin = make_cross_case(cuda, oracle, 1, (4, 8, 8), 64, 256, 2, 512)
+    dit.project_modulation(dev(t_feat))
+    mod = dit.modulation(0).cpu().numpy()
+    W = oracle_weights(oracle, host[0], t_feat, True)
+    assert rel_l2(mod.reshape(6, -1), W["modulation"]) < 1e-5
+    xb = dev(x, torch.bfloat16)
+    tb = dev(text, torch.bfloat16)
+    y = dit.block_forward(0, xb, dev(cos), dev(sin), text=tb)
+    cuda.check()
+    xh, th = xb.float().cpu().numpy(), tb.float().cpu().numpy()
+    kw = dict(heads=2, head_dim=128, ffn=512)
+    same = oracle.block_b(W, xh, th, cos, sin, quantised=True, bf16_stream=True, **kw)
+    e_same = rel_l2(y.float().cpu().numpy(), same)
+    # same-precision oracle (int8 linears, bf16 stored tensors): <= 2e-3 relative L2
+    assert e_same < 2e-3, e_same
+    full = oracle.block_b(oracle_weights(oracle, host[0], t_feat, False), xh, th, cos, sin, quantised=False,
+                          bf16_stream=False, **kw)
+    e_full = rel_l2(y.float().cpu().numpy(), full)
+    # fp32 CPU block (f32 weights, no activation quantisation): <= 2e-2 relative L2
+    assert e_full < 2e-2, e_full
+    dit.close()
+
+
+def test_chain_host_entry_point_matches_device_chain(cuda, oracle):
+    """h3b_dit_layers_forward_f32 (host buffers in/out) == cast + device chain, and two chained blocks
+    agree with the oracle applied twice."""
+    geo, dit, host, x, text, t_feat, cos, sin = make_cross_case(cuda, oracle, 2, (2, 8, 8), 32, 256, 2, 512, n_blocks=2)
+    y_host = dit.layers_forward_f32(t_feat, x, cos, sin, text=text)
+    dit.project_modulation(dev(t_feat))
+    y_dev = dit.layers_forward(dev(x, torch.bfloat16), dev(cos), dev(sin), text=dev(text, torch.bfloat16),
+                               row_map=torch.zeros(x.shape[0], dtype=torch.int32, device="cuda"))
+    cuda.check()
+    assert np.array_equal(y_host, y_dev.float().cpu().numpy())
+    cur = dev(x, torch.bfloat16).float().cpu().numpy()
+    th = dev(text, torch.bfloat16).float().cpu().numpy()
+    for b in range(2):
+        cur = oracle.block_b(oracle_weights(oracle, host[b], t_feat, True), cur, th, cos, sin, heads=2, head_dim=128,
+                             ffn=512, quantised=True, bf16_stream=True)
+    assert rel_l2(y_host, cur) < 3e-3
+    assert dit.launches_per_block == 17
+    dit.close()
