@@ -84,7 +84,9 @@ def test_cross_gelu_block_bf16_stream(cuda, oracle):
     assert rel_l2(mod.reshape(6, -1), W["modulation"]) < 1e-5
     xb = dev(x, torch.bfloat16)
     tb = dev(text, torch.bfloat16)
-    y = dit.block_forward(0, xb, dev(cos), dev(sin), text=tb)
+    # one modulation row shared by every token: the row map is all zeros (NULL would mean row r -> row r)
+    rmap = torch.zeros(x.shape[0], dtype=torch.int32, device="cuda")
+    y = dit.block_forward(0, xb, dev(cos), dev(sin), text=tb, row_map=rmap)
     cuda.check()
     xh, th = xb.float().cpu().numpy(), tb.float().cpu().numpy()
     kw = dict(heads=2, head_dim=128, ffn=512)
