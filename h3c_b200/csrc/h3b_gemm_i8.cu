@@ -68,6 +68,14 @@ __device__ __forceinline__ float gelu_tanh_dev(float v) {   // h3_vision_cuda.c:
     return 0.5f * v * (1.0f + tanhf(inner));
 }
 
+// tanh-GELU with the hardware tanh approximation (relative error about 2^-11), used when the result
+// is stored in a 16-bit type whose own rounding step (2^-9 for bf16) is coarser than that error.
+__device__ __forceinline__ float gelu_tanh_fast(float v) {
+    float inner = 0.7978845608028654f * (v + 0.044715f * v * v * v), t;
+    asm("tanh.approx.f32 %0, %1;" : "=f"(t) : "f"(inner));
+    return 0.5f * v * (1.0f + t);
+}
+
 template <typename T> struct OutTraits;
 template <> struct OutTraits<float> {
     static constexpr int VEC = 4;
@@ -270,7 +278,7 @@ __global__ void __launch_bounds__(gemm::THREADS, 1) k_gemm_i8(const __grid_const
                                     const float g = gate ? __ldg(gate + c) : 1.0f;
                                     val = __fadd_rn(resv[i], __fmul_rn(val, g));
                                 } else if (EPI == H3B_EPI_GELU) {
-                                    val = gelu_tanh_dev(val);
+                                    val = sizeof(OutT) == 2 ? gelu_tanh_fast(val) : gelu_tanh_dev(val);
                                 } else if (EPI == H3B_EPI_SWIGLU) {
                                     const float u = __fmul_rn(__fmul_rn(a, __ldg(p.s_channel + p.n_out + c)),
                                                               (float)(int32_t)r2[v + i]);
