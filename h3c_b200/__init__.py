@@ -215,6 +215,16 @@ class Cuda:
              None, backend, 32, C.byref(epi) if epi is not None else None)
         return y
 
+    def gemm_i8_dequant_f32_w_act_dev_noalloc(self, weight: Weight, x_f32, convrot_gs=0, out=None):
+        """The linear for hosts that must not allocate device memory: same result as
+        gemm_i8_dequant_f32_w_act_dev, scratch taken from a fixed area inside the library."""
+        import torch
+        m = x_f32.shape[0]
+        if out is None:
+            out = torch.empty((m, weight.n), dtype=torch.float32, device=x_f32.device)
+        call("h3b_gemm_i8_dequant_f32_w_act_dev_noalloc", self.h, weight.h, ptr(x_f32), convrot_gs, m, ptr(out))
+        return out
+
     # ---- attention
     def sdpa_bf16(self, q, k, v, scale=None, out=None):
         """q [lq,H,128], k/v [lk,H,128] bf16 views whose last two dims are contiguous -> [lq, H*128] bf16."""

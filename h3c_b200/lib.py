@@ -117,6 +117,9 @@ _SIGS = {
                                                         C.POINTER(DitGemmEpi)) + _ERR),
     "h3_cuda_gemm_i8_dequant_f32_dev_pre_q": (i32, (vp, vp, vp, vp, sz, vp, dbl_p, dbl_p, cs, sz,
                                                     C.POINTER(DitGemmEpi)) + _ERR),
+    "h3b_gemm_i8_dequant_f32_w_act_dev_noalloc": (i32, (vp, vp, vp, i32, sz, vp) + _ERR),
+    "h3b_linear_noalloc_max_codes": (sz, ()),
+    "h3b_linear_noalloc_max_rows": (sz, ()),
     "h3_cuda_convrot_act_f32_dd": (i32, (vp, vp, sz, sz, i32, vp) + _ERR),
     "h3b_gemm_i8_dev": (i32, (vp, vp, vp, vp, sz, vp, C.POINTER(GemmEpi)) + _ERR),
     "h3b_quantize_act_int8_dev": (i32, (vp, vp, i32, sz, sz, vp, vp) + _ERR),

@@ -192,6 +192,29 @@ int h3_cuda_convrot_act_f32_dd(h3_cuda *cuda, const float *d_x, size_t m, size_t
                                int convrot_groupsize, float *d_y, char *error,
                                size_t error_size);                             /* :137 */
 
+/* No counterpart in the reference.  Same result as h3_cuda_gemm_i8_dequant_f32_w_act_dev
+ * (f32 activations in, ConvRot + per-row INT8 quantisation + INT8 GEMM inside, f32 out) for
+ * callers that cannot allocate device memory: a host whose device memory is already fully
+ * committed (resident weights up to the last byte), or one that cannot afford the device-wide
+ * synchronisation cudaMalloc/cudaFree bring in the middle of its step loop, or one that runs the
+ * handle where growth of library scratch is refused.  The INT8 codes and row scales go to a
+ * fixed area compiled into the library (8 MiB + 64 KiB per GPU, held from library load to
+ * process exit) instead of scratch grown on demand, so the call performs no cudaMalloc, cudaFree
+ * or other allocating call.
+ *   - limits: m <= h3b_linear_noalloc_max_rows() (16384) and m * K <= h3b_linear_noalloc_max_codes()
+ *     (8 Mi); larger shapes are rejected with an error that names the limits
+ *   - the first call on each device looks up the area's device address (that device is made
+ *     current); make that first call before starting any stream capture
+ *   - every call on a device shares the one area and leaves its codes behind; each call
+ *     overwrites what it reads, so nothing needs clearing, but two calls whose kernels can run at
+ *     the same time on one GPU (different streams, threads or handles) race on it: serialise them
+ *   - the weight's upload must be complete (h3_cuda_w4a8_weight_ensure_ready). */
+int h3b_gemm_i8_dequant_f32_w_act_dev_noalloc(h3_cuda *cuda, const h3_cuda_w4a8_weight *weight,
+                                              const float *d_x_f32, int convrot_groupsize, size_t m,
+                                              float *d_y_f32, char *error, size_t error_size);
+size_t h3b_linear_noalloc_max_codes(void);
+size_t h3b_linear_noalloc_max_rows(void);
+
 /* Additions: the general form every linear above is built on. */
 enum {            /* element types of activations / outputs */
     H3B_F32 = 0,
