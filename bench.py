@@ -105,7 +105,7 @@ class ClockSampler:
 
 # ------------------------------------------------------------------------------- CPU baseline
 
-def cpu_block_sample(kind: str, threads: int, budget_s: float = 15.0):
+def cpu_block_sample(kind: str, threads: int, budget_s: float = 15.0, grid=None):
     """Times the reference's CPU block path on a bounded row sample of the N=1 workload.
 
     kind "reference": the reference's own C functions (oracle/_ref/libh3_ref.so) driven over row slices
@@ -114,7 +114,8 @@ def cpu_block_sample(kind: str, threads: int, budget_s: float = 15.0):
     Returns (ms_per_step_extrapolated, description)."""
     from oracle.pyoracle import Oracle, Ref
     dim, heads, hd, ffn, text_len = GEO["dim"], GEO["heads"], GEO["head_dim"], GEO["ffn"], GEO["text"]
-    m_full = GRID_1GPU[0] * GRID_1GPU[1] * GRID_1GPU[2]
+    grid = grid or GRID_1GPU
+    m_full = grid[0] * grid[1] * grid[2]
     oracle = Oracle(threads=1)
     impl = Ref() if kind == "reference" else oracle
     rng = np.random.default_rng(0)
@@ -129,7 +130,7 @@ def cpu_block_sample(kind: str, threads: int, budget_s: float = 15.0):
     qn = rng.normal(1, 0.1, hd).astype(np.float32)
     mod = rng.normal(0, 0.3, (1, 6, dim)).astype(np.float32)
     inv_freq = (1.0 / (10000.0 ** (np.arange(16) / 16.0))).astype(np.float32)
-    pt, ph, pw = oracle.fill_video_pos(text_len, GRID_1GPU[0], 2 * GRID_1GPU[1], 2 * GRID_1GPU[2])
+    pt, ph, pw = oracle.fill_video_pos(text_len, grid[0], 2 * grid[1], 2 * grid[2])
     cos, sin = oracle.rope_tables(inv_freq, pt, ph, pw, 1.0)
     k_all = rng.normal(0, 1, (m_full, heads, hd)).astype(np.float32)
     v_all = rng.normal(0, 1, (m_full, heads, hd)).astype(np.float32)
@@ -188,13 +189,13 @@ def reference_arm(args):
     vals = []
     desc = ""
     for _ in range(max(1, min(args.steps, 2))):    # each "step" is one bounded sample; two are plenty on a CPU
-        v, desc = cpu_block_sample(kind, cores, budget_s=20.0)
+        v, desc = cpu_block_sample(kind, cores, budget_s=20.0, grid=GRID_1GPU if args.gpus == 1 else GRID_ULYSSES)
         vals.append(v)
     value = float(np.median(vals))
     line = {"impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": value, "higher_is_better": False,
-            "scaling": "weak", "vs_baseline": None, "dtype": "int8 linears + f32 attention (CPU)", "data": "synthetic",
-            "config": workload_config(1),
+            "scaling": "weak" if args.gpus == 1 else "strong", "vs_baseline": None, "dtype": "int8 linears + f32 attention (CPU)", "data": "synthetic",
+            "config": workload_config(args.gpus),
             "cpu_baseline": {"value": value, "unit": UNIT, "cores": cores, "kind": kind, "sample": desc},
             "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
             "gpu_launches": 0}
@@ -216,6 +217,16 @@ def workload_config(n_gpus):
 
 # -------------------------------------------------------------------------------------- GPU arm
 
+def shard_rows(seq_real, world, rank, align=64):
+    """Ulysses row split (h3_dit_w4a8.c:6275-6277): pad to a multiple of 64, equal slices per rank.
+    Returns (seq_pad, seq_local, first_row, real_rows_of_this_rank)."""
+    seq_pad = (seq_real + align - 1) // align * align
+    seq_local = seq_pad // world
+    first = rank * seq_local
+    real = max(0, min(seq_local, seq_real - first))
+    return seq_pad, seq_local, first, real
+
+
 def gpu_arm(args):
     import torch
     import h3c_b200
@@ -227,108 +238,156 @@ def gpu_arm(args):
     local = int(os.environ.get("LOCAL_RANK", "0"))
     if world != args.gpus:
         raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}: launch with torchrun --nproc-per-node {args.gpus}")
-    if world > 1:
-        raise SystemExit("the Ulysses multi-GPU step is not wired into bench.py yet")
     torch.cuda.set_device(local)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     cuda = h3c_b200.Cuda(local)
     cuda.set_quiet(True)
     geo = D.DitGeometry(dim=GEO["dim"], heads=GEO["heads"], head_dim=GEO["head_dim"], ffn=GEO["ffn"],
                         n_blocks=GEO["n_blocks"], mod_rows=1, t_dim=256, kind=D.BLOCK_CROSS_GELU, stream_dtype=D.BF16)
-    dit = D.build_synthetic(cuda, geo, seed=0)
-    grid = GRID_1GPU
-    seq, text_len = grid[0] * grid[1] * grid[2], GEO["text"]
+    dit = D.build_synthetic(cuda, geo, seed=0)   # same seed on every rank: replicated weights
+    ulysses = world > 1 or args.workload == "ulysses"
+    grid = GRID_ULYSSES if ulysses else GRID_1GPU
+    seq_real, text_len = grid[0] * grid[1] * grid[2], GEO["text"]
+    seq_pad, seq_local, first_row, real_rows = shard_rows(seq_real, world, rank)
+    comm = None
+    if world > 1:
+        uid = torch.zeros(128, dtype=torch.uint8, device="cuda")
+        if rank == 0:
+            uid.copy_(torch.frombuffer(bytearray(h3c_b200.UlyssesComm.unique_id()), dtype=torch.uint8))
+        dist.broadcast(uid, 0)
+        comm = h3c_b200.UlyssesComm(rank, world, bytes(uid.cpu().numpy().tobytes()), local)
+        dit.set_ulysses(comm)
+    rows = seq_local if world > 1 else seq_real
     oracle = Oracle()
     inv_freq = (1.0 / (10000.0 ** (np.arange(16) / 16.0))).astype(np.float32)
     pt, ph, pw = oracle.fill_video_pos(text_len, grid[0], 2 * grid[1], 2 * grid[2])
     cos_h, sin_h = oracle.rope_tables(inv_freq, pt, ph, pw, 1.0)
-    rng = np.random.default_rng(0)
-    # host (pinned) inputs of one step
-    x_h = torch.from_numpy(rng.normal(0, 1, (seq, geo.dim)).astype(np.float32)).pin_memory()
-    text_h = torch.from_numpy(rng.normal(0, 1, (text_len, geo.dim)).astype(np.float32)).pin_memory()
+    if world > 1:   # tables cover the padded gathered sequence; pad rows get angle 0
+        padc = np.ones((seq_pad - seq_real, cos_h.shape[1]), np.float32)
+        cos_h = np.concatenate([cos_h, padc])
+        sin_h = np.concatenate([sin_h, 0 * padc])
+    rng = np.random.default_rng(1000 + rank)
+    x_np = rng.normal(0, 1, (rows, geo.dim)).astype(np.float32)
+    if world > 1:
+        x_np[real_rows:] = 0.0   # pad rows of the last rank
+    text_np = np.random.default_rng(7).normal(0, 1, (text_len, geo.dim)).astype(np.float32)   # replicated
+    x_h = torch.from_numpy(x_np).pin_memory()
+    text_h = torch.from_numpy(text_np).pin_memory()
     cos_p, sin_p = torch.from_numpy(cos_h).pin_memory(), torch.from_numpy(sin_h).pin_memory()
     # timestep t = 0.5: sinusoidal feature of width t_dim (synthetic stand-in for the embedding table)
     half = geo.t_dim // 2
     freqs = np.exp(-np.log(10000.0) * np.arange(half) / half)
     t_feat_h = torch.from_numpy(np.concatenate([np.cos(500.0 * freqs), np.sin(500.0 * freqs)]).astype(np.float32)).pin_memory()
-    y_h = torch.empty((seq, geo.dim), dtype=torch.float32).pin_memory()
-    # device-resident copies
+    y_h = torch.empty((rows, geo.dim), dtype=torch.float32).pin_memory()
     x_d = x_h.cuda().to(torch.bfloat16)
     text_d = text_h.cuda().to(torch.bfloat16)
     cos_d, sin_d, t_d = cos_p.cuda(), sin_p.cuda(), t_feat_h.cuda()
-    rmap_d = torch.zeros(seq, dtype=torch.int32, device="cuda")
+    rmap_d = torch.zeros(rows, dtype=torch.int32, device="cuda")
     y_d = torch.empty_like(x_d)
-    dit.reserve(seq, text_len)
+    dit.reserve(rows, text_len)
 
     def step_resident():
         dit.project_modulation(t_d)
-        dit.layers_forward(x_d, cos_d, sin_d, row_map=rmap_d, text=text_d, out=y_d)
+        if world > 1:
+            dit.layers_forward_ulysses(x_d, seq_real, cos_d, sin_d, row_map=rmap_d, text=text_d, out=y_d)
+        else:
+            dit.layers_forward(x_d, cos_d, sin_d, row_map=rmap_d, text=text_d, out=y_d)
 
     def step_e2e():
-        dit.layers_forward_f32(t_feat_h, x_h, cos_p, sin_p, text=text_h, out=y_h)
+        if world > 1:
+            dit.layers_forward_ulysses_f32(t_feat_h, x_h, seq_real, cos_p, sin_p, text=text_h, out=y_h)
+        else:
+            dit.layers_forward_f32(t_feat_h, x_h, cos_p, sin_p, text=text_h, out=y_h)
+
+    def sync_all():
+        torch.cuda.synchronize()
+        if dist is not None:
+            dist.barrier()
+            torch.cuda.synchronize()
+
+    def max_over_ranks(ms):
+        if dist is None:
+            return ms
+        t = torch.tensor([ms], dtype=torch.float64, device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
 
     for _ in range(args.warmup):
         step_resident()
-    torch.cuda.synchronize()
+    sync_all()
     cuda.check()
 
     sampler = ClockSampler(local)
     sampler.start()
     time.sleep(0.3)
     cuda.launch_count(reset=True)
-    ev = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps + 1)]
-    torch.cuda.synchronize()
-    ev[0].record()
-    for i in range(args.steps):
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    sync_all()
+    e0.record()
+    for _ in range(args.steps):
         step_resident()
-        ev[i + 1].record()
-    torch.cuda.synchronize()
+    e1.record()
+    sync_all()
     launches = cuda.launch_count(reset=True)
-    total_ms = ev[0].elapsed_time(ev[-1])
+    ms_step = max_over_ranks(e0.elapsed_time(e1) / args.steps)
     clocks = sampler.stop()
     cuda.check()
-    ms_step = total_ms / args.steps
 
-    # per-kernel-class device time of one step (events around every launch of the class)
     prof = profile_classes(cuda, dit, step_resident)
+    sync_all()
 
-    # end to end through the host-buffer entry point
     e2e_ms = None
     if not args.skip_e2e:
         for _ in range(max(1, min(args.warmup, 2))):
             step_e2e()
-        torch.cuda.synchronize()
+        sync_all()
         t0 = time.perf_counter()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
         for _ in range(args.steps):
             step_e2e()
         e1.record()
         torch.cuda.synchronize()
-        e2e_ms = max(e0.elapsed_time(e1), (time.perf_counter() - t0) * 1e3) / args.steps
-    h2d = x_h.numel() * 4 + text_h.numel() * 4 + cos_p.numel() * 8 + t_feat_h.numel() * 4
+        e2e_ms = max_over_ranks(max(e0.elapsed_time(e1), (time.perf_counter() - t0) * 1e3) / args.steps)
+    tables = cos_p.numel() * 8
+    h2d = x_h.numel() * 4 + text_h.numel() * 4 + tables + t_feat_h.numel() * 4
     d2h = y_h.numel() * 4
 
-    pk = peaks()
-    lin_f, attn_f = block_flops(seq, text_len, geo.dim, geo.ffn)
-    roof = roofline(prof, lin_f, attn_f, geo.n_blocks, pk)
-    if args.skip_cpu_baseline:
-        cpu_ms, cpu_desc = None, "skipped (--skip-cpu-baseline)"
-    else:
-        cpu_ms, cpu_desc = cpu_block_sample("reference" if ref_available() else "port", os.cpu_count() or 1)
-
-    line = {"metric": METRIC, "value": ms_step, "unit": UNIT, "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
-            "ms_per_step": ms_step, "higher_is_better": False, "scaling": "weak", "vs_baseline": None,
-            "dtype": "int8 (linears, int32 accumulate) + bf16 (attention, f32 accumulate)", "data": "synthetic",
-            "config": workload_config(1),
-            "e2e": {"value": e2e_ms, "unit": UNIT, "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": int(d2h)},
-            "gpu_launches": int(launches), "clocks": clocks, "roofline": roof,
-            "cpu_baseline": {"value": cpu_ms, "unit": UNIT, "cores": os.cpu_count() or 1,
-                             "kind": "reference" if ref_available() else "port", "sample": cpu_desc},
-            "step_tflops": (lin_f + attn_f) * geo.n_blocks / (ms_step * 1e-3) / 1e12,
-            "kernel_classes": prof}
-    print(json.dumps(line))
+    if rank == 0:
+        pk = peaks()
+        # algorithmic work of this rank: its rows through every linear, heads/U heads of the full attention
+        lin_f, _ = block_flops(rows, text_len, geo.dim, geo.ffn)
+        attn_f = (4.0 * seq_real * seq_real * geo.dim) / world + 4.0 * rows * text_len * geo.dim
+        roof = roofline(prof, lin_f, attn_f, geo.n_blocks, pk)
+        lin_all, attn_all = block_flops(seq_real, text_len, geo.dim, geo.ffn)
+        if args.skip_cpu_baseline or world > 1:
+            cpu = None
+        else:
+            kind = "reference" if ref_available() else "port"
+            cpu_ms, cpu_desc = cpu_block_sample(kind, os.cpu_count() or 1)
+            cpu = {"value": cpu_ms, "unit": UNIT, "cores": os.cpu_count() or 1, "kind": kind, "sample": cpu_desc}
+        cfg = workload_config(world if world > 1 else (8 if ulysses else 1))
+        if world == 1 and ulysses:
+            cfg["parallelism"] = "single GPU (same workload as the Ulysses runs)"
+        line = {"metric": METRIC, "value": ms_step, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+                "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": False,
+                "scaling": "strong" if ulysses else "weak", "vs_baseline": None,
+                "dtype": "int8 (linears, int32 accumulate) + bf16 (attention, f32 accumulate)", "data": "synthetic",
+                "config": cfg,
+                "e2e": {"value": e2e_ms, "unit": UNIT, "h2d_bytes_per_step": int(h2d) * world,
+                        "d2h_bytes_per_step": int(d2h) * world},
+                "gpu_launches": int(launches) * world, "clocks": clocks, "roofline": roof, "cpu_baseline": cpu,
+                "step_tflops": (lin_all + attn_all) * geo.n_blocks / (ms_step * 1e-3) / 1e12, "kernel_classes": prof}
+        print(json.dumps(line))
+    sync_all()
     dit.close()
+    if comm is not None:
+        comm.close()
     cuda.close()
+    if dist is not None:
+        dist.destroy_process_group()
 
 
 def ref_available():
@@ -383,6 +442,8 @@ def main():
     ap.add_argument("--steps", type=int, default=5)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="auto", choices=["auto", "ulysses"],
+                    help="'ulysses' runs the 50,220-token workload at any N (N=1 gives the scaling reference)")
     ap.add_argument("--skip-cpu-baseline", action="store_true", help="omit the CPU sample (profiling runs)")
     ap.add_argument("--skip-e2e", action="store_true", help="omit the host-buffer measurement (profiling runs)")
     args = ap.parse_args()

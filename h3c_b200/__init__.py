@@ -280,3 +280,32 @@ def ulysses_pad_seq(seq, align=64):
 
 def ulysses_local_rows(seq_pad, ulysses, rank):
     return int(load().h3_ulysses_local_rows(seq_pad, ulysses, rank))
+
+
+class UlyssesComm:
+    """Per-rank sequence-parallel communicator (h3_ulysses_cfg + h3b_ulysses_comm_init_rank)."""
+
+    def __init__(self, rank: int, world_size: int, unique_id: bytes, device_index: int):
+        self.cfg = _l.UlyssesCfg(1, world_size, 1, rank, world_size, None)
+        buf = C.create_string_buffer(unique_id, 128)
+        call("h3b_ulysses_comm_init_rank", C.byref(self.cfg), rank, world_size, buf, device_index)
+        self.rank, self.world_size = rank, world_size
+
+    @staticmethod
+    def unique_id() -> bytes:
+        buf = C.create_string_buffer(128)
+        call("h3b_ulysses_unique_id", buf)
+        return buf.raw
+
+    def set_compute(self, stream):
+        call("h3_ulysses_comm_set_compute", C.byref(self.cfg), self.rank, stream.cuda_stream)
+
+    def a2a_qkv(self, x, out, seq_local, heads, head_dim):
+        call("h3_ulysses_a2a_qkv", C.byref(self.cfg), ptr(x), ptr(out), seq_local, heads, head_dim, x.element_size())
+
+    def a2a_attn_out(self, x, out, seq_local, heads, head_dim):
+        call("h3_ulysses_a2a_attn_out", C.byref(self.cfg), ptr(x), ptr(out), seq_local, heads, head_dim,
+             x.element_size())
+
+    def close(self):
+        load().h3_ulysses_comm_destroy(C.byref(self.cfg))

@@ -50,6 +50,7 @@ struct h3b_dit {
     void *text_dev;         /* stream-dtype copy of the text tokens */
     uint32_t *st_map;
     float *st_cos, *st_sin, *st_t;
+    h3_ulysses_cfg *uly;    /* attached per-rank communicator, or NULL */
 };
 
 static int fail(char *error, size_t error_size, const char *fmt, ...) {
@@ -211,13 +212,14 @@ const float *h3b_dit_modulation(h3b_dit *d, unsigned block) {
 }
 
 int h3b_dit_reserve(h3b_dit *d, size_t seq, size_t text_seq, char *error, size_t error_size) {
-    size_t D, I, F, widest, es;
+    size_t D, I, F, widest, es, table_rows;
     if (!d || !seq) return fail(error, error_size, "h3b_dit_reserve: invalid arguments");
     if (seq <= d->cap_seq && text_seq <= d->cap_text) return 1;
     if (h3_cuda_graph_capture(d->cuda)) return fail(error, error_size, "workspace growth is forbidden during graph capture");
     cudaStreamSynchronize((cudaStream_t)h3_cuda_op_stream(d->cuda));
     free_ws(d);
     D = d->cfg.dim; I = inner(d); F = d->cfg.ffn; es = elem(d);
+    table_rows = seq * (size_t)((d->uly && d->uly->comm) ? d->uly->ulysses : 1);
     widest = D > F ? D : F;
     if (I > widest) widest = I;
     if (!dmalloc(&d->xa, seq * D * es, error, error_size) || !dmalloc(&d->xb, seq * D * es, error, error_size) ||
@@ -229,8 +231,8 @@ int h3b_dit_reserve(h3b_dit *d, size_t seq, size_t text_seq, char *error, size_t
         !dmalloc((void **)&d->s8, seq * sizeof(float), error, error_size) ||
         !dmalloc((void **)&d->st_x, seq * D * sizeof(float), error, error_size) ||
         !dmalloc((void **)&d->st_map, seq * sizeof(uint32_t), error, error_size) ||
-        !dmalloc((void **)&d->st_cos, seq * (d->cfg.rope_half ? d->cfg.rope_half : 1) * sizeof(float), error, error_size) ||
-        !dmalloc((void **)&d->st_sin, seq * (d->cfg.rope_half ? d->cfg.rope_half : 1) * sizeof(float), error, error_size) ||
+        !dmalloc((void **)&d->st_cos, table_rows * (d->cfg.rope_half ? d->cfg.rope_half : 1) * sizeof(float), error, error_size) ||
+        !dmalloc((void **)&d->st_sin, table_rows * (d->cfg.rope_half ? d->cfg.rope_half : 1) * sizeof(float), error, error_size) ||
         !dmalloc((void **)&d->st_t, (d->cfg.t_dim ? d->cfg.t_dim : 1) * sizeof(float), error, error_size))
         return 0;
     if (d->cfg.kind == H3B_BLOCK_CROSS_GELU) {
@@ -274,16 +276,16 @@ static int gemm(h3b_dit *d, const h3_cuda_w4a8_weight *w, const int8_t *q, const
     return h3b_gemm_i8_dev(d->cuda, w, q, s, m, y, &e, error, error_size);
 }
 
-int h3b_dit_block_forward_dev(h3b_dit *d, unsigned block, const void *d_x, size_t seq, const float *d_modulation,
-                              const uint32_t *d_row_map, const float *d_cos, const float *d_sin, const void *d_text,
-                              size_t text_seq, void *d_y, char *error, size_t error_size) {
+static int block_forward(h3b_dit *d, unsigned block, const void *d_x, size_t seq, size_t seq_real,
+                         const float *d_modulation, const uint32_t *d_row_map, const float *d_cos, const float *d_sin,
+                         const void *d_text, size_t text_seq, void *d_y, char *error, size_t error_size) {
     const h3b_block *b;
     const float *mod;
     size_t D, I, F;
     int dt, i;
     float scale;
     if (!d || block >= d->cfg.n_blocks || !d_x || !d_y || !seq)
-        return fail(error, error_size, "h3b_dit_block_forward_dev: invalid arguments");
+        return fail(error, error_size, "block forward: invalid arguments");
     b = &d->blocks[block];
     mod = d_modulation ? d_modulation : b->modulation;
     if (!mod) return fail(error, error_size, "block %u: no modulation given or projected", block);
@@ -301,12 +303,34 @@ int h3b_dit_block_forward_dev(h3b_dit *d, unsigned block, const void *d_x, size_
     if (!norm_quant(d, d_x, dt, seq, D, b->norm1, mod, d_row_map, 0, 1, 0, d->q8, d->s8, error, error_size)) return 0;
     if (!gemm(d, b->lin[H3B_LIN_QKV], d->q8, d->s8, seq, d->qkv, H3B_EPI_PLAIN, dt, NULL, NULL, NULL, 0, error, error_size))
         return 0;
-    if (!h3b_qkv_rope_dev(d->cuda, d->qkv, dt, b->q_norm, b->k_norm, d_cos, d_sin, seq, d->cfg.heads, d->cfg.head_dim,
-                          d->cfg.rope_half, d->cfg.eps, 0, 1, d->q, d->k, d->v, H3B_BF16, error, error_size))
-        return 0;
-    if (!h3b_sdpa_bf16_dev(d->cuda, d->q, I, d->k, I, d->v, I, seq, seq, d->cfg.heads, d->cfg.head_dim, scale, d->att, I,
-                           error, error_size))
-        return 0;
+    if (!d->uly || !d->uly->comm) {
+        if (!h3b_qkv_rope_dev(d->cuda, d->qkv, dt, b->q_norm, b->k_norm, d_cos, d_sin, seq, d->cfg.heads,
+                              d->cfg.head_dim, d->cfg.rope_half, d->cfg.eps, 0, 1, d->q, d->k, d->v, H3B_BF16, error,
+                              error_size))
+            return 0;
+        if (!h3b_sdpa_bf16_dev(d->cuda, d->q, I, d->k, I, d->v, I, seq, seq, d->cfg.heads, d->cfg.head_dim, scale,
+                               d->att, I, error, error_size))
+            return 0;
+    } else {
+        /* Ulysses: rows are this rank's slice.  Exchange sequence for heads, attend over the whole
+         * (real) sequence with heads/U heads, exchange back.  Both exchanges run in place. */
+        const size_t U = (size_t)d->uly->ulysses, hl = d->cfg.heads / U, seq_pad = seq * U, Il = hl * d->cfg.head_dim;
+        const size_t es = dt == H3B_F32 ? 4 : 2;
+        if (!h3_ulysses_a2a_qkv(d->uly, d->qkv, d->qkv, seq, d->cfg.heads, d->cfg.head_dim, (int)es, error, error_size))
+            return 0;
+        if (!h3b_qkv_rope_dev(d->cuda, d->qkv, dt, b->q_norm, b->k_norm, d_cos, d_sin, seq_pad, hl, d->cfg.head_dim,
+                              d->cfg.rope_half, d->cfg.eps, 0, 1, d->q, d->k, d->v, H3B_BF16, error, error_size))
+            return 0;
+        if (!h3b_sdpa_bf16_dev(d->cuda, d->q, Il, d->k, Il, d->v, Il, seq_real, seq_real, hl, d->cfg.head_dim, scale,
+                               d->att, Il, error, error_size))
+            return 0;
+        if (seq_pad > seq_real &&
+            cudaMemsetAsync((char *)d->att + seq_real * Il * 2, 0, (seq_pad - seq_real) * Il * 2,
+                            (cudaStream_t)h3_cuda_op_stream(d->cuda)) != cudaSuccess)
+            return fail(error, error_size, "block %u: clearing pad rows failed", block);
+        if (!h3_ulysses_a2a_attn_out(d->uly, d->att, d->att, seq, d->cfg.heads, d->cfg.head_dim, 2, error, error_size))
+            return 0;
+    }
     if (!norm_quant(d, d->att, H3B_BF16, seq, I, NULL, NULL, NULL, 0, 0, 1, d->q8, d->s8, error, error_size)) return 0;
     /* x1 -> xa */
     if (!gemm(d, b->lin[H3B_LIN_OUT], d->q8, d->s8, seq, d->xa, H3B_EPI_GATE, dt, d_x, mod, d_row_map, 2, error,
@@ -351,6 +375,49 @@ int h3b_dit_block_forward_dev(h3b_dit *d, unsigned block, const void *d_x, size_
                 error_size);
 }
 
+int h3b_dit_block_forward_dev(h3b_dit *d, unsigned block, const void *d_x, size_t seq, const float *d_modulation,
+                              const uint32_t *d_row_map, const float *d_cos, const float *d_sin, const void *d_text,
+                              size_t text_seq, void *d_y, char *error, size_t error_size) {
+    if (d && d->uly && d->uly->comm)
+        return fail(error, error_size, "block_forward_dev: a Ulysses communicator is attached; use the ulysses chain");
+    return block_forward(d, block, d_x, seq, seq, d_modulation, d_row_map, d_cos, d_sin, d_text, text_seq, d_y, error,
+                         error_size);
+}
+
+int h3b_dit_set_ulysses(h3b_dit *d, h3_ulysses_cfg *cfg, char *error, size_t error_size) {
+    if (!d) return fail(error, error_size, "h3b_dit_set_ulysses: NULL context");
+    if (cfg && cfg->comm) {
+        if (!h3_ulysses_validate((int)d->cfg.heads, H3_ULYSSES_PACKED_ALIGN, 1, cfg->ulysses, 1, error, error_size)) return 0;
+        if (!h3_ulysses_comm_set_compute(cfg, cfg->rank, h3_cuda_op_stream(d->cuda), error, error_size)) return 0;
+    }
+    if (d->uly != cfg) {
+        /* staging tables are sized for the gathered sequence: start from an empty workspace */
+        cudaStreamSynchronize((cudaStream_t)h3_cuda_op_stream(d->cuda));
+        free_ws(d);
+    }
+    d->uly = cfg;
+    return 1;
+}
+
+int h3b_dit_layers_forward_ulysses_dev(h3b_dit *d, unsigned first, unsigned n, const void *d_x, size_t seq_local,
+                                       size_t seq_real, const uint32_t *d_row_map, const float *d_cos_full,
+                                       const float *d_sin_full, const void *d_text, size_t text_seq, void *d_y,
+                                       char *error, size_t error_size) {
+    unsigned i;
+    const void *cur = d_x;
+    if (!d || !n || first + n > d->cfg.n_blocks) return fail(error, error_size, "layers_forward_ulysses: bad block range");
+    if (!d->uly || !d->uly->comm) return fail(error, error_size, "layers_forward_ulysses: no communicator attached");
+    if (!seq_real || seq_real > seq_local * (size_t)d->uly->ulysses)
+        return fail(error, error_size, "layers_forward_ulysses: seq_real must be in (0, U*seq_local]");
+    for (i = 0; i < n; i++) {
+        if (!block_forward(d, first + i, cur, seq_local, seq_real, NULL, d_row_map, d_cos_full, d_sin_full, d_text,
+                           text_seq, d_y, error, error_size))
+            return 0;
+        cur = d_y;
+    }
+    return 1;
+}
+
 int h3b_dit_layers_forward_dev(h3b_dit *d, unsigned first, unsigned n, const void *d_x, size_t seq,
                                const uint32_t *d_row_map, const float *d_cos, const float *d_sin, const void *d_text,
                                size_t text_seq, void *d_y, char *error, size_t error_size) {
@@ -359,25 +426,29 @@ int h3b_dit_layers_forward_dev(h3b_dit *d, unsigned first, unsigned n, const voi
     if (!d || !n || first + n > d->cfg.n_blocks) return fail(error, error_size, "layers_forward: bad block range");
     /* every block writes its result to d_y; inside a block the input is last read by the
      * out-projection epilogue, before anything is written to d_y, so in-place chaining is safe */
+    if (d->uly && d->uly->comm) return fail(error, error_size, "layers_forward: a Ulysses communicator is attached");
     for (i = 0; i < n; i++) {
-        if (!h3b_dit_block_forward_dev(d, first + i, cur, seq, NULL, d_row_map, d_cos, d_sin, d_text, text_seq, d_y, error,
-                                       error_size))
+        if (!block_forward(d, first + i, cur, seq, seq, NULL, d_row_map, d_cos, d_sin, d_text, text_seq, d_y, error,
+                           error_size))
             return 0;
         cur = d_y;
     }
     return 1;
 }
 
-int h3b_dit_layers_forward_f32(h3b_dit *d, unsigned first, unsigned n, const float *t_feat, const float *x, size_t seq,
-                               const uint32_t *row_map, const float *rope_cos, const float *rope_sin, const float *text,
-                               size_t text_seq, float *y, char *error, size_t error_size) {
+static int layers_forward_host(h3b_dit *d, unsigned first, unsigned n, const float *t_feat, const float *x, size_t seq,
+                               size_t seq_real, const uint32_t *row_map, const float *rope_cos, const float *rope_sin,
+                               const float *text, size_t text_seq, float *y, char *error, size_t error_size) {
     cudaStream_t st;
-    size_t D, rh;
+    size_t D, rh, table_rows;
+    const int uly = seq_real != 0;
     void *dx;
     const void *dtext = NULL;
     cudaError_t e;
     if (!d || !x || !y || !seq || !t_feat) return fail(error, error_size, "layers_forward_f32: invalid arguments");
+    if (uly && (!d->uly || !d->uly->comm)) return fail(error, error_size, "layers_forward_ulysses_f32: no communicator attached");
     if (!h3b_dit_reserve(d, seq, text_seq, error, error_size)) return 0;
+    table_rows = uly ? seq * (size_t)d->uly->ulysses : seq;
     st = (cudaStream_t)h3_cuda_op_stream(d->cuda);
     D = d->cfg.dim; rh = d->cfg.rope_half;
     cudaMemcpyAsync(d->st_x, x, seq * D * sizeof(float), cudaMemcpyHostToDevice, st);
@@ -386,8 +457,8 @@ int h3b_dit_layers_forward_f32(h3b_dit *d, unsigned first, unsigned n, const flo
     else cudaMemsetAsync(d->st_map, 0, seq * sizeof(uint32_t), st);
     if (rh) {
         if (!rope_cos || !rope_sin) return fail(error, error_size, "layers_forward_f32: rope tables missing");
-        cudaMemcpyAsync(d->st_cos, rope_cos, seq * rh * sizeof(float), cudaMemcpyHostToDevice, st);
-        cudaMemcpyAsync(d->st_sin, rope_sin, seq * rh * sizeof(float), cudaMemcpyHostToDevice, st);
+        cudaMemcpyAsync(d->st_cos, rope_cos, table_rows * rh * sizeof(float), cudaMemcpyHostToDevice, st);
+        cudaMemcpyAsync(d->st_sin, rope_sin, table_rows * rh * sizeof(float), cudaMemcpyHostToDevice, st);
     }
     if (d->cfg.kind == H3B_BLOCK_CROSS_GELU) {
         if (!text || !text_seq) return fail(error, error_size, "layers_forward_f32: text tokens missing");
@@ -407,9 +478,14 @@ int h3b_dit_layers_forward_f32(h3b_dit *d, unsigned first, unsigned n, const flo
         if (!h3b_cast_dev(d->cuda, d->st_x, H3B_F32, d->io, d->cfg.stream_dtype, seq * D, error, error_size)) return 0;
         dx = d->io;
     }
-    if (!h3b_dit_layers_forward_dev(d, first, n, dx, seq, d->st_map, d->st_cos, d->st_sin, dtext, text_seq, dx, error,
-                                    error_size))
+    if (uly) {
+        if (!h3b_dit_layers_forward_ulysses_dev(d, first, n, dx, seq, seq_real, d->st_map, d->st_cos, d->st_sin, dtext,
+                                                text_seq, dx, error, error_size))
+            return 0;
+    } else if (!h3b_dit_layers_forward_dev(d, first, n, dx, seq, d->st_map, d->st_cos, d->st_sin, dtext, text_seq, dx,
+                                           error, error_size)) {
         return 0;
+    }
     if (d->cfg.stream_dtype != H3B_F32) {
         if (!h3b_cast_dev(d->cuda, dx, d->cfg.stream_dtype, d->st_x, H3B_F32, seq * D, error, error_size)) return 0;
         dx = d->st_x;
@@ -418,4 +494,20 @@ int h3b_dit_layers_forward_f32(h3b_dit *d, unsigned first, unsigned n, const flo
     if (e == cudaSuccess) e = cudaStreamSynchronize(st);
     if (e != cudaSuccess) return fail(error, error_size, "layers_forward_f32 download: %s", cudaGetErrorString(e));
     return h3b_cuda_check(d->cuda, NULL, error, error_size);
+}
+
+int h3b_dit_layers_forward_f32(h3b_dit *d, unsigned first, unsigned n, const float *t_feat, const float *x, size_t seq,
+                               const uint32_t *row_map, const float *rope_cos, const float *rope_sin, const float *text,
+                               size_t text_seq, float *y, char *error, size_t error_size) {
+    return layers_forward_host(d, first, n, t_feat, x, seq, 0, row_map, rope_cos, rope_sin, text, text_seq, y, error,
+                               error_size);
+}
+
+int h3b_dit_layers_forward_ulysses_f32(h3b_dit *d, unsigned first, unsigned n, const float *t_feat, const float *x_local,
+                                       size_t seq_local, size_t seq_real, const uint32_t *row_map,
+                                       const float *rope_cos_full, const float *rope_sin_full, const float *text,
+                                       size_t text_seq, float *y_local, char *error, size_t error_size) {
+    if (!seq_real) return fail(error, error_size, "layers_forward_ulysses_f32: seq_real must be > 0");
+    return layers_forward_host(d, first, n, t_feat, x_local, seq_local, seq_real, row_map, rope_cos_full, rope_sin_full,
+                               text, text_seq, y_local, error, error_size);
 }

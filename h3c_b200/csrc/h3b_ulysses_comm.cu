@@ -1,0 +1,390 @@
+// Ulysses sequence<->head all-to-all around self-attention (the reference's h3_ulysses_comm.cu,
+// six-function API kept) over NCCL point-to-point groups on NVLink.
+//
+// Two ways to own ranks:
+//   h3_ulysses_comm_init       one process drives every GPU (the reference's model,
+//                              h3_ulysses_comm.cu:221 ncclCommInitAll)
+//   h3b_ulysses_comm_init_rank one process per GPU: the caller distributes a 128-byte NCCL
+//                              unique id (h3b_ulysses_unique_id) by its own means
+// Index maps (h3_ulysses_comm.cu:256-344), hl = heads / U:
+//   QKV:       in[s][q][h][d] -> pack[peer = h / hl][s][q][h % hl][d]; peer p's chunk lands as
+//              out[(src * seq_local + s)][q][hl][d] on rank p -- the received chunks already are
+//              the output layout, so they are received in place and no unpack kernel is needed
+//   attn-out:  in[(src * seq_local + s)][hl][d] is already chunked by destination, sent as it is;
+//              unpack[peer][s][hl][d] -> out[s][peer * hl + hl'][d]
+// NCCL is bound at run time (dlopen of libnccl.so.2) so the library loads where NCCL is absent;
+// every entry point then fails with a message, like the reference's stub (h3_ulysses_comm_stub.c).
+#include <dlfcn.h>
+#include <nccl.h>
+#include <stdlib.h>
+#include <string.h>
+
+#include "h3b_internal.h"
+
+namespace h3b {
+
+struct NcclApi {
+    void *handle;
+    ncclResult_t (*GetUniqueId)(ncclUniqueId *);
+    ncclResult_t (*CommInitRank)(ncclComm_t *, int, ncclUniqueId, int);
+    ncclResult_t (*CommInitAll)(ncclComm_t *, int, const int *);
+    ncclResult_t (*CommDestroy)(ncclComm_t);
+    ncclResult_t (*Send)(const void *, size_t, ncclDataType_t, int, ncclComm_t, cudaStream_t);
+    ncclResult_t (*Recv)(void *, size_t, ncclDataType_t, int, ncclComm_t, cudaStream_t);
+    ncclResult_t (*GroupStart)(void);
+    ncclResult_t (*GroupEnd)(void);
+    const char *(*GetErrorString)(ncclResult_t);
+};
+
+static NcclApi *nccl_api(char *err, size_t err_size) {
+    static NcclApi api;
+    static int state = 0;   // 0 untried, 1 ok, -1 failed
+    if (state == 0) {
+        const char *names[] = {"libnccl.so.2", "libnccl.so"};
+        for (int i = 0; i < 2 && !api.handle; i++) api.handle = dlopen(names[i], RTLD_NOW | RTLD_GLOBAL);
+        state = -1;
+        if (api.handle) {
+#define H3B_SYM(field, name) *(void **)(&api.field) = dlsym(api.handle, name)
+            H3B_SYM(GetUniqueId, "ncclGetUniqueId");
+            H3B_SYM(CommInitRank, "ncclCommInitRank");
+            H3B_SYM(CommInitAll, "ncclCommInitAll");
+            H3B_SYM(CommDestroy, "ncclCommDestroy");
+            H3B_SYM(Send, "ncclSend");
+            H3B_SYM(Recv, "ncclRecv");
+            H3B_SYM(GroupStart, "ncclGroupStart");
+            H3B_SYM(GroupEnd, "ncclGroupEnd");
+            H3B_SYM(GetErrorString, "ncclGetErrorString");
+#undef H3B_SYM
+            if (api.GetUniqueId && api.CommInitRank && api.CommInitAll && api.CommDestroy && api.Send && api.Recv &&
+                api.GroupStart && api.GroupEnd)
+                state = 1;
+        }
+    }
+    if (state != 1) {
+        fail(err, err_size, "ulysses comm: NCCL not available (libnccl.so.2 could not be loaded)");
+        return NULL;
+    }
+    return &api;
+}
+
+enum { MAX_U = 8 };
+
+struct CommState {
+    int n_ranks;             // U
+    int n_local;             // ranks owned by this process
+    int local_rank[MAX_U];   // global rank of each owned slot
+    int device[MAX_U];
+    ncclComm_t comm[MAX_U];
+    cudaStream_t stream[MAX_U];    // communication stream
+    cudaStream_t compute[MAX_U];   // borrowed compute stream (NULL = legacy default)
+    cudaEvent_t ev_compute[MAX_U], ev_comm[MAX_U];
+    void *scratch[MAX_U];
+    size_t scratch_bytes[MAX_U];
+    const void *bound_in[MAX_U];
+    void *bound_out[MAX_U];
+};
+
+static int slot_of(const CommState *st, int rank) {
+    for (int i = 0; i < st->n_local; i++)
+        if (st->local_rank[i] == rank) return i;
+    return -1;
+}
+
+// in[s][q][h][d] -> out[peer][s][q][hl][d]; 16-byte vectors (head_dim * elem is a multiple of 16)
+__global__ void k_ulysses_pack_qkv(const uint4 *in, uint4 *out, size_t seq_local, unsigned heads, unsigned vec_per_head,
+                                   unsigned u) {
+    const unsigned hl = heads / u;
+    const size_t n = seq_local * 3 * heads * vec_per_head;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
+        const unsigned d = (unsigned)(i % vec_per_head);
+        size_t t = i / vec_per_head;
+        const unsigned h = (unsigned)(t % heads);
+        t /= heads;
+        const unsigned q = (unsigned)(t % 3);
+        const size_t s = t / 3;
+        const unsigned peer = h / hl;
+        out[((((size_t)peer * seq_local + s) * 3 + q) * hl + (h - peer * hl)) * vec_per_head + d] = in[i];
+    }
+}
+
+// in[peer][s][hl][d] -> out[s][peer * hl + hl'][d]
+__global__ void k_ulysses_unpack_attn(const uint4 *in, uint4 *out, size_t seq_local, unsigned heads,
+                                      unsigned vec_per_head, unsigned u) {
+    const unsigned hl = heads / u;
+    const size_t n = (size_t)u * seq_local * hl * vec_per_head;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
+        const unsigned d = (unsigned)(i % vec_per_head);
+        size_t t = i / vec_per_head;
+        const unsigned h = (unsigned)(t % hl);
+        t /= hl;
+        const size_t s = t % seq_local;
+        const unsigned peer = (unsigned)(t / seq_local);
+        out[(s * heads + peer * hl + h) * vec_per_head + d] = in[i];
+    }
+}
+
+static unsigned copy_grid(size_t n) {
+    size_t g = (n + 255) / 256;
+    return (unsigned)(g < 1 ? 1 : (g > 148 * 16 ? 148 * 16 : g));
+}
+
+static int ensure_scratch(CommState *st, int slot, size_t bytes, char *err, size_t err_size) {
+    if (st->scratch_bytes[slot] >= bytes) return 1;
+    if (st->scratch[slot]) {
+        cudaStreamSynchronize(st->stream[slot]);
+        cudaFree(st->scratch[slot]);
+        st->scratch[slot] = NULL;
+        st->scratch_bytes[slot] = 0;
+    }
+    cudaError_t e = cudaMalloc(&st->scratch[slot], bytes);
+    if (e != cudaSuccess) return cuda_fail(e, "ulysses a2a: scratch allocation", err, err_size);
+    st->scratch_bytes[slot] = bytes;
+    return 1;
+}
+
+static int finish_init(h3_ulysses_cfg *cfg, CommState *st, char *err, size_t err_size) {
+    for (int i = 0; i < st->n_local; i++) {
+        if (cudaSetDevice(st->device[i]) != cudaSuccess ||
+            cudaStreamCreateWithFlags(&st->stream[i], cudaStreamNonBlocking) != cudaSuccess ||
+            cudaEventCreateWithFlags(&st->ev_compute[i], cudaEventDisableTiming) != cudaSuccess ||
+            cudaEventCreateWithFlags(&st->ev_comm[i], cudaEventDisableTiming) != cudaSuccess)
+            return fail(err, err_size, "ulysses comm: stream/event creation failed on device %d", st->device[i]);
+    }
+    cfg->comm = st;
+    return 1;
+}
+
+// order: compute stream -> comm stream
+static int wait_compute(CommState *st, int i, char *err, size_t err_size) {
+    cudaError_t e = cudaEventRecord(st->ev_compute[i], st->compute[i]);
+    if (e == cudaSuccess) e = cudaStreamWaitEvent(st->stream[i], st->ev_compute[i], 0);
+    if (e != cudaSuccess) return cuda_fail(e, "ulysses a2a: wait compute", err, err_size);
+    return 1;
+}
+// order: comm stream -> compute stream
+static int publish_comm(CommState *st, int i, char *err, size_t err_size) {
+    cudaError_t e = cudaEventRecord(st->ev_comm[i], st->stream[i]);
+    if (e == cudaSuccess) e = cudaStreamWaitEvent(st->compute[i], st->ev_comm[i], 0);
+    if (e != cudaSuccess) return cuda_fail(e, "ulysses a2a: publish", err, err_size);
+    return 1;
+}
+
+// exchange: slot i sends send[i] + p*chunk to rank p and receives chunk p into recv[i] + p*chunk
+static int exchange(CommState *st, NcclApi *api, const char *const *send, char *const *recv, size_t chunk_bytes,
+                    char *err, size_t err_size) {
+    ncclResult_t rc = api->GroupStart();
+    if (rc != ncclSuccess) return fail(err, err_size, "ncclGroupStart: %s", api->GetErrorString ? api->GetErrorString(rc) : "error");
+    for (int i = 0; i < st->n_local; i++)
+        for (int p = 0; p < st->n_ranks; p++) {
+            rc = api->Send(send[i] + (size_t)p * chunk_bytes, chunk_bytes, ncclInt8, p, st->comm[i], st->stream[i]);
+            if (rc == ncclSuccess)
+                rc = api->Recv(recv[i] + (size_t)p * chunk_bytes, chunk_bytes, ncclInt8, p, st->comm[i], st->stream[i]);
+            if (rc != ncclSuccess) {
+                api->GroupEnd();
+                return fail(err, err_size, "nccl send/recv a2a failed: %s", api->GetErrorString ? api->GetErrorString(rc) : "error");
+            }
+        }
+    rc = api->GroupEnd();
+    if (rc != ncclSuccess) return fail(err, err_size, "ncclGroupEnd: %s", api->GetErrorString ? api->GetErrorString(rc) : "error");
+    return 1;
+}
+
+static int check_geometry(const CommState *st, size_t seq_local, size_t heads, size_t head_dim, int dtype_bytes,
+                          char *err, size_t err_size) {
+    if (!seq_local || !heads || !head_dim) return fail(err, err_size, "ulysses a2a: zero dimension");
+    if (dtype_bytes != 2 && dtype_bytes != 4) return fail(err, err_size, "ulysses a2a: dtype_bytes must be 2 or 4");
+    if (heads % (size_t)st->n_ranks) return fail(err, err_size, "ulysses a2a: heads %% U != 0");
+    if ((head_dim * (size_t)dtype_bytes) % 16) return fail(err, err_size, "ulysses a2a: head_dim * dtype_bytes must be a multiple of 16");
+    return 1;
+}
+
+}  // namespace h3b
+
+using namespace h3b;
+
+extern "C" {
+
+int h3b_ulysses_unique_id(void *out128, char *err, size_t err_size) {
+    NcclApi *api = nccl_api(err, err_size);
+    if (!api) return 0;
+    if (!out128) return fail(err, err_size, "ulysses unique id: NULL buffer");
+    ncclUniqueId id;
+    ncclResult_t rc = api->GetUniqueId(&id);
+    if (rc != ncclSuccess) return fail(err, err_size, "ncclGetUniqueId failed");
+    memcpy(out128, &id, sizeof(id));
+    return 1;
+}
+
+int h3b_ulysses_comm_init_rank(h3_ulysses_cfg *cfg, int rank, int world_size, const void *unique_id128, int device,
+                               char *err, size_t err_size) {
+    if (!cfg || !unique_id128) return fail(err, err_size, "ulysses init: invalid arguments");
+    if (world_size != 1 && world_size != 2 && world_size != 4 && world_size != 8)
+        return fail(err, err_size, "ulysses=%d illegal (legal {1,2,4,8}; packed align)", world_size);
+    if (rank < 0 || rank >= world_size) return fail(err, err_size, "ulysses init: rank %d out of range", rank);
+    cfg->comm = NULL;
+    cfg->ulysses = world_size; cfg->world_size = world_size; cfg->rank = rank;
+    if (!cfg->tp_size) cfg->tp_size = 1;
+    if (!cfg->ring) cfg->ring = 1;
+    if (world_size == 1) return 1;   // U = 1: no communicator, a2a calls are refused like the reference
+    NcclApi *api = nccl_api(err, err_size);
+    if (!api) return 0;
+    CommState *st = (CommState *)calloc(1, sizeof(CommState));
+    if (!st) return fail(err, err_size, "ulysses init: out of memory");
+    st->n_ranks = world_size; st->n_local = 1; st->local_rank[0] = rank; st->device[0] = device;
+    if (cudaSetDevice(device) != cudaSuccess) {
+        free(st);
+        return fail(err, err_size, "ulysses init: cudaSetDevice(%d) failed", device);
+    }
+    ncclUniqueId id;
+    memcpy(&id, unique_id128, sizeof(id));
+    ncclResult_t rc = api->CommInitRank(&st->comm[0], world_size, id, rank);
+    if (rc != ncclSuccess) {
+        free(st);
+        return fail(err, err_size, "ncclCommInitRank failed: %s", api->GetErrorString ? api->GetErrorString(rc) : "error");
+    }
+    if (!finish_init(cfg, st, err, err_size)) {
+        api->CommDestroy(st->comm[0]);
+        free(st);
+        cfg->comm = NULL;
+        return 0;
+    }
+    return 1;
+}
+
+int h3_ulysses_comm_init(h3_ulysses_cfg *cfg, const int *device_ids, int n_dev, char *err, size_t err_size) {
+    if (!cfg) return fail(err, err_size, "ulysses init: NULL cfg");
+    cfg->comm = NULL;
+    if (n_dev <= 1) return 1;   // U = 1 needs no communicator (h3_ulysses_comm_stub.c:16)
+    if (!device_ids) return fail(err, err_size, "ulysses init: NULL device list");
+    if (n_dev != 2 && n_dev != 4 && n_dev != 8) return fail(err, err_size, "ulysses=%d illegal (legal {1,2,4,8}; packed align)", n_dev);
+    NcclApi *api = nccl_api(err, err_size);
+    if (!api) return 0;
+    CommState *st = (CommState *)calloc(1, sizeof(CommState));
+    if (!st) return fail(err, err_size, "ulysses init: out of memory");
+    st->n_ranks = n_dev; st->n_local = n_dev;
+    for (int i = 0; i < n_dev; i++) {
+        st->local_rank[i] = i;
+        st->device[i] = device_ids[i];
+    }
+    ncclResult_t rc = api->CommInitAll(st->comm, n_dev, device_ids);
+    if (rc != ncclSuccess) {
+        free(st);
+        return fail(err, err_size, "ncclCommInitAll failed: %s", api->GetErrorString ? api->GetErrorString(rc) : "error");
+    }
+    if (!finish_init(cfg, st, err, err_size)) {
+        for (int i = 0; i < n_dev; i++) api->CommDestroy(st->comm[i]);
+        free(st);
+        cfg->comm = NULL;
+        return 0;
+    }
+    cfg->ulysses = n_dev; cfg->world_size = n_dev;
+    return 1;
+}
+
+void h3_ulysses_comm_destroy(h3_ulysses_cfg *cfg) {
+    if (!cfg || !cfg->comm) return;
+    CommState *st = (CommState *)cfg->comm;
+    NcclApi *api = nccl_api(NULL, 0);
+    for (int i = 0; i < st->n_local; i++) {
+        cudaSetDevice(st->device[i]);
+        if (st->stream[i]) cudaStreamSynchronize(st->stream[i]);
+        if (api && st->comm[i]) api->CommDestroy(st->comm[i]);
+        if (st->scratch[i]) cudaFree(st->scratch[i]);
+        if (st->ev_compute[i]) cudaEventDestroy(st->ev_compute[i]);
+        if (st->ev_comm[i]) cudaEventDestroy(st->ev_comm[i]);
+        if (st->stream[i]) cudaStreamDestroy(st->stream[i]);
+    }
+    free(st);
+    cfg->comm = NULL;
+}
+
+int h3_ulysses_comm_bind(h3_ulysses_cfg *cfg, int rank, const void *d_in, void *d_out, char *err, size_t err_size) {
+    if (!cfg || !cfg->comm) return fail(err, err_size, "ulysses bind: not inited");
+    CommState *st = (CommState *)cfg->comm;
+    int i = slot_of(st, rank);
+    if (i < 0) return fail(err, err_size, "ulysses bind: bad rank");
+    st->bound_in[i] = d_in;
+    st->bound_out[i] = d_out;
+    return 1;
+}
+
+int h3_ulysses_comm_set_compute(h3_ulysses_cfg *cfg, int rank, void *stream, char *err, size_t err_size) {
+    if (!cfg || !cfg->comm) return fail(err, err_size, "ulysses set_compute: not inited");
+    CommState *st = (CommState *)cfg->comm;
+    int i = slot_of(st, rank);
+    if (i < 0) return fail(err, err_size, "ulysses set_compute: bad rank");
+    st->compute[i] = (cudaStream_t)stream;
+    return 1;
+}
+
+// d_in / d_out: with one owned rank they may be passed directly; NULL (or several owned ranks)
+// selects the buffers bound per rank.  In and out may alias.
+int h3_ulysses_a2a_qkv(h3_ulysses_cfg *cfg, const void *d_in, void *d_out, size_t seq_local, size_t heads,
+                       size_t head_dim, int dtype_bytes, char *err, size_t err_size) {
+    if (!cfg || !cfg->comm) return fail(err, err_size, "ulysses a2a_qkv: not inited");
+    CommState *st = (CommState *)cfg->comm;
+    NcclApi *api = nccl_api(err, err_size);
+    if (!api) return 0;
+    if (!check_geometry(st, seq_local, heads, head_dim, dtype_bytes, err, err_size)) return 0;
+    const size_t total = seq_local * 3 * heads * head_dim * (size_t)dtype_bytes;
+    const size_t chunk = total / (size_t)st->n_ranks;
+    const unsigned vec = (unsigned)(head_dim * (size_t)dtype_bytes / 16);
+    const char *send[MAX_U];
+    char *recv[MAX_U];
+    for (int i = 0; i < st->n_local; i++) {
+        const void *in = (st->n_local == 1 && d_in) ? d_in : st->bound_in[i];
+        void *out = (st->n_local == 1 && d_out) ? d_out : st->bound_out[i];
+        if (!in || !out) return fail(err, err_size, "ulysses a2a_qkv: rank %d has no buffers", st->local_rank[i]);
+        if (cudaSetDevice(st->device[i]) != cudaSuccess) return fail(err, err_size, "ulysses a2a: set device");
+        if (!ensure_scratch(st, i, total, err, err_size) || !wait_compute(st, i, err, err_size)) return 0;
+        k_ulysses_pack_qkv<<<copy_grid(total / 16), 256, 0, st->stream[i]>>>((const uint4 *)in, (uint4 *)st->scratch[i],
+                                                                            seq_local, (unsigned)heads, vec,
+                                                                            (unsigned)st->n_ranks);
+        if (cudaGetLastError() != cudaSuccess) return fail(err, err_size, "ulysses a2a_qkv: pack launch failed");
+        send[i] = (const char *)st->scratch[i];
+        recv[i] = (char *)out;
+    }
+    if (!exchange(st, api, send, recv, chunk, err, err_size)) return 0;
+    for (int i = 0; i < st->n_local; i++) {
+        if (cudaSetDevice(st->device[i]) != cudaSuccess) return fail(err, err_size, "ulysses a2a: set device");
+        if (!publish_comm(st, i, err, err_size)) return 0;
+    }
+    return 1;
+}
+
+int h3_ulysses_a2a_attn_out(h3_ulysses_cfg *cfg, const void *d_in, void *d_out, size_t seq_local, size_t heads,
+                            size_t head_dim, int dtype_bytes, char *err, size_t err_size) {
+    if (!cfg || !cfg->comm) return fail(err, err_size, "ulysses a2a_attn_out: not inited");
+    CommState *st = (CommState *)cfg->comm;
+    NcclApi *api = nccl_api(err, err_size);
+    if (!api) return 0;
+    if (!check_geometry(st, seq_local, heads, head_dim, dtype_bytes, err, err_size)) return 0;
+    const size_t total = seq_local * heads * head_dim * (size_t)dtype_bytes;
+    const size_t chunk = total / (size_t)st->n_ranks;
+    const unsigned vec = (unsigned)(head_dim * (size_t)dtype_bytes / 16);
+    const char *send[MAX_U];
+    char *recv[MAX_U];
+    void *outs[MAX_U];
+    for (int i = 0; i < st->n_local; i++) {
+        const void *in = (st->n_local == 1 && d_in) ? d_in : st->bound_in[i];
+        outs[i] = (st->n_local == 1 && d_out) ? d_out : st->bound_out[i];
+        if (!in || !outs[i]) return fail(err, err_size, "ulysses a2a_attn_out: rank %d has no buffers", st->local_rank[i]);
+        if (cudaSetDevice(st->device[i]) != cudaSuccess) return fail(err, err_size, "ulysses a2a: set device");
+        if (!ensure_scratch(st, i, total, err, err_size) || !wait_compute(st, i, err, err_size)) return 0;
+        send[i] = (const char *)in;
+        recv[i] = (char *)st->scratch[i];
+    }
+    if (!exchange(st, api, send, recv, chunk, err, err_size)) return 0;
+    for (int i = 0; i < st->n_local; i++) {
+        if (cudaSetDevice(st->device[i]) != cudaSuccess) return fail(err, err_size, "ulysses a2a: set device");
+        k_ulysses_unpack_attn<<<copy_grid(total / 16), 256, 0, st->stream[i]>>>((const uint4 *)st->scratch[i],
+                                                                               (uint4 *)outs[i], seq_local,
+                                                                               (unsigned)heads, vec,
+                                                                               (unsigned)st->n_ranks);
+        if (cudaGetLastError() != cudaSuccess) return fail(err, err_size, "ulysses a2a_attn_out: unpack launch failed");
+        if (!publish_comm(st, i, err, err_size)) return 0;
+    }
+    return 1;
+}
+
+}  // extern "C"

@@ -110,6 +110,30 @@ class Dit:
              ptr(sin), ptr(text), 0 if text is None else text.shape[0], ptr(out))
         return out
 
+    def set_ulysses(self, comm):
+        """Attaches a per-rank `UlyssesComm` (None detaches)."""
+        call("h3b_dit_set_ulysses", self.h, C.byref(comm.cfg) if comm is not None else None)
+        self._uly = comm
+
+    def layers_forward_ulysses(self, x_local, seq_real, cos_full, sin_full, *, first=0, n=None, row_map=None, text=None,
+                               out=None):
+        import torch
+        n = self.geo.n_blocks - first if n is None else n
+        out = torch.empty_like(x_local) if out is None else out
+        call("h3b_dit_layers_forward_ulysses_dev", self.h, first, n, ptr(x_local), x_local.shape[0], seq_real,
+             ptr(row_map), ptr(cos_full), ptr(sin_full), ptr(text), 0 if text is None else text.shape[0], ptr(out))
+        return out
+
+    def layers_forward_ulysses_f32(self, t_feat, x_local, seq_real, cos_full, sin_full, *, first=0, n=None, row_map=None,
+                                   text=None, out=None):
+        n = self.geo.n_blocks - first if n is None else n
+        if out is None:
+            out = np.empty((x_local.shape[0], x_local.shape[1]), np.float32)
+        call("h3b_dit_layers_forward_ulysses_f32", self.h, first, n, ptr(t_feat), ptr(x_local), x_local.shape[0],
+             seq_real, ptr(row_map), ptr(cos_full), ptr(sin_full), ptr(text), 0 if text is None else text.shape[0],
+             ptr(out))
+        return out
+
     @property
     def launches_per_block(self):
         return int(load().h3b_dit_launches_per_block(self.h))

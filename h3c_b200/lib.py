@@ -164,6 +164,17 @@ _SIGS = {
     "h3b_dit_layers_forward_dev": (i32, (vp, C.c_uint, C.c_uint, vp, sz, vp, vp, vp, vp, sz, vp) + _ERR),
     "h3b_dit_layers_forward_f32": (i32, (vp, C.c_uint, C.c_uint, vp, vp, sz, vp, vp, vp, vp, sz, vp) + _ERR),
     "h3b_dit_launches_per_block": (i32, (vp,)),
+    "h3_ulysses_comm_init": (i32, (C.POINTER(UlyssesCfg), C.POINTER(i32), i32) + _ERR),
+    "h3_ulysses_comm_destroy": (None, (C.POINTER(UlyssesCfg),)),
+    "h3_ulysses_comm_bind": (i32, (C.POINTER(UlyssesCfg), i32, vp, vp) + _ERR),
+    "h3_ulysses_comm_set_compute": (i32, (C.POINTER(UlyssesCfg), i32, vp) + _ERR),
+    "h3_ulysses_a2a_qkv": (i32, (C.POINTER(UlyssesCfg), vp, vp, sz, sz, sz, i32) + _ERR),
+    "h3_ulysses_a2a_attn_out": (i32, (C.POINTER(UlyssesCfg), vp, vp, sz, sz, sz, i32) + _ERR),
+    "h3b_ulysses_unique_id": (i32, (vp,) + _ERR),
+    "h3b_ulysses_comm_init_rank": (i32, (C.POINTER(UlyssesCfg), i32, i32, vp, i32) + _ERR),
+    "h3b_dit_set_ulysses": (i32, (vp, C.POINTER(UlyssesCfg)) + _ERR),
+    "h3b_dit_layers_forward_ulysses_dev": (i32, (vp, C.c_uint, C.c_uint, vp, sz, sz, vp, vp, vp, vp, sz, vp) + _ERR),
+    "h3b_dit_layers_forward_ulysses_f32": (i32, (vp, C.c_uint, C.c_uint, vp, vp, sz, sz, vp, vp, vp, vp, sz, vp) + _ERR),
     "h3_ulysses_validate": (i32, (i32, i32, i32, i32, i32) + _ERR),
     "h3_ulysses_pad_seq": (sz, (sz, i32)),
     "h3_ulysses_local_rows": (sz, (sz, i32, i32)),

@@ -459,6 +459,49 @@ int h3_ulysses_validate(int heads, int packed_align, int tp, int ulysses, int ri
 size_t h3_ulysses_pad_seq(size_t seq, int align);                                   /* :23 */
 size_t h3_ulysses_local_rows(size_t seq_pad, int ulysses, int rank);                /* :24 */
 
+/* Communication (h3_ulysses_comm.h:13-33), same six calls.  dtype_bytes 2 or 4; buffers are device
+ * pointers; d_in [seq_local, 3*heads*head_dim] -> d_out [seq_pad, 3*(heads/U)*head_dim] for QKV and
+ * d_in [seq_pad, (heads/U)*head_dim] -> d_out [seq_local, heads*head_dim] for the attention output;
+ * in and out may alias.  The exchange runs on the communicator's own stream, ordered after the rank's
+ * compute stream (h3_ulysses_comm_set_compute) and before its later work; nothing blocks the host. */
+int h3_ulysses_comm_init(h3_ulysses_cfg *cfg, const int *device_ids, int n_dev, char *err,
+                         size_t err_size);                                          /* h3_ulysses_comm.h:13 */
+void h3_ulysses_comm_destroy(h3_ulysses_cfg *cfg);                                  /* :15 */
+int h3_ulysses_comm_bind(h3_ulysses_cfg *cfg, int rank, const void *d_in, void *d_out, char *err,
+                         size_t err_size);                                          /* :18 */
+int h3_ulysses_comm_set_compute(h3_ulysses_cfg *cfg, int rank, void *stream, char *err,
+                                size_t err_size);                                   /* :22 */
+int h3_ulysses_a2a_qkv(h3_ulysses_cfg *cfg, const void *d_in, void *d_out, size_t seq_local,
+                       size_t heads, size_t head_dim, int dtype_bytes, char *err,
+                       size_t err_size);                                            /* :26 */
+int h3_ulysses_a2a_attn_out(h3_ulysses_cfg *cfg, const void *d_in, void *d_out, size_t seq_local,
+                            size_t heads, size_t head_dim, int dtype_bytes, char *err,
+                            size_t err_size);                                       /* :31 */
+/* Additions for one process per GPU: rank 0 makes a 128-byte id, the caller distributes it (any
+ * transport), every rank joins with it.  With world_size 1 no communicator is made. */
+int h3b_ulysses_unique_id(void *out128, char *err, size_t err_size);
+int h3b_ulysses_comm_init_rank(h3_ulysses_cfg *cfg, int rank, int world_size, const void *unique_id128,
+                               int device, char *err, size_t err_size);
+/* Host f32 rows of this rank in and out (see h3b_dit_layers_forward_f32); rope tables cover all
+ * U*seq_local rows. */
+int h3b_dit_layers_forward_ulysses_f32(h3b_dit *dit, unsigned first_block, unsigned n_blocks,
+                                       const float *t_feat, const float *x_local, size_t seq_local,
+                                       size_t seq_real, const uint32_t *row_map,
+                                       const float *rope_cos_full, const float *rope_sin_full,
+                                       const float *text, size_t text_seq, float *y_local, char *error,
+                                       size_t error_size);
+/* Attaches an initialised per-rank communicator to a block context (the reference's
+ * h3_dit_w4a8_set_ulysses, h3_dit_w4a8.h:305, for one rank).  NULL detaches. */
+int h3b_dit_set_ulysses(h3b_dit *dit, h3_ulysses_cfg *cfg, char *error, size_t error_size);
+/* Sequence-parallel chain on this rank's rows (h3_dit_w4a8.c:6261 layers_forward_ulysses, one rank):
+ * d_x / d_y [seq_local, dim]; rope tables for ALL seq_pad = U*seq_local rows; only the first
+ * seq_real rows of the gathered sequence enter attention, pad rows of its output are zero. */
+int h3b_dit_layers_forward_ulysses_dev(h3b_dit *dit, unsigned first_block, unsigned n_blocks,
+                                       const void *d_x, size_t seq_local, size_t seq_real,
+                                       const uint32_t *d_row_map, const float *d_rope_cos_full,
+                                       const float *d_rope_sin_full, const void *d_text,
+                                       size_t text_seq, void *d_y, char *error, size_t error_size);
+
 #ifdef __cplusplus
 }
 #endif
