@@ -4,14 +4,19 @@
 // reference's h3_dit_w4a8_sdpa_f32 (h3_dit_w4a8.c:3073-3116) evaluated tile by tile
 // with a running maximum.
 //
-// One CTA per (128-query tile, head):
-//   warp 0     TMA: Q once, then K and V tiles of 128 keys into two-deep rings
-//   warp 1     MMA: S = Q K^T (128x128x128) into one of two TMEM score buffers,
-//              issued one tile ahead; O += P V (128x128x128) into a TMEM accumulator
-//   warps 2-5  softmax: one query row per thread.  Pass 1 reads the scores from TMEM
-//              for the row maximum, pass 2 re-reads them, exponentiates and writes P
-//              (bf16) to shared memory in the MMA's swizzled layout.  The accumulator
-//              is rescaled only when the running maximum grew by more than 2^8.
+// One CTA per (256 queries = two 128-row tiles A and B, head); 320 threads:
+//   warp 0      TMA: both Q tiles once, then K and V tiles of 128 keys, two-deep rings
+//   warp 1      MMA issuer.  Per key tile and per query tile: S = Q K^T (128x128x128) into the
+//               tile's TMEM score buffer, then O += P V (128x128x128) with P read from TMEM.
+//               The two query tiles are interleaved so that the tensor core works on one
+//               while the other is in its softmax.
+//   warps 2-5   softmax of tile A, warps 6-9 softmax of tile B: one query row per thread.
+//               Pass 1 reads the scores from TMEM for the row maximum, pass 2 re-reads them,
+//               exponentiates and writes P (bf16 pairs) back to TMEM over the scores just
+//               consumed.  The accumulator is rescaled only when the running maximum grew
+//               by more than 2^8; the final division by the row sum undoes the stale scale.
+// TMEM (512 columns): S_A 0..127, S_B 128..255 (P overlays the first 64 columns of each),
+// O_A 256..383, O_B 384..511.
 #include <cuda_bf16.h>
 
 #include "h3b_internal.h"
@@ -23,10 +28,10 @@ namespace attn {
 constexpr int BQ = 128, BKV = 128, HD = 128;
 constexpr int SLAB = BQ * 64 * 2;        // 128 rows x 64 bf16: one 128-byte-swizzled slab (16 KiB)
 constexpr int TILE = 2 * SLAB;           // 128 x 128 bf16 tile (32 KiB)
-constexpr int THREADS = 192;
+constexpr int THREADS = 320;
 constexpr int TMEM_COLS = 512;
-constexpr uint32_t S_COL0 = 0, S_COL1 = 128, O_COL = 256;
-// shared memory: Q | K0 K1 | V0 V1 | P | barriers
+constexpr uint32_t S_COL = 0, O_COL = 256;   // + 128 * tile
+// shared memory: Q_A Q_B | K0 K1 | V0 V1 | barriers
 constexpr size_t SMEM_BYTES = 1024 + 6 * (size_t)TILE + 256;
 }  // namespace attn
 
@@ -49,16 +54,18 @@ __global__ void __launch_bounds__(attn::THREADS, 1) k_attn_bf16(const __grid_con
     using namespace attn;
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
-    uint8_t *sQ = smem, *sK = smem + TILE, *sV = smem + 3 * TILE, *sP = smem + 5 * TILE;
+    uint8_t *sQ = smem, *sK = smem + 2 * TILE, *sV = smem + 4 * TILE;
     uint64_t *bars = reinterpret_cast<uint64_t *>(smem + 6 * TILE);
     uint64_t *q_full = bars, *k_full = bars + 1, *v_full = bars + 3, *k_empty = bars + 5, *v_empty = bars + 7,
-             *s_full = bars + 9, *s_empty = bars + 11, *p_full = bars + 13, *pv_done = bars + 14;
-    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 15);
+             *s_full = bars + 9, *p_full = bars + 11, *o_done = bars + 13;
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 14);
     volatile int *abort_word = reinterpret_cast<volatile int *>(tmem_slot + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int q0 = blockIdx.x * BQ, head = blockIdx.y;
+    const int q0 = blockIdx.x * (2 * BQ), head = blockIdx.y;
     const int n_kv = (p.lk + BKV - 1) / BKV;
+    // the second query tile may lie entirely beyond lq: it is then skipped by every role
+    const int n_tiles = (q0 + BQ < p.lq) ? 2 : 1;
 
     if (threadIdx.x == 0) {
         mbar_init(q_full, 1);
@@ -68,10 +75,9 @@ __global__ void __launch_bounds__(attn::THREADS, 1) k_attn_bf16(const __grid_con
             mbar_init(&k_empty[i], 1);
             mbar_init(&v_empty[i], 1);
             mbar_init(&s_full[i], 1);
-            mbar_init(&s_empty[i], 4);
+            mbar_init(&p_full[i], 4);
         }
-        mbar_init(p_full, 4);
-        mbar_init(pv_done, 1);
+        mbar_init(o_done, 1);
         *abort_word = 0;
         mbar_fence_init();
         tma_prefetch_desc(&p.tmap_q);
@@ -89,9 +95,11 @@ __global__ void __launch_bounds__(attn::THREADS, 1) k_attn_bf16(const __grid_con
 
     if (warp == 0) {
         if (lane == 0) {
-            mbar_expect_tx(q_full, TILE);
-            tma_load_3d(sQ, &p.tmap_q, q_full, 0, head, q0);
-            tma_load_3d(sQ + SLAB, &p.tmap_q, q_full, 64, head, q0);
+            mbar_expect_tx(q_full, n_tiles * TILE);
+            for (int t = 0; t < n_tiles; t++) {
+                tma_load_3d(sQ + t * TILE, &p.tmap_q, q_full, 0, head, q0 + t * BQ);
+                tma_load_3d(sQ + t * TILE + SLAB, &p.tmap_q, q_full, 64, head, q0 + t * BQ);
+            }
             for (int j = 0; j < n_kv; j++) {
                 const int st = j & 1;
                 const uint32_t ph = ((j >> 1) & 1) ^ 1;
@@ -108,62 +116,71 @@ __global__ void __launch_bounds__(attn::THREADS, 1) k_attn_bf16(const __grid_con
         __syncwarp();
     } else if (warp == 1) {
         if (lane == 0) {
-            // S = Q K^T : both operands K-major (d contiguous).  O += P V : P K-major (keys contiguous),
-            // V as stored ([key][d], d contiguous) is the N-major form of the B operand.
+            // S = Q K^T : both operands K-major in shared memory (d contiguous).
+            // O += P V  : P from TMEM (row = lane, two bf16 keys per 32-bit column); V as stored
+            //             ([key][d], d contiguous) is the N-major form of the B operand.
             constexpr uint32_t idesc_s = umma_idesc(1, 1, 1, BQ, BKV, 0, 0);
             constexpr uint32_t idesc_o = umma_idesc(1, 1, 1, BQ, HD, 0, 1);
-            const uint32_t q_addr = smem_u32(sQ), p_addr = smem_u32(sP);
-            auto issue_s = [&](int j) -> bool {
-                const int st = j & 1;
-                if (!mbar_wait(&k_full[st], (j >> 1) & 1, abort_word, p.status, H3B_ST_TIMEOUT_FULL)) return false;
-                if (!mbar_wait(&s_empty[st], ((j >> 1) & 1) ^ 1, abort_word, p.status, H3B_ST_TIMEOUT_TMEM_EMPTY))
-                    return false;
-                tc_fence_after();
-                const uint32_t k_addr = smem_u32(sK + st * TILE);
-                const uint32_t d_tmem = tmem_base + (st ? S_COL1 : S_COL0);
+            auto issue_s = [&](int t, int j) {
+                const uint32_t q_addr = smem_u32(sQ + t * TILE), k_addr = smem_u32(sK + (j & 1) * TILE);
+                const uint32_t d_tmem = tmem_base + S_COL + 128u * t;
 #pragma unroll
                 for (int k = 0; k < HD / 16; k++) {
                     const uint32_t off = (uint32_t)(k >> 2) * SLAB + (uint32_t)(k & 3) * 32;
                     umma_f16_ss(d_tmem, umma_desc_k_sw128(q_addr + off), umma_desc_k_sw128(k_addr + off), idesc_s,
                                 (uint32_t)(k != 0));
                 }
-                tc_commit(&s_full[st]);
-                tc_commit(&k_empty[st]);
-                return true;
+                tc_commit(&s_full[t]);
             };
-            bool ok = mbar_wait(q_full, 0, abort_word, p.status, H3B_ST_TIMEOUT_FULL);
-            if (ok) ok = issue_s(0);
-            for (int j = 0; ok && j < n_kv; j++) {
-                if (j + 1 < n_kv && !issue_s(j + 1)) break;
-                const int st = j & 1;
-                if (!mbar_wait(p_full, j & 1, abort_word, p.status, H3B_ST_TIMEOUT_OTHER)) break;
-                if (!mbar_wait(&v_full[st], (j >> 1) & 1, abort_word, p.status, H3B_ST_TIMEOUT_FULL)) break;
-                tc_fence_after();
-                const uint32_t v_addr = smem_u32(sV + st * TILE);
+            auto issue_pv = [&](int t, int j) {
+                const uint32_t v_addr = smem_u32(sV + (j & 1) * TILE);
 #pragma unroll
-                for (int k = 0; k < BKV / 16; k++) {
-                    const uint32_t a_off = (uint32_t)(k >> 2) * SLAB + (uint32_t)(k & 3) * 32;
-                    umma_f16_ss(tmem_base + O_COL, umma_desc_k_sw128(p_addr + a_off),
+                for (int k = 0; k < BKV / 16; k++)
+                    umma_f16_ts(tmem_base + O_COL + 128u * t, tmem_base + S_COL + 128u * t + (uint32_t)k * 8,
                                 umma_desc_mn_sw128(v_addr + (uint32_t)k * 2048, SLAB, 1024), idesc_o,
                                 (uint32_t)((j | k) != 0));
-                }
-                tc_commit(&v_empty[st]);
-                tc_commit(pv_done);
+            };
+            bool ok = mbar_wait(q_full, 0, abort_word, p.status, H3B_ST_TIMEOUT_FULL) &&
+                      mbar_wait(&k_full[0], 0, abort_word, p.status, H3B_ST_TIMEOUT_FULL);
+            if (ok) {
+                tc_fence_after();
+                for (int t = 0; t < n_tiles; t++) issue_s(t, 0);
+                tc_commit(&k_empty[0]);
             }
+            for (int j = 0; ok && j < n_kv; j++) {
+                const int st = j & 1, nx = (j + 1) & 1;
+                const bool more = j + 1 < n_kv;
+                if (!mbar_wait(&v_full[st], (j >> 1) & 1, abort_word, p.status, H3B_ST_TIMEOUT_FULL)) break;
+                if (more && !mbar_wait(&k_full[nx], ((j + 1) >> 1) & 1, abort_word, p.status, H3B_ST_TIMEOUT_FULL)) break;
+                for (int t = 0; t < n_tiles && ok; t++) {
+                    // P of this tile is in TMEM (and its scores are fully consumed)
+                    ok = mbar_wait(&p_full[t], j & 1, abort_word, p.status, H3B_ST_TIMEOUT_OTHER);
+                    if (!ok) break;
+                    tc_fence_after();
+                    issue_pv(t, j);
+                    if (t == n_tiles - 1) tc_commit(&v_empty[st]);
+                    if (more) {
+                        issue_s(t, j + 1);   // overwrites the tile's scores / P, in order after the P V product
+                        if (t == n_tiles - 1) tc_commit(&k_empty[nx]);
+                    }
+                }
+            }
+            tc_commit(o_done);
         }
         __syncwarp();
     } else {
         // ------------------------------------------------------------ softmax
-        const int q = warp & 3;
+        const int t = (warp - 2) >> 2;                     // query tile of this warp group
+        const int q = warp & 3;                            // TMEM lane quarter of this warp
         const int r = q * 32 + lane;                       // query row inside the tile
         const uint32_t lane_base = (uint32_t)(q * 32) << 16;
+        const uint32_t s_addr = tmem_base + lane_base + S_COL + 128u * t;
+        const uint32_t o_addr = tmem_base + lane_base + O_COL + 128u * t;
         float m_run = -INFINITY, l_run = 0.0f;
-        bool ok = true;
+        bool ok = t < n_tiles;
         for (int j = 0; j < n_kv && ok; j++) {
-            const int st = j & 1;
-            const uint32_t s_addr = tmem_base + lane_base + (st ? S_COL1 : S_COL0);
             const int valid = min(BKV, p.lk - j * BKV);    // keys of this tile that exist
-            ok = mbar_wait(&s_full[st], (j >> 1) & 1, abort_word, p.status, H3B_ST_TIMEOUT_TMEM_FULL);
+            ok = mbar_wait(&s_full[t], j & 1, abort_word, p.status, H3B_ST_TIMEOUT_TMEM_FULL);
             if (!ok) break;
             tc_fence_after();
             // pass 1: row maximum
@@ -173,37 +190,39 @@ __global__ void __launch_bounds__(attn::THREADS, 1) k_attn_bf16(const __grid_con
                 uint32_t v[32];
                 tmem_ld_32x32b_x32(s_addr + ch * 32, v);
                 tmem_ld_wait();
+                if (valid == BKV) {
 #pragma unroll
-                for (int i = 0; i < 32; i++)
-                    if (ch * 32 + i < valid) mx = fmaxf(mx, __uint_as_float(v[i]));
+                    for (int i = 0; i < 32; i++) mx = fmaxf(mx, __uint_as_float(v[i]));
+                } else {
+#pragma unroll
+                    for (int i = 0; i < 32; i++)
+                        if (ch * 32 + i < valid) mx = fmaxf(mx, __uint_as_float(v[i]));
+                }
             }
             const float m_new = fmaxf(m_run, mx * p.scale_log2);
-            float alpha = 1.0f;
             const bool grow_me = (m_new - m_run) > 8.0f;   // also true on the first tile (m_run = -inf)
-            if (grow_me) {
-                alpha = ex2_approx(m_run - m_new);         // 0 on the first tile
-                m_run = m_new;
-                l_run *= alpha;
-            }
-            // P's buffer and the accumulator are free once the previous P V product has completed
-            if (j > 0) {
-                ok = mbar_wait(pv_done, (j - 1) & 1, abort_word, p.status, H3B_ST_TIMEOUT_OTHER);
-                if (!ok) break;
-                tc_fence_after();
-                if (__any_sync(0xffffffffu, grow_me)) {
+            if (__any_sync(0xffffffffu, grow_me)) {
+                float alpha = 1.0f;
+                if (grow_me) {
+                    alpha = ex2_approx(m_run - m_new);     // 0 on the first tile
+                    m_run = m_new;
+                    l_run *= alpha;
+                }
+                // The score buffer of tile j became full only after the P V product of tile j-1 had
+                // completed (same issuing thread, in order), so the accumulator is at rest here.
+                if (j > 0) {
 #pragma unroll 1
                     for (int ch = 0; ch < HD / 16; ch++) {
                         uint32_t o[16];
-                        tmem_ld_32x32b_x16(tmem_base + lane_base + O_COL + ch * 16, o);
+                        tmem_ld_32x32b_x16(o_addr + ch * 16, o);
                         tmem_ld_wait();
 #pragma unroll
                         for (int i = 0; i < 16; i++) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
-                        tmem_st_32x32b_x16(tmem_base + lane_base + O_COL + ch * 16, o);
+                        tmem_st_32x32b_x16(o_addr + ch * 16, o);
                     }
-                    tmem_st_wait();
                 }
             }
-            // pass 2: probabilities -> bf16 -> shared memory (K-major, 128-byte swizzle, two 64-key slabs)
+            // pass 2: probabilities -> bf16 pairs -> TMEM, over the score columns already consumed
             float l_add = 0.0f;
 #pragma unroll 1
             for (int ch = 0; ch < BKV / 32; ch++) {
@@ -213,52 +232,47 @@ __global__ void __launch_bounds__(attn::THREADS, 1) k_attn_bf16(const __grid_con
                 uint32_t packed[16];
 #pragma unroll
                 for (int i = 0; i < 32; i += 2) {
-                    float p0 = (ch * 32 + i < valid) ? ex2_approx(fmaf(__uint_as_float(v[i]), p.scale_log2, -m_run)) : 0.0f;
-                    float p1 = (ch * 32 + i + 1 < valid) ? ex2_approx(fmaf(__uint_as_float(v[i + 1]), p.scale_log2, -m_run)) : 0.0f;
+                    float p0 = ex2_approx(fmaf(__uint_as_float(v[i]), p.scale_log2, -m_run));
+                    float p1 = ex2_approx(fmaf(__uint_as_float(v[i + 1]), p.scale_log2, -m_run));
+                    if (valid != BKV) {
+                        if (ch * 32 + i >= valid) p0 = 0.0f;
+                        if (ch * 32 + i + 1 >= valid) p1 = 0.0f;
+                    }
                     l_add += p0 + p1;
                     __nv_bfloat162 h = __floats2bfloat162_rn(p0, p1);
                     packed[i >> 1] = *reinterpret_cast<uint32_t *>(&h);
                 }
-                // 32 keys = four 16-byte chunks of this row
-                uint8_t *slab = sP + (ch >> 1) * SLAB + r * 128;
-#pragma unroll
-                for (int c = 0; c < 4; c++) {
-                    const int chunk = ((ch & 1) * 4 + c) ^ (r & 7);
-                    *reinterpret_cast<uint4 *>(slab + chunk * 16) =
-                        make_uint4(packed[4 * c], packed[4 * c + 1], packed[4 * c + 2], packed[4 * c + 3]);
-                }
+                tmem_st_32x32b_x16(s_addr + ch * 16, packed);
             }
             l_run += l_add;
-            // scores consumed: the buffer may be overwritten by the tile after next
+            tmem_st_wait();
             tc_fence_before();
-            fence_proxy_async_smem();
             __syncwarp();
-            if (lane == 0) {
-                mbar_arrive(&s_empty[st]);
-                mbar_arrive(p_full);
-            }
+            if (lane == 0) mbar_arrive(&p_full[t]);
         }
         // ---- final: O / l -> bf16 -> global
-        if (ok) ok = mbar_wait(pv_done, (n_kv - 1) & 1, abort_word, p.status, H3B_ST_TIMEOUT_OTHER);
-        tc_fence_after();
-        const int row = q0 + r;
-        const float inv_l = 1.0f / l_run;
-        __nv_bfloat16 *dst = p.out + (size_t)row * p.o_stride + (size_t)head * HD;
+        if (t < n_tiles) {
+            if (ok) ok = mbar_wait(o_done, 0, abort_word, p.status, H3B_ST_TIMEOUT_OTHER);
+            tc_fence_after();
+            const int row = q0 + t * BQ + r;
+            const float inv_l = 1.0f / l_run;
+            __nv_bfloat16 *dst = p.out + (size_t)row * p.o_stride + (size_t)head * HD;
 #pragma unroll 1
-        for (int ch = 0; ch < HD / 32; ch++) {
-            uint32_t o[32];
-            tmem_ld_32x32b_x32(tmem_base + lane_base + O_COL + ch * 32, o);
-            tmem_ld_wait();
-            if (ok && row < p.lq) {
+            for (int ch = 0; ch < HD / 32; ch++) {
+                uint32_t o[32];
+                tmem_ld_32x32b_x32(o_addr + ch * 32, o);
+                tmem_ld_wait();
+                if (ok && row < p.lq) {
 #pragma unroll
-                for (int i = 0; i < 32; i += 8) {
-                    uint4 raw;
-                    __nv_bfloat162 *h = reinterpret_cast<__nv_bfloat162 *>(&raw);
+                    for (int i = 0; i < 32; i += 8) {
+                        uint4 raw;
+                        __nv_bfloat162 *h = reinterpret_cast<__nv_bfloat162 *>(&raw);
 #pragma unroll
-                    for (int t = 0; t < 4; t++)
-                        h[t] = __floats2bfloat162_rn(__uint_as_float(o[i + 2 * t]) * inv_l,
-                                                     __uint_as_float(o[i + 2 * t + 1]) * inv_l);
-                    *reinterpret_cast<uint4 *>(dst + ch * 32 + i) = raw;
+                        for (int u = 0; u < 4; u++)
+                            h[u] = __floats2bfloat162_rn(__uint_as_float(o[i + 2 * u]) * inv_l,
+                                                         __uint_as_float(o[i + 2 * u + 1]) * inv_l);
+                        *reinterpret_cast<uint4 *>(dst + ch * 32 + i) = raw;
+                    }
                 }
             }
         }
@@ -303,7 +317,7 @@ int launch_sdpa_bf16(h3_cuda *cuda, const void *q, size_t qs, const void *k, siz
     p.status = cuda->d_status;
     H3B_CUDA_OK(cudaFuncSetAttribute(k_attn_bf16, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)attn::SMEM_BYTES),
                 "sdpa smem attribute");
-    dim3 grid((unsigned)ceil_div(lq, attn::BQ), (unsigned)heads);
+    dim3 grid((unsigned)ceil_div(lq, 2 * attn::BQ), (unsigned)heads);
     ProfScope prof(cuda, PROF_ATTN);
     k_attn_bf16<<<grid, attn::THREADS, attn::SMEM_BYTES, cuda->op_stream>>>(p);
     cuda->launches++;

@@ -277,6 +277,20 @@ def test_sdpa_bf16(cuda, oracle, lq, lk, heads):
     assert rel_l2(host(out), want) < 4e-3
 
 
+def test_sdpa_growing_row_maximum(cuda, oracle):
+    """Later key tiles carry much larger scores, so the running maximum jumps by more than the lazy-rescale
+    threshold several times and the accumulator rescale path runs."""
+    rng = np.random.default_rng(44)
+    lq, lk, heads, hd = 300, 1024, 2, 128
+    q = dev(rng.normal(0, 1, (lq, heads, hd)).astype(np.float32), torch.bfloat16)
+    kf = rng.normal(0, 1, (lk, heads, hd)).astype(np.float32) * np.linspace(0.05, 6.0, lk, dtype=np.float32)[:, None, None]
+    k = dev(kf, torch.bfloat16)
+    v = dev(rng.normal(0, 1, (lk, heads, hd)).astype(np.float32), torch.bfloat16)
+    out = cuda.sdpa_bf16(q, k, v)
+    cuda.check()
+    assert rel_l2(host(out), oracle.sdpa(host(q), host(k), host(v))) < 4e-3
+
+
 def test_sdpa_cross_strided(cuda, oracle):
     """Cross-attention: K and V are the two halves of one [T, 2*D] projection (row stride 2*D)."""
     rng = np.random.default_rng(45)
