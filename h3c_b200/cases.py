@@ -1,0 +1,95 @@
+"""Single-kernel cases on synthetic data: times one operator of the library with CUDA events and prints
+achieved TFLOP/s or GB/s.  Also the small, self-contained commands used for ncu captures.
+
+    python -m h3c_b200.cases gemm --m 6144 --n 9216 --k 3072 [--epi plain|gate|gelu|swiglu]
+    python -m h3c_b200.cases attn --lq 6144 --lk 6144 --heads 24
+    python -m h3c_b200.cases norm --m 6144 --k 3072 [--plain-quant]
+    python -m h3c_b200.cases rope --m 6144 --heads 24
+"""
+from __future__ import annotations
+
+import argparse
+import json
+
+import numpy as np
+
+
+def _time(fn, iters, warmup=3):
+    import torch
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(iters):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / iters
+
+
+def main():
+    import torch
+    import h3c_b200
+    ap = argparse.ArgumentParser()
+    ap.add_argument("case", choices=["gemm", "attn", "norm", "rope"])
+    ap.add_argument("--m", type=int, default=6144)
+    ap.add_argument("--n", type=int, default=9216)
+    ap.add_argument("--k", type=int, default=3072)
+    ap.add_argument("--lq", type=int, default=6144)
+    ap.add_argument("--lk", type=int, default=0)
+    ap.add_argument("--heads", type=int, default=24)
+    ap.add_argument("--epi", default="plain", choices=["plain", "gate", "gelu", "swiglu"])
+    ap.add_argument("--plain-quant", action="store_true")
+    ap.add_argument("--iters", type=int, default=20)
+    a = ap.parse_args()
+    cuda = h3c_b200.Cuda(0)
+    g = torch.Generator(device="cuda")
+    g.manual_seed(0)
+    out = {"case": a.case}
+    if a.case == "gemm":
+        w_i8 = np.random.default_rng(0).integers(-127, 128, (a.n, a.k), dtype=np.int8)
+        w = cuda.weight_from_i8(w_i8, np.full(a.n, 1e-3, np.float32))
+        x = torch.randint(-127, 128, (a.m, a.k), generator=g, device="cuda", dtype=torch.int8)
+        s = torch.full((a.m,), 0.01, device="cuda")
+        kind = {"plain": h3c_b200.EPI_PLAIN, "gate": h3c_b200.EPI_GATE, "gelu": h3c_b200.EPI_GELU,
+                "swiglu": h3c_b200.EPI_SWIGLU}[a.epi]
+        n_out = a.n // 2 if a.epi == "swiglu" else a.n
+        y = torch.empty((a.m, n_out), dtype=torch.bfloat16, device="cuda")
+        res = torch.zeros_like(y) if a.epi == "gate" else None
+        ms = _time(lambda: cuda.gemm_i8(w, x, s, kind=kind, residual=res, out=y), a.iters)
+        out.update(m=a.m, n=a.n, k=a.k, epi=a.epi, ms=ms, tops=2.0 * a.m * a.n * a.k / ms / 1e9)
+    elif a.case == "attn":
+        lk = a.lk or a.lq
+        q = torch.randn((a.lq, a.heads, 128), generator=g, device="cuda").to(torch.bfloat16)
+        k = torch.randn((lk, a.heads, 128), generator=g, device="cuda").to(torch.bfloat16)
+        v = torch.randn((lk, a.heads, 128), generator=g, device="cuda").to(torch.bfloat16)
+        o = torch.empty((a.lq, a.heads * 128), dtype=torch.bfloat16, device="cuda")
+        ms = _time(lambda: cuda.sdpa_bf16(q, k, v, out=o), a.iters)
+        out.update(lq=a.lq, lk=lk, heads=a.heads, ms=ms, tflops=4.0 * a.lq * lk * a.heads * 128 / ms / 1e9)
+    elif a.case == "norm":
+        x = torch.randn((a.m, a.k), generator=g, device="cuda").to(torch.bfloat16)
+        q = torch.empty((a.m, a.k), dtype=torch.int8, device="cuda")
+        s = torch.empty(a.m, dtype=torch.float32, device="cuda")
+        if a.plain_quant:
+            ms = _time(lambda: cuda.norm(x, identity=True, q=q, scales=s), a.iters)
+        else:
+            nw = torch.ones(a.k, device="cuda")
+            mod = torch.zeros((1, 6, a.k), device="cuda")
+            rm = torch.zeros(a.m, dtype=torch.int32, device="cuda")
+            ms = _time(lambda: cuda.norm(x, norm_w=nw, modulation=mod, row_map=rm, slots=6, shift_slot=0, scale_slot=1,
+                                         q=q, scales=s), a.iters)
+        out.update(m=a.m, k=a.k, ms=ms, gbs=(a.m * a.k * 3 + a.m * 4) / ms / 1e6)
+    else:
+        qkv = torch.randn((a.m, 3 * a.heads * 128), generator=g, device="cuda").to(torch.bfloat16)
+        qn = torch.ones(128, device="cuda")
+        cos = torch.ones((a.m, 48), device="cuda")
+        sin = torch.zeros((a.m, 48), device="cuda")
+        ms = _time(lambda: cuda.qkv_rope(qkv, qn, qn, cos, sin, a.heads, 128, 48), a.iters)
+        out.update(m=a.m, heads=a.heads, ms=ms, gbs=a.m * a.heads * 128 * 3 * 4 / ms / 1e6)
+    cuda.check()
+    print(json.dumps(out))
+
+
+if __name__ == "__main__":
+    main()
