@@ -6,9 +6,9 @@
 //              4-stage shared-memory ring, 128-byte swizzle
 //   warp 1     MMA issuer: four 128x256x32 tcgen05.mma per stage into one of two
 //              256-column TMEM accumulators; tcgen05.commit frees the stage
-//   warps 2-5  epilogue: tcgen05.ld the finished accumulator (one output row per
-//              thread), scale, apply gate+residual / SwiGLU / tanh-GELU, store.
-//              Runs while the MMA warp fills the other accumulator.
+//   warps 2-9  epilogue: tcgen05.ld the finished accumulator (one output row and half of the
+//              tile's columns per thread), scale, apply gate+residual / SwiGLU / tanh-GELU,
+//              store.  Runs while the MMA warp fills the other accumulator.
 // Accumulators are exact int32, so the integer part is bit-identical to
 // h3_w4a8_gemm_i8_dequant_f32 (h3_w4a8_dequant.c:692); the float part follows the
 // reference's operation order (a * s) * (float)acc and h3_dit_fused_epi.h:87-141.
@@ -28,7 +28,7 @@ constexpr int STAGES = 4;
 constexpr int A_BYTES = BM * BK;             // 16 KiB
 constexpr int B_BYTES = BN * BK;             // 32 KiB
 constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
-constexpr int THREADS = 192;
+constexpr int THREADS = 320;
 constexpr int TMEM_COLS = 512;
 constexpr int GROUP_M = 8;       // rasterisation: bands of 8 row-tiles share the weight tiles in L2
 constexpr size_t SMEM_BYTES = 1024 /*alignment slack*/ + (size_t)STAGES * STAGE_BYTES + 256;
@@ -150,7 +150,7 @@ __global__ void __launch_bounds__(gemm::THREADS, 1) k_gemm_i8(const __grid_const
         }
         for (int b = 0; b < 2; b++) {
             mbar_init(&tmem_full[b], 1);
-            mbar_init(&tmem_empty[b], 4);   // one arrival per epilogue warp
+            mbar_init(&tmem_empty[b], 8);   // one arrival per epilogue warp
         }
         *abort_word = 0;
         mbar_fence_init();
@@ -224,11 +224,15 @@ __global__ void __launch_bounds__(gemm::THREADS, 1) k_gemm_i8(const __grid_const
         __syncwarp();
     } else {
         // ----------------------------------------------------------- epilogue
-        const int q = warp & 3;                 // TMEM lane quarter this warp may read
+        // Eight warps: warp w reads TMEM lane quarter w % 4 (rows) and half (w - 2) / 4 of the tile's
+        // columns, 32 columns at a time.  Two warps per scheduler hide each other's load latency.
+        const int q = warp & 3;
+        const int half = (warp - 2) >> 2;
         const uint32_t lane_base = (uint32_t)(q * 32) << 16;
         OutT *y = reinterpret_cast<OutT *>(p.y);
         const OutT *res = reinterpret_cast<const OutT *>(p.residual);
         constexpr int VEC = OutTraits<OutT>::VEC;
+        constexpr int CHUNKS = (EPI == H3B_EPI_SWIGLU) ? (BN / 2) / 64 : BN / 64;   // per warp
         int it = 0;
         for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, it++) {
             int mt, nt;
@@ -246,16 +250,54 @@ __global__ void __launch_bounds__(gemm::THREADS, 1) k_gemm_i8(const __grid_const
             bool ok = mbar_wait(&tmem_full[buf], (it >> 1) & 1, abort_word, p.status, H3B_ST_TIMEOUT_TMEM_FULL);
             tc_fence_after();
             const uint32_t t_addr = tmem_base + lane_base + (uint32_t)buf * BN;
-            constexpr int CHUNKS = (EPI == H3B_EPI_SWIGLU) ? (BN / 2) / 32 : BN / 32;
             if (ok) {
 #pragma unroll 1
-                for (int ch = 0; ch < CHUNKS; ch++) {
+                for (int i = 0; i < CHUNKS; i++) {
+                    const int ch = half * CHUNKS + i;
                     const int col = c0 + ch * 32;
                     if (col >= p.n_out) break;   // uniform across the warp
                     uint32_t r[32];
                     tmem_ld_32x32b_x32(t_addr + ch * 32, r);
                     uint32_t r2[32];
                     if (EPI == H3B_EPI_SWIGLU) tmem_ld_32x32b_x32(t_addr + BN / 2 + ch * 32, r2);
+                    const bool full = col + 32 <= p.n_out;
+                    // column scales (and gate) of the chunk: the same addresses for every lane, fetched as
+                    // vectors while the TMEM load is in flight
+                    float sc[32], sc2[32], gt[32];
+                    if (full) {
+#pragma unroll
+                        for (int v = 0; v < 8; v++) {
+                            const float4 t4 = __ldg(reinterpret_cast<const float4 *>(p.s_channel + col) + v);
+                            sc[4 * v] = t4.x; sc[4 * v + 1] = t4.y; sc[4 * v + 2] = t4.z; sc[4 * v + 3] = t4.w;
+                        }
+                        if (EPI == H3B_EPI_SWIGLU) {
+#pragma unroll
+                            for (int v = 0; v < 8; v++) {
+                                const float4 t4 = __ldg(reinterpret_cast<const float4 *>(p.s_channel + p.n_out + col) + v);
+                                sc2[4 * v] = t4.x; sc2[4 * v + 1] = t4.y; sc2[4 * v + 2] = t4.z; sc2[4 * v + 3] = t4.w;
+                            }
+                        }
+                        if (EPI == H3B_EPI_GATE) {
+                            if (gate) {
+#pragma unroll
+                                for (int v = 0; v < 8; v++) {
+                                    const float4 t4 = __ldg(reinterpret_cast<const float4 *>(gate + col) + v);
+                                    gt[4 * v] = t4.x; gt[4 * v + 1] = t4.y; gt[4 * v + 2] = t4.z; gt[4 * v + 3] = t4.w;
+                                }
+                            } else {
+#pragma unroll
+                                for (int v = 0; v < 32; v++) gt[v] = 1.0f;
+                            }
+                        }
+                    } else {
+#pragma unroll
+                        for (int v = 0; v < 32; v++) {
+                            const bool in = col + v < p.n_out;
+                            sc[v] = in ? __ldg(p.s_channel + col + v) : 0.0f;
+                            if (EPI == H3B_EPI_SWIGLU) sc2[v] = in ? __ldg(p.s_channel + p.n_out + col + v) : 0.0f;
+                            if (EPI == H3B_EPI_GATE) gt[v] = (in && gate) ? __ldg(gate + col + v) : 1.0f;
+                        }
+                    }
                     tmem_ld_wait();
                     if (!row_ok) continue;
                     if constexpr (std::is_same<OutT, int32_t>::value) {
@@ -267,24 +309,21 @@ __global__ void __launch_bounds__(gemm::THREADS, 1) k_gemm_i8(const __grid_const
                     } else {
 #pragma unroll
                         for (int v = 0; v < 32; v += VEC) {
-                            if (col + v >= p.n_out) break;
+                            if (!full && col + v >= p.n_out) break;
                             float out[VEC], resv[VEC];
                             if (EPI == H3B_EPI_GATE) OutTraits<OutT>::load(res + (size_t)row * p.n_out + col + v, resv);
 #pragma unroll
-                            for (int i = 0; i < VEC; i++) {
-                                const int c = col + v + i;
-                                float val = __fmul_rn(__fmul_rn(a, __ldg(p.s_channel + c)), (float)(int32_t)r[v + i]);
+                            for (int e = 0; e < VEC; e++) {
+                                float val = __fmul_rn(__fmul_rn(a, sc[v + e]), (float)(int32_t)r[v + e]);
                                 if (EPI == H3B_EPI_GATE) {
-                                    const float g = gate ? __ldg(gate + c) : 1.0f;
-                                    val = __fadd_rn(resv[i], __fmul_rn(val, g));
+                                    val = __fadd_rn(resv[e], __fmul_rn(val, gt[v + e]));
                                 } else if (EPI == H3B_EPI_GELU) {
                                     val = sizeof(OutT) == 2 ? gelu_tanh_fast(val) : gelu_tanh_dev(val);
                                 } else if (EPI == H3B_EPI_SWIGLU) {
-                                    const float u = __fmul_rn(__fmul_rn(a, __ldg(p.s_channel + p.n_out + c)),
-                                                              (float)(int32_t)r2[v + i]);
+                                    const float u = __fmul_rn(__fmul_rn(a, sc2[v + e]), (float)(int32_t)r2[v + e]);
                                     val = __fmul_rn(val / __fadd_rn(1.0f, expf(-val)), u);
                                 }
-                                out[i] = val;
+                                out[e] = val;
                             }
                             OutTraits<OutT>::store(y + (size_t)row * p.n_out + col + v, out);
                         }
