@@ -11,9 +11,9 @@
 //               The two query tiles are interleaved so that the tensor core works on one
 //               while the other is in its softmax.
 //   warps 2-5   softmax of tile A, warps 6-9 softmax of tile B: one query row per thread.
-//               Pass 1 reads the scores from TMEM for the row maximum, pass 2 re-reads them,
-//               exponentiates and writes P (bf16 pairs) back to TMEM over the scores just
-//               consumed.  The accumulator is rescaled only when the running maximum grew
+//               The 128 scores of the row are read from TMEM into registers once; maximum,
+//               exponentials and row sum are computed there and P (bf16 pairs) is written back
+//               to TMEM over the score columns.  The accumulator is rescaled only when the running maximum grew
 //               by more than 2^8; the final division by the row sum undoes the stale scale.
 // TMEM (512 columns): S_A 0..127, S_B 128..255 (P overlays the first 64 columns of each),
 // O_A 256..383, O_B 384..511.
@@ -183,22 +183,26 @@ __global__ void __launch_bounds__(attn::THREADS, 1) k_attn_bf16(const __grid_con
             ok = mbar_wait(&s_full[t], j & 1, abort_word, p.status, H3B_ST_TIMEOUT_TMEM_FULL);
             if (!ok) break;
             tc_fence_after();
-            // pass 1: row maximum
-            float mx = -INFINITY;
-#pragma unroll 1
-            for (int ch = 0; ch < BKV / 32; ch++) {
-                uint32_t v[32];
-                tmem_ld_32x32b_x32(s_addr + ch * 32, v);
-                tmem_ld_wait();
-                if (valid == BKV) {
+            // all 128 scores of the row in registers (one TMEM round trip)
+            uint32_t sv[BKV];
 #pragma unroll
-                    for (int i = 0; i < 32; i++) mx = fmaxf(mx, __uint_as_float(v[i]));
-                } else {
+            for (int ch = 0; ch < BKV / 32; ch++)
+                tmem_ld_32x32b_x32(s_addr + ch * 32, *reinterpret_cast<uint32_t(*)[32]>(&sv[ch * 32]));
+            tmem_ld_wait();
+            if (valid != BKV) {
 #pragma unroll
-                    for (int i = 0; i < 32; i++)
-                        if (ch * 32 + i < valid) mx = fmaxf(mx, __uint_as_float(v[i]));
-                }
+                for (int i = 0; i < BKV; i++)
+                    if (i >= valid) sv[i] = 0xff800000u;   // -inf: exp2 gives 0
             }
+            float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
+#pragma unroll
+            for (int i = 0; i < BKV; i += 4) {
+                mx0 = fmaxf(mx0, __uint_as_float(sv[i]));
+                mx1 = fmaxf(mx1, __uint_as_float(sv[i + 1]));
+                mx2 = fmaxf(mx2, __uint_as_float(sv[i + 2]));
+                mx3 = fmaxf(mx3, __uint_as_float(sv[i + 3]));
+            }
+            const float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
             const float m_new = fmaxf(m_run, mx * p.scale_log2);
             const bool grow_me = (m_new - m_run) > 8.0f;   // also true on the first tile (m_run = -inf)
             if (__any_sync(0xffffffffu, grow_me)) {
@@ -222,28 +226,26 @@ __global__ void __launch_bounds__(attn::THREADS, 1) k_attn_bf16(const __grid_con
                     }
                 }
             }
-            // pass 2: probabilities -> bf16 pairs -> TMEM, over the score columns already consumed
-            float l_add = 0.0f;
-#pragma unroll 1
+            // probabilities -> bf16 pairs -> TMEM, over the score columns (already in registers)
+            float l0 = 0.0f, l1 = 0.0f, l2 = 0.0f, l3 = 0.0f;
+            const float neg_m = -m_run;
+#pragma unroll
             for (int ch = 0; ch < BKV / 32; ch++) {
-                uint32_t v[32];
-                tmem_ld_32x32b_x32(s_addr + ch * 32, v);
-                tmem_ld_wait();
                 uint32_t packed[16];
 #pragma unroll
-                for (int i = 0; i < 32; i += 2) {
-                    float p0 = ex2_approx(fmaf(__uint_as_float(v[i]), p.scale_log2, -m_run));
-                    float p1 = ex2_approx(fmaf(__uint_as_float(v[i + 1]), p.scale_log2, -m_run));
-                    if (valid != BKV) {
-                        if (ch * 32 + i >= valid) p0 = 0.0f;
-                        if (ch * 32 + i + 1 >= valid) p1 = 0.0f;
-                    }
-                    l_add += p0 + p1;
-                    __nv_bfloat162 h = __floats2bfloat162_rn(p0, p1);
-                    packed[i >> 1] = *reinterpret_cast<uint32_t *>(&h);
+                for (int i = 0; i < 32; i += 4) {
+                    const float p0 = ex2_approx(fmaf(__uint_as_float(sv[ch * 32 + i]), p.scale_log2, neg_m));
+                    const float p1 = ex2_approx(fmaf(__uint_as_float(sv[ch * 32 + i + 1]), p.scale_log2, neg_m));
+                    const float p2 = ex2_approx(fmaf(__uint_as_float(sv[ch * 32 + i + 2]), p.scale_log2, neg_m));
+                    const float p3 = ex2_approx(fmaf(__uint_as_float(sv[ch * 32 + i + 3]), p.scale_log2, neg_m));
+                    l0 += p0; l1 += p1; l2 += p2; l3 += p3;
+                    __nv_bfloat162 h0 = __floats2bfloat162_rn(p0, p1), h1 = __floats2bfloat162_rn(p2, p3);
+                    packed[i >> 1] = *reinterpret_cast<uint32_t *>(&h0);
+                    packed[(i >> 1) + 1] = *reinterpret_cast<uint32_t *>(&h1);
                 }
                 tmem_st_32x32b_x16(s_addr + ch * 16, packed);
             }
+            const float l_add = (l0 + l1) + (l2 + l3);
             l_run += l_add;
             tmem_st_wait();
             tc_fence_before();

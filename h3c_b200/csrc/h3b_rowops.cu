@@ -24,14 +24,22 @@ template <> __device__ __forceinline__ __half from_f<__half>(float v) { return _
 // value as it reads back after being stored in T
 template <typename T> __device__ __forceinline__ float round_to(float v) { return to_f<T>(from_f<T>(v)); }
 
-template <typename T, int V> struct Vec { T v[V]; };
-
+// V consecutive elements as one or two aligned vector accesses (4, 8, 16 or 32 bytes in total)
 template <typename T, int V>
 __device__ __forceinline__ void load_vec(const T *p, float (&out)[V]) {
+    constexpr int BYTES = sizeof(T) * V;
     if constexpr (V == 1) {
         out[0] = to_f<T>(p[0]);
+    } else if constexpr (BYTES == 32) {
+        uint4 raw[2];
+        raw[0] = reinterpret_cast<const uint4 *>(p)[0];
+        raw[1] = reinterpret_cast<const uint4 *>(p)[1];
+        const T *e = reinterpret_cast<const T *>(raw);
+#pragma unroll
+        for (int i = 0; i < V; i++) out[i] = to_f<T>(e[i]);
     } else {
-        using VT = typename std::conditional<sizeof(T) * V == 16, uint4, uint2>::type;
+        static_assert(BYTES == 16 || BYTES == 8 || BYTES == 4, "unsupported vector width");
+        using VT = typename std::conditional<BYTES == 16, uint4, typename std::conditional<BYTES == 8, uint2, uint32_t>::type>::type;
         VT raw = *reinterpret_cast<const VT *>(p);
         const T *e = reinterpret_cast<const T *>(&raw);
 #pragma unroll
@@ -40,10 +48,19 @@ __device__ __forceinline__ void load_vec(const T *p, float (&out)[V]) {
 }
 template <typename T, int V>
 __device__ __forceinline__ void store_vec(T *p, const float (&in)[V]) {
+    constexpr int BYTES = sizeof(T) * V;
     if constexpr (V == 1) {
         p[0] = from_f<T>(in[0]);
+    } else if constexpr (BYTES == 32) {
+        uint4 raw[2];
+        T *e = reinterpret_cast<T *>(raw);
+#pragma unroll
+        for (int i = 0; i < V; i++) e[i] = from_f<T>(in[i]);
+        reinterpret_cast<uint4 *>(p)[0] = raw[0];
+        reinterpret_cast<uint4 *>(p)[1] = raw[1];
     } else {
-        using VT = typename std::conditional<sizeof(T) * V == 16, uint4, uint2>::type;
+        static_assert(BYTES == 16 || BYTES == 8 || BYTES == 4, "unsupported vector width");
+        using VT = typename std::conditional<BYTES == 16, uint4, typename std::conditional<BYTES == 8, uint2, uint32_t>::type>::type;
         VT raw;
         T *e = reinterpret_cast<T *>(&raw);
 #pragma unroll
@@ -201,8 +218,126 @@ __global__ void __launch_bounds__(256) k_norm(NormParams p) {
     }
 }
 
+// Register-resident variant for 16-bit rows whose width is THREADS * NV * 8: each thread keeps
+// NV 16-byte vectors (8 elements each) of the row, so the row is read from HBM once and never
+// staged in shared memory.  Same arithmetic, same order per element as k_norm; the row
+// reductions combine per-thread partials (fixed order), so results are deterministic.
+template <typename T, int NV, int THREADS>
+__global__ void __launch_bounds__(THREADS) k_norm_reg(NormParams p) {
+    __shared__ float red[THREADS / 32];
+    const size_t r = blockIdx.x;
+    const unsigned W = p.width;
+    const size_t mrow = p.row_map ? p.row_map[r] : r;
+    const float *mod = p.mod ? p.mod + mrow * p.slots * W : nullptr;
+    const T *x = reinterpret_cast<const T *>(p.x) + r * W;
+    const T *br = p.branch ? reinterpret_cast<const T *>(p.branch) + r * W : nullptr;
+    T *gated = p.gated ? reinterpret_cast<T *>(p.gated) + r * W : nullptr;
+    T *normed = p.normed ? reinterpret_cast<T *>(p.normed) + r * W : nullptr;
+    float v[NV][8];
+    float ss = 0.0f;
+#pragma unroll
+    for (int j = 0; j < NV; j++) {
+        const unsigned c = (j * THREADS + threadIdx.x) * 8;
+        load_vec<T, 8>(x + c, v[j]);
+        if (br) {
+            float b[8];
+            load_vec<T, 8>(br + c, b);
+#pragma unroll
+            for (int i = 0; i < 8; i++) {
+                const float g = mod ? mod[p.gate_slot * W + c + i] : 1.0f;
+                v[j][i] = round_to<T>(__fadd_rn(v[j][i], __fmul_rn(b[i], g)));
+            }
+            if (gated) store_vec<T, 8>(gated + c, v[j]);
+        }
+#pragma unroll
+        for (int i = 0; i < 8; i++) ss = __fadd_rn(ss, __fmul_rn(v[j][i], v[j][i]));
+    }
+    float amax = 0.0f;
+    if (!p.identity) {
+        ss = block_sum(ss, red);
+        const float inv = 1.0f / sqrtf(ss / (float)W + p.eps);
+#pragma unroll
+        for (int j = 0; j < NV; j++) {
+            const unsigned c = (j * THREADS + threadIdx.x) * 8;
+            float w[8], sc[8], sh[8];
+            if (p.norm_w) {
+                load_vec<float, 4>(p.norm_w + c, reinterpret_cast<float(&)[4]>(w[0]));
+                load_vec<float, 4>(p.norm_w + c + 4, reinterpret_cast<float(&)[4]>(w[4]));
+            }
+            if (mod) {
+                load_vec<float, 4>(mod + p.scale_slot * W + c, reinterpret_cast<float(&)[4]>(sc[0]));
+                load_vec<float, 4>(mod + p.scale_slot * W + c + 4, reinterpret_cast<float(&)[4]>(sc[4]));
+                load_vec<float, 4>(mod + p.shift_slot * W + c, reinterpret_cast<float(&)[4]>(sh[0]));
+                load_vec<float, 4>(mod + p.shift_slot * W + c + 4, reinterpret_cast<float(&)[4]>(sh[4]));
+            }
+#pragma unroll
+            for (int i = 0; i < 8; i++) {
+                float n = __fmul_rn(__fmul_rn(v[j][i], inv), p.norm_w ? w[i] : 1.0f);
+                if (mod) n = __fadd_rn(__fmul_rn(n, __fadd_rn(1.0f, sc[i])), sh[i]);
+                v[j][i] = round_to<T>(n);
+                amax = fmaxf(amax, fabsf(v[j][i]));
+            }
+            if (normed) store_vec<T, 8>(normed + c, v[j]);
+        }
+    } else {
+#pragma unroll
+        for (int j = 0; j < NV; j++)
+#pragma unroll
+            for (int i = 0; i < 8; i++) amax = fmaxf(amax, fabsf(v[j][i]));
+    }
+    if (p.q) {
+        amax = block_max(amax, red);
+        const float scale = amax > 0.0f ? amax / 127.0f : 1.0f;
+        const float inv = 1.0f / scale;
+        if (threadIdx.x == 0) p.scales[r] = scale;
+        int8_t *q = p.q + r * W;
+#pragma unroll
+        for (int j = 0; j < NV; j++) {
+            const unsigned c = (j * THREADS + threadIdx.x) * 8;
+            union { int8_t b[8]; uint2 u; } o;
+#pragma unroll
+            for (int i = 0; i < 8; i++) o.b[i] = quant_code(v[j][i], inv);
+            *reinterpret_cast<uint2 *>(q + c) = o.u;
+        }
+    }
+}
+
+template <typename T, int NV, int THREADS>
+static int norm_reg_launch(h3_cuda *cuda, const NormParams &p, size_t rows, char *error, size_t error_size) {
+    ProfScope prof(cuda, PROF_ROWS);
+    k_norm_reg<T, NV, THREADS><<<(unsigned)rows, THREADS, 0, cuda->op_stream>>>(p);
+    cuda->launches++;
+    H3B_CUDA_OK(cudaGetLastError(), "k_norm_reg launch");
+    return 1;
+}
+
+// Picks the register-resident kernel when the shape allows it; returns -1 when it does not apply.
+template <typename T>
+static int norm_reg_dispatch(h3_cuda *cuda, const NormParams &p, size_t rows, char *error, size_t error_size) {
+    if (sizeof(T) != 2 || p.gs != 0 || p.rot || p.width % 1024) return -1;
+    auto al16 = [](const void *q_) { return !q_ || (reinterpret_cast<uintptr_t>(q_) & 15) == 0; };
+    if (!al16(p.x) || !al16(p.branch) || !al16(p.gated) || !al16(p.normed) || !al16(p.norm_w) || !al16(p.mod) ||
+        (p.q && (reinterpret_cast<uintptr_t>(p.q) & 7)))
+        return -1;
+    switch (p.width) {
+    case 1024: return norm_reg_launch<T, 1, 128>(cuda, p, rows, error, error_size);
+    case 2048: return norm_reg_launch<T, 2, 128>(cuda, p, rows, error, error_size);
+    case 3072: return norm_reg_launch<T, 3, 128>(cuda, p, rows, error, error_size);
+    case 4096: return norm_reg_launch<T, 4, 128>(cuda, p, rows, error, error_size);
+    case 6144: return norm_reg_launch<T, 3, 256>(cuda, p, rows, error, error_size);
+    case 8192: return norm_reg_launch<T, 4, 256>(cuda, p, rows, error, error_size);
+    case 12288: return norm_reg_launch<T, 6, 256>(cuda, p, rows, error, error_size);
+    case 16384: return norm_reg_launch<T, 4, 512>(cuda, p, rows, error, error_size);
+    }
+    return -1;
+}
+
 template <typename T>
 static int norm_dispatch(h3_cuda *cuda, const NormParams &p, size_t rows, bool vec, char *error, size_t error_size) {
+    if (sizeof(T) == 2) {
+        int rc = norm_reg_dispatch<T>(cuda, p, rows, error, error_size);
+        if (rc >= 0) return rc;
+    }
     size_t smem = (size_t)p.width * sizeof(float);
     if (smem > 200 * 1024) return fail(error, error_size, "row width %u too large for the row kernel", p.width);
     auto kv = k_norm<T, 4>;
@@ -367,18 +502,20 @@ int launch_swiglu(h3_cuda *cuda, const void *fused, size_t rows, size_t width, v
 
 // ---------------------------------------------------------- QK-norm + RoPE
 //
-// One warp per (row, head); each lane owns EPL = head_dim / 32 consecutive
-// dimensions.  Split-half pairing (d, d + rope_half) lives rope_half / EPL lanes
-// apart; consecutive pairing (2d, 2d+1) lives inside one lane.
-template <typename TI, typename TO, int EPL>
+// LANES = head_dim / EPL threads per (row, head); each owns EPL consecutive dimensions
+// (16-byte loads for 16-bit inputs with EPL = 8).  Split-half pairing (d, d + rope_half)
+// lives rope_half / EPL lanes apart; consecutive pairing (2d, 2d+1) lives inside one lane.
+template <typename TI, typename TO, int EPL, int LANES>
 __global__ void __launch_bounds__(256) k_qkv_rope(const TI *qkv, const float *q_norm, const float *k_norm,
                                                   const float *cosT, const float *sinT, size_t seq, unsigned heads,
                                                   unsigned rope_half, float eps, int grouped, int split_half, TO *q,
                                                   TO *k, TO *v) {
-    constexpr unsigned HD = EPL * 32;
-    const unsigned lane = threadIdx.x & 31;
-    const size_t item = (size_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
-    if (item >= seq * heads) return;
+    constexpr unsigned HD = EPL * LANES;
+    const unsigned lane = threadIdx.x % LANES;
+    size_t item = (size_t)blockIdx.x * (blockDim.x / LANES) + threadIdx.x / LANES;
+    // surplus groups of the last CTA redo the last item (identical values) so that every lane of a
+    // warp takes part in the shuffles below
+    if (item >= seq * heads) item = seq * heads - 1;
     const size_t row = item / heads;
     const unsigned head = (unsigned)(item - row * heads);
     const size_t inner = (size_t)heads * HD;
@@ -397,7 +534,7 @@ __global__ void __launch_bounds__(256) k_qkv_rope(const TI *qkv, const float *q_
         qs += qv[i] * qv[i];
         ks += kv[i] * kv[i];
     }
-    for (int o = 16; o > 0; o >>= 1) {
+    for (int o = LANES / 2; o > 0; o >>= 1) {
         qs += __shfl_xor_sync(0xffffffffu, qs, o);
         ks += __shfl_xor_sync(0xffffffffu, ks, o);
     }
@@ -415,10 +552,10 @@ __global__ void __launch_bounds__(256) k_qkv_rope(const TI *qkv, const float *q_
 #pragma unroll
             for (int i = 0; i < EPL; i++) {
                 // partner values: from lane + off for the low half, lane - off for the high half
-                float q_up = __shfl_down_sync(0xffffffffu, qv[i], lane_off);
-                float q_dn = __shfl_up_sync(0xffffffffu, qv[i], lane_off);
-                float k_up = __shfl_down_sync(0xffffffffu, kv[i], lane_off);
-                float k_dn = __shfl_up_sync(0xffffffffu, kv[i], lane_off);
+                float q_up = __shfl_down_sync(0xffffffffu, qv[i], lane_off, LANES);
+                float q_dn = __shfl_up_sync(0xffffffffu, qv[i], lane_off, LANES);
+                float k_up = __shfl_down_sync(0xffffffffu, kv[i], lane_off, LANES);
+                float k_dn = __shfl_up_sync(0xffffffffu, kv[i], lane_off, LANES);
                 unsigned d = d0 + i;
                 if (d < rope_half) {
                     float c = cr[d], s = sr[d];
@@ -464,14 +601,14 @@ static int qkv_rope_dispatch(h3_cuda *cuda, const void *qkv, const float *qn, co
                              const float *s, size_t seq, size_t heads, size_t hd, size_t rope_half, float eps,
                              int grouped, int split_half, void *q, void *k, void *v, char *error, size_t error_size) {
     size_t items = seq * heads;
-    unsigned grid = (unsigned)ceil_div(items, 8);
+    unsigned grid = (unsigned)ceil_div(items, 16);   // 16 lanes per item, 256 threads
     ProfScope prof(cuda, PROF_ROPE);
-#define H3B_ROPE(EPL)                                                                                          \
-    k_qkv_rope<TI, TO, EPL><<<grid, 256, 0, cuda->op_stream>>>((const TI *)qkv, qn, kn, c, s, seq, (unsigned)heads, \
-                                                               (unsigned)rope_half, eps, grouped, split_half,  \
-                                                               (TO *)q, (TO *)k, (TO *)v)
-    if (hd == 128) H3B_ROPE(4);
-    else if (hd == 64) H3B_ROPE(2);
+#define H3B_ROPE(EPL)                                                                                              \
+    k_qkv_rope<TI, TO, EPL, 16><<<grid, 256, 0, cuda->op_stream>>>((const TI *)qkv, qn, kn, c, s, seq, (unsigned)heads, \
+                                                                   (unsigned)rope_half, eps, grouped, split_half,  \
+                                                                   (TO *)q, (TO *)k, (TO *)v)
+    if (hd == 128) H3B_ROPE(8);
+    else if (hd == 64) H3B_ROPE(4);
     else return fail(error, error_size, "qkv_rope: head_dim %zu unsupported (64 or 128)", hd);
 #undef H3B_ROPE
     cuda->launches++;
@@ -573,8 +710,11 @@ int h3b_qkv_rope_dev(h3_cuda *cuda, const void *d_qkv, int in_dtype, const float
         (rope_half > 0 && (!d_rope_cos || !d_rope_sin)))
         return fail(error, error_size, "invalid qkv_rope args");
     if (rope_half * 2 > head_dim) return fail(error, error_size, "rope_half too large for head_dim");
-    if (split_half && rope_half % (head_dim / 32))
-        return fail(error, error_size, "qkv_rope: rope_half must be a multiple of head_dim/32");
+    if ((reinterpret_cast<uintptr_t>(d_qkv) | reinterpret_cast<uintptr_t>(d_query) | reinterpret_cast<uintptr_t>(d_key) |
+         reinterpret_cast<uintptr_t>(d_value)) & 15)
+        return fail(error, error_size, "qkv_rope: tensors must be 16-byte aligned");
+    if (split_half && rope_half % (head_dim / 16))
+        return fail(error, error_size, "qkv_rope: rope_half must be a multiple of head_dim/16");
 #define H3B_QR(TI, TO)                                                                                             \
     return qkv_rope_dispatch<TI, TO>(cuda, d_qkv, d_q_norm, d_k_norm, d_rope_cos, d_rope_sin, seq, heads, head_dim, \
                                      rope_half, epsilon, grouped, split_half, d_query, d_key, d_value, error,      \
