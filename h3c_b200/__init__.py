@@ -255,6 +255,51 @@ class Cuda:
         call("h3_cuda_quantize_act_nvfp4_dev", self.h, ptr(x), m, k, ptr(packed), ptr(sf))
         return packed, sf
 
+    def gemm_fp4(self, w_fp4, sf_w, x_fp4, sf_x, alpha=1.0, out_dtype=None):
+        """Block-scaled NVFP4 GEMM: packed E2M1 [n,k/2] x [m,k/2] with blocked UE4M3 scales -> [m,n]."""
+        import torch
+        out_dtype = out_dtype or torch.float32
+        n, m, k = w_fp4.shape[0], x_fp4.shape[0], x_fp4.shape[1] * 2
+        y = torch.empty((m, n), dtype=out_dtype, device=x_fp4.device)
+        call("h3b_gemm_fp4_dev", self.h, ptr(w_fp4), ptr(sf_w), ptr(x_fp4), ptr(sf_x), m, n, k, float(alpha), ptr(y),
+             _dt(y))
+        return y
+
+    def nvfp4_weight(self, packed, sf, scale2, n, k):
+        import numpy as np
+        packed = np.ascontiguousarray(packed, np.uint8)
+        sf = np.ascontiguousarray(sf, np.uint8)
+        h = C.c_void_p()
+        call("h3_cuda_nvfp4_weight_create", self.h, packed.ctypes.data, sf.ctypes.data, float(scale2), n, k, C.byref(h),
+             None)
+        return h.value
+
+    def nvfp4_weight_free(self, handle):
+        load().h3_cuda_nvfp4_weight_free(self.h, handle)
+
+    def gemm_fp4_w_act_dev(self, weight_handle, x_f32, act_scale=1.0, kind="plain", residual=None, modulation=None,
+                           row_map=None, slots=0, gate_slot=0):
+        """h3_cuda_gemm_fp4_w_act_dev / _swiglu / _gate: f32 activations in, f32 out."""
+        import torch
+        lib = load()
+        n = int(lib.h3_cuda_nvfp4_weight_n(weight_handle))
+        m = x_f32.shape[0]
+        y = torch.empty((m, n // 2 if kind == "swiglu" else n), dtype=torch.float32, device=x_f32.device)
+        err = C.create_string_buffer(_l.ERR_LEN)
+        if kind == "plain":
+            rc = lib.h3_cuda_gemm_fp4_w_act_dev(self.h, weight_handle, ptr(x_f32), act_scale, m, ptr(y), None, None, None,
+                                                err, _l.ERR_LEN, None)
+        elif kind == "swiglu":
+            rc = lib.h3_cuda_gemm_fp4_w_act_dev_swiglu(self.h, weight_handle, ptr(x_f32), act_scale, m, None, ptr(y), None,
+                                                       None, None, err, _l.ERR_LEN, None)
+        else:
+            rc = lib.h3_cuda_gemm_fp4_w_act_dev_gate(self.h, weight_handle, ptr(x_f32), act_scale, m, ptr(residual),
+                                                     ptr(modulation), ptr(row_map), slots, gate_slot, None, ptr(y), None,
+                                                     None, None, err, _l.ERR_LEN, None)
+        if rc != 1:
+            raise H3Error(f"gemm_fp4_w_act_dev[{kind}]: {err.value.decode(errors='replace')}")
+        return y
+
     # ---- host-buffer forms (numpy in, numpy out)
     def adaln_f32(self, x, norm_w, modulation, row_map, slots, shift_slot, scale_slot, eps=1e-5):
         import numpy as np

@@ -1,0 +1,472 @@
+// NVFP4 block-scaled GEMM on tcgen05 (kind::mxf4nvf4, one UE4M3 scale per 16 E2M1 values):
+//   Y[m,n] = alpha * sum_k  (x4[m,k] * sfx[m,k/16]) * (w4[n,k] * sfw[n,k/16])
+// replacing the reference's cuBLASLt call + bf16 round trip + separate dequant epilogue
+// (h3_gpu_cuda.cu:5696-5932 h3_cuda_lt_gemm_fp4_bf16, :6351 h3_cuda_fp4_gemm_run, :757-808).
+//
+// Operands are the reference's tensors unchanged: packed E2M1 [rows, K/2] with the high nibble
+// holding the even k (the tensor core assumes the opposite order, but X and W are swapped the
+// same way inside every byte, so each product pairs the right elements and every 16-block keeps
+// its scale), and UE4M3 scales in the 128x4 blocked layout (h3_gpu_cuda.cu:4534), which is the
+// layout tcgen05.cp moves into tensor memory as it is: one 512-byte block = 128 rows x 64 k.
+//
+// Persistent kernel, tile 128 x 128, 256 k (128 packed bytes) per stage:
+//   warp 0     TMA: X and W tiles (128-byte swizzle) + four scale blocks each (plain bulk copies)
+//   warp 1     per stage: tcgen05.cp the eight scale blocks into TMEM, then four
+//              128x128x64 block-scaled MMAs into one of two 128-column accumulators
+//   warps 2-9  epilogue (one row, 64 columns per thread): alpha, optional gate + residual, store
+#include <cuda_bf16.h>
+
+#include "h3b_internal.h"
+#include "h3b_ptx.cuh"
+
+namespace h3b {
+
+namespace fp4 {
+constexpr int BM = 128, BN = 128;
+constexpr int BK_BYTES = 128;                 // 256 four-bit values of K per stage
+constexpr int STAGES = 5;
+constexpr int A_BYTES = BM * BK_BYTES;        // 16 KiB
+constexpr int B_BYTES = BN * BK_BYTES;        // 16 KiB
+constexpr int SF_BYTES = 4 * 512;             // four 128x64 scale blocks per operand and stage
+constexpr int STAGE_BYTES = A_BYTES + B_BYTES + 2 * SF_BYTES;
+constexpr int THREADS = 320;
+constexpr int TMEM_COLS = 512;
+constexpr uint32_t ACC_COL = 0;               // two accumulators of 128 columns
+constexpr uint32_t SF_COL = 256;              // per stage parity: 16 columns SFA + 16 columns SFB
+constexpr size_t SMEM_BYTES = 1024 + (size_t)STAGES * STAGE_BYTES + 256;
+}  // namespace fp4
+
+struct Fp4Params {
+    CUtensorMap tmap_x;   // [M, K/2] bytes, box 128 x 128
+    CUtensorMap tmap_w;   // [N, K/2] bytes, box 128 x 128
+    const uint8_t *sf_x, *sf_w;
+    int M, N, K;
+    int m_tiles, n_tiles, k_blocks;
+    int sf_tiles_per_rowblock;   // K / 64
+    float alpha;
+    int gate;                    // 0 plain, 1 y = residual + alpha * acc * gate
+    int out_bf16;                // 0 f32, 1 bf16
+    void *y;
+    const void *residual;
+    const float *mod;
+    const uint32_t *row_map;
+    int slots, gate_slot;
+    int *status;
+};
+
+__device__ __forceinline__ void bulk_load(void *dst, const void *src, uint32_t bytes, uint64_t *bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                     smem_u32(dst)),
+                 "l"(src), "r"(bytes), "r"(smem_u32(bar))
+                 : "memory");
+}
+
+// Shared-memory descriptor of one 512-byte scale block, read as 32 rows of 16 bytes (rows 16 bytes
+// apart, 8-row groups 128 bytes apart, no swizzle); tcgen05.cp broadcasts it to the four lane quarters.
+__device__ __forceinline__ uint64_t sf_desc(uint32_t addr) {
+    uint64_t d = 0;
+    d |= (uint64_t)((addr & 0x3ffff) >> 4);
+    d |= (uint64_t)(128 >> 4) << 32;   // stride between 8-row groups
+    d |= (uint64_t)1 << 46;
+    return d;
+}
+__device__ __forceinline__ void tmem_cp_32x128b_warpx4(uint32_t taddr, uint64_t desc) {
+    asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(taddr), "l"(desc) : "memory");
+}
+__device__ __forceinline__ void umma_nvfp4_ss(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                              uint32_t sfa, uint32_t sfb, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::mxf4nvf4.block_scale.block16 [%0], %1, %2, %3, [%5], [%6], p;\n\t}"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(sfa), "r"(sfb)
+        : "memory");
+}
+
+// block-scaled instruction descriptor: E2M1 x E2M1, UE4M3 scales, K = 64 per instruction
+__host__ __device__ constexpr uint32_t fp4_idesc(uint32_t m, uint32_t n) {
+    return (1u << 7) | (1u << 10) | ((n >> 3) << 17) | (0u << 23) | ((m >> 4) << 24);
+}
+
+__global__ void __launch_bounds__(fp4::THREADS, 1) k_gemm_nvfp4(const __grid_constant__ Fp4Params p) {
+    using namespace fp4;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    uint64_t *bars = reinterpret_cast<uint64_t *>(smem + (size_t)STAGES * STAGE_BYTES);
+    uint64_t *full = bars, *empty = bars + STAGES, *tmem_full = bars + 2 * STAGES, *tmem_empty = bars + 2 * STAGES + 2;
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 2 * STAGES + 4);
+    volatile int *abort_word = reinterpret_cast<volatile int *>(tmem_slot + 1);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int total_tiles = p.m_tiles * p.n_tiles;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; s++) {
+            mbar_init(&full[s], 1);
+            mbar_init(&empty[s], 1);
+        }
+        for (int b = 0; b < 2; b++) {
+            mbar_init(&tmem_full[b], 1);
+            mbar_init(&tmem_empty[b], 8);
+        }
+        *abort_word = 0;
+        mbar_fence_init();
+        tma_prefetch_desc(&p.tmap_x);
+        tma_prefetch_desc(&p.tmap_w);
+    }
+    if (warp == 1) {
+        tmem_alloc(tmem_slot, TMEM_COLS);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            int s = 0;
+            uint32_t ph = 0;
+            for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
+                const int mt = tile % p.m_tiles, nt = tile / p.m_tiles;
+                for (int kb = 0; kb < p.k_blocks; kb++) {
+                    if (!mbar_wait(&empty[s], ph ^ 1, abort_word, p.status, H3B_ST_TIMEOUT_EMPTY)) break;
+                    uint8_t *a_dst = smem + (size_t)s * STAGE_BYTES;
+                    uint8_t *b_dst = a_dst + A_BYTES, *sfa_dst = b_dst + B_BYTES, *sfb_dst = sfa_dst + SF_BYTES;
+                    // scale blocks of this stage: k tiles [4 kb, 4 kb + 4) of the row block, clipped at K / 64
+                    const int kt0 = kb * 4;
+                    const int nkt = min(4, p.sf_tiles_per_rowblock - kt0);
+                    const uint32_t sf_bytes = (uint32_t)nkt * 512;
+                    mbar_expect_tx(&full[s], A_BYTES + B_BYTES + 2 * sf_bytes);
+                    tma_load_2d(a_dst, &p.tmap_x, &full[s], kb * BK_BYTES, mt * BM);
+                    tma_load_2d(b_dst, &p.tmap_w, &full[s], kb * BK_BYTES, nt * BN);
+                    bulk_load(sfa_dst, p.sf_x + ((size_t)mt * p.sf_tiles_per_rowblock + kt0) * 512, sf_bytes, &full[s]);
+                    bulk_load(sfb_dst, p.sf_w + ((size_t)nt * p.sf_tiles_per_rowblock + kt0) * 512, sf_bytes, &full[s]);
+                    if (++s == STAGES) { s = 0; ph ^= 1; }
+                }
+                if (*abort_word) break;
+            }
+        }
+        __syncwarp();
+    } else if (warp == 1) {
+        if (lane == 0) {
+            constexpr uint32_t idesc = fp4_idesc(BM, BN);
+            int s = 0, it = 0, sfbuf = 0;
+            uint32_t ph = 0;
+            for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, it++) {
+                const int buf = it & 1;
+                if (!mbar_wait(&tmem_empty[buf], ((it >> 1) & 1) ^ 1, abort_word, p.status, H3B_ST_TIMEOUT_TMEM_EMPTY))
+                    break;
+                tc_fence_after();
+                const uint32_t d_tmem = tmem_base + ACC_COL + (uint32_t)buf * BN;
+                for (int kb = 0; kb < p.k_blocks; kb++) {
+                    if (!mbar_wait(&full[s], ph, abort_word, p.status, H3B_ST_TIMEOUT_FULL)) break;
+                    tc_fence_after();
+                    const uint32_t a_addr = smem_u32(smem + (size_t)s * STAGE_BYTES);
+                    const uint32_t b_addr = a_addr + A_BYTES, sfa_addr = b_addr + B_BYTES, sfb_addr = sfa_addr + SF_BYTES;
+                    const int nkt = min(4, p.sf_tiles_per_rowblock - kb * 4);   // MMAs (64 k each) with data
+                    const uint32_t sf_t = tmem_base + SF_COL + (uint32_t)sfbuf * 32;
+                    for (int j = 0; j < nkt; j++) {
+                        tmem_cp_32x128b_warpx4(sf_t + j * 4, sf_desc(sfa_addr + j * 512));
+                        tmem_cp_32x128b_warpx4(sf_t + 16 + j * 4, sf_desc(sfb_addr + j * 512));
+                    }
+                    for (int j = 0; j < nkt; j++)
+                        umma_nvfp4_ss(d_tmem, umma_desc_k_sw128(a_addr + j * 32), umma_desc_k_sw128(b_addr + j * 32), idesc,
+                                      sf_t + j * 4, sf_t + 16 + j * 4, (uint32_t)((kb | j) != 0));
+                    tc_commit(&empty[s]);
+                    sfbuf ^= 1;
+                    if (++s == STAGES) { s = 0; ph ^= 1; }
+                }
+                if (*abort_word) break;
+                tc_commit(&tmem_full[buf]);
+            }
+        }
+        __syncwarp();
+    } else {
+        const int q = warp & 3, half = (warp - 2) >> 2;
+        const uint32_t lane_base = (uint32_t)(q * 32) << 16;
+        int it = 0;
+        for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, it++) {
+            const int mt = tile % p.m_tiles, nt = tile / p.m_tiles;
+            const int buf = it & 1;
+            const int row = mt * BM + q * 32 + lane;
+            const bool row_ok = row < p.M;
+            const float *gate = nullptr;
+            if (p.gate && p.mod && row_ok) {
+                const size_t mrow = p.row_map ? p.row_map[row] : (size_t)row;
+                gate = p.mod + (mrow * p.slots + p.gate_slot) * (size_t)p.N;
+            }
+            bool ok = mbar_wait(&tmem_full[buf], (it >> 1) & 1, abort_word, p.status, H3B_ST_TIMEOUT_TMEM_FULL);
+            tc_fence_after();
+            const uint32_t t_addr = tmem_base + lane_base + ACC_COL + (uint32_t)buf * BN;
+            if (ok) {
+#pragma unroll 1
+                for (int i = 0; i < 2; i++) {
+                    const int ch = half * 2 + i;
+                    const int col = nt * BN + ch * 32;
+                    if (col >= p.N) break;
+                    uint32_t r[32];
+                    tmem_ld_32x32b_x32(t_addr + ch * 32, r);
+                    tmem_ld_wait();
+                    if (!row_ok) continue;
+#pragma unroll
+                    for (int v = 0; v < 32; v += 8) {
+                        if (col + v >= p.N) break;
+                        float out[8];
+#pragma unroll
+                        for (int e = 0; e < 8; e++) out[e] = __fmul_rn(p.alpha, __uint_as_float(r[v + e]));
+                        if (p.gate) {
+#pragma unroll
+                            for (int e = 0; e < 8; e++) {
+                                const size_t idx = (size_t)row * p.N + col + v + e;
+                                const float resv = p.out_bf16
+                                                       ? __bfloat162float(reinterpret_cast<const __nv_bfloat16 *>(p.residual)[idx])
+                                                       : reinterpret_cast<const float *>(p.residual)[idx];
+                                const float g = gate ? __ldg(gate + col + v + e) : 1.0f;
+                                out[e] = __fadd_rn(resv, __fmul_rn(out[e], g));
+                            }
+                        }
+                        if (p.out_bf16) {
+                            uint4 raw;
+                            __nv_bfloat162 *h = reinterpret_cast<__nv_bfloat162 *>(&raw);
+#pragma unroll
+                            for (int e = 0; e < 4; e++) h[e] = __floats2bfloat162_rn(out[2 * e], out[2 * e + 1]);
+                            *reinterpret_cast<uint4 *>(reinterpret_cast<__nv_bfloat16 *>(p.y) + (size_t)row * p.N + col + v) = raw;
+                        } else {
+                            float *dst = reinterpret_cast<float *>(p.y) + (size_t)row * p.N + col + v;
+                            *reinterpret_cast<float4 *>(dst) = make_float4(out[0], out[1], out[2], out[3]);
+                            *reinterpret_cast<float4 *>(dst + 4) = make_float4(out[4], out[5], out[6], out[7]);
+                        }
+                    }
+                }
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&tmem_empty[buf]);
+            if (*abort_word) break;
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, TMEM_COLS);
+    }
+}
+
+int launch_gemm_nvfp4(h3_cuda *cuda, const uint8_t *w_fp4, const uint8_t *sf_w, const uint8_t *x_fp4, const uint8_t *sf_x,
+                      size_t m, size_t n, size_t k, float alpha, void *y, int out_dtype, int gate, const void *residual,
+                      const float *mod, const uint32_t *row_map, size_t slots, size_t gate_slot, char *error,
+                      size_t error_size) {
+    using namespace fp4;
+    if (!cuda || !w_fp4 || !sf_w || !x_fp4 || !sf_x || !y || !m || !n || !k)
+        return fail(error, error_size, "gemm_fp4: invalid arguments");
+    if (k % 64) return fail(error, error_size, "gemm_fp4: K=%zu must be a multiple of 64", k);
+    if (n % 8) return fail(error, error_size, "gemm_fp4: N=%zu must be a multiple of 8", n);
+    if (out_dtype != H3B_F32 && out_dtype != H3B_BF16) return fail(error, error_size, "gemm_fp4: output must be f32 or bf16");
+    if (((uintptr_t)w_fp4 | (uintptr_t)x_fp4 | (uintptr_t)sf_w | (uintptr_t)sf_x | (uintptr_t)y) & 15)
+        return fail(error, error_size, "gemm_fp4: buffers must be 16-byte aligned");
+    if (gate && !residual) return fail(error, error_size, "gemm_fp4: gate epilogue needs a residual");
+    if (m > 0x7fffff00u || n > 0x7fffff00u) return fail(error, error_size, "gemm_fp4: shape too large");
+    Fp4Params p;
+    memset(&p, 0, sizeof(p));
+    int rc = h3b_encode_tmap_2d(&p.tmap_x, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, x_fp4, k / 2, m, k / 2, BK_BYTES, BM,
+                                CU_TENSOR_MAP_SWIZZLE_128B);
+    if (rc == 0)
+        rc = h3b_encode_tmap_2d(&p.tmap_w, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, w_fp4, k / 2, n, k / 2, BK_BYTES, BN,
+                                CU_TENSOR_MAP_SWIZZLE_128B);
+    if (rc != 0) return fail(error, error_size, "gemm_fp4: cuTensorMapEncodeTiled failed (%d)", rc);
+    p.sf_x = sf_x; p.sf_w = sf_w; p.M = (int)m; p.N = (int)n; p.K = (int)k;
+    p.m_tiles = (int)ceil_div(m, BM); p.n_tiles = (int)ceil_div(n, BN); p.k_blocks = (int)ceil_div(k / 2, BK_BYTES);
+    p.sf_tiles_per_rowblock = (int)(k / 64);
+    p.alpha = alpha; p.gate = gate; p.out_bf16 = out_dtype == H3B_BF16; p.y = y; p.residual = residual; p.mod = mod;
+    p.row_map = row_map; p.slots = (int)slots; p.gate_slot = (int)gate_slot; p.status = cuda->d_status;
+    H3B_CUDA_OK(cudaFuncSetAttribute(k_gemm_nvfp4, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES),
+                "gemm_fp4 smem attribute");
+    int tiles = p.m_tiles * p.n_tiles;
+    int grid = tiles < cuda->sm_count ? tiles : cuda->sm_count;
+    ProfScope prof(cuda, PROF_GEMM);
+    k_gemm_nvfp4<<<grid, THREADS, SMEM_BYTES, cuda->op_stream>>>(p);
+    cuda->launches++;
+    H3B_CUDA_OK(cudaGetLastError(), "k_gemm_nvfp4 launch");
+    return 1;
+}
+
+// bf16 accumulators [m, 2w] * scale -> SwiGLU -> f32 [m, w] (h3_gpu_cuda.cu:757-808 fp4 swiglu epilogue)
+__global__ void k_fp4_swiglu(const __nv_bfloat16 *acc, float scale, size_t rows, unsigned width, float *out) {
+    const size_t n = rows * width;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
+        const size_t r = i / width;
+        const unsigned c = (unsigned)(i - r * width);
+        const float g = __fmul_rn(scale, __bfloat162float(acc[r * 2 * width + c]));
+        const float u = __fmul_rn(scale, __bfloat162float(acc[r * 2 * width + width + c]));
+        out[i] = __fmul_rn(g / __fadd_rn(1.0f, expf(-g)), u);
+    }
+}
+
+}  // namespace h3b
+
+struct h3_cuda_nvfp4_weight {
+    h3_cuda *cuda;
+    int device;
+    size_t n, k;
+    uint8_t *d_packed, *d_sf;
+    float scale2;
+};
+
+using namespace h3b;
+
+extern "C" {
+
+size_t h3_cuda_nvfp4_gemm_scratch_bytes(size_t m, size_t n, size_t k) {
+    const size_t m_pad = (m + 127) / 128 * 128;
+    return m_pad * k / 2 + h3_cuda_nvfp4_sf_bytes(m, k) + m_pad * n * 2;
+}
+
+int h3_cuda_nvfp4_weight_create(h3_cuda *cuda, const uint8_t *packed_host, const uint8_t *sf_swizzled_host, float scale2,
+                                size_t n, size_t k, h3_cuda_nvfp4_weight **out, double *h2d_ms, char *error,
+                                size_t error_size) {
+    if (out) *out = NULL;
+    if (!cuda || !packed_host || !sf_swizzled_host || !out || !n || !k || (k % 64))
+        return fail(error, error_size, "invalid nvfp4_weight_create arguments");
+    h3_cuda_nvfp4_weight *w = (h3_cuda_nvfp4_weight *)calloc(1, sizeof(*w));
+    if (!w) return fail(error, error_size, "nvfp4_weight_create: out of memory");
+    w->cuda = cuda; w->device = cuda->device; w->n = n; w->k = k; w->scale2 = scale2;
+    const size_t sfb = h3_cuda_nvfp4_sf_bytes(n, k);
+    cudaSetDevice(cuda->device);
+    if (cudaMalloc((void **)&w->d_packed, n * k / 2) != cudaSuccess || cudaMalloc((void **)&w->d_sf, sfb) != cudaSuccess) {
+        cudaError_t e = cudaGetLastError();
+        if (w->d_packed) cudaFree(w->d_packed);
+        free(w);
+        return cuda_fail(e, "nvfp4_weight_create: device allocation", error, error_size);
+    }
+    Timer t(cuda, h2d_ms);
+    cudaMemcpyAsync(w->d_packed, packed_host, n * k / 2, cudaMemcpyHostToDevice, cuda->op_stream);
+    cudaMemcpyAsync(w->d_sf, sf_swizzled_host, sfb, cudaMemcpyHostToDevice, cuda->op_stream);
+    t.stop();
+    cudaError_t e = cudaStreamSynchronize(cuda->op_stream);   // host buffers may be released by the caller
+    if (e != cudaSuccess) {
+        cudaFree(w->d_packed);
+        cudaFree(w->d_sf);
+        free(w);
+        return cuda_fail(e, "nvfp4_weight_create: upload", error, error_size);
+    }
+    *out = w;
+    return 1;
+}
+
+int h3_cuda_nvfp4_weight_ensure_ready(h3_cuda_nvfp4_weight *w, char *error, size_t error_size) {
+    if (!w) return fail(error, error_size, "nvfp4_weight_ensure_ready: NULL weight");
+    return 1;   // uploads complete inside create
+}
+
+void h3_cuda_nvfp4_weight_free(h3_cuda *cuda, h3_cuda_nvfp4_weight *w) {
+    (void)cuda;
+    if (!w) return;
+    cudaSetDevice(w->device);
+    if (w->d_packed) cudaFree(w->d_packed);
+    if (w->d_sf) cudaFree(w->d_sf);
+    free(w);
+}
+
+const uint8_t *h3_cuda_nvfp4_weight_packed(const h3_cuda_nvfp4_weight *w) { return w ? w->d_packed : NULL; }
+const uint8_t *h3_cuda_nvfp4_weight_sf(const h3_cuda_nvfp4_weight *w) { return w ? w->d_sf : NULL; }
+float h3_cuda_nvfp4_weight_scale2(const h3_cuda_nvfp4_weight *w) { return w ? w->scale2 : 0.0f; }
+size_t h3_cuda_nvfp4_weight_n(const h3_cuda_nvfp4_weight *w) { return w ? w->n : 0; }
+size_t h3_cuda_nvfp4_weight_k(const h3_cuda_nvfp4_weight *w) { return w ? w->k : 0; }
+
+int h3_cuda_gemm_fp4_bs_dev(h3_cuda *cuda, const uint8_t *d_w_fp4, const uint8_t *d_sf_w, const uint8_t *d_x_fp4,
+                            const uint8_t *d_sf_x, size_t m, size_t n, size_t k, void *d_y_bf16, double *gemm_ms,
+                            char *error, size_t error_size) {
+    if (!cuda) return fail(error, error_size, "gemm_fp4_bs: NULL handle");
+    Timer t(cuda, gemm_ms);
+    int ok = launch_gemm_nvfp4(cuda, d_w_fp4, d_sf_w, d_x_fp4, d_sf_x, m, n, k, 1.0f, d_y_bf16, H3B_BF16, 0, NULL, NULL,
+                               NULL, 0, 0, error, error_size);
+    t.stop();
+    return ok;
+}
+
+/* Addition: general form (alpha, f32 or bf16 output, optional gate + residual). */
+int h3b_gemm_fp4_dev(h3_cuda *cuda, const uint8_t *d_w_fp4, const uint8_t *d_sf_w, const uint8_t *d_x_fp4,
+                     const uint8_t *d_sf_x, size_t m, size_t n, size_t k, float alpha, void *d_y, int out_dtype,
+                     char *error, size_t error_size) {
+    return launch_gemm_nvfp4(cuda, d_w_fp4, d_sf_w, d_x_fp4, d_sf_x, m, n, k, alpha, d_y, out_dtype, 0, NULL, NULL, NULL, 0,
+                             0, error, error_size);
+}
+
+// activation quantisation into the scratch area; returns pointers into it
+static int fp4_prepare(h3_cuda *cuda, const h3_cuda_nvfp4_weight *w, const float *d_x, size_t m, uint8_t *scratch,
+                       uint8_t **x4, uint8_t **sfx, uint8_t **acc, double *prep_ms, char *error, size_t error_size) {
+    if (!cuda || !w || !d_x || !m) return fail(error, error_size, "gemm_fp4_w_act: invalid arguments");
+    const size_t k = w->k, m_pad = (m + 127) / 128 * 128;
+    if (!scratch) {
+        if (!grow(cuda, &cuda->act_rot, &cuda->act_rot_bytes, h3_cuda_nvfp4_gemm_scratch_bytes(m, w->n, k), error, error_size))
+            return 0;
+        scratch = (uint8_t *)cuda->act_rot;
+    }
+    *x4 = scratch;
+    *sfx = scratch + m_pad * k / 2;
+    *acc = *sfx + h3_cuda_nvfp4_sf_bytes(m, k);
+    Timer t(cuda, prep_ms);
+    int ok = h3_cuda_quantize_act_nvfp4_dev(cuda, d_x, m, k, *x4, *sfx, error, error_size);
+    t.stop();
+    return ok;
+}
+
+int h3_cuda_gemm_fp4_w_act_dev(h3_cuda *cuda, const h3_cuda_nvfp4_weight *weight, const float *d_x, float act_scale,
+                               size_t m, float *d_y_f32, uint8_t *scratch, double *prep_ms, double *gemm_ms, char *error,
+                               size_t error_size, const char *tag) {
+    uint8_t *x4, *sfx, *acc;
+    (void)tag;
+    if (!d_y_f32) return fail(error, error_size, "gemm_fp4_w_act: NULL output");
+    if (!fp4_prepare(cuda, weight, d_x, m, scratch, &x4, &sfx, &acc, prep_ms, error, error_size)) return 0;
+    Timer t(cuda, gemm_ms);
+    int ok = launch_gemm_nvfp4(cuda, weight->d_packed, weight->d_sf, x4, sfx, m, weight->n, weight->k,
+                               weight->scale2 * act_scale, d_y_f32, H3B_F32, 0, NULL, NULL, NULL, 0, 0, error, error_size);
+    t.stop();
+    return ok;
+}
+
+int h3_cuda_gemm_fp4_w_act_dev_gate(h3_cuda *cuda, const h3_cuda_nvfp4_weight *weight, const float *d_x, float act_scale,
+                                    size_t m, const float *d_residual, const float *d_modulation,
+                                    const uint32_t *d_row_map, size_t slots, size_t gate_slot, const float *d_lora,
+                                    float *d_y_f32, uint8_t *scratch, double *prep_ms, double *gemm_ms, char *error,
+                                    size_t error_size, const char *tag) {
+    uint8_t *x4, *sfx, *acc;
+    (void)tag;
+    if (d_lora) return fail(error, error_size, "gemm_fp4_w_act_gate: LoRA deltas are not supported by this library");
+    if (!d_y_f32 || !d_residual || !d_modulation || !slots) return fail(error, error_size, "gemm_fp4_w_act_gate: invalid arguments");
+    if (!fp4_prepare(cuda, weight, d_x, m, scratch, &x4, &sfx, &acc, prep_ms, error, error_size)) return 0;
+    Timer t(cuda, gemm_ms);
+    int ok = launch_gemm_nvfp4(cuda, weight->d_packed, weight->d_sf, x4, sfx, m, weight->n, weight->k,
+                               weight->scale2 * act_scale, d_y_f32, H3B_F32, 1, d_residual, d_modulation, d_row_map, slots,
+                               gate_slot, error, error_size);
+    t.stop();
+    return ok;
+}
+
+int h3_cuda_gemm_fp4_w_act_dev_swiglu(h3_cuda *cuda, const h3_cuda_nvfp4_weight *weight, const float *d_x,
+                                      float act_scale, size_t m, const float *d_lora, float *d_y_f32, uint8_t *scratch,
+                                      double *prep_ms, double *gemm_ms, char *error, size_t error_size, const char *tag) {
+    uint8_t *x4, *sfx, *acc;
+    (void)tag;
+    if (d_lora) return fail(error, error_size, "gemm_fp4_w_act_swiglu: LoRA deltas are not supported by this library");
+    if (!d_y_f32 || (weight && (weight->n % 2))) return fail(error, error_size, "gemm_fp4_w_act_swiglu: invalid arguments");
+    if (!fp4_prepare(cuda, weight, d_x, m, scratch, &x4, &sfx, &acc, prep_ms, error, error_size)) return 0;
+    Timer t(cuda, gemm_ms);
+    // block-scaled GEMM to bf16 accumulators in the scratch area (as the reference does), then the SwiGLU epilogue
+    int ok = launch_gemm_nvfp4(cuda, weight->d_packed, weight->d_sf, x4, sfx, m, weight->n, weight->k, 1.0f, acc, H3B_BF16, 0,
+                               NULL, NULL, NULL, 0, 0, error, error_size);
+    if (ok) {
+        const size_t width = weight->n / 2, total = m * width;
+        size_t grid = ceil_div(total, 256);
+        if (grid > (size_t)cuda->sm_count * 16) grid = (size_t)cuda->sm_count * 16;
+        k_fp4_swiglu<<<(unsigned)grid, 256, 0, cuda->op_stream>>>((const __nv_bfloat16 *)acc, weight->scale2 * act_scale, m,
+                                                                 (unsigned)width, d_y_f32);
+        cuda->launches++;
+        if (cudaGetLastError() != cudaSuccess) ok = fail(error, error_size, "k_fp4_swiglu launch failed");
+    }
+    t.stop();
+    return ok;
+}
+
+}  // extern "C"

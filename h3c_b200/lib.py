@@ -164,6 +164,20 @@ _SIGS = {
     "h3b_dit_layers_forward_dev": (i32, (vp, C.c_uint, C.c_uint, vp, sz, vp, vp, vp, vp, sz, vp) + _ERR),
     "h3b_dit_layers_forward_f32": (i32, (vp, C.c_uint, C.c_uint, vp, vp, sz, vp, vp, vp, vp, sz, vp) + _ERR),
     "h3b_dit_launches_per_block": (i32, (vp,)),
+    "h3_cuda_gemm_fp4_bs_dev": (i32, (vp, vp, vp, vp, vp, sz, sz, sz, vp, dbl_p) + _ERR),
+    "h3b_gemm_fp4_dev": (i32, (vp, vp, vp, vp, vp, sz, sz, sz, f32, vp, i32) + _ERR),
+    "h3_cuda_nvfp4_weight_create": (i32, (vp, vp, vp, f32, sz, sz, C.POINTER(vp), dbl_p) + _ERR),
+    "h3_cuda_nvfp4_weight_ensure_ready": (i32, (vp,) + _ERR),
+    "h3_cuda_nvfp4_weight_free": (None, (vp, vp)),
+    "h3_cuda_nvfp4_weight_packed": (vp, (vp,)),
+    "h3_cuda_nvfp4_weight_sf": (vp, (vp,)),
+    "h3_cuda_nvfp4_weight_scale2": (f32, (vp,)),
+    "h3_cuda_nvfp4_weight_n": (sz, (vp,)),
+    "h3_cuda_nvfp4_weight_k": (sz, (vp,)),
+    "h3_cuda_nvfp4_gemm_scratch_bytes": (sz, (sz, sz, sz)),
+    "h3_cuda_gemm_fp4_w_act_dev": (i32, (vp, vp, vp, f32, sz, vp, vp, dbl_p, dbl_p) + _ERR + (cs,)),
+    "h3_cuda_gemm_fp4_w_act_dev_swiglu": (i32, (vp, vp, vp, f32, sz, vp, vp, vp, dbl_p, dbl_p) + _ERR + (cs,)),
+    "h3_cuda_gemm_fp4_w_act_dev_gate": (i32, (vp, vp, vp, f32, sz, vp, vp, vp, sz, sz, vp, vp, vp, dbl_p, dbl_p) + _ERR + (cs,)),
     "h3_ulysses_comm_init": (i32, (C.POINTER(UlyssesCfg), C.POINTER(i32), i32) + _ERR),
     "h3_ulysses_comm_destroy": (None, (C.POINTER(UlyssesCfg),)),
     "h3_ulysses_comm_bind": (i32, (C.POINTER(UlyssesCfg), i32, vp, vp) + _ERR),

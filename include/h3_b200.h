@@ -375,6 +375,43 @@ size_t h3_cuda_nvfp4_sf_bytes(size_t rows, size_t k);                           
 int h3_cuda_quantize_act_nvfp4_dev(h3_cuda *cuda, const float *d_x, size_t m, size_t k,
                                    uint8_t *d_x_fp4, uint8_t *d_sf, char *error,
                                    size_t error_size);                              /* :433 */
+/* Block-scaled FP4 GEMM: A = weights [n,k] packed E2M1, B = activations [m,k] packed E2M1, both with
+ * 128x4-blocked UE4M3 scales; out bf16 [m,n].  K a multiple of 64.  h3_gpu_cuda.h:424 */
+int h3_cuda_gemm_fp4_bs_dev(h3_cuda *cuda, const uint8_t *d_w_fp4, const uint8_t *d_sf_w,
+                            const uint8_t *d_x_fp4, const uint8_t *d_sf_x, size_t m, size_t n, size_t k,
+                            void *d_y_bf16, double *gemm_ms, char *error, size_t error_size);
+int h3_cuda_nvfp4_weight_create(h3_cuda *cuda, const uint8_t *packed_host,
+                                const uint8_t *sf_swizzled_host, float scale2, size_t n, size_t k,
+                                h3_cuda_nvfp4_weight **out, double *h2d_ms, char *error,
+                                size_t error_size);                                 /* :452 */
+int h3_cuda_nvfp4_weight_ensure_ready(h3_cuda_nvfp4_weight *weight, char *error, size_t error_size); /* :457 */
+void h3_cuda_nvfp4_weight_free(h3_cuda *cuda, h3_cuda_nvfp4_weight *w);             /* :459 */
+const uint8_t *h3_cuda_nvfp4_weight_packed(const h3_cuda_nvfp4_weight *w);          /* :460 */
+const uint8_t *h3_cuda_nvfp4_weight_sf(const h3_cuda_nvfp4_weight *w);              /* :461 */
+float h3_cuda_nvfp4_weight_scale2(const h3_cuda_nvfp4_weight *w);                   /* :462 */
+size_t h3_cuda_nvfp4_weight_n(const h3_cuda_nvfp4_weight *w);                       /* :463 */
+size_t h3_cuda_nvfp4_weight_k(const h3_cuda_nvfp4_weight *w);                       /* :464 */
+size_t h3_cuda_nvfp4_gemm_scratch_bytes(size_t m, size_t n, size_t k);              /* :468 */
+/* f32 activations in: NVFP4 quantise + block-scaled GEMM + epilogue (scale2 * act_scale applied to the
+ * f32 accumulator).  scratch NULL = library scratch.  d_lora must be NULL.  h3_gpu_cuda.h:480-504 */
+int h3_cuda_gemm_fp4_w_act_dev(h3_cuda *cuda, const h3_cuda_nvfp4_weight *weight, const float *d_x,
+                               float act_scale, size_t m, float *d_y_f32, uint8_t *scratch,
+                               double *prep_ms, double *gemm_ms, char *error, size_t error_size,
+                               const char *tag);
+int h3_cuda_gemm_fp4_w_act_dev_swiglu(h3_cuda *cuda, const h3_cuda_nvfp4_weight *weight, const float *d_x,
+                                      float act_scale, size_t m, const float *d_lora, float *d_y_f32,
+                                      uint8_t *scratch, double *prep_ms, double *gemm_ms, char *error,
+                                      size_t error_size, const char *tag);
+int h3_cuda_gemm_fp4_w_act_dev_gate(h3_cuda *cuda, const h3_cuda_nvfp4_weight *weight, const float *d_x,
+                                    float act_scale, size_t m, const float *d_residual,
+                                    const float *d_modulation, const uint32_t *d_row_map, size_t slots,
+                                    size_t gate_slot, const float *d_lora, float *d_y_f32,
+                                    uint8_t *scratch, double *prep_ms, double *gemm_ms, char *error,
+                                    size_t error_size, const char *tag);
+/* Addition: block-scaled GEMM with a scalar alpha and f32 or bf16 output. */
+int h3b_gemm_fp4_dev(h3_cuda *cuda, const uint8_t *d_w_fp4, const uint8_t *d_sf_w, const uint8_t *d_x_fp4,
+                     const uint8_t *d_sf_x, size_t m, size_t n, size_t k, float alpha, void *d_y,
+                     int out_dtype, char *error, size_t error_size);
 
 /* ---------------------------------------------------------- DiT block / chain */
 

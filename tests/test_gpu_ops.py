@@ -347,6 +347,48 @@ def test_quantize_act_nvfp4_exact(cuda, oracle, m, k):
     assert np.array_equal(host(sf), so)
 
 
+@pytest.mark.parametrize("m,n,k", [(128, 128, 256), (200, 384, 512), (130, 256, 3072), (64, 128, 192)])
+def test_gemm_nvfp4(cuda, oracle, m, n, k):
+    """Block-scaled FP4 GEMM against the dequantised f32 product of the same codes and scales."""
+    rng = np.random.default_rng(60 + m)
+    x = acts(rng, m, k)
+    w = rng.normal(0, 0.02, (n, k)).astype(np.float32)
+    w4, sfw = oracle.quantize_nvfp4(w, rule=1)           # the reference's weight-side quantiser
+    x4, sfx = cuda.quantize_act_nvfp4(dev(x))            # its activation-side rule, on the device
+    y = cuda.gemm_fp4(dev(w4), dev(sfw), x4, sfx, alpha=0.5)
+    cuda.check()
+    want = oracle.gemm_nvfp4(host(x4), host(sfx), w4, sfw, 0.5)
+    assert rel_l2(host(y), want) < 1e-5
+    yb = cuda.gemm_fp4(dev(w4), dev(sfw), x4, sfx, alpha=1.0, out_dtype=torch.bfloat16)
+    assert rel_l2(host(yb), oracle.gemm_nvfp4(host(x4), host(sfx), w4, sfw, 1.0)) < 3e-3
+    # quantisation itself costs a few percent against the f32 product: a sanity bound on the whole path
+    assert rel_l2(host(y), 0.5 * x @ w.T) < 0.2
+
+
+def test_reference_nvfp4_linear_entry_points(cuda, oracle):
+    rng = np.random.default_rng(61)
+    m, n, k, slots = 150, 256, 512, 6
+    x = acts(rng, m, k)
+    w = rng.normal(0, 0.02, (n, k)).astype(np.float32)
+    w4, sfw = oracle.quantize_nvfp4(w, rule=1)
+    wh = cuda.nvfp4_weight(w4, sfw, 0.75, n, k)
+    x4, sfx = oracle.quantize_nvfp4(x)
+    base = oracle.gemm_nvfp4(x4, sfx, w4, sfw, 0.75)
+    y = cuda.gemm_fp4_w_act_dev(wh, dev(x))
+    assert rel_l2(host(y), base) < 1e-5
+    res = rng.normal(0, 1, (m, n)).astype(np.float32)
+    mod = rng.normal(0, 0.5, (3, slots, n)).astype(np.float32)
+    rmap = (np.arange(m) % 3).astype(np.uint32)
+    y = cuda.gemm_fp4_w_act_dev(wh, dev(x), kind="gate", residual=dev(res), modulation=dev(mod),
+                                row_map=dev(rmap.view(np.int32)), slots=slots, gate_slot=5)
+    assert rel_l2(host(y), oracle.gate(res, base, mod, rmap, slots, 5)) < 1e-5
+    y = cuda.gemm_fp4_w_act_dev(wh, dev(x), kind="swiglu")
+    fused = oracle.bf16_round(oracle.gemm_nvfp4(x4, sfx, w4, sfw, 1.0)) * np.float32(0.75)
+    assert rel_l2(host(y), oracle.swiglu(fused)) < 2e-3   # bf16 accumulators, as in the reference's fp4 path
+    cuda.check()
+    cuda.nvfp4_weight_free(wh)
+
+
 def test_host_buffer_adaln(cuda, oracle):
     rng = np.random.default_rng(51)
     x = rng.normal(0, 1, (9, 64)).astype(np.float32)
