@@ -199,7 +199,7 @@ def reference_arm(args):
             "cpu_baseline": {"value": value, "unit": UNIT, "cores": cores, "kind": kind, "sample": desc},
             "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
             "gpu_launches": 0}
-    print(json.dumps(line))
+    OUT.emit(json.dumps(line))
 
 
 def workload_config(n_gpus):
@@ -380,7 +380,7 @@ def gpu_arm(args):
                         "d2h_bytes_per_step": int(d2h) * world},
                 "gpu_launches": int(launches) * world, "clocks": clocks, "roofline": roof, "cpu_baseline": cpu,
                 "step_tflops": (lin_all + attn_all) * geo.n_blocks / (ms_step * 1e-3) / 1e12, "kernel_classes": prof}
-        print(json.dumps(line))
+        OUT.emit(json.dumps(line))
     sync_all()
     dit.close()
     if comm is not None:
@@ -436,7 +436,26 @@ def roofline(prof, lin_flops_block, attn_flops_block, n_blocks, pk):
             "share_of_step": p["ms"] / sum(v["ms"] for v in prof.values())}
 
 
+class QuietStdout:
+    """Keeps file descriptor 1 free of library chatter (NCCL prints its version banner there): everything
+    written to stdout is sent to stderr until `emit` writes the one JSON line to the real stdout."""
+
+    def __init__(self):
+        sys.stdout.flush()
+        self.real = os.dup(1)
+        os.dup2(2, 1)
+
+    def emit(self, text):
+        sys.stdout.flush()
+        os.write(self.real, (text + "\n").encode())
+
+
+OUT = None
+
+
 def main():
+    global OUT
+    OUT = QuietStdout()
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=5)

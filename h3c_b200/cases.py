@@ -5,6 +5,8 @@ achieved TFLOP/s or GB/s.  Also the small, self-contained commands used for ncu 
     python -m h3c_b200.cases attn --lq 6144 --lk 6144 --heads 24
     python -m h3c_b200.cases norm --m 6144 --k 3072 [--plain-quant]
     python -m h3c_b200.cases rope --m 6144 --heads 24
+    python -m h3c_b200.cases gemm_fp4 --m 6144 --n 9216 --k 3072
+    python -m h3c_b200.cases peak            # tensor-pipe rate, burst and sustained
 """
 from __future__ import annotations
 
@@ -32,7 +34,7 @@ def main():
     import torch
     import h3c_b200
     ap = argparse.ArgumentParser()
-    ap.add_argument("case", choices=["gemm", "attn", "norm", "rope"])
+    ap.add_argument("case", choices=["gemm", "gemm_fp4", "attn", "norm", "rope", "peak"])
     ap.add_argument("--m", type=int, default=6144)
     ap.add_argument("--n", type=int, default=9216)
     ap.add_argument("--k", type=int, default=3072)
@@ -59,6 +61,23 @@ def main():
         res = torch.zeros_like(y) if a.epi == "gate" else None
         ms = _time(lambda: cuda.gemm_i8(w, x, s, kind=kind, residual=res, out=y), a.iters)
         out.update(m=a.m, n=a.n, k=a.k, epi=a.epi, ms=ms, tops=2.0 * a.m * a.n * a.k / ms / 1e9)
+    elif a.case == "peak":
+        import ctypes as C
+        from .lib import call
+        for kind, name in ((0, "int8"), (1, "bf16"), (2, "nvfp4")):
+            v = C.c_double(0)
+            call("h3b_umma_peak_dev", cuda.h, kind, 20000, C.byref(v))     # ~10 ms of MMAs: burst clocks
+            out[name + "_burst_tops"] = v.value
+            call("h3b_umma_peak_dev", cuda.h, kind, 2000000, C.byref(v))   # ~1 s: under the power limit
+            out[name + "_sustained_tops"] = v.value
+    elif a.case == "gemm_fp4":
+        x4 = torch.randint(0, 256, (a.m, a.k // 2), generator=g, device="cuda", dtype=torch.uint8)
+        w4 = torch.randint(0, 256, (a.n, a.k // 2), generator=g, device="cuda", dtype=torch.uint8)
+        sfb = lambda rows: int(h3c_b200.load().h3_cuda_nvfp4_sf_bytes(rows, a.k))
+        sfx = torch.full((sfb(a.m),), 0x38, device="cuda", dtype=torch.uint8)
+        sfw = torch.full((sfb(a.n),), 0x38, device="cuda", dtype=torch.uint8)
+        ms = _time(lambda: cuda.gemm_fp4(w4, sfw, x4, sfx, out_dtype=torch.bfloat16), a.iters)
+        out.update(m=a.m, n=a.n, k=a.k, ms=ms, tflops=2.0 * a.m * a.n * a.k / ms / 1e9)
     elif a.case == "attn":
         lk = a.lk or a.lq
         q = torch.randn((a.lq, a.heads, 128), generator=g, device="cuda").to(torch.bfloat16)

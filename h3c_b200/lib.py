@@ -93,6 +93,7 @@ _SIGS = {
     "h3_cuda_host_alloc": (vp, (sz, C.POINTER(i32))),
     "h3_cuda_host_free": (None, (vp, i32)),
     "h3b_cuda_check": (i32, (vp, C.POINTER(i32)) + _ERR),
+    "h3b_umma_peak_dev": (i32, (vp, i32, i32, dbl_p) + _ERR),
     "h3b_cuda_launch_count": (C.c_ulonglong, (vp, i32)),
     "h3b_cuda_profile_begin": (None, (vp,)),
     "h3b_cuda_profile_end": (i32, (vp, dbl_p, C.POINTER(i32), i32)),
