@@ -201,9 +201,20 @@ class Cuda:
         n_out = weight.n // 2 if kind == EPI_SWIGLU else weight.n
         if out is None:
             out = torch.empty((m, n_out), dtype=out_dtype, device=x_i8.device)
-        e = _l.GemmEpi(kind, _dt(out), ptr(residual), ptr(modulation), ptr(row_map), slots, gate_slot)
+        e = _l.GemmEpi(kind, _dt(out), ptr(residual), ptr(modulation), ptr(row_map), slots, gate_slot)  # rest zero
         call("h3b_gemm_i8_dev", self.h, weight.h, ptr(x_i8), ptr(act_scales), m, ptr(out), C.byref(e))
         return out
+
+    def gemm_i8_qkv_rope(self, weight: Weight, x_i8, act_scales, q_norm, k_norm, cos, sin, rope_half, eps=1e-5,
+                         round_qkv=True):
+        """QKV projection with QK-norm + RoPE in the epilogue -> (q, k, v) bf16 [m, heads, 128]."""
+        import torch
+        m, heads = x_i8.shape[0], weight.n // 384
+        q, k, v = (torch.empty((m, heads, 128), dtype=torch.bfloat16, device=x_i8.device) for _ in range(3))
+        e = _l.GemmEpi(_l.EPI_QKV_ROPE, BF16, None, None, None, 0, 0, ptr(k), ptr(v), ptr(q_norm), ptr(k_norm), ptr(cos),
+                       ptr(sin), rope_half, eps, int(round_qkv))
+        call("h3b_gemm_i8_dev", self.h, weight.h, ptr(x_i8), ptr(act_scales), m, ptr(q), C.byref(e))
+        return q, k, v
 
     def gemm_i8_dequant_f32_w_act_dev(self, weight: Weight, x_f32, convrot_gs=0, epi: _l.DitGemmEpi | None = None):
         import torch

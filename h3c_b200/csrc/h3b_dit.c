@@ -251,7 +251,8 @@ int h3b_dit_reserve(h3b_dit *d, size_t seq, size_t text_seq, char *error, size_t
 
 int h3b_dit_launches_per_block(const h3b_dit *d) {
     if (!d) return 0;
-    return d->cfg.kind == H3B_BLOCK_REFERENCE ? 10 : 17;
+    /* the QKV projection carries the QK-norm and RoPE in its epilogue */
+    return d->cfg.kind == H3B_BLOCK_REFERENCE ? 9 : 16;
 }
 
 /* rows -> (gate) -> norm -> (modulate) -> (rotate) -> int8 codes in d->q8 / d->s8 */
@@ -301,13 +302,25 @@ static int block_forward(h3b_dit *d, unsigned block, const void *d_x, size_t seq
 
     /* ---- self-attention: adaLN(0,1) -> QKV -> QK-norm + RoPE -> SDPA -> out * gate(2) + x */
     if (!norm_quant(d, d_x, dt, seq, D, b->norm1, mod, d_row_map, 0, 1, 0, d->q8, d->s8, error, error_size)) return 0;
-    if (!gemm(d, b->lin[H3B_LIN_QKV], d->q8, d->s8, seq, d->qkv, H3B_EPI_PLAIN, dt, NULL, NULL, NULL, 0, error, error_size))
-        return 0;
     if (!d->uly || !d->uly->comm) {
-        if (!h3b_qkv_rope_dev(d->cuda, d->qkv, dt, b->q_norm, b->k_norm, d_cos, d_sin, seq, d->cfg.heads,
-                              d->cfg.head_dim, d->cfg.rope_half, d->cfg.eps, 0, 1, d->q, d->k, d->v, H3B_BF16, error,
-                              error_size))
-            return 0;
+        /* QKV projection with the QK-norm and RoPE applied in the GEMM epilogue: Q, K, V leave the kernel
+         * as bf16 [seq, heads, 128]; the [seq, 3*inner] intermediate is never written */
+        if (d->cfg.rope_half == 0 || d->cfg.rope_half == 48 || d->cfg.rope_half == 64) {
+            h3b_gemm_epi e;
+            memset(&e, 0, sizeof(e));
+            e.kind = H3B_EPI_QKV_ROPE; e.out_dtype = H3B_BF16; e.d_key = d->k; e.d_value = d->v;
+            e.d_q_norm = b->q_norm; e.d_k_norm = b->k_norm; e.d_rope_cos = d_cos; e.d_rope_sin = d_sin;
+            e.rope_half = d->cfg.rope_half; e.epsilon = d->cfg.eps; e.round_qkv = dt != H3B_F32;
+            if (!h3b_gemm_i8_dev(d->cuda, b->lin[H3B_LIN_QKV], d->q8, d->s8, seq, d->q, &e, error, error_size)) return 0;
+        } else {
+            if (!gemm(d, b->lin[H3B_LIN_QKV], d->q8, d->s8, seq, d->qkv, H3B_EPI_PLAIN, dt, NULL, NULL, NULL, 0, error,
+                      error_size))
+                return 0;
+            if (!h3b_qkv_rope_dev(d->cuda, d->qkv, dt, b->q_norm, b->k_norm, d_cos, d_sin, seq, d->cfg.heads,
+                                  d->cfg.head_dim, d->cfg.rope_half, d->cfg.eps, 0, 1, d->q, d->k, d->v, H3B_BF16, error,
+                                  error_size))
+                return 0;
+        }
         if (!h3b_sdpa_bf16_dev(d->cuda, d->q, I, d->k, I, d->v, I, seq, seq, d->cfg.heads, d->cfg.head_dim, scale,
                                d->att, I, error, error_size))
             return 0;
@@ -316,6 +329,9 @@ static int block_forward(h3b_dit *d, unsigned block, const void *d_x, size_t seq
          * (real) sequence with heads/U heads, exchange back.  Both exchanges run in place. */
         const size_t U = (size_t)d->uly->ulysses, hl = d->cfg.heads / U, seq_pad = seq * U, Il = hl * d->cfg.head_dim;
         const size_t es = dt == H3B_F32 ? 4 : 2;
+        if (!gemm(d, b->lin[H3B_LIN_QKV], d->q8, d->s8, seq, d->qkv, H3B_EPI_PLAIN, dt, NULL, NULL, NULL, 0, error,
+                  error_size))
+            return 0;
         if (!h3_ulysses_a2a_qkv(d->uly, d->qkv, d->qkv, seq, d->cfg.heads, d->cfg.head_dim, (int)es, error, error_size))
             return 0;
         if (!h3b_qkv_rope_dev(d->cuda, d->qkv, dt, b->q_norm, b->k_norm, d_cos, d_sin, seq_pad, hl, d->cfg.head_dim,

@@ -49,6 +49,11 @@ struct GemmParams {
     const uint32_t *row_map;  // gate: [M] or NULL
     int slots, gate_slot;
     int *status;
+    // QKV + QK-norm + RoPE epilogue
+    void *y_k, *y_v;
+    const float *q_norm, *k_norm, *cosT, *sinT;
+    int rope_half, heads, round_qkv;
+    float eps;
 };
 
 __device__ __forceinline__ void tile_coords(int tile, int m_tiles, int n_tiles, int &mt, int &nt) {
@@ -74,6 +79,25 @@ __device__ __forceinline__ float gelu_tanh_fast(float v) {
     float inner = 0.7978845608028654f * (v + 0.044715f * v * v * v), t;
     asm("tanh.approx.f32 %0, %1;" : "=f"(t) : "f"(inner));
     return 0.5f * v * (1.0f + t);
+}
+
+// split-half RoPE on one head held in registers: dimension d pairs with d + RH
+// (h3_dit_w4a8.c:2850-2883), cos/sin rows of RH floats
+template <int RH>
+__device__ __forceinline__ void rope_split_half(float (&v)[128], const float *cr, const float *sr) {
+#pragma unroll
+    for (int d4 = 0; d4 < RH / 4; d4++) {
+        const float4 c4 = __ldg(reinterpret_cast<const float4 *>(cr) + d4);
+        const float4 s4 = __ldg(reinterpret_cast<const float4 *>(sr) + d4);
+        const float cc[4] = {c4.x, c4.y, c4.z, c4.w}, sn[4] = {s4.x, s4.y, s4.z, s4.w};
+#pragma unroll
+        for (int e = 0; e < 4; e++) {
+            const int d = d4 * 4 + e;
+            const float lo = v[d], hi = v[d + RH];
+            v[d] = __fsub_rn(__fmul_rn(lo, cc[e]), __fmul_rn(hi, sn[e]));
+            v[d + RH] = __fadd_rn(__fmul_rn(hi, cc[e]), __fmul_rn(lo, sn[e]));
+        }
+    }
 }
 
 template <typename T> struct OutTraits;
@@ -250,6 +274,55 @@ __global__ void __launch_bounds__(gemm::THREADS, 1) k_gemm_i8(const __grid_const
             bool ok = mbar_wait(&tmem_full[buf], (it >> 1) & 1, abort_word, p.status, H3B_ST_TIMEOUT_TMEM_FULL);
             tc_fence_after();
             const uint32_t t_addr = tmem_base + lane_base + (uint32_t)buf * BN;
+            if constexpr (EPI == H3B_EPI_QKV_ROPE) {
+                // This warp's 128 columns are exactly one head of Q, K or V; the thread holds its row of it.
+                const int col = c0 + half * 128;
+                if (ok && col < p.N) {
+                    const int g = col >> 7, which = g / p.heads, head = g - which * p.heads;
+                    uint32_t r[128];
+#pragma unroll
+                    for (int ch = 0; ch < 4; ch++)
+                        tmem_ld_32x32b_x32(t_addr + half * 128 + ch * 32, *reinterpret_cast<uint32_t(*)[32]>(&r[ch * 32]));
+                    tmem_ld_wait();
+                    float v[128];
+#pragma unroll
+                    for (int c4 = 0; c4 < 32; c4++) {
+                        const float4 s4 = __ldg(reinterpret_cast<const float4 *>(p.s_channel + col) + c4);
+                        const float sc[4] = {s4.x, s4.y, s4.z, s4.w};
+#pragma unroll
+                        for (int e = 0; e < 4; e++) {
+                            float val = __fmul_rn(__fmul_rn(a, sc[e]), (float)(int32_t)r[4 * c4 + e]);
+                            if (p.round_qkv) val = __bfloat162float(__float2bfloat16_rn(val));
+                            v[4 * c4 + e] = val;
+                        }
+                    }
+                    if (row_ok) {
+                        if (which < 2) {
+                            float ss = 0.0f;
+#pragma unroll
+                            for (int d = 0; d < 128; d++) ss = __fadd_rn(ss, __fmul_rn(v[d], v[d]));
+                            const float inv = 1.0f / sqrtf(ss / 128.0f + p.eps);
+                            const float *nw = which == 0 ? p.q_norm : p.k_norm;
+#pragma unroll
+                            for (int c4 = 0; c4 < 32; c4++) {
+                                const float4 n4 = __ldg(reinterpret_cast<const float4 *>(nw) + c4);
+                                v[4 * c4] = __fmul_rn(__fmul_rn(v[4 * c4], inv), n4.x);
+                                v[4 * c4 + 1] = __fmul_rn(__fmul_rn(v[4 * c4 + 1], inv), n4.y);
+                                v[4 * c4 + 2] = __fmul_rn(__fmul_rn(v[4 * c4 + 2], inv), n4.z);
+                                v[4 * c4 + 3] = __fmul_rn(__fmul_rn(v[4 * c4 + 3], inv), n4.w);
+                            }
+                            if (p.rope_half == 48)
+                                rope_split_half<48>(v, p.cosT + (size_t)row * 48, p.sinT + (size_t)row * 48);
+                            else if (p.rope_half == 64)
+                                rope_split_half<64>(v, p.cosT + (size_t)row * 64, p.sinT + (size_t)row * 64);
+                        }
+                        __nv_bfloat16 *dst = reinterpret_cast<__nv_bfloat16 *>(which == 0 ? p.y : which == 1 ? p.y_k : p.y_v) +
+                                             ((size_t)row * p.heads + head) * 128;
+#pragma unroll
+                        for (int d = 0; d < 128; d += 8) OutTraits<__nv_bfloat16>::store(dst + d, &v[d]);
+                    }
+                }
+            } else
             if (ok) {
 #pragma unroll 1
                 for (int i = 0; i < CHUNKS; i++) {
@@ -403,6 +476,22 @@ int launch_gemm_i8(h3_cuda *cuda, const h3_cuda_w4a8_weight *w, const int8_t *x,
         if (!epi->d_residual) return fail(error, error_size, "gemm_i8: gate epilogue needs a residual");
         if (epi->d_modulation && epi->slots == 0) return fail(error, error_size, "gemm_i8: gate epilogue needs slots > 0");
         if (reinterpret_cast<uintptr_t>(epi->d_residual) & 15) return fail(error, error_size, "gemm_i8: residual must be 16-byte aligned");
+    }
+    if (epi->kind == H3B_EPI_QKV_ROPE) {
+        if (epi->out_dtype != H3B_BF16) return fail(error, error_size, "gemm_i8: the QKV+RoPE epilogue writes bf16");
+        if (N % 384) return fail(error, error_size, "gemm_i8: QKV+RoPE needs N = 3 * heads * 128 (N=%zu)", N);
+        if (!epi->d_key || !epi->d_value || !epi->d_q_norm || !epi->d_k_norm)
+            return fail(error, error_size, "gemm_i8: QKV+RoPE needs key/value outputs and q/k norm weights");
+        if (epi->rope_half != 0 && epi->rope_half != 48 && epi->rope_half != 64)
+            return fail(error, error_size, "gemm_i8: QKV+RoPE supports rope_half 0, 48 or 64 (got %zu)", epi->rope_half);
+        if (epi->rope_half && (!epi->d_rope_cos || !epi->d_rope_sin)) return fail(error, error_size, "gemm_i8: rope tables missing");
+        if (((uintptr_t)epi->d_key | (uintptr_t)epi->d_value | (uintptr_t)epi->d_q_norm | (uintptr_t)epi->d_k_norm |
+             (uintptr_t)epi->d_rope_cos | (uintptr_t)epi->d_rope_sin) & 15)
+            return fail(error, error_size, "gemm_i8: QKV+RoPE tensors must be 16-byte aligned");
+        p.y_k = epi->d_key; p.y_v = epi->d_value; p.q_norm = epi->d_q_norm; p.k_norm = epi->d_k_norm;
+        p.cosT = epi->d_rope_cos; p.sinT = epi->d_rope_sin; p.rope_half = (int)epi->rope_half;
+        p.heads = (int)(N / 384); p.eps = epi->epsilon; p.round_qkv = epi->round_qkv;
+        return gemm_launch_t<H3B_EPI_QKV_ROPE, __nv_bfloat16>(cuda, p, error, error_size);
     }
     switch (epi->kind) {
     case H3B_EPI_PLAIN:

@@ -13,7 +13,7 @@ HERE = Path(__file__).resolve().parent
 LIB_PATH = HERE / "libh3_b200.so"
 
 F32, BF16, F16, I32 = 0, 1, 2, 3
-EPI_PLAIN, EPI_GATE, EPI_SWIGLU, EPI_GELU = 0, 1, 2, 3
+EPI_PLAIN, EPI_GATE, EPI_SWIGLU, EPI_GELU, EPI_QKV_ROPE = 0, 1, 2, 3, 4
 ERR_LEN = 512
 
 vp = C.c_void_p
@@ -43,7 +43,8 @@ class DitGemmEpi(C.Structure):  # h3_cuda_dit_gemm_epi, the reference's epilogue
 
 class GemmEpi(C.Structure):  # h3b_gemm_epi
     _fields_ = [("kind", i32), ("out_dtype", i32), ("d_residual", vp), ("d_modulation", vp), ("d_row_map", vp),
-                ("slots", sz), ("gate_slot", sz)]
+                ("slots", sz), ("gate_slot", sz), ("d_key", vp), ("d_value", vp), ("d_q_norm", vp), ("d_k_norm", vp),
+                ("d_rope_cos", vp), ("d_rope_sin", vp), ("rope_half", sz), ("epsilon", f32), ("round_qkv", i32)]
 
 
 class NormArgs(C.Structure):  # h3b_norm_args

@@ -231,7 +231,10 @@ enum {            /* epilogue kinds */
     H3B_EPI_PLAIN = 0,   /* y = a[m] s[n] acc                                         */
     H3B_EPI_GATE = 1,    /* y = residual + (a s acc) * gate[row_map[m]][slot][n]; gate NULL -> 1 */
     H3B_EPI_SWIGLU = 2,  /* y[m,c] = silu(g) * u, g = col c, u = col n/2 + c           */
-    H3B_EPI_GELU = 3     /* y = gelu_tanh(a s acc)                                     */
+    H3B_EPI_GELU = 3,    /* y = gelu_tanh(a s acc)                                     */
+    H3B_EPI_QKV_ROPE = 4 /* QKV projection: columns are [Q | K | V] x heads x 128; per head apply the QK RMS-norm and
+                            split-half RoPE of h3_dit_w4a8_qkv_rope_f32 (h3_dit_w4a8.c:2805) and write
+                            Q / K / V [m, heads, 128] (d_y = Q, d_key, d_value), bf16 */
 };
 typedef struct h3b_gemm_epi {
     int kind;                    /* H3B_EPI_* */
@@ -240,6 +243,14 @@ typedef struct h3b_gemm_epi {
     const float *d_modulation;   /* gate: [mod_rows, slots, n] or NULL */
     const uint32_t *d_row_map;   /* gate: [m] or NULL (identity) */
     size_t slots, gate_slot;
+    /* H3B_EPI_QKV_ROPE only */
+    void *d_key, *d_value;       /* with d_y = query */
+    const float *d_q_norm, *d_k_norm;     /* [128] */
+    const float *d_rope_cos, *d_rope_sin; /* [m, rope_half]; NULL with rope_half = 0 */
+    size_t rope_half;            /* <= 64 */
+    float epsilon;
+    int round_qkv;               /* 1: round the projection to out_dtype before the norm (what a stored
+                                    intermediate would have been) */
 } h3b_gemm_epi;
 /* d_x_i8 [m,k] codes, d_act_scales [m]; d_y is [m,n] ([m,n/2] for swiglu). */
 int h3b_gemm_i8_dev(h3_cuda *cuda, const h3_cuda_w4a8_weight *weight, const int8_t *d_x_i8,

@@ -221,6 +221,33 @@ def test_gemm_epilogues(cuda, oracle):
     cuda.check()
 
 
+def test_gemm_qkv_rope_epilogue(cuda, oracle):
+    """QKV projection with the QK-norm and split-half RoPE fused into the GEMM epilogue, against the oracle
+    chain dequant -> (round to bf16) -> h3_dit_w4a8_qkv_rope_f32."""
+    rng = np.random.default_rng(33)
+    heads, hd, k = 3, 128, 256
+    pt, ph, pw = oracle.fill_video_pos(16, 5, 8, 12)
+    inv_freq = (1.0 / (10000.0 ** (np.arange(16) / 16.0))).astype(np.float32)
+    cos, sin = oracle.rope_tables(inv_freq, pt, ph, pw, 1.0)
+    m = len(pt)   # 120 rows: not a multiple of the row tile
+    w, w_i8, s = make_weight(cuda, rng, 3 * heads * hd, k)
+    xq, xs = oracle.quantize_act_int8(acts(rng, m, k))
+    qn, kn = rng.normal(1, 0.1, hd).astype(np.float32), rng.normal(1, 0.1, hd).astype(np.float32)
+    qkv = oracle.gemm_i8_dequant(xq, w_i8, xs, s)
+    for rope_half, rnd in ((48, True), (48, False), (0, True), (64, True)):
+        c, sn = (cos, sin) if rope_half == 48 else (np.ones((m, 64), np.float32), np.zeros((m, 64), np.float32))
+        c, sn = (None, None) if rope_half == 0 else (c, sn)
+        q, kk, v = cuda.gemm_i8_qkv_rope(w, dev(xq), dev(xs), dev(qn), dev(kn), None if c is None else dev(c),
+                                         None if sn is None else dev(sn), rope_half, round_qkv=rnd)
+        cuda.check()
+        src = oracle.bf16_round(qkv) if rnd else qkv
+        qo, ko, vo = oracle.qkv_rope(src, qn, kn, c, sn, heads, hd, rope_half)
+        # the thread-sequential sum of squares is the oracle's own order: outputs agree to bf16 rounding
+        assert rel_l2(host(q), qo) < 3e-3 and rel_l2(host(kk), ko) < 3e-3
+        assert np.array_equal(host(v), oracle.bf16_round(vo))
+        assert np.mean(host(q) != oracle.bf16_round(qo)) < 2e-3
+
+
 def test_reference_linear_entry_point(cuda, oracle):
     """h3_cuda_gemm_i8_dequant_f32_w_act_dev(_epi): f32 activations in, ConvRot + quant + GEMM inside."""
     from h3c_b200.lib import DitGemmEpi
