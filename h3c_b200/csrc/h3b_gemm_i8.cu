@@ -1,11 +1,15 @@
 // INT8 x INT8 -> INT32 GEMM on the 5th-generation tensor cores (tcgen05, kind::i8)
 // with the DiT epilogues fused:  Y = epi( a[m] * s[n] * sum_k X[m,k] W[n,k] ).
 //
-// Persistent kernel, one CTA per SM, 128 x 256 output tile, K in 128-byte blocks:
-//   warp 0     TMA producer: A (activation codes) and B (weight) tiles into a
-//              4-stage shared-memory ring, 128-byte swizzle
-//   warp 1     MMA issuer: four 128x256x32 tcgen05.mma per stage into one of two
-//              256-column TMEM accumulators; tcgen05.commit frees the stage
+// Persistent kernel, one CTA per SM, K in 128-byte blocks.  Two tile shapes:
+//   CTAS = 2   a pair of CTAs (cluster of two SMs) computes a 256 x 256 tile with cta_group::2 MMAs:
+//              each CTA loads its own 128 rows of A and HALF of the B tile (32 KiB per stage instead
+//              of 48), which lowers the L2 -> shared-memory traffic per MMA by a third; six stages
+//   CTAS = 1   one CTA computes a 128 x 256 tile (four stages); used when M <= 128
+//   warp 0     TMA producer: A (activation codes) and B (weight) tiles into the
+//              shared-memory ring, 128-byte swizzle
+//   warp 1     MMA issuer (of the even CTA of a pair): four K=32 tcgen05.mma per stage into one of
+//              two 256-column TMEM accumulators; tcgen05.commit frees the stage in both CTAs
 //   warps 2-9  epilogue: tcgen05.ld the finished accumulator (one output row and half of the
 //              tile's columns per thread), scale, apply gate+residual / SwiGLU / tanh-GELU,
 //              store.  Runs while the MMA warp fills the other accumulator.
@@ -14,6 +18,8 @@
 // reference's operation order (a * s) * (float)acc and h3_dit_fused_epi.h:87-141.
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
+
+#include <stdlib.h>
 
 #include "h3b_internal.h"
 #include "h3b_ptx.cuh"
@@ -24,14 +30,17 @@ namespace gemm {
 constexpr int BM = 128;          // rows of X per tile
 constexpr int BN = 256;          // rows of W per tile (TMEM columns per accumulator)
 constexpr int BK = 128;          // int8 elements (= bytes) of K per stage
-constexpr int STAGES = 4;
 constexpr int A_BYTES = BM * BK;             // 16 KiB
-constexpr int B_BYTES = BN * BK;             // 32 KiB
-constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
 constexpr int THREADS = 320;
 constexpr int TMEM_COLS = 512;
 constexpr int GROUP_M = 8;       // rasterisation: bands of 8 row-tiles share the weight tiles in L2
-constexpr size_t SMEM_BYTES = 1024 /*alignment slack*/ + (size_t)STAGES * STAGE_BYTES + 256;
+template <int CTAS> struct Shape {
+    static constexpr int STAGES = CTAS == 2 ? 6 : 4;
+    static constexpr int B_BYTES = BN * BK / CTAS;          // B rows held by one CTA: 32 KiB or 16 KiB
+    static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;   // per CTA
+    static constexpr int TILE_M = BM * CTAS;
+    static constexpr size_t SMEM_BYTES = 1024 /*alignment slack*/ + (size_t)STAGES * STAGE_BYTES + 256;
+};
 }  // namespace gemm
 
 struct GemmParams {
@@ -153,9 +162,11 @@ template <> struct OutTraits<int32_t> {
     __device__ static void load(const int32_t *p, float *v) { (void)p; (void)v; }
 };
 
-template <int EPI, typename OutT>
+template <int EPI, typename OutT, int CTAS>
 __global__ void __launch_bounds__(gemm::THREADS, 1) k_gemm_i8(const __grid_constant__ GemmParams p) {
     using namespace gemm;
+    constexpr int STAGES = Shape<CTAS>::STAGES, STAGE_BYTES = Shape<CTAS>::STAGE_BYTES,
+                  B_BYTES = Shape<CTAS>::B_BYTES, TILE_M = Shape<CTAS>::TILE_M;
     extern __shared__ uint8_t smem_raw[];
     // 1024-byte alignment: required by the 128-byte swizzle pattern of TMA and the MMA descriptors
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
@@ -166,6 +177,10 @@ __global__ void __launch_bounds__(gemm::THREADS, 1) k_gemm_i8(const __grid_const
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int total_tiles = p.m_tiles * p.n_tiles;
+    // A pair walks the tile list together; cta_rank selects this CTA's rows of A, half of B and rows of Y.
+    const int cta_rank = CTAS == 2 ? (int)cluster_ctarank() : 0;
+    const int first_tile = CTAS == 2 ? (int)(blockIdx.x >> 1) : (int)blockIdx.x;
+    const int tile_step = CTAS == 2 ? (int)(gridDim.x >> 1) : (int)gridDim.x;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; s++) {
@@ -174,7 +189,7 @@ __global__ void __launch_bounds__(gemm::THREADS, 1) k_gemm_i8(const __grid_const
         }
         for (int b = 0; b < 2; b++) {
             mbar_init(&tmem_full[b], 1);
-            mbar_init(&tmem_empty[b], 8);   // one arrival per epilogue warp
+            mbar_init(&tmem_empty[b], 8 * CTAS);   // one arrival per epilogue warp of every CTA of the pair
         }
         *abort_word = 0;
         mbar_fence_init();
@@ -182,11 +197,17 @@ __global__ void __launch_bounds__(gemm::THREADS, 1) k_gemm_i8(const __grid_const
         tma_prefetch_desc(&p.tmap_b);
     }
     if (warp == 1) {
-        tmem_alloc(tmem_slot, TMEM_COLS);
-        tmem_relinquish();
+        if (CTAS == 2) {
+            tmem_alloc_pair(tmem_slot, TMEM_COLS);
+            tmem_relinquish_pair();
+        } else {
+            tmem_alloc(tmem_slot, TMEM_COLS);
+            tmem_relinquish();
+        }
     }
     tc_fence_before();
-    __syncthreads();
+    if (CTAS == 2) cluster_sync_all();   // the peer's barriers must exist before anything signals them
+    else __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
 
@@ -195,20 +216,30 @@ __global__ void __launch_bounds__(gemm::THREADS, 1) k_gemm_i8(const __grid_const
         if (lane == 0) {
             int s = 0;
             uint32_t ph = 0;
-            for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
+            for (int tile = first_tile; tile < total_tiles; tile += tile_step) {
                 int mt, nt;
                 tile_coords(tile, p.m_tiles, p.n_tiles, mt, nt);
-                const int m0 = mt * BM;
+                const int m0 = mt * TILE_M + cta_rank * BM;
                 const int n0 = p.swiglu ? nt * (BN / 2) : nt * BN;
                 const int n1 = p.swiglu ? p.N / 2 + n0 : n0 + BN / 2;
                 for (int kb = 0; kb < p.k_blocks; kb++) {
                     if (!mbar_wait(&empty[s], ph ^ 1, abort_word, p.status, H3B_ST_TIMEOUT_EMPTY)) break;
                     uint8_t *a_dst = smem + (size_t)s * STAGE_BYTES;
                     uint8_t *b_dst = a_dst + A_BYTES;
-                    mbar_expect_tx(&full[s], STAGE_BYTES);
-                    tma_load_2d(a_dst, &p.tmap_a, &full[s], kb * BK, m0);
-                    tma_load_2d(b_dst, &p.tmap_b, &full[s], kb * BK, n0);
-                    tma_load_2d(b_dst + B_BYTES / 2, &p.tmap_b, &full[s], kb * BK, n1);
+                    if (CTAS == 2) {
+                        // Both CTAs' loads are counted on the even CTA's barrier, which expects the bytes of
+                        // both.  A stage is refilled only after the MMAs that read it have completed, i.e.
+                        // after that barrier has moved on to the phase these loads belong to.
+                        const uint32_t bar = mapa_shared(smem_u32(&full[s]), 0);
+                        if (cta_rank == 0) mbar_expect_tx(&full[s], 2 * STAGE_BYTES);
+                        tma_load_2d_pair(a_dst, &p.tmap_a, bar, kb * BK, m0);
+                        tma_load_2d_pair(b_dst, &p.tmap_b, bar, kb * BK, cta_rank == 0 ? n0 : n1);
+                    } else {
+                        mbar_expect_tx(&full[s], STAGE_BYTES);
+                        tma_load_2d(a_dst, &p.tmap_a, &full[s], kb * BK, m0);
+                        tma_load_2d(b_dst, &p.tmap_b, &full[s], kb * BK, n0);
+                        tma_load_2d(b_dst + B_BYTES / 2, &p.tmap_b, &full[s], kb * BK, n1);
+                    }
                     if (++s == STAGES) { s = 0; ph ^= 1; }
                 }
                 if (*abort_word) break;
@@ -217,12 +248,12 @@ __global__ void __launch_bounds__(gemm::THREADS, 1) k_gemm_i8(const __grid_const
         __syncwarp();
     } else if (warp == 1) {
         // --------------------------------------------------------- MMA issuer
-        if (lane == 0) {
-            constexpr uint32_t idesc = umma_idesc(2 /*s32*/, 1 /*s8*/, 1 /*s8*/, BM, BN, 0, 0);
+        if (lane == 0 && cta_rank == 0) {
+            constexpr uint32_t idesc = umma_idesc(2 /*s32*/, 1 /*s8*/, 1 /*s8*/, TILE_M, BN, 0, 0);
             int s = 0;
             uint32_t ph = 0;
             int it = 0;
-            for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, it++) {
+            for (int tile = first_tile; tile < total_tiles; tile += tile_step, it++) {
                 const int buf = it & 1;
                 if (!mbar_wait(&tmem_empty[buf], ((it >> 1) & 1) ^ 1, abort_word, p.status, H3B_ST_TIMEOUT_TMEM_EMPTY))
                     break;
@@ -235,14 +266,22 @@ __global__ void __launch_bounds__(gemm::THREADS, 1) k_gemm_i8(const __grid_const
                     const uint64_t a_desc = umma_desc_k_sw128(a_addr);
                     const uint64_t b_desc = umma_desc_k_sw128(a_addr + A_BYTES);
 #pragma unroll
-                    for (int k = 0; k < BK / 32; k++)
-                        umma_i8_ss(d_tmem, a_desc + (uint64_t)(k * 2), b_desc + (uint64_t)(k * 2), idesc,
-                                   (uint32_t)((kb | k) != 0));
-                    tc_commit(&empty[s]);   // stage is free once these MMAs have read it
+                    for (int k = 0; k < BK / 32; k++) {
+                        if (CTAS == 2)
+                            umma_i8_ss_pair(d_tmem, a_desc + (uint64_t)(k * 2), b_desc + (uint64_t)(k * 2), idesc,
+                                            (uint32_t)((kb | k) != 0));
+                        else
+                            umma_i8_ss(d_tmem, a_desc + (uint64_t)(k * 2), b_desc + (uint64_t)(k * 2), idesc,
+                                       (uint32_t)((kb | k) != 0));
+                    }
+                    // the stage is free (in both CTAs) once these MMAs have read it
+                    if (CTAS == 2) tc_commit_pair(&empty[s], 3);
+                    else tc_commit(&empty[s]);
                     if (++s == STAGES) { s = 0; ph ^= 1; }
                 }
                 if (*abort_word) break;
-                tc_commit(&tmem_full[buf]);
+                if (CTAS == 2) tc_commit_pair(&tmem_full[buf], 3);
+                else tc_commit(&tmem_full[buf]);
             }
         }
         __syncwarp();
@@ -258,11 +297,11 @@ __global__ void __launch_bounds__(gemm::THREADS, 1) k_gemm_i8(const __grid_const
         constexpr int VEC = OutTraits<OutT>::VEC;
         constexpr int CHUNKS = (EPI == H3B_EPI_SWIGLU) ? (BN / 2) / 64 : BN / 64;   // per warp
         int it = 0;
-        for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, it++) {
+        for (int tile = first_tile; tile < total_tiles; tile += tile_step, it++) {
             int mt, nt;
             tile_coords(tile, p.m_tiles, p.n_tiles, mt, nt);
             const int buf = it & 1;
-            const int row = mt * BM + q * 32 + lane;
+            const int row = mt * TILE_M + cta_rank * BM + q * 32 + lane;
             const bool row_ok = row < p.M;
             const int c0 = (EPI == H3B_EPI_SWIGLU) ? nt * (BN / 2) : nt * BN;   // first output column
             const float a = row_ok ? p.act_scale[row] : 0.0f;
@@ -406,35 +445,83 @@ __global__ void __launch_bounds__(gemm::THREADS, 1) k_gemm_i8(const __grid_const
             // hand the accumulator back to the MMA warp
             tc_fence_before();
             __syncwarp();
-            if (lane == 0) mbar_arrive(&tmem_empty[buf]);
+            if (lane == 0) {
+                if (CTAS == 2) mbar_arrive_cluster(mapa_shared(smem_u32(&tmem_empty[buf]), 0));
+                else mbar_arrive(&tmem_empty[buf]);
+            }
             if (*abort_word) break;
         }
     }
 
     tc_fence_before();
-    __syncthreads();
+    // A pair leaves together: neither CTA may exit while the other can still signal its barriers,
+    // read its shared memory or write its tensor memory.
+    if (CTAS == 2) cluster_sync_all();
+    else __syncthreads();
     if (warp == 1) {
         tc_fence_after();
-        tmem_dealloc(tmem_base, TMEM_COLS);
+        if (CTAS == 2) tmem_dealloc_pair(tmem_base, TMEM_COLS);
+        else tmem_dealloc(tmem_base, TMEM_COLS);
     }
 }
 
 template <int EPI, typename OutT>
-static int gemm_launch_t(h3_cuda *cuda, const GemmParams &p, char *error, size_t error_size) {
-    auto kern = k_gemm_i8<EPI, OutT>;
-    H3B_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)gemm::SMEM_BYTES),
+static int gemm_launch_t(h3_cuda *cuda, GemmParams &p, char *error, size_t error_size) {
+    using namespace gemm;
+    // CTA pairs whenever there is more than one 128-row band (H3B_GEMM_PAIRS=0 keeps single CTAs)
+    static const bool pairs_allowed = [] {
+        const char *e = getenv("H3B_GEMM_PAIRS");
+        return !(e && e[0] == '0');
+    }();
+    if (pairs_allowed && p.M > BM) {
+        auto kern = k_gemm_i8<EPI, OutT, 2>;
+        constexpr size_t smem = Shape<2>::SMEM_BYTES;
+        // co-resident pairs on this device (an SM without a free neighbour cannot host half a pair);
+        // asked once per kernel and device
+        static int max_pairs[64];
+        const int dev = cuda->device & 63;
+        cudaLaunchConfig_t cfg;
+        memset(&cfg, 0, sizeof(cfg));
+        cudaLaunchAttribute attr;
+        attr.id = cudaLaunchAttributeClusterDimension;
+        attr.val.clusterDim.x = 2; attr.val.clusterDim.y = 1; attr.val.clusterDim.z = 1;
+        cfg.blockDim = dim3(THREADS);
+        cfg.dynamicSmemBytes = smem;
+        cfg.stream = cuda->op_stream;
+        cfg.attrs = &attr;
+        cfg.numAttrs = 1;
+        if (max_pairs[dev] == 0) {
+            H3B_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem),
+                        "gemm smem attribute");
+            cfg.gridDim = dim3((unsigned)(cuda->sm_count & ~1));
+            int n = 0;
+            H3B_CUDA_OK(cudaOccupancyMaxActiveClusters(&n, kern, &cfg), "gemm cluster occupancy");
+            if (n < 1) return fail(error, error_size, "gemm_i8: no CTA pair fits on this device");
+            max_pairs[dev] = n;
+        }
+        p.m_tiles = (p.M + Shape<2>::TILE_M - 1) / Shape<2>::TILE_M;
+        const int tiles = p.m_tiles * p.n_tiles;
+        const int n_pairs = tiles < max_pairs[dev] ? tiles : max_pairs[dev];
+        cfg.gridDim = dim3((unsigned)(2 * n_pairs));
+        ProfScope prof(cuda, PROF_GEMM);
+        H3B_CUDA_OK(cudaLaunchKernelEx(&cfg, kern, p), "k_gemm_i8 pair launch");
+        cuda->launches++;
+        return 1;
+    }
+    auto kern = k_gemm_i8<EPI, OutT, 1>;
+    H3B_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Shape<1>::SMEM_BYTES),
                 "gemm smem attribute");
     int tiles = p.m_tiles * p.n_tiles;
     int grid = tiles < cuda->sm_count ? tiles : cuda->sm_count;
     ProfScope prof(cuda, PROF_GEMM);
-    kern<<<grid, gemm::THREADS, gemm::SMEM_BYTES, cuda->op_stream>>>(p);
+    kern<<<grid, THREADS, Shape<1>::SMEM_BYTES, cuda->op_stream>>>(p);
     cuda->launches++;
     H3B_CUDA_OK(cudaGetLastError(), "k_gemm_i8 launch");
     return 1;
 }
 
 template <int EPI>
-static int gemm_launch_e(h3_cuda *cuda, const GemmParams &p, int out_dtype, char *error, size_t error_size) {
+static int gemm_launch_e(h3_cuda *cuda, GemmParams &p, int out_dtype, char *error, size_t error_size) {
     switch (out_dtype) {
     case H3B_F32: return gemm_launch_t<EPI, float>(cuda, p, error, error_size);
     case H3B_BF16: return gemm_launch_t<EPI, __nv_bfloat16>(cuda, p, error, error_size);

@@ -172,8 +172,9 @@ def make_weight(cuda, rng, n, k):
 
 
 @pytest.mark.parametrize("m,n,k", [(1, 128, 128), (127, 256, 256), (129, 384, 512), (300, 640, 3072),
-                                   (16, 256, 144), (257, 24, 64)])
+                                   (16, 256, 144), (257, 24, 64), (1000, 1280, 1024)])
 def test_gemm_int32_accumulators_exact(cuda, m, n, k):
+    """m <= 128 runs the single-CTA tile, larger m the CTA-pair (256 x 256) tile."""
     import h3c_b200
     rng = np.random.default_rng(20 + m)
     w, w_i8, _ = make_weight(cuda, rng, n, k)
@@ -184,10 +185,11 @@ def test_gemm_int32_accumulators_exact(cuda, m, n, k):
     assert np.array_equal(host(acc), x.astype(np.int32) @ w_i8.astype(np.int32).T)
 
 
-def test_gemm_epilogues(cuda, oracle):
+@pytest.mark.parametrize("m", [200, 96])   # CTA-pair tile, single-CTA tile
+def test_gemm_epilogues(cuda, oracle, m):
     import h3c_b200
     rng = np.random.default_rng(30)
-    m, n, k, slots = 200, 512, 256, 6
+    n, k, slots = 512, 256, 6
     w, w_i8, s = make_weight(cuda, rng, n, k)
     x = acts(rng, m, k)
     xq, xs = oracle.quantize_act_int8(x)
