@@ -115,7 +115,11 @@ __global__ void __launch_bounds__(attn::THREADS, 1) k_attn_bf16(const __grid_con
         }
         __syncwarp();
     } else if (warp == 1) {
-        if (lane == 0) {
+        // The whole warp walks the loop, converged, so that descriptor arithmetic stays in uniform
+        // registers; one elected lane issues each tcgen05 instruction.  (With a single active lane the
+        // operands cross from vector to uniform registers per instruction, which cost about 85 cycles per
+        // MMA against the 64 the MMA itself takes.)
+        {
             // S = Q K^T : both operands K-major in shared memory (d contiguous).
             // O += P V  : P from TMEM (row = lane, two bf16 keys per 32-bit column); V as stored
             //             ([key][d], d contiguous) is the N-major form of the B operand.
@@ -127,16 +131,17 @@ __global__ void __launch_bounds__(attn::THREADS, 1) k_attn_bf16(const __grid_con
 #pragma unroll
                 for (int k = 0; k < HD / 16; k++) {
                     const uint32_t off = (uint32_t)(k >> 2) * SLAB + (uint32_t)(k & 3) * 32;
-                    umma_f16_ss(d_tmem, umma_desc_k_sw128(q_addr + off), umma_desc_k_sw128(k_addr + off), idesc_s,
-                                (uint32_t)(k != 0));
+                    if (elect_one())
+                        umma_f16_ss(d_tmem, umma_desc_k_sw128(q_addr + off), umma_desc_k_sw128(k_addr + off), idesc_s,
+                                    (uint32_t)(k != 0));
                 }
-                tc_commit(&s_full[t]);
+                if (elect_one()) tc_commit(&s_full[t]);
             };
             auto issue_pv = [&](int t, int j) {
                 const uint32_t v_addr = smem_u32(sV + (j & 1) * TILE);
 #pragma unroll
                 for (int k = 0; k < BKV / 16; k++)
-                    umma_f16_ts(tmem_base + O_COL + 128u * t, tmem_base + S_COL + 128u * t + (uint32_t)k * 8,
+                    if (elect_one()) umma_f16_ts(tmem_base + O_COL + 128u * t, tmem_base + S_COL + 128u * t + (uint32_t)k * 8,
                                 umma_desc_mn_sw128(v_addr + (uint32_t)k * 2048, SLAB, 1024), idesc_o,
                                 (uint32_t)((j | k) != 0));
             };
@@ -145,7 +150,7 @@ __global__ void __launch_bounds__(attn::THREADS, 1) k_attn_bf16(const __grid_con
             if (ok) {
                 tc_fence_after();
                 for (int t = 0; t < n_tiles; t++) issue_s(t, 0);
-                tc_commit(&k_empty[0]);
+                if (elect_one()) tc_commit(&k_empty[0]);
             }
             for (int j = 0; ok && j < n_kv; j++) {
                 const int st = j & 1, nx = (j + 1) & 1;
@@ -158,14 +163,14 @@ __global__ void __launch_bounds__(attn::THREADS, 1) k_attn_bf16(const __grid_con
                     if (!ok) break;
                     tc_fence_after();
                     issue_pv(t, j);
-                    if (t == n_tiles - 1) tc_commit(&v_empty[st]);
+                    if (t == n_tiles - 1 && elect_one()) tc_commit(&v_empty[st]);
                     if (more) {
                         issue_s(t, j + 1);   // overwrites the tile's scores / P, in order after the P V product
-                        if (t == n_tiles - 1) tc_commit(&k_empty[nx]);
+                        if (t == n_tiles - 1 && elect_one()) tc_commit(&k_empty[nx]);
                     }
                 }
             }
-            tc_commit(o_done);
+            if (elect_one()) tc_commit(o_done);
         }
         __syncwarp();
     } else {

@@ -15,7 +15,9 @@ __device__ __forceinline__ void umma_nvfp4_probe(uint32_t d_tmem, uint64_t a_des
         : "memory");
 }
 
-// KIND 0: int8 128x256x32, 1: bf16 128x256x16, 2: nvfp4 128x256x64 (zero scales)
+// KIND 0: int8 128x256x32, 1: bf16 128x256x16, 2: nvfp4 128x256x64 (zero scales),
+// 3: bf16 128x128x16, both operands K-major in shared memory (the attention score product),
+// 4: bf16 128x128x16, A from tensor memory, B MN-major (the attention P V product)
 template <int KIND>
 __global__ void __launch_bounds__(128, 1) k_umma_peak(int iters, int *status) {
     extern __shared__ uint8_t smem_raw[];
@@ -44,13 +46,18 @@ __global__ void __launch_bounds__(128, 1) k_umma_peak(int iters, int *status) {
         const uint32_t a_addr = smem_u32(smem), b_addr = a_addr + 16384;
         constexpr uint32_t idesc = KIND == 0   ? umma_idesc(2, 1, 1, 128, 256, 0, 0)
                                    : KIND == 1 ? umma_idesc(1, 1, 1, 128, 256, 0, 0)
+                                   : KIND == 3 ? umma_idesc(1, 1, 1, 128, 128, 0, 0)
+                                   : KIND == 4 ? umma_idesc(1, 1, 1, 128, 128, 0, 1)
                                                : ((1u << 7) | (1u << 10) | ((256u >> 3) << 17) | ((128u >> 4) << 24));
         for (int it = 0; it < iters; it++) {
 #pragma unroll
             for (int k = 0; k < 4; k++) {
                 const uint64_t ad = umma_desc_k_sw128(a_addr + k * 32), bd = umma_desc_k_sw128(b_addr + k * 32);
                 if (KIND == 0) umma_i8_ss(tmem_base, ad, bd, idesc, 1);
-                else if (KIND == 1) umma_f16_ss(tmem_base, ad, bd, idesc, 1);
+                else if (KIND == 1 || KIND == 3) umma_f16_ss(tmem_base, ad, bd, idesc, 1);
+                else if (KIND == 4)
+                    umma_f16_ts(tmem_base, tmem_base + 256 + k * 8, umma_desc_mn_sw128(b_addr + k * 2048, 16384, 1024),
+                                idesc, 1);
                 else umma_nvfp4_probe(tmem_base, ad, bd, idesc, tmem_base + 256, tmem_base + 272, 1);
             }
         }
@@ -71,11 +78,11 @@ using namespace h3b;
 
 extern "C" int h3b_umma_peak_dev(h3_cuda *cuda, int kind, int iters, double *tera_ops_per_s, char *error,
                                  size_t error_size) {
-    if (!cuda || !tera_ops_per_s || iters <= 0 || kind < 0 || kind > 2)
+    if (!cuda || !tera_ops_per_s || iters <= 0 || kind < 0 || kind > 4)
         return fail(error, error_size, "umma_peak: invalid arguments");
     const size_t smem = 1024 + 16384 + 32768;
     cudaEvent_t e0 = cuda->ev0, e1 = cuda->ev1;
-    const double ops_per_mma = 2.0 * 128 * 256 * (kind == 0 ? 32 : kind == 1 ? 16 : 64);
+    const double ops_per_mma = kind >= 3 ? 2.0 * 128 * 128 * 16 : 2.0 * 128 * 256 * (kind == 0 ? 32 : kind == 1 ? 16 : 64);
     for (int rep = 0; rep < 2; rep++) {   // first launch warms up
         H3B_CUDA_OK(cudaEventRecord(e0, cuda->op_stream), "cudaEventRecord");
         if (kind == 0) {
@@ -84,6 +91,12 @@ extern "C" int h3b_umma_peak_dev(h3_cuda *cuda, int kind, int iters, double *ter
         } else if (kind == 1) {
             H3B_CUDA_OK(cudaFuncSetAttribute(k_umma_peak<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem), "attr");
             k_umma_peak<1><<<cuda->sm_count, 128, smem, cuda->op_stream>>>(iters, cuda->d_status);
+        } else if (kind == 3) {
+            H3B_CUDA_OK(cudaFuncSetAttribute(k_umma_peak<3>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem), "attr");
+            k_umma_peak<3><<<cuda->sm_count, 128, smem, cuda->op_stream>>>(iters, cuda->d_status);
+        } else if (kind == 4) {
+            H3B_CUDA_OK(cudaFuncSetAttribute(k_umma_peak<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem), "attr");
+            k_umma_peak<4><<<cuda->sm_count, 128, smem, cuda->op_stream>>>(iters, cuda->d_status);
         } else {
             H3B_CUDA_OK(cudaFuncSetAttribute(k_umma_peak<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem), "attr");
             k_umma_peak<2><<<cuda->sm_count, 128, smem, cuda->op_stream>>>(iters, cuda->d_status);
