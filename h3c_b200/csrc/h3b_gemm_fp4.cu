@@ -147,7 +147,8 @@ __global__ void __launch_bounds__(fp4::THREADS, 1) k_gemm_nvfp4(const __grid_con
         }
         __syncwarp();
     } else if (warp == 1) {
-        if (lane == 0) {
+        // whole warp converged (uniform descriptor arithmetic); one elected lane issues
+        {
             constexpr uint32_t idesc = fp4_idesc(BM, BN);
             int s = 0, it = 0, sfbuf = 0;
             uint32_t ph = 0;
@@ -164,19 +165,23 @@ __global__ void __launch_bounds__(fp4::THREADS, 1) k_gemm_nvfp4(const __grid_con
                     const uint32_t b_addr = a_addr + A_BYTES, sfa_addr = b_addr + B_BYTES, sfb_addr = sfa_addr + SF_BYTES;
                     const int nkt = min(4, p.sf_tiles_per_rowblock - kb * 4);   // MMAs (64 k each) with data
                     const uint32_t sf_t = tmem_base + SF_COL + (uint32_t)sfbuf * 32;
-                    for (int j = 0; j < nkt; j++) {
-                        tmem_cp_32x128b_warpx4(sf_t + j * 4, sf_desc(sfa_addr + j * 512));
-                        tmem_cp_32x128b_warpx4(sf_t + 16 + j * 4, sf_desc(sfb_addr + j * 512));
+                    if (elect_one()) {
+                        for (int j = 0; j < nkt; j++) {
+                            tmem_cp_32x128b_warpx4(sf_t + j * 4, sf_desc(sfa_addr + j * 512));
+                            tmem_cp_32x128b_warpx4(sf_t + 16 + j * 4, sf_desc(sfb_addr + j * 512));
+                        }
+                        for (int j = 0; j < nkt; j++)
+                            umma_nvfp4_ss(d_tmem, umma_desc_k_sw128(a_addr + j * 32), umma_desc_k_sw128(b_addr + j * 32),
+                                          idesc, sf_t + j * 4, sf_t + 16 + j * 4, (uint32_t)((kb | j) != 0));
+                        tc_commit(&empty[s]);
                     }
-                    for (int j = 0; j < nkt; j++)
-                        umma_nvfp4_ss(d_tmem, umma_desc_k_sw128(a_addr + j * 32), umma_desc_k_sw128(b_addr + j * 32), idesc,
-                                      sf_t + j * 4, sf_t + 16 + j * 4, (uint32_t)((kb | j) != 0));
-                    tc_commit(&empty[s]);
+                    __syncwarp();
                     sfbuf ^= 1;
                     if (++s == STAGES) { s = 0; ph ^= 1; }
                 }
                 if (*abort_word) break;
-                tc_commit(&tmem_full[buf]);
+                if (elect_one()) tc_commit(&tmem_full[buf]);
+                __syncwarp();
             }
         }
         __syncwarp();

@@ -248,7 +248,9 @@ __global__ void __launch_bounds__(gemm::THREADS, 1) k_gemm_i8(const __grid_const
         __syncwarp();
     } else if (warp == 1) {
         // --------------------------------------------------------- MMA issuer
-        if (lane == 0 && cta_rank == 0) {
+        // The whole warp walks the loop, converged (descriptor arithmetic stays in uniform registers);
+        // one elected lane issues each tcgen05 instruction.
+        if (cta_rank == 0) {
             constexpr uint32_t idesc = umma_idesc(2 /*s32*/, 1 /*s8*/, 1 /*s8*/, TILE_M, BN, 0, 0);
             int s = 0;
             uint32_t ph = 0;
@@ -265,23 +267,28 @@ __global__ void __launch_bounds__(gemm::THREADS, 1) k_gemm_i8(const __grid_const
                     const uint32_t a_addr = smem_u32(smem + (size_t)s * STAGE_BYTES);
                     const uint64_t a_desc = umma_desc_k_sw128(a_addr);
                     const uint64_t b_desc = umma_desc_k_sw128(a_addr + A_BYTES);
+                    if (elect_one()) {
 #pragma unroll
-                    for (int k = 0; k < BK / 32; k++) {
-                        if (CTAS == 2)
-                            umma_i8_ss_pair(d_tmem, a_desc + (uint64_t)(k * 2), b_desc + (uint64_t)(k * 2), idesc,
-                                            (uint32_t)((kb | k) != 0));
-                        else
-                            umma_i8_ss(d_tmem, a_desc + (uint64_t)(k * 2), b_desc + (uint64_t)(k * 2), idesc,
-                                       (uint32_t)((kb | k) != 0));
+                        for (int k = 0; k < BK / 32; k++) {
+                            if (CTAS == 2)
+                                umma_i8_ss_pair(d_tmem, a_desc + (uint64_t)(k * 2), b_desc + (uint64_t)(k * 2), idesc,
+                                                (uint32_t)((kb | k) != 0));
+                            else
+                                umma_i8_ss(d_tmem, a_desc + (uint64_t)(k * 2), b_desc + (uint64_t)(k * 2), idesc,
+                                           (uint32_t)((kb | k) != 0));
+                        }
+                        // the stage is free (in both CTAs) once these MMAs have read it
+                        if (CTAS == 2) tc_commit_pair(&empty[s], 3);
+                        else tc_commit(&empty[s]);
                     }
-                    // the stage is free (in both CTAs) once these MMAs have read it
-                    if (CTAS == 2) tc_commit_pair(&empty[s], 3);
-                    else tc_commit(&empty[s]);
+                    __syncwarp();
                     if (++s == STAGES) { s = 0; ph ^= 1; }
                 }
                 if (*abort_word) break;
-                if (CTAS == 2) tc_commit_pair(&tmem_full[buf], 3);
-                else tc_commit(&tmem_full[buf]);
+                if (elect_one()) {
+                    if (CTAS == 2) tc_commit_pair(&tmem_full[buf], 3);
+                    else tc_commit(&tmem_full[buf]);
+                }
             }
         }
         __syncwarp();
