@@ -19,6 +19,8 @@
 // O_A 256..383, O_B 384..511.
 #include <cuda_bf16.h>
 
+#include <type_traits>
+
 #include "h3b_internal.h"
 #include "h3b_ptx.cuh"
 
@@ -50,6 +52,28 @@ __device__ __forceinline__ float ex2_approx(float x) {
     return y;
 }
 
+// max of three (one instruction on sm_100)
+__device__ __forceinline__ float max3(float a, float b, float c) {
+    float d;
+    asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+    return d;
+}
+// two-wide f32 FMA / add: one issue slot for two independent IEEE operations
+__device__ __forceinline__ void fma2(float &d0, float &d1, float a0, float a1, float b, float c) {
+    asm("{\n\t.reg .b64 ra, rb, rc, rd;\n\t"
+        "mov.b64 ra, {%2, %3};\n\tmov.b64 rb, {%4, %4};\n\tmov.b64 rc, {%5, %5};\n\t"
+        "fma.rn.f32x2 rd, ra, rb, rc;\n\tmov.b64 {%0, %1}, rd;\n\t}"
+        : "=f"(d0), "=f"(d1)
+        : "f"(a0), "f"(a1), "f"(b), "f"(c));
+}
+__device__ __forceinline__ void add2(float &d0, float &d1, float a0, float a1) {
+    asm("{\n\t.reg .b64 ra, rd;\n\t"
+        "mov.b64 rd, {%0, %1};\n\tmov.b64 ra, {%2, %3};\n\t"
+        "add.rn.f32x2 rd, rd, ra;\n\tmov.b64 {%0, %1}, rd;\n\t}"
+        : "+f"(d0), "+f"(d1)
+        : "f"(a0), "f"(a1));
+}
+
 __global__ void __launch_bounds__(attn::THREADS, 1) k_attn_bf16(const __grid_constant__ AttnParams p) {
     using namespace attn;
     extern __shared__ uint8_t smem_raw[];
@@ -57,8 +81,8 @@ __global__ void __launch_bounds__(attn::THREADS, 1) k_attn_bf16(const __grid_con
     uint8_t *sQ = smem, *sK = smem + 2 * TILE, *sV = smem + 4 * TILE;
     uint64_t *bars = reinterpret_cast<uint64_t *>(smem + 6 * TILE);
     uint64_t *q_full = bars, *k_full = bars + 1, *v_full = bars + 3, *k_empty = bars + 5, *v_empty = bars + 7,
-             *s_full = bars + 9, *p_full = bars + 11, *o_done = bars + 13;
-    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 14);
+             *s_full = bars + 9, *p_full = bars + 11 /* [tile][half] */, *o_done = bars + 15;
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 16);
     volatile int *abort_word = reinterpret_cast<volatile int *>(tmem_slot + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -75,7 +99,8 @@ __global__ void __launch_bounds__(attn::THREADS, 1) k_attn_bf16(const __grid_con
             mbar_init(&k_empty[i], 1);
             mbar_init(&v_empty[i], 1);
             mbar_init(&s_full[i], 1);
-            mbar_init(&p_full[i], 4);
+            mbar_init(&p_full[2 * i], 4);
+            mbar_init(&p_full[2 * i + 1], 4);
         }
         mbar_init(o_done, 1);
         *abort_word = 0;
@@ -115,18 +140,26 @@ __global__ void __launch_bounds__(attn::THREADS, 1) k_attn_bf16(const __grid_con
         }
         __syncwarp();
     } else if (warp == 1) {
+        // ------------------------------------------------------------ MMA issuer
         // The whole warp walks the loop, converged, so that descriptor arithmetic stays in uniform
         // registers; one elected lane issues each tcgen05 instruction.  (With a single active lane the
         // operands cross from vector to uniform registers per instruction, which cost about 85 cycles per
-        // MMA against the 64 the MMA itself takes.)
+        // MMA against the 64 the MMA itself takes.)  The issuing thread is held back by the tensor pipe's
+        // queue while its MMAs run, so whatever it does between two blocks happens with the pipe idle:
+        // the K/V stage barriers of the NEXT iteration are therefore polled right after a block has been
+        // issued (while the queue drains), and the loop is unrolled by two so that every shared-memory
+        // descriptor is a loop-invariant value.
+        // (One issuer per tile was tried: their MMAs interleave in the pipe, both tiles finish late, and the
+        // kernel ran 30 % slower.)
         {
             // S = Q K^T : both operands K-major in shared memory (d contiguous).
             // O += P V  : P from TMEM (row = lane, two bf16 keys per 32-bit column); V as stored
             //             ([key][d], d contiguous) is the N-major form of the B operand.
             constexpr uint32_t idesc_s = umma_idesc(1, 1, 1, BQ, BKV, 0, 0);
             constexpr uint32_t idesc_o = umma_idesc(1, 1, 1, BQ, HD, 0, 1);
-            auto issue_s = [&](int t, int j) {
-                const uint32_t q_addr = smem_u32(sQ + t * TILE), k_addr = smem_u32(sK + (j & 1) * TILE);
+            const uint32_t q_base = smem_u32(sQ), k_base = smem_u32(sK), v_base = smem_u32(sV);
+            auto issue_s = [&](int t, int stage) {   // scores of tile t against the K tile in `stage`
+                const uint32_t q_addr = q_base + t * TILE, k_addr = k_base + stage * TILE;
                 const uint32_t d_tmem = tmem_base + S_COL + 128u * t;
 #pragma unroll
                 for (int k = 0; k < HD / 16; k++) {
@@ -137,13 +170,14 @@ __global__ void __launch_bounds__(attn::THREADS, 1) k_attn_bf16(const __grid_con
                 }
                 if (elect_one()) tc_commit(&s_full[t]);
             };
-            auto issue_pv = [&](int t, int j) {
-                const uint32_t v_addr = smem_u32(sV + (j & 1) * TILE);
+            auto issue_pv = [&](int t, int stage, int half, bool first) {
+                const uint32_t v_addr = v_base + stage * TILE;
 #pragma unroll
-                for (int k = 0; k < BKV / 16; k++)
-                    if (elect_one()) umma_f16_ts(tmem_base + O_COL + 128u * t, tmem_base + S_COL + 128u * t + (uint32_t)k * 8,
-                                umma_desc_mn_sw128(v_addr + (uint32_t)k * 2048, SLAB, 1024), idesc_o,
-                                (uint32_t)((j | k) != 0));
+                for (int k = half * (BKV / 32); k < (half + 1) * (BKV / 32); k++)
+                    if (elect_one())
+                        umma_f16_ts(tmem_base + O_COL + 128u * t, tmem_base + S_COL + 128u * t + (uint32_t)k * 8,
+                                    umma_desc_mn_sw128(v_addr + (uint32_t)k * 2048, SLAB, 1024), idesc_o,
+                                    (uint32_t)(!first || k != 0));
             };
             bool ok = mbar_wait(q_full, 0, abort_word, p.status, H3B_ST_TIMEOUT_FULL) &&
                       mbar_wait(&k_full[0], 0, abort_word, p.status, H3B_ST_TIMEOUT_FULL);
@@ -151,31 +185,49 @@ __global__ void __launch_bounds__(attn::THREADS, 1) k_attn_bf16(const __grid_con
                 tc_fence_after();
                 for (int t = 0; t < n_tiles; t++) issue_s(t, 0);
                 if (elect_one()) tc_commit(&k_empty[0]);
+                ok = mbar_wait(&v_full[0], 0, abort_word, p.status, H3B_ST_TIMEOUT_FULL) &&
+                     (n_kv < 2 || mbar_wait(&k_full[1], 0, abort_word, p.status, H3B_ST_TIMEOUT_FULL));
             }
-            for (int j = 0; ok && j < n_kv; j++) {
-                const int st = j & 1, nx = (j + 1) & 1;
+            // one iteration with the K/V stage index as a compile-time constant
+            auto step = [&](int j, auto stage_c) {
+                constexpr int st = decltype(stage_c)::value, nx = st ^ 1;
                 const bool more = j + 1 < n_kv;
-                if (!mbar_wait(&v_full[st], (j >> 1) & 1, abort_word, p.status, H3B_ST_TIMEOUT_FULL)) break;
-                if (more && !mbar_wait(&k_full[nx], ((j + 1) >> 1) & 1, abort_word, p.status, H3B_ST_TIMEOUT_FULL)) break;
                 for (int t = 0; t < n_tiles && ok; t++) {
-                    // P of this tile is in TMEM (and its scores are fully consumed)
-                    ok = mbar_wait(&p_full[t], j & 1, abort_word, p.status, H3B_ST_TIMEOUT_OTHER);
+                    // P of this tile arrives in TMEM in two halves of 64 keys (all its scores are in the
+                    // softmax threads' registers by then); the product over the first half runs while the
+                    // second half is still being exponentiated
+                    ok = mbar_wait(&p_full[2 * t], j & 1, abort_word, p.status, H3B_ST_TIMEOUT_OTHER);
                     if (!ok) break;
                     tc_fence_after();
-                    issue_pv(t, j);
+                    issue_pv(t, st, 0, j == 0);
+                    ok = mbar_wait(&p_full[2 * t + 1], j & 1, abort_word, p.status, H3B_ST_TIMEOUT_OTHER);
+                    if (!ok) break;
+                    tc_fence_after();
+                    issue_pv(t, st, 1, false);
                     if (t == n_tiles - 1 && elect_one()) tc_commit(&v_empty[st]);
                     if (more) {
-                        issue_s(t, j + 1);   // overwrites the tile's scores / P, in order after the P V product
+                        issue_s(t, nx);   // overwrites the tile's scores / P, in order after the P V product
                         if (t == n_tiles - 1 && elect_one()) tc_commit(&k_empty[nx]);
                     }
                 }
+                // stages of the next iteration: V(j+1) in stage nx, K(j+2) in stage st
+                if (ok && more) {
+                    ok = mbar_wait(&v_full[nx], ((j + 1) >> 1) & 1, abort_word, p.status, H3B_ST_TIMEOUT_FULL);
+                    if (ok && j + 2 < n_kv)
+                        ok = mbar_wait(&k_full[st], ((j + 2) >> 1) & 1, abort_word, p.status, H3B_ST_TIMEOUT_FULL);
+                    tc_fence_after();
+                }
+            };
+            for (int j = 0; ok && j < n_kv; j += 2) {
+                step(j, std::integral_constant<int, 0>{});
+                if (ok && j + 1 < n_kv) step(j + 1, std::integral_constant<int, 1>{});
             }
             if (elect_one()) tc_commit(o_done);
         }
         __syncwarp();
     } else {
         // ------------------------------------------------------------ softmax
-        const int t = (warp - 2) >> 2;                     // query tile of this warp group
+        const int t = (warp - 2) >> 2;                     // query tile of this warp group (warps 2-5: A, 6-9: B)
         const int q = warp & 3;                            // TMEM lane quarter of this warp
         const int r = q * 32 + lane;                       // query row inside the tile
         const uint32_t lane_base = (uint32_t)(q * 32) << 16;
@@ -201,11 +253,11 @@ __global__ void __launch_bounds__(attn::THREADS, 1) k_attn_bf16(const __grid_con
             }
             float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
 #pragma unroll
-            for (int i = 0; i < BKV; i += 4) {
-                mx0 = fmaxf(mx0, __uint_as_float(sv[i]));
-                mx1 = fmaxf(mx1, __uint_as_float(sv[i + 1]));
-                mx2 = fmaxf(mx2, __uint_as_float(sv[i + 2]));
-                mx3 = fmaxf(mx3, __uint_as_float(sv[i + 3]));
+            for (int i = 0; i < BKV; i += 8) {
+                mx0 = max3(mx0, __uint_as_float(sv[i]), __uint_as_float(sv[i + 1]));
+                mx1 = max3(mx1, __uint_as_float(sv[i + 2]), __uint_as_float(sv[i + 3]));
+                mx2 = max3(mx2, __uint_as_float(sv[i + 4]), __uint_as_float(sv[i + 5]));
+                mx3 = max3(mx3, __uint_as_float(sv[i + 6]), __uint_as_float(sv[i + 7]));
             }
             const float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
             const float m_new = fmaxf(m_run, mx * p.scale_log2);
@@ -239,23 +291,26 @@ __global__ void __launch_bounds__(attn::THREADS, 1) k_attn_bf16(const __grid_con
                 uint32_t packed[16];
 #pragma unroll
                 for (int i = 0; i < 32; i += 4) {
-                    const float p0 = ex2_approx(fmaf(__uint_as_float(sv[ch * 32 + i]), p.scale_log2, neg_m));
-                    const float p1 = ex2_approx(fmaf(__uint_as_float(sv[ch * 32 + i + 1]), p.scale_log2, neg_m));
-                    const float p2 = ex2_approx(fmaf(__uint_as_float(sv[ch * 32 + i + 2]), p.scale_log2, neg_m));
-                    const float p3 = ex2_approx(fmaf(__uint_as_float(sv[ch * 32 + i + 3]), p.scale_log2, neg_m));
-                    l0 += p0; l1 += p1; l2 += p2; l3 += p3;
+                    float x0, x1, x2, x3;
+                    fma2(x0, x1, __uint_as_float(sv[ch * 32 + i]), __uint_as_float(sv[ch * 32 + i + 1]), p.scale_log2, neg_m);
+                    fma2(x2, x3, __uint_as_float(sv[ch * 32 + i + 2]), __uint_as_float(sv[ch * 32 + i + 3]), p.scale_log2, neg_m);
+                    const float p0 = ex2_approx(x0), p1 = ex2_approx(x1), p2 = ex2_approx(x2), p3 = ex2_approx(x3);
+                    add2(l0, l1, p0, p1);
+                    add2(l2, l3, p2, p3);
                     __nv_bfloat162 h0 = __floats2bfloat162_rn(p0, p1), h1 = __floats2bfloat162_rn(p2, p3);
                     packed[i >> 1] = *reinterpret_cast<uint32_t *>(&h0);
                     packed[(i >> 1) + 1] = *reinterpret_cast<uint32_t *>(&h1);
                 }
                 tmem_st_32x32b_x16(s_addr + ch * 16, packed);
+                if (ch & 1) {   // a half (64 keys) of P is complete: hand it to the MMA warp
+                    tmem_st_wait();
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(&p_full[2 * t + (ch >> 1)]);
+                }
             }
             const float l_add = (l0 + l1) + (l2 + l3);
             l_run += l_add;
-            tmem_st_wait();
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(&p_full[t]);
         }
         // ---- final: O / l -> bf16 -> global
         if (t < n_tiles) {
