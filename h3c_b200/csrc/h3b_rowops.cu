@@ -302,6 +302,258 @@ __global__ void __launch_bounds__(THREADS) k_norm_reg(NormParams p) {
     }
 }
 
+// ---------------------------------------------------------------------------------------------
+// Streaming row kernel for the block's hot cases (16-bit rows, no branch / ConvRot): RMSNorm and/or
+// adaLN modulate -> round to the stream type -> per-row INT8 quantisation, or quantisation alone.
+// Persistent CTAs walk the rows with a stride of the grid; the norm weight and the row's modulation
+// vectors stay in registers while consecutive rows map to the same modulation row (the usual case: one
+// conditioning vector for all video tokens), the next row is fetched while the current one is reduced,
+// and the per-element work is trimmed to about ten instructions (two-wide f32 arithmetic, one block
+// barrier per reduction).  Element arithmetic is the reference's, operation by operation; only the
+// row-sum order differs.
+
+__device__ __forceinline__ void mul2(float &d0, float &d1, float a0, float a1, float b0, float b1) {
+    asm("{\n\t.reg .b64 ra, rb, rd;\n\tmov.b64 ra, {%2, %3};\n\tmov.b64 rb, {%4, %5};\n\t"
+        "mul.rn.f32x2 rd, ra, rb;\n\tmov.b64 {%0, %1}, rd;\n\t}"
+        : "=f"(d0), "=f"(d1) : "f"(a0), "f"(a1), "f"(b0), "f"(b1));
+}
+__device__ __forceinline__ void add2f(float &d0, float &d1, float a0, float a1, float b0, float b1) {
+    asm("{\n\t.reg .b64 ra, rb, rd;\n\tmov.b64 ra, {%2, %3};\n\tmov.b64 rb, {%4, %5};\n\t"
+        "add.rn.f32x2 rd, ra, rb;\n\tmov.b64 {%0, %1}, rd;\n\t}"
+        : "=f"(d0), "=f"(d1) : "f"(a0), "f"(a1), "f"(b0), "f"(b1));
+}
+__device__ __forceinline__ void fma2f(float &d0, float &d1, float a0, float a1, float b0, float b1) {   // d += a * b
+    asm("{\n\t.reg .b64 ra, rb, rd;\n\tmov.b64 rd, {%0, %1};\n\tmov.b64 ra, {%2, %3};\n\tmov.b64 rb, {%4, %5};\n\t"
+        "fma.rn.f32x2 rd, ra, rb, rd;\n\tmov.b64 {%0, %1}, rd;\n\t}"
+        : "+f"(d0), "+f"(d1) : "f"(a0), "f"(a1), "f"(b0), "f"(b1));
+}
+__device__ __forceinline__ float max3f(float a, float b, float c) {
+    float d;
+    asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+    return d;
+}
+// two 16-bit stream values of one 32-bit word as floats
+template <typename T> __device__ __forceinline__ void unpack2(uint32_t w, float &lo, float &hi);
+template <> __device__ __forceinline__ void unpack2<__nv_bfloat16>(uint32_t w, float &lo, float &hi) {
+    lo = __uint_as_float(w << 16);
+    hi = __uint_as_float(w & 0xffff0000u);
+}
+template <> __device__ __forceinline__ void unpack2<__half>(uint32_t w, float &lo, float &hi) {
+    float2 f = __half22float2(*reinterpret_cast<const __half2 *>(&w));
+    lo = f.x; hi = f.y;
+}
+template <typename T> __device__ __forceinline__ uint32_t pack2(float lo, float hi);
+template <> __device__ __forceinline__ uint32_t pack2<__nv_bfloat16>(float lo, float hi) {
+    __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t *>(&h);
+}
+template <> __device__ __forceinline__ uint32_t pack2<__half>(float lo, float hi) {
+    __half2 h = __floats2half2_rn(lo, hi);
+    return *reinterpret_cast<uint32_t *>(&h);
+}
+// roundf(y) for |y| < 2^22 as an integer: truncation of y + copysign(pred(0.5), y).  Adding the
+// predecessor of one half instead of one half keeps 0.49999997 from rounding up to 1 in the addition;
+// checked against floor(|y| + 0.5) for every float in [0, 128].
+__device__ __forceinline__ int round_half_away(float y) {
+    const float h = __uint_as_float((__float_as_uint(y) & 0x80000000u) | 0x3effffffu);
+    return __float2int_rz(__fadd_rn(y, h));
+}
+// four codes -> one word, saturating to int8 (byte 0 = a)
+__device__ __forceinline__ uint32_t pack_codes(int a, int b, int c, int d) {
+    uint32_t hi, out;
+    asm("cvt.pack.sat.s8.s32.b32 %0, %1, %2, 0;" : "=r"(hi) : "r"(d), "r"(c));
+    asm("cvt.pack.sat.s8.s32.b32 %0, %1, %2, %3;" : "=r"(out) : "r"(b), "r"(a), "r"(hi));
+    return out;
+}
+
+template <typename T, int NV, int THREADS, bool NORM>
+__global__ void __launch_bounds__(THREADS) k_rowq(NormParams p, unsigned rows) {
+    constexpr int NW = THREADS / 32;
+    __shared__ float red_ss[NW];
+    __shared__ float red_mx[2][NW];
+    const unsigned W = p.width;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const T *xbase = reinterpret_cast<const T *>(p.x);
+    unsigned r = blockIdx.x;
+    if (r >= rows) return;
+
+    float w[NORM ? NV : 1][8], sc1[NORM ? NV : 1][8], sh[NORM ? NV : 1][8];   // norm weight, 1 + scale, shift
+    size_t cached_mrow = ~(size_t)0;
+    if (NORM) {
+#pragma unroll
+        for (int j = 0; j < NV; j++) {
+            const unsigned c = (j * THREADS + threadIdx.x) * 8;
+#pragma unroll
+            for (int i = 0; i < 8; i++) w[j][i] = 1.0f;
+            if (p.norm_w) {
+                load_vec<float, 4>(p.norm_w + c, reinterpret_cast<float(&)[4]>(w[j][0]));
+                load_vec<float, 4>(p.norm_w + c + 4, reinterpret_cast<float(&)[4]>(w[j][4]));
+            }
+        }
+    }
+    uint4 cur[NV], nxt[NV];
+#pragma unroll
+    for (int j = 0; j < NV; j++)
+        cur[j] = *reinterpret_cast<const uint4 *>(xbase + (size_t)r * W + (j * THREADS + threadIdx.x) * 8);
+    unsigned par = 0;
+    while (true) {
+        const unsigned rn = r + gridDim.x;
+        if (rn < rows) {
+#pragma unroll
+            for (int j = 0; j < NV; j++)
+                nxt[j] = *reinterpret_cast<const uint4 *>(xbase + (size_t)rn * W + (j * THREADS + threadIdx.x) * 8);
+        }
+        float v[NV][8];
+#pragma unroll
+        for (int j = 0; j < NV; j++) {
+            const uint32_t *u = reinterpret_cast<const uint32_t *>(&cur[j]);
+#pragma unroll
+            for (int i = 0; i < 4; i++) unpack2<T>(u[i], v[j][2 * i], v[j][2 * i + 1]);
+        }
+        float amax = 0.0f;
+        if (NORM) {
+            const size_t mrow = p.mod ? (p.row_map ? p.row_map[r] : (size_t)r) : 0;
+            if (p.mod && mrow != cached_mrow) {
+                const float *mod = p.mod + mrow * p.slots * W;
+#pragma unroll
+                for (int j = 0; j < NV; j++) {
+                    const unsigned c = (j * THREADS + threadIdx.x) * 8;
+                    load_vec<float, 4>(mod + p.scale_slot * W + c, reinterpret_cast<float(&)[4]>(sc1[j][0]));
+                    load_vec<float, 4>(mod + p.scale_slot * W + c + 4, reinterpret_cast<float(&)[4]>(sc1[j][4]));
+                    load_vec<float, 4>(mod + p.shift_slot * W + c, reinterpret_cast<float(&)[4]>(sh[j][0]));
+                    load_vec<float, 4>(mod + p.shift_slot * W + c + 4, reinterpret_cast<float(&)[4]>(sh[j][4]));
+#pragma unroll
+                    for (int i = 0; i < 8; i++) sc1[j][i] = __fadd_rn(1.0f, sc1[j][i]);
+                }
+                cached_mrow = mrow;
+            }
+            float s0 = 0.0f, s1 = 0.0f;
+#pragma unroll
+            for (int j = 0; j < NV; j++)
+#pragma unroll
+                for (int i = 0; i < 8; i += 2) fma2f(s0, s1, v[j][i], v[j][i + 1], v[j][i], v[j][i + 1]);
+            float ss = s0 + s1;
+            for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+            if (lane == 0) red_ss[warp] = ss;
+            __syncthreads();
+            ss = 0.0f;
+#pragma unroll
+            for (int i = 0; i < NW; i++) ss += red_ss[i];
+            const float inv = 1.0f / sqrtf(ss / (float)W + p.eps);
+            T *normed = p.normed ? reinterpret_cast<T *>(p.normed) + (size_t)r * W : nullptr;
+#pragma unroll
+            for (int j = 0; j < NV; j++) {
+                uint32_t packed[4];
+#pragma unroll
+                for (int i = 0; i < 8; i += 2) {
+                    float n0, n1;
+                    mul2(n0, n1, v[j][i], v[j][i + 1], inv, inv);
+                    mul2(n0, n1, n0, n1, w[j][i], w[j][i + 1]);
+                    if (p.mod) {
+                        mul2(n0, n1, n0, n1, sc1[j][i], sc1[j][i + 1]);
+                        add2f(n0, n1, n0, n1, sh[j][i], sh[j][i + 1]);
+                    }
+                    packed[i >> 1] = pack2<T>(n0, n1);
+                    unpack2<T>(packed[i >> 1], v[j][i], v[j][i + 1]);
+                    amax = max3f(amax, fabsf(v[j][i]), fabsf(v[j][i + 1]));
+                }
+                if (normed)
+                    *reinterpret_cast<uint4 *>(normed + (j * THREADS + threadIdx.x) * 8) =
+                        make_uint4(packed[0], packed[1], packed[2], packed[3]);
+            }
+        } else {
+#pragma unroll
+            for (int j = 0; j < NV; j++)
+#pragma unroll
+                for (int i = 0; i < 8; i += 2) amax = max3f(amax, fabsf(v[j][i]), fabsf(v[j][i + 1]));
+        }
+        if (p.q) {
+            for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+            if (lane == 0) red_mx[par][warp] = amax;
+            __syncthreads();
+            amax = 0.0f;
+#pragma unroll
+            for (int i = 0; i < NW; i++) amax = fmaxf(amax, red_mx[par][i]);
+            par ^= 1;
+            const float scale = amax > 0.0f ? amax / 127.0f : 1.0f;
+            const float inv = 1.0f / scale;
+            if (threadIdx.x == 0) p.scales[r] = scale;
+            int8_t *q = p.q + (size_t)r * W;
+#pragma unroll
+            for (int j = 0; j < NV; j++) {
+                float y[8];
+#pragma unroll
+                for (int i = 0; i < 8; i += 2) mul2(y[i], y[i + 1], v[j][i], v[j][i + 1], inv, inv);
+                uint2 o;
+                o.x = pack_codes(round_half_away(y[0]), round_half_away(y[1]), round_half_away(y[2]), round_half_away(y[3]));
+                o.y = pack_codes(round_half_away(y[4]), round_half_away(y[5]), round_half_away(y[6]), round_half_away(y[7]));
+                *reinterpret_cast<uint2 *>(q + (j * THREADS + threadIdx.x) * 8) = o;
+            }
+        }
+        if (rn >= rows) break;
+#pragma unroll
+        for (int j = 0; j < NV; j++) cur[j] = nxt[j];
+        r = rn;
+    }
+}
+
+template <typename T, int NV, int THREADS, bool NORM>
+static int rowq_launch_k(h3_cuda *cuda, const NormParams &p, size_t rows, char *error, size_t error_size) {
+    auto kern = k_rowq<T, NV, THREADS, NORM>;
+    static int per_sm[64];   // resident CTAs per SM of this kernel, asked once per device
+    const int dev = cuda->device & 63;
+    if (per_sm[dev] == 0) {
+        int n = 0;
+        H3B_CUDA_OK(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, kern, THREADS, 0), "k_rowq occupancy");
+        per_sm[dev] = n > 0 ? n : 1;
+    }
+    size_t grid = (size_t)cuda->sm_count * per_sm[dev];
+    if (grid > rows) grid = rows;
+    ProfScope prof(cuda, PROF_ROWS);
+    kern<<<(unsigned)grid, THREADS, 0, cuda->op_stream>>>(p, (unsigned)rows);
+    cuda->launches++;
+    H3B_CUDA_OK(cudaGetLastError(), "k_rowq launch");
+    return 1;
+}
+// Streaming kernel when the shape allows it; returns -1 when it does not apply.
+template <typename T>
+static int rowq_dispatch(h3_cuda *cuda, const NormParams &p, size_t rows, char *error, size_t error_size) {
+    if constexpr (sizeof(T) != 2) {
+        return -1;
+    } else {
+    if (p.gs != 0 || p.rot || p.branch || p.gated) return -1;
+    auto al16 = [](const void *q_) { return !q_ || (reinterpret_cast<uintptr_t>(q_) & 15) == 0; };
+    if (!al16(p.x) || !al16(p.normed) || !al16(p.norm_w) || !al16(p.mod) || (p.q && (reinterpret_cast<uintptr_t>(p.q) & 7)))
+        return -1;
+    // Quantisation alone is latency-bound: many threads with one vector each.  With a norm, the two block
+    // reductions per row cost as many instructions as eight elements' arithmetic, so each thread takes
+    // three or four vectors and the CTA has few warps.
+    if (!p.identity) {
+        switch (p.width) {
+        case 1024: return rowq_launch_k<T, 1, 128, true>(cuda, p, rows, error, error_size);
+        case 2048: return rowq_launch_k<T, 2, 128, true>(cuda, p, rows, error, error_size);
+        case 3072: return rowq_launch_k<T, 3, 128, true>(cuda, p, rows, error, error_size);
+        case 4096: return rowq_launch_k<T, 4, 128, true>(cuda, p, rows, error, error_size);
+        case 6144: return rowq_launch_k<T, 3, 256, true>(cuda, p, rows, error, error_size);
+        case 8192: return rowq_launch_k<T, 4, 256, true>(cuda, p, rows, error, error_size);
+        case 12288: return rowq_launch_k<T, 3, 512, true>(cuda, p, rows, error, error_size);
+        }
+        return -1;
+    }
+    switch (p.width) {
+    case 1024: return rowq_launch_k<T, 1, 128, false>(cuda, p, rows, error, error_size);
+    case 2048: return rowq_launch_k<T, 1, 256, false>(cuda, p, rows, error, error_size);
+    case 3072: return rowq_launch_k<T, 1, 384, false>(cuda, p, rows, error, error_size);
+    case 4096: return rowq_launch_k<T, 1, 512, false>(cuda, p, rows, error, error_size);
+    case 6144: return rowq_launch_k<T, 2, 384, false>(cuda, p, rows, error, error_size);
+    case 8192: return rowq_launch_k<T, 2, 512, false>(cuda, p, rows, error, error_size);
+    case 12288: return rowq_launch_k<T, 3, 512, false>(cuda, p, rows, error, error_size);
+    case 16384: return rowq_launch_k<T, 4, 512, false>(cuda, p, rows, error, error_size);
+    }
+    return -1;
+    }
+}
+
 template <typename T, int NV, int THREADS>
 static int norm_reg_launch(h3_cuda *cuda, const NormParams &p, size_t rows, char *error, size_t error_size) {
     ProfScope prof(cuda, PROF_ROWS);
@@ -335,7 +587,9 @@ static int norm_reg_dispatch(h3_cuda *cuda, const NormParams &p, size_t rows, ch
 template <typename T>
 static int norm_dispatch(h3_cuda *cuda, const NormParams &p, size_t rows, bool vec, char *error, size_t error_size) {
     if (sizeof(T) == 2) {
-        int rc = norm_reg_dispatch<T>(cuda, p, rows, error, error_size);
+        int rc = rowq_dispatch<T>(cuda, p, rows, error, error_size);
+        if (rc >= 0) return rc;
+        rc = norm_reg_dispatch<T>(cuda, p, rows, error, error_size);
         if (rc >= 0) return rc;
     }
     size_t smem = (size_t)p.width * sizeof(float);
