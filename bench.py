@@ -15,6 +15,7 @@ host<->device copies inside the timed region.
 from __future__ import annotations
 
 import argparse
+import ctypes
 import json
 import os
 import subprocess
@@ -361,6 +362,17 @@ def gpu_arm(args):
         lin_f, _ = block_flops(rows, text_len, geo.dim, geo.ffn)
         attn_f = (4.0 * seq_real * seq_real * geo.dim) / world + 4.0 * rows * text_len * geo.dim
         roof = roofline(prof, lin_f, attn_f, geo.n_blocks, pk)
+        if roof and roof.get("kernel") == "gemm_i8":
+            if not ulysses and seq_real == 6144:
+                roof["traffic"] = GEMM_DRAM_BYTES_PER_LAUNCH_6144
+                roof["traffic_note"] = ("dram__bytes_read.sum + dram__bytes_write.sum, mean over the seven GEMM launches "
+                                        "of one block, one cold-cache ncu capture of this command")
+            # the int8 rate this GPU sustains on back-to-back MMAs with no loads (about a second of them)
+            v = ctypes.c_double(0)
+            from h3c_b200.lib import call
+            call("h3b_umma_peak_dev", cuda.h, 0, 1000000, ctypes.byref(v))
+            roof["probe_peak"] = v.value
+            roof["frac_of_probe"] = roof["achieved"] / v.value
         lin_all, attn_all = block_flops(seq_real, text_len, geo.dim, geo.ffn)
         if args.skip_cpu_baseline or world > 1:
             cpu = None
@@ -408,6 +420,11 @@ def profile_classes(cuda, dit, step):
     n = lib.h3b_cuda_profile_end(cuda.h, ms, cnt, 8)
     names = ["gemm_i8", "attention", "rows", "rope", "other"]
     return {names[i]: {"launches": int(cnt[i]), "ms": float(ms[i])} for i in range(min(n, len(names))) if cnt[i]}
+
+
+# DRAM bytes per int8 GEMM launch of the 6,144-token block (mean of its seven GEMMs): 847 MB per block / 7.
+# The algorithmic figure (codes + weights + outputs + residuals of the seven) is 857 MB per block.
+GEMM_DRAM_BYTES_PER_LAUNCH_6144 = 121.0e6
 
 
 def roofline(prof, lin_flops_block, attn_flops_block, n_blocks, pk):

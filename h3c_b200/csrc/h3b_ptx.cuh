@@ -175,9 +175,12 @@ __device__ __forceinline__ uint32_t mapa_shared(uint32_t addr, uint32_t rank) {
 __device__ __forceinline__ void cluster_sync_all() {
     asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
-// arrive on an mbarrier of another CTA of the cluster (address from mapa_shared)
+// Arrive on an mbarrier of another CTA of the cluster (address from mapa_shared).  Relaxed: a release
+// at cluster scope would first wait for all of the thread's earlier global stores (a whole output tile in
+// the GEMM epilogue).  What the arrival has to order, the TMEM reads, is ordered by tcgen05.wait::ld and
+// tcgen05.fence::before_thread_sync before it.
 __device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
-    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+    asm volatile("mbarrier.arrive.relaxed.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
 }
 // 2-D tiled load into this CTA's shared memory whose completion is counted on an mbarrier that may
 // live in the other CTA of the pair (`bar_cluster_addr` from mapa_shared).  No multicast.
