@@ -2,10 +2,11 @@
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
 
-N = 1 (default): the full 50-block W4A8 step at 6,144 video tokens (6x32x32 patch grid) + 512 text
-tokens, D = 3072, 24 x 128 heads, FFN 12288, bf16 residual stream, t = 0.5 -- BASELINE.json configs[3].
-N > 1 (under torchrun, one rank per GPU): the Ulysses sequence-parallel step at 50,220 tokens
-(31x30x54 grid) -- configs[4].
+Workload at every N: the full 50-block W4A8 step at 50,220 video tokens (31x30x54 patch grid) + 512 text
+tokens, D = 3072, 24 x 128 heads, FFN 12288, bf16 residual stream, t = 0.5 -- BASELINE.json configs[4].
+N = 1 runs it on one GPU; N > 1 (under torchrun, one rank per GPU) shards the rows across the ranks
+(Ulysses sequence parallelism), so the per-N values are the same work and compare directly.
+`--workload step6144` times the 6,144-token single-GPU step (6x32x32 grid, configs[3]) instead.
 `--impl reference` times the reference's CPU implementation of the same block on the host cores.
 
 Prints ONE JSON line (rank 0).  `value` is ms per step with every input resident in HBM; `e2e` is the
@@ -107,7 +108,7 @@ class ClockSampler:
 # ------------------------------------------------------------------------------- CPU baseline
 
 def cpu_block_sample(kind: str, threads: int, budget_s: float = 15.0, grid=None):
-    """Times the reference's CPU block path on a bounded row sample of the N=1 workload.
+    """Times the reference's CPU block path on a bounded row sample of the workload given by `grid`.
 
     kind "reference": the reference's own C functions (oracle/_ref/libh3_ref.so) driven over row slices
     from `threads` host threads (its loops are serial); attention rows use the rectangular restatement of
@@ -190,30 +191,39 @@ def reference_arm(args):
     vals = []
     desc = ""
     for _ in range(max(1, min(args.steps, 2))):    # each "step" is one bounded sample; two are plenty on a CPU
-        v, desc = cpu_block_sample(kind, cores, budget_s=20.0, grid=GRID_1GPU if args.gpus == 1 else GRID_ULYSSES)
+        v, desc = cpu_block_sample(kind, cores, budget_s=20.0, grid=GRID_ULYSSES if big_workload(args) else GRID_1GPU)
         vals.append(v)
     value = float(np.median(vals))
     line = {"impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": value, "higher_is_better": False,
-            "scaling": "weak" if args.gpus == 1 else "strong", "vs_baseline": None, "dtype": "int8 linears + f32 attention (CPU)", "data": "synthetic",
-            "config": workload_config(args.gpus),
+            "scaling": "strong" if big_workload(args) else "weak", "vs_baseline": None,
+            "dtype": "int8 linears + f32 attention (CPU)", "data": "synthetic",
+            "config": workload_config(args.gpus, big_workload(args)),
             "cpu_baseline": {"value": value, "unit": UNIT, "cores": cores, "kind": kind, "sample": desc},
             "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
             "gpu_launches": 0}
     OUT.emit(json.dumps(line))
 
 
-def workload_config(n_gpus):
-    grid = GRID_1GPU if n_gpus == 1 else GRID_ULYSSES
+def big_workload(args):
+    """The metric's workload is the 50,220-token step at every N (the same work on 1, 2, 4 or 8 GPUs, so that
+    per-N values compare); `--workload step6144` selects the 6,144-token single-GPU step instead."""
+    return args.workload != "step6144"
+
+
+def workload_config(n_gpus, big):
+    grid = GRID_ULYSSES if big else GRID_1GPU
     tokens = grid[0] * grid[1] * grid[2]
-    return {"workload": ("50-block W4A8 DiT denoiser step, 512x512x22 frames" if n_gpus == 1 else
-                         "Ulysses sequence-parallel 50-block W4A8 DiT step, 864x480x121 frames"),
+    return {"workload": ("50-block W4A8 DiT denoiser step, 864x480x121 frames (Ulysses sequence-parallel for N > 1)"
+                         if big else "50-block W4A8 DiT denoiser step, 512x512x22 frames"),
             "tokens": tokens, "patch_grid": list(grid), "text_tokens": GEO["text"], "dim": GEO["dim"],
             "heads": GEO["heads"], "head_dim": GEO["head_dim"], "ffn": GEO["ffn"], "blocks": GEO["n_blocks"],
             "weights": "int4 group-128 f16 scales, decoded once to resident int8 + per-channel scale",
             "activations": "per-token absmax int8, bf16 residual stream", "timestep": 0.5,
             "parallelism": "single GPU" if n_gpus == 1 else f"ulysses{n_gpus}",
-            "l2": "each step streams 3.4 GB of weights and >1 GB of activations, far above the 126 MB L2"}
+            "l2": "each step streams 3.4 GB of weights and >1 GB of activations, far above the 126 MB L2",
+            "other_workload": "--workload step6144 times the 6,144-token single-GPU step" if big else
+                              "default (no --workload) times the 50,220-token step"}
 
 
 # -------------------------------------------------------------------------------------- GPU arm
@@ -249,7 +259,9 @@ def gpu_arm(args):
     geo = D.DitGeometry(dim=GEO["dim"], heads=GEO["heads"], head_dim=GEO["head_dim"], ffn=GEO["ffn"],
                         n_blocks=GEO["n_blocks"], mod_rows=1, t_dim=256, kind=D.BLOCK_CROSS_GELU, stream_dtype=D.BF16)
     dit = D.build_synthetic(cuda, geo, seed=0)   # same seed on every rank: replicated weights
-    ulysses = world > 1 or args.workload == "ulysses"
+    ulysses = big_workload(args)
+    if world > 1 and not ulysses:
+        raise SystemExit("--workload step6144 is a single-GPU workload")
     grid = GRID_ULYSSES if ulysses else GRID_1GPU
     seq_real, text_len = grid[0] * grid[1] * grid[2], GEO["text"]
     seq_pad, seq_local, first_row, real_rows = shard_rows(seq_real, world, rank)
@@ -362,6 +374,15 @@ def gpu_arm(args):
         lin_f, _ = block_flops(rows, text_len, geo.dim, geo.ffn)
         attn_f = (4.0 * seq_real * seq_real * geo.dim) / world + 4.0 * rows * text_len * geo.dim
         roof = roofline(prof, lin_f, attn_f, geo.n_blocks, pk)
+        if roof and roof.get("kernel") == "attention" and world == 1 and seq_real == 50220:
+            roof["traffic"] = ATTN_DRAM_BYTES_PER_LAUNCH_50220
+            roof["traffic_note"] = ("dram__bytes_read.sum + dram__bytes_write.sum, mean of the self- and the "
+                                    "cross-attention launch of one block, one cold-cache ncu capture of this command")
+            v = ctypes.c_double(0)
+            from h3c_b200.lib import call
+            call("h3b_umma_peak_dev", cuda.h, 3, 1000000, ctypes.byref(v))   # bf16 128x128x16, about a second
+            roof["probe_peak"] = v.value
+            roof["frac_of_probe"] = roof["achieved"] / v.value
         if roof and roof.get("kernel") == "gemm_i8":
             if not ulysses and seq_real == 6144:
                 roof["traffic"] = GEMM_DRAM_BYTES_PER_LAUNCH_6144
@@ -378,11 +399,9 @@ def gpu_arm(args):
             cpu = None
         else:
             kind = "reference" if ref_available() else "port"
-            cpu_ms, cpu_desc = cpu_block_sample(kind, os.cpu_count() or 1)
+            cpu_ms, cpu_desc = cpu_block_sample(kind, os.cpu_count() or 1, grid=grid)
             cpu = {"value": cpu_ms, "unit": UNIT, "cores": os.cpu_count() or 1, "kind": kind, "sample": cpu_desc}
-        cfg = workload_config(world if world > 1 else (8 if ulysses else 1))
-        if world == 1 and ulysses:
-            cfg["parallelism"] = "single GPU (same workload as the Ulysses runs)"
+        cfg = workload_config(world, ulysses)
         line = {"metric": METRIC, "value": ms_step, "unit": UNIT, "n_gpus": world, "steps": args.steps,
                 "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": False,
                 "scaling": "strong" if ulysses else "weak", "vs_baseline": None,
@@ -425,6 +444,9 @@ def profile_classes(cuda, dit, step):
 # DRAM bytes per int8 GEMM launch of the 6,144-token block (mean of its seven GEMMs): 847 MB per block / 7.
 # The algorithmic figure (codes + weights + outputs + residuals of the seven) is 857 MB per block.
 GEMM_DRAM_BYTES_PER_LAUNCH_6144 = 121.0e6
+# DRAM bytes per attention launch of the 50,220-token block on one GPU: self-attention 1277 MB (Q, K, V read
+# and O written once: 1234 MB algorithmic), cross-attention 576 MB (624 MB algorithmic); mean of the two.
+ATTN_DRAM_BYTES_PER_LAUNCH_50220 = 926.4e6
 
 
 def roofline(prof, lin_flops_block, attn_flops_block, n_blocks, pk):
@@ -478,8 +500,8 @@ def main():
     ap.add_argument("--steps", type=int, default=5)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="auto", choices=["auto", "ulysses"],
-                    help="'ulysses' runs the 50,220-token workload at any N (N=1 gives the scaling reference)")
+    ap.add_argument("--workload", default="auto", choices=["auto", "ulysses", "step6144"],
+                    help="auto / ulysses: the 50,220-token step at any N; step6144: the 6,144-token single-GPU step")
     ap.add_argument("--skip-cpu-baseline", action="store_true", help="omit the CPU sample (profiling runs)")
     ap.add_argument("--skip-e2e", action="store_true", help="omit the host-buffer measurement (profiling runs)")
     args = ap.parse_args()

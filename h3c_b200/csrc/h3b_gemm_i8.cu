@@ -344,9 +344,22 @@ __global__ void __launch_bounds__(gemm::THREADS, 1) k_gemm_i8(const __grid_const
                     }
                     if (row_ok) {
                         if (which < 2) {
-                            float ss = 0.0f;
+                            // Sum of squares in the order of the stand-alone kernel (k_qkv_rope: sixteen lanes
+                            // with eight consecutive values each, then an xor butterfly), so that a chain
+                            // that runs QK-norm here and one that runs it there give the same bits.
+                            float part[16];
 #pragma unroll
-                            for (int d = 0; d < 128; d++) ss = __fadd_rn(ss, __fmul_rn(v[d], v[d]));
+                            for (int l = 0; l < 16; l++) {
+                                float t = 0.0f;
+#pragma unroll
+                                for (int i = 0; i < 8; i++) t = __fmaf_rn(v[8 * l + i], v[8 * l + i], t);
+                                part[l] = t;
+                            }
+#pragma unroll
+                            for (int o = 8; o > 0; o >>= 1)
+#pragma unroll
+                                for (int l = 0; l < o; l++) part[l] = __fadd_rn(part[l], part[l + o]);
+                            const float ss = part[0];
                             const float inv = 1.0f / sqrtf(ss / 128.0f + p.eps);
                             const float *nw = which == 0 ? p.q_norm : p.k_norm;
 #pragma unroll

@@ -784,13 +784,13 @@ __global__ void __launch_bounds__(256) k_qkv_rope(const TI *qkv, const float *q_
     load_vec<TI, EPL>(vb + d0, vv);
     float qs = 0.0f, ks = 0.0f;
 #pragma unroll
-    for (int i = 0; i < EPL; i++) {
-        qs += qv[i] * qv[i];
-        ks += kv[i] * kv[i];
+    for (int i = 0; i < EPL; i++) {   // the QKV GEMM epilogue repeats this order exactly
+        qs = __fmaf_rn(qv[i], qv[i], qs);
+        ks = __fmaf_rn(kv[i], kv[i], ks);
     }
     for (int o = LANES / 2; o > 0; o >>= 1) {
-        qs += __shfl_xor_sync(0xffffffffu, qs, o);
-        ks += __shfl_xor_sync(0xffffffffu, ks, o);
+        qs = __fadd_rn(qs, __shfl_xor_sync(0xffffffffu, qs, o));
+        ks = __fadd_rn(ks, __shfl_xor_sync(0xffffffffu, ks, o));
     }
     const float qi = 1.0f / sqrtf(qs / (float)HD + eps), ki = 1.0f / sqrtf(ks / (float)HD + eps);
 #pragma unroll
