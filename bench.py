@@ -272,6 +272,10 @@ def gpu_arm(args):
             uid.copy_(torch.frombuffer(bytearray(h3c_b200.UlyssesComm.unique_id()), dtype=torch.uint8))
         dist.broadcast(uid, 0)
         comm = h3c_b200.UlyssesComm(rank, world, bytes(uid.cpu().numpy().tobytes()), local)
+        comm.set_compute(torch.cuda.current_stream())
+        if os.environ.get("H3B_ULYSSES_DIRECT", "1") != "0":
+            # peers' Q/K/V and attention-row buffers mapped into this rank: the epilogues store across NVLink
+            comm.setup_direct(seq_local, geo.heads, geo.head_dim)
         dit.set_ulysses(comm)
     rows = seq_local if world > 1 else seq_real
     oracle = Oracle()

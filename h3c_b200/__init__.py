@@ -363,5 +363,13 @@ class UlyssesComm:
         call("h3_ulysses_a2a_attn_out", C.byref(self.cfg), ptr(x), ptr(out), seq_local, heads, head_dim,
              x.element_size())
 
+    def setup_direct(self, seq_local, heads, head_dim):
+        """Maps every rank's gathered Q/K/V and attention-row buffers (collective): the sequence-parallel chain
+        then stores into peer memory from the GEMM and attention epilogues instead of exchanging."""
+        call("h3b_ulysses_direct_setup", C.byref(self.cfg), seq_local, heads, head_dim)
+
+    def barrier(self):
+        call("h3b_ulysses_barrier", C.byref(self.cfg))
+
     def close(self):
         load().h3_ulysses_comm_destroy(C.byref(self.cfg))

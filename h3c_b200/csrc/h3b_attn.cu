@@ -44,6 +44,11 @@ struct AttnParams {
     int lq, lk, heads;
     float scale_log2;                     // scale * log2(e)
     int *status;
+    // optional scatter of the output rows by owner (sequence parallelism): row r goes to
+    // sc_out[r / sc_rows] (possibly another GPU's memory) at row r % sc_rows, head sc_head0 + head of
+    // sc_heads; sc_rows == 0 = off
+    int sc_rows, sc_heads, sc_head0;
+    __nv_bfloat16 *sc_out[8];
 };
 
 __device__ __forceinline__ float ex2_approx(float x) {
@@ -318,7 +323,14 @@ __global__ void __launch_bounds__(attn::THREADS, 1) k_attn_bf16(const __grid_con
             tc_fence_after();
             const int row = q0 + t * BQ + r;
             const float inv_l = 1.0f / l_run;
-            __nv_bfloat16 *dst = p.out + (size_t)row * p.o_stride + (size_t)head * HD;
+            __nv_bfloat16 *dst;
+            if (p.sc_rows) {
+                const int owner = row / p.sc_rows;
+                dst = p.sc_out[owner < 8 ? owner : 0] +
+                      ((size_t)(row - owner * p.sc_rows) * p.sc_heads + p.sc_head0 + head) * HD;
+            } else {
+                dst = p.out + (size_t)row * p.o_stride + (size_t)head * HD;
+            }
 #pragma unroll 1
             for (int ch = 0; ch < HD / 32; ch++) {
                 uint32_t o[32];
@@ -356,9 +368,19 @@ static int make_map(CUtensorMap *map, const void *base, size_t stride_elems, siz
     return 1;
 }
 
+static int launch_sdpa_impl(h3_cuda *cuda, const void *q, size_t qs, const void *k, size_t ks, const void *v, size_t vs,
+                            size_t lq, size_t lk, size_t heads, size_t hd, float scale, void *out, size_t os,
+                            const h3b_ulysses_direct *sc, char *error, size_t error_size);
+
 int launch_sdpa_bf16(h3_cuda *cuda, const void *q, size_t qs, const void *k, size_t ks, const void *v, size_t vs,
                      size_t lq, size_t lk, size_t heads, size_t hd, float scale, void *out, size_t os, char *error,
                      size_t error_size) {
+    return launch_sdpa_impl(cuda, q, qs, k, ks, v, vs, lq, lk, heads, hd, scale, out, os, nullptr, error, error_size);
+}
+
+static int launch_sdpa_impl(h3_cuda *cuda, const void *q, size_t qs, const void *k, size_t ks, const void *v, size_t vs,
+                            size_t lq, size_t lk, size_t heads, size_t hd, float scale, void *out, size_t os,
+                            const h3b_ulysses_direct *sc, char *error, size_t error_size) {
     if (!cuda || !q || !k || !v || !out || !lq || !lk || !heads) return fail(error, error_size, "invalid sdpa args");
     if (hd != attn::HD) return fail(error, error_size, "sdpa: head_dim %zu unsupported (128 only)", hd);
     if ((qs % 8) || (ks % 8) || (vs % 8) || (os % 8) || ((uintptr_t)q & 15) || ((uintptr_t)k & 15) ||
@@ -377,6 +399,16 @@ int launch_sdpa_bf16(h3_cuda *cuda, const void *q, size_t qs, const void *k, siz
     p.out = (__nv_bfloat16 *)out; p.o_stride = os; p.lq = (int)lq; p.lk = (int)lk; p.heads = (int)heads;
     p.scale_log2 = scale * 1.4426950408889634f;
     p.status = cuda->d_status;
+    if (sc) {
+        // lq rows of the gathered sequence, each owned by rank row / seq_local
+        if (lq > (size_t)sc->ulysses * sc->seq_local) return fail(error, error_size, "sdpa scatter: more rows than the ranks own");
+        p.sc_rows = (int)sc->seq_local; p.sc_heads = (int)sc->heads;
+        p.sc_head0 = (int)((size_t)sc->rank * (sc->heads / (size_t)sc->ulysses));
+        for (int r = 0; r < sc->ulysses; r++) {
+            if (!sc->peer_att[r]) return fail(error, error_size, "sdpa scatter: buffer of rank %d is not mapped", r);
+            p.sc_out[r] = (__nv_bfloat16 *)sc->peer_att[r];
+        }
+    }
     H3B_CUDA_OK(cudaFuncSetAttribute(k_attn_bf16, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)attn::SMEM_BYTES),
                 "sdpa smem attribute");
     dim3 grid((unsigned)ceil_div(lq, 2 * attn::BQ), (unsigned)heads);
@@ -400,6 +432,20 @@ int h3b_sdpa_bf16_dev(h3_cuda *cuda, const void *d_q, size_t q_stride, const voi
                       float scale, void *d_out, size_t o_stride, char *error, size_t error_size) {
     int ok = launch_sdpa_bf16(cuda, d_q, q_stride, d_k, k_stride, d_v, v_stride, lq, lk, heads, head_dim, scale, d_out,
                               o_stride, error, error_size);
+    if (ok) g_last_backend = "tcgen05_flash_bf16";
+    return ok;
+}
+
+int h3b_sdpa_bf16_scatter_dev(h3_cuda *cuda, const h3b_ulysses_direct *sc, size_t seq_real, float scale, char *error,
+                              size_t error_size) {
+    if (!cuda || !sc || !seq_real) return fail(error, error_size, "sdpa scatter: invalid arguments");
+    if (sc->ulysses < 1 || sc->ulysses > 8 || sc->rank < 0 || sc->rank >= sc->ulysses || sc->head_dim != 128 ||
+        !sc->heads || sc->heads % (size_t)sc->ulysses || !sc->q || !sc->k || !sc->v)
+        return fail(error, error_size, "sdpa scatter: bad geometry");
+    const size_t hl = sc->heads / (size_t)sc->ulysses, il = hl * sc->head_dim;
+    // `out` of the plain form is only checked for alignment: rows are stored through the scatter table
+    int ok = launch_sdpa_impl(cuda, sc->q, il, sc->k, il, sc->v, il, seq_real, seq_real, hl, sc->head_dim, scale, sc->att,
+                              sc->heads * sc->head_dim, sc, error, error_size);
     if (ok) g_last_backend = "tcgen05_flash_bf16";
     return ok;
 }

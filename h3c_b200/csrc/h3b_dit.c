@@ -329,6 +329,29 @@ static int block_forward(h3b_dit *d, unsigned block, const void *d_x, size_t seq
          * (real) sequence with heads/U heads, exchange back.  Both exchanges run in place. */
         const size_t U = (size_t)d->uly->ulysses, hl = d->cfg.heads / U, seq_pad = seq * U, Il = hl * d->cfg.head_dim;
         const size_t es = dt == H3B_F32 ? 4 : 2;
+        const h3b_ulysses_direct *dir = h3b_ulysses_direct_get(d->uly);
+        if (dir && dir->seq_local == seq && dir->heads == d->cfg.heads && dir->head_dim == d->cfg.head_dim &&
+            d->cfg.head_dim == 128 && dt != H3B_F32 &&
+            (d->cfg.rope_half == 0 || d->cfg.rope_half == 48 || d->cfg.rope_half == 64)) {
+            /* Exchange-free form: the QKV epilogue (QK-norm and RoPE included: both are per row and head) stores
+             * every head slice into the gathered buffer of the rank that attends that head, the attention
+             * epilogue stores every output row into the buffer of the rank that owns the row.  A barrier
+             * after each makes the stores of all ranks visible before they are read; it also keeps a rank
+             * from overwriting a buffer that a slower rank still reads. */
+            h3b_gemm_epi e;
+            const size_t off = (size_t)dir->rank * seq * d->cfg.rope_half;   /* this rank's rows of the tables */
+            memset(&e, 0, sizeof(e));
+            e.kind = H3B_EPI_QKV_ROPE; e.out_dtype = H3B_BF16; e.scatter = dir;
+            e.d_q_norm = b->q_norm; e.d_k_norm = b->k_norm;
+            e.d_rope_cos = d->cfg.rope_half ? d_cos + off : NULL; e.d_rope_sin = d->cfg.rope_half ? d_sin + off : NULL;
+            e.rope_half = d->cfg.rope_half; e.epsilon = d->cfg.eps; e.round_qkv = 1;
+            if (!h3b_gemm_i8_dev(d->cuda, b->lin[H3B_LIN_QKV], d->q8, d->s8, seq, NULL, &e, error, error_size)) return 0;
+            if (!h3b_ulysses_barrier(d->uly, error, error_size)) return 0;
+            if (!h3b_sdpa_bf16_scatter_dev(d->cuda, dir, seq_real, scale, error, error_size)) return 0;
+            if (!h3b_ulysses_barrier(d->uly, error, error_size)) return 0;
+            if (!norm_quant(d, dir->att, H3B_BF16, seq, I, NULL, NULL, NULL, 0, 0, 1, d->q8, d->s8, error, error_size)) return 0;
+            goto attention_done;
+        }
         if (!gemm(d, b->lin[H3B_LIN_QKV], d->q8, d->s8, seq, d->qkv, H3B_EPI_PLAIN, dt, NULL, NULL, NULL, 0, error,
                   error_size))
             return 0;
@@ -348,6 +371,7 @@ static int block_forward(h3b_dit *d, unsigned block, const void *d_x, size_t seq
             return 0;
     }
     if (!norm_quant(d, d->att, H3B_BF16, seq, I, NULL, NULL, NULL, 0, 0, 1, d->q8, d->s8, error, error_size)) return 0;
+attention_done:
     /* x1 -> xa */
     if (!gemm(d, b->lin[H3B_LIN_OUT], d->q8, d->s8, seq, d->xa, H3B_EPI_GATE, dt, d_x, mod, d_row_map, 2, error,
               error_size))

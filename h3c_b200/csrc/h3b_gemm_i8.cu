@@ -63,6 +63,10 @@ struct GemmParams {
     const float *q_norm, *k_norm, *cosT, *sinT;
     int rope_half, heads, round_qkv;
     float eps;
+    // optional scatter of the QKV+RoPE outputs by head group (sequence parallelism): head h of row r goes to
+    // sc_{q,k,v}[h / sc_hl] (possibly another GPU's memory) at row sc_row0 + r, head h % sc_hl; 0 = off
+    int sc_hl, sc_row0;
+    void *sc_q[8], *sc_k[8], *sc_v[8];
 };
 
 __device__ __forceinline__ void tile_coords(int tile, int m_tiles, int n_tiles, int &mt, int &nt) {
@@ -375,8 +379,16 @@ __global__ void __launch_bounds__(gemm::THREADS, 1) k_gemm_i8(const __grid_const
                             else if (p.rope_half == 64)
                                 rope_split_half<64>(v, p.cosT + (size_t)row * 64, p.sinT + (size_t)row * 64);
                         }
-                        __nv_bfloat16 *dst = reinterpret_cast<__nv_bfloat16 *>(which == 0 ? p.y : which == 1 ? p.y_k : p.y_v) +
-                                             ((size_t)row * p.heads + head) * 128;
+                        __nv_bfloat16 *dst;
+                        if (p.sc_hl) {
+                            const int peer = head / p.sc_hl;
+                            void *base = which == 0 ? p.sc_q[peer] : which == 1 ? p.sc_k[peer] : p.sc_v[peer];
+                            dst = reinterpret_cast<__nv_bfloat16 *>(base) +
+                                  ((size_t)(p.sc_row0 + row) * p.sc_hl + (head - peer * p.sc_hl)) * 128;
+                        } else {
+                            dst = reinterpret_cast<__nv_bfloat16 *>(which == 0 ? p.y : which == 1 ? p.y_k : p.y_v) +
+                                  ((size_t)row * p.heads + head) * 128;
+                        }
 #pragma unroll
                         for (int d = 0; d < 128; d += 8) OutTraits<__nv_bfloat16>::store(dst + d, &v[d]);
                     }
@@ -553,7 +565,8 @@ static int gemm_launch_e(h3_cuda *cuda, GemmParams &p, int out_dtype, char *erro
 int launch_gemm_i8(h3_cuda *cuda, const h3_cuda_w4a8_weight *w, const int8_t *x, const float *a, size_t m, void *y,
                    const h3b_gemm_epi *epi, char *error, size_t error_size) {
     using namespace gemm;
-    if (!cuda || !w || !x || !a || !y || !epi || m == 0) return fail(error, error_size, "gemm_i8: invalid arguments");
+    const h3b_ulysses_direct *sc = (epi && epi->kind == H3B_EPI_QKV_ROPE) ? epi->scatter : nullptr;
+    if (!cuda || !w || !x || !a || (!y && !sc) || !epi || m == 0) return fail(error, error_size, "gemm_i8: invalid arguments");
     if (!w->tmap_ok) return fail(error, error_size, "gemm_i8: weight has no tensor map (K %% 16 != 0?)");
     if (w->device != cuda->device) return fail(error, error_size, "gemm_i8: weight lives on device %d, handle on %d", w->device, cuda->device);
     const size_t N = w->n, K = w->k;
@@ -587,8 +600,20 @@ int launch_gemm_i8(h3_cuda *cuda, const h3_cuda_w4a8_weight *w, const int8_t *x,
     if (epi->kind == H3B_EPI_QKV_ROPE) {
         if (epi->out_dtype != H3B_BF16) return fail(error, error_size, "gemm_i8: the QKV+RoPE epilogue writes bf16");
         if (N % 384) return fail(error, error_size, "gemm_i8: QKV+RoPE needs N = 3 * heads * 128 (N=%zu)", N);
-        if (!epi->d_key || !epi->d_value || !epi->d_q_norm || !epi->d_k_norm)
+        if ((!sc && (!epi->d_key || !epi->d_value)) || !epi->d_q_norm || !epi->d_k_norm)
             return fail(error, error_size, "gemm_i8: QKV+RoPE needs key/value outputs and q/k norm weights");
+        if (sc) {
+            if (sc->ulysses < 1 || sc->ulysses > 8 || sc->rank < 0 || sc->rank >= sc->ulysses || sc->head_dim != 128 ||
+                sc->heads * 384 != N || sc->heads % (size_t)sc->ulysses || m > sc->seq_local)
+                return fail(error, error_size, "gemm_i8: scatter geometry does not match (N=%zu, m=%zu)", N, m);
+            p.sc_hl = (int)(sc->heads / (size_t)sc->ulysses);
+            p.sc_row0 = (int)((size_t)sc->rank * sc->seq_local);
+            for (int r = 0; r < sc->ulysses; r++) {
+                if (!sc->peer_q[r] || !sc->peer_k[r] || !sc->peer_v[r])
+                    return fail(error, error_size, "gemm_i8: scatter buffer of rank %d is not mapped", r);
+                p.sc_q[r] = sc->peer_q[r]; p.sc_k[r] = sc->peer_k[r]; p.sc_v[r] = sc->peer_v[r];
+            }
+        }
         if (epi->rope_half != 0 && epi->rope_half != 48 && epi->rope_half != 64)
             return fail(error, error_size, "gemm_i8: QKV+RoPE supports rope_half 0, 48 or 64 (got %zu)", epi->rope_half);
         if (epi->rope_half && (!epi->d_rope_cos || !epi->d_rope_sin)) return fail(error, error_size, "gemm_i8: rope tables missing");

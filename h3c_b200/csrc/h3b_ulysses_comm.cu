@@ -33,6 +33,8 @@ struct NcclApi {
     ncclResult_t (*Recv)(void *, size_t, ncclDataType_t, int, ncclComm_t, cudaStream_t);
     ncclResult_t (*GroupStart)(void);
     ncclResult_t (*GroupEnd)(void);
+    ncclResult_t (*AllGather)(const void *, void *, size_t, ncclDataType_t, ncclComm_t, cudaStream_t);
+    ncclResult_t (*AllReduce)(const void *, void *, size_t, ncclDataType_t, ncclRedOp_t, ncclComm_t, cudaStream_t);
     const char *(*GetErrorString)(ncclResult_t);
 };
 
@@ -53,10 +55,12 @@ static NcclApi *nccl_api(char *err, size_t err_size) {
             H3B_SYM(Recv, "ncclRecv");
             H3B_SYM(GroupStart, "ncclGroupStart");
             H3B_SYM(GroupEnd, "ncclGroupEnd");
+            H3B_SYM(AllGather, "ncclAllGather");
+            H3B_SYM(AllReduce, "ncclAllReduce");
             H3B_SYM(GetErrorString, "ncclGetErrorString");
 #undef H3B_SYM
             if (api.GetUniqueId && api.CommInitRank && api.CommInitAll && api.CommDestroy && api.Send && api.Recv &&
-                api.GroupStart && api.GroupEnd)
+                api.GroupStart && api.GroupEnd && api.AllGather && api.AllReduce)
                 state = 1;
         }
     }
@@ -82,6 +86,13 @@ struct CommState {
     size_t scratch_bytes[MAX_U];
     const void *bound_in[MAX_U];
     void *bound_out[MAX_U];
+    // direct stores (one owned rank only): this rank's slab [q | k | v | att], the peers' slabs as mapped
+    // here through CUDA IPC, and the one-word buffers of the barrier
+    h3b_ulysses_direct direct;
+    int direct_ready;
+    void *slab;
+    void *peer_slab[MAX_U];
+    int *d_barrier;
 };
 
 static int slot_of(const CommState *st, int rank) {
@@ -290,6 +301,13 @@ void h3_ulysses_comm_destroy(h3_ulysses_cfg *cfg) {
         if (st->stream[i]) cudaStreamSynchronize(st->stream[i]);
         if (api && st->comm[i]) api->CommDestroy(st->comm[i]);
         if (st->scratch[i]) cudaFree(st->scratch[i]);
+        if (i == 0) {
+            cudaDeviceSynchronize();
+            for (int pr = 0; pr < st->n_ranks; pr++)
+                if (st->peer_slab[pr] && st->peer_slab[pr] != st->slab) cudaIpcCloseMemHandle(st->peer_slab[pr]);
+            if (st->slab) cudaFree(st->slab);
+            if (st->d_barrier) cudaFree(st->d_barrier);
+        }
         if (st->ev_compute[i]) cudaEventDestroy(st->ev_compute[i]);
         if (st->ev_comm[i]) cudaEventDestroy(st->ev_comm[i]);
         if (st->stream[i]) cudaStreamDestroy(st->stream[i]);
@@ -384,6 +402,89 @@ int h3_ulysses_a2a_attn_out(h3_ulysses_cfg *cfg, const void *d_in, void *d_out, 
         if (cudaGetLastError() != cudaSuccess) return fail(err, err_size, "ulysses a2a_attn_out: unpack launch failed");
         if (!publish_comm(st, i, err, err_size)) return 0;
     }
+    return 1;
+}
+
+// ---------------------------------------------------------------- direct stores over peer memory
+
+int h3b_ulysses_direct_setup(h3_ulysses_cfg *cfg, size_t seq_local, size_t heads, size_t head_dim, char *err,
+                             size_t err_size) {
+    if (!cfg || !cfg->comm) return fail(err, err_size, "ulysses direct: not inited");
+    CommState *st = (CommState *)cfg->comm;
+    NcclApi *api = nccl_api(err, err_size);
+    if (!api) return 0;
+    if (st->n_local != 1) return fail(err, err_size, "ulysses direct: needs one process per GPU");
+    if (st->direct_ready) return fail(err, err_size, "ulysses direct: already set up");
+    if (!seq_local || !heads || !head_dim || heads % (size_t)st->n_ranks || (head_dim * 2) % 16)
+        return fail(err, err_size, "ulysses direct: bad geometry (seq_local %zu, heads %zu, head_dim %zu, U %d)", seq_local,
+                    heads, head_dim, st->n_ranks);
+    const int U = st->n_ranks, rank = st->local_rank[0];
+    if (cudaSetDevice(st->device[0]) != cudaSuccess) return fail(err, err_size, "ulysses direct: set device");
+    // the four buffers have the same size: U*seq_local rows of heads/U heads = seq_local rows of all heads
+    const size_t part = (seq_local * heads * head_dim * 2 + 255) & ~(size_t)255;
+    cudaError_t e = cudaMalloc(&st->slab, 4 * part);
+    if (e != cudaSuccess) return cuda_fail(e, "ulysses direct: slab allocation", err, err_size);
+    e = cudaMemset(st->slab, 0, 4 * part);
+    char *d_handles = NULL;
+    if (e == cudaSuccess) e = cudaMalloc((void **)&d_handles, (size_t)U * sizeof(cudaIpcMemHandle_t));
+    if (e == cudaSuccess) e = cudaMalloc((void **)&st->d_barrier, 2 * sizeof(int));
+    if (e == cudaSuccess) e = cudaMemset(st->d_barrier, 0, 2 * sizeof(int));
+    cudaIpcMemHandle_t mine, all[MAX_U];
+    if (e == cudaSuccess) e = cudaIpcGetMemHandle(&mine, st->slab);
+    if (e == cudaSuccess)
+        e = cudaMemcpy(d_handles + (size_t)rank * sizeof(mine), &mine, sizeof(mine), cudaMemcpyHostToDevice);
+    if (e != cudaSuccess) {
+        if (d_handles) cudaFree(d_handles);
+        return cuda_fail(e, "ulysses direct: IPC handle", err, err_size);
+    }
+    ncclResult_t rc = api->AllGather(d_handles + (size_t)rank * sizeof(mine), d_handles, sizeof(mine), ncclInt8, st->comm[0],
+                                     st->stream[0]);
+    if (rc != ncclSuccess) {
+        cudaFree(d_handles);
+        return fail(err, err_size, "ulysses direct: ncclAllGather failed: %s", api->GetErrorString ? api->GetErrorString(rc) : "error");
+    }
+    e = cudaStreamSynchronize(st->stream[0]);
+    if (e == cudaSuccess) e = cudaMemcpy(all, d_handles, (size_t)U * sizeof(mine), cudaMemcpyDeviceToHost);
+    cudaFree(d_handles);
+    if (e != cudaSuccess) return cuda_fail(e, "ulysses direct: handle exchange", err, err_size);
+    for (int pr = 0; pr < U; pr++) {
+        if (pr == rank) {
+            st->peer_slab[pr] = st->slab;
+            continue;
+        }
+        e = cudaIpcOpenMemHandle(&st->peer_slab[pr], all[pr], cudaIpcMemLazyEnablePeerAccess);
+        if (e != cudaSuccess) {
+            st->peer_slab[pr] = NULL;
+            return cuda_fail(e, "ulysses direct: cudaIpcOpenMemHandle (no peer access between the GPUs?)", err, err_size);
+        }
+    }
+    h3b_ulysses_direct *d = &st->direct;
+    d->ulysses = U; d->rank = rank; d->seq_local = seq_local; d->heads = heads; d->head_dim = head_dim;
+    for (int pr = 0; pr < U; pr++) {
+        char *b = (char *)st->peer_slab[pr];
+        d->peer_q[pr] = b; d->peer_k[pr] = b + part; d->peer_v[pr] = b + 2 * part; d->peer_att[pr] = b + 3 * part;
+    }
+    d->q = d->peer_q[rank]; d->k = d->peer_k[rank]; d->v = d->peer_v[rank]; d->att = d->peer_att[rank];
+    st->direct_ready = 1;
+    // nobody stores into a peer before every rank has mapped and zeroed its slab
+    return h3b_ulysses_barrier(cfg, err, err_size) && cudaStreamSynchronize(st->compute[0]) == cudaSuccess;
+}
+
+const h3b_ulysses_direct *h3b_ulysses_direct_get(const h3_ulysses_cfg *cfg) {
+    if (!cfg || !cfg->comm) return NULL;
+    const CommState *st = (const CommState *)cfg->comm;
+    return st->direct_ready ? &st->direct : NULL;
+}
+
+int h3b_ulysses_barrier(h3_ulysses_cfg *cfg, char *err, size_t err_size) {
+    if (!cfg || !cfg->comm) return fail(err, err_size, "ulysses barrier: not inited");
+    CommState *st = (CommState *)cfg->comm;
+    NcclApi *api = nccl_api(err, err_size);
+    if (!api) return 0;
+    if (st->n_local != 1 || !st->d_barrier) return fail(err, err_size, "ulysses barrier: direct mode is not set up");
+    ncclResult_t rc = api->AllReduce(st->d_barrier, st->d_barrier + 1, 1, ncclInt32, ncclSum, st->comm[0], st->compute[0]);
+    if (rc != ncclSuccess)
+        return fail(err, err_size, "ulysses barrier: ncclAllReduce failed: %s", api->GetErrorString ? api->GetErrorString(rc) : "error");
     return 1;
 }
 

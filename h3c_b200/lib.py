@@ -44,7 +44,8 @@ class DitGemmEpi(C.Structure):  # h3_cuda_dit_gemm_epi, the reference's epilogue
 class GemmEpi(C.Structure):  # h3b_gemm_epi
     _fields_ = [("kind", i32), ("out_dtype", i32), ("d_residual", vp), ("d_modulation", vp), ("d_row_map", vp),
                 ("slots", sz), ("gate_slot", sz), ("d_key", vp), ("d_value", vp), ("d_q_norm", vp), ("d_k_norm", vp),
-                ("d_rope_cos", vp), ("d_rope_sin", vp), ("rope_half", sz), ("epsilon", f32), ("round_qkv", i32)]
+                ("d_rope_cos", vp), ("d_rope_sin", vp), ("rope_half", sz), ("epsilon", f32), ("round_qkv", i32),
+                ("scatter", vp)]
 
 
 class NormArgs(C.Structure):  # h3b_norm_args
@@ -189,6 +190,10 @@ _SIGS = {
     "h3b_ulysses_unique_id": (i32, (vp,) + _ERR),
     "h3b_ulysses_comm_init_rank": (i32, (C.POINTER(UlyssesCfg), i32, i32, vp, i32) + _ERR),
     "h3b_dit_set_ulysses": (i32, (vp, C.POINTER(UlyssesCfg)) + _ERR),
+    "h3b_ulysses_direct_setup": (i32, (C.POINTER(UlyssesCfg), sz, sz, sz) + _ERR),
+    "h3b_ulysses_direct_get": (vp, (C.POINTER(UlyssesCfg),)),
+    "h3b_ulysses_barrier": (i32, (C.POINTER(UlyssesCfg),) + _ERR),
+    "h3b_sdpa_bf16_scatter_dev": (i32, (vp, vp, sz, f32) + _ERR),
     "h3b_dit_layers_forward_ulysses_dev": (i32, (vp, C.c_uint, C.c_uint, vp, sz, sz, vp, vp, vp, vp, sz, vp) + _ERR),
     "h3b_dit_layers_forward_ulysses_f32": (i32, (vp, C.c_uint, C.c_uint, vp, vp, sz, sz, vp, vp, vp, vp, sz, vp) + _ERR),
     "h3_ulysses_validate": (i32, (i32, i32, i32, i32, i32) + _ERR),

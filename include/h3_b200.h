@@ -237,6 +237,19 @@ enum {            /* epilogue kinds */
                             split-half RoPE of h3_dit_w4a8_qkv_rope_f32 (h3_dit_w4a8.c:2805) and write
                             Q / K / V [m, heads, 128] (d_y = Q, d_key, d_value), bf16 */
 };
+/* Addition (no counterpart in the reference): exchange-free Ulysses.  Every rank maps the gathered
+ * Q / K / V buffers and the attention-row buffer of all ranks (CUDA IPC), so that the QKV GEMM epilogue
+ * and the attention epilogue store each (row, head) slice straight into the memory of the rank that
+ * needs it, over NVLink, instead of packing, exchanging through NCCL and unpacking.  Filled by
+ * h3b_ulysses_direct_setup (below, with the other sequence-parallel calls). */
+typedef struct h3b_ulysses_direct {
+    int ulysses, rank;
+    size_t seq_local, heads, head_dim;   /* heads = all heads; a rank attends heads / ulysses of them */
+    void *q, *k, *v;   /* this rank's gathered Q, K, V: [ulysses*seq_local, heads/ulysses, head_dim] bf16 */
+    void *att;         /* this rank's attention rows: [seq_local, heads, head_dim] bf16 */
+    void *peer_q[8], *peer_k[8], *peer_v[8], *peer_att[8];   /* the same buffers of rank p, mapped here */
+} h3b_ulysses_direct;
+
 typedef struct h3b_gemm_epi {
     int kind;                    /* H3B_EPI_* */
     int out_dtype;               /* H3B_F32 / H3B_BF16 / H3B_F16 / H3B_I32 (plain only) */
@@ -252,6 +265,10 @@ typedef struct h3b_gemm_epi {
     float epsilon;
     int round_qkv;               /* 1: round the projection to out_dtype before the norm (what a stored
                                     intermediate would have been) */
+    /* H3B_EPI_QKV_ROPE, optional: row r, head h goes to scatter->peer_{q,k,v}[h / hl] at row
+     * rank*seq_local + r, head h % hl (hl = heads / ulysses); d_y / d_key / d_value are then unused.
+     * d_rope_cos / d_rope_sin are the rows of THIS rank ([m, rope_half]). */
+    const h3b_ulysses_direct *scatter;
 } h3b_gemm_epi;
 /* d_x_i8 [m,k] codes, d_act_scales [m]; d_y is [m,n] ([m,n/2] for swiglu). */
 int h3b_gemm_i8_dev(h3_cuda *cuda, const h3_cuda_w4a8_weight *weight, const int8_t *d_x_i8,
@@ -384,6 +401,11 @@ int h3b_sdpa_bf16_dev(h3_cuda *cuda, const void *d_q, size_t q_stride, const voi
                       size_t k_stride, const void *d_v, size_t v_stride, size_t lq, size_t lk,
                       size_t heads, size_t head_dim, float scale, void *d_out, size_t o_stride,
                       char *error, size_t error_size);
+/* Addition: the same attention over this rank's heads/ulysses heads of the gathered sequence
+ * (scatter->q, ->k, ->v, lq = lk = seq_real), each output row stored into scatter->peer_att of the
+ * rank that owns the row, at head rank*hl + h. */
+int h3b_sdpa_bf16_scatter_dev(h3_cuda *cuda, const h3b_ulysses_direct *scatter, size_t seq_real,
+                              float scale, char *error, size_t error_size);
 
 /* -------------------------------------------------------------------- NVFP4 */
 
@@ -536,6 +558,17 @@ int h3_ulysses_a2a_attn_out(h3_ulysses_cfg *cfg, const void *d_in, void *d_out, 
 int h3b_ulysses_unique_id(void *out128, char *err, size_t err_size);
 int h3b_ulysses_comm_init_rank(h3_ulysses_cfg *cfg, int rank, int world_size, const void *unique_id128,
                                int device, char *err, size_t err_size);
+/* Additions, one process per GPU only.  _direct_setup allocates this rank's four buffers (zeroed),
+ * exchanges their IPC handles through the communicator and maps the peers'; it is collective (every rank
+ * calls it with the same sizes) and synchronises the device.  Once set up, the sequence-parallel chain
+ * (h3b_dit_layers_forward_ulysses_*) of a context with matching geometry uses the direct stores and
+ * two h3b_ulysses_barrier calls per block instead of the two exchanges.  _direct_get returns NULL when
+ * nothing is set up.  _barrier: all ranks, enqueued on the rank's compute stream (one-word NCCL
+ * all-reduce); work enqueued after it on any rank starts only when every rank's earlier work is done. */
+int h3b_ulysses_direct_setup(h3_ulysses_cfg *cfg, size_t seq_local, size_t heads, size_t head_dim,
+                             char *err, size_t err_size);
+const h3b_ulysses_direct *h3b_ulysses_direct_get(const h3_ulysses_cfg *cfg);
+int h3b_ulysses_barrier(h3_ulysses_cfg *cfg, char *err, size_t err_size);
 /* Host f32 rows of this rank in and out (see h3b_dit_layers_forward_f32); rope tables cover all
  * U*seq_local rows. */
 int h3b_dit_layers_forward_ulysses_f32(h3b_dit *dit, unsigned first_block, unsigned n_blocks,

@@ -1,6 +1,7 @@
 """Two-GPU checks of the sequence-parallel path (skipped with fewer than two GPUs): the NCCL exchange is an
 exact permutation (the reference's own 2-GPU test, tests/test_h3_ulysses_a2a.cu, uses integer fills and
-max-abs == 0), and the Ulysses chain reproduces the single-GPU chain bit for bit on the real rows."""
+max-abs == 0), and the Ulysses chain reproduces the single-GPU chain bit for bit on the real rows, both
+through the NCCL exchange and through direct stores into the peers' memory."""
 import os
 import socket
 
@@ -79,8 +80,20 @@ def _worker(rank, world, port, out_dir):
                                          text=dev(text, torch.bfloat16),
                                          row_map=torch.zeros(sl, dtype=torch.int32, device="cuda"))
     cuda.check()
+    # the same chain with direct stores into peer memory instead of the NCCL exchange (collective set-up)
+    comm.setup_direct(sl, geo.heads, geo.head_dim)
+    y_direct = dit.layers_forward_ulysses(dev(x[first:first + sl], torch.bfloat16), seq_real, dev(cos_full), dev(sin_full),
+                                          text=dev(text, torch.bfloat16),
+                                          row_map=torch.zeros(sl, dtype=torch.int32, device="cuda"))
+    cuda.check()
+    y_direct2 = dit.layers_forward_ulysses(dev(x[first:first + sl], torch.bfloat16), seq_real, dev(cos_full), dev(sin_full),
+                                           text=dev(text, torch.bfloat16),
+                                           row_map=torch.zeros(sl, dtype=torch.int32, device="cuda"))
+    cuda.check()
     result["y_single"] = y_single.float().cpu().numpy()
     result["y_local"] = y_local.float().cpu().numpy()
+    result["y_direct"] = y_direct.float().cpu().numpy()
+    result["y_direct2"] = y_direct2.float().cpu().numpy()
     result["first"], result["real"] = first, real
     np.savez(os.path.join(out_dir, f"r{rank}.npz"), **result)
     dist.barrier()
@@ -107,3 +120,5 @@ def test_two_gpu_exchange_and_chain(tmp_path):
     for r in range(world):
         first, real = int(res[r]["first"]), int(res[r]["real"])
         assert np.array_equal(res[r]["y_local"][:real], res[r]["y_single"][first:first + real])
+        assert np.array_equal(res[r]["y_direct"][:real], res[r]["y_single"][first:first + real])
+        assert np.array_equal(res[r]["y_direct2"], res[r]["y_direct"])
