@@ -34,12 +34,20 @@ constexpr int A_BYTES = BM * BK;             // 16 KiB
 constexpr int THREADS = 320;
 constexpr int TMEM_COLS = 512;
 constexpr int GROUP_M = 8;       // rasterisation: bands of 8 row-tiles share the weight tiles in L2
-template <int CTAS> struct Shape {
-    static constexpr int STAGES = CTAS == 2 ? 6 : 4;
+// internal epilogue id: QKV + QK-norm + RoPE whose rows go to (peer) buffers selected by head group; the rows
+// are first transposed through shared memory so that every store instruction writes whole 256-byte head
+// slices (a thread-per-row store pattern reached 0.18 TB/s over NVLink)
+constexpr int EPI_QKV_ROPE_SCATTER = 5;
+constexpr int STG_ROW = 256 + 16;                 // staged bf16 head slice + pad against bank conflicts
+constexpr int STG_WARP = 32 * STG_ROW;            // per epilogue warp
+template <int CTAS, int EPI = 0> struct Shape {
+    static constexpr bool STAGED = EPI == EPI_QKV_ROPE_SCATTER;
+    static constexpr int STAGES = STAGED ? (CTAS == 2 ? 4 : 3) : CTAS == 2 ? 6 : 4;
     static constexpr int B_BYTES = BN * BK / CTAS;          // B rows held by one CTA: 32 KiB or 16 KiB
     static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;   // per CTA
     static constexpr int TILE_M = BM * CTAS;
-    static constexpr size_t SMEM_BYTES = 1024 /*alignment slack*/ + (size_t)STAGES * STAGE_BYTES + 256;
+    static constexpr size_t SMEM_BYTES = 1024 /*alignment slack*/ + (size_t)STAGES * STAGE_BYTES + 256 +
+                                         (STAGED ? 8 * (size_t)STG_WARP : 0);
 };
 }  // namespace gemm
 
@@ -169,8 +177,8 @@ template <> struct OutTraits<int32_t> {
 template <int EPI, typename OutT, int CTAS>
 __global__ void __launch_bounds__(gemm::THREADS, 1) k_gemm_i8(const __grid_constant__ GemmParams p) {
     using namespace gemm;
-    constexpr int STAGES = Shape<CTAS>::STAGES, STAGE_BYTES = Shape<CTAS>::STAGE_BYTES,
-                  B_BYTES = Shape<CTAS>::B_BYTES, TILE_M = Shape<CTAS>::TILE_M;
+    constexpr int STAGES = Shape<CTAS, EPI>::STAGES, STAGE_BYTES = Shape<CTAS, EPI>::STAGE_BYTES,
+                  B_BYTES = Shape<CTAS, EPI>::B_BYTES, TILE_M = Shape<CTAS, EPI>::TILE_M;
     extern __shared__ uint8_t smem_raw[];
     // 1024-byte alignment: required by the 128-byte swizzle pattern of TMA and the MMA descriptors
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
@@ -324,7 +332,7 @@ __global__ void __launch_bounds__(gemm::THREADS, 1) k_gemm_i8(const __grid_const
             bool ok = mbar_wait(&tmem_full[buf], (it >> 1) & 1, abort_word, p.status, H3B_ST_TIMEOUT_TMEM_FULL);
             tc_fence_after();
             const uint32_t t_addr = tmem_base + lane_base + (uint32_t)buf * BN;
-            if constexpr (EPI == H3B_EPI_QKV_ROPE) {
+            if constexpr (EPI == H3B_EPI_QKV_ROPE || EPI == EPI_QKV_ROPE_SCATTER) {
                 // This warp's 128 columns are exactly one head of Q, K or V; the thread holds its row of it.
                 const int col = c0 + half * 128;
                 if (ok && col < p.N) {
@@ -379,18 +387,35 @@ __global__ void __launch_bounds__(gemm::THREADS, 1) k_gemm_i8(const __grid_const
                             else if (p.rope_half == 64)
                                 rope_split_half<64>(v, p.cosT + (size_t)row * 64, p.sinT + (size_t)row * 64);
                         }
-                        __nv_bfloat16 *dst;
-                        if (p.sc_hl) {
-                            const int peer = head / p.sc_hl;
-                            void *base = which == 0 ? p.sc_q[peer] : which == 1 ? p.sc_k[peer] : p.sc_v[peer];
-                            dst = reinterpret_cast<__nv_bfloat16 *>(base) +
-                                  ((size_t)(p.sc_row0 + row) * p.sc_hl + (head - peer * p.sc_hl)) * 128;
-                        } else {
-                            dst = reinterpret_cast<__nv_bfloat16 *>(which == 0 ? p.y : which == 1 ? p.y_k : p.y_v) +
-                                  ((size_t)row * p.heads + head) * 128;
-                        }
+                        if constexpr (EPI == H3B_EPI_QKV_ROPE) {
+                            __nv_bfloat16 *dst = reinterpret_cast<__nv_bfloat16 *>(which == 0 ? p.y : which == 1 ? p.y_k : p.y_v) +
+                                                 ((size_t)row * p.heads + head) * 128;
 #pragma unroll
-                        for (int d = 0; d < 128; d += 8) OutTraits<__nv_bfloat16>::store(dst + d, &v[d]);
+                            for (int d = 0; d < 128; d += 8) OutTraits<__nv_bfloat16>::store(dst + d, &v[d]);
+                        }
+                    }
+                    if constexpr (EPI == EPI_QKV_ROPE_SCATTER) {
+                        // lane = row: park the head slices of the warp's 32 rows in shared memory, then let sixteen
+                        // lanes write one 256-byte slice each, two rows per store instruction
+                        uint8_t *stg = smem + (size_t)STAGES * STAGE_BYTES + 256 + (size_t)(warp - 2) * STG_WARP;
+#pragma unroll
+                        for (int d = 0; d < 128; d += 8)
+                            OutTraits<__nv_bfloat16>::store(reinterpret_cast<__nv_bfloat16 *>(stg + lane * STG_ROW) + d, &v[d]);
+                        __syncwarp();
+                        const int peer = head / p.sc_hl;
+                        uint8_t *base = reinterpret_cast<uint8_t *>(which == 0 ? p.sc_q[peer] : which == 1 ? p.sc_k[peer] : p.sc_v[peer]);
+                        const int row_first = mt * TILE_M + cta_rank * BM + q * 32;   // row of lane 0
+                        const size_t row_pitch = (size_t)p.sc_hl * 256;
+                        uint8_t *dst0 = base + ((size_t)(p.sc_row0 + row_first) * p.sc_hl + (head - peer * p.sc_hl)) * 256;
+                        const int sub = lane >> 4, chunk = lane & 15;
+#pragma unroll
+                        for (int k2 = 0; k2 < 16; k2++) {
+                            const int rr = 2 * k2 + sub;
+                            if (row_first + rr < p.M)
+                                *reinterpret_cast<uint4 *>(dst0 + (size_t)rr * row_pitch + chunk * 16) =
+                                    *reinterpret_cast<const uint4 *>(stg + rr * STG_ROW + chunk * 16);
+                        }
+                        __syncwarp();
                     }
                 }
             } else
@@ -507,7 +532,7 @@ static int gemm_launch_t(h3_cuda *cuda, GemmParams &p, char *error, size_t error
     }();
     if (pairs_allowed && p.M > BM) {
         auto kern = k_gemm_i8<EPI, OutT, 2>;
-        constexpr size_t smem = Shape<2>::SMEM_BYTES;
+        constexpr size_t smem = Shape<2, EPI>::SMEM_BYTES;
         // co-resident pairs on this device (an SM without a free neighbour cannot host half a pair);
         // asked once per kernel and device
         static int max_pairs[64];
@@ -531,7 +556,7 @@ static int gemm_launch_t(h3_cuda *cuda, GemmParams &p, char *error, size_t error
             if (n < 1) return fail(error, error_size, "gemm_i8: no CTA pair fits on this device");
             max_pairs[dev] = n;
         }
-        p.m_tiles = (p.M + Shape<2>::TILE_M - 1) / Shape<2>::TILE_M;
+        p.m_tiles = (p.M + Shape<2, EPI>::TILE_M - 1) / Shape<2, EPI>::TILE_M;
         const int tiles = p.m_tiles * p.n_tiles;
         const int n_pairs = tiles < max_pairs[dev] ? tiles : max_pairs[dev];
         cfg.gridDim = dim3((unsigned)(2 * n_pairs));
@@ -541,12 +566,12 @@ static int gemm_launch_t(h3_cuda *cuda, GemmParams &p, char *error, size_t error
         return 1;
     }
     auto kern = k_gemm_i8<EPI, OutT, 1>;
-    H3B_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Shape<1>::SMEM_BYTES),
+    H3B_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Shape<1, EPI>::SMEM_BYTES),
                 "gemm smem attribute");
     int tiles = p.m_tiles * p.n_tiles;
     int grid = tiles < cuda->sm_count ? tiles : cuda->sm_count;
     ProfScope prof(cuda, PROF_GEMM);
-    kern<<<grid, THREADS, Shape<1>::SMEM_BYTES, cuda->op_stream>>>(p);
+    kern<<<grid, THREADS, Shape<1, EPI>::SMEM_BYTES, cuda->op_stream>>>(p);
     cuda->launches++;
     H3B_CUDA_OK(cudaGetLastError(), "k_gemm_i8 launch");
     return 1;
@@ -623,6 +648,7 @@ int launch_gemm_i8(h3_cuda *cuda, const h3_cuda_w4a8_weight *w, const int8_t *x,
         p.y_k = epi->d_key; p.y_v = epi->d_value; p.q_norm = epi->d_q_norm; p.k_norm = epi->d_k_norm;
         p.cosT = epi->d_rope_cos; p.sinT = epi->d_rope_sin; p.rope_half = (int)epi->rope_half;
         p.heads = (int)(N / 384); p.eps = epi->epsilon; p.round_qkv = epi->round_qkv;
+        if (sc) return gemm_launch_t<gemm::EPI_QKV_ROPE_SCATTER, __nv_bfloat16>(cuda, p, error, error_size);
         return gemm_launch_t<H3B_EPI_QKV_ROPE, __nv_bfloat16>(cuda, p, error, error_size);
     }
     switch (epi->kind) {
