@@ -274,8 +274,16 @@ def gpu_arm(args):
         comm = h3c_b200.UlyssesComm(rank, world, bytes(uid.cpu().numpy().tobytes()), local)
         comm.set_compute(torch.cuda.current_stream())
         if os.environ.get("H3B_ULYSSES_DIRECT", "1") != "0":
-            # peers' Q/K/V and attention-row buffers mapped into this rank: the epilogues store across NVLink
-            comm.setup_direct(seq_local, geo.heads, geo.head_dim)
+            # peers' Q/K/V and attention-row buffers mapped into this rank: the epilogues store across NVLink.
+            # If the mapping fails on any rank (no peer access), every rank falls back to the NCCL exchange.
+            ok = torch.ones(1, dtype=torch.int32, device="cuda")
+            try:
+                comm.setup_direct(seq_local, geo.heads, geo.head_dim)
+            except h3c_b200.H3Error as exc:
+                print(f"rank {rank}: direct stores unavailable ({exc}); using the exchange", file=sys.stderr)
+                ok.zero_()
+            dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+            comm.enable_direct(bool(ok.item()))
         dit.set_ulysses(comm)
     rows = seq_local if world > 1 else seq_real
     oracle = Oracle()
@@ -406,6 +414,9 @@ def gpu_arm(args):
             cpu_ms, cpu_desc = cpu_block_sample(kind, os.cpu_count() or 1, grid=grid)
             cpu = {"value": cpu_ms, "unit": UNIT, "cores": os.cpu_count() or 1, "kind": kind, "sample": cpu_desc}
         cfg = workload_config(world, ulysses)
+        if comm is not None:
+            cfg["exchange"] = ("direct stores into peer memory from the QKV and attention epilogues + 2 barriers per block"
+                               if comm.direct else "NCCL send/recv all-to-all around self-attention")
         line = {"metric": METRIC, "value": ms_step, "unit": UNIT, "n_gpus": world, "steps": args.steps,
                 "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": False,
                 "scaling": "strong" if ulysses else "weak", "vs_baseline": None,

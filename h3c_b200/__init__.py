@@ -368,6 +368,13 @@ class UlyssesComm:
         then stores into peer memory from the GEMM and attention epilogues instead of exchanging."""
         call("h3b_ulysses_direct_setup", C.byref(self.cfg), seq_local, heads, head_dim)
 
+    def enable_direct(self, on: bool):
+        load().h3b_ulysses_direct_enable(C.byref(self.cfg), int(on))
+
+    @property
+    def direct(self) -> bool:
+        return bool(load().h3b_ulysses_direct_get(C.byref(self.cfg)))
+
     def barrier(self):
         call("h3b_ulysses_barrier", C.byref(self.cfg))
 

@@ -89,7 +89,7 @@ struct CommState {
     // direct stores (one owned rank only): this rank's slab [q | k | v | att], the peers' slabs as mapped
     // here through CUDA IPC, and the one-word buffers of the barrier
     h3b_ulysses_direct direct;
-    int direct_ready;
+    int direct_ready, direct_off;
     void *slab;
     void *peer_slab[MAX_U];
     int *d_barrier;
@@ -447,6 +447,7 @@ int h3b_ulysses_direct_setup(h3_ulysses_cfg *cfg, size_t seq_local, size_t heads
     if (e == cudaSuccess) e = cudaMemcpy(all, d_handles, (size_t)U * sizeof(mine), cudaMemcpyDeviceToHost);
     cudaFree(d_handles);
     if (e != cudaSuccess) return cuda_fail(e, "ulysses direct: handle exchange", err, err_size);
+    int mapped = 1;
     for (int pr = 0; pr < U; pr++) {
         if (pr == rank) {
             st->peer_slab[pr] = st->slab;
@@ -455,8 +456,27 @@ int h3b_ulysses_direct_setup(h3_ulysses_cfg *cfg, size_t seq_local, size_t heads
         e = cudaIpcOpenMemHandle(&st->peer_slab[pr], all[pr], cudaIpcMemLazyEnablePeerAccess);
         if (e != cudaSuccess) {
             st->peer_slab[pr] = NULL;
-            return cuda_fail(e, "ulysses direct: cudaIpcOpenMemHandle (no peer access between the GPUs?)", err, err_size);
+            cuda_fail(e, "ulysses direct: cudaIpcOpenMemHandle (no peer access between the GPUs?)", err, err_size);
+            mapped = 0;
         }
+    }
+    // Every rank reaches this reduction whether or not its own mappings worked, and all of them take the
+    // same decision: a rank that returned early would leave the others waiting in the collective.
+    int agreed = 0;
+    e = cudaMemcpy(st->d_barrier, &mapped, sizeof(int), cudaMemcpyHostToDevice);
+    if (e == cudaSuccess) {
+        rc = api->AllReduce(st->d_barrier, st->d_barrier + 1, 1, ncclInt32, ncclMin, st->comm[0], st->stream[0]);
+        if (rc == ncclSuccess && cudaStreamSynchronize(st->stream[0]) == cudaSuccess)
+            cudaMemcpy(&agreed, st->d_barrier + 1, sizeof(int), cudaMemcpyDeviceToHost);
+    }
+    cudaMemset(st->d_barrier, 0, 2 * sizeof(int));
+    if (!agreed) {
+        for (int pr = 0; pr < U; pr++) {
+            if (st->peer_slab[pr] && st->peer_slab[pr] != st->slab) cudaIpcCloseMemHandle(st->peer_slab[pr]);
+            st->peer_slab[pr] = NULL;
+        }
+        if (mapped) fail(err, err_size, "ulysses direct: another rank could not map the peers' buffers");
+        return 0;
     }
     h3b_ulysses_direct *d = &st->direct;
     d->ulysses = U; d->rank = rank; d->seq_local = seq_local; d->heads = heads; d->head_dim = head_dim;
@@ -473,7 +493,11 @@ int h3b_ulysses_direct_setup(h3_ulysses_cfg *cfg, size_t seq_local, size_t heads
 const h3b_ulysses_direct *h3b_ulysses_direct_get(const h3_ulysses_cfg *cfg) {
     if (!cfg || !cfg->comm) return NULL;
     const CommState *st = (const CommState *)cfg->comm;
-    return st->direct_ready ? &st->direct : NULL;
+    return (st->direct_ready && !st->direct_off) ? &st->direct : NULL;
+}
+
+void h3b_ulysses_direct_enable(h3_ulysses_cfg *cfg, int on) {
+    if (cfg && cfg->comm) ((CommState *)cfg->comm)->direct_off = !on;
 }
 
 int h3b_ulysses_barrier(h3_ulysses_cfg *cfg, char *err, size_t err_size) {

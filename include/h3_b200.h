@@ -563,11 +563,14 @@ int h3b_ulysses_comm_init_rank(h3_ulysses_cfg *cfg, int rank, int world_size, co
  * calls it with the same sizes) and synchronises the device.  Once set up, the sequence-parallel chain
  * (h3b_dit_layers_forward_ulysses_*) of a context with matching geometry uses the direct stores and
  * two h3b_ulysses_barrier calls per block instead of the two exchanges.  _direct_get returns NULL when
- * nothing is set up.  _barrier: all ranks, enqueued on the rank's compute stream (one-word NCCL
+ * nothing is set up or the path is switched off.  _barrier: all ranks, enqueued on the rank's compute stream (one-word NCCL
  * all-reduce); work enqueued after it on any rank starts only when every rank's earlier work is done. */
 int h3b_ulysses_direct_setup(h3_ulysses_cfg *cfg, size_t seq_local, size_t heads, size_t head_dim,
                              char *err, size_t err_size);
 const h3b_ulysses_direct *h3b_ulysses_direct_get(const h3_ulysses_cfg *cfg);
+/* Switches the use of a set-up direct path off (0) or back on (1); the mappings stay.  For launchers that
+ * found the set-up failing on some rank and fall back to the exchange on all of them. */
+void h3b_ulysses_direct_enable(h3_ulysses_cfg *cfg, int on);
 int h3b_ulysses_barrier(h3_ulysses_cfg *cfg, char *err, size_t err_size);
 /* Host f32 rows of this rank in and out (see h3b_dit_layers_forward_f32); rope tables cover all
  * U*seq_local rows. */
