@@ -321,32 +321,44 @@ __global__ void __launch_bounds__(attn::THREADS, 1) k_attn_bf16(const __grid_con
         if (t < n_tiles) {
             if (ok) ok = mbar_wait(o_done, 0, abort_word, p.status, H3B_ST_TIMEOUT_OTHER);
             tc_fence_after();
-            const int row = q0 + t * BQ + r;
             const float inv_l = 1.0f / l_run;
-            __nv_bfloat16 *dst;
-            if (p.sc_rows) {
-                const int owner = row / p.sc_rows;
-                dst = p.sc_out[owner < 8 ? owner : 0] +
-                      ((size_t)(row - owner * p.sc_rows) * p.sc_heads + p.sc_head0 + head) * HD;
-            } else {
-                dst = p.out + (size_t)row * p.o_stride + (size_t)head * HD;
-            }
+            // All MMAs and loads of the CTA are done: its tile memory is free.  Lane = row here; the rows of
+            // the warp are parked in shared memory and written out sixteen lanes per 256-byte head slice,
+            // two rows per store instruction (whole slices matter when the owner of a row is another GPU).
+            constexpr int STG_ROW = 256 + 16;
+            uint8_t *stg = smem + (size_t)(warp - 2) * 32 * STG_ROW;
 #pragma unroll 1
             for (int ch = 0; ch < HD / 32; ch++) {
                 uint32_t o[32];
                 tmem_ld_32x32b_x32(o_addr + ch * 32, o);
                 tmem_ld_wait();
+#pragma unroll
+                for (int i = 0; i < 32; i += 8) {
+                    uint4 raw;
+                    __nv_bfloat162 *h = reinterpret_cast<__nv_bfloat162 *>(&raw);
+#pragma unroll
+                    for (int u = 0; u < 4; u++)
+                        h[u] = __floats2bfloat162_rn(__uint_as_float(o[i + 2 * u]) * inv_l,
+                                                     __uint_as_float(o[i + 2 * u + 1]) * inv_l);
+                    *reinterpret_cast<uint4 *>(stg + lane * STG_ROW + (ch * 32 + i) * 2) = raw;
+                }
+            }
+            __syncwarp();
+            const int row_first = q0 + t * BQ + q * 32;   // row of lane 0
+            const int sub = lane >> 4, chunk = lane & 15;
+#pragma unroll
+            for (int k2 = 0; k2 < 16; k2++) {
+                const int rr = 2 * k2 + sub, row = row_first + rr;
                 if (ok && row < p.lq) {
-#pragma unroll
-                    for (int i = 0; i < 32; i += 8) {
-                        uint4 raw;
-                        __nv_bfloat162 *h = reinterpret_cast<__nv_bfloat162 *>(&raw);
-#pragma unroll
-                        for (int u = 0; u < 4; u++)
-                            h[u] = __floats2bfloat162_rn(__uint_as_float(o[i + 2 * u]) * inv_l,
-                                                         __uint_as_float(o[i + 2 * u + 1]) * inv_l);
-                        *reinterpret_cast<uint4 *>(dst + ch * 32 + i) = raw;
+                    __nv_bfloat16 *dst;
+                    if (p.sc_rows) {
+                        const int owner = row / p.sc_rows;
+                        dst = p.sc_out[owner < 8 ? owner : 0] +
+                              ((size_t)(row - owner * p.sc_rows) * p.sc_heads + p.sc_head0 + head) * HD;
+                    } else {
+                        dst = p.out + (size_t)row * p.o_stride + (size_t)head * HD;
                     }
+                    *reinterpret_cast<uint4 *>(dst + chunk * 8) = *reinterpret_cast<const uint4 *>(stg + rr * STG_ROW + chunk * 16);
                 }
             }
         }
