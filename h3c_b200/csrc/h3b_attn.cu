@@ -13,8 +13,12 @@
 //   warps 2-5   softmax of tile A, warps 6-9 softmax of tile B: one query row per thread.
 //               The 128 scores of the row are read from TMEM into registers once; maximum,
 //               exponentials and row sum are computed there and P (bf16 pairs) is written back
-//               to TMEM over the score columns.  The accumulator is rescaled only when the running maximum grew
-//               by more than 2^8; the final division by the row sum undoes the stale scale.
+//               to TMEM over the score columns, handed to the MMA warp in two halves of 64 keys.
+//               The accumulator is rescaled only when the running maximum grew by more than 2^8;
+//               the final division by the row sum undoes the stale scale.  At the end the rows go
+//               through the CTA's (then free) tile memory so that each store instruction writes
+//               whole 256-byte head slices, to this GPU's output or, under sequence parallelism,
+//               to the mapped buffer of the rank that owns the row.
 // TMEM (512 columns): S_A 0..127, S_B 128..255 (P overlays the first 64 columns of each),
 // O_A 256..383, O_B 384..511.
 #include <cuda_bf16.h>

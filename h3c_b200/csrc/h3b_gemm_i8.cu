@@ -12,7 +12,9 @@
 //              two 256-column TMEM accumulators; tcgen05.commit frees the stage in both CTAs
 //   warps 2-9  epilogue: tcgen05.ld the finished accumulator (one output row and half of the
 //              tile's columns per thread), scale, apply gate+residual / SwiGLU / tanh-GELU,
-//              store.  Runs while the MMA warp fills the other accumulator.
+//              store.  Runs while the MMA warp fills the other accumulator.  The QKV epilogue applies
+//              QK-norm and split-half RoPE to whole heads in registers and can scatter the head slices
+//              to per-rank (peer) buffers through a shared-memory transpose.
 // Accumulators are exact int32, so the integer part is bit-identical to
 // h3_w4a8_gemm_i8_dequant_f32 (h3_w4a8_dequant.c:692); the float part follows the
 // reference's operation order (a * s) * (float)acc and h3_dit_fused_epi.h:87-141.
