@@ -321,6 +321,24 @@ def gpu_arm(args):
         else:
             dit.layers_forward(x_d, cos_d, sin_d, row_map=rmap_d, text=text_d, out=y_d)
 
+    if args.graph and world == 1:
+        # The resident step as one CUDA graph: the chain allocates nothing after `reserve` and syncs nowhere,
+        # so its ~800 launches can be captured once and replayed (removes the host launch gaps).
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            cuda.use_stream(side)
+            step_resident()   # first launches of every kernel happen outside the capture
+            side.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            cuda.launch_count(reset=True)
+            with torch.cuda.graph(graph, stream=side):
+                step_resident()
+            graph_launches = cuda.launch_count(reset=True)   # kernel nodes of one replay
+        torch.cuda.current_stream().wait_stream(side)
+        cuda.use_stream(torch.cuda.current_stream())
+        eager_step, step_resident = step_resident, graph.replay
+
     def step_e2e():
         if world > 1:
             dit.layers_forward_ulysses_f32(t_feat_h, x_h, seq_real, cos_p, sin_p, text=text_h, out=y_h)
@@ -357,11 +375,13 @@ def gpu_arm(args):
     e1.record()
     sync_all()
     launches = cuda.launch_count(reset=True)
+    if args.graph and world == 1:
+        launches = graph_launches * args.steps
     ms_step = max_over_ranks(e0.elapsed_time(e1) / args.steps)
     clocks = sampler.stop()
     cuda.check()
 
-    prof = profile_classes(cuda, dit, step_resident)
+    prof = profile_classes(cuda, dit, eager_step if (args.graph and world == 1) else step_resident)
     sync_all()
 
     e2e_ms = None
@@ -414,6 +434,8 @@ def gpu_arm(args):
             cpu_ms, cpu_desc = cpu_block_sample(kind, os.cpu_count() or 1, grid=grid)
             cpu = {"value": cpu_ms, "unit": UNIT, "cores": os.cpu_count() or 1, "kind": kind, "sample": cpu_desc}
         cfg = workload_config(world, ulysses)
+        if args.graph and world == 1:
+            cfg["launch"] = "one CUDA graph replay per step"
         if comm is not None:
             cfg["exchange"] = ("direct stores into peer memory from the QKV and attention epilogues + 2 barriers per block"
                                if comm.direct else "NCCL send/recv all-to-all around self-attention")
@@ -517,6 +539,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="auto", choices=["auto", "ulysses", "step6144"],
                     help="auto / ulysses: the 50,220-token step at any N; step6144: the 6,144-token single-GPU step")
+    ap.add_argument("--graph", action="store_true", help="replay the resident step as one CUDA graph (N = 1)")
     ap.add_argument("--skip-cpu-baseline", action="store_true", help="omit the CPU sample (profiling runs)")
     ap.add_argument("--skip-e2e", action="store_true", help="omit the host-buffer measurement (profiling runs)")
     args = ap.parse_args()
