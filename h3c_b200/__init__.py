@@ -216,6 +216,18 @@ class Cuda:
         call("h3b_gemm_i8_dev", self.h, weight.h, ptr(x_i8), ptr(act_scales), m, ptr(q), C.byref(e))
         return q, k, v
 
+    def gemm_i8_qkv_rope_scatter(self, weight: Weight, x_i8, act_scales, q_norm, k_norm, cos, sin, rope_half,
+                                 direct: "_l.UlyssesDirect", eps=1e-5):
+        """The same projection with every (row, head) slice stored into direct.peer_{q,k,v}[head // hl]."""
+        e = _l.GemmEpi(_l.EPI_QKV_ROPE, BF16, None, None, None, 0, 0, None, None, ptr(q_norm), ptr(k_norm), ptr(cos),
+                       ptr(sin), rope_half, eps, 1, C.addressof(direct))
+        call("h3b_gemm_i8_dev", self.h, weight.h, ptr(x_i8), ptr(act_scales), x_i8.shape[0], None, C.byref(e))
+
+    def sdpa_bf16_scatter(self, direct: "_l.UlyssesDirect", seq_real, scale=None):
+        """Attention over direct.q/k/v (this rank's heads of the gathered sequence); rows go to direct.peer_att."""
+        call("h3b_sdpa_bf16_scatter_dev", self.h, C.addressof(direct), seq_real,
+             float(scale if scale is not None else direct.head_dim ** -0.5))
+
     def gemm_i8_dequant_f32_w_act_dev(self, weight: Weight, x_f32, convrot_gs=0, epi: _l.DitGemmEpi | None = None):
         import torch
         m = x_f32.shape[0]

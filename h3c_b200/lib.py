@@ -61,6 +61,12 @@ class DitConfig(C.Structure):  # h3b_dit_config
                 ("eps", f32)]
 
 
+class UlyssesDirect(C.Structure):  # h3b_ulysses_direct
+    _fields_ = [("ulysses", i32), ("rank", i32), ("seq_local", sz), ("heads", sz), ("head_dim", sz),
+                ("q", vp), ("k", vp), ("v", vp), ("att", vp),
+                ("peer_q", vp * 8), ("peer_k", vp * 8), ("peer_v", vp * 8), ("peer_att", vp * 8)]
+
+
 class UlyssesCfg(C.Structure):  # h3_ulysses_cfg
     _fields_ = [("tp_size", i32), ("ulysses", i32), ("ring", i32), ("rank", i32), ("world_size", i32), ("comm", vp)]
 

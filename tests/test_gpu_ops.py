@@ -431,3 +431,49 @@ def test_host_buffer_adaln(cuda, oracle):
     mod = rng.normal(0, 0.3, (3, 6, 64)).astype(np.float32)
     rmap = (np.arange(9) % 3).astype(np.uint32)
     assert rel_l2(cuda.adaln_f32(x, nw, mod, rmap, 6, 0, 1), oracle.adaln(x, nw, mod, rmap, 6, 0, 1)) < 2e-6
+
+
+def test_scatter_epilogues_on_one_gpu(cuda, oracle):
+    """The sequence-parallel stores of the QKV GEMM epilogue and of the attention epilogue, exercised on one
+    GPU: two emulated ranks whose "peer" buffers are all local.  Gathered Q/K/V must be the plain kernel's
+    output permuted by the reference's all-to-all map, and the scattered attention rows the plain
+    attention's output, bit for bit."""
+    from h3c_b200.lib import UlyssesDirect
+    rng = np.random.default_rng(41)
+    u, heads, hd, k, seq_local = 2, 4, 128, 256, 150          # seq_local not a multiple of the row tile
+    hl, seq = heads // u, u * seq_local
+    pt, ph, pw = oracle.fill_video_pos(16, 12, 10, 10)
+    inv_freq = (1.0 / (10000.0 ** (np.arange(16) / 16.0))).astype(np.float32)
+    cos, sin = oracle.rope_tables(inv_freq, pt[:seq], ph[:seq], pw[:seq], 1.0)
+    w, w_i8, s = make_weight(cuda, rng, 3 * heads * hd, k)
+    xq, xs = oracle.quantize_act_int8(acts(rng, seq, k))
+    qn, kn = rng.normal(1, 0.1, hd).astype(np.float32), rng.normal(1, 0.1, hd).astype(np.float32)
+    dqn, dkn, dcos, dsin = dev(qn), dev(kn), dev(cos), dev(sin)
+    q_ref, k_ref, v_ref = cuda.gemm_i8_qkv_rope(w, dev(xq), dev(xs), dqn, dkn, dcos, dsin, 48)   # [seq, heads, hd]
+    # per emulated rank: gathered Q/K/V [seq, hl, hd] and attention rows [seq_local, heads, hd]
+    gq, gk, gv = ([torch.zeros((seq, hl, hd), dtype=torch.bfloat16, device="cuda") for _ in range(u)] for _ in range(3))
+    att = [torch.zeros((seq_local, heads, hd), dtype=torch.bfloat16, device="cuda") for _ in range(u)]
+    directs = []
+    for r in range(u):
+        d = UlyssesDirect()
+        d.ulysses, d.rank, d.seq_local, d.heads, d.head_dim = u, r, seq_local, heads, hd
+        d.q, d.k, d.v, d.att = gq[r].data_ptr(), gk[r].data_ptr(), gv[r].data_ptr(), att[r].data_ptr()
+        for p_ in range(u):
+            d.peer_q[p_], d.peer_k[p_], d.peer_v[p_] = gq[p_].data_ptr(), gk[p_].data_ptr(), gv[p_].data_ptr()
+            d.peer_att[p_] = att[p_].data_ptr()
+        directs.append(d)
+    for r in range(u):
+        rows = slice(r * seq_local, (r + 1) * seq_local)
+        cuda.gemm_i8_qkv_rope_scatter(w, dev(xq[rows]), dev(xs[rows]), dqn, dkn, dev(cos[rows]), dev(sin[rows]), 48,
+                                      directs[r])
+    cuda.check()
+    for r in range(u):
+        for got, ref in ((gq[r], q_ref), (gk[r], k_ref), (gv[r], v_ref)):
+            assert torch.equal(got, ref[:, r * hl:(r + 1) * hl])
+    seq_real = seq - 7                                            # pad rows stay zero
+    o_ref = cuda.sdpa_bf16(q_ref[:seq_real], k_ref[:seq_real], v_ref[:seq_real]).view(seq_real, heads, hd)
+    for r in range(u):
+        cuda.sdpa_bf16_scatter(directs[r], seq_real)
+    cuda.check()
+    got = torch.cat(att, 0)
+    assert torch.equal(got[:seq_real], o_ref) and not got[seq_real:].any()
