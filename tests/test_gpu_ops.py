@@ -477,3 +477,24 @@ def test_scatter_epilogues_on_one_gpu(cuda, oracle):
     cuda.check()
     got = torch.cat(att, 0)
     assert torch.equal(got[:seq_real], o_ref) and not got[seq_real:].any()
+
+
+def test_empty_and_misaligned_inputs_are_refused(cuda):
+    """Zero-sized or misaligned calls return the reference-style error instead of launching anything."""
+    import h3c_b200
+    rng = np.random.default_rng(42)
+    w, _, _ = make_weight(cuda, rng, 128, 128)
+    x0 = torch.empty((0, 128), dtype=torch.int8, device="cuda")
+    with pytest.raises(h3c_b200.H3Error):
+        cuda.gemm_i8(w, x0, torch.empty(0, device="cuda"))
+    with pytest.raises(h3c_b200.H3Error):
+        cuda.quantize_act_int8(torch.empty((0, 128), device="cuda"))
+    q = torch.zeros((8, 2, 128), dtype=torch.bfloat16, device="cuda")
+    with pytest.raises(h3c_b200.H3Error):
+        cuda.sdpa_bf16(q[:0], q, q)
+    with pytest.raises(h3c_b200.H3Error):                       # head_dim 64 is not built
+        cuda.sdpa_bf16(q[..., :64].contiguous(), q[..., :64].contiguous(), q[..., :64].contiguous())
+    xq = torch.zeros((9, 129), dtype=torch.int8, device="cuda")[:, 1:]   # rows not 16-byte aligned
+    with pytest.raises(h3c_b200.H3Error):
+        cuda.gemm_i8(w, xq, torch.ones(9, device="cuda"))
+    cuda.check()
