@@ -194,7 +194,7 @@ class Cuda:
 
     # ---- linears
     def gemm_i8(self, weight: Weight, x_i8, act_scales, *, kind=EPI_PLAIN, out_dtype=None, residual=None,
-                modulation=None, row_map=None, slots=0, gate_slot=0, out=None):
+                modulation=None, row_map=None, slots=0, gate_slot=0, out=None, lora=None):
         import torch
         out_dtype = out_dtype or torch.float32
         m = x_i8.shape[0]
@@ -202,6 +202,7 @@ class Cuda:
         if out is None:
             out = torch.empty((m, n_out), dtype=out_dtype, device=x_i8.device)
         e = _l.GemmEpi(kind, _dt(out), ptr(residual), ptr(modulation), ptr(row_map), slots, gate_slot)  # rest zero
+        e.d_lora = ptr(lora)   # optional [m, n] f32 delta (h3_dit_fused_epi.h:85-141)
         call("h3b_gemm_i8_dev", self.h, weight.h, ptr(x_i8), ptr(act_scales), m, ptr(out), C.byref(e))
         return out
 

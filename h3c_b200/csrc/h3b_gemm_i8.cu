@@ -67,6 +67,7 @@ struct GemmParams {
     const float *mod;         // gate: [mod_rows, slots, n_out] or NULL
     const uint32_t *row_map;  // gate: [M] or NULL
     int slots, gate_slot;
+    const float *lora;        // optional [M, N] f32 delta added to the dequantised value
     int *status;
     // QKV + QK-norm + RoPE epilogue
     void *y_k, *y_v;
@@ -486,12 +487,14 @@ __global__ void __launch_bounds__(gemm::THREADS, 1) k_gemm_i8(const __grid_const
 #pragma unroll
                             for (int e = 0; e < VEC; e++) {
                                 float val = __fmul_rn(__fmul_rn(a, sc[v + e]), (float)(int32_t)r[v + e]);
+                                if (p.lora) val = __fadd_rn(val, __ldg(p.lora + (size_t)row * p.N + col + v + e));
                                 if (EPI == H3B_EPI_GATE) {
                                     val = __fadd_rn(resv[e], __fmul_rn(val, gt[v + e]));
                                 } else if (EPI == H3B_EPI_GELU) {
                                     val = sizeof(OutT) == 2 ? gelu_tanh_fast(val) : gelu_tanh_dev(val);
                                 } else if (EPI == H3B_EPI_SWIGLU) {
-                                    const float u = __fmul_rn(__fmul_rn(a, sc2[v + e]), (float)(int32_t)r2[v + e]);
+                                    float u = __fmul_rn(__fmul_rn(a, sc2[v + e]), (float)(int32_t)r2[v + e]);
+                                    if (p.lora) u = __fadd_rn(u, __ldg(p.lora + (size_t)row * p.N + p.n_out + col + v + e));
                                     val = __fmul_rn(val / __fadd_rn(1.0f, expf(-val)), u);
                                 }
                                 out[e] = val;
@@ -614,6 +617,14 @@ int launch_gemm_i8(h3_cuda *cuda, const h3_cuda_w4a8_weight *w, const int8_t *x,
     p.act_scale = a; p.s_channel = w->d_s; p.y = y;
     p.residual = epi->d_residual; p.mod = epi->d_modulation; p.row_map = epi->d_row_map;
     p.slots = (int)epi->slots; p.gate_slot = (int)epi->gate_slot;
+    p.lora = epi->d_lora;
+    if (epi->d_lora) {
+        if (epi->kind == H3B_EPI_QKV_ROPE || epi->out_dtype == H3B_I32)
+            return fail(error, error_size, "gemm_i8: a LoRA delta goes with the plain, gate, swiglu or gelu epilogue");
+        if (reinterpret_cast<uintptr_t>(epi->d_lora) & 3) return fail(error, error_size, "gemm_i8: LoRA delta must be 4-byte aligned");
+        if (epi->lora_ready)
+            H3B_CUDA_OK(cudaStreamWaitEvent(cuda->op_stream, (cudaEvent_t)epi->lora_ready, 0), "wait for the LoRA delta");
+    }
     p.status = cuda->d_status;
     p.tmap_b = w->tmap_b;
     int rc = h3b_encode_tmap_2d(&p.tmap_a, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, x, K, m, K, BK, BM,

@@ -319,7 +319,8 @@ static int map_epi(const h3_cuda_dit_gemm_epi *in, h3b_gemm_epi *out, char *erro
     out->out_dtype = H3B_F32;
     if (!in) return 1;
     if (in->swiglu && in->gate) return fail(error, error_size, "gemm epilogue: swiglu and gate are mutually exclusive");
-    if (in->d_lora) return fail(error, error_size, "gemm epilogue: LoRA deltas are not supported by this library");
+    out->d_lora = in->d_lora;
+    out->lora_ready = in->d_lora ? in->lora_ready : NULL;
     if (in->requant_mode) return fail(error, error_size, "gemm epilogue: fused requant (requant_mode=%d) is not supported", in->requant_mode);
     if (in->swiglu) out->kind = H3B_EPI_SWIGLU;
     if (in->gate) {

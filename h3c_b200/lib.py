@@ -45,7 +45,7 @@ class GemmEpi(C.Structure):  # h3b_gemm_epi
     _fields_ = [("kind", i32), ("out_dtype", i32), ("d_residual", vp), ("d_modulation", vp), ("d_row_map", vp),
                 ("slots", sz), ("gate_slot", sz), ("d_key", vp), ("d_value", vp), ("d_q_norm", vp), ("d_k_norm", vp),
                 ("d_rope_cos", vp), ("d_rope_sin", vp), ("rope_half", sz), ("epsilon", f32), ("round_qkv", i32),
-                ("scatter", vp)]
+                ("scatter", vp), ("d_lora", vp), ("lora_ready", vp)]
 
 
 class NormArgs(C.Structure):  # h3b_norm_args

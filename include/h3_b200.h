@@ -269,6 +269,11 @@ typedef struct h3b_gemm_epi {
      * rank*seq_local + r, head h % hl (hl = heads / ulysses); d_y / d_key / d_value are then unused.
      * d_rope_cos / d_rope_sin are the rows of THIS rank ([m, rope_half]). */
     const h3b_ulysses_direct *scatter;
+    /* Plain / gate / swiglu / gelu, optional: already-scaled LoRA delta [m, n] f32 added to the dequantised
+     * value before the activation or gate (h3_dit_fused_epi.h:85-141: gate += lora[c], up += lora[w+c];
+     * br += lora[c]).  lora_ready: a cudaEvent_t the launch waits for, or NULL. */
+    const float *d_lora;
+    void *lora_ready;
 } h3b_gemm_epi;
 /* d_x_i8 [m,k] codes, d_act_scales [m]; d_y is [m,n] ([m,n/2] for swiglu). */
 int h3b_gemm_i8_dev(h3_cuda *cuda, const h3_cuda_w4a8_weight *weight, const int8_t *d_x_i8,

@@ -213,6 +213,15 @@ def test_gemm_epilogues(cuda, oracle, m):
     assert y.shape == (m, n // 2) and rel_l2(host(y), oracle.dequant_swiglu(acc, xs, s)) < 1e-6
     y = cuda.gemm_i8(w, dq, ds, kind=h3c_b200.EPI_GELU)
     assert rel_l2(host(y), oracle.dequant_gelu(acc, xs, s)) < 1e-6
+    # already-scaled LoRA deltas added before the gate / activation (h3_dit_fused_epi.h:85-141)
+    lora = rng.normal(0, 0.05, (m, n)).astype(np.float32)
+    y = cuda.gemm_i8(w, dq, ds, kind=h3c_b200.EPI_GATE, residual=dev(res), modulation=dev(mod),
+                     row_map=dev(rmap.view(np.int32)), slots=slots, gate_slot=5, lora=dev(lora))
+    assert np.array_equal(host(y), oracle.dequant_gate(acc, xs, s, res, mod, rmap, slots, 5, lora))
+    y = cuda.gemm_i8(w, dq, ds, kind=h3c_b200.EPI_SWIGLU, lora=dev(lora))
+    assert rel_l2(host(y), oracle.dequant_swiglu(acc, xs, s, lora)) < 1e-6
+    y = cuda.gemm_i8(w, dq, ds, lora=dev(lora))
+    assert np.array_equal(host(y), oracle.gemm_i8_dequant(xq, w_i8, xs, s) + lora)
     # bf16 outputs are the f32 results rounded once
     y = cuda.gemm_i8(w, dq, ds, out_dtype=torch.bfloat16)
     assert np.array_equal(host(y), oracle.bf16_round(oracle.gemm_i8_dequant(xq, w_i8, xs, s)))
@@ -276,6 +285,11 @@ def test_reference_linear_entry_point(cuda, oracle):
     y = cuda.gemm_i8_dequant_f32_w_act_dev(w, dev(x), 0, epi)
     xq, xs = oracle.quantize_act_int8(x)
     assert rel_l2(host(y), oracle.dequant_swiglu(oracle.gemm_i8_i32(xq, w_i8), xs, s)) < 1e-6
+    # the reference's d_lora field through its own entry point
+    lora = dev(rng.normal(0, 0.05, (m, n)).astype(np.float32))
+    epi.d_lora = lora.data_ptr()
+    y = cuda.gemm_i8_dequant_f32_w_act_dev(w, dev(x), 0, epi)
+    assert rel_l2(host(y), oracle.dequant_swiglu(oracle.gemm_i8_i32(xq, w_i8), xs, s, host(lora))) < 1e-6
 
 
 def test_gemm_full_size_sampled(cuda):
