@@ -9,11 +9,16 @@
 // its scale), and UE4M3 scales in the 128x4 blocked layout (h3_gpu_cuda.cu:4534), which is the
 // layout tcgen05.cp moves into tensor memory as it is: one 512-byte block = 128 rows x 64 k.
 //
-// Persistent kernel, tile 128 x 128, 256 k (128 packed bytes) per stage:
-//   warp 0     TMA: X and W tiles (128-byte swizzle) + four scale blocks each (plain bulk copies)
-//   warp 1     per stage: tcgen05.cp the eight scale blocks into TMEM, then four
-//              128x128x64 block-scaled MMAs into one of two 128-column accumulators
-//   warps 2-9  epilogue (one row, 64 columns per thread): alpha, optional gate + residual, store
+// Persistent kernel, tile 128 x 128, 256 k (128 packed bytes) per stage.  A 128x128x64 fp4 MMA executes in
+// 64 cycles, while one stage costs its issuing warp a barrier poll (about 100 cycles), eight tcgen05.cp
+// scale copies, four MMAs and a commit: a single issuer kept the pipe a third busy.  So the CTA runs TWO
+// independent pipelines, each with its own TMA warp, issuing warp, three-stage ring, accumulator and
+// scale-factor columns; pipeline p takes the CTA's tiles number p, p+2, p+4, ... and the epilogue drains
+// the two accumulators alternately, so a tile's epilogue still overlaps the other pipeline's mainloop.
+//   warps 0, 10  TMA of pipeline 0 / 1: X and W tiles (128-byte swizzle) + four scale blocks each (bulk copies)
+//   warps 1, 11  issuers: per stage tcgen05.cp the eight scale blocks into TMEM, then four 128x128x64
+//                block-scaled MMAs into the pipeline's 128-column accumulator
+//   warps 2-9    epilogue (one row, 64 columns per thread): alpha, optional gate + residual, store
 #include <cuda_bf16.h>
 
 #include "h3b_internal.h"
@@ -24,16 +29,17 @@ namespace h3b {
 namespace fp4 {
 constexpr int BM = 128, BN = 128;
 constexpr int BK_BYTES = 128;                 // 256 four-bit values of K per stage
-constexpr int STAGES = 5;
+constexpr int PIPES = 2;
+constexpr int STAGES = 3;                     // per pipeline
 constexpr int A_BYTES = BM * BK_BYTES;        // 16 KiB
 constexpr int B_BYTES = BN * BK_BYTES;        // 16 KiB
 constexpr int SF_BYTES = 4 * 512;             // four 128x64 scale blocks per operand and stage
 constexpr int STAGE_BYTES = A_BYTES + B_BYTES + 2 * SF_BYTES;
-constexpr int THREADS = 320;
+constexpr int THREADS = 384;
 constexpr int TMEM_COLS = 512;
-constexpr uint32_t ACC_COL = 0;               // two accumulators of 128 columns
-constexpr uint32_t SF_COL = 256;              // per stage parity: 16 columns SFA + 16 columns SFB
-constexpr size_t SMEM_BYTES = 1024 + (size_t)STAGES * STAGE_BYTES + 256;
+constexpr uint32_t ACC_COL = 0;               // two accumulators of 128 columns, one per pipeline
+constexpr uint32_t SF_COL = 256;              // per pipeline 64 columns: two parities of 16 SFA + 16 SFB columns
+constexpr size_t SMEM_BYTES = 1024 + (size_t)PIPES * STAGES * STAGE_BYTES + 256;
 }  // namespace fp4
 
 struct Fp4Params {
@@ -87,19 +93,21 @@ __host__ __device__ constexpr uint32_t fp4_idesc(uint32_t m, uint32_t n) {
     return (1u << 7) | (1u << 10) | ((n >> 3) << 17) | (0u << 23) | ((m >> 4) << 24);
 }
 
+template <bool GATE, bool OUT_BF16>
 __global__ void __launch_bounds__(fp4::THREADS, 1) k_gemm_nvfp4(const __grid_constant__ Fp4Params p) {
     using namespace fp4;
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
-    uint64_t *bars = reinterpret_cast<uint64_t *>(smem + (size_t)STAGES * STAGE_BYTES);
-    uint64_t *full = bars, *empty = bars + STAGES, *tmem_full = bars + 2 * STAGES, *tmem_empty = bars + 2 * STAGES + 2;
-    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 2 * STAGES + 4);
+    constexpr int NST = PIPES * STAGES;
+    uint64_t *bars = reinterpret_cast<uint64_t *>(smem + (size_t)NST * STAGE_BYTES);
+    uint64_t *full = bars, *empty = bars + NST, *tmem_full = bars + 2 * NST, *tmem_empty = bars + 2 * NST + 2;
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 2 * NST + 4);
     volatile int *abort_word = reinterpret_cast<volatile int *>(tmem_slot + 1);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int total_tiles = p.m_tiles * p.n_tiles;
 
     if (threadIdx.x == 0) {
-        for (int s = 0; s < STAGES; s++) {
+        for (int s = 0; s < NST; s++) {
             mbar_init(&full[s], 1);
             mbar_init(&empty[s], 1);
         }
@@ -121,15 +129,18 @@ __global__ void __launch_bounds__(fp4::THREADS, 1) k_gemm_nvfp4(const __grid_con
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
 
-    if (warp == 0) {
+    if (warp == 0 || warp == 10) {
+        const int pipe = warp == 0 ? 0 : 1;
         if (lane == 0) {
             int s = 0;
             uint32_t ph = 0;
-            for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
+            uint64_t *full = bars + pipe * STAGES, *empty = bars + NST + pipe * STAGES;   // this pipeline's ring
+            uint8_t *ring = smem + (size_t)pipe * STAGES * STAGE_BYTES;
+            for (int tile = blockIdx.x + pipe * gridDim.x; tile < total_tiles; tile += 2 * gridDim.x) {
                 const int mt = tile % p.m_tiles, nt = tile / p.m_tiles;
                 for (int kb = 0; kb < p.k_blocks; kb++) {
                     if (!mbar_wait(&empty[s], ph ^ 1, abort_word, p.status, H3B_ST_TIMEOUT_EMPTY)) break;
-                    uint8_t *a_dst = smem + (size_t)s * STAGE_BYTES;
+                    uint8_t *a_dst = ring + (size_t)s * STAGE_BYTES;
                     uint8_t *b_dst = a_dst + A_BYTES, *sfa_dst = b_dst + B_BYTES, *sfb_dst = sfa_dst + SF_BYTES;
                     // scale blocks of this stage: k tiles [4 kb, 4 kb + 4) of the row block, clipped at K / 64
                     const int kt0 = kb * 4;
@@ -146,25 +157,27 @@ __global__ void __launch_bounds__(fp4::THREADS, 1) k_gemm_nvfp4(const __grid_con
             }
         }
         __syncwarp();
-    } else if (warp == 1) {
+    } else if (warp == 1 || warp == 11) {
         // whole warp converged (uniform descriptor arithmetic); one elected lane issues
         {
             constexpr uint32_t idesc = fp4_idesc(BM, BN);
-            int s = 0, it = 0, sfbuf = 0;
+            const int pipe = warp == 1 ? 0 : 1, buf = pipe;
+            uint64_t *full = bars + pipe * STAGES, *empty = bars + NST + pipe * STAGES;
+            uint8_t *ring = smem + (size_t)pipe * STAGES * STAGE_BYTES;
+            int s = 0, it = 0, sfbuf = 0;   // it: tiles of this pipeline so far
             uint32_t ph = 0;
-            for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, it++) {
-                const int buf = it & 1;
-                if (!mbar_wait(&tmem_empty[buf], ((it >> 1) & 1) ^ 1, abort_word, p.status, H3B_ST_TIMEOUT_TMEM_EMPTY))
+            for (int tile = blockIdx.x + pipe * gridDim.x; tile < total_tiles; tile += 2 * gridDim.x, it++) {
+                if (!mbar_wait(&tmem_empty[buf], (it & 1) ^ 1, abort_word, p.status, H3B_ST_TIMEOUT_TMEM_EMPTY))
                     break;
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + ACC_COL + (uint32_t)buf * BN;
                 for (int kb = 0; kb < p.k_blocks; kb++) {
                     if (!mbar_wait(&full[s], ph, abort_word, p.status, H3B_ST_TIMEOUT_FULL)) break;
                     tc_fence_after();
-                    const uint32_t a_addr = smem_u32(smem + (size_t)s * STAGE_BYTES);
+                    const uint32_t a_addr = smem_u32(ring + (size_t)s * STAGE_BYTES);
                     const uint32_t b_addr = a_addr + A_BYTES, sfa_addr = b_addr + B_BYTES, sfb_addr = sfa_addr + SF_BYTES;
                     const int nkt = min(4, p.sf_tiles_per_rowblock - kb * 4);   // MMAs (64 k each) with data
-                    const uint32_t sf_t = tmem_base + SF_COL + (uint32_t)sfbuf * 32;
+                    const uint32_t sf_t = tmem_base + SF_COL + (uint32_t)pipe * 64 + (uint32_t)sfbuf * 32;
                     if (elect_one()) {
                         for (int j = 0; j < nkt; j++) {
                             tmem_cp_32x128b_warpx4(sf_t + j * 4, sf_desc(sfa_addr + j * 512));
@@ -195,7 +208,7 @@ __global__ void __launch_bounds__(fp4::THREADS, 1) k_gemm_nvfp4(const __grid_con
             const int row = mt * BM + q * 32 + lane;
             const bool row_ok = row < p.M;
             const float *gate = nullptr;
-            if (p.gate && p.mod && row_ok) {
+            if (GATE && p.mod && row_ok) {
                 const size_t mrow = p.row_map ? p.row_map[row] : (size_t)row;
                 gate = p.mod + (mrow * p.slots + p.gate_slot) * (size_t)p.N;
             }
@@ -203,40 +216,56 @@ __global__ void __launch_bounds__(fp4::THREADS, 1) k_gemm_nvfp4(const __grid_con
             tc_fence_after();
             const uint32_t t_addr = tmem_base + lane_base + ACC_COL + (uint32_t)buf * BN;
             if (ok) {
-#pragma unroll 1
-                for (int i = 0; i < 2; i++) {
-                    const int ch = half * 2 + i;
-                    const int col = nt * BN + ch * 32;
-                    if (col >= p.N) break;
-                    uint32_t r[32];
-                    tmem_ld_32x32b_x32(t_addr + ch * 32, r);
-                    tmem_ld_wait();
-                    if (!row_ok) continue;
+                // this warp's 64 columns in one TMEM round trip
+                const int col0 = nt * BN + half * 64;
+                uint32_t r[64];
+                tmem_ld_32x32b_x32(t_addr + half * 64, *reinterpret_cast<uint32_t(*)[32]>(&r[0]));
+                tmem_ld_32x32b_x32(t_addr + half * 64 + 32, *reinterpret_cast<uint32_t(*)[32]>(&r[32]));
+                tmem_ld_wait();
+                if (row_ok) {
 #pragma unroll
-                    for (int v = 0; v < 32; v += 8) {
-                        if (col + v >= p.N) break;
+                    for (int v = 0; v < 64; v += 8) {
+                        const int col = col0 + v;
+                        if (col >= p.N) break;
                         float out[8];
 #pragma unroll
                         for (int e = 0; e < 8; e++) out[e] = __fmul_rn(p.alpha, __uint_as_float(r[v + e]));
-                        if (p.gate) {
+                        if (GATE) {
+                            float resv[8], g[8];
+                            const size_t idx = (size_t)row * p.N + col;
+                            if (OUT_BF16) {
+                                const uint4 raw = *reinterpret_cast<const uint4 *>(reinterpret_cast<const __nv_bfloat16 *>(p.residual) + idx);
+                                const __nv_bfloat162 *h = reinterpret_cast<const __nv_bfloat162 *>(&raw);
 #pragma unroll
-                            for (int e = 0; e < 8; e++) {
-                                const size_t idx = (size_t)row * p.N + col + v + e;
-                                const float resv = p.out_bf16
-                                                       ? __bfloat162float(reinterpret_cast<const __nv_bfloat16 *>(p.residual)[idx])
-                                                       : reinterpret_cast<const float *>(p.residual)[idx];
-                                const float g = gate ? __ldg(gate + col + v + e) : 1.0f;
-                                out[e] = __fadd_rn(resv, __fmul_rn(out[e], g));
+                                for (int e = 0; e < 4; e++) {
+                                    const float2 f = __bfloat1622float2(h[e]);
+                                    resv[2 * e] = f.x; resv[2 * e + 1] = f.y;
+                                }
+                            } else {
+                                const float4 r0 = *reinterpret_cast<const float4 *>(reinterpret_cast<const float *>(p.residual) + idx);
+                                const float4 r1 = *reinterpret_cast<const float4 *>(reinterpret_cast<const float *>(p.residual) + idx + 4);
+                                resv[0] = r0.x; resv[1] = r0.y; resv[2] = r0.z; resv[3] = r0.w;
+                                resv[4] = r1.x; resv[5] = r1.y; resv[6] = r1.z; resv[7] = r1.w;
                             }
+                            if (gate) {
+                                const float4 g0 = __ldg(reinterpret_cast<const float4 *>(gate + col));
+                                const float4 g1 = __ldg(reinterpret_cast<const float4 *>(gate + col + 4));
+                                g[0] = g0.x; g[1] = g0.y; g[2] = g0.z; g[3] = g0.w; g[4] = g1.x; g[5] = g1.y; g[6] = g1.z; g[7] = g1.w;
+                            } else {
+#pragma unroll
+                                for (int e = 0; e < 8; e++) g[e] = 1.0f;
+                            }
+#pragma unroll
+                            for (int e = 0; e < 8; e++) out[e] = __fadd_rn(resv[e], __fmul_rn(out[e], g[e]));
                         }
-                        if (p.out_bf16) {
+                        if (OUT_BF16) {
                             uint4 raw;
                             __nv_bfloat162 *h = reinterpret_cast<__nv_bfloat162 *>(&raw);
 #pragma unroll
                             for (int e = 0; e < 4; e++) h[e] = __floats2bfloat162_rn(out[2 * e], out[2 * e + 1]);
-                            *reinterpret_cast<uint4 *>(reinterpret_cast<__nv_bfloat16 *>(p.y) + (size_t)row * p.N + col + v) = raw;
+                            *reinterpret_cast<uint4 *>(reinterpret_cast<__nv_bfloat16 *>(p.y) + (size_t)row * p.N + col) = raw;
                         } else {
-                            float *dst = reinterpret_cast<float *>(p.y) + (size_t)row * p.N + col + v;
+                            float *dst = reinterpret_cast<float *>(p.y) + (size_t)row * p.N + col;
                             *reinterpret_cast<float4 *>(dst) = make_float4(out[0], out[1], out[2], out[3]);
                             *reinterpret_cast<float4 *>(dst + 4) = make_float4(out[4], out[5], out[6], out[7]);
                         }
@@ -285,12 +314,15 @@ int launch_gemm_nvfp4(h3_cuda *cuda, const uint8_t *w_fp4, const uint8_t *sf_w, 
     p.sf_tiles_per_rowblock = (int)(k / 64);
     p.alpha = alpha; p.gate = gate; p.out_bf16 = out_dtype == H3B_BF16; p.y = y; p.residual = residual; p.mod = mod;
     p.row_map = row_map; p.slots = (int)slots; p.gate_slot = (int)gate_slot; p.status = cuda->d_status;
-    H3B_CUDA_OK(cudaFuncSetAttribute(k_gemm_nvfp4, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES),
+    if (gate && (((uintptr_t)residual | (uintptr_t)mod) & 15)) return fail(error, error_size, "gemm_fp4: residual and modulation must be 16-byte aligned");
+    auto kern = gate ? (p.out_bf16 ? k_gemm_nvfp4<true, true> : k_gemm_nvfp4<true, false>)
+                     : (p.out_bf16 ? k_gemm_nvfp4<false, true> : k_gemm_nvfp4<false, false>);
+    H3B_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES),
                 "gemm_fp4 smem attribute");
     int tiles = p.m_tiles * p.n_tiles;
     int grid = tiles < cuda->sm_count ? tiles : cuda->sm_count;
     ProfScope prof(cuda, PROF_GEMM);
-    k_gemm_nvfp4<<<grid, THREADS, SMEM_BYTES, cuda->op_stream>>>(p);
+    kern<<<grid, THREADS, SMEM_BYTES, cuda->op_stream>>>(p);
     cuda->launches++;
     H3B_CUDA_OK(cudaGetLastError(), "k_gemm_nvfp4 launch");
     return 1;
