@@ -64,7 +64,7 @@ def main():
     elif a.case == "peak":
         import ctypes as C
         from .lib import call
-        for kind, name in ((0, "int8"), (1, "bf16"), (2, "nvfp4"), (3, "bf16_n128_ss"), (4, "bf16_n128_ts")):
+        for kind, name in ((0, "int8"), (1, "bf16"), (2, "nvfp4"), (3, "bf16_n128_ss"), (4, "bf16_n128_ts"), (5, "nvfp4_n128")):
             v = C.c_double(0)
             call("h3b_umma_peak_dev", cuda.h, kind, 20000, C.byref(v))     # ~10 ms of MMAs: burst clocks
             out[name + "_burst_tops"] = v.value

@@ -17,7 +17,8 @@ __device__ __forceinline__ void umma_nvfp4_probe(uint32_t d_tmem, uint64_t a_des
 
 // KIND 0: int8 128x256x32, 1: bf16 128x256x16, 2: nvfp4 128x256x64 (zero scales),
 // 3: bf16 128x128x16, both operands K-major in shared memory (the attention score product),
-// 4: bf16 128x128x16, A from tensor memory, B MN-major (the attention P V product)
+// 4: bf16 128x128x16, A from tensor memory, B MN-major (the attention P V product),
+// 5: nvfp4 128x128x64 (zero scales)
 template <int KIND>
 __global__ void __launch_bounds__(128, 1) k_umma_peak(int iters, int *status) {
     extern __shared__ uint8_t smem_raw[];
@@ -48,6 +49,7 @@ __global__ void __launch_bounds__(128, 1) k_umma_peak(int iters, int *status) {
                                    : KIND == 1 ? umma_idesc(1, 1, 1, 128, 256, 0, 0)
                                    : KIND == 3 ? umma_idesc(1, 1, 1, 128, 128, 0, 0)
                                    : KIND == 4 ? umma_idesc(1, 1, 1, 128, 128, 0, 1)
+                                   : KIND == 5 ? ((1u << 7) | (1u << 10) | ((128u >> 3) << 17) | ((128u >> 4) << 24))
                                                : ((1u << 7) | (1u << 10) | ((256u >> 3) << 17) | ((128u >> 4) << 24));
         for (int it = 0; it < iters; it++) {
 #pragma unroll
@@ -78,11 +80,11 @@ using namespace h3b;
 
 extern "C" int h3b_umma_peak_dev(h3_cuda *cuda, int kind, int iters, double *tera_ops_per_s, char *error,
                                  size_t error_size) {
-    if (!cuda || !tera_ops_per_s || iters <= 0 || kind < 0 || kind > 4)
+    if (!cuda || !tera_ops_per_s || iters <= 0 || kind < 0 || kind > 5)
         return fail(error, error_size, "umma_peak: invalid arguments");
     const size_t smem = 1024 + 16384 + 32768;
     cudaEvent_t e0 = cuda->ev0, e1 = cuda->ev1;
-    const double ops_per_mma = kind >= 3 ? 2.0 * 128 * 128 * 16 : 2.0 * 128 * 256 * (kind == 0 ? 32 : kind == 1 ? 16 : 64);
+    const double ops_per_mma = kind == 5 ? 2.0 * 128 * 128 * 64 : kind >= 3 ? 2.0 * 128 * 128 * 16 : 2.0 * 128 * 256 * (kind == 0 ? 32 : kind == 1 ? 16 : 64);
     for (int rep = 0; rep < 2; rep++) {   // first launch warms up
         H3B_CUDA_OK(cudaEventRecord(e0, cuda->op_stream), "cudaEventRecord");
         if (kind == 0) {
@@ -97,6 +99,9 @@ extern "C" int h3b_umma_peak_dev(h3_cuda *cuda, int kind, int iters, double *ter
         } else if (kind == 4) {
             H3B_CUDA_OK(cudaFuncSetAttribute(k_umma_peak<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem), "attr");
             k_umma_peak<4><<<cuda->sm_count, 128, smem, cuda->op_stream>>>(iters, cuda->d_status);
+        } else if (kind == 5) {
+            H3B_CUDA_OK(cudaFuncSetAttribute(k_umma_peak<5>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem), "attr");
+            k_umma_peak<5><<<cuda->sm_count, 128, smem, cuda->op_stream>>>(iters, cuda->d_status);
         } else {
             H3B_CUDA_OK(cudaFuncSetAttribute(k_umma_peak<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem), "attr");
             k_umma_peak<2><<<cuda->sm_count, 128, smem, cuda->op_stream>>>(iters, cuda->d_status);

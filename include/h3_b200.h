@@ -89,7 +89,7 @@ void h3b_cuda_profile_begin(h3_cuda *cuda);
 int h3b_cuda_profile_end(h3_cuda *cuda, double *ms_by_class, int *launches_by_class, int n_classes);
 /* Addition.  Sustained tensor-pipe rate of this GPU: every SM issues `iters` x 4 back-to-back
  * tcgen05.mma (kind 0 int8 128x256x32, 1 bf16 128x256x16, 2 nvfp4 128x256x64, 3 bf16 128x128x16 from
- * shared memory, 4 bf16 128x128x16 with A in tensor memory and B MN-major) on a resident tile,
+ * shared memory, 4 bf16 128x128x16 with A in tensor memory and B MN-major, 5 nvfp4 128x128x64) on a resident tile,
  * no loads or epilogue; returns tera-operations per second (2*M*N*K per MMA). */
 int h3b_umma_peak_dev(h3_cuda *cuda, int kind, int iters, double *tera_ops_per_s, char *error,
                       size_t error_size);
