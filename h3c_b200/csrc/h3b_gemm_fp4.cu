@@ -20,6 +20,7 @@
 //                block-scaled MMAs into the pipeline's 128-column accumulator
 //   warps 2-9    epilogue (one row, 64 columns per thread): alpha, optional gate + residual, store
 #include <cuda_bf16.h>
+#include <stdlib.h>
 
 #include "h3b_internal.h"
 #include "h3b_ptx.cuh"
@@ -45,6 +46,8 @@ constexpr size_t SMEM_BYTES = 1024 + (size_t)PIPES * STAGES * STAGE_BYTES + 256;
 struct Fp4Params {
     CUtensorMap tmap_x;   // [M, K/2] bytes, box 128 x 128
     CUtensorMap tmap_w;   // [N, K/2] bytes, box 128 x 128
+    CUtensorMap tmap_y;   // wide form: [M, N] outputs, box 128 bytes x 32 rows, 128-byte swizzle
+    CUtensorMap tmap_res; // wide form, gate epilogue: the residual, same geometry
     const uint8_t *sf_x, *sf_w;
     int M, N, K;
     int m_tiles, n_tiles, k_blocks;
@@ -287,6 +290,242 @@ __global__ void __launch_bounds__(fp4::THREADS, 1) k_gemm_nvfp4(const __grid_con
     }
 }
 
+// ---------------------------------------------------------------------------------------------
+// Wide form, tile 128 x 256 with N = 256 instructions.  A 128x128 tile reads 128 B/clk of operands from shared
+// memory while TMA writes 128 B/clk into it, twice what shared memory moves: 50 % is its ceiling.  At 128x256 the
+// two streams are 96 B/clk each.  Two 256-column accumulators would leave no tensor memory for the scale
+// factors, so there is ONE accumulator; the epilogue pulls its 128 columns per warp into registers and hands
+// the accumulator back before it converts and stores, which keeps the hole between two tiles short.
+// Scale factors of B: the two 128-row blocks of the tile sit in eight consecutive TMEM columns per MMA
+// (block 0 in columns 0-3, block 1 in columns 4-7).
+// Outputs leave through shared memory and TMA stores, 32 rows x 128 bytes per warp and copy.  A thread that
+// stores its own row straight to global memory makes every store instruction touch 32 lines; the load/store
+// unit then spends 32 passes per instruction, 4096 cycles per tile, and the mbarrier polls and TMA / MMA
+// issues of the other warps queue behind them: measured as a fixed 41 us per 113 MB of bf16 output on top
+// of a mainloop that by itself runs at 5900 TFLOP/s.  The gate epilogue fetches the residual the same way.
+namespace fp4w {
+constexpr int BM = 128, BN = 256, BK_BYTES = 128, STAGES = 3;
+constexpr int A_BYTES = BM * BK_BYTES, B_BYTES = BN * BK_BYTES;   // 16 KiB, 32 KiB
+constexpr int OUT_STAGE_BYTES = 32 * 128;                         // per epilogue warp: 32 rows of 128 bytes
+constexpr int SFA_BYTES = 4 * 512, SFB_BYTES = 8 * 512;            // per stage: 4 MMAs x (1 | 2) blocks
+constexpr int STAGE_BYTES = A_BYTES + B_BYTES + SFA_BYTES + SFB_BYTES;
+constexpr int THREADS = 320;
+constexpr uint32_t SF_COL = 256;                                    // per stage 16 SFA + 32 SFB columns
+constexpr size_t SMEM_BYTES = 1024 + (size_t)STAGES * STAGE_BYTES + 8 * OUT_STAGE_BYTES + 256;
+}  // namespace fp4w
+
+template <bool GATE, bool OUT_BF16>
+__global__ void __launch_bounds__(fp4w::THREADS, 1) k_gemm_nvfp4_wide(const __grid_constant__ Fp4Params p) {
+    using namespace fp4w;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    uint8_t *out_stage = smem + (size_t)STAGES * STAGE_BYTES;
+    uint64_t *bars = reinterpret_cast<uint64_t *>(out_stage + 8 * OUT_STAGE_BYTES);
+    uint64_t *full = bars, *empty = bars + STAGES, *tmem_full = bars + 2 * STAGES, *tmem_empty = bars + 2 * STAGES + 1;
+    uint64_t *res_bar = bars + 2 * STAGES + 2;   // one per epilogue warp
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 2 * STAGES + 10);
+    volatile int *abort_word = reinterpret_cast<volatile int *>(tmem_slot + 1);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int total_tiles = p.m_tiles * p.n_tiles;
+    const int n_blocks = (p.N + 127) / 128;   // scale row blocks of W
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; s++) {
+            mbar_init(&full[s], 1);
+            mbar_init(&empty[s], 1);
+        }
+        mbar_init(tmem_full, 1);
+        mbar_init(tmem_empty, 8);
+        for (int w = 0; w < 8; w++) mbar_init(&res_bar[w], 1);
+        *abort_word = 0;
+        mbar_fence_init();
+        tma_prefetch_desc(&p.tmap_x);
+        tma_prefetch_desc(&p.tmap_w);
+        tma_prefetch_desc(&p.tmap_y);
+    }
+    if (warp == 1) {
+        tmem_alloc(tmem_slot, 512);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            int s = 0;
+            uint32_t ph = 0;
+            for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
+                const int mt = tile % p.m_tiles, nt = tile / p.m_tiles;
+                const int nb0 = 2 * nt, nb1 = min(2 * nt + 1, n_blocks - 1);   // a missing second block repeats the first
+                for (int kb = 0; kb < p.k_blocks; kb++) {
+                    if (!mbar_wait(&empty[s], ph ^ 1, abort_word, p.status, H3B_ST_TIMEOUT_EMPTY)) break;
+                    uint8_t *a_dst = smem + (size_t)s * STAGE_BYTES;
+                    uint8_t *b_dst = a_dst + A_BYTES, *sfa_dst = b_dst + B_BYTES, *sfb_dst = sfa_dst + SFA_BYTES;
+                    const int kt0 = kb * 4;
+                    const int nkt = min(4, p.sf_tiles_per_rowblock - kt0);
+                    const uint32_t sf_bytes = (uint32_t)nkt * 512;
+                    mbar_expect_tx(&full[s], A_BYTES + B_BYTES + 3 * sf_bytes);
+                    tma_load_2d(a_dst, &p.tmap_x, &full[s], kb * BK_BYTES, mt * BM);
+                    tma_load_2d(b_dst, &p.tmap_w, &full[s], kb * BK_BYTES, nt * BN);
+                    tma_load_2d(b_dst + B_BYTES / 2, &p.tmap_w, &full[s], kb * BK_BYTES, nt * BN + 128);
+                    bulk_load(sfa_dst, p.sf_x + ((size_t)mt * p.sf_tiles_per_rowblock + kt0) * 512, sf_bytes, &full[s]);
+                    bulk_load(sfb_dst, p.sf_w + ((size_t)nb0 * p.sf_tiles_per_rowblock + kt0) * 512, sf_bytes, &full[s]);
+                    bulk_load(sfb_dst + 4 * 512, p.sf_w + ((size_t)nb1 * p.sf_tiles_per_rowblock + kt0) * 512, sf_bytes, &full[s]);
+                    if (++s == STAGES) { s = 0; ph ^= 1; }
+                }
+                if (*abort_word) break;
+            }
+        }
+        __syncwarp();
+    } else if (warp == 1) {
+        constexpr uint32_t idesc = fp4_idesc(BM, BN);
+        int s = 0, it = 0;
+        uint32_t ph = 0;
+        for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, it++) {
+            if (!mbar_wait(tmem_empty, (it & 1) ^ 1, abort_word, p.status, H3B_ST_TIMEOUT_TMEM_EMPTY)) break;
+            tc_fence_after();
+            const uint32_t d_tmem = tmem_base;
+            for (int kb = 0; kb < p.k_blocks; kb++) {
+                if (!mbar_wait(&full[s], ph, abort_word, p.status, H3B_ST_TIMEOUT_FULL)) break;
+                tc_fence_after();
+                const uint32_t a_addr = smem_u32(smem + (size_t)s * STAGE_BYTES);
+                const uint32_t b_addr = a_addr + A_BYTES, sfa_addr = b_addr + B_BYTES, sfb_addr = sfa_addr + SFA_BYTES;
+                const int nkt = min(4, p.sf_tiles_per_rowblock - kb * 4);
+                const uint32_t sfa_t = tmem_base + SF_COL + (uint32_t)s * 48, sfb_t = sfa_t + 16;
+                if (elect_one()) {
+                    for (int j = 0; j < nkt; j++) {
+                        tmem_cp_32x128b_warpx4(sfa_t + j * 4, sf_desc(sfa_addr + j * 512));
+                        tmem_cp_32x128b_warpx4(sfb_t + j * 8, sf_desc(sfb_addr + j * 512));
+                        tmem_cp_32x128b_warpx4(sfb_t + j * 8 + 4, sf_desc(sfb_addr + (4 + j) * 512));
+                    }
+                    for (int j = 0; j < nkt; j++)
+                        umma_nvfp4_ss(d_tmem, umma_desc_k_sw128(a_addr + j * 32), umma_desc_k_sw128(b_addr + j * 32), idesc,
+                                      sfa_t + j * 4, sfb_t + j * 8, (uint32_t)((kb | j) != 0));
+                    tc_commit(&empty[s]);
+                }
+                __syncwarp();
+                if (++s == STAGES) { s = 0; ph ^= 1; }
+            }
+            if (*abort_word) break;
+            if (elect_one()) tc_commit(tmem_full);
+            __syncwarp();
+        }
+        __syncwarp();
+    } else {
+        const int q = warp & 3, half = (warp - 2) >> 2;
+        const uint32_t lane_base = (uint32_t)(q * 32) << 16;
+        constexpr int CH_COLS = OUT_BF16 ? 64 : 32;   // 128 bytes of a row per copy
+        constexpr int NCH = 128 / CH_COLS;
+        constexpr int UNIT = OUT_BF16 ? 8 : 4;        // values per 16-byte unit
+        uint8_t *stg = out_stage + (size_t)(warp - 2) * OUT_STAGE_BYTES;
+        uint64_t *rbar = &res_bar[warp - 2];
+        uint32_t res_phase = 0;
+        int it = 0;
+        for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, it++) {
+            const int mt = tile % p.m_tiles, nt = tile / p.m_tiles;
+            const int row0 = mt * BM + q * 32;
+            const float *gate = nullptr;
+            if (GATE && p.mod) {
+                const int row = min(row0 + lane, p.M - 1);   // rows past M are clipped by the store
+                const size_t mrow = p.row_map ? p.row_map[row] : (size_t)row;
+                gate = p.mod + (mrow * p.slots + p.gate_slot) * (size_t)p.N;
+            }
+            bool ok = mbar_wait(tmem_full, it & 1, abort_word, p.status, H3B_ST_TIMEOUT_TMEM_FULL);
+            tc_fence_after();
+            const uint32_t t_addr = tmem_base + lane_base + (uint32_t)half * 128;
+            uint32_t r[128];
+            if (ok) {
+#pragma unroll
+                for (int ch = 0; ch < 4; ch++)
+                    tmem_ld_32x32b_x32(t_addr + ch * 32, *reinterpret_cast<uint32_t(*)[32]>(&r[ch * 32]));
+                tmem_ld_wait();
+            }
+            // the values are in registers: the accumulator can take the next tile
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(tmem_empty);
+            const int col0 = nt * BN + half * 128;
+            if (ok && row0 < p.M) {
+#pragma unroll
+                for (int ch = 0; ch < NCH; ch++) {
+                    const int col = col0 + ch * CH_COLS;
+                    if (col >= p.N) break;
+                    if (lane == 0) tma_store_wait_read<0>();   // the previous copy has left the buffer
+                    __syncwarp();
+                    if (GATE) {
+                        if (lane == 0) {
+                            mbar_expect_tx(rbar, OUT_STAGE_BYTES);
+                            tma_load_2d(stg, &p.tmap_res, rbar, col, row0);
+                        }
+                        ok = mbar_wait(rbar, res_phase, abort_word, p.status, H3B_ST_TIMEOUT_FULL);
+                        res_phase ^= 1;
+                        if (!ok) break;
+                    }
+#pragma unroll
+                    for (int u = 0; u < 8; u++) {
+                        uint4 *cell = reinterpret_cast<uint4 *>(stg + lane * 128 + ((u ^ (lane & 7)) << 4));
+                        const int v = ch * CH_COLS + u * UNIT;
+                        float out[UNIT];
+#pragma unroll
+                        for (int e = 0; e < UNIT; e++) out[e] = __fmul_rn(p.alpha, __uint_as_float(r[v + e]));
+                        if (GATE) {
+                            float resv[UNIT], g[UNIT];
+                            const uint4 raw = *cell;
+                            if (OUT_BF16) {
+                                const __nv_bfloat162 *h = reinterpret_cast<const __nv_bfloat162 *>(&raw);
+#pragma unroll
+                                for (int e = 0; e < UNIT / 2; e++) {
+                                    const float2 f = __bfloat1622float2(h[e]);
+                                    resv[2 * e] = f.x; resv[2 * e + 1] = f.y;
+                                }
+                            } else {
+                                resv[0] = __uint_as_float(raw.x); resv[1] = __uint_as_float(raw.y);
+                                resv[2] = __uint_as_float(raw.z); resv[3] = __uint_as_float(raw.w);
+                            }
+                            const int gc = min(col + u * UNIT, p.N - UNIT);   // columns past N are clipped by the store
+#pragma unroll
+                            for (int e = 0; e < UNIT; e += 4) {
+                                float4 gv = make_float4(1.0f, 1.0f, 1.0f, 1.0f);
+                                if (gate) gv = __ldg(reinterpret_cast<const float4 *>(gate + gc + e));
+                                g[e] = gv.x; g[e + 1] = gv.y; g[e + 2] = gv.z; g[e + 3] = gv.w;
+                            }
+#pragma unroll
+                            for (int e = 0; e < UNIT; e++) out[e] = __fadd_rn(resv[e], __fmul_rn(out[e], g[e]));
+                        }
+                        uint4 pack;
+                        if (OUT_BF16) {
+                            __nv_bfloat162 *h = reinterpret_cast<__nv_bfloat162 *>(&pack);
+#pragma unroll
+                            for (int e = 0; e < UNIT / 2; e++) h[e] = __floats2bfloat162_rn(out[2 * e], out[2 * e + 1]);
+                        } else {
+                            pack = make_uint4(__float_as_uint(out[0]), __float_as_uint(out[1]), __float_as_uint(out[2]),
+                                              __float_as_uint(out[3]));
+                        }
+                        *cell = pack;
+                    }
+                    fence_proxy_async_smem();
+                    __syncwarp();
+                    if (lane == 0) {
+                        tma_store_2d(&p.tmap_y, stg, col, row0);
+                        tma_store_commit();
+                    }
+                }
+            }
+            if (*abort_word) break;
+        }
+        if (lane == 0) tma_store_wait<0>();
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, 512);
+    }
+}
+
 int launch_gemm_nvfp4(h3_cuda *cuda, const uint8_t *w_fp4, const uint8_t *sf_w, const uint8_t *x_fp4, const uint8_t *sf_x,
                       size_t m, size_t n, size_t k, float alpha, void *y, int out_dtype, int gate, const void *residual,
                       const float *mod, const uint32_t *row_map, size_t slots, size_t gate_slot, char *error,
@@ -315,6 +554,36 @@ int launch_gemm_nvfp4(h3_cuda *cuda, const uint8_t *w_fp4, const uint8_t *sf_w, 
     p.alpha = alpha; p.gate = gate; p.out_bf16 = out_dtype == H3B_BF16; p.y = y; p.residual = residual; p.mod = mod;
     p.row_map = row_map; p.slots = (int)slots; p.gate_slot = (int)gate_slot; p.status = cuda->d_status;
     if (gate && (((uintptr_t)residual | (uintptr_t)mod) & 15)) return fail(error, error_size, "gemm_fp4: residual and modulation must be 16-byte aligned");
+    // 128 x 256 tiles whenever N has two column blocks; H3B_FP4_WIDE=0 keeps the 128 x 128 form (A/B timing)
+    static const bool wide_on = [] {
+        const char *e = getenv("H3B_FP4_WIDE");
+        return !(e && e[0] == '0');
+    }();
+    if (wide_on && n >= 256) {
+        int rc2 = h3b_encode_tmap_2d(&p.tmap_w, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, w_fp4, k / 2, n, k / 2, BK_BYTES, 128,
+                                     CU_TENSOR_MAP_SWIZZLE_128B);
+        if (rc2 != 0) return fail(error, error_size, "gemm_fp4: cuTensorMapEncodeTiled failed (%d)", rc2);
+        p.n_tiles = (int)ceil_div(n, (size_t)fp4w::BN);
+        const bool bf = out_dtype == H3B_BF16;
+        const CUtensorMapDataType odt = bf ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32;
+        const size_t osz = bf ? 2 : 4;
+        rc2 = h3b_encode_tmap_2d(&p.tmap_y, odt, osz, y, n, m, n * osz, (uint32_t)(128 / osz), 32, CU_TENSOR_MAP_SWIZZLE_128B);
+        if (rc2 == 0 && gate)
+            rc2 = h3b_encode_tmap_2d(&p.tmap_res, odt, osz, residual, n, m, n * osz, (uint32_t)(128 / osz), 32,
+                                     CU_TENSOR_MAP_SWIZZLE_128B);
+        if (rc2 != 0) return fail(error, error_size, "gemm_fp4: cuTensorMapEncodeTiled (outputs) failed (%d)", rc2);
+        auto kw = gate ? (p.out_bf16 ? k_gemm_nvfp4_wide<true, true> : k_gemm_nvfp4_wide<true, false>)
+                       : (p.out_bf16 ? k_gemm_nvfp4_wide<false, true> : k_gemm_nvfp4_wide<false, false>);
+        H3B_CUDA_OK(cudaFuncSetAttribute(kw, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)fp4w::SMEM_BYTES),
+                    "gemm_fp4 smem attribute");
+        const int tiles_w = p.m_tiles * p.n_tiles;
+        const int grid_w = tiles_w < cuda->sm_count ? tiles_w : cuda->sm_count;
+        ProfScope prof(cuda, PROF_GEMM);
+        kw<<<grid_w, fp4w::THREADS, fp4w::SMEM_BYTES, cuda->op_stream>>>(p);
+        cuda->launches++;
+        H3B_CUDA_OK(cudaGetLastError(), "k_gemm_nvfp4_wide launch");
+        return 1;
+    }
     auto kern = gate ? (p.out_bf16 ? k_gemm_nvfp4<true, true> : k_gemm_nvfp4<true, false>)
                      : (p.out_bf16 ? k_gemm_nvfp4<false, true> : k_gemm_nvfp4<false, false>);
     H3B_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES),
