@@ -41,7 +41,7 @@ def main():
     ap.add_argument("--lq", type=int, default=6144)
     ap.add_argument("--lk", type=int, default=0)
     ap.add_argument("--heads", type=int, default=24)
-    ap.add_argument("--epi", default="plain", choices=["plain", "gate", "gelu", "swiglu"])
+    ap.add_argument("--epi", default="plain", choices=["plain", "gate", "gelu", "swiglu", "qkv"])
     ap.add_argument("--plain-quant", action="store_true")
     ap.add_argument("--iters", type=int, default=20)
     a = ap.parse_args()
@@ -54,6 +54,14 @@ def main():
         w = cuda.weight_from_i8(w_i8, np.full(a.n, 1e-3, np.float32))
         x = torch.randint(-127, 128, (a.m, a.k), generator=g, device="cuda", dtype=torch.int8)
         s = torch.full((a.m,), 0.01, device="cuda")
+        if a.epi == "qkv":   # QKV projection with QK-norm and RoPE in the epilogue (N = 3 * heads * 128)
+            qn = torch.ones(128, device="cuda")
+            cos = torch.rand((a.m, 64), generator=g, device="cuda")
+            sin = torch.rand((a.m, 64), generator=g, device="cuda")
+            ms = _time(lambda: cuda.gemm_i8_qkv_rope(w, x, s, qn, qn, cos, sin, 64), a.iters)
+            out.update(m=a.m, n=a.n, k=a.k, epi=a.epi, ms=ms, tops=2.0 * a.m * a.n * a.k / ms / 1e9)
+            print(json.dumps(out))
+            return
         kind = {"plain": h3c_b200.EPI_PLAIN, "gate": h3c_b200.EPI_GATE, "gelu": h3c_b200.EPI_GELU,
                 "swiglu": h3c_b200.EPI_SWIGLU}[a.epi]
         n_out = a.n // 2 if a.epi == "swiglu" else a.n

@@ -42,20 +42,35 @@ constexpr int GROUP_M = 8;       // rasterisation: bands of 8 row-tiles share th
 constexpr int EPI_QKV_ROPE_SCATTER = 5;
 constexpr int STG_ROW = 256 + 16;                 // staged bf16 head slice + pad against bank conflicts
 constexpr int STG_WARP = 32 * STG_ROW;            // per epilogue warp
+constexpr int OUT_WARP = 32 * 128;                // TMA-store staging per epilogue warp
+constexpr int TAB_GROUP = 4 * 32 * 128;           // cos and sin rows of one 32-row group: four boxes of 32 x 128 bytes
+constexpr int BAR_BYTES = 512;                    // barriers, TMEM slot, abort word
 template <int CTAS, int EPI = 0> struct Shape {
     static constexpr bool STAGED = EPI == EPI_QKV_ROPE_SCATTER;
-    static constexpr int STAGES = STAGED ? (CTAS == 2 ? 4 : 3) : CTAS == 2 ? 6 : 4;
+    // QKV + RoPE epilogue of a pair: cos / sin rows arrive by TMA (16 KiB per 32-row group) and Q, K, V leave by
+    // TMA stores, which takes two stages of the ring
+    static constexpr bool QTMA = EPI == H3B_EPI_QKV_ROPE && CTAS == 2;
+    static constexpr int STAGES = STAGED ? (CTAS == 2 ? 4 : 3) : QTMA ? 4 : CTAS == 2 ? 6 : 4;
     static constexpr int B_BYTES = BN * BK / CTAS;          // B rows held by one CTA: 32 KiB or 16 KiB
     static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;   // per CTA
     static constexpr int TILE_M = BM * CTAS;
-    static constexpr size_t SMEM_BYTES = 1024 /*alignment slack*/ + (size_t)STAGES * STAGE_BYTES + 256 +
-                                         (STAGED ? 8 * (size_t)STG_WARP : 0);
+    // Every other epilogue leaves through TMA stores: each of the eight epilogue warps owns 32 rows x 128 bytes
+    // of shared memory (128-byte swizzle), placed between the operand ring and the barriers.
+    static constexpr bool TSTORE = EPI != EPI_QKV_ROPE_SCATTER && EPI != H3B_EPI_QKV_ROPE;
+    static constexpr int OUT_BYTES = (TSTORE || QTMA) ? 8 * OUT_WARP : 0;
+    static constexpr int TAB_BYTES = QTMA ? 4 * TAB_GROUP : 0;
+    static constexpr size_t SMEM_BYTES = 1024 /*alignment slack*/ + (size_t)STAGES * STAGE_BYTES + OUT_BYTES + TAB_BYTES +
+                                         BAR_BYTES + (STAGED ? 8 * (size_t)STG_WARP : 0);
 };
 }  // namespace gemm
 
 struct GemmParams {
     CUtensorMap tmap_a;   // X codes  [M, K] int8, box 128 (k) x 128 (m)
     CUtensorMap tmap_b;   // W        [N, K] int8, box 128 (k) x 128 (n)
+    CUtensorMap tmap_y;   // Y        [M, n_out], box 128 bytes x 32 rows, 128-byte swizzle
+    CUtensorMap tmap_res; // residual of the gate epilogue, same geometry
+    CUtensorMap tmap_yk, tmap_yv;     // QKV + RoPE by TMA: K and V outputs [M, heads * 128] bf16 (Q is tmap_y)
+    CUtensorMap tmap_cos, tmap_sin;   // QKV + RoPE by TMA: tables [M, rope_half] f32, box 32 floats x 32 rows
     int M, N, K;          // N = rows of W
     int n_out;            // columns of Y (N, or N/2 for SwiGLU)
     int m_tiles, n_tiles, k_blocks;
@@ -113,6 +128,26 @@ __device__ __forceinline__ void rope_split_half(float (&v)[128], const float *cr
     for (int d4 = 0; d4 < RH / 4; d4++) {
         const float4 c4 = __ldg(reinterpret_cast<const float4 *>(cr) + d4);
         const float4 s4 = __ldg(reinterpret_cast<const float4 *>(sr) + d4);
+        const float cc[4] = {c4.x, c4.y, c4.z, c4.w}, sn[4] = {s4.x, s4.y, s4.z, s4.w};
+#pragma unroll
+        for (int e = 0; e < 4; e++) {
+            const int d = d4 * 4 + e;
+            const float lo = v[d], hi = v[d + RH];
+            v[d] = __fsub_rn(__fmul_rn(lo, cc[e]), __fmul_rn(hi, sn[e]));
+            v[d + RH] = __fadd_rn(__fmul_rn(hi, cc[e]), __fmul_rn(lo, sn[e]));
+        }
+    }
+}
+
+// The same with the cos / sin rows of the warp's 32 rows in shared memory, as TMA left them: per table two
+// boxes of 32 rows x 128 bytes (dimensions 0-31 and 32-63) under the 128-byte swizzle; sin follows cos.
+template <int RH>
+__device__ __forceinline__ void rope_split_half_smem(float (&v)[128], const uint8_t *tab, int lane) {
+#pragma unroll
+    for (int d4 = 0; d4 < RH / 4; d4++) {
+        const uint32_t off = (uint32_t)(d4 >> 3) * 4096u + (uint32_t)lane * 128u + (uint32_t)(((d4 & 7) ^ (lane & 7)) << 4);
+        const float4 c4 = *reinterpret_cast<const float4 *>(tab + off);
+        const float4 s4 = *reinterpret_cast<const float4 *>(tab + 8192 + off);
         const float cc[4] = {c4.x, c4.y, c4.z, c4.w}, sn[4] = {s4.x, s4.y, s4.z, s4.w};
 #pragma unroll
         for (int e = 0; e < 4; e++) {
@@ -185,9 +220,15 @@ __global__ void __launch_bounds__(gemm::THREADS, 1) k_gemm_i8(const __grid_const
     extern __shared__ uint8_t smem_raw[];
     // 1024-byte alignment: required by the 128-byte swizzle pattern of TMA and the MMA descriptors
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
-    uint64_t *bars = reinterpret_cast<uint64_t *>(smem + (size_t)STAGES * STAGE_BYTES);
+    constexpr bool TSTORE = Shape<CTAS, EPI>::TSTORE;
+    uint8_t *out_stage = smem + (size_t)STAGES * STAGE_BYTES;
+    constexpr bool QTMA = Shape<CTAS, EPI>::QTMA;
+    uint8_t *tab_stage = out_stage + Shape<CTAS, EPI>::OUT_BYTES;
+    uint64_t *bars = reinterpret_cast<uint64_t *>(tab_stage + Shape<CTAS, EPI>::TAB_BYTES);
     uint64_t *full = bars, *empty = bars + STAGES, *tmem_full = bars + 2 * STAGES, *tmem_empty = bars + 2 * STAGES + 2;
-    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 2 * STAGES + 4);
+    uint64_t *res_bar = bars + 2 * STAGES + 4;   // one per epilogue warp (residual tiles of the gate epilogue)
+    uint64_t *tab_full = bars + 2 * STAGES + 12, *tab_empty = bars + 2 * STAGES + 16;   // per 32-row group
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 2 * STAGES + 20);
     volatile int *abort_word = reinterpret_cast<volatile int *>(tmem_slot + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -206,10 +247,16 @@ __global__ void __launch_bounds__(gemm::THREADS, 1) k_gemm_i8(const __grid_const
             mbar_init(&tmem_full[b], 1);
             mbar_init(&tmem_empty[b], 8 * CTAS);   // one arrival per epilogue warp of every CTA of the pair
         }
+        for (int w = 0; w < 8; w++) mbar_init(&res_bar[w], 1);
+        for (int g = 0; g < 4; g++) {
+            mbar_init(&tab_full[g], 1);
+            mbar_init(&tab_empty[g], 2);   // the two warps that share the rows
+        }
         *abort_word = 0;
         mbar_fence_init();
         tma_prefetch_desc(&p.tmap_a);
         tma_prefetch_desc(&p.tmap_b);
+        if (TSTORE || QTMA) tma_prefetch_desc(&p.tmap_y);
     }
     if (warp == 1) {
         if (CTAS == 2) {
@@ -315,15 +362,20 @@ __global__ void __launch_bounds__(gemm::THREADS, 1) k_gemm_i8(const __grid_const
         const int half = (warp - 2) >> 2;
         const uint32_t lane_base = (uint32_t)(q * 32) << 16;
         OutT *y = reinterpret_cast<OutT *>(p.y);
-        const OutT *res = reinterpret_cast<const OutT *>(p.residual);
+        (void)y;
         constexpr int VEC = OutTraits<OutT>::VEC;
         constexpr int CHUNKS = (EPI == H3B_EPI_SWIGLU) ? (BN / 2) / 64 : BN / 64;   // per warp
+        uint8_t *ostg = out_stage + (size_t)(warp - 2) * OUT_WARP;
+        uint64_t *rbar = &res_bar[warp - 2];
+        uint32_t res_phase = 0;
+        int tab_it = 0;   // tiles of this CTA that used the cos / sin buffer so far
         int it = 0;
         for (int tile = first_tile; tile < total_tiles; tile += tile_step, it++) {
             int mt, nt;
             tile_coords(tile, p.m_tiles, p.n_tiles, mt, nt);
             const int buf = it & 1;
-            const int row = mt * TILE_M + cta_rank * BM + q * 32 + lane;
+            const int row0 = mt * TILE_M + cta_rank * BM + q * 32;
+            const int row = row0 + lane;
             const bool row_ok = row < p.M;
             const int c0 = (EPI == H3B_EPI_SWIGLU) ? nt * (BN / 2) : nt * BN;   // first output column
             const float a = row_ok ? p.act_scale[row] : 0.0f;
@@ -332,13 +384,29 @@ __global__ void __launch_bounds__(gemm::THREADS, 1) k_gemm_i8(const __grid_const
                 const size_t mrow = p.row_map ? p.row_map[row] : (size_t)row;
                 gate = p.mod + (mrow * p.slots + p.gate_slot) * (size_t)p.n_out;
             }
+            // QKV + RoPE by TMA: does a head of this tile rotate?  Both warps of a row group see the same answer.
+            bool tile_rope = false;
+            uint8_t *tab = tab_stage + (size_t)q * TAB_GROUP;
+            if constexpr (QTMA) {
+                const int g0 = c0 >> 7;
+                tile_rope = p.rope_half != 0 && (g0 / p.heads < 2 || (c0 + 128 < p.N && (g0 + 1) / p.heads < 2));
+                if (tile_rope && half == 0 && lane == 0 &&
+                    mbar_wait(&tab_empty[q], (tab_it & 1) ^ 1, abort_word, p.status, H3B_ST_TIMEOUT_EMPTY)) {
+                    mbar_expect_tx(&tab_full[q], TAB_GROUP);
+                    tma_load_2d(tab, &p.tmap_cos, &tab_full[q], 0, row0);
+                    tma_load_2d(tab + 4096, &p.tmap_cos, &tab_full[q], 32, row0);
+                    tma_load_2d(tab + 8192, &p.tmap_sin, &tab_full[q], 0, row0);
+                    tma_load_2d(tab + 12288, &p.tmap_sin, &tab_full[q], 32, row0);
+                }
+                __syncwarp();
+            }
             bool ok = mbar_wait(&tmem_full[buf], (it >> 1) & 1, abort_word, p.status, H3B_ST_TIMEOUT_TMEM_FULL);
             tc_fence_after();
             const uint32_t t_addr = tmem_base + lane_base + (uint32_t)buf * BN;
             if constexpr (EPI == H3B_EPI_QKV_ROPE || EPI == EPI_QKV_ROPE_SCATTER) {
                 // This warp's 128 columns are exactly one head of Q, K or V; the thread holds its row of it.
                 const int col = c0 + half * 128;
-                if (ok && col < p.N) {
+                if (ok && col < p.N && (!QTMA || row0 < p.M)) {
                     const int g = col >> 7, which = g / p.heads, head = g - which * p.heads;
                     uint32_t r[128];
 #pragma unroll
@@ -357,7 +425,7 @@ __global__ void __launch_bounds__(gemm::THREADS, 1) k_gemm_i8(const __grid_const
                             v[4 * c4 + e] = val;
                         }
                     }
-                    if (row_ok) {
+                    if (row_ok || QTMA) {   // by TMA every lane computes; rows past M are clipped by the store
                         if (which < 2) {
                             // Sum of squares in the order of the stand-alone kernel (k_qkv_rope: sixteen lanes
                             // with eight consecutive values each, then an xor butterfly), so that a chain
@@ -385,12 +453,38 @@ __global__ void __launch_bounds__(gemm::THREADS, 1) k_gemm_i8(const __grid_const
                                 v[4 * c4 + 2] = __fmul_rn(__fmul_rn(v[4 * c4 + 2], inv), n4.z);
                                 v[4 * c4 + 3] = __fmul_rn(__fmul_rn(v[4 * c4 + 3], inv), n4.w);
                             }
-                            if (p.rope_half == 48)
-                                rope_split_half<48>(v, p.cosT + (size_t)row * 48, p.sinT + (size_t)row * 48);
-                            else if (p.rope_half == 64)
-                                rope_split_half<64>(v, p.cosT + (size_t)row * 64, p.sinT + (size_t)row * 64);
+                            if constexpr (QTMA) {
+                                if (p.rope_half) {
+                                    if (!mbar_wait(&tab_full[q], tab_it & 1, abort_word, p.status, H3B_ST_TIMEOUT_FULL)) break;
+                                    if (p.rope_half == 48) rope_split_half_smem<48>(v, tab, lane);
+                                    else rope_split_half_smem<64>(v, tab, lane);
+                                }
+                            } else {
+                                if (p.rope_half == 48)
+                                    rope_split_half<48>(v, p.cosT + (size_t)row * 48, p.sinT + (size_t)row * 48);
+                                else if (p.rope_half == 64)
+                                    rope_split_half<64>(v, p.cosT + (size_t)row * 64, p.sinT + (size_t)row * 64);
+                            }
                         }
-                        if constexpr (EPI == H3B_EPI_QKV_ROPE) {
+                        if constexpr (QTMA) {
+                            const CUtensorMap *om = which == 0 ? &p.tmap_y : which == 1 ? &p.tmap_yk : &p.tmap_yv;
+#pragma unroll
+                            for (int gi = 0; gi < 2; gi++) {   // the head in two groups of 64 dimensions
+                                if (lane == 0) tma_store_wait_read<0>();
+                                __syncwarp();
+#pragma unroll
+                                for (int u = 0; u < 8; u++)
+                                    OutTraits<__nv_bfloat16>::store(
+                                        reinterpret_cast<__nv_bfloat16 *>(ostg + lane * 128 + ((u ^ (lane & 7)) << 4)),
+                                        &v[gi * 64 + u * 8]);
+                                fence_proxy_async_smem();
+                                __syncwarp();
+                                if (lane == 0) {
+                                    tma_store_2d(om, ostg, head * 128 + gi * 64, row0);
+                                    tma_store_commit();
+                                }
+                            }
+                        } else if constexpr (EPI == H3B_EPI_QKV_ROPE) {
                             __nv_bfloat16 *dst = reinterpret_cast<__nv_bfloat16 *>(which == 0 ? p.y : which == 1 ? p.y_k : p.y_v) +
                                                  ((size_t)row * p.heads + head) * 128;
 #pragma unroll
@@ -400,7 +494,7 @@ __global__ void __launch_bounds__(gemm::THREADS, 1) k_gemm_i8(const __grid_const
                     if constexpr (EPI == EPI_QKV_ROPE_SCATTER) {
                         // lane = row: park the head slices of the warp's 32 rows in shared memory, then let sixteen
                         // lanes write one 256-byte slice each, two rows per store instruction
-                        uint8_t *stg = smem + (size_t)STAGES * STAGE_BYTES + 256 + (size_t)(warp - 2) * STG_WARP;
+                        uint8_t *stg = reinterpret_cast<uint8_t *>(bars) + BAR_BYTES + (size_t)(warp - 2) * STG_WARP;
 #pragma unroll
                         for (int d = 0; d < 128; d += 8)
                             OutTraits<__nv_bfloat16>::store(reinterpret_cast<__nv_bfloat16 *>(stg + lane * STG_ROW) + d, &v[d]);
@@ -422,12 +516,29 @@ __global__ void __launch_bounds__(gemm::THREADS, 1) k_gemm_i8(const __grid_const
                     }
                 }
             } else
-            if (ok) {
+            if (ok && row0 < p.M) {
+                // 128 bytes of every row form one staged group: two 32-column chunks of a 16-bit type, one of a
+                // 32-bit type.  A thread that stored its own row straight to global memory made each store touch
+                // 32 lines: 32 passes of the load/store unit per instruction, behind which the mbarrier polls
+                // and the TMA and MMA issues of the other warps queued (13,000 cycles per tile of bf16, 29,000
+                // with the residual reads of the gate).
+                constexpr int PER = sizeof(OutT) == 2 ? 2 : 1;   // chunks per group
+                constexpr int UPC = 32 / VEC;                    // 16-byte units per chunk
 #pragma unroll 1
                 for (int i = 0; i < CHUNKS; i++) {
                     const int ch = half * CHUNKS + i;
                     const int col = c0 + ch * 32;
                     if (col >= p.n_out) break;   // uniform across the warp
+                    const int sub = i & (PER - 1);
+                    const int gcol = col - sub * 32;
+                    if (sub == 0) {
+                        if (lane == 0) tma_store_wait_read<0>();   // the previous group has left the buffer
+                        __syncwarp();
+                        if (EPI == H3B_EPI_GATE && lane == 0) {
+                            mbar_expect_tx(rbar, OUT_WARP);
+                            tma_load_2d(ostg, &p.tmap_res, rbar, gcol, row0);
+                        }
+                    }
                     uint32_t r[32];
                     tmem_ld_32x32b_x32(t_addr + ch * 32, r);
                     uint32_t r2[32];
@@ -471,37 +582,59 @@ __global__ void __launch_bounds__(gemm::THREADS, 1) k_gemm_i8(const __grid_const
                         }
                     }
                     tmem_ld_wait();
-                    if (!row_ok) continue;
-                    if constexpr (std::is_same<OutT, int32_t>::value) {
+                    if (EPI == H3B_EPI_GATE && sub == 0) {
+                        ok = mbar_wait(rbar, res_phase, abort_word, p.status, H3B_ST_TIMEOUT_FULL);
+                        res_phase ^= 1;
+                        if (!ok) break;
+                    }
+                    const bool lora_on = p.lora && row_ok;
 #pragma unroll
-                        for (int v = 0; v < 32; v += 4)
-                            if (col + v < p.n_out)
-                                *reinterpret_cast<uint4 *>(y + (size_t)row * p.n_out + col + v) =
-                                    make_uint4(r[v], r[v + 1], r[v + 2], r[v + 3]);
-                    } else {
-#pragma unroll
-                        for (int v = 0; v < 32; v += VEC) {
-                            if (!full && col + v >= p.n_out) break;
+                    for (int v = 0; v < 32; v += VEC) {
+                        // rows past M and columns past n_out are clipped by the store
+                        uint8_t *cell = ostg + lane * 128 + (((sub * UPC + v / VEC) ^ (lane & 7)) << 4);
+                        if constexpr (std::is_same<OutT, int32_t>::value) {
+                            *reinterpret_cast<uint4 *>(cell) = make_uint4(r[v], r[v + 1], r[v + 2], r[v + 3]);
+                        } else {
                             float out[VEC], resv[VEC];
-                            if (EPI == H3B_EPI_GATE) OutTraits<OutT>::load(res + (size_t)row * p.n_out + col + v, resv);
+                            if (EPI == H3B_EPI_GATE) OutTraits<OutT>::load(reinterpret_cast<const OutT *>(cell), resv);
 #pragma unroll
                             for (int e = 0; e < VEC; e++) {
                                 float val = __fmul_rn(__fmul_rn(a, sc[v + e]), (float)(int32_t)r[v + e]);
-                                if (p.lora) val = __fadd_rn(val, __ldg(p.lora + (size_t)row * p.N + col + v + e));
+                                if (lora_on && col + v + e < p.n_out)
+                                    val = __fadd_rn(val, __ldg(p.lora + (size_t)row * p.N + col + v + e));
                                 if (EPI == H3B_EPI_GATE) {
                                     val = __fadd_rn(resv[e], __fmul_rn(val, gt[v + e]));
                                 } else if (EPI == H3B_EPI_GELU) {
                                     val = sizeof(OutT) == 2 ? gelu_tanh_fast(val) : gelu_tanh_dev(val);
                                 } else if (EPI == H3B_EPI_SWIGLU) {
                                     float u = __fmul_rn(__fmul_rn(a, sc2[v + e]), (float)(int32_t)r2[v + e]);
-                                    if (p.lora) u = __fadd_rn(u, __ldg(p.lora + (size_t)row * p.N + p.n_out + col + v + e));
+                                    if (lora_on && col + v + e < p.n_out)
+                                        u = __fadd_rn(u, __ldg(p.lora + (size_t)row * p.N + p.n_out + col + v + e));
                                     val = __fmul_rn(val / __fadd_rn(1.0f, expf(-val)), u);
                                 }
                                 out[e] = val;
                             }
-                            OutTraits<OutT>::store(y + (size_t)row * p.n_out + col + v, out);
+                            OutTraits<OutT>::store(reinterpret_cast<OutT *>(cell), out);
                         }
                     }
+                    if (sub == PER - 1 || col + 32 >= p.n_out) {
+                        fence_proxy_async_smem();
+                        __syncwarp();
+                        if (lane == 0) {
+                            tma_store_2d(&p.tmap_y, ostg, gcol, row0);
+                            tma_store_commit();
+                        }
+                    }
+                }
+            }
+            if constexpr (QTMA) {
+                // Give the cos / sin buffer back.  A warp that did not rotate (a V head, rows past M) still waits
+                // for the tables first, so that it cannot run a tile ahead and arrive twice in one phase.
+                if (tile_rope) {
+                    const bool seen = mbar_wait(&tab_full[q], tab_it & 1, abort_word, p.status, H3B_ST_TIMEOUT_FULL);
+                    __syncwarp();
+                    if (seen && lane == 0) mbar_arrive(&tab_empty[q]);
+                    tab_it++;
                 }
             }
             // hand the accumulator back to the MMA warp
@@ -513,6 +646,7 @@ __global__ void __launch_bounds__(gemm::THREADS, 1) k_gemm_i8(const __grid_const
             }
             if (*abort_word) break;
         }
+        if (TSTORE && lane == 0) tma_store_wait<0>();
     }
 
     tc_fence_before();
@@ -531,6 +665,36 @@ template <int EPI, typename OutT>
 static int gemm_launch_t(h3_cuda *cuda, GemmParams &p, char *error, size_t error_size) {
     using namespace gemm;
     // CTA pairs whenever there is more than one 128-row band (H3B_GEMM_PAIRS=0 keeps single CTAs)
+    if constexpr (Shape<1, EPI>::TSTORE) {
+        const CUtensorMapDataType dt = std::is_same<OutT, float>::value           ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32
+                                       : std::is_same<OutT, int32_t>::value       ? CU_TENSOR_MAP_DATA_TYPE_INT32
+                                       : std::is_same<OutT, __nv_bfloat16>::value ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
+                                                                                  : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+        const uint32_t box = 128 / sizeof(OutT);
+        int rc = h3b_encode_tmap_2d(&p.tmap_y, dt, sizeof(OutT), p.y, (uint64_t)p.n_out, (uint64_t)p.M,
+                                    (uint64_t)p.n_out * sizeof(OutT), box, 32, CU_TENSOR_MAP_SWIZZLE_128B);
+        if (rc == 0 && EPI == H3B_EPI_GATE)
+            rc = h3b_encode_tmap_2d(&p.tmap_res, dt, sizeof(OutT), p.residual, (uint64_t)p.n_out, (uint64_t)p.M,
+                                    (uint64_t)p.n_out * sizeof(OutT), box, 32, CU_TENSOR_MAP_SWIZZLE_128B);
+        if (rc != 0) return fail(error, error_size, "gemm_i8: cuTensorMapEncodeTiled(Y) failed (%d)", rc);
+    }
+    if constexpr (EPI == H3B_EPI_QKV_ROPE) {
+        const uint64_t width = (uint64_t)p.heads * 128;
+        void *outs[3] = {p.y, p.y_k, p.y_v};
+        CUtensorMap *maps[3] = {&p.tmap_y, &p.tmap_yk, &p.tmap_yv};
+        int rc = 0;
+        for (int i = 0; i < 3 && rc == 0; i++)
+            rc = h3b_encode_tmap_2d(maps[i], CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, outs[i], width, (uint64_t)p.M, width * 2, 64, 32,
+                                    CU_TENSOR_MAP_SWIZZLE_128B);
+        if (rc == 0 && p.rope_half) {
+            rc = h3b_encode_tmap_2d(&p.tmap_cos, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, p.cosT, (uint64_t)p.rope_half, (uint64_t)p.M,
+                                    (uint64_t)p.rope_half * 4, 32, 32, CU_TENSOR_MAP_SWIZZLE_128B);
+            if (rc == 0)
+                rc = h3b_encode_tmap_2d(&p.tmap_sin, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, p.sinT, (uint64_t)p.rope_half,
+                                        (uint64_t)p.M, (uint64_t)p.rope_half * 4, 32, 32, CU_TENSOR_MAP_SWIZZLE_128B);
+        }
+        if (rc != 0) return fail(error, error_size, "gemm_i8: cuTensorMapEncodeTiled(QKV outputs, RoPE tables) failed (%d)", rc);
+    }
     static const bool pairs_allowed = [] {
         const char *e = getenv("H3B_GEMM_PAIRS");
         return !(e && e[0] == '0');
