@@ -159,6 +159,46 @@ __device__ __forceinline__ void rope_split_half_smem(float (&v)[128], const uint
     }
 }
 
+// The same for a warp that owns a staging buffer of 32 rows x STG_ROW bytes: the tables of the warp's 32 rows
+// come in by coalesced loads, 32 dimensions at a time (cos in the first 128 bytes of a row, sin in the next),
+// and every thread then reads its own row from shared memory.  Called by the whole warp.
+template <int RH, int ROW_BYTES>
+__device__ __forceinline__ void rope_split_half_staged(float (&v)[128], const float *cosT, const float *sinT, int row_first,
+                                                       int rows, uint8_t *stg, int lane) {
+#pragma unroll
+    for (int ph = 0; ph < 2; ph++) {
+        constexpr int FULL = 32;
+        const int nd = (RH - FULL * ph) < FULL ? (RH - FULL * ph) : FULL;   // dimensions of this pass
+        const int u = lane & 7;
+#pragma unroll 2
+        for (int rr = 0; rr < 8; rr++) {
+            const int r = rr * 4 + (lane >> 3);
+            if (u < nd / 4 && row_first + r < rows) {
+                const size_t at = (size_t)(row_first + r) * RH + FULL * ph + u * 4;
+                *reinterpret_cast<float4 *>(stg + r * ROW_BYTES + u * 16) = __ldg(reinterpret_cast<const float4 *>(cosT + at));
+                *reinterpret_cast<float4 *>(stg + r * ROW_BYTES + 128 + u * 16) = __ldg(reinterpret_cast<const float4 *>(sinT + at));
+            }
+        }
+        __syncwarp();
+#pragma unroll
+        for (int d4 = 0; d4 < FULL / 4; d4++) {
+            if (d4 < nd / 4) {
+                const float4 c4 = *reinterpret_cast<const float4 *>(stg + lane * ROW_BYTES + d4 * 16);
+                const float4 s4 = *reinterpret_cast<const float4 *>(stg + lane * ROW_BYTES + 128 + d4 * 16);
+                const float cc[4] = {c4.x, c4.y, c4.z, c4.w}, sn[4] = {s4.x, s4.y, s4.z, s4.w};
+#pragma unroll
+                for (int e = 0; e < 4; e++) {
+                    const int d = FULL * ph + d4 * 4 + e;
+                    const float lo = v[d], hi = v[d + RH];
+                    v[d] = __fsub_rn(__fmul_rn(lo, cc[e]), __fmul_rn(hi, sn[e]));
+                    v[d + RH] = __fadd_rn(__fmul_rn(hi, cc[e]), __fmul_rn(lo, sn[e]));
+                }
+            }
+        }
+        __syncwarp();
+    }
+}
+
 template <typename T> struct OutTraits;
 template <> struct OutTraits<float> {
     static constexpr int VEC = 4;
@@ -425,7 +465,8 @@ __global__ void __launch_bounds__(gemm::THREADS, 1) k_gemm_i8(const __grid_const
                             v[4 * c4 + e] = val;
                         }
                     }
-                    if (row_ok || QTMA) {   // by TMA every lane computes; rows past M are clipped by the store
+                    // by TMA and in the scatter form every lane computes; rows past M are not stored
+                    if (row_ok || QTMA || EPI == EPI_QKV_ROPE_SCATTER) {
                         if (which < 2) {
                             // Sum of squares in the order of the stand-alone kernel (k_qkv_rope: sixteen lanes
                             // with eight consecutive values each, then an xor butterfly), so that a chain
@@ -459,6 +500,10 @@ __global__ void __launch_bounds__(gemm::THREADS, 1) k_gemm_i8(const __grid_const
                                     if (p.rope_half == 48) rope_split_half_smem<48>(v, tab, lane);
                                     else rope_split_half_smem<64>(v, tab, lane);
                                 }
+                            } else if constexpr (EPI == EPI_QKV_ROPE_SCATTER) {
+                                uint8_t *tstg = reinterpret_cast<uint8_t *>(bars) + BAR_BYTES + (size_t)(warp - 2) * STG_WARP;
+                                if (p.rope_half == 48) rope_split_half_staged<48, STG_ROW>(v, p.cosT, p.sinT, row0, p.M, tstg, lane);
+                                else if (p.rope_half == 64) rope_split_half_staged<64, STG_ROW>(v, p.cosT, p.sinT, row0, p.M, tstg, lane);
                             } else {
                                 if (p.rope_half == 48)
                                     rope_split_half<48>(v, p.cosT + (size_t)row * 48, p.sinT + (size_t)row * 48);
