@@ -249,6 +249,41 @@ class Cuda:
         call("h3b_gemm_i8_dequant_f32_w_act_dev_noalloc", self.h, weight.h, ptr(x_f32), convrot_gs, m, ptr(out))
         return out
 
+    # ---- the step on either side of the block chain (f32, device tensors)
+    def gemm_f32_dd(self, x, w):
+        """h3_cuda_gemm_f32_dd: x [m,k] @ w [n,k]^T -> [m,n], all f32."""
+        import torch
+        y = torch.empty((x.shape[0], w.shape[0]), dtype=torch.float32, device=x.device)
+        call("h3_cuda_gemm_f32_dd", self.h, ptr(x), ptr(w), x.shape[0], w.shape[0], x.shape[1], ptr(y), None)
+        return y
+
+    def bias_add_f32(self, y, bias):
+        call("h3_cuda_bias_add_f32_dev", self.h, ptr(y), ptr(bias), y.shape[0], y.shape[1])
+        return y
+
+    def dense_f32(self, x, w, bias=None):
+        """y = x W^T + b in one launch (patch embedding: k = 96; final heads: n = 96 or 32)."""
+        import torch
+        y = torch.empty((x.shape[0], w.shape[0]), dtype=torch.float32, device=x.device)
+        call("h3b_dense_f32_dev", self.h, ptr(x), ptr(w), ptr(bias), x.shape[0], w.shape[0], x.shape[1], ptr(y))
+        return y
+
+    def final_head_f32(self, x, norm_w, modulation, w, bias, eps=1e-5):
+        """adaLN with shift = modulation[0], scale = modulation[1] for every token, then the dense head."""
+        import torch
+        seq, hidden = x.shape
+        need = int(load().h3b_final_head_scratch_bytes(seq, hidden))
+        scratch = torch.empty(need, dtype=torch.uint8, device=x.device)
+        y = torch.empty((seq, w.shape[0]), dtype=torch.float32, device=x.device)
+        call("h3b_final_head_f32_dev", self.h, ptr(x), ptr(norm_w), ptr(modulation), seq, hidden, ptr(w), ptr(bias),
+             w.shape[0], float(eps), ptr(scratch), need, ptr(y))
+        return y
+
+    def euler_step_f32(self, sample, velocity, sigma, sigma_next):
+        """In place: sample += (sigma - sigma_next) * velocity; raises H3Error for a pair the reference rejects."""
+        call("h3b_euler_step_f32_dev", self.h, ptr(sample), ptr(velocity), sample.numel(), float(sigma), float(sigma_next))
+        return sample
+
     # ---- attention
     def sdpa_bf16(self, q, k, v, scale=None, out=None):
         """q [lq,H,128], k/v [lk,H,128] bf16 views whose last two dims are contiguous -> [lq, H*128] bf16."""

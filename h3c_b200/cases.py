@@ -34,7 +34,7 @@ def main():
     import torch
     import h3c_b200
     ap = argparse.ArgumentParser()
-    ap.add_argument("case", choices=["gemm", "gemm_fp4", "attn", "norm", "rope", "peak"])
+    ap.add_argument("case", choices=["gemm", "gemm_fp4", "attn", "norm", "rope", "peak", "sides"])
     ap.add_argument("--m", type=int, default=6144)
     ap.add_argument("--n", type=int, default=9216)
     ap.add_argument("--k", type=int, default=3072)
@@ -78,6 +78,17 @@ def main():
             out[name + "_burst_tops"] = v.value
             call("h3b_umma_peak_dev", cuda.h, kind, 2000000, C.byref(v))   # ~1 s: under the power limit
             out[name + "_sustained_tops"] = v.value
+    elif a.case == "sides":   # patch embedding, final head and Euler update of a.m tokens (f32, hidden = a.n)
+        lat = torch.randn((a.m, 96), generator=g, device="cuda")
+        pw, pb = torch.randn((a.n, 96), generator=g, device="cuda"), torch.randn(a.n, generator=g, device="cuda")
+        x = torch.randn((a.m, a.n), generator=g, device="cuda")
+        nw, mod = torch.ones(a.n, device="cuda"), torch.zeros((2, a.n), device="cuda")
+        fw, fb = torch.randn((96, a.n), generator=g, device="cuda"), torch.randn(96, generator=g, device="cuda")
+        vel = torch.randn((a.m, 96), generator=g, device="cuda")
+        out.update(m=a.m, hidden=a.n,
+                   patch_embed_ms=_time(lambda: cuda.dense_f32(lat, pw, pb), a.iters),
+                   final_head_ms=_time(lambda: cuda.final_head_f32(x, nw, mod, fw, fb), a.iters),
+                   euler_ms=_time(lambda: cuda.euler_step_f32(lat, vel, 0.8, 0.7), a.iters))
     elif a.case == "gemm_fp4":
         x4 = torch.randint(0, 256, (a.m, a.k // 2), generator=g, device="cuda", dtype=torch.uint8)
         w4 = torch.randint(0, 256, (a.n, a.k // 2), generator=g, device="cuda", dtype=torch.uint8)

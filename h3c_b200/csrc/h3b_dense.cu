@@ -12,23 +12,26 @@
 #include <math.h>
 #include <stdint.h>
 
-#include "h3_b200.h"
 #include "h3b_internal.h"
 
 namespace h3b {
 
 namespace dense {
-constexpr int BM = 64, BN = 64, BK = 16, THREADS = 256, PAD = 4;
+constexpr int BN = 64, BK = 16, PAD = 4;
 }
 
 // y[m, n] = sum_k x[m, k] * w[n, k] (+ bias[n]); both operands row-major with k contiguous.
-// 64 x 64 tile per CTA, 16 k per step, a 4 x 4 block of outputs per thread; operands are transposed into
-// shared memory so that a thread reads its four rows / columns as one float4.
-template <bool VEC>
-__global__ void __launch_bounds__(dense::THREADS) k_dense_f32(const float *__restrict__ x, const float *__restrict__ w,
-                                                               const float *__restrict__ bias, size_t m, size_t n, size_t k,
-                                                               float *__restrict__ y) {
+// BM x 64 tile per CTA (BM = 64 with 256 threads, or 32 with 128 where the taller tile would leave SMs idle),
+// 16 k per step, a 4 x 4 block of outputs per thread; operands are transposed into shared memory so that a
+// thread reads its four rows / columns as one float4, and the next step's global loads are in flight while
+// the current step is multiplied.
+template <int BM, bool VEC>
+__global__ void __launch_bounds__(BM * 4) k_dense_f32(const float *__restrict__ x, const float *__restrict__ w,
+                                                      const float *__restrict__ bias, size_t m, size_t n, size_t k,
+                                                      float *__restrict__ y) {
     using namespace dense;
+    constexpr int THREADS = BM * 4;
+    constexpr int WREP = BN * 4 / THREADS;   // rows of W each thread fetches per step (1 or 2)
     __shared__ __align__(16) float xs[BK][BM + PAD];
     __shared__ __align__(16) float ws[BK][BN + PAD];
     const int t = threadIdx.x, tx = t & 15, ty = t >> 4;
@@ -40,38 +43,38 @@ __global__ void __launch_bounds__(dense::THREADS) k_dense_f32(const float *__res
 #pragma unroll
         for (int j = 0; j < 4; j++) acc[i][j] = 0.0f;
 
+    auto fetch = [&](const float *base, size_t row, size_t rows, size_t kk, float (&v)[4]) {
+        v[0] = v[1] = v[2] = v[3] = 0.0f;
+        if (row >= rows) return;
+        const float *src = base + row * k + kk;
+        if (VEC && kk + 4 <= k) {
+            const float4 q = __ldg(reinterpret_cast<const float4 *>(src));
+            v[0] = q.x; v[1] = q.y; v[2] = q.z; v[3] = q.w;
+        } else {
+#pragma unroll
+            for (int i = 0; i < 4; i++)
+                if (kk + i < k) v[i] = __ldg(src + i);
+        }
+    };
+    float xv[4], wv[WREP][4];
+    fetch(x, row0 + lr, m, lk, xv);
+#pragma unroll
+    for (int rep = 0; rep < WREP; rep++) fetch(w, col0 + lr + rep * (THREADS / 4), n, lk, wv[rep]);
+
     for (size_t k0 = 0; k0 < k; k0 += BK) {
-        float xv[4] = {0.0f, 0.0f, 0.0f, 0.0f}, wv[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-        const size_t kk = k0 + lk;
-        if (row0 + lr < m) {
-            const float *src = x + (row0 + lr) * k + kk;
-            if (VEC && kk + 4 <= k) {
-                const float4 v = __ldg(reinterpret_cast<const float4 *>(src));
-                xv[0] = v.x; xv[1] = v.y; xv[2] = v.z; xv[3] = v.w;
-            } else {
-#pragma unroll
-                for (int i = 0; i < 4; i++)
-                    if (kk + i < k) xv[i] = __ldg(src + i);
-            }
-        }
-        if (col0 + lr < n) {
-            const float *src = w + (col0 + lr) * k + kk;
-            if (VEC && kk + 4 <= k) {
-                const float4 v = __ldg(reinterpret_cast<const float4 *>(src));
-                wv[0] = v.x; wv[1] = v.y; wv[2] = v.z; wv[3] = v.w;
-            } else {
-#pragma unroll
-                for (int i = 0; i < 4; i++)
-                    if (kk + i < k) wv[i] = __ldg(src + i);
-            }
-        }
         __syncthreads();   // the previous step's reads are done
 #pragma unroll
         for (int i = 0; i < 4; i++) {
             xs[lk + i][lr] = xv[i];
-            ws[lk + i][lr] = wv[i];
+#pragma unroll
+            for (int rep = 0; rep < WREP; rep++) ws[lk + i][lr + rep * (THREADS / 4)] = wv[rep][i];
         }
         __syncthreads();
+        if (k0 + BK < k) {
+            fetch(x, row0 + lr, m, k0 + BK + lk, xv);
+#pragma unroll
+            for (int rep = 0; rep < WREP; rep++) fetch(w, col0 + lr + rep * (THREADS / 4), n, k0 + BK + lk, wv[rep]);
+        }
 #pragma unroll
         for (int kq = 0; kq < BK; kq++) {
             const float4 a = *reinterpret_cast<const float4 *>(&xs[kq][ty * 4]);
@@ -83,28 +86,49 @@ __global__ void __launch_bounds__(dense::THREADS) k_dense_f32(const float *__res
                 for (int j = 0; j < 4; j++) acc[i][j] = __fmaf_rn(av[i], bv[j], acc[i][j]);
         }
     }
+    const size_t c = col0 + tx * 4;
+    float bv[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+    if (bias)
+#pragma unroll
+        for (int j = 0; j < 4; j++)
+            if (c + j < n) bv[j] = __ldg(bias + c + j);
+    const bool wide = n % 4 == 0 && c + 4 <= n && !((uintptr_t)y & 15);
 #pragma unroll
     for (int i = 0; i < 4; i++) {
         const size_t r = row0 + ty * 4 + i;
         if (r >= m) continue;
+        float o[4];
 #pragma unroll
-        for (int j = 0; j < 4; j++) {
-            const size_t c = col0 + tx * 4 + j;
-            if (c < n) y[r * n + c] = bias ? __fadd_rn(acc[i][j], __ldg(bias + c)) : acc[i][j];
+        for (int j = 0; j < 4; j++) o[j] = bias ? __fadd_rn(acc[i][j], bv[j]) : acc[i][j];
+        if (wide) {
+            *reinterpret_cast<float4 *>(y + r * n + c) = make_float4(o[0], o[1], o[2], o[3]);
+        } else {
+#pragma unroll
+            for (int j = 0; j < 4; j++)
+                if (c + j < n) y[r * n + c + j] = o[j];
         }
     }
+}
+
+template <int BM>
+static void dense_launch_t(h3_cuda *cuda, bool vec, const float *d_x, const float *d_w, const float *d_bias, size_t m, size_t n,
+                           size_t k, float *d_y) {
+    const dim3 grid((unsigned)((n + dense::BN - 1) / dense::BN), (unsigned)((m + BM - 1) / BM));
+    if (vec) k_dense_f32<BM, true><<<grid, BM * 4, 0, cuda->op_stream>>>(d_x, d_w, d_bias, m, n, k, d_y);
+    else k_dense_f32<BM, false><<<grid, BM * 4, 0, cuda->op_stream>>>(d_x, d_w, d_bias, m, n, k, d_y);
 }
 
 static int launch_dense(h3_cuda *cuda, const float *d_x, const float *d_w, const float *d_bias, size_t m, size_t n, size_t k,
                         float *d_y, char *error, size_t error_size) {
     using namespace dense;
     if (!cuda || !d_x || !d_w || !d_y || m == 0 || n == 0 || k == 0) return fail(error, error_size, "invalid dense_f32 arguments");
-    const size_t gy = (m + BM - 1) / BM, gx = (n + BN - 1) / BN;
-    if (gy > 65535) return fail(error, error_size, "dense_f32: more than %d rows", 65535 * BM);
+    if ((m + 31) / 32 > 65535) return fail(error, error_size, "dense_f32: more than %d rows", 65535 * 32);
     const bool vec = k % 4 == 0 && !(((uintptr_t)d_x | (uintptr_t)d_w) & 15);
+    // the taller tile only where it still gives every SM several CTAs
+    const size_t ctas64 = ((m + 63) / 64) * ((n + BN - 1) / BN);
     ProfScope prof(cuda, PROF_OTHER);
-    if (vec) k_dense_f32<true><<<dim3((unsigned)gx, (unsigned)gy), THREADS, 0, cuda->op_stream>>>(d_x, d_w, d_bias, m, n, k, d_y);
-    else k_dense_f32<false><<<dim3((unsigned)gx, (unsigned)gy), THREADS, 0, cuda->op_stream>>>(d_x, d_w, d_bias, m, n, k, d_y);
+    if (ctas64 >= (size_t)cuda->sm_count * 4) dense_launch_t<64>(cuda, vec, d_x, d_w, d_bias, m, n, k, d_y);
+    else dense_launch_t<32>(cuda, vec, d_x, d_w, d_bias, m, n, k, d_y);
     cuda->launches++;
     H3B_CUDA_OK(cudaGetLastError(), "k_dense_f32 launch");
     return 1;

@@ -161,6 +161,12 @@ _SIGS = {
     "h3_cuda_nvfp4_sf_bytes": (sz, (sz, sz)),
     "h3_cuda_quantize_act_nvfp4_dev": (i32, (vp, vp, sz, sz, vp, vp) + _ERR),
     "h3b_adaln_project_dev": (i32, (vp, vp, vp, sz, sz, vp, vp) + _ERR),
+    "h3_cuda_gemm_f32_dd": (i32, (vp, vp, vp, sz, sz, sz, vp, dbl_p) + _ERR),
+    "h3_cuda_bias_add_f32_dev": (i32, (vp, vp, vp, sz, sz) + _ERR),
+    "h3b_dense_f32_dev": (i32, (vp, vp, vp, vp, sz, sz, sz, vp) + _ERR),
+    "h3b_final_head_scratch_bytes": (sz, (sz, sz)),
+    "h3b_final_head_f32_dev": (i32, (vp, vp, vp, vp, sz, sz, vp, vp, sz, f32, vp, sz, vp) + _ERR),
+    "h3b_euler_step_f32_dev": (i32, (vp, vp, vp, sz, f32, f32) + _ERR),
     "h3b_dit_create": (vp, (vp, C.POINTER(DitConfig)) + _ERR),
     "h3b_dit_free": (None, (vp,)),
     "h3b_dit_set_linear": (i32, (vp, C.c_uint, i32, vp) + _ERR),

@@ -374,6 +374,32 @@ int h3b_adaln_project_dev(h3_cuda *cuda, const float *d_w, const float *d_b, siz
 int h3b_gelu_tanh_dev(h3_cuda *cuda, const void *d_in, void *d_out, int dtype, size_t n, char *error,
                       size_t error_size);
 
+/* ------------------------------------------- the step on either side of the chain */
+
+/* d_y[m,n] = d_x[m,k] @ d_weight[n,k]^T, all f32 on the device (h3_gpu_cuda.h:120; the patch
+ * embeddings and final heads call it through dense_f32_cuda_to_dev, h3_dit_w4a8.c:5370). */
+int h3_cuda_gemm_f32_dd(h3_cuda *cuda, const float *d_x, const float *d_weight, size_t m, size_t n,
+                        size_t k, float *d_y, double *gemm_ms, char *error, size_t error_size);
+/* d_y[r,c] += d_bias[c] (h3_gpu_cuda.h:263). */
+int h3_cuda_bias_add_f32_dev(h3_cuda *cuda, float *d_y, const float *d_bias, size_t rows, size_t width,
+                             char *error, size_t error_size);
+/* The two calls above in one launch: y = x W^T + b (h3_dit_w4a8.c:5298 h3_dit_w4a8_dense_f32);
+ * d_bias may be NULL.  Patch embedding: m = tokens, n = hidden, k = 96 (video) or 32 (audio). */
+int h3b_dense_f32_dev(h3_cuda *cuda, const float *d_x, const float *d_weight, const float *d_bias,
+                      size_t m, size_t n, size_t k, float *d_y, char *error, size_t error_size);
+/* Final head (h3_dit_w4a8.c:5578 final_head_cuda): adaLN of every token with shift = d_modulation[0,:]
+ * and scale = d_modulation[1,:] (one modulation row of two slots), then y = normed W^T + b with
+ * W [out_dim, hidden].  d_scratch: h3b_final_head_scratch_bytes(seq, hidden) bytes, 16-byte aligned. */
+size_t h3b_final_head_scratch_bytes(size_t seq, size_t hidden);
+int h3b_final_head_f32_dev(h3_cuda *cuda, const float *d_x, const float *d_norm_w,
+                           const float *d_modulation, size_t seq, size_t hidden, const float *d_weight,
+                           const float *d_bias, size_t out_dim, float epsilon, void *d_scratch,
+                           size_t scratch_bytes, float *d_y, char *error, size_t error_size);
+/* sample += (sigma - sigma_next) * velocity on the device; refuses a pair that is not finite,
+ * not decreasing or negative, like h3_dit_w4a8.c:8822 h3_dit_w4a8_euler_step_f32. */
+int h3b_euler_step_f32_dev(h3_cuda *cuda, float *d_sample, const float *d_velocity, size_t count,
+                           float sigma, float sigma_next, char *error, size_t error_size);
+
 /* ---------------------------------------------------------------- attention */
 
 /* F32 Q/K/V/out on the device, [seq, heads, head_dim]; computed in bf16 on the

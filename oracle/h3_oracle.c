@@ -724,6 +724,28 @@ void ho_adaln_project_f32(const float *w, const float *b, size_t out_dim, size_t
     }
 }
 
+/* h3_dit_w4a8.c:5298-5318: y = x W^T + b, the bias is the first term of the sum */
+void ho_dense_f32(const float *x, const float *w, const float *bias, size_t m, size_t n, size_t k, float *y) {
+    size_t r, o, i;
+    for (r = 0; r < m; r++)
+        for (o = 0; o < n; o++) {
+            float sum = bias ? bias[o] : 0.0f;
+            for (i = 0; i < k; i++) sum += x[r * k + i] * w[o * k + i];
+            y[r * n + o] = sum;
+        }
+}
+
+/* h3_dit_w4a8.c:8822-8839: returns 0 for a sigma pair the reference rejects */
+int ho_euler_step_f32(float *sample, const float *velocity, size_t count, float sigma, float sigma_next) {
+    size_t i;
+    float delta;
+    if (!sample || !velocity || count == 0) return 0;
+    if (!isfinite(sigma) || !isfinite(sigma_next) || !(sigma > sigma_next) || sigma_next < 0.0f) return 0;
+    delta = sigma - sigma_next;
+    for (i = 0; i < count; i++) sample[i] += delta * velocity[i];
+    return 1;
+}
+
 /* -------------------------------------------------------------------- NVFP4 */
 
 /* tests/test_h3_nvfp4_sf_bytes.c:8-14, h3_gpu_cuda.cu:5940-5948 */

@@ -125,6 +125,12 @@ int ho_fill_video_pos(size_t text_len, int latent_t, int latent_h, int latent_w,
 void ho_adaln_project_f32(const float *w, const float *b, size_t out_dim,
                           size_t in_dim, const float *t_feat, float *mod);
 
+/* ---- either side of the chain: dense f32 linear and Euler update (h3_dit_w4a8.c:5298, 8822) ---- */
+void ho_dense_f32(const float *x, const float *w, const float *bias, size_t m, size_t n, size_t k,
+                  float *y);
+int ho_euler_step_f32(float *sample, const float *velocity, size_t count, float sigma,
+                      float sigma_next);
+
 /* ---- NVFP4 (h3_gpu_cuda.cu:4455-4614, 5940; tools/quant_dit_nvfp4.py:65) ---- */
 size_t ho_nvfp4_sf_bytes(size_t rows, size_t k);
 size_t ho_nvfp4_sf_offset(size_t row, size_t block16, size_t k);

@@ -302,6 +302,29 @@ class Oracle:
                                       _p(f32(t_feat), c_f32p), _p(mod, c_f32p))
         return mod
 
+    def dense(self, x, w, bias=None):
+        """y = x W^T + b in f32 (patch embeddings, final heads)."""
+        x, w = f32(x), f32(w)
+        y = np.empty((x.shape[0], w.shape[0]), np.float32)
+        b = f32(bias) if bias is not None else None
+        self.lib.ho_dense_f32(_p(x, c_f32p), _p(w, c_f32p), _p(b, c_f32p) if b is not None else None, sz(x.shape[0]),
+                              sz(w.shape[0]), sz(x.shape[1]), _p(y, c_f32p))
+        return y
+
+    def euler_step(self, sample, velocity, sigma, sigma_next):
+        """Returns the updated sample, or None where the reference rejects the sigma pair."""
+        out = f32(sample).copy()
+        self.lib.ho_euler_step_f32.restype = C.c_int
+        ok = self.lib.ho_euler_step_f32(_p(out, c_f32p), _p(f32(velocity), c_f32p), sz(out.size), C.c_float(sigma),
+                                        C.c_float(sigma_next))
+        return out if ok == 1 else None
+
+    def final_head(self, x, norm_w, modulation, w, bias, eps=1e-5):
+        """adaLN with shift = modulation[0], scale = modulation[1] for every token, then the dense head."""
+        x = f32(x)
+        zeros = np.zeros(x.shape[0], np.uint32)
+        return self.dense(self.adaln(x, norm_w, f32(modulation).reshape(1, 2, -1), zeros, 2, 0, 1, eps), w, bias)
+
     # ---- nvfp4
     def nvfp4_sf_bytes(self, rows, k):
         return int(self.lib.ho_nvfp4_sf_bytes(sz(rows), sz(k)))
@@ -530,6 +553,25 @@ class Ref:
                                        _p(row_map, c_u32p), sz(x.shape[0]), sz(x.shape[1]), sz(slots),
                                        sz(shift_slot), sz(scale_slot), C.c_float(eps), _p(out, c_f32p))
         return out
+
+    def dense(self, x, w, bias=None):
+        x, w = f32(x), f32(w)
+        y = np.empty((x.shape[0], w.shape[0]), np.float32)
+        b = f32(bias) if bias is not None else None
+        err = C.create_string_buffer(256)
+        self.lib.h3_dit_w4a8_dense_f32.restype = C.c_int
+        ok = self.lib.h3_dit_w4a8_dense_f32(_p(x, c_f32p), _p(w, c_f32p), _p(b, c_f32p) if b is not None else None,
+                                            sz(x.shape[0]), sz(w.shape[0]), sz(x.shape[1]), _p(y, c_f32p), err, sz(256))
+        assert ok == 1, err.value
+        return y
+
+    def euler_step(self, sample, velocity, sigma, sigma_next):
+        out = f32(sample).copy()
+        err = C.create_string_buffer(256)
+        self.lib.h3_dit_w4a8_euler_step_f32.restype = C.c_int
+        ok = self.lib.h3_dit_w4a8_euler_step_f32(_p(out, c_f32p), _p(f32(velocity), c_f32p), sz(out.size),
+                                                 C.c_float(sigma), C.c_float(sigma_next), err, sz(256))
+        return out if ok == 1 else None
 
     def gate(self, residual, branch, modulation, row_map, slots, gate_slot):
         residual = f32(residual)

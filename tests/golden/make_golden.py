@@ -189,6 +189,31 @@ def main():
     save("nvfp4_weight", w_i8=w_i8, scale=scale, packed=packed, sf=sf, ue4m3_in=vals,
          ue4m3_bytes=mod_q.f32_to_ue4m3(vals), ue4m3_table=mod_q.ue4m3_to_f32(np.arange(0x7F, dtype=np.uint8)))
 
+    step_sides(ref)
+
+
+def step_sides(ref):
+    """The step on either side of the block chain (own seed, so that it can be generated alone):
+    patch embedding, final head = adaLN with one modulation row + dense, Euler update."""
+    rng = np.random.default_rng(77)
+    seq, hidden, patch = 70, 256, 96
+    lat = rng.normal(0, 1, (seq, patch)).astype(np.float32)
+    pw = rng.normal(0, 0.1, (hidden, patch)).astype(np.float32)
+    pb = rng.normal(0, 0.1, hidden).astype(np.float32)
+    x = rng.normal(0, 1, (seq, hidden)).astype(np.float32)
+    norm_w = rng.normal(1, 0.1, hidden).astype(np.float32)
+    mod = rng.normal(0, 0.2, (1, 2, hidden)).astype(np.float32)
+    fw = rng.normal(0, 0.05, (patch, hidden)).astype(np.float32)
+    fb = rng.normal(0, 0.1, patch).astype(np.float32)
+    normed = ref.adaln(x, norm_w, mod, np.zeros(seq, np.uint32), 2, 0, 1)
+    vel = ref.dense(normed, fw, fb)
+    save("step_sides", latent=lat, patch_w=pw, patch_b=pb, embedded=ref.dense(lat, pw, pb), x=x, norm_w=norm_w,
+         modulation=mod, final_w=fw, final_b=fb, velocity=vel, sigma=np.array([0.8, 0.55], np.float32),
+         stepped=ref.euler_step(lat, vel, 0.8, 0.55))
+
 
 if __name__ == "__main__":
-    main()
+    if len(sys.argv) > 1 and sys.argv[1] == "step_sides":
+        step_sides(Ref())
+    else:
+        main()

@@ -150,3 +150,14 @@ def test_nvfp4_sf_bytes(oracle):
     assert oracle.nvfp4_sf_bytes(1, 64) == 512
     assert oracle.nvfp4_sf_bytes(256, 512) == 2 * 8 * 512
     assert oracle.nvfp4_sf_bytes(1, 63) == 0 and oracle.nvfp4_sf_bytes(0, 64) == 0
+
+
+def test_step_sides(oracle, golden):
+    """Patch embedding, final head and Euler update against vectors the reference's own functions produced
+    (h3_dit_w4a8_dense_f32, h3_dit_w4a8_adaln_f32, h3_dit_w4a8_euler_step_f32)."""
+    g = golden("step_sides")
+    assert np.array_equal(oracle.dense(g["latent"], g["patch_w"], g["patch_b"]), g["embedded"])
+    vel = oracle.final_head(g["x"], g["norm_w"], g["modulation"], g["final_w"], g["final_b"])
+    assert np.array_equal(vel, g["velocity"])
+    s0, s1 = (float(v) for v in g["sigma"])
+    assert np.array_equal(oracle.euler_step(g["latent"], vel, s0, s1), g["stepped"])

@@ -512,3 +512,39 @@ def test_empty_and_misaligned_inputs_are_refused(cuda):
     with pytest.raises(h3c_b200.H3Error):
         cuda.gemm_i8(w, xq, torch.ones(9, device="cuda"))
     cuda.check()
+
+
+# ------------------------------------------------- the step on either side of the block chain
+
+@pytest.mark.parametrize("m,n,k", [(70, 256, 96), (300, 96, 3072), (129, 32, 1000), (17, 65, 30)])
+def test_dense_f32(cuda, oracle, m, n, k):
+    """Patch-embedding / final-head linear: f32 FMA chain in k order against the reference's scalar loop
+    (which starts its sum at the bias); 1e-5 relative L2 covers the different rounding of the partial sums."""
+    rng = np.random.default_rng(70 + m)
+    x = rng.normal(0, 1, (m, k)).astype(np.float32)
+    w = rng.normal(0, 0.05, (n, k)).astype(np.float32)
+    b = rng.normal(0, 0.1, n).astype(np.float32)
+    want = oracle.dense(x, w, b)
+    assert rel_l2(host(cuda.dense_f32(dev(x), dev(w), dev(b))), want) < 1e-5
+    two_calls = cuda.bias_add_f32(cuda.gemm_f32_dd(dev(x), dev(w)), dev(b))   # the reference's pair of calls
+    assert rel_l2(host(two_calls), want) < 1e-5
+    assert rel_l2(host(cuda.dense_f32(dev(x), dev(w))), oracle.dense(x, w)) < 1e-5
+    if k % 4:   # the scalar-load form is also reached by a misaligned view
+        assert rel_l2(host(cuda.gemm_f32_dd(dev(x), dev(w))), oracle.dense(x, w)) < 1e-5
+
+
+def test_step_sides_against_golden_vectors(cuda, golden):
+    """Patch embedding, final head (adaLN with one modulation row + dense) and Euler update on the vectors
+    that the reference's own functions produced; the Euler update is bit-exact given the same velocity."""
+    import h3c_b200
+    g = golden("step_sides")
+    emb = cuda.dense_f32(dev(g["latent"]), dev(g["patch_w"]), dev(g["patch_b"]))
+    assert rel_l2(host(emb), g["embedded"]) < 1e-5
+    vel = cuda.final_head_f32(dev(g["x"]), dev(g["norm_w"]), dev(g["modulation"]), dev(g["final_w"]), dev(g["final_b"]))
+    assert rel_l2(host(vel), g["velocity"]) < 1e-5
+    s0, s1 = (float(v) for v in g["sigma"])
+    stepped = cuda.euler_step_f32(dev(g["latent"]), dev(g["velocity"]), s0, s1)
+    assert np.array_equal(host(stepped), g["stepped"])
+    for sigma, nxt in ((0.5, 0.5), (0.25, 0.5), (0.5, -0.1), (float("nan"), 0.1)):   # pairs the reference rejects
+        with pytest.raises(h3c_b200.H3Error):
+            cuda.euler_step_f32(dev(g["latent"]), dev(g["velocity"]), sigma, nxt)

@@ -63,3 +63,19 @@ def test_rect_sdpa_reduces_to_reference_on_square(oracle, ref):
 def test_checksum(oracle, ref):
     x = np.random.default_rng(6).normal(0, 1, 1000).astype(np.float32)
     assert oracle.checksum_f32(x) == ref.checksum_f32(x)
+
+
+def test_dense_and_euler_step_bit_exact(oracle, ref):
+    """Patch-embedding / final-head linear and the Euler update: the restatement against the reference's
+    own functions (h3_dit_w4a8_dense_f32, h3_dit_w4a8_euler_step_f32), including the rejected sigma pairs."""
+    rng = np.random.default_rng(90)
+    for m, n, k, with_bias in ((37, 64, 96, True), (5, 96, 3072, True), (9, 32, 40, False)):
+        x = rng.normal(0, 1, (m, k)).astype(np.float32)
+        w = rng.normal(0, 0.05, (n, k)).astype(np.float32)
+        b = rng.normal(0, 0.1, n).astype(np.float32) if with_bias else None
+        assert np.array_equal(oracle.dense(x, w, b), ref.dense(x, w, b))
+    s = rng.normal(0, 1, 1000).astype(np.float32)
+    v = rng.normal(0, 1, 1000).astype(np.float32)
+    assert np.array_equal(oracle.euler_step(s, v, 0.75, 0.5), ref.euler_step(s, v, 0.75, 0.5))
+    for sigma, nxt in ((0.5, 0.5), (0.25, 0.5), (0.5, -0.1), (float("nan"), 0.1), (float("inf"), 0.1)):
+        assert oracle.euler_step(s, v, sigma, nxt) is None and ref.euler_step(s, v, sigma, nxt) is None
