@@ -478,9 +478,9 @@ def profile_classes(cuda, dit, step):
     return {names[i]: {"launches": int(cnt[i]), "ms": float(ms[i])} for i in range(min(n, len(names))) if cnt[i]}
 
 
-# DRAM bytes per int8 GEMM launch of the 6,144-token block (mean of its seven GEMMs): 847 MB per block / 7.
+# DRAM bytes per int8 GEMM launch of the 6,144-token block (mean of its seven GEMMs): 894 MB per block / 7.
 # The algorithmic figure (codes + weights + outputs + residuals of the seven) is 857 MB per block.
-GEMM_DRAM_BYTES_PER_LAUNCH_6144 = 121.0e6
+GEMM_DRAM_BYTES_PER_LAUNCH_6144 = 127.8e6
 # DRAM bytes per attention launch of the 50,220-token block on one GPU: self-attention 1277 MB (Q, K, V read
 # and O written once: 1234 MB algorithmic), cross-attention 576 MB (624 MB algorithmic); mean of the two.
 ATTN_DRAM_BYTES_PER_LAUNCH_50220 = 926.4e6
