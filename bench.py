@@ -380,6 +380,8 @@ def gpu_arm(args):
     ms_step = max_over_ranks(e0.elapsed_time(e1) / args.steps)
     clocks = sampler.stop()
     cuda.check()
+    if comm is not None:
+        comm.check()
 
     prof = profile_classes(cuda, dit, eager_step if (args.graph and world == 1) else step_resident)
     sync_all()

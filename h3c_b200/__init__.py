@@ -426,5 +426,9 @@ class UlyssesComm:
     def barrier(self):
         call("h3b_ulysses_barrier", C.byref(self.cfg))
 
+    def check(self):
+        """Synchronises the compute stream; raises H3Error if a barrier between the ranks gave up waiting."""
+        call("h3b_ulysses_check", C.byref(self.cfg), None)
+
     def close(self):
         load().h3_ulysses_comm_destroy(C.byref(self.cfg))

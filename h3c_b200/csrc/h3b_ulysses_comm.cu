@@ -98,7 +98,9 @@ struct CommState {
     int direct_ready, direct_off;
     void *slab;
     void *peer_slab[MAX_U];
-    int *d_barrier;
+    int *d_barrier;                // [0..1] words of the NCCL barrier, [2] epoch of the flag barrier, [3] its status
+    uint32_t *peer_flags[MAX_U];   // rank r's arrival flags (one word per rank) at the end of its slab
+    int flag_barrier;              // 1: barriers are the flag kernel, 0: the one-word all-reduce
 };
 
 static int slot_of(const CommState *st, int rank) {
@@ -108,6 +110,45 @@ static int slot_of(const CommState *st, int rank) {
 }
 
 // in[s][q][h][d] -> out[peer][s][q][hl][d]; 16-byte vectors (head_dim * elem is a multiple of 16)
+// Barrier of the exchange-free form: every rank writes the next epoch into its word of every peer's flag row
+// and waits until its own row shows that epoch (or a later one: a rank that is already through may have moved
+// on) from everybody.  One warp, lane r talks to rank r.  The earlier kernels of the stream have finished, so
+// their stores into peer memory are ordered before the release store of the flag on the same NVLink path; the
+// acquire load orders the reads of the kernels that follow.  The wait is bounded: after about two seconds the
+// kernel records status 6 in `state[1]` and returns, and later barriers only signal until the status is read.
+struct FlagBarrier {
+    uint32_t *peer_flags[8];
+    int *state;   // [0] epoch, [1] status
+    int rank, world;
+    long long budget;
+};
+__global__ void k_ulysses_flag_barrier(const __grid_constant__ FlagBarrier p) {
+    __shared__ uint32_t epoch_s;
+    if (threadIdx.x == 0) {
+        epoch_s = (uint32_t)p.state[0] + 1u;
+        p.state[0] = (int)epoch_s;
+    }
+    __syncthreads();
+    const uint32_t epoch = epoch_s;
+    __threadfence_system();
+    const int r = (int)threadIdx.x;
+    if (r >= p.world) return;
+    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p.peer_flags[r] + p.rank), "r"(epoch) : "memory");
+    const uint32_t *mine = p.peer_flags[p.rank] + r;
+    if (*(volatile int *)&p.state[1] != 0) return;   // an earlier barrier gave up: signal, but do not wait again
+    const long long start = clock64();
+    uint32_t spins = 0;
+    while (true) {
+        uint32_t seen;
+        asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(mine) : "memory");
+        if ((int32_t)(seen - epoch) >= 0) break;
+        if ((++spins & 0xff) == 0 && clock64() - start > p.budget) {
+            atomicCAS(&p.state[1], 0, 6);
+            break;
+        }
+    }
+}
+
 __global__ void k_ulysses_pack_qkv(const uint4 *in, uint4 *out, size_t seq_local, unsigned heads, unsigned vec_per_head,
                                    unsigned u) {
     const unsigned hl = heads / u;
@@ -428,13 +469,13 @@ int h3b_ulysses_direct_setup(h3_ulysses_cfg *cfg, size_t seq_local, size_t heads
     if (cudaSetDevice(st->device[0]) != cudaSuccess) return fail(err, err_size, "ulysses direct: set device");
     // the four buffers have the same size: U*seq_local rows of heads/U heads = seq_local rows of all heads
     const size_t part = (seq_local * heads * head_dim * 2 + 255) & ~(size_t)255;
-    cudaError_t e = cudaMalloc(&st->slab, 4 * part);
+    cudaError_t e = cudaMalloc(&st->slab, 4 * part + 256);   // + one row of arrival flags
     if (e != cudaSuccess) return cuda_fail(e, "ulysses direct: slab allocation", err, err_size);
-    e = cudaMemset(st->slab, 0, 4 * part);
+    e = cudaMemset(st->slab, 0, 4 * part + 256);
     char *d_handles = NULL;
     if (e == cudaSuccess) e = cudaMalloc((void **)&d_handles, (size_t)U * sizeof(cudaIpcMemHandle_t));
-    if (e == cudaSuccess) e = cudaMalloc((void **)&st->d_barrier, 2 * sizeof(int));
-    if (e == cudaSuccess) e = cudaMemset(st->d_barrier, 0, 2 * sizeof(int));
+    if (e == cudaSuccess) e = cudaMalloc((void **)&st->d_barrier, 4 * sizeof(int));
+    if (e == cudaSuccess) e = cudaMemset(st->d_barrier, 0, 4 * sizeof(int));
     cudaIpcMemHandle_t mine, all[MAX_U];
     if (e == cudaSuccess) e = cudaIpcGetMemHandle(&mine, st->slab);
     if (e == cudaSuccess)
@@ -491,9 +532,15 @@ int h3b_ulysses_direct_setup(h3_ulysses_cfg *cfg, size_t seq_local, size_t heads
         d->peer_q[pr] = b; d->peer_k[pr] = b + part; d->peer_v[pr] = b + 2 * part; d->peer_att[pr] = b + 3 * part;
     }
     d->q = d->peer_q[rank]; d->k = d->peer_k[rank]; d->v = d->peer_v[rank]; d->att = d->peer_att[rank];
+    for (int pr = 0; pr < U; pr++) st->peer_flags[pr] = (uint32_t *)((char *)st->peer_slab[pr] + 4 * part);
     st->direct_ready = 1;
-    // nobody stores into a peer before every rank has mapped and zeroed its slab
-    return h3b_ulysses_barrier(cfg, err, err_size) && cudaStreamSynchronize(st->compute[0]) == cudaSuccess;
+    // nobody stores into a peer (data or flags) before every rank has mapped and zeroed its slab: this first
+    // barrier is the all-reduce; later ones are the flag kernel unless H3B_ULYSSES_BARRIER=nccl
+    st->flag_barrier = 0;
+    if (!(h3b_ulysses_barrier(cfg, err, err_size) && cudaStreamSynchronize(st->compute[0]) == cudaSuccess)) return 0;
+    const char *mode = getenv("H3B_ULYSSES_BARRIER");
+    st->flag_barrier = !(mode && strcmp(mode, "nccl") == 0);
+    return 1;
 }
 
 const h3b_ulysses_direct *h3b_ulysses_direct_get(const h3_ulysses_cfg *cfg) {
@@ -512,9 +559,38 @@ int h3b_ulysses_barrier(h3_ulysses_cfg *cfg, char *err, size_t err_size) {
     NcclApi *api = nccl_api(err, err_size);
     if (!api) return 0;
     if (st->n_local != 1 || !st->d_barrier) return fail(err, err_size, "ulysses barrier: direct mode is not set up");
+    if (st->flag_barrier) {
+        FlagBarrier fb;
+        memset(&fb, 0, sizeof(fb));
+        for (int pr = 0; pr < st->n_ranks; pr++) fb.peer_flags[pr] = st->peer_flags[pr];
+        fb.state = st->d_barrier + 2;
+        fb.rank = st->local_rank[0];
+        fb.world = st->n_ranks;
+        fb.budget = 4000000000ll;   // about two seconds of SM clocks, as the waits of the GEMM and attention kernels
+        k_ulysses_flag_barrier<<<1, 32, 0, st->compute[0]>>>(fb);
+        if (cudaGetLastError() != cudaSuccess) return fail(err, err_size, "ulysses barrier: launch failed");
+        return 1;
+    }
     ncclResult_t rc = api->AllReduce(st->d_barrier, st->d_barrier + 1, 1, ncclInt32, ncclSum, st->comm[0], st->compute[0]);
     if (rc != ncclSuccess)
         return fail(err, err_size, "ulysses barrier: ncclAllReduce failed: %s", api->GetErrorString ? api->GetErrorString(rc) : "error");
+    return 1;
+}
+
+int h3b_ulysses_check(h3_ulysses_cfg *cfg, int *status_out, char *err, size_t err_size) {
+    if (!cfg || !cfg->comm) return fail(err, err_size, "ulysses check: not inited");
+    CommState *st = (CommState *)cfg->comm;
+    if (status_out) *status_out = 0;
+    if (st->n_local != 1 || !st->d_barrier) return 1;
+    int status = 0;
+    if (cudaStreamSynchronize(st->compute[0]) != cudaSuccess ||
+        cudaMemcpy(&status, st->d_barrier + 3, sizeof(int), cudaMemcpyDeviceToHost) != cudaSuccess)
+        return fail(err, err_size, "ulysses check: CUDA error");
+    if (status_out) *status_out = status;
+    if (status != 0) {
+        cudaMemset(st->d_barrier + 3, 0, sizeof(int));
+        return fail(err, err_size, "a barrier between the ranks gave up waiting (status %d); results after it are invalid", status);
+    }
     return 1;
 }
 

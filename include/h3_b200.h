@@ -594,8 +594,11 @@ int h3b_ulysses_comm_init_rank(h3_ulysses_cfg *cfg, int rank, int world_size, co
  * calls it with the same sizes) and synchronises the device.  Once set up, the sequence-parallel chain
  * (h3b_dit_layers_forward_ulysses_*) of a context with matching geometry uses the direct stores and
  * two h3b_ulysses_barrier calls per block instead of the two exchanges.  _direct_get returns NULL when
- * nothing is set up or the path is switched off.  _barrier: all ranks, enqueued on the rank's compute stream (one-word NCCL
- * all-reduce); work enqueued after it on any rank starts only when every rank's earlier work is done. */
+ * nothing is set up or the path is switched off.  _barrier: all ranks, enqueued on the rank's compute stream;
+ * work enqueued after it on any rank starts only when every rank's earlier work is done.  It is a one-warp
+ * kernel that writes an epoch into a flag word in every peer's buffer and waits (bounded) for the peers'
+ * words; H3B_ULYSSES_BARRIER=nccl in the environment at set-up time selects a one-word NCCL all-reduce
+ * instead.  _check synchronises the compute stream and reports whether a barrier gave up waiting. */
 int h3b_ulysses_direct_setup(h3_ulysses_cfg *cfg, size_t seq_local, size_t heads, size_t head_dim,
                              char *err, size_t err_size);
 const h3b_ulysses_direct *h3b_ulysses_direct_get(const h3_ulysses_cfg *cfg);
@@ -603,6 +606,7 @@ const h3b_ulysses_direct *h3b_ulysses_direct_get(const h3_ulysses_cfg *cfg);
  * found the set-up failing on some rank and fall back to the exchange on all of them. */
 void h3b_ulysses_direct_enable(h3_ulysses_cfg *cfg, int on);
 int h3b_ulysses_barrier(h3_ulysses_cfg *cfg, char *err, size_t err_size);
+int h3b_ulysses_check(h3_ulysses_cfg *cfg, int *status_out, char *err, size_t err_size);
 /* Host f32 rows of this rank in and out (see h3b_dit_layers_forward_f32); rope tables cover all
  * U*seq_local rows. */
 int h3b_dit_layers_forward_ulysses_f32(h3b_dit *dit, unsigned first_block, unsigned n_blocks,

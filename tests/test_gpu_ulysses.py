@@ -90,6 +90,7 @@ def _worker(rank, world, port, out_dir):
                                            text=dev(text, torch.bfloat16),
                                            row_map=torch.zeros(sl, dtype=torch.int32, device="cuda"))
     cuda.check()
+    comm.check()   # no barrier between the ranks gave up waiting
     result["y_single"] = y_single.float().cpu().numpy()
     result["y_local"] = y_local.float().cpu().numpy()
     result["y_direct"] = y_direct.float().cpu().numpy()
