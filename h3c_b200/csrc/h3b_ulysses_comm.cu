@@ -15,9 +15,9 @@
 // Exchange-free form (h3b_ulysses_direct_*, one process per GPU): every rank allocates one slab
 // [gathered Q | K | V | attention rows], the ranks swap CUDA IPC handles through the communicator and
 // map each other's slabs; the QKV GEMM epilogue and the attention epilogue then store across NVLink
-// into the slab of the rank that needs each (row, head) slice, and a one-word all-reduce on the compute
-// stream is the barrier that makes the stores of all ranks visible (and keeps a fast rank from
-// overwriting what a slow one still reads).  No pack, exchange or unpack remains on the critical path.
+// into the slab of the rank that needs each (row, head) slice, and a flag kernel on the compute stream
+// (or a one-word all-reduce) is the barrier that makes the stores of all ranks visible (and keeps a fast
+// rank from overwriting what a slow one still reads).  No pack, exchange or unpack remains on the critical path.
 // NCCL is bound at run time (dlopen of libnccl.so.2) so the library loads where NCCL is absent;
 // every entry point then fails with a message, like the reference's stub (h3_ulysses_comm_stub.c).
 #include <dlfcn.h>
