@@ -577,6 +577,45 @@ int h3b_ulysses_barrier(h3_ulysses_cfg *cfg, char *err, size_t err_size) {
     return 1;
 }
 
+int h3b_ulysses_barrier_selftest(long long budget_cycles, int *status_arrived, int *status_absent, char *err,
+                                 size_t err_size) {
+    // Two ranks' flag rows in one local buffer, this GPU playing rank 0.  First the peer's word is preset to the
+    // epoch the kernel will use (the barrier passes: status 0), then it is left at zero (the wait runs out
+    // after `budget_cycles` and the kernel returns with status 6).  Nothing faults and the context stays usable.
+    if (budget_cycles <= 0 || budget_cycles > 2000000000ll || !status_arrived || !status_absent)
+        return fail(err, err_size, "barrier selftest: budget must be in (0, 2e9] cycles");
+    uint32_t *flags = NULL;
+    int *state = NULL;
+    cudaError_t e = cudaMalloc((void **)&flags, 64 * sizeof(uint32_t));
+    if (e == cudaSuccess) e = cudaMalloc((void **)&state, 2 * sizeof(int));
+    int ok = 0;
+    for (int pass = 0; pass < 2 && e == cudaSuccess; pass++) {
+        uint32_t host_flags[64] = {0};
+        if (pass == 0) host_flags[1] = 1;   // row of rank 0, word of rank 1: already at epoch 1
+        e = cudaMemcpy(flags, host_flags, sizeof(host_flags), cudaMemcpyHostToDevice);
+        if (e == cudaSuccess) e = cudaMemset(state, 0, 2 * sizeof(int));
+        if (e != cudaSuccess) break;
+        FlagBarrier fb;
+        memset(&fb, 0, sizeof(fb));
+        fb.peer_flags[0] = flags;        // rank 0's row
+        fb.peer_flags[1] = flags + 32;   // rank 1's row (only written)
+        fb.state = state; fb.rank = 0; fb.world = 2; fb.budget = budget_cycles;
+        k_ulysses_flag_barrier<<<1, 32>>>(fb);
+        e = cudaGetLastError();
+        if (e == cudaSuccess) e = cudaDeviceSynchronize();
+        int st2[2] = {0, 0};
+        if (e == cudaSuccess) e = cudaMemcpy(st2, state, sizeof(st2), cudaMemcpyDeviceToHost);
+        if (e == cudaSuccess) {
+            *(pass == 0 ? status_arrived : status_absent) = st2[1];
+            ok = pass == 1;
+        }
+    }
+    if (flags) cudaFree(flags);
+    if (state) cudaFree(state);
+    if (e != cudaSuccess) return cuda_fail(e, "barrier selftest", err, err_size);
+    return ok;
+}
+
 int h3b_ulysses_check(h3_ulysses_cfg *cfg, int *status_out, char *err, size_t err_size) {
     if (!cfg || !cfg->comm) return fail(err, err_size, "ulysses check: not inited");
     CommState *st = (CommState *)cfg->comm;

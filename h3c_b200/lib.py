@@ -207,6 +207,7 @@ _SIGS = {
     "h3b_ulysses_direct_enable": (None, (C.POINTER(UlyssesCfg), i32)),
     "h3b_ulysses_barrier": (i32, (C.POINTER(UlyssesCfg),) + _ERR),
     "h3b_ulysses_check": (i32, (C.POINTER(UlyssesCfg), C.POINTER(C.c_int)) + _ERR),
+    "h3b_ulysses_barrier_selftest": (i32, (C.c_longlong, C.POINTER(C.c_int), C.POINTER(C.c_int)) + _ERR),
     "h3b_sdpa_bf16_scatter_dev": (i32, (vp, vp, sz, f32) + _ERR),
     "h3b_dit_layers_forward_ulysses_dev": (i32, (vp, C.c_uint, C.c_uint, vp, sz, sz, vp, vp, vp, vp, sz, vp) + _ERR),
     "h3b_dit_layers_forward_ulysses_f32": (i32, (vp, C.c_uint, C.c_uint, vp, vp, sz, sz, vp, vp, vp, vp, sz, vp) + _ERR),

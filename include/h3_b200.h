@@ -607,6 +607,11 @@ const h3b_ulysses_direct *h3b_ulysses_direct_get(const h3_ulysses_cfg *cfg);
 void h3b_ulysses_direct_enable(h3_ulysses_cfg *cfg, int on);
 int h3b_ulysses_barrier(h3_ulysses_cfg *cfg, char *err, size_t err_size);
 int h3b_ulysses_check(h3_ulysses_cfg *cfg, int *status_out, char *err, size_t err_size);
+/* Runs the flag-barrier kernel on the current device against a local stand-in for a second rank: once with
+ * the peer's word already set (*status_arrived = 0) and once with a peer that never arrives, where the wait
+ * ends after budget_cycles SM clocks (*status_absent = 6).  Needs no communicator and no second GPU. */
+int h3b_ulysses_barrier_selftest(long long budget_cycles, int *status_arrived, int *status_absent, char *err,
+                                 size_t err_size);
 /* Host f32 rows of this rank in and out (see h3b_dit_layers_forward_f32); rope tables cover all
  * U*seq_local rows. */
 int h3b_dit_layers_forward_ulysses_f32(h3b_dit *dit, unsigned first_block, unsigned n_blocks,

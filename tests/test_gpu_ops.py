@@ -551,3 +551,16 @@ def test_step_sides_against_golden_vectors(cuda, golden):
     for sigma, nxt in ((0.5, 0.5), (0.25, 0.5), (0.5, -0.1), (float("nan"), 0.1)):   # pairs the reference rejects
         with pytest.raises(h3c_b200.H3Error):
             cuda.euler_step_f32(dev(g["latent"]), dev(g["velocity"]), sigma, nxt)
+
+
+def test_flag_barrier_gives_up_on_an_absent_rank(cuda):
+    """The barrier of the exchange-free Ulysses form waits a bounded time: with the peer's word set it passes,
+    with a peer that never arrives it returns after the budget with status 6 and the context stays usable."""
+    import ctypes as C
+    from h3c_b200.lib import call
+    arrived, absent = C.c_int(-1), C.c_int(-1)
+    call("h3b_ulysses_barrier_selftest", 2_000_000, C.byref(arrived), C.byref(absent))   # about a millisecond
+    assert arrived.value == 0 and absent.value == 6
+    x = torch.arange(8, device="cuda")
+    assert int(x.sum().item()) == 28
+    cuda.check()
