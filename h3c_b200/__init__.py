@@ -257,6 +257,16 @@ class Cuda:
         call("h3_cuda_gemm_f32_dd", self.h, ptr(x), ptr(w), x.shape[0], w.shape[0], x.shape[1], ptr(y), None)
         return y
 
+    def gemm_f32_dd_ex(self, x, w, y, alpha=1.0, beta=0.0, tf32_name=False):
+        """In place: y = alpha * (x @ w^T) + beta * y (h3_cuda_gemm_f32_dd_ex / _tf32_ex)."""
+        if tf32_name:
+            call("h3_cuda_gemm_f32_dd_tf32_ex", self.h, ptr(x), ptr(w), x.shape[0], w.shape[0], x.shape[1], ptr(y),
+                 float(alpha), float(beta))
+        else:
+            call("h3_cuda_gemm_f32_dd_ex", self.h, ptr(x), ptr(w), x.shape[0], w.shape[0], x.shape[1], ptr(y),
+                 float(alpha), float(beta), None)
+        return y
+
     def bias_add_f32(self, y, bias):
         call("h3_cuda_bias_add_f32_dev", self.h, ptr(y), ptr(bias), y.shape[0], y.shape[1])
         return y

@@ -28,7 +28,7 @@ constexpr int BN = 64, BK = 16, PAD = 4;
 template <int BM, bool VEC>
 __global__ void __launch_bounds__(BM * 4) k_dense_f32(const float *__restrict__ x, const float *__restrict__ w,
                                                       const float *__restrict__ bias, size_t m, size_t n, size_t k,
-                                                      float *__restrict__ y) {
+                                                      float *y, float alpha, float beta) {
     using namespace dense;
     constexpr int THREADS = BM * 4;
     constexpr int WREP = BN * 4 / THREADS;   // rows of W each thread fetches per step (1 or 2)
@@ -100,6 +100,13 @@ __global__ void __launch_bounds__(BM * 4) k_dense_f32(const float *__restrict__ 
         float o[4];
 #pragma unroll
         for (int j = 0; j < 4; j++) o[j] = bias ? __fadd_rn(acc[i][j], bv[j]) : acc[i][j];
+        if (alpha != 1.0f || beta != 0.0f) {   // y = alpha * (x W^T) + beta * y, the LoRA second product
+#pragma unroll
+            for (int j = 0; j < 4; j++) {
+                o[j] = __fmul_rn(alpha, o[j]);
+                if (beta != 0.0f && c + j < n) o[j] = __fmaf_rn(beta, y[r * n + c + j], o[j]);
+            }
+        }
         if (wide) {
             *reinterpret_cast<float4 *>(y + r * n + c) = make_float4(o[0], o[1], o[2], o[3]);
         } else {
@@ -112,14 +119,14 @@ __global__ void __launch_bounds__(BM * 4) k_dense_f32(const float *__restrict__ 
 
 template <int BM>
 static void dense_launch_t(h3_cuda *cuda, bool vec, const float *d_x, const float *d_w, const float *d_bias, size_t m, size_t n,
-                           size_t k, float *d_y) {
+                           size_t k, float *d_y, float alpha, float beta) {
     const dim3 grid((unsigned)((n + dense::BN - 1) / dense::BN), (unsigned)((m + BM - 1) / BM));
-    if (vec) k_dense_f32<BM, true><<<grid, BM * 4, 0, cuda->op_stream>>>(d_x, d_w, d_bias, m, n, k, d_y);
-    else k_dense_f32<BM, false><<<grid, BM * 4, 0, cuda->op_stream>>>(d_x, d_w, d_bias, m, n, k, d_y);
+    if (vec) k_dense_f32<BM, true><<<grid, BM * 4, 0, cuda->op_stream>>>(d_x, d_w, d_bias, m, n, k, d_y, alpha, beta);
+    else k_dense_f32<BM, false><<<grid, BM * 4, 0, cuda->op_stream>>>(d_x, d_w, d_bias, m, n, k, d_y, alpha, beta);
 }
 
 static int launch_dense(h3_cuda *cuda, const float *d_x, const float *d_w, const float *d_bias, size_t m, size_t n, size_t k,
-                        float *d_y, char *error, size_t error_size) {
+                        float *d_y, char *error, size_t error_size, float alpha = 1.0f, float beta = 0.0f) {
     using namespace dense;
     if (!cuda || !d_x || !d_w || !d_y || m == 0 || n == 0 || k == 0) return fail(error, error_size, "invalid dense_f32 arguments");
     if ((m + 31) / 32 > 65535) return fail(error, error_size, "dense_f32: more than %d rows", 65535 * 32);
@@ -127,8 +134,8 @@ static int launch_dense(h3_cuda *cuda, const float *d_x, const float *d_w, const
     // the taller tile only where it still gives every SM several CTAs
     const size_t ctas64 = ((m + 63) / 64) * ((n + BN - 1) / BN);
     ProfScope prof(cuda, PROF_OTHER);
-    if (ctas64 >= (size_t)cuda->sm_count * 4) dense_launch_t<64>(cuda, vec, d_x, d_w, d_bias, m, n, k, d_y);
-    else dense_launch_t<32>(cuda, vec, d_x, d_w, d_bias, m, n, k, d_y);
+    if (ctas64 >= (size_t)cuda->sm_count * 4) dense_launch_t<64>(cuda, vec, d_x, d_w, d_bias, m, n, k, d_y, alpha, beta);
+    else dense_launch_t<32>(cuda, vec, d_x, d_w, d_bias, m, n, k, d_y, alpha, beta);
     cuda->launches++;
     H3B_CUDA_OK(cudaGetLastError(), "k_dense_f32 launch");
     return 1;
@@ -162,6 +169,21 @@ int h3_cuda_gemm_f32_dd(h3_cuda *cuda, const float *d_x, const float *d_weight, 
     const int ok = launch_dense(cuda, d_x, d_weight, nullptr, m, n, k, d_y, error, error_size);
     t.stop();
     return ok;
+}
+
+int h3_cuda_gemm_f32_dd_ex(h3_cuda *cuda, const float *d_x, const float *d_weight, size_t m, size_t n, size_t k, float *d_y,
+                           float alpha, float beta, double *gemm_ms, char *error, size_t error_size) {
+    Timer t(cuda, gemm_ms);
+    const int ok = launch_dense(cuda, d_x, d_weight, nullptr, m, n, k, d_y, error, error_size, alpha, beta);
+    t.stop();
+    return ok;
+}
+
+// The reference's TF32 form of the same product (CUBLAS_COMPUTE_32F_FAST_TF32, its LoRA option): computed
+// in full f32 here, which is at least as accurate.
+int h3_cuda_gemm_f32_dd_tf32_ex(h3_cuda *cuda, const float *d_x, const float *d_weight, size_t m, size_t n, size_t k,
+                                float *d_y, float alpha, float beta, char *error, size_t error_size) {
+    return launch_dense(cuda, d_x, d_weight, nullptr, m, n, k, d_y, error, error_size, alpha, beta);
 }
 
 int h3_cuda_bias_add_f32_dev(h3_cuda *cuda, float *d_y, const float *d_bias, size_t rows, size_t width, char *error,

@@ -163,6 +163,8 @@ _SIGS = {
     "h3b_adaln_project_dev": (i32, (vp, vp, vp, sz, sz, vp, vp) + _ERR),
     "h3_cuda_gemm_f32_dd": (i32, (vp, vp, vp, sz, sz, sz, vp, dbl_p) + _ERR),
     "h3_cuda_bias_add_f32_dev": (i32, (vp, vp, vp, sz, sz) + _ERR),
+    "h3_cuda_gemm_f32_dd_ex": (i32, (vp, vp, vp, sz, sz, sz, vp, f32, f32, dbl_p) + _ERR),
+    "h3_cuda_gemm_f32_dd_tf32_ex": (i32, (vp, vp, vp, sz, sz, sz, vp, f32, f32) + _ERR),
     "h3b_dense_f32_dev": (i32, (vp, vp, vp, vp, sz, sz, sz, vp) + _ERR),
     "h3b_final_head_scratch_bytes": (sz, (sz, sz)),
     "h3b_final_head_f32_dev": (i32, (vp, vp, vp, vp, sz, sz, vp, vp, sz, f32, vp, sz, vp) + _ERR),

@@ -380,6 +380,16 @@ int h3b_gelu_tanh_dev(h3_cuda *cuda, const void *d_in, void *d_out, int dtype, s
  * embeddings and final heads call it through dense_f32_cuda_to_dev, h3_dit_w4a8.c:5370). */
 int h3_cuda_gemm_f32_dd(h3_cuda *cuda, const float *d_x, const float *d_weight, size_t m, size_t n,
                         size_t k, float *d_y, double *gemm_ms, char *error, size_t error_size);
+/* d_y = alpha * (d_x @ d_weight^T) + beta * d_y (h3_gpu_cuda.h:125, :130).  The LoRA delta of a linear is
+ * t = x A^T (h3_cuda_gemm_f32_dd) followed by delta = scale * t B^T + beta * delta (this call), as
+ * h3_dit_w4a8.c:1036-1050 issues them; the delta then enters the INT8 GEMM epilogue as d_lora.  The _tf32_
+ * name computes in full f32 here. */
+int h3_cuda_gemm_f32_dd_ex(h3_cuda *cuda, const float *d_x, const float *d_weight, size_t m, size_t n,
+                           size_t k, float *d_y, float alpha, float beta, double *gemm_ms, char *error,
+                           size_t error_size);
+int h3_cuda_gemm_f32_dd_tf32_ex(h3_cuda *cuda, const float *d_x, const float *d_weight, size_t m,
+                                size_t n, size_t k, float *d_y, float alpha, float beta, char *error,
+                                size_t error_size);
 /* d_y[r,c] += d_bias[c] (h3_gpu_cuda.h:263). */
 int h3_cuda_bias_add_f32_dev(h3_cuda *cuda, float *d_y, const float *d_bias, size_t rows, size_t width,
                              char *error, size_t error_size);

@@ -564,3 +564,20 @@ def test_flag_barrier_gives_up_on_an_absent_rank(cuda):
     x = torch.arange(8, device="cuda")
     assert int(x.sum().item()) == 28
     cuda.check()
+
+
+def test_lora_delta_by_the_reference_call_pair(cuda, oracle):
+    """t = x A^T, delta = scale * t B^T + beta * delta with the reference's two calls (h3_dit_w4a8.c:1036-1050),
+    against the same products in float64; the delta then rides the INT8 GEMM epilogue as d_lora (tested above)."""
+    rng = np.random.default_rng(95)
+    m, k, r, n, scale = 200, 512, 16, 384, 0.7
+    x = rng.normal(0, 1, (m, k)).astype(np.float32)
+    a = rng.normal(0, 0.05, (r, k)).astype(np.float32)
+    b = rng.normal(0, 0.05, (n, r)).astype(np.float32)
+    d0 = rng.normal(0, 0.1, (m, n)).astype(np.float32)
+    t = cuda.gemm_f32_dd(dev(x), dev(a))
+    assert rel_l2(host(t), oracle.dense(x, a)) < 1e-5
+    for beta, tf32_name in ((0.0, False), (1.0, False), (0.5, True)):
+        want = scale * (x.astype(np.float64) @ a.T.astype(np.float64)) @ b.T.astype(np.float64) + beta * d0
+        got = cuda.gemm_f32_dd_ex(t, dev(b), dev(d0.copy()), alpha=scale, beta=beta, tf32_name=tf32_name)
+        assert rel_l2(host(got), want.astype(np.float32)) < 1e-5
