@@ -110,6 +110,19 @@ class Dit:
              ptr(sin), ptr(text), 0 if text is None else text.shape[0], ptr(out))
         return out
 
+    def denoise_step(self, latent, patch_w, patch_b, final_norm, final_mod, final_w, final_b, cos, sin, sigma, sigma_next, *,
+                     text=None, row_map=None):
+        """One sampler step with everything on the device: patch embedding (f32 dense) -> block chain in the
+        stream type -> final adaLN head (f32) -> Euler update of `latent` in place.  The modulation of the blocks
+        must have been projected for this step's time feature (project_modulation).  Returns the velocity."""
+        import torch
+        stream_dtype = {1: torch.bfloat16, 2: torch.float16}.get(self.geo.stream_dtype, torch.float32)
+        hidden = self.cuda.dense_f32(latent, patch_w, patch_b)
+        y = self.layers_forward(hidden.to(stream_dtype), cos, sin, row_map=row_map, text=text)
+        velocity = self.cuda.final_head_f32(y.float(), final_norm, final_mod, final_w, final_b)
+        self.cuda.euler_step_f32(latent, velocity, sigma, sigma_next)
+        return velocity
+
     def set_ulysses(self, comm):
         """Attaches a per-rank `UlyssesComm` (None detaches)."""
         call("h3b_dit_set_ulysses", self.h, C.byref(comm.cfg) if comm is not None else None)

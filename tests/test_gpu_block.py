@@ -120,3 +120,34 @@ def test_chain_host_entry_point_matches_device_chain(cuda, oracle):
     assert rel_l2(y_host, cur) < 3e-3
     assert dit.launches_per_block == 16
     dit.close()
+
+
+def test_device_resident_denoise_step(cuda, oracle):
+    """Patch embedding -> two blocks -> final adaLN head -> Euler update, all on the device, against the oracle's
+    composition of the same pieces at the same precision (f32 heads, int8 linears, bf16 stream)."""
+    geo, dit, host, _, text, t_feat, cos, sin = make_cross_case(cuda, oracle, 5, (2, 8, 8), 32, 256, 2, 512, n_blocks=2)
+    rng = np.random.default_rng(321)
+    seq, dim, patch = 128, 256, 96
+    latent = rng.normal(0, 1, (seq, patch)).astype(np.float32)
+    pw = rng.normal(0, 0.1, (dim, patch)).astype(np.float32)
+    pb = rng.normal(0, 0.1, dim).astype(np.float32)
+    fnorm = rng.normal(1, 0.1, dim).astype(np.float32)
+    fmod = rng.normal(0, 0.2, (2, dim)).astype(np.float32)
+    fw = rng.normal(0, 0.05, (patch, dim)).astype(np.float32)
+    fb = rng.normal(0, 0.1, patch).astype(np.float32)
+    dit.project_modulation(dev(t_feat))
+    lat_dev = dev(latent)
+    vel = dit.denoise_step(lat_dev, dev(pw), dev(pb), dev(fnorm), dev(fmod), dev(fw), dev(fb), dev(cos), dev(sin), 0.9, 0.6,
+                           text=dev(text, torch.bfloat16), row_map=torch.zeros(seq, dtype=torch.int32, device="cuda"))
+    cuda.check()
+    cur = dev(oracle.dense(latent, pw, pb), torch.bfloat16).float().cpu().numpy()
+    th = dev(text, torch.bfloat16).float().cpu().numpy()
+    for b in range(2):
+        cur = oracle.block_b(oracle_weights(oracle, host[b], t_feat, True), cur, th, cos, sin, heads=2, head_dim=128,
+                             ffn=512, quantised=True, bf16_stream=True)
+    want_vel = oracle.final_head(cur, fnorm, fmod, fw, fb)
+    got_vel = vel.cpu().numpy()
+    assert rel_l2(got_vel, want_vel) < 5e-3, rel_l2(got_vel, want_vel)
+    # the Euler update itself is exact given the velocity the device computed
+    assert np.array_equal(lat_dev.cpu().numpy(), oracle.euler_step(latent, got_vel, 0.9, 0.6))
+    dit.close()
