@@ -607,8 +607,8 @@ int h3b_ulysses_comm_init_rank(h3_ulysses_cfg *cfg, int rank, int world_size, co
  * nothing is set up or the path is switched off.  _barrier: all ranks, enqueued on the rank's compute stream;
  * work enqueued after it on any rank starts only when every rank's earlier work is done.  It is a one-warp
  * kernel that writes an epoch into a flag word in every peer's buffer and waits (bounded) for the peers'
- * words; H3B_ULYSSES_BARRIER=nccl in the environment at set-up time selects a one-word NCCL all-reduce
- * instead.  _check synchronises the compute stream and reports whether a barrier gave up waiting. */
+ * words; H3B_ULYSSES_BARRIER=nccl in the environment at set-up time (the same on every rank) selects a
+ * one-word NCCL all-reduce instead.  _check synchronises the compute stream and reports whether a barrier gave up waiting. */
 int h3b_ulysses_direct_setup(h3_ulysses_cfg *cfg, size_t seq_local, size_t heads, size_t head_dim,
                              char *err, size_t err_size);
 const h3b_ulysses_direct *h3b_ulysses_direct_get(const h3_ulysses_cfg *cfg);
