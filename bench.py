@@ -242,7 +242,6 @@ def gpu_arm(args):
     import torch
     import h3c_b200
     from h3c_b200 import dit as D
-    from oracle.pyoracle import Oracle  # checker side only: positions / RoPE tables of the workload
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
@@ -286,14 +285,11 @@ def gpu_arm(args):
             comm.enable_direct(bool(ok.item()))
         dit.set_ulysses(comm)
     rows = seq_local if world > 1 else seq_real
-    oracle = Oracle()
     inv_freq = (1.0 / (10000.0 ** (np.arange(16) / 16.0))).astype(np.float32)
-    pt, ph, pw = oracle.fill_video_pos(text_len, grid[0], 2 * grid[1], 2 * grid[2])
-    cos_h, sin_h = oracle.rope_tables(inv_freq, pt, ph, pw, 1.0)
-    if world > 1:   # tables cover the padded gathered sequence; pad rows get angle 0
-        padc = np.ones((seq_pad - seq_real, cos_h.shape[1]), np.float32)
-        cos_h = np.concatenate([cos_h, padc])
-        sin_h = np.concatenate([sin_h, 0 * padc])
+    # positions and RoPE tables come from the library's own host code; under sequence parallelism they
+    # cover the padded gathered sequence (pad rows get angle 0)
+    cos_h, sin_h = h3c_b200.video_rope_tables(inv_freq, text_len, grid, 1.0,
+                                              pad_rows=(seq_pad - seq_real) if world > 1 else 0)
     rng = np.random.default_rng(1000 + rank)
     x_np = rng.normal(0, 1, (rows, geo.dim)).astype(np.float32)
     if world > 1:

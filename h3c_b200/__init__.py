@@ -396,6 +396,47 @@ def ulysses_local_rows(seq_pad, ulysses, rank):
     return int(load().h3_ulysses_local_rows(seq_pad, ulysses, rank))
 
 
+def fill_video_pos(text_len, latent_t, latent_h, latent_w):
+    """RoPE coordinates (t, h, w) of the video tokens (h3_dit_w4a8_fill_metal_video_pos); host arrays."""
+    import numpy as np
+    n = latent_t * (latent_h // 2) * (latent_w // 2)
+    pt, ph, pw = (np.empty(max(n, 1), np.float32) for _ in range(3))
+    call("h3_dit_w4a8_fill_metal_video_pos", text_len, latent_t, latent_h, latent_w, pt.ctypes.data, ph.ctypes.data,
+         pw.ctypes.data)
+    return pt[:n], ph[:n], pw[:n]
+
+
+def rope_tables(inv_freq, pos_t, pos_h, pos_w, spatial_scale=1.0):
+    """cos / sin [seq, 48] from 16 inverse frequencies and the three coordinates (h3_dit_w4a8_rope_tables_f32)."""
+    import numpy as np
+    inv_freq, pos_t, pos_h, pos_w = (np.ascontiguousarray(a, np.float32) for a in (inv_freq, pos_t, pos_h, pos_w))
+    if inv_freq.size != 16:
+        raise H3Error("rope_tables: inv_freq must hold 16 frequencies")
+    cos = np.empty((len(pos_t), 48), np.float32)
+    sin = np.empty_like(cos)
+    call("h3_dit_w4a8_rope_tables_f32", inv_freq.ctypes.data, len(pos_t), pos_t.ctypes.data, pos_h.ctypes.data,
+         pos_w.ctypes.data, C.c_float(spatial_scale), cos.ctypes.data, sin.ctypes.data)
+    return cos, sin
+
+
+def video_rope_tables(inv_freq, text_len, grid, spatial_scale=1.0, pad_rows=0):
+    """Tables of a whole step for the token grid (t, h, w), with `pad_rows` trailing rows of angle zero."""
+    import numpy as np
+    inv_freq = np.ascontiguousarray(inv_freq, np.float32)
+    if inv_freq.size != 16:
+        raise H3Error("video_rope_tables: inv_freq must hold 16 frequencies")
+    rows = grid[0] * grid[1] * grid[2] + pad_rows
+    cos = np.empty((rows, 48), np.float32)
+    sin = np.empty_like(cos)
+    call("h3b_dit_video_rope_tables", inv_freq.ctypes.data, text_len, grid[0], grid[1], grid[2],
+         C.c_float(spatial_scale), pad_rows, cos.ctypes.data, sin.ctypes.data)
+    return cos, sin
+
+
+def t_row_from_sigma(sigma, t_table_rows):
+    return int(load().h3_dit_w4a8_t_row_from_sigma(C.c_float(sigma), t_table_rows))
+
+
 class UlyssesComm:
     """Per-rank sequence-parallel communicator (h3_ulysses_cfg + h3b_ulysses_comm_init_rank)."""
 

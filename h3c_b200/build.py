@@ -56,7 +56,7 @@ def build(force: bool = False) -> Path:
     with ThreadPoolExecutor(max_workers=min(8, os.cpu_count() or 1)) as ex:
         objs = list(ex.map(lambda s: _compile(s, hdr, force), cu + c))
     if force or _stale(LIB, objs):
-        cmd = ["nvcc", "-shared", "-o", str(LIB)] + [str(o) for o in objs] + ["-lpthread", "-ldl"]
+        cmd = ["nvcc", "-shared", "-o", str(LIB)] + [str(o) for o in objs] + ["-lpthread", "-ldl", "-Xlinker", "-Bsymbolic"]
         res = subprocess.run(cmd, capture_output=True, text=True)
         if res.returncode != 0:
             raise RuntimeError(f"{' '.join(cmd)}\n{res.stdout}{res.stderr}")

@@ -213,6 +213,11 @@ _SIGS = {
     "h3b_sdpa_bf16_scatter_dev": (i32, (vp, vp, sz, f32) + _ERR),
     "h3b_dit_layers_forward_ulysses_dev": (i32, (vp, C.c_uint, C.c_uint, vp, sz, sz, vp, vp, vp, vp, sz, vp) + _ERR),
     "h3b_dit_layers_forward_ulysses_f32": (i32, (vp, C.c_uint, C.c_uint, vp, vp, sz, sz, vp, vp, vp, vp, sz, vp) + _ERR),
+    "h3_dit_w4a8_fill_metal_video_pos": (i32, (sz, i32, i32, i32, vp, vp, vp) + _ERR),
+    "h3_dit_w4a8_video_span_sum": (f32, (i32,)),
+    "h3_dit_w4a8_rope_tables_f32": (i32, (vp, sz, vp, vp, vp, f32, vp, vp) + _ERR),
+    "h3_dit_w4a8_t_row_from_sigma": (sz, (f32, sz)),
+    "h3b_dit_video_rope_tables": (i32, (vp, sz, i32, i32, i32, f32, sz, vp, vp) + _ERR),
     "h3_ulysses_validate": (i32, (i32, i32, i32, i32, i32) + _ERR),
     "h3_ulysses_pad_seq": (sz, (sz, i32)),
     "h3_ulysses_local_rows": (sz, (sz, i32, i32)),

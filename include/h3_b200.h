@@ -560,6 +560,26 @@ int h3b_dit_layers_forward_f32(h3b_dit *dit, unsigned first_block, unsigned n_bl
 /* Kernel launches one block forward issues (for launch accounting). */
 int h3b_dit_launches_per_block(const h3b_dit *dit);
 
+/* Host-side tables of a step, same names and arithmetic as the reference (bit-identical results).
+ * Positions of the video tokens: latent dims (latent_t, latent_h, latent_w), token grid latent_h/2 x
+ * latent_w/2 per frame, time starting at text_len.  h3_dit_w4a8.h:382, body h3_dit_w4a8.c:2496 */
+int h3_dit_w4a8_fill_metal_video_pos(size_t text_len, int latent_t, int latent_h, int latent_w, float *pos_t,
+                                     float *pos_h, float *pos_w, char *error, size_t error_size);
+float h3_dit_w4a8_video_span_sum(int latent_t);                                     /* h3_dit_w4a8.h:395 */
+/* cos/sin [seq, 48]: 3 axes (t, h*spatial_scale, w*spatial_scale) x 16 frequencies.
+ * h3_dit_w4a8.h:366, body h3_dit_w4a8.c:2412 */
+int h3_dit_w4a8_rope_tables_f32(const float *inv_freq, size_t seq, const float *pos_t, const float *pos_h,
+                                const float *pos_w, float spatial_scale, float *cos_out, float *sin_out, char *error,
+                                size_t error_size);
+/* Row of the time-feature table for noise level sigma in [0,1] (indexed by 1 - sigma; the switch
+ * H3_DIT_T_ROW_BY_SIGMA=1 indexes by sigma).  h3_dit_w4a8.h:545, body h3_dit_w4a8.c:5229 */
+size_t h3_dit_w4a8_t_row_from_sigma(float sigma, size_t t_table_rows);
+/* Addition: the two calls above for a token grid grid_t x grid_h x grid_w in one call, plus `pad_rows`
+ * trailing rows of angle zero (cos 1, sin 0) for a sequence padded for sequence parallelism. */
+int h3b_dit_video_rope_tables(const float *inv_freq16, size_t text_len, int grid_t, int grid_h, int grid_w,
+                              float spatial_scale, size_t pad_rows, float *cos_out, float *sin_out, char *error,
+                              size_t error_size);
+
 /* ------------------------------------------------------------------ Ulysses */
 
 enum { H3_ULYSSES_PACKED_ALIGN = 64 };                                              /* h3_ulysses.h:10 */

@@ -190,6 +190,7 @@ def main():
          ue4m3_bytes=mod_q.f32_to_ue4m3(vals), ue4m3_table=mod_q.ue4m3_to_f32(np.arange(0x7F, dtype=np.uint8)))
 
     step_sides(ref)
+    step_tables(ref)
 
 
 def step_sides(ref):
@@ -212,8 +213,41 @@ def step_sides(ref):
          stepped=ref.euler_step(lat, vel, 0.8, 0.55))
 
 
+def step_tables(ref):
+    """Positions, RoPE tables and time-table rows of the three benchmark grids, as the reference computes
+    them.  The tables are large (50,220 x 48), so the file keeps their FNV-1a checksums (the reference's own
+    h3_dit_w4a8_checksum_f32) plus the first and last rows."""
+    import ctypes as C
+    inv_freq = (1.0 / (10000.0 ** (np.arange(16) / 16.0))).astype(np.float32)
+    out = {"inv_freq": inv_freq, "grids": np.array([(6, 32, 32), (24, 32, 32), (31, 30, 54)], np.int32),
+           "text_len": np.array([512], np.int64)}
+    for i, g in enumerate(out["grids"]):
+        pt, ph, pw = ref.fill_video_pos(512, int(g[0]), 2 * int(g[1]), 2 * int(g[2]))
+        cos, sin = ref.rope_tables(inv_freq, pt, ph, pw, 1.0)
+        out[f"sum_{i}"] = np.array([ref.checksum_f32(x) for x in (pt, ph, pw, cos, sin)], np.uint64)
+        out[f"cos_head_{i}"], out[f"cos_tail_{i}"] = cos[:4], cos[-4:]
+        out[f"sin_head_{i}"], out[f"sin_tail_{i}"] = sin[:4], sin[-4:]
+    fn = ref.lib.h3_dit_w4a8_t_row_from_sigma
+    fn.restype, fn.argtypes = C.c_size_t, [C.c_float, C.c_size_t]
+    sig = np.concatenate([np.linspace(-0.25, 1.25, 61), [0.5, 0.49951171875, 0.999, 1e-4]]).astype(np.float32)
+    out["sigma"] = sig
+    out["t_rows"] = np.array([[fn(float(s), r) for r in (0, 1, 2, 1025)] for s in sig], np.uint64)
+    out["span_sum"] = np.array([ref.lib.h3_dit_w4a8_video_span_sum(t) for t in range(0, 40)], np.float32) \
+        if _span_ready(ref) else np.zeros(0, np.float32)
+    save("step_tables", **out)
+
+
+def _span_ready(ref):
+    import ctypes as C
+    ref.lib.h3_dit_w4a8_video_span_sum.restype = C.c_float
+    ref.lib.h3_dit_w4a8_video_span_sum.argtypes = [C.c_int]
+    return True
+
+
 if __name__ == "__main__":
     if len(sys.argv) > 1 and sys.argv[1] == "step_sides":
         step_sides(Ref())
+    elif len(sys.argv) > 1 and sys.argv[1] == "step_tables":
+        step_tables(Ref())
     else:
         main()
