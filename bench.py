@@ -510,6 +510,112 @@ def roofline(prof, lin_flops_block, attn_flops_block, n_blocks, pk):
             "share_of_step": p["ms"] / sum(v["ms"] for v in prof.values())}
 
 
+# ------------------------------------------------------------------------- single kernels
+
+def _time_kernel(fn, iters, warmup=3):
+    import torch
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(iters):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / iters
+
+
+def kernel_arm(a):
+    """One operator of the library on synthetic data, timed with CUDA events on the launching stream; prints
+    achieved TFLOP/s or GB/s.  These are also the small, self-contained commands behind the ncu summaries
+    under profiles/."""
+    import torch
+    import h3c_b200
+    cuda = h3c_b200.Cuda(0)
+    g = torch.Generator(device="cuda")
+    g.manual_seed(0)
+    out = {"kernel": a.kernel}
+    if a.kernel == "gemm":
+        w_i8 = np.random.default_rng(0).integers(-127, 128, (a.n, a.k), dtype=np.int8)
+        w = cuda.weight_from_i8(w_i8, np.full(a.n, 1e-3, np.float32))
+        x = torch.randint(-127, 128, (a.m, a.k), generator=g, device="cuda", dtype=torch.int8)
+        s = torch.full((a.m,), 0.01, device="cuda")
+        if a.epi == "qkv":   # QKV projection with QK-norm and RoPE in the epilogue (N = 3 * heads * 128)
+            qn = torch.ones(128, device="cuda")
+            cos = torch.rand((a.m, 64), generator=g, device="cuda")
+            sin = torch.rand((a.m, 64), generator=g, device="cuda")
+            ms = _time_kernel(lambda: cuda.gemm_i8_qkv_rope(w, x, s, qn, qn, cos, sin, 64), a.iters)
+            out.update(m=a.m, n=a.n, k=a.k, epi=a.epi, ms=ms, tops=2.0 * a.m * a.n * a.k / ms / 1e9)
+            OUT.emit(json.dumps(out))
+            return
+        kind = {"plain": h3c_b200.EPI_PLAIN, "gate": h3c_b200.EPI_GATE, "gelu": h3c_b200.EPI_GELU,
+                "swiglu": h3c_b200.EPI_SWIGLU}[a.epi]
+        n_out = a.n // 2 if a.epi == "swiglu" else a.n
+        y = torch.empty((a.m, n_out), dtype=torch.bfloat16, device="cuda")
+        res = torch.zeros_like(y) if a.epi == "gate" else None
+        ms = _time_kernel(lambda: cuda.gemm_i8(w, x, s, kind=kind, residual=res, out=y), a.iters)
+        out.update(m=a.m, n=a.n, k=a.k, epi=a.epi, ms=ms, tops=2.0 * a.m * a.n * a.k / ms / 1e9)
+    elif a.kernel == "peak":
+        import ctypes as C
+        from h3c_b200.lib import call
+        for kind, name in ((0, "int8"), (1, "bf16"), (2, "nvfp4"), (3, "bf16_n128_ss"), (4, "bf16_n128_ts"), (5, "nvfp4_n128")):
+            v = C.c_double(0)
+            call("h3b_umma_peak_dev", cuda.h, kind, 20000, C.byref(v))     # ~10 ms of MMAs: burst clocks
+            out[name + "_burst_tops"] = v.value
+            call("h3b_umma_peak_dev", cuda.h, kind, 2000000, C.byref(v))   # ~1 s: under the power limit
+            out[name + "_sustained_tops"] = v.value
+    elif a.kernel == "sides":   # patch embedding, final head and Euler update of a.m tokens (f32, hidden = a.n)
+        lat = torch.randn((a.m, 96), generator=g, device="cuda")
+        pw, pb = torch.randn((a.n, 96), generator=g, device="cuda"), torch.randn(a.n, generator=g, device="cuda")
+        x = torch.randn((a.m, a.n), generator=g, device="cuda")
+        nw, mod = torch.ones(a.n, device="cuda"), torch.zeros((2, a.n), device="cuda")
+        fw, fb = torch.randn((96, a.n), generator=g, device="cuda"), torch.randn(96, generator=g, device="cuda")
+        vel = torch.randn((a.m, 96), generator=g, device="cuda")
+        out.update(m=a.m, hidden=a.n,
+                   patch_embed_ms=_time_kernel(lambda: cuda.dense_f32(lat, pw, pb), a.iters),
+                   final_head_ms=_time_kernel(lambda: cuda.final_head_f32(x, nw, mod, fw, fb), a.iters),
+                   euler_ms=_time_kernel(lambda: cuda.euler_step_f32(lat, vel, 0.8, 0.7), a.iters))
+    elif a.kernel == "gemm_fp4":
+        x4 = torch.randint(0, 256, (a.m, a.k // 2), generator=g, device="cuda", dtype=torch.uint8)
+        w4 = torch.randint(0, 256, (a.n, a.k // 2), generator=g, device="cuda", dtype=torch.uint8)
+        sfb = lambda rows: int(h3c_b200.load().h3_cuda_nvfp4_sf_bytes(rows, a.k))
+        sfx = torch.full((sfb(a.m),), 0x38, device="cuda", dtype=torch.uint8)
+        sfw = torch.full((sfb(a.n),), 0x38, device="cuda", dtype=torch.uint8)
+        ms = _time_kernel(lambda: cuda.gemm_fp4(w4, sfw, x4, sfx, out_dtype=torch.bfloat16), a.iters)
+        out.update(m=a.m, n=a.n, k=a.k, ms=ms, tflops=2.0 * a.m * a.n * a.k / ms / 1e9)
+    elif a.kernel == "attn":
+        lk = a.lk or a.lq
+        q = torch.randn((a.lq, a.heads, 128), generator=g, device="cuda").to(torch.bfloat16)
+        k = torch.randn((lk, a.heads, 128), generator=g, device="cuda").to(torch.bfloat16)
+        v = torch.randn((lk, a.heads, 128), generator=g, device="cuda").to(torch.bfloat16)
+        o = torch.empty((a.lq, a.heads * 128), dtype=torch.bfloat16, device="cuda")
+        ms = _time_kernel(lambda: cuda.sdpa_bf16(q, k, v, out=o), a.iters)
+        out.update(lq=a.lq, lk=lk, heads=a.heads, ms=ms, tflops=4.0 * a.lq * lk * a.heads * 128 / ms / 1e9)
+    elif a.kernel == "norm":
+        x = torch.randn((a.m, a.k), generator=g, device="cuda").to(torch.bfloat16)
+        q = torch.empty((a.m, a.k), dtype=torch.int8, device="cuda")
+        s = torch.empty(a.m, dtype=torch.float32, device="cuda")
+        if a.plain_quant:
+            ms = _time_kernel(lambda: cuda.norm(x, identity=True, q=q, scales=s), a.iters)
+        else:
+            nw = torch.ones(a.k, device="cuda")
+            mod = torch.zeros((1, 6, a.k), device="cuda")
+            rm = torch.zeros(a.m, dtype=torch.int32, device="cuda")
+            ms = _time_kernel(lambda: cuda.norm(x, norm_w=nw, modulation=mod, row_map=rm, slots=6, shift_slot=0, scale_slot=1,
+                                         q=q, scales=s), a.iters)
+        out.update(m=a.m, k=a.k, ms=ms, gbs=(a.m * a.k * 3 + a.m * 4) / ms / 1e6)
+    else:
+        qkv = torch.randn((a.m, 3 * a.heads * 128), generator=g, device="cuda").to(torch.bfloat16)
+        qn = torch.ones(128, device="cuda")
+        cos = torch.ones((a.m, 48), device="cuda")
+        sin = torch.zeros((a.m, 48), device="cuda")
+        ms = _time_kernel(lambda: cuda.qkv_rope(qkv, qn, qn, cos, sin, a.heads, 128, 48), a.iters)
+        out.update(m=a.m, heads=a.heads, ms=ms, gbs=a.m * a.heads * 128 * 3 * 4 / ms / 1e6)
+    cuda.check()
+    OUT.emit(json.dumps(out))
+
+
 class QuietStdout:
     """Keeps file descriptor 1 free of library chatter (NCCL prints its version banner there): everything
     written to stdout is sent to stderr until `emit` writes the one JSON line to the real stdout."""
@@ -540,8 +646,22 @@ def main():
     ap.add_argument("--graph", action="store_true", help="replay the resident step as one CUDA graph (N = 1)")
     ap.add_argument("--skip-cpu-baseline", action="store_true", help="omit the CPU sample (profiling runs)")
     ap.add_argument("--skip-e2e", action="store_true", help="omit the host-buffer measurement (profiling runs)")
+    ap.add_argument("--kernel", default=None,
+                    choices=["gemm", "gemm_fp4", "attn", "norm", "rope", "peak", "sides"],
+                    help="time ONE operator on synthetic data instead of the step (also the ncu capture commands)")
+    ap.add_argument("--m", type=int, default=6144)
+    ap.add_argument("--n", type=int, default=9216)
+    ap.add_argument("--k", type=int, default=3072)
+    ap.add_argument("--lq", type=int, default=6144)
+    ap.add_argument("--lk", type=int, default=0)
+    ap.add_argument("--heads", type=int, default=24)
+    ap.add_argument("--epi", default="plain", choices=["plain", "gate", "gelu", "swiglu", "qkv"])
+    ap.add_argument("--plain-quant", action="store_true")
+    ap.add_argument("--iters", type=int, default=20)
     args = ap.parse_args()
-    if args.impl == "reference":
+    if args.kernel:
+        kernel_arm(args)
+    elif args.impl == "reference":
         reference_arm(args)
     else:
         gpu_arm(args)

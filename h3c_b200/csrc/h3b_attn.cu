@@ -22,7 +22,11 @@
 // TMEM (512 columns): S_A 0..127, S_B 128..255 (P overlays the first 64 columns of each),
 // O_A 256..383, O_B 384..511.
 #include <cuda_bf16.h>
+#include <cuda_fp16.h>
 
+#include <stdlib.h>
+
+#include <algorithm>
 #include <type_traits>
 
 #include "h3b_internal.h"
@@ -43,7 +47,7 @@ constexpr size_t SMEM_BYTES = 1024 + 6 * (size_t)TILE + 256;
 
 struct AttnParams {
     CUtensorMap tmap_q, tmap_k, tmap_v;   // 3-D {d, head, row}, box {64, 1, 128}
-    __nv_bfloat16 *out;
+    void *out;                            // 16-bit elements of the kernel's type
     size_t o_stride;                      // elements between output rows
     int lq, lk, heads;
     float scale_log2;                     // scale * log2(e)
@@ -52,7 +56,25 @@ struct AttnParams {
     // sc_out[r / sc_rows] (possibly another GPU's memory) at row r % sc_rows, head sc_head0 + head of
     // sc_heads; sc_rows == 0 = off
     int sc_rows, sc_heads, sc_head0;
-    __nv_bfloat16 *sc_out[8];
+    void *sc_out[8];
+};
+
+// The two 16-bit operand types: bf16 (the benchmark's residual-stream type) and f16 (what the reference's
+// own f16 attention entry points stage in: three more mantissa bits in Q, K, V and in the probabilities).
+template <typename T> struct Elem;
+template <> struct Elem<__nv_bfloat16> {
+    static constexpr uint32_t FMT = 1;   // tcgen05 kind::f16 operand format code
+    static __device__ __forceinline__ uint32_t pack(float a, float b) {
+        __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
+        return *reinterpret_cast<uint32_t *>(&h);
+    }
+};
+template <> struct Elem<__half> {
+    static constexpr uint32_t FMT = 0;
+    static __device__ __forceinline__ uint32_t pack(float a, float b) {
+        __half2 h = __floats2half2_rn(a, b);
+        return *reinterpret_cast<uint32_t *>(&h);
+    }
 };
 
 __device__ __forceinline__ float ex2_approx(float x) {
@@ -83,7 +105,8 @@ __device__ __forceinline__ void add2(float &d0, float &d1, float a0, float a1) {
         : "f"(a0), "f"(a1));
 }
 
-__global__ void __launch_bounds__(attn::THREADS, 1) k_attn_bf16(const __grid_constant__ AttnParams p) {
+template <typename T>
+__global__ void __launch_bounds__(attn::THREADS, 1) k_attn(const __grid_constant__ AttnParams p) {
     using namespace attn;
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
@@ -164,8 +187,8 @@ __global__ void __launch_bounds__(attn::THREADS, 1) k_attn_bf16(const __grid_con
             // S = Q K^T : both operands K-major in shared memory (d contiguous).
             // O += P V  : P from TMEM (row = lane, two bf16 keys per 32-bit column); V as stored
             //             ([key][d], d contiguous) is the N-major form of the B operand.
-            constexpr uint32_t idesc_s = umma_idesc(1, 1, 1, BQ, BKV, 0, 0);
-            constexpr uint32_t idesc_o = umma_idesc(1, 1, 1, BQ, HD, 0, 1);
+            constexpr uint32_t idesc_s = umma_idesc(1, Elem<T>::FMT, Elem<T>::FMT, BQ, BKV, 0, 0);
+            constexpr uint32_t idesc_o = umma_idesc(1, Elem<T>::FMT, Elem<T>::FMT, BQ, HD, 0, 1);
             const uint32_t q_base = smem_u32(sQ), k_base = smem_u32(sK), v_base = smem_u32(sV);
             auto issue_s = [&](int t, int stage) {   // scores of tile t against the K tile in `stage`
                 const uint32_t q_addr = q_base + t * TILE, k_addr = k_base + stage * TILE;
@@ -306,9 +329,8 @@ __global__ void __launch_bounds__(attn::THREADS, 1) k_attn_bf16(const __grid_con
                     const float p0 = ex2_approx(x0), p1 = ex2_approx(x1), p2 = ex2_approx(x2), p3 = ex2_approx(x3);
                     add2(l0, l1, p0, p1);
                     add2(l2, l3, p2, p3);
-                    __nv_bfloat162 h0 = __floats2bfloat162_rn(p0, p1), h1 = __floats2bfloat162_rn(p2, p3);
-                    packed[i >> 1] = *reinterpret_cast<uint32_t *>(&h0);
-                    packed[(i >> 1) + 1] = *reinterpret_cast<uint32_t *>(&h1);
+                    packed[i >> 1] = Elem<T>::pack(p0, p1);
+                    packed[(i >> 1) + 1] = Elem<T>::pack(p2, p3);
                 }
                 tmem_st_32x32b_x16(s_addr + ch * 16, packed);
                 if (ch & 1) {   // a half (64 keys) of P is complete: hand it to the MMA warp
@@ -339,11 +361,10 @@ __global__ void __launch_bounds__(attn::THREADS, 1) k_attn_bf16(const __grid_con
 #pragma unroll
                 for (int i = 0; i < 32; i += 8) {
                     uint4 raw;
-                    __nv_bfloat162 *h = reinterpret_cast<__nv_bfloat162 *>(&raw);
+                    uint32_t *h = reinterpret_cast<uint32_t *>(&raw);
 #pragma unroll
                     for (int u = 0; u < 4; u++)
-                        h[u] = __floats2bfloat162_rn(__uint_as_float(o[i + 2 * u]) * inv_l,
-                                                     __uint_as_float(o[i + 2 * u + 1]) * inv_l);
+                        h[u] = Elem<T>::pack(__uint_as_float(o[i + 2 * u]) * inv_l, __uint_as_float(o[i + 2 * u + 1]) * inv_l);
                     *reinterpret_cast<uint4 *>(stg + lane * STG_ROW + (ch * 32 + i) * 2) = raw;
                 }
             }
@@ -354,13 +375,13 @@ __global__ void __launch_bounds__(attn::THREADS, 1) k_attn_bf16(const __grid_con
             for (int k2 = 0; k2 < 16; k2++) {
                 const int rr = 2 * k2 + sub, row = row_first + rr;
                 if (ok && row < p.lq) {
-                    __nv_bfloat16 *dst;
+                    T *dst;
                     if (p.sc_rows) {
                         const int owner = row / p.sc_rows;
-                        dst = p.sc_out[owner < 8 ? owner : 0] +
+                        dst = reinterpret_cast<T *>(p.sc_out[owner < 8 ? owner : 0]) +
                               ((size_t)(row - owner * p.sc_rows) * p.sc_heads + p.sc_head0 + head) * HD;
                     } else {
-                        dst = p.out + (size_t)row * p.o_stride + (size_t)head * HD;
+                        dst = reinterpret_cast<T *>(p.out) + (size_t)row * p.o_stride + (size_t)head * HD;
                     }
                     *reinterpret_cast<uint4 *>(dst + chunk * 8) = *reinterpret_cast<const uint4 *>(stg + rr * STG_ROW + chunk * 16);
                 }
@@ -376,9 +397,10 @@ __global__ void __launch_bounds__(attn::THREADS, 1) k_attn_bf16(const __grid_con
     }
 }
 
-static int make_map(CUtensorMap *map, const void *base, size_t stride_elems, size_t rows, size_t heads, char *error,
+static int make_map(CUtensorMap *map, const void *base, size_t stride_elems, size_t rows, size_t heads, int f16, char *error,
                     size_t error_size, const char *what) {
-    int rc = h3b_encode_tmap_3d(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, base, attn::HD, heads, rows,
+    int rc = h3b_encode_tmap_3d(map, f16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, base,
+                                attn::HD, heads, rows,
                                 attn::HD * 2, stride_elems * 2, 64, 1, 128, CU_TENSOR_MAP_SWIZZLE_128B);
     if (rc != 0) return fail(error, error_size, "sdpa: cuTensorMapEncodeTiled(%s) failed (%d)", what, rc);
     return 1;
@@ -386,17 +408,22 @@ static int make_map(CUtensorMap *map, const void *base, size_t stride_elems, siz
 
 static int launch_sdpa_impl(h3_cuda *cuda, const void *q, size_t qs, const void *k, size_t ks, const void *v, size_t vs,
                             size_t lq, size_t lk, size_t heads, size_t hd, float scale, void *out, size_t os,
-                            const h3b_ulysses_direct *sc, char *error, size_t error_size);
+                            const h3b_ulysses_direct *sc, int f16, char *error, size_t error_size);
 
 int launch_sdpa_bf16(h3_cuda *cuda, const void *q, size_t qs, const void *k, size_t ks, const void *v, size_t vs,
                      size_t lq, size_t lk, size_t heads, size_t hd, float scale, void *out, size_t os, char *error,
                      size_t error_size) {
-    return launch_sdpa_impl(cuda, q, qs, k, ks, v, vs, lq, lk, heads, hd, scale, out, os, nullptr, error, error_size);
+    return launch_sdpa_impl(cuda, q, qs, k, ks, v, vs, lq, lk, heads, hd, scale, out, os, nullptr, 0, error, error_size);
+}
+int launch_sdpa_f16(h3_cuda *cuda, const void *q, size_t qs, const void *k, size_t ks, const void *v, size_t vs,
+                    size_t lq, size_t lk, size_t heads, size_t hd, float scale, void *out, size_t os, char *error,
+                    size_t error_size) {
+    return launch_sdpa_impl(cuda, q, qs, k, ks, v, vs, lq, lk, heads, hd, scale, out, os, nullptr, 1, error, error_size);
 }
 
 static int launch_sdpa_impl(h3_cuda *cuda, const void *q, size_t qs, const void *k, size_t ks, const void *v, size_t vs,
                             size_t lq, size_t lk, size_t heads, size_t hd, float scale, void *out, size_t os,
-                            const h3b_ulysses_direct *sc, char *error, size_t error_size) {
+                            const h3b_ulysses_direct *sc, int f16, char *error, size_t error_size) {
     if (!cuda || !q || !k || !v || !out || !lq || !lk || !heads) return fail(error, error_size, "invalid sdpa args");
     if (hd != attn::HD) return fail(error, error_size, "sdpa: head_dim %zu unsupported (128 only)", hd);
     if ((qs % 8) || (ks % 8) || (vs % 8) || (os % 8) || ((uintptr_t)q & 15) || ((uintptr_t)k & 15) ||
@@ -408,11 +435,11 @@ static int launch_sdpa_impl(h3_cuda *cuda, const void *q, size_t qs, const void 
     if (!(scale > 0.0f)) return fail(error, error_size, "sdpa: scale must be positive");
     AttnParams p;
     memset(&p, 0, sizeof(p));
-    if (!make_map(&p.tmap_q, q, qs, lq, heads, error, error_size, "Q") ||
-        !make_map(&p.tmap_k, k, ks, lk, heads, error, error_size, "K") ||
-        !make_map(&p.tmap_v, v, vs, lk, heads, error, error_size, "V"))
+    if (!make_map(&p.tmap_q, q, qs, lq, heads, f16, error, error_size, "Q") ||
+        !make_map(&p.tmap_k, k, ks, lk, heads, f16, error, error_size, "K") ||
+        !make_map(&p.tmap_v, v, vs, lk, heads, f16, error, error_size, "V"))
         return 0;
-    p.out = (__nv_bfloat16 *)out; p.o_stride = os; p.lq = (int)lq; p.lk = (int)lk; p.heads = (int)heads;
+    p.out = out; p.o_stride = os; p.lq = (int)lq; p.lk = (int)lk; p.heads = (int)heads;
     p.scale_log2 = scale * 1.4426950408889634f;
     p.status = cuda->d_status;
     if (sc) {
@@ -422,16 +449,17 @@ static int launch_sdpa_impl(h3_cuda *cuda, const void *q, size_t qs, const void 
         p.sc_head0 = (int)((size_t)sc->rank * (sc->heads / (size_t)sc->ulysses));
         for (int r = 0; r < sc->ulysses; r++) {
             if (!sc->peer_att[r]) return fail(error, error_size, "sdpa scatter: buffer of rank %d is not mapped", r);
-            p.sc_out[r] = (__nv_bfloat16 *)sc->peer_att[r];
+            p.sc_out[r] = sc->peer_att[r];
         }
     }
-    H3B_CUDA_OK(cudaFuncSetAttribute(k_attn_bf16, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)attn::SMEM_BYTES),
+    auto kernel = f16 ? k_attn<__half> : k_attn<__nv_bfloat16>;
+    H3B_CUDA_OK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)attn::SMEM_BYTES),
                 "sdpa smem attribute");
     dim3 grid((unsigned)ceil_div(lq, 2 * attn::BQ), (unsigned)heads);
     ProfScope prof(cuda, PROF_ATTN);
-    k_attn_bf16<<<grid, attn::THREADS, attn::SMEM_BYTES, cuda->op_stream>>>(p);
+    kernel<<<grid, attn::THREADS, attn::SMEM_BYTES, cuda->op_stream>>>(p);
     cuda->launches++;
-    H3B_CUDA_OK(cudaGetLastError(), "k_attn_bf16 launch");
+    H3B_CUDA_OK(cudaGetLastError(), "k_attn launch");
     return 1;
 }
 
@@ -461,15 +489,28 @@ int h3b_sdpa_bf16_scatter_dev(h3_cuda *cuda, const h3b_ulysses_direct *sc, size_
     const size_t hl = sc->heads / (size_t)sc->ulysses, il = hl * sc->head_dim;
     // `out` of the plain form is only checked for alignment: rows are stored through the scatter table
     int ok = launch_sdpa_impl(cuda, sc->q, il, sc->k, il, sc->v, il, seq_real, seq_real, hl, sc->head_dim, scale, sc->att,
-                              sc->heads * sc->head_dim, sc, error, error_size);
+                              sc->heads * sc->head_dim, sc, 0, error, error_size);
     if (ok) g_last_backend = "tcgen05_flash_bf16";
     return ok;
 }
 
-const char *h3_cuda_sdpa_backend_name(void) { return "tcgen05_flash_bf16"; }
+const char *h3_cuda_sdpa_backend_name(void) { return "tcgen05_flash"; }
 const char *h3_cuda_sdpa_last_backend_name(void) { return g_last_backend; }
 
-// F32 tensors in and out: cast to bf16 staging, run the bf16 kernel, cast back.
+// ---- the reference's f16 attention entry points --------------------------------------------------------------
+// F32 tensors in and out; Q, K, V and the result are staged as f16 like the reference's default path
+// (h3_gpu_cuda.cu:12084-12220), the attention runs on the f16 form of the kernel above.
+
+// layout of the handle's staging area for `n` elements per tensor: Q | K | V | O (f16)
+static int stage4(h3_cuda *cuda, size_t n, __half **q, __half **k, __half **v, __half **o, char *error, size_t error_size) {
+    if (!grow(cuda, &cuda->attn, &cuda->attn_bytes, 4 * n * sizeof(__half), error, error_size)) return 0;
+    *q = (__half *)cuda->attn;
+    *k = *q + n;
+    *v = *k + n;
+    *o = *v + n;
+    return 1;
+}
+
 int h3_cuda_sdpa_f16_dev_ex(h3_cuda *cuda, const float *d_query, const float *d_key, const float *d_value,
                             size_t seq, size_t heads, size_t head_dim, float scale, int attn_window, float *d_out,
                             double *sdpa_ms, char *backend_out, size_t backend_out_size, char *error,
@@ -477,18 +518,18 @@ int h3_cuda_sdpa_f16_dev_ex(h3_cuda *cuda, const float *d_query, const float *d_
     if (!cuda || !d_query || !d_key || !d_value || !d_out || !seq || !heads || !head_dim)
         return fail(error, error_size, "invalid sdpa args");
     if (attn_window != 0) return fail(error, error_size, "sdpa: windowed attention (attn_window=%d) is not supported", attn_window);
-    const size_t n = seq * heads * head_dim;
-    if (!grow(cuda, &cuda->attn, &cuda->attn_bytes, 4 * n * 2, error, error_size)) return 0;
-    __nv_bfloat16 *q = (__nv_bfloat16 *)cuda->attn, *k = q + n, *v = k + n, *o = v + n;
+    const size_t n = seq * heads * head_dim, row = heads * head_dim;
+    __half *q, *k, *v, *o;
+    if (!stage4(cuda, n, &q, &k, &v, &o, error, error_size)) return 0;
     Timer t(cuda, sdpa_ms);
-    int ok = h3b_cast_dev(cuda, d_query, H3B_F32, q, H3B_BF16, n, error, error_size) &&
-             h3b_cast_dev(cuda, d_key, H3B_F32, k, H3B_BF16, n, error, error_size) &&
-             h3b_cast_dev(cuda, d_value, H3B_F32, v, H3B_BF16, n, error, error_size) &&
-             h3b_sdpa_bf16_dev(cuda, q, heads * head_dim, k, heads * head_dim, v, heads * head_dim, seq, seq, heads,
-                               head_dim, scale, o, heads * head_dim, error, error_size) &&
-             h3b_cast_dev(cuda, o, H3B_BF16, d_out, H3B_F32, n, error, error_size);
+    int ok = h3b_cast_dev(cuda, d_query, H3B_F32, q, H3B_F16, n, error, error_size) &&
+             h3b_cast_dev(cuda, d_key, H3B_F32, k, H3B_F16, n, error, error_size) &&
+             h3b_cast_dev(cuda, d_value, H3B_F32, v, H3B_F16, n, error, error_size) &&
+             launch_sdpa_f16(cuda, q, row, k, row, v, row, seq, seq, heads, head_dim, scale, o, row, error, error_size) &&
+             h3b_cast_dev(cuda, o, H3B_F16, d_out, H3B_F32, n, error, error_size);
     t.stop();
-    if (backend_out && backend_out_size) snprintf(backend_out, backend_out_size, "tcgen05_flash_bf16");
+    if (ok) g_last_backend = "tcgen05_flash_f16";
+    if (backend_out && backend_out_size) snprintf(backend_out, backend_out_size, "tcgen05_flash_f16");
     return ok;
 }
 
@@ -499,6 +540,8 @@ int h3_cuda_sdpa_f16_dev(h3_cuda *cuda, const float *d_query, const float *d_key
                                    0, error, error_size);
 }
 
+// The reference's f32 name runs an FP32 flash kernel; here it runs the f16 tensor-core kernel (f32 softmax and
+// accumulation, 11-bit operands): results agree with an f32 evaluation to about 5e-4 relative L2, not to f32 rounding.
 int h3_cuda_sdpa_f32_dev(h3_cuda *cuda, const float *d_query, const float *d_key, const float *d_value, size_t seq,
                          size_t heads, size_t head_dim, float scale, float *d_out, double *sdpa_ms, char *error,
                          size_t error_size) {
@@ -506,28 +549,190 @@ int h3_cuda_sdpa_f32_dev(h3_cuda *cuda, const float *d_query, const float *d_key
                                    0, error, error_size);
 }
 
+// Host tensors in and out (h3_gpu_cuda.h:562, :573, :610).
+static int sdpa_host(h3_cuda *cuda, const float *query, const float *key, const float *value, size_t seq, size_t heads,
+                     size_t head_dim, float scale, int attn_window, float *out, double *sdpa_ms, char *backend_out,
+                     size_t backend_out_size, char *error, size_t error_size) {
+    if (!cuda || !query || !key || !value || !out || !seq || !heads || !head_dim) return fail(error, error_size, "invalid sdpa args");
+    const size_t bytes = seq * heads * head_dim * sizeof(float);
+    float *d[4] = {NULL, NULL, NULL, NULL};
+    int ok = 1;
+    for (int i = 0; i < 4 && ok; i++)
+        if (cudaMalloc((void **)&d[i], bytes) != cudaSuccess) ok = fail(error, error_size, "sdpa: device staging failed");
+    const float *src[3] = {query, key, value};
+    for (int i = 0; i < 3 && ok; i++)
+        if (cudaMemcpyAsync(d[i], src[i], bytes, cudaMemcpyHostToDevice, cuda->op_stream) != cudaSuccess)
+            ok = fail(error, error_size, "sdpa: upload failed");
+    ok = ok && h3_cuda_sdpa_f16_dev_ex(cuda, d[0], d[1], d[2], seq, heads, head_dim, scale, attn_window, d[3], sdpa_ms, backend_out,
+                                       backend_out_size, error, error_size);
+    if (ok && (cudaMemcpyAsync(out, d[3], bytes, cudaMemcpyDeviceToHost, cuda->op_stream) != cudaSuccess ||
+               cudaStreamSynchronize(cuda->op_stream) != cudaSuccess))
+        ok = fail(error, error_size, "sdpa: download failed");
+    cudaStreamSynchronize(cuda->op_stream);
+    for (int i = 0; i < 4; i++)
+        if (d[i]) cudaFree(d[i]);
+    return ok;
+}
+int h3_cuda_sdpa_f16_ex(h3_cuda *cuda, const float *query, const float *key, const float *value, size_t seq, size_t heads,
+                        size_t head_dim, float scale, int attn_window, float *out, double *sdpa_ms, char *backend_out,
+                        size_t backend_out_size, char *error, size_t error_size) {
+    return sdpa_host(cuda, query, key, value, seq, heads, head_dim, scale, attn_window, out, sdpa_ms, backend_out,
+                     backend_out_size, error, error_size);
+}
+int h3_cuda_sdpa_f16(h3_cuda *cuda, const float *query, const float *key, const float *value, size_t seq, size_t heads,
+                     size_t head_dim, float scale, float *out, double *sdpa_ms, char *error, size_t error_size) {
+    return sdpa_host(cuda, query, key, value, seq, heads, head_dim, scale, 0, out, sdpa_ms, NULL, 0, error, error_size);
+}
+int h3_cuda_sdpa_f32(h3_cuda *cuda, const float *query, const float *key, const float *value, size_t seq, size_t heads,
+                     size_t head_dim, float scale, float *out, double *sdpa_ms, char *error, size_t error_size) {
+    return sdpa_host(cuda, query, key, value, seq, heads, head_dim, scale, 0, out, sdpa_ms, NULL, 0, error, error_size);
+}
+
+// ---- extra keys / values for the next QK-norm + RoPE + attention call (h3_gpu_cuda.h:815-819): a history of
+// post-RoPE f16 K / V rows [hist_n, heads, head_dim] appended to the current ones (queries stay `seq` long), and a
+// gather of chosen current K / V rows into caller buffers.  Process-wide, like the reference's.
+static const void *g_kvcat_k, *g_kvcat_v;
+static size_t g_kvcat_n;
+static void *g_kvsave_k, *g_kvsave_v;
+static const uint32_t *g_kvsave_idx;
+static size_t g_kvsave_n;
+
+void h3_cuda_sdpa_bind_kvcat(const void *d_k_hist, const void *d_v_hist, size_t hist_n) {
+    g_kvcat_k = d_k_hist;
+    g_kvcat_v = d_v_hist;
+    g_kvcat_n = hist_n;
+}
+void h3_cuda_sdpa_bind_kvsave(void *d_k_save, void *d_v_save, const uint32_t *d_idx, size_t save_n) {
+    g_kvsave_k = d_k_save;
+    g_kvsave_v = d_v_save;
+    g_kvsave_idx = d_idx;
+    g_kvsave_n = save_n;
+}
+void h3_cuda_sdpa_clear_kvext(void) {
+    g_kvcat_k = g_kvcat_v = NULL;
+    g_kvcat_n = 0;
+    g_kvsave_k = g_kvsave_v = NULL;
+    g_kvsave_idx = NULL;
+    g_kvsave_n = 0;
+}
+
+}  // extern "C"
+
+namespace h3b {
+// dst row r = src row idx[r]; rows are `row` f16 elements (a multiple of 8), moved 16 bytes per thread
+__global__ void k_gather_rows_f16(const __half *src, __half *dst, const uint32_t *idx, size_t n_idx, size_t row) {
+    const size_t vec = row / 8, total = n_idx * vec;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+        const size_t r = i / vec, c = i - r * vec;
+        reinterpret_cast<uint4 *>(dst + r * row)[c] = reinterpret_cast<const uint4 *>(src + (size_t)idx[r] * row)[c];
+    }
+}
+}  // namespace h3b
+
+extern "C" {
+
+// common tail of the four QK-norm + RoPE + attention entry points: q/k/v are f16 [seq, heads, 128] in the staging area
+static int rope_sdpa_tail(h3_cuda *cuda, __half *q, __half *k, __half *v, __half *o, size_t seq, size_t heads, size_t head_dim,
+                          float scale, float *d_attn_out, double *sdpa_ms, char *backend_out, size_t backend_out_size,
+                          char *error, size_t error_size) {
+    const size_t row = heads * head_dim, n = seq * row;
+    if (g_kvsave_n && g_kvsave_idx && g_kvsave_k && g_kvsave_v) {
+        const unsigned grid = (unsigned)std::min<size_t>(ceil_div(g_kvsave_n * row / 8, 256), (size_t)cuda->sm_count * 8);
+        k_gather_rows_f16<<<grid ? grid : 1, 256, 0, cuda->op_stream>>>(k, (__half *)g_kvsave_k, g_kvsave_idx, g_kvsave_n, row);
+        k_gather_rows_f16<<<grid ? grid : 1, 256, 0, cuda->op_stream>>>(v, (__half *)g_kvsave_v, g_kvsave_idx, g_kvsave_n, row);
+        cuda->launches += 2;
+        H3B_CUDA_OK(cudaGetLastError(), "kvsave gather");
+    }
+    Timer t(cuda, sdpa_ms);
+    int ok;
+    if (g_kvcat_n > 0 && g_kvcat_k && g_kvcat_v) {
+        // keys / values = [current | history] in one contiguous buffer, queries unchanged: rectangular attention
+        const size_t lk = seq + g_kvcat_n;
+        if (!grow(cuda, &cuda->kvx, &cuda->kvx_bytes, 2 * lk * row * sizeof(__half), error, error_size)) return 0;
+        __half *kc = (__half *)cuda->kvx, *vc = kc + lk * row;
+        cudaStream_t st = cuda->op_stream;
+        H3B_CUDA_OK(cudaMemcpyAsync(kc, k, n * sizeof(__half), cudaMemcpyDeviceToDevice, st), "kvcat K");
+        H3B_CUDA_OK(cudaMemcpyAsync(kc + n, g_kvcat_k, g_kvcat_n * row * sizeof(__half), cudaMemcpyDeviceToDevice, st), "kvcat K history");
+        H3B_CUDA_OK(cudaMemcpyAsync(vc, v, n * sizeof(__half), cudaMemcpyDeviceToDevice, st), "kvcat V");
+        H3B_CUDA_OK(cudaMemcpyAsync(vc + n, g_kvcat_v, g_kvcat_n * row * sizeof(__half), cudaMemcpyDeviceToDevice, st), "kvcat V history");
+        ok = launch_sdpa_f16(cuda, q, row, kc, row, vc, row, seq, lk, heads, head_dim, scale, o, row, error, error_size);
+    } else {
+        ok = launch_sdpa_f16(cuda, q, row, k, row, v, row, seq, seq, heads, head_dim, scale, o, row, error, error_size);
+    }
+    ok = ok && h3b_cast_dev(cuda, o, H3B_F16, d_attn_out, H3B_F32, n, error, error_size);
+    t.stop();
+    if (ok) g_last_backend = "tcgen05_flash_f16";
+    if (backend_out && backend_out_size) snprintf(backend_out, backend_out_size, "tcgen05_flash_f16");
+    return ok;
+}
+
+static int rope_sdpa(h3_cuda *cuda, const void *d_qkv, int in_dtype, const float *d_q_norm, const float *d_k_norm,
+                     const float *d_rope_cos, const float *d_rope_sin, size_t seq, size_t heads, size_t head_dim,
+                     size_t rope_half, float epsilon, float scale, int attn_window, int grouped, int split_half,
+                     float *d_attn_out, double *rope_ms, double *sdpa_ms, char *backend_out, size_t backend_out_size,
+                     char *error, size_t error_size) {
+    if (rope_ms) *rope_ms = 0.0;
+    if (sdpa_ms) *sdpa_ms = 0.0;
+    if (!cuda || !d_qkv || !d_attn_out || !seq || !heads || !head_dim) return fail(error, error_size, "invalid qkv_rope_sdpa args");
+    if (attn_window != 0) return fail(error, error_size, "sdpa: windowed attention (attn_window=%d) is not supported", attn_window);
+    const size_t n = seq * heads * head_dim;
+    __half *q, *k, *v, *o;
+    if (!stage4(cuda, n, &q, &k, &v, &o, error, error_size)) return 0;
+    Timer tr(cuda, rope_ms);
+    if (!h3b_qkv_rope_dev(cuda, d_qkv, in_dtype, d_q_norm, d_k_norm, d_rope_cos, d_rope_sin, seq, heads, head_dim, rope_half,
+                          epsilon, grouped, split_half, q, k, v, H3B_F16, error, error_size))
+        return 0;
+    tr.stop();
+    return rope_sdpa_tail(cuda, q, k, v, o, seq, heads, head_dim, scale, d_attn_out, sdpa_ms, backend_out, backend_out_size,
+                          error, error_size);
+}
+
+// layout defaults of the reference (h3_gpu_cuda.cu:54-69): contiguous [Q|K|V] thirds unless H3_DIT_QKV_GROUPED=1,
+// split-half RoPE pairing unless H3_DIT_ROPE_HALF_OFFSET=1 or H3_DIT_ROPE_SPLIT_HALF=0
+static int env_is(const char *name, char c) {
+    const char *e = getenv(name);
+    return e && e[0] == c && !e[1];
+}
+static int default_grouped(void) { return env_is("H3_DIT_QKV_GROUPED", '1'); }
+static int default_split_half(void) { return !(env_is("H3_DIT_ROPE_HALF_OFFSET", '1') || env_is("H3_DIT_ROPE_SPLIT_HALF", '0')); }
+
+int h3_cuda_qkv_rope_sdpa_f16_dev_layout(h3_cuda *cuda, const float *d_qkv, const float *d_q_norm, const float *d_k_norm,
+                                         const float *d_rope_cos, const float *d_rope_sin, size_t seq, size_t heads,
+                                         size_t head_dim, size_t rope_half, float epsilon, float scale, int attn_window,
+                                         int grouped, int split_half, float *d_attn_out, double *rope_ms, double *sdpa_ms,
+                                         char *backend_out, size_t backend_out_size, char *error, size_t error_size) {
+    return rope_sdpa(cuda, d_qkv, H3B_F32, d_q_norm, d_k_norm, d_rope_cos, d_rope_sin, seq, heads, head_dim, rope_half, epsilon,
+                     scale, attn_window, grouped, split_half, d_attn_out, rope_ms, sdpa_ms, backend_out, backend_out_size, error,
+                     error_size);
+}
 int h3_cuda_qkv_rope_sdpa_f16_dev(h3_cuda *cuda, const float *d_qkv, const float *d_q_norm, const float *d_k_norm,
                                   const float *d_rope_cos, const float *d_rope_sin, size_t seq, size_t heads,
                                   size_t head_dim, size_t rope_half, float epsilon, float scale, int attn_window,
                                   float *d_attn_out, double *rope_ms, double *sdpa_ms, char *backend_out,
                                   size_t backend_out_size, char *error, size_t error_size) {
-    if (!cuda || !d_qkv || !d_attn_out || !seq || !heads || !head_dim) return fail(error, error_size, "invalid qkv_rope_sdpa args");
-    if (attn_window != 0) return fail(error, error_size, "sdpa: windowed attention (attn_window=%d) is not supported", attn_window);
-    const size_t n = seq * heads * head_dim;
-    if (!grow(cuda, &cuda->attn, &cuda->attn_bytes, 4 * n * 2, error, error_size)) return 0;
-    __nv_bfloat16 *q = (__nv_bfloat16 *)cuda->attn, *k = q + n, *v = k + n, *o = v + n;
-    Timer tr(cuda, rope_ms);
-    if (!h3b_qkv_rope_dev(cuda, d_qkv, H3B_F32, d_q_norm, d_k_norm, d_rope_cos, d_rope_sin, seq, heads, head_dim,
-                          rope_half, epsilon, 0, 1, q, k, v, H3B_BF16, error, error_size))
-        return 0;
-    tr.stop();
-    Timer ts(cuda, sdpa_ms);
-    int ok = h3b_sdpa_bf16_dev(cuda, q, heads * head_dim, k, heads * head_dim, v, heads * head_dim, seq, seq, heads,
-                               head_dim, scale, o, heads * head_dim, error, error_size) &&
-             h3b_cast_dev(cuda, o, H3B_BF16, d_attn_out, H3B_F32, n, error, error_size);
-    ts.stop();
-    if (backend_out && backend_out_size) snprintf(backend_out, backend_out_size, "tcgen05_flash_bf16");
-    return ok;
+    return rope_sdpa(cuda, d_qkv, H3B_F32, d_q_norm, d_k_norm, d_rope_cos, d_rope_sin, seq, heads, head_dim, rope_half, epsilon,
+                     scale, attn_window, default_grouped(), default_split_half(), d_attn_out, rope_ms, sdpa_ms, backend_out,
+                     backend_out_size, error, error_size);
+}
+// the same with the QKV projection already stored as f16 (h3_gpu_cuda.h:779-793)
+int h3_cuda_qkv_rope_sdpa_f16_dev_layout_f16qkv(h3_cuda *cuda, const void *d_qkv_half, const float *d_q_norm,
+                                                const float *d_k_norm, const float *d_rope_cos, const float *d_rope_sin,
+                                                size_t seq, size_t heads, size_t head_dim, size_t rope_half, float epsilon,
+                                                float scale, int attn_window, int grouped, int split_half, float *d_attn_out,
+                                                double *rope_ms, double *sdpa_ms, char *backend_out, size_t backend_out_size,
+                                                char *error, size_t error_size) {
+    return rope_sdpa(cuda, d_qkv_half, H3B_F16, d_q_norm, d_k_norm, d_rope_cos, d_rope_sin, seq, heads, head_dim, rope_half,
+                     epsilon, scale, attn_window, grouped, split_half, d_attn_out, rope_ms, sdpa_ms, backend_out, backend_out_size,
+                     error, error_size);
+}
+int h3_cuda_qkv_rope_sdpa_f16_dev_f16qkv(h3_cuda *cuda, const void *d_qkv_half, const float *d_q_norm, const float *d_k_norm,
+                                         const float *d_rope_cos, const float *d_rope_sin, size_t seq, size_t heads,
+                                         size_t head_dim, size_t rope_half, float epsilon, float scale, int attn_window,
+                                         float *d_attn_out, double *rope_ms, double *sdpa_ms, char *backend_out,
+                                         size_t backend_out_size, char *error, size_t error_size) {
+    return rope_sdpa(cuda, d_qkv_half, H3B_F16, d_q_norm, d_k_norm, d_rope_cos, d_rope_sin, seq, heads, head_dim, rope_half,
+                     epsilon, scale, attn_window, default_grouped(), default_split_half(), d_attn_out, rope_ms, sdpa_ms,
+                     backend_out, backend_out_size, error, error_size);
 }
 
 }  // extern "C"

@@ -121,8 +121,8 @@ template <int BM>
 static void dense_launch_t(h3_cuda *cuda, bool vec, const float *d_x, const float *d_w, const float *d_bias, size_t m, size_t n,
                            size_t k, float *d_y, float alpha, float beta) {
     const dim3 grid((unsigned)((n + dense::BN - 1) / dense::BN), (unsigned)((m + BM - 1) / BM));
-    if (vec) k_dense_f32<BM, true><<<grid, BM * 4, 0, cuda->op_stream>>>(d_x, d_w, d_bias, m, n, k, d_y, alpha, beta);
-    else k_dense_f32<BM, false><<<grid, BM * 4, 0, cuda->op_stream>>>(d_x, d_w, d_bias, m, n, k, d_y, alpha, beta);
+    if (vec) k_dense_f32<BM, true><<<grid, BM * 4, 0, dense_stream(cuda)>>>(d_x, d_w, d_bias, m, n, k, d_y, alpha, beta);
+    else k_dense_f32<BM, false><<<grid, BM * 4, 0, dense_stream(cuda)>>>(d_x, d_w, d_bias, m, n, k, d_y, alpha, beta);
 }
 
 static int launch_dense(h3_cuda *cuda, const float *d_x, const float *d_w, const float *d_bias, size_t m, size_t n, size_t k,

@@ -25,6 +25,10 @@ struct h3_cuda {
     void *act_s;   size_t act_s_bytes;     // per-row activation scales
     void *act_rot; size_t act_rot_bytes;   // ConvRot output (f32)
     void *attn;    size_t attn_bytes;      // 16-bit Q/K/V/O staging for the f32 attention entry points
+    void *rq;      size_t rq_bytes;        // codes + scales handed out by h3_cuda_epi_fuse_ink_prep_fc2
+    void *kvx;     size_t kvx_bytes;       // K/V with bound history appended (h3_cuda_sdpa_bind_kvcat)
+    void *wtmp;    size_t wtmp_bytes;      // f32 copy of 16-bit weights (mixed-precision dense GEMM)
+    int blas_side;                         // f32 GEMMs run on side[1] (h3_cuda_cublas_use_side)
     int pregrown;
     // optional per-launch timing (h3b_cuda_profile_begin / _end)
     int prof_on, prof_n, prof_cap;
@@ -97,8 +101,14 @@ int launch_gemm_nvfp4(h3_cuda *cuda, const uint8_t *w_fp4, const uint8_t *sf_w, 
                       size_t m, size_t n, size_t k, float alpha, void *y, int out_dtype, int gate, const void *residual,
                       const float *mod, const uint32_t *row_map, size_t slots, size_t gate_slot, char *error,
                       size_t error_size);
+// stream the f32 dense GEMMs run on: the op stream, or side stream 1 while h3_cuda_cublas_use_side is on
+static inline cudaStream_t dense_stream(const h3_cuda *c) { return c->blas_side ? c->side[1] : c->op_stream; }
 int launch_sdpa_bf16(h3_cuda *cuda, const void *q, size_t qs, const void *k, size_t ks, const void *v, size_t vs,
                      size_t lq, size_t lk, size_t heads, size_t hd, float scale, void *out, size_t os,
                      char *error, size_t error_size);
+
+int launch_sdpa_f16(h3_cuda *cuda, const void *q, size_t qs, const void *k, size_t ks, const void *v, size_t vs,
+                    size_t lq, size_t lk, size_t heads, size_t hd, float scale, void *out, size_t os,
+                    char *error, size_t error_size);
 
 }  // namespace h3b

@@ -977,6 +977,8 @@ int h3b_qkv_rope_dev(h3_cuda *cuda, const void *d_qkv, int in_dtype, const float
     if (in_dtype == H3B_F32 && out_dtype == H3B_BF16) H3B_QR(float, __nv_bfloat16);
     if (in_dtype == H3B_BF16 && out_dtype == H3B_BF16) H3B_QR(__nv_bfloat16, __nv_bfloat16);
     if (in_dtype == H3B_BF16 && out_dtype == H3B_F32) H3B_QR(__nv_bfloat16, float);
+    if (in_dtype == H3B_F32 && out_dtype == H3B_F16) H3B_QR(float, __half);
+    if (in_dtype == H3B_F16 && out_dtype == H3B_F16) H3B_QR(__half, __half);
 #undef H3B_QR
     return fail(error, error_size, "qkv_rope: unsupported dtype pair %d -> %d", in_dtype, out_dtype);
 }

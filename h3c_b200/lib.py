@@ -218,6 +218,52 @@ _SIGS = {
     "h3_dit_w4a8_rope_tables_f32": (i32, (vp, sz, vp, vp, vp, f32, vp, vp) + _ERR),
     "h3_dit_w4a8_t_row_from_sigma": (sz, (f32, sz)),
     "h3b_dit_video_rope_tables": (i32, (vp, sz, i32, i32, i32, f32, sz, vp, vp) + _ERR),
+    # ---- the rest of the reference's operator surface
+    "h3_cuda_copy_stream_synchronize": (i32, (vp,) + _ERR),
+    "h3_cuda_cublas_use_side": (i32, (vp, i32) + _ERR),
+    "h3_cuda_cublas_stream": (vp, (vp,)),
+    "h3_cuda_recreate_blas": (i32, (vp,) + _ERR),
+    "h3_cuda_dit_scratch_rehome": (i32, (vp,) + _ERR),
+    "h3_cuda_dit_scratch_check": (i32, (vp,) + _ERR),
+    "h3_cuda_host_register": (i32, (vp, sz) + _ERR),
+    "h3_cuda_host_unregister": (None, (vp,)),
+    "h3_cuda_gemm_f32": (i32, (vp, vp, vp, sz, sz, sz, vp, dbl_p) + _ERR),
+    "h3_cuda_gemm_f32_dw": (i32, (vp, vp, vp, sz, sz, sz, vp, dbl_p) + _ERR),
+    "h3_cuda_gemm_f32in_f16w_f32out_dd_ex": (i32, (vp, vp, vp, sz, sz, sz, vp, f32, f32) + _ERR),
+    "h3_cuda_convrot_act_f16_dd": (i32, (vp, vp, sz, sz, i32, vp) + _ERR),
+    "h3_cuda_epi_fuse_ink_prep_fc2": (i32, (vp, vp, sz, sz, i32, C.POINTER(vp), C.POINTER(vp)) + _ERR),
+    "h3_cutlass_nvfp4_fc1_f32_run": (i32, (vp, vp, vp, vp, vp, sz, sz, sz, vp, dbl_p) + _ERR),
+    "h3_nvfp4_swiglu_requant_dev": (i32, (vp, vp, f32, vp, sz, sz, vp, vp) + _ERR),
+    "h3_cuda_nvfp4_chain_scratch_bytes": (sz, (sz, sz, sz)),
+    "h3_cuda_gemm_fp4_pre_q_dev": (i32, (vp, vp, vp, vp, sz, vp, vp, vp, sz, sz, vp, vp, vp, dbl_p) + _ERR + (cs,)),
+    "h3_nvfp4_debug_nan_dev": (i32, ()),
+    "h3_nvfp4_debug_scan_dev": (None, (vp, vp, sz, cs, cs, cs)),
+    "h3_cuda_sdpa_f32": (i32, (vp, vp, vp, vp, sz, sz, sz, f32, vp, dbl_p) + _ERR),
+    "h3_cuda_sdpa_f16": (i32, (vp, vp, vp, vp, sz, sz, sz, f32, vp, dbl_p) + _ERR),
+    "h3_cuda_sdpa_f16_ex": (i32, (vp, vp, vp, vp, sz, sz, sz, f32, i32, vp, dbl_p, cs, sz) + _ERR),
+    "h3_cuda_qkv_rope_sdpa_f16_dev_layout": (i32, (vp, vp, vp, vp, vp, vp, sz, sz, sz, sz, f32, f32, i32, i32, i32, vp,
+                                                   dbl_p, dbl_p, cs, sz) + _ERR),
+    "h3_cuda_qkv_rope_sdpa_f16_dev_layout_f16qkv": (i32, (vp, vp, vp, vp, vp, vp, sz, sz, sz, sz, f32, f32, i32, i32, i32,
+                                                          vp, dbl_p, dbl_p, cs, sz) + _ERR),
+    "h3_cuda_qkv_rope_sdpa_f16_dev_f16qkv": (i32, (vp, vp, vp, vp, vp, vp, sz, sz, sz, sz, f32, f32, i32, vp, dbl_p, dbl_p,
+                                                   cs, sz) + _ERR),
+    "h3_cuda_sdpa_bind_kvcat": (None, (vp, vp, sz)),
+    "h3_cuda_sdpa_bind_kvsave": (None, (vp, vp, vp, sz)),
+    "h3_cuda_sdpa_clear_kvext": (None, ()),
+    "h3_cuda_token_pool_f32": (i32, (vp, vp, sz, vp, vp, sz, sz, sz, vp, C.POINTER(vp), C.POINTER(vp), dbl_p) + _ERR),
+    "h3_cuda_token_expand_f32": (i32, (vp, vp, vp, vp, vp, vp, sz, sz, sz, sz, C.c_uint32, C.c_uint32, f32, vp, dbl_p) + _ERR),
+    "h3_cuda_token_pool_f32_dev": (i32, (vp, vp, sz, vp, vp, sz, sz, sz, vp, vp, vp, dbl_p) + _ERR),
+    "h3_cuda_token_expand_f32_dev": (i32, (vp, vp, vp, vp, vp, vp, sz, sz, sz, sz, C.c_uint32, C.c_uint32, f32, vp, dbl_p) + _ERR),
+    "h3_cuda_dist_attn_configure": (i32, (vp, sz, sz, sz, i32, i32, i32, f32, f32, i32) + _ERR),
+    "h3_cuda_dist_attn_clear": (None, ()),
+    "h3_cuda_dist_attn_active": (i32, ()),
+    "h3_cuda_sol_cute_set_step": (None, (i32,)),
+    "h3_cuda_sol_profile_add_unpack": (None, (C.c_double,)),
+    "h3_cuda_sage3_pool_bytes": (sz, ()),
+    "h3_nvfp4_cuda_enabled": (i32, ()),
+    "h3_nvfp4_cuda_cache_clear": (None, ()),
+    "h3_nvfp4_cuda_encode_text_layers": (i32, (vp, vp, sz, C.c_uint) + _ERR),
+    "h3_nvfp4_cuda_gqa_causal": (i32, (vp, vp, vp, sz, sz, sz, sz, vp) + _ERR),
     "h3_ulysses_validate": (i32, (i32, i32, i32, i32, i32) + _ERR),
     "h3_ulysses_pad_seq": (sz, (sz, i32)),
     "h3_ulysses_local_rows": (sz, (sz, i32, i32)),

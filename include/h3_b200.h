@@ -493,6 +493,123 @@ int h3b_gemm_fp4_dev(h3_cuda *cuda, const uint8_t *d_w_fp4, const uint8_t *d_sf_
                      const uint8_t *d_sf_x, size_t m, size_t n, size_t k, float alpha, void *d_y,
                      int out_dtype, char *error, size_t error_size);
 
+/* ------------------------------------------- the rest of the reference's operator surface
+ * Everything below keeps the reference's name and signature (h3_gpu_cuda.h line cited per entry) so that the
+ * reference's own DiT host (h3_dit_w4a8.c) links against this library without a change. */
+
+/* housekeeping */
+int h3_cuda_copy_stream_synchronize(h3_cuda *cuda, char *error, size_t error_size);                 /* :334 */
+/* moves the f32 dense GEMMs (LoRA deltas) onto side stream 1 / back to the op stream */
+int h3_cuda_cublas_use_side(h3_cuda *cuda, int on, char *error, size_t error_size);                  /* :220 */
+void *h3_cuda_cublas_stream(const h3_cuda *cuda);                                                    /* :223 */
+int h3_cuda_recreate_blas(h3_cuda *cuda, char *error, size_t error_size);                            /* :60 */
+int h3_cuda_dit_scratch_rehome(h3_cuda *cuda, char *error, size_t error_size);                       /* :58 */
+int h3_cuda_dit_scratch_check(h3_cuda *cuda, char *error, size_t error_size);                        /* :59 */
+int h3_cuda_host_register(void *p, size_t bytes, char *error, size_t error_size);                    /* :321 */
+void h3_cuda_host_unregister(void *p);                                                               /* :322 */
+
+/* f32 GEMM y = x W^T with host x / host or device W (:91, :115), and with f16 weights + alpha/beta (:183) */
+int h3_cuda_gemm_f32(h3_cuda *cuda, const float *x, const float *weight, size_t m, size_t n, size_t k, float *y,
+                     double *gemm_ms, char *error, size_t error_size);
+int h3_cuda_gemm_f32_dw(h3_cuda *cuda, const float *x, const float *d_weight, size_t m, size_t n, size_t k, float *y,
+                        double *gemm_ms, char *error, size_t error_size);
+int h3_cuda_gemm_f32in_f16w_f32out_dd_ex(h3_cuda *cuda, const float *d_x_f32, const void *d_w_h, size_t m, size_t n,
+                                         size_t k, float *d_y_f32, float alpha, float beta, char *error,
+                                         size_t error_size);
+
+/* ConvRot on f16 activations (:149); ConvRot + per-row INT8 into library scratch for a following _dev_pre_q
+ * GEMM (:143): *out_xi8 [ceil128(m), k], *out_scales [ceil128(m)], valid until the next call that grows it */
+int h3_cuda_convrot_act_f16_dd(h3_cuda *cuda, const void *d_x_half, size_t m, size_t k, int convrot_groupsize,
+                               void *d_y_half, char *error, size_t error_size);
+int h3_cuda_epi_fuse_ink_prep_fc2(h3_cuda *cuda, const float *d_swiglu, size_t m, size_t k, int convrot_groupsize,
+                                  int8_t **out_xi8, float **out_scales, char *error, size_t error_size);
+
+/* NVFP4 FC1 -> SwiGLU -> requantise -> FC2 chain (:519-549).  _fc1_f32_run: block-scaled GEMM with the f32
+ * accumulators written out [m, n]; _swiglu_requant: silu(acc_scale * gate (+lora)) * (acc_scale * up (+lora)) ->
+ * E2M1 + UE4M3 scales in the layout of h3_cuda_quantize_act_nvfp4_dev; _pre_q: FC2 on those codes with the gate +
+ * residual epilogue (d_bf16_scratch is not used, d_lora must be NULL). */
+int h3_cutlass_nvfp4_fc1_f32_run(h3_cuda *cuda, const uint8_t *d_w_fp4, const uint8_t *d_sf_w, const uint8_t *d_x_fp4,
+                                 const uint8_t *d_sf_x, size_t m, size_t n, size_t k, float *d_acc_f32, double *gemm_ms,
+                                 char *error, size_t error_size);
+int h3_nvfp4_swiglu_requant_dev(h3_cuda *cuda, const float *d_acc_f32, float acc_scale, const float *d_lora, size_t m,
+                                size_t ffn, uint8_t *d_act_fp4, uint8_t *d_sf_act, char *error, size_t error_size);
+size_t h3_cuda_nvfp4_chain_scratch_bytes(size_t m, size_t kdim, size_t ffn);
+int h3_cuda_gemm_fp4_pre_q_dev(h3_cuda *cuda, const h3_cuda_nvfp4_weight *weight, const uint8_t *d_x_fp4,
+                               const uint8_t *d_sf_x, size_t m, const float *d_residual, const float *d_modulation,
+                               const uint32_t *d_row_map, size_t slots, size_t gate_slot, const float *d_lora,
+                               float *d_y_f32, void *d_bf16_scratch, double *gemm_ms, char *error, size_t error_size,
+                               const char *tag);
+int h3_nvfp4_debug_nan_dev(void);                                                                    /* :554 */
+void h3_nvfp4_debug_scan_dev(h3_cuda *cuda, const void *ptr, size_t n, const char *kind, const char *tag,
+                             const char *stage);                                                     /* :555 */
+
+/* attention: host-tensor forms (:562, :573, :610), explicit-layout and f16-QKV forms of QK-norm + RoPE +
+ * attention (:779-801), history keys / values appended to the next such call and a gather of current K / V rows
+ * (:815-819, f16 [rows, heads, head_dim]) */
+int h3_cuda_sdpa_f32(h3_cuda *cuda, const float *query, const float *key, const float *value, size_t seq, size_t heads,
+                     size_t head_dim, float scale, float *out, double *sdpa_ms, char *error, size_t error_size);
+int h3_cuda_sdpa_f16(h3_cuda *cuda, const float *query, const float *key, const float *value, size_t seq, size_t heads,
+                     size_t head_dim, float scale, float *out, double *sdpa_ms, char *error, size_t error_size);
+int h3_cuda_sdpa_f16_ex(h3_cuda *cuda, const float *query, const float *key, const float *value, size_t seq, size_t heads,
+                        size_t head_dim, float scale, int attn_window, float *out, double *sdpa_ms, char *backend_out,
+                        size_t backend_out_size, char *error, size_t error_size);
+int h3_cuda_qkv_rope_sdpa_f16_dev_layout(h3_cuda *cuda, const float *d_qkv, const float *d_q_norm, const float *d_k_norm,
+                                         const float *d_rope_cos, const float *d_rope_sin, size_t seq, size_t heads,
+                                         size_t head_dim, size_t rope_half, float epsilon, float scale, int attn_window,
+                                         int grouped, int split_half, float *d_attn_out, double *rope_ms, double *sdpa_ms,
+                                         char *backend_out, size_t backend_out_size, char *error, size_t error_size);
+int h3_cuda_qkv_rope_sdpa_f16_dev_layout_f16qkv(h3_cuda *cuda, const void *d_qkv_half, const float *d_q_norm,
+                                                const float *d_k_norm, const float *d_rope_cos, const float *d_rope_sin,
+                                                size_t seq, size_t heads, size_t head_dim, size_t rope_half, float epsilon,
+                                                float scale, int attn_window, int grouped, int split_half, float *d_attn_out,
+                                                double *rope_ms, double *sdpa_ms, char *backend_out, size_t backend_out_size,
+                                                char *error, size_t error_size);
+int h3_cuda_qkv_rope_sdpa_f16_dev_f16qkv(h3_cuda *cuda, const void *d_qkv_half, const float *d_q_norm, const float *d_k_norm,
+                                         const float *d_rope_cos, const float *d_rope_sin, size_t seq, size_t heads,
+                                         size_t head_dim, size_t rope_half, float epsilon, float scale, int attn_window,
+                                         float *d_attn_out, double *rope_ms, double *sdpa_ms, char *backend_out,
+                                         size_t backend_out_size, char *error, size_t error_size);
+void h3_cuda_sdpa_bind_kvcat(const void *d_k_hist, const void *d_v_hist, size_t hist_n);
+void h3_cuda_sdpa_bind_kvsave(void *d_k_save, void *d_v_save, const uint32_t *d_idx, size_t save_n);
+void h3_cuda_sdpa_clear_kvext(void);
+
+/* token reduction (:827-858): pool pairs of rows, expand back with the delta against a baseline */
+int h3_cuda_token_pool_f32(h3_cuda *cuda, const float *input, size_t full_rows, const uint32_t *pairs,
+                           const uint32_t *baseline_idx, size_t reduced_rows, size_t baseline_rows, size_t width,
+                           float *output, float **d_original_out, float **d_baseline_out, double *op_ms, char *error,
+                           size_t error_size);
+int h3_cuda_token_expand_f32(h3_cuda *cuda, const float *d_original, const float *reduced, const float *d_baseline,
+                             const uint32_t *baseline_idx, const uint32_t *parents, size_t full_rows, size_t reduced_rows,
+                             size_t baseline_rows, size_t width, uint32_t video_start, uint32_t video_rows,
+                             float update_scale, float *output, double *op_ms, char *error, size_t error_size);
+int h3_cuda_token_pool_f32_dev(h3_cuda *cuda, const float *d_input, size_t full_rows, const uint32_t *pairs,
+                               const uint32_t *baseline_idx, size_t reduced_rows, size_t baseline_rows, size_t width,
+                               float *d_output, float *d_original, float *d_baseline, double *op_ms, char *error,
+                               size_t error_size);
+int h3_cuda_token_expand_f32_dev(h3_cuda *cuda, const float *d_original, const float *d_reduced, const float *d_baseline,
+                                 const uint32_t *baseline_idx, const uint32_t *parents, size_t full_rows,
+                                 size_t reduced_rows, size_t baseline_rows, size_t width, uint32_t video_start,
+                                 uint32_t video_rows, float update_scale, float *d_output, double *op_ms, char *error,
+                                 size_t error_size);
+
+/* optional features of the reference that this library does not have: switching them on is refused with
+ * "... not supported by libh3_b200", everything else is a harmless success (:590-595, :653, :685, :689;
+ * h3_nvfp4_cuda.h:26-44 for the text encoder's four) */
+int h3_cuda_dist_attn_configure(h3_cuda *cuda, size_t seq, size_t video_start, size_t video_seq, int grid_t, int grid_h,
+                                int grid_w, float scale, float temporal_weight, int enabled, char *error,
+                                size_t error_size);
+void h3_cuda_dist_attn_clear(void);
+int h3_cuda_dist_attn_active(void);
+void h3_cuda_sol_cute_set_step(int step);
+void h3_cuda_sol_profile_add_unpack(double ms);
+size_t h3_cuda_sage3_pool_bytes(void);
+int h3_nvfp4_cuda_enabled(void);
+void h3_nvfp4_cuda_cache_clear(void);
+int h3_nvfp4_cuda_encode_text_layers(const void *store, float *hidden, size_t tokens, unsigned n_layers, char *error,
+                                     size_t error_size);
+int h3_nvfp4_cuda_gqa_causal(const float *q, const float *k, const float *v, size_t tokens, size_t q_heads, size_t kv_heads,
+                             size_t head_dim, float *out, char *error, size_t error_size);
+
 /* ---------------------------------------------------------- DiT block / chain */
 
 /* Additions.  The reference's block-level entry points (h3_dit_w4a8.h:527

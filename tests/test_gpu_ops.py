@@ -379,7 +379,7 @@ def test_reference_sdpa_entry_point(cuda, oracle):
     q, k, v = (rng.normal(0, 1, (seq, heads, hd)).astype(np.float32) for _ in range(3))
     out = cuda.sdpa_f16_dev(dev(q), dev(k), dev(v))
     cuda.check()
-    assert rel_l2(host(out), oracle.sdpa(q, k, v)) < 1e-2  # inputs rounded to bf16 as well
+    assert rel_l2(host(out), oracle.sdpa(q, k, v)) < 1e-3  # f16 staging like the reference: 11-bit operands, f32 accumulation
 
 
 # --------------------------------------------------------------------- NVFP4

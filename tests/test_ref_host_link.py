@@ -1,0 +1,50 @@
+"""Drop-in check on the CPU: the reference's UNMODIFIED DiT host (h3_dit_w4a8.c and the weight-format files
+beneath it, compiled from the reference sources where they lie) links against libh3_b200.so in place of the
+reference's CUDA operator library with no undefined symbol left."""
+import subprocess
+from pathlib import Path
+
+import pytest
+
+ROOT = Path(__file__).resolve().parent.parent
+REF_OUT = ROOT / "oracle" / "_ref"
+GPU_PREFIXES = ("h3_cuda_", "h3_nvfp4_", "h3_cutlass_", "h3_ulysses_")
+
+
+def _symbols(args):
+    out = subprocess.run(["nm"] + args, capture_output=True, text=True, check=True).stdout
+    return {line.split()[-1] for line in out.splitlines() if line.strip()}
+
+
+@pytest.fixture(scope="module")
+def product_lib():
+    from h3c_b200 import build
+    return build.build()
+
+
+def test_every_gpu_entry_point_the_reference_host_imports_is_exported(product_lib):
+    names = ("h3_dit_w4a8", "h3_w4a8_cache", "h3_w4a8_dequant", "h3_w4a8", "h3_safetensors", "h3_dit_int8", "h3_dit_nvfp4",
+             "h3_nvfp4", "h3_lora", "h3_sdpa_registry", "h3_cuda_device_caps")
+    objs = [str(REF_OUT / f"{n}.o") for n in names]
+    if not all(Path(o).exists() for o in objs):
+        pytest.skip("reference host objects not built (reference tree absent)")
+    own = _symbols(["--defined-only"] + objs)          # what the host files define among themselves
+    wanted = {s for s in _symbols(["-u"] + objs) if s.startswith(GPU_PREFIXES)} - own
+    assert len(wanted) > 80          # the host calls about ninety operator-level entry points
+    exported = _symbols(["-D", "--defined-only", str(product_lib)])
+    assert not sorted(wanted - exported), f"undefined for the reference host: {sorted(wanted - exported)}"
+
+
+def test_reference_host_links_with_no_undefined_symbol(product_lib):
+    import importlib.util
+    import os
+    spec = importlib.util.spec_from_file_location("_h3_oracle_build", ROOT / "oracle" / "build.py")
+    ob = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(ob)
+    ref_root = Path(os.environ.get("H3_REFERENCE_ROOT", "/root/reference"))
+    lib = ob.build_ref_host(ref_root, product_lib, force=True)      # links with -Wl,-z,defs: raises on any gap
+    if lib is None:
+        pytest.skip("reference host objects not built (reference tree absent)")
+    assert lib.exists()
+    needed = subprocess.run(["readelf", "-d", str(lib)], capture_output=True, text=True, check=True).stdout
+    assert "libh3_b200.so" in needed
