@@ -272,7 +272,7 @@ def gpu_arm(args):
         dist.broadcast(uid, 0)
         comm = h3c_b200.UlyssesComm(rank, world, bytes(uid.cpu().numpy().tobytes()), local)
         comm.set_compute(torch.cuda.current_stream())
-        if os.environ.get("H3B_ULYSSES_DIRECT", "1") != "0":
+        if h3c_b200.plugin_enabled("H3B_ULYSSES_DIRECT"):
             # peers' Q/K/V and attention-row buffers mapped into this rank: the epilogues store across NVLink.
             # If the mapping fails on any rank (no peer access), every rank falls back to the NCCL exchange.
             ok = torch.ones(1, dtype=torch.int32, device="cuda")

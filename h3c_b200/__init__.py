@@ -396,6 +396,28 @@ def ulysses_local_rows(seq_pad, ulysses, rank):
     return int(load().h3_ulysses_local_rows(seq_pad, ulysses, rank))
 
 
+def plugin_value(name: str):
+    """Value of a registered switch (environment, else its default); raises for an unregistered name."""
+    v = load().h3b_plugin_value(name.encode())
+    if v is None:
+        raise H3Error(f"switch {name} is not in the registry (include/h3b_plugin.h)")
+    return v.decode()
+
+
+def plugin_enabled(name: str) -> bool:
+    plugin_value(name)
+    return bool(load().h3b_plugin_enabled(name.encode()))
+
+
+def plugin_catalogue():
+    out = []
+    n, s, g, d = (C.c_char_p() for _ in range(4))
+    for i in range(load().h3b_plugin_count()):
+        load().h3b_plugin_get(i, C.byref(n), C.byref(s), C.byref(g), C.byref(d))
+        out.append((n.value.decode(), s.value.decode(), g.value.decode(), d.value.decode()))
+    return out
+
+
 def fill_video_pos(text_len, latent_t, latent_h, latent_w):
     """RoPE coordinates (t, h, w) of the video tokens (h3_dit_w4a8_fill_metal_video_pos); host arrays."""
     import numpy as np

@@ -17,6 +17,7 @@ HERE = Path(__file__).resolve().parent
 CSRC = HERE / "csrc"
 OBJ = HERE / "_obj"
 LIB = HERE / "libh3_b200.so"
+SDPA_PLUGIN = HERE / "libh3_b200_sdpa.so"   # the attention kernel behind the reference's dlopen plugin ABI
 
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "-Xcompiler", "-fPIC"]
@@ -57,6 +58,13 @@ def build(force: bool = False) -> Path:
         objs = list(ex.map(lambda s: _compile(s, hdr, force), cu + c))
     if force or _stale(LIB, objs):
         cmd = ["nvcc", "-shared", "-o", str(LIB)] + [str(o) for o in objs] + ["-lpthread", "-ldl", "-Xlinker", "-Bsymbolic"]
+        res = subprocess.run(cmd, capture_output=True, text=True)
+        if res.returncode != 0:
+            raise RuntimeError(f"{' '.join(cmd)}\n{res.stdout}{res.stderr}")
+    plugin_src = CSRC / "plugin" / "h3b_sdpa_plugin.c"
+    if force or _stale(SDPA_PLUGIN, [plugin_src, LIB] + hdr):
+        cmd = ["gcc"] + GCC_FLAGS + ["-shared", "-I/usr/local/cuda/include", str(plugin_src), "-o", str(SDPA_PLUGIN),
+                                     f"-L{HERE}", "-lh3_b200", "-Wl,-rpath,$ORIGIN", "-L/usr/local/cuda/lib64", "-lcudart"]
         res = subprocess.run(cmd, capture_output=True, text=True)
         if res.returncode != 0:
             raise RuntimeError(f"{' '.join(cmd)}\n{res.stdout}{res.stderr}")

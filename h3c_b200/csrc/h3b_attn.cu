@@ -48,7 +48,7 @@ constexpr size_t SMEM_BYTES = 1024 + 6 * (size_t)TILE + 256;
 struct AttnParams {
     CUtensorMap tmap_q, tmap_k, tmap_v;   // 3-D {d, head, row}, box {64, 1, 128}
     void *out;                            // 16-bit elements of the kernel's type
-    size_t o_stride;                      // elements between output rows
+    size_t o_stride, o_head_stride;       // elements between output rows / between heads of a row
     int lq, lk, heads;
     float scale_log2;                     // scale * log2(e)
     int *status;
@@ -83,6 +83,37 @@ __device__ __forceinline__ float ex2_approx(float x) {
     return y;
 }
 
+// 2^x for two values on the FMA pipe instead of the special-function unit (which is the unit the softmax
+// saturates: 16 results per clock and SM against 128 FMA lanes).  x is clamped to >= -127, split into
+// floor and fraction by adding 1.5 * 2^23 with round-down (the floor lands in the low mantissa bits), the
+// fraction goes through a degree-3 minimax polynomial (relative error 8.6e-5, far below the rounding of the
+// probabilities to 16 bits) and the floor is added to the exponent field.  Packed two-wide f32 instructions.
+__device__ __forceinline__ void ex2_emu2(float &p0, float &p1, float x0, float x1) {
+    x0 = fmaxf(x0, -127.0f);
+    x1 = fmaxf(x1, -127.0f);
+    uint32_t r0, r1, q0, q1;
+    asm("{\n\t.reg .b64 x, m, r, b, f, p, c;\n\t"
+        "mov.b64 x, {%4, %5};\n\t"
+        "mov.b64 m, {%6, %6};\n\t"
+        "add.rm.ftz.f32x2 r, x, m;\n\t"
+        "sub.rn.ftz.f32x2 b, r, m;\n\t"
+        "sub.rn.ftz.f32x2 f, x, b;\n\t"
+        "mov.b64 p, {%7, %7};\n\t"
+        "mov.b64 c, {%8, %8};\n\t"
+        "fma.rn.ftz.f32x2 p, p, f, c;\n\t"
+        "mov.b64 c, {%9, %9};\n\t"
+        "fma.rn.ftz.f32x2 p, p, f, c;\n\t"
+        "mov.b64 c, {%10, %10};\n\t"
+        "fma.rn.ftz.f32x2 p, p, f, c;\n\t"
+        "mov.b64 {%0, %1}, r;\n\t"
+        "mov.b64 {%2, %3}, p;\n\t}"
+        : "=r"(r0), "=r"(r1), "=r"(q0), "=r"(q1)
+        : "f"(x0), "f"(x1), "f"(12582912.0f), "f"(0.07706703990697861f), "f"(0.22764499485492706f),
+          "f"(0.6951167583465576f), "f"(1.0f));
+    p0 = __uint_as_float(q0 + (r0 << 23));
+    p1 = __uint_as_float(q1 + (r1 << 23));
+}
+
 // max of three (one instruction on sm_100)
 __device__ __forceinline__ float max3(float a, float b, float c) {
     float d;
@@ -105,7 +136,8 @@ __device__ __forceinline__ void add2(float &d0, float &d1, float a0, float a1) {
         : "f"(a0), "f"(a1));
 }
 
-template <typename T>
+// EMU: bit q set = the q-th group of four probabilities of every 32 is computed by ex2_emu2 instead of ex2.approx
+template <typename T, uint32_t EMU>
 __global__ void __launch_bounds__(attn::THREADS, 1) k_attn(const __grid_constant__ AttnParams p) {
     using namespace attn;
     extern __shared__ uint8_t smem_raw[];
@@ -326,7 +358,13 @@ __global__ void __launch_bounds__(attn::THREADS, 1) k_attn(const __grid_constant
                     float x0, x1, x2, x3;
                     fma2(x0, x1, __uint_as_float(sv[ch * 32 + i]), __uint_as_float(sv[ch * 32 + i + 1]), p.scale_log2, neg_m);
                     fma2(x2, x3, __uint_as_float(sv[ch * 32 + i + 2]), __uint_as_float(sv[ch * 32 + i + 3]), p.scale_log2, neg_m);
-                    const float p0 = ex2_approx(x0), p1 = ex2_approx(x1), p2 = ex2_approx(x2), p3 = ex2_approx(x3);
+                    float p0, p1, p2, p3;
+                    if ((EMU >> (i >> 2)) & 1u) {
+                        ex2_emu2(p0, p1, x0, x1);
+                        ex2_emu2(p2, p3, x2, x3);
+                    } else {
+                        p0 = ex2_approx(x0); p1 = ex2_approx(x1); p2 = ex2_approx(x2); p3 = ex2_approx(x3);
+                    }
                     add2(l0, l1, p0, p1);
                     add2(l2, l3, p2, p3);
                     packed[i >> 1] = Elem<T>::pack(p0, p1);
@@ -381,7 +419,7 @@ __global__ void __launch_bounds__(attn::THREADS, 1) k_attn(const __grid_constant
                         dst = reinterpret_cast<T *>(p.sc_out[owner < 8 ? owner : 0]) +
                               ((size_t)(row - owner * p.sc_rows) * p.sc_heads + p.sc_head0 + head) * HD;
                     } else {
-                        dst = reinterpret_cast<T *>(p.out) + (size_t)row * p.o_stride + (size_t)head * HD;
+                        dst = reinterpret_cast<T *>(p.out) + (size_t)row * p.o_stride + (size_t)head * p.o_head_stride;
                     }
                     *reinterpret_cast<uint4 *>(dst + chunk * 8) = *reinterpret_cast<const uint4 *>(stg + rr * STG_ROW + chunk * 16);
                 }
@@ -397,18 +435,23 @@ __global__ void __launch_bounds__(attn::THREADS, 1) k_attn(const __grid_constant
     }
 }
 
-static int make_map(CUtensorMap *map, const void *base, size_t stride_elems, size_t rows, size_t heads, int f16, char *error,
-                    size_t error_size, const char *what) {
+static int make_map(CUtensorMap *map, const void *base, size_t stride_elems, size_t head_stride_elems, size_t rows,
+                    size_t heads, int f16, char *error, size_t error_size, const char *what) {
     int rc = h3b_encode_tmap_3d(map, f16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, base,
                                 attn::HD, heads, rows,
-                                attn::HD * 2, stride_elems * 2, 64, 1, 128, CU_TENSOR_MAP_SWIZZLE_128B);
+                                head_stride_elems * 2, stride_elems * 2, 64, 1, 128, CU_TENSOR_MAP_SWIZZLE_128B);
     if (rc != 0) return fail(error, error_size, "sdpa: cuTensorMapEncodeTiled(%s) failed (%d)", what, rc);
     return 1;
 }
 
+// distances between heads of one row, in elements (0 = heads are contiguous, head_dim apart)
+struct HeadStrides {
+    size_t q = 0, k = 0, v = 0, o = 0;
+};
 static int launch_sdpa_impl(h3_cuda *cuda, const void *q, size_t qs, const void *k, size_t ks, const void *v, size_t vs,
                             size_t lq, size_t lk, size_t heads, size_t hd, float scale, void *out, size_t os,
-                            const h3b_ulysses_direct *sc, int f16, char *error, size_t error_size);
+                            const h3b_ulysses_direct *sc, int f16, char *error, size_t error_size,
+                            HeadStrides hs = HeadStrides());
 
 int launch_sdpa_bf16(h3_cuda *cuda, const void *q, size_t qs, const void *k, size_t ks, const void *v, size_t vs,
                      size_t lq, size_t lk, size_t heads, size_t hd, float scale, void *out, size_t os, char *error,
@@ -423,23 +466,29 @@ int launch_sdpa_f16(h3_cuda *cuda, const void *q, size_t qs, const void *k, size
 
 static int launch_sdpa_impl(h3_cuda *cuda, const void *q, size_t qs, const void *k, size_t ks, const void *v, size_t vs,
                             size_t lq, size_t lk, size_t heads, size_t hd, float scale, void *out, size_t os,
-                            const h3b_ulysses_direct *sc, int f16, char *error, size_t error_size) {
+                            const h3b_ulysses_direct *sc, int f16, char *error, size_t error_size, HeadStrides hs) {
     if (!cuda || !q || !k || !v || !out || !lq || !lk || !heads) return fail(error, error_size, "invalid sdpa args");
     if (hd != attn::HD) return fail(error, error_size, "sdpa: head_dim %zu unsupported (128 only)", hd);
     if ((qs % 8) || (ks % 8) || (vs % 8) || (os % 8) || ((uintptr_t)q & 15) || ((uintptr_t)k & 15) ||
         ((uintptr_t)v & 15) || ((uintptr_t)out & 15))
         return fail(error, error_size, "sdpa: pointers must be 16-byte aligned and row strides multiples of 8 elements");
-    if (qs < heads * hd || ks < heads * hd || vs < heads * hd || os < heads * hd)
+    const bool packed = !hs.q && !hs.k && !hs.v && !hs.o;
+    if (packed && (qs < heads * hd || ks < heads * hd || vs < heads * hd || os < heads * hd))
         return fail(error, error_size, "sdpa: row stride smaller than heads*head_dim");
+    if (!hs.q) hs.q = hd;
+    if (!hs.k) hs.k = hd;
+    if (!hs.v) hs.v = hd;
+    if (!hs.o) hs.o = hd;
+    if ((hs.q | hs.k | hs.v | hs.o) % 8) return fail(error, error_size, "sdpa: head strides must be multiples of 8 elements");
     if (lq > 0x7fffff00u || lk > 0x7fffff00u || heads > 65535) return fail(error, error_size, "sdpa: shape too large");
     if (!(scale > 0.0f)) return fail(error, error_size, "sdpa: scale must be positive");
     AttnParams p;
     memset(&p, 0, sizeof(p));
-    if (!make_map(&p.tmap_q, q, qs, lq, heads, f16, error, error_size, "Q") ||
-        !make_map(&p.tmap_k, k, ks, lk, heads, f16, error, error_size, "K") ||
-        !make_map(&p.tmap_v, v, vs, lk, heads, f16, error, error_size, "V"))
+    if (!make_map(&p.tmap_q, q, qs, hs.q, lq, heads, f16, error, error_size, "Q") ||
+        !make_map(&p.tmap_k, k, ks, hs.k, lk, heads, f16, error, error_size, "K") ||
+        !make_map(&p.tmap_v, v, vs, hs.v, lk, heads, f16, error, error_size, "V"))
         return 0;
-    p.out = out; p.o_stride = os; p.lq = (int)lq; p.lk = (int)lk; p.heads = (int)heads;
+    p.out = out; p.o_stride = os; p.o_head_stride = hs.o; p.lq = (int)lq; p.lk = (int)lk; p.heads = (int)heads;
     p.scale_log2 = scale * 1.4426950408889634f;
     p.status = cuda->d_status;
     if (sc) {
@@ -452,7 +501,14 @@ static int launch_sdpa_impl(h3_cuda *cuda, const void *q, size_t qs, const void 
             p.sc_out[r] = sc->peer_att[r];
         }
     }
-    auto kernel = f16 ? k_attn<__half> : k_attn<__nv_bfloat16>;
+    // share of the exponentials moved from the special-function unit to the FMA pipe: H3B_ATTN_EMU = 0, 2, 3, 4
+    // (eighths); the f16 form keeps the hardware exponential (its probabilities carry three more bits)
+    static const int emu = atoi(h3_plugin_value("H3B_ATTN_EMU"));
+    void (*kernel)(const AttnParams) = k_attn<__nv_bfloat16, 0>;
+    if (f16) kernel = k_attn<__half, 0>;
+    else if (emu == 2) kernel = k_attn<__nv_bfloat16, 0x11>;
+    else if (emu == 3) kernel = k_attn<__nv_bfloat16, 0x49>;
+    else if (emu == 4) kernel = k_attn<__nv_bfloat16, 0x55>;
     H3B_CUDA_OK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)attn::SMEM_BYTES),
                 "sdpa smem attribute");
     dim3 grid((unsigned)ceil_div(lq, 2 * attn::BQ), (unsigned)heads);
@@ -477,6 +533,24 @@ int h3b_sdpa_bf16_dev(h3_cuda *cuda, const void *d_q, size_t q_stride, const voi
     int ok = launch_sdpa_bf16(cuda, d_q, q_stride, d_k, k_stride, d_v, v_stride, lq, lk, heads, head_dim, scale, d_out,
                               o_stride, error, error_size);
     if (ok) g_last_backend = "tcgen05_flash_bf16";
+    return ok;
+}
+
+// General form: bf16 or f16 tensors, explicit row AND head strides for every tensor (elements).  With head
+// strides of lq * 128 / lk * 128 and row strides of 128 this is the [heads, rows, 128] layout of the reference's
+// attention plugins.
+int h3b_sdpa_strided_dev(h3_cuda *cuda, int dtype, const void *d_q, size_t q_row_stride, size_t q_head_stride,
+                         const void *d_k, size_t k_row_stride, size_t k_head_stride, const void *d_v, size_t v_row_stride,
+                         size_t v_head_stride, size_t lq, size_t lk, size_t heads, size_t head_dim, float scale, void *d_out,
+                         size_t o_row_stride, size_t o_head_stride, char *error, size_t error_size) {
+    if (dtype != H3B_BF16 && dtype != H3B_F16) return fail(error, error_size, "sdpa: dtype must be bf16 or f16");
+    if (!q_head_stride || !k_head_stride || !v_head_stride || !o_head_stride)
+        return fail(error, error_size, "sdpa: head strides must be given");
+    HeadStrides hs;
+    hs.q = q_head_stride; hs.k = k_head_stride; hs.v = v_head_stride; hs.o = o_head_stride;
+    int ok = launch_sdpa_impl(cuda, d_q, q_row_stride, d_k, k_row_stride, d_v, v_row_stride, lq, lk, heads, head_dim, scale,
+                              d_out, o_row_stride, nullptr, dtype == H3B_F16, error, error_size, hs);
+    if (ok) g_last_backend = dtype == H3B_F16 ? "tcgen05_flash_f16" : "tcgen05_flash_bf16";
     return ok;
 }
 
@@ -689,12 +763,10 @@ static int rope_sdpa(h3_cuda *cuda, const void *d_qkv, int in_dtype, const float
 
 // layout defaults of the reference (h3_gpu_cuda.cu:54-69): contiguous [Q|K|V] thirds unless H3_DIT_QKV_GROUPED=1,
 // split-half RoPE pairing unless H3_DIT_ROPE_HALF_OFFSET=1 or H3_DIT_ROPE_SPLIT_HALF=0
-static int env_is(const char *name, char c) {
-    const char *e = getenv(name);
-    return e && e[0] == c && !e[1];
+static int default_grouped(void) { return strcmp(h3_plugin_value("H3_DIT_QKV_GROUPED"), "1") == 0; }
+static int default_split_half(void) {
+    return !(strcmp(h3_plugin_value("H3_DIT_ROPE_HALF_OFFSET"), "1") == 0 || strcmp(h3_plugin_value("H3_DIT_ROPE_SPLIT_HALF"), "0") == 0);
 }
-static int default_grouped(void) { return env_is("H3_DIT_QKV_GROUPED", '1'); }
-static int default_split_half(void) { return !(env_is("H3_DIT_ROPE_HALF_OFFSET", '1') || env_is("H3_DIT_ROPE_SPLIT_HALF", '0')); }
 
 int h3_cuda_qkv_rope_sdpa_f16_dev_layout(h3_cuda *cuda, const float *d_qkv, const float *d_q_norm, const float *d_k_norm,
                                          const float *d_rope_cos, const float *d_rope_sin, size_t seq, size_t heads,

@@ -12,6 +12,7 @@
 #include <string.h>
 
 #include "../../include/h3_b200.h"
+#include "../../include/h3b_plugin.h"
 
 enum { ROPE_FREQS = 16, ROPE_AXES = 3, ROPE_HALF = ROPE_FREQS * ROPE_AXES };
 
@@ -96,14 +97,14 @@ int h3_dit_w4a8_rope_tables_f32(const float *inv_freq, size_t seq, const float *
 }
 
 size_t h3_dit_w4a8_t_row_from_sigma(float sigma, size_t t_table_rows) {
-    const char *by_sigma = getenv("H3_DIT_T_ROW_BY_SIGMA");
+    const int by_sigma = strcmp(h3_plugin_value("H3_DIT_T_ROW_BY_SIGMA"), "1") == 0;
     float t;
     size_t row;
     if (!t_table_rows) return 0;
     if (!isfinite(sigma) || sigma < 0.0f) sigma = 0.0f;
     if (sigma > 1.0f) sigma = 1.0f;
     /* the table is laid out over time = 1 - sigma; the switch restores the older sigma axis */
-    t = (by_sigma && by_sigma[0] == '1' && !by_sigma[1]) ? sigma : 1.0f - sigma;
+    t = by_sigma ? sigma : 1.0f - sigma;
     row = (size_t)llround((double)t * (double)(t_table_rows - 1));
     return row < t_table_rows ? row : t_table_rows - 1;
 }

@@ -557,10 +557,7 @@ int launch_gemm_nvfp4(h3_cuda *cuda, const uint8_t *w_fp4, const uint8_t *sf_w, 
     p.row_map = row_map; p.slots = (int)slots; p.gate_slot = (int)gate_slot; p.status = cuda->d_status;
     if (gate && (((uintptr_t)residual | (uintptr_t)mod) & 15)) return fail(error, error_size, "gemm_fp4: residual and modulation must be 16-byte aligned");
     // 128 x 256 tiles whenever N has two column blocks; H3B_FP4_WIDE=0 keeps the 128 x 128 form (A/B timing)
-    static const bool wide_on = [] {
-        const char *e = getenv("H3B_FP4_WIDE");
-        return !(e && e[0] == '0');
-    }();
+    static const bool wide_on = h3_plugin_enabled("H3B_FP4_WIDE") != 0;
     if (wide_on && n >= 256) {
         int rc2 = h3b_encode_tmap_2d(&p.tmap_w, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, w_fp4, k / 2, n, k / 2, BK_BYTES, 128,
                                      CU_TENSOR_MAP_SWIZZLE_128B);

@@ -740,10 +740,7 @@ static int gemm_launch_t(h3_cuda *cuda, GemmParams &p, char *error, size_t error
         }
         if (rc != 0) return fail(error, error_size, "gemm_i8: cuTensorMapEncodeTiled(QKV outputs, RoPE tables) failed (%d)", rc);
     }
-    static const bool pairs_allowed = [] {
-        const char *e = getenv("H3B_GEMM_PAIRS");
-        return !(e && e[0] == '0');
-    }();
+    static const bool pairs_allowed = h3_plugin_enabled("H3B_GEMM_PAIRS") != 0;
     if (pairs_allowed && p.M > BM) {
         auto kern = k_gemm_i8<EPI, OutT, 2>;
         constexpr size_t smem = Shape<2, EPI>::SMEM_BYTES;

@@ -8,6 +8,7 @@
 #include <stdio.h>
 
 #include "../../include/h3_b200.h"
+#include "../../include/h3b_plugin.h"
 
 struct h3_cuda {
     int device;

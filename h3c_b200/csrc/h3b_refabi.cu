@@ -388,8 +388,7 @@ int h3_cuda_gemm_fp4_pre_q_dev(h3_cuda *cuda, const h3_cuda_nvfp4_weight *weight
 
 // H3_NVFP4_DEBUG_NAN=1 turns on a synchronous scan for non-finite values.  h3_gpu_cuda.h:554-557
 int h3_nvfp4_debug_nan_dev(void) {
-    const char *e = getenv("H3_NVFP4_DEBUG_NAN");
-    return e && e[0] == '1' && !e[1];
+    return strcmp(h3_plugin_value("H3_NVFP4_DEBUG_NAN"), "1") == 0;
 }
 void h3_nvfp4_debug_scan_dev(h3_cuda *cuda, const void *ptr, size_t n, const char *kind, const char *tag, const char *stage) {
     if (!cuda || !ptr || !n || !h3_nvfp4_debug_nan_dev()) return;

@@ -538,8 +538,7 @@ int h3b_ulysses_direct_setup(h3_ulysses_cfg *cfg, size_t seq_local, size_t heads
     // barrier is the all-reduce; later ones are the flag kernel unless H3B_ULYSSES_BARRIER=nccl
     st->flag_barrier = 0;
     if (!(h3b_ulysses_barrier(cfg, err, err_size) && cudaStreamSynchronize(st->compute[0]) == cudaSuccess)) return 0;
-    const char *mode = getenv("H3B_ULYSSES_BARRIER");
-    st->flag_barrier = !(mode && strcmp(mode, "nccl") == 0);
+    st->flag_barrier = strcmp(h3_plugin_value("H3B_ULYSSES_BARRIER"), "nccl") != 0;
     return 1;
 }
 

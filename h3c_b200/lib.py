@@ -264,6 +264,21 @@ _SIGS = {
     "h3_nvfp4_cuda_cache_clear": (None, ()),
     "h3_nvfp4_cuda_encode_text_layers": (i32, (vp, vp, sz, C.c_uint) + _ERR),
     "h3_nvfp4_cuda_gqa_causal": (i32, (vp, vp, vp, sz, sz, sz, sz, vp) + _ERR),
+    "h3b_sdpa_strided_dev": (i32, (vp, i32, vp, sz, sz, vp, sz, sz, vp, sz, sz, sz, sz, sz, sz, f32, vp, sz, sz) + _ERR),
+    "h3_dit_patchify_video": (i32, (vp, i32, i32, i32, i32, vp, sz)),
+    "h3_dit_unpatchify_video": (i32, (vp, i32, i32, i32, i32, vp, sz)),
+    "h3_dit_pack_audio": (i32, (vp, i32, i32, vp, sz)),
+    "h3_dit_unpack_audio": (i32, (vp, i32, i32, vp, sz)),
+    "h3_dit_reuse_schedule": (i32, (i32, i32, vp, sz)),
+    "h3_dit_forward": (i32, (vp, i32, vp, vp, vp, vp) + _ERR),
+    "h3_dit_denoise_euler": (i32, (vp, vp, vp, i32, vp, vp) + _ERR),
+    "h3_dit_video_elements": (sz, (vp,)),
+    "h3_dit_audio_elements": (sz, (vp,)),
+    "h3_dit_free": (None, (vp,)),
+    "h3b_plugin_count": (sz, ()),
+    "h3b_plugin_get": (i32, (sz, C.POINTER(cs), C.POINTER(cs), C.POINTER(cs), C.POINTER(cs))),
+    "h3b_plugin_value": (cs, (cs,)),
+    "h3b_plugin_enabled": (i32, (cs,)),
     "h3_ulysses_validate": (i32, (i32, i32, i32, i32, i32) + _ERR),
     "h3_ulysses_pad_seq": (sz, (sz, i32)),
     "h3_ulysses_local_rows": (sz, (sz, i32, i32)),

@@ -96,6 +96,14 @@ int h3b_umma_peak_dev(h3_cuda *cuda, int kind, int iters, double *tera_ops_per_s
 /* Addition.  Kernel launches issued through this handle since the last call. */
 unsigned long long h3b_cuda_launch_count(h3_cuda *cuda, int reset);
 
+/* Additions: the switch registry (include/h3b_plugin.h, the counterpart of the reference's tools/h3_plugin.h)
+ * as exported functions.  _value: the environment's value if set and not empty, else the registered default;
+ * NULL for an unregistered name.  _enabled: that value is not one of "", "0", "false", "off", "no". */
+size_t h3b_plugin_count(void);
+int h3b_plugin_get(size_t index, const char **name, const char **status, const char **stage, const char **default_value);
+const char *h3b_plugin_value(const char *name);
+int h3b_plugin_enabled(const char *name);
+
 /* ----------------------------------------------------------------- weights */
 
 typedef struct h3_cuda_w4a8_weight h3_cuda_w4a8_weight;   /* h3_gpu_cuda.h:284 */
@@ -442,6 +450,12 @@ int h3b_sdpa_bf16_dev(h3_cuda *cuda, const void *d_q, size_t q_stride, const voi
                       size_t k_stride, const void *d_v, size_t v_stride, size_t lq, size_t lk,
                       size_t heads, size_t head_dim, float scale, void *d_out, size_t o_stride,
                       char *error, size_t error_size);
+/* Addition: the general form.  dtype H3B_BF16 or H3B_F16 for all four tensors; row and head strides in elements
+ * (multiples of 8); e.g. [heads, rows, 128] tensors have row stride 128 and head stride rows * 128. */
+int h3b_sdpa_strided_dev(h3_cuda *cuda, int dtype, const void *d_q, size_t q_row_stride, size_t q_head_stride,
+                         const void *d_k, size_t k_row_stride, size_t k_head_stride, const void *d_v, size_t v_row_stride,
+                         size_t v_head_stride, size_t lq, size_t lk, size_t heads, size_t head_dim, float scale, void *d_out,
+                         size_t o_row_stride, size_t o_head_stride, char *error, size_t error_size);
 /* Addition: the same attention over this rank's heads/ulysses heads of the gathered sequence
  * (scatter->q, ->k, ->v, lq = lk = seq_real), each output row stored into scatter->peer_att of the
  * rank that owns the row, at head rank*hl + h. */
@@ -696,6 +710,27 @@ size_t h3_dit_w4a8_t_row_from_sigma(float sigma, size_t t_table_rows);
 int h3b_dit_video_rope_tables(const float *inv_freq16, size_t text_len, int grid_t, int grid_h, int grid_w,
                               float spatial_scale, size_t pad_rows, float *cos_out, float *sin_out, char *error,
                               size_t error_size);
+
+/* ------------------------------------------------- Metal-twin signatures (h3_dit.h:94-140), thin shims
+ * Row-order conversions and the reuse schedule are implemented (host arithmetic, int 1 = ok / 0 = bad
+ * arguments; the schedule returns the number of selected steps or -1).  The calls that need the Apple-GPU
+ * transformer object fail with "Metal path: unavailable on this box". */
+typedef struct h3_dit h3_dit;                                                                 /* h3_dit.h:11 */
+typedef void (*h3_dit_progress)(const char *phase, int completed, int total, void *opaque);   /* h3_dit.h:13 */
+int h3_dit_patchify_video(const float *latent, int channels, int time, int height, int width, float *rows,
+                          size_t row_elements);                                               /* :131 */
+int h3_dit_unpatchify_video(const float *rows, int channels, int time, int height, int width, float *latent,
+                            size_t latent_elements);                                          /* :134 */
+int h3_dit_pack_audio(const float *latent, int channels, int time, float *rows, size_t row_elements);     /* :137 */
+int h3_dit_unpack_audio(const float *rows, int channels, int time, float *latent, size_t latent_elements); /* :139 */
+int h3_dit_reuse_schedule(int steps, int reuse_interval, uint8_t *selected, size_t selected_count);       /* :124 */
+int h3_dit_forward(h3_dit *dit, int step, const float *video_latent, const float *audio_latent, float *video_velocity,
+                   float *audio_velocity, char *error, size_t error_size);                    /* :94 */
+int h3_dit_denoise_euler(h3_dit *dit, float *video_latent, float *audio_latent, int reuse_interval,
+                         h3_dit_progress progress, void *progress_opaque, char *error, size_t error_size); /* :106 */
+size_t h3_dit_video_elements(const h3_dit *dit);                                              /* :88 */
+size_t h3_dit_audio_elements(const h3_dit *dit);                                              /* :89 */
+void h3_dit_free(h3_dit *dit);                                                                /* :77 */
 
 /* ------------------------------------------------------------------ Ulysses */
 

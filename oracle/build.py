@@ -12,7 +12,8 @@ The reference's DiT source file also contains its CUDA orchestration, so it has 
 undefined h3_cuda_* / cuda* symbols.  Its CPU functions never reach them; they are given
 aborting stubs generated from `nm -u` so the shared object loads without a CUDA runtime.
 
-Usage: python oracle/build.py [--ref-root PATH]   (default PATH: $H3_REFERENCE_ROOT or /root/reference)
+Usage: python oracle/build.py [--ref-root PATH]   (default PATH: $H3_REFERENCE_ROOT, else the directory
+"reference" beside this repository)
 """
 from __future__ import annotations
 
@@ -41,6 +42,12 @@ REF_SOURCES = [
     "h3_sdpa_registry.c",
     "h3_cuda_device_caps.c",
 ]
+
+
+def default_ref_root() -> Path:
+    """Where the h3.c tree is looked for: $H3_REFERENCE_ROOT, else a directory "reference" beside this repository."""
+    env = os.environ.get("H3_REFERENCE_ROOT")
+    return Path(env) if env else HERE.parent.parent / "reference"
 
 
 def _run(cmd: list[str]) -> None:
@@ -185,7 +192,7 @@ def build_ref_host(ref_root: Path, product_lib: Path, force: bool = False) -> Pa
 
 def main() -> None:
     ap = argparse.ArgumentParser()
-    ap.add_argument("--ref-root", default=os.environ.get("H3_REFERENCE_ROOT", "/root/reference"))
+    ap.add_argument("--ref-root", default=str(default_ref_root()))
     ap.add_argument("--force", action="store_true")
     args = ap.parse_args()
     print("oracle:", build_oracle(args.force))

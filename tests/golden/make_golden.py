@@ -24,7 +24,7 @@ sys.path.insert(0, str(ROOT))
 
 from oracle.pyoracle import Ref  # noqa: E402
 
-REF_ROOT = Path(os.environ.get("H3_REFERENCE_ROOT", "/root/reference"))
+REF_ROOT = Path(os.environ["H3_REFERENCE_ROOT"]) if os.environ.get("H3_REFERENCE_ROOT") else ROOT.parent / "reference"
 
 
 def save(name, **arrays):

@@ -4,6 +4,8 @@ attention entry points with history keys / values, token-reduction pool / expand
 optional features this library does not have."""
 import ctypes as C
 
+from h3c_b200.lib import load
+
 import numpy as np
 import pytest
 
@@ -66,7 +68,8 @@ def test_host_and_mixed_f32_gemms(cuda):
     wh = dev(w, torch.float16)
     y0 = rng.normal(0, 1, (m, n)).astype(np.float32)
     dy = dev(y0)
-    call("h3_cuda_gemm_f32in_f16w_f32out_dd_ex", cuda.h, p(dev(x)), p(wh), m, n, k, p(dy), 0.75, 1.0)
+    dx = dev(x)
+    call("h3_cuda_gemm_f32in_f16w_f32out_dd_ex", cuda.h, p(dx), p(wh), m, n, k, p(dy), 0.75, 1.0)
     cuda.check()
     want = 0.75 * (x.astype(np.float64) @ host(wh).astype(np.float64).T) + y0
     assert rel_l2(host(dy), want) < 1e-5
@@ -74,7 +77,7 @@ def test_host_and_mixed_f32_gemms(cuda):
     call("h3_cuda_cublas_use_side", cuda.h, 1)
     from h3c_b200.lib import load
     assert load().h3_cuda_cublas_stream(cuda.h) == load().h3_cuda_stream(cuda.h, 1)
-    y3 = cuda.gemm_f32_dd(dev(x), dw)
+    y3 = cuda.gemm_f32_dd(dx, dw)
     torch.cuda.synchronize()
     call("h3_cuda_cublas_use_side", cuda.h, 0)
     assert load().h3_cuda_cublas_stream(cuda.h) == load().h3_cuda_op_stream(cuda.h)
@@ -157,8 +160,10 @@ def test_nvfp4_fc1_swiglu_requant_fc2_chain(cuda, oracle):
     mod = rng.normal(0, 0.5, (3, slots, dim)).astype(np.float32)
     rmap = (np.arange(m) % 3).astype(np.uint32)
     y = torch.empty((m, dim), dtype=torch.float32, device="cuda")
-    call("h3_cuda_gemm_fp4_pre_q_dev", cuda.h, wh, p(a4), p(asf), m, p(dev(res)), p(dev(mod)), p(dev(rmap.view(np.int32))),
-         slots, 5, None, p(y), None, None, b"test.fc2")
+    d_res, d_mod, d_map = dev(res), dev(mod), dev(rmap.view(np.int32))
+    err = C.create_string_buffer(512)
+    assert load().h3_cuda_gemm_fp4_pre_q_dev(cuda.h, wh, p(a4), p(asf), m, p(d_res), p(d_mod), p(d_map), slots, 5, None, p(y),
+                                             None, None, err, 512, b"test.fc2") == 1, err.value
     cuda.check()
     base = oracle.gemm_nvfp4(host(a4)[:m], host(asf), w2q, w2sf, 0.5)
     assert rel_l2(host(y), oracle.gate(res, base, mod, rmap, slots, 5)) < 1e-5
@@ -189,8 +194,9 @@ def test_reference_rope_sdpa_entry_points_f16(cuda, oracle):
     want = oracle.sdpa(q, k, v)
     out = torch.empty((seq, heads * hd), dtype=torch.float32, device="cuda")
     be = C.create_string_buffer(64)
-    args = (p(dev(qn)), p(dev(kn)), p(dev(cos)), p(dev(sin)), seq, heads, hd, 48, 1e-5, hd ** -0.5, 0)
-    call("h3_cuda_qkv_rope_sdpa_f16_dev_layout", cuda.h, p(dev(qkv)), *args, 0, 1, p(out), None, None, be, 64)
+    d_qkv, d_qn, d_kn, d_cos, d_sin = dev(qkv), dev(qn), dev(kn), dev(cos), dev(sin)    # kept alive across the calls
+    args = (p(d_qn), p(d_kn), p(d_cos), p(d_sin), seq, heads, hd, 48, 1e-5, hd ** -0.5, 0)
+    call("h3_cuda_qkv_rope_sdpa_f16_dev_layout", cuda.h, p(d_qkv), *args, 0, 1, p(out), None, None, be, 64)
     cuda.check()
     assert be.value == b"tcgen05_flash_f16"
     e32 = rel_l2(host(out), want)
@@ -204,7 +210,7 @@ def test_reference_rope_sdpa_entry_points_f16(cuda, oracle):
     # windowed attention is refused, not ignored
     import h3c_b200
     with pytest.raises(h3c_b200.H3Error, match="windowed"):
-        call("h3_cuda_qkv_rope_sdpa_f16_dev_layout", cuda.h, p(dev(qkv)), *args[:-1], 24, 0, 1, p(out), None, None, None, 0)
+        call("h3_cuda_qkv_rope_sdpa_f16_dev_layout", cuda.h, p(d_qkv), *args[:-1], 24, 0, 1, p(out), None, None, None, 0)
 
 
 def test_history_keys_and_saved_rows(cuda, oracle):
@@ -224,7 +230,8 @@ def test_history_keys_and_saved_rows(cuda, oracle):
     load().h3_cuda_sdpa_bind_kvcat(p(kh), p(vh), hist)
     load().h3_cuda_sdpa_bind_kvsave(p(ks), p(vs), p(d_idx), len(idx))
     out = torch.empty((seq, heads * hd), dtype=torch.float32, device="cuda")
-    call("h3_cuda_qkv_rope_sdpa_f16_dev", cuda.h, p(dev(qkv)), p(dev(qn)), p(dev(kn)), p(dev(cos)), p(dev(sin)), seq, heads, hd,
+    d_qkv, d_qn, d_kn, d_cos, d_sin = dev(qkv), dev(qn), dev(kn), dev(cos), dev(sin)    # kept alive across the calls
+    call("h3_cuda_qkv_rope_sdpa_f16_dev", cuda.h, p(d_qkv), p(d_qn), p(d_kn), p(d_cos), p(d_sin), seq, heads, hd,
          48, 1e-5, hd ** -0.5, 0, p(out), None, None, None, 0)
     load().h3_cuda_sdpa_clear_kvext()
     cuda.check()
@@ -233,7 +240,7 @@ def test_history_keys_and_saved_rows(cuda, oracle):
     assert rel_l2(host(out), oracle.sdpa(q.reshape(seq, heads, hd), k_all, v_all)) < 1e-3
     assert rel_l2(host(ks), k.reshape(seq, heads, hd)[idx]) < 5e-4 and rel_l2(host(vs), v.reshape(seq, heads, hd)[idx]) < 5e-4
     # cleared: the next call is square again
-    call("h3_cuda_qkv_rope_sdpa_f16_dev", cuda.h, p(dev(qkv)), p(dev(qn)), p(dev(kn)), p(dev(cos)), p(dev(sin)), seq, heads, hd,
+    call("h3_cuda_qkv_rope_sdpa_f16_dev", cuda.h, p(d_qkv), p(d_qn), p(d_kn), p(d_cos), p(d_sin), seq, heads, hd,
          48, 1e-5, hd ** -0.5, 0, p(out), None, None, None, 0)
     cuda.check()
     assert rel_l2(host(out), oracle.sdpa(q, k, v)) < 1e-3
@@ -346,3 +353,36 @@ def test_housekeeping_and_absent_features(cuda):
     with pytest.raises(h3c_b200.H3Error, match="not supported by libh3_b200"):
         call("h3_nvfp4_cuda_encode_text_layers", None, None, 0, 0)
     assert L.h3_nvfp4_debug_nan_dev() in (0, 1)
+
+
+# ------------------------------------------------------------------ the attention plugin ABI
+
+def test_sdpa_plugin_through_dlopen(cuda, oracle):
+    """libh3_b200_sdpa.so: the four symbols the reference looks up in an attention plugin (h3_sage3_init / _fwd /
+    _fwd_ex / _warmup).  Driven the way the reference drives a plugin: init returns four f16 [heads, seq, 128]
+    buffers owned by the plugin, the caller fills Q / K / V, calls fwd, reads O."""
+    from h3c_b200 import build
+    lib = C.CDLL(str(build.SDPA_PLUGIN))
+    rng = np.random.default_rng(8)
+    seq, heads, hd = 333, 3, 128
+    err, be = C.create_string_buffer(512), C.create_string_buffer(64)
+    ptrs = [C.c_void_p() for _ in range(4)]
+    assert lib.h3_sage3_warmup(b"", seq, heads, hd, C.c_float(hd ** -0.5), 0, 0, err, C.c_size_t(512)) == 1, err.value
+    assert lib.h3_sage3_init(b"", seq, heads, hd, C.c_float(hd ** -0.5), 0, 0, *[C.byref(x) for x in ptrs], be, C.c_size_t(64), err,
+                             C.c_size_t(512)) == 1, err.value
+    assert be.value == b"h3_b200_tcgen05_flash_f16" and all(x.value for x in ptrs)
+    q, k, v = (rng.normal(0, 1, (heads, seq, hd)).astype(np.float16) for _ in range(3))     # [heads, seq, 128]
+    rt = C.CDLL("libcudart.so.12")
+    for dst, a in zip(ptrs[:3], (q, k, v)):
+        assert rt.cudaMemcpy(dst, C.c_void_p(a.ctypes.data), C.c_size_t(a.nbytes), 1) == 0
+    kern_ms = C.c_double(0)
+    assert lib.h3_sage3_fwd_ex(err, C.c_size_t(512), None, C.byref(kern_ms), None, None, None) == 1, err.value
+    o = np.empty_like(q)
+    assert rt.cudaMemcpy(C.c_void_p(o.ctypes.data), ptrs[3], C.c_size_t(o.nbytes), 2) == 0
+    want = oracle.sdpa(*(np.ascontiguousarray(a.astype(np.float32).transpose(1, 0, 2)) for a in (q, k, v)))
+    got = o.astype(np.float32).transpose(1, 0, 2).reshape(seq, heads * hd)
+    assert rel_l2(got, want) < 1e-3 and kern_ms.value > 0
+    assert lib.h3_sage3_fwd(err, C.c_size_t(512)) == 1
+    # shapes the kernel does not serve are refused with a message, like the reference's plugin errors
+    assert lib.h3_sage3_init(b"", seq, heads, 64, C.c_float(0.125), 0, 0, *[C.byref(x) for x in ptrs], be, C.c_size_t(64), err,
+                             C.c_size_t(512)) == 0 and b"head_dim 128" in err.value

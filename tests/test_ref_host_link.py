@@ -41,7 +41,7 @@ def test_reference_host_links_with_no_undefined_symbol(product_lib):
     spec = importlib.util.spec_from_file_location("_h3_oracle_build", ROOT / "oracle" / "build.py")
     ob = importlib.util.module_from_spec(spec)
     spec.loader.exec_module(ob)
-    ref_root = Path(os.environ.get("H3_REFERENCE_ROOT", "/root/reference"))
+    ref_root = ob.default_ref_root()
     lib = ob.build_ref_host(ref_root, product_lib, force=True)      # links with -Wl,-z,defs: raises on any gap
     if lib is None:
         pytest.skip("reference host objects not built (reference tree absent)")
