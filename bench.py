@@ -3,11 +3,12 @@
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
 
 Workload at every N: the full 50-block W4A8 step at 50,220 video tokens (31x30x54 patch grid) + 512 text
-tokens, D = 3072, 24 x 128 heads, FFN 12288, bf16 residual stream, t = 0.5 -- BASELINE.json configs[4].
+tokens, D = 3072, 24 x 128 heads, FFN 12288, bf16 residual stream, t = 0.5 (the metric's headline workload).
 N = 1 runs it on one GPU; N > 1 (under torchrun, one rank per GPU) shards the rows across the ranks
 (Ulysses sequence parallelism), so the per-N values are the same work and compare directly.
-`--workload step6144` times the 6,144-token single-GPU step (6x32x32 grid, configs[3]) instead.
+`--workload step6144` times the 6,144-token single-GPU step (6x32x32 grid) instead.
 `--impl reference` times the reference's CPU implementation of the same block on the host cores.
+`--kernel NAME` times one operator on synthetic data (the commands behind the summaries under profiles/).
 
 Prints ONE JSON line (rank 0).  `value` is ms per step with every input resident in HBM; `e2e` is the
 same step through the host-buffer entry point (h3b_dit_layers_forward_f32) with pinned host arrays,
@@ -190,15 +191,22 @@ def reference_arm(args):
     cores = os.cpu_count() or 1
     vals = []
     desc = ""
-    for _ in range(max(1, min(args.steps, 2))):    # each "step" is one bounded sample; two are plenty on a CPU
+    # a whole step would take about a day of CPU time: every "step" here is one bounded row sample of one block,
+    # scaled to 50 blocks; two samples are taken whatever --steps asks for, and the line says so
+    samples = max(1, min(args.steps, 2))
+    for _ in range(samples):
         v, desc = cpu_block_sample(kind, cores, budget_s=20.0, grid=GRID_ULYSSES if big_workload(args) else GRID_1GPU)
         vals.append(v)
     value = float(np.median(vals))
+    cfg = workload_config(1, big_workload(args))
+    cfg["parallelism"] = f"{cores} host threads (the CPU path does not shard over GPUs; the same figure is reported at every N)"
     line = {"impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
-            "steps": args.steps, "warmup": args.warmup, "ms_per_step": value, "higher_is_better": False,
+            "steps": samples, "warmup": 0, "steps_asked": args.steps, "ms_per_step": value, "higher_is_better": False,
+            "extrapolated": True,
+            "extrapolation": "median of the samples, each scaled from its sampled query rows of ONE block to all rows x 50 blocks",
             "scaling": "strong" if big_workload(args) else "weak", "vs_baseline": None,
             "dtype": "int8 linears + f32 attention (CPU)", "data": "synthetic",
-            "config": workload_config(args.gpus, big_workload(args)),
+            "config": cfg,
             "cpu_baseline": {"value": value, "unit": UNIT, "cores": cores, "kind": kind, "sample": desc},
             "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
             "gpu_launches": 0}
@@ -228,16 +236,6 @@ def workload_config(n_gpus, big):
 
 # -------------------------------------------------------------------------------------- GPU arm
 
-def shard_rows(seq_real, world, rank, align=64):
-    """Ulysses row split (h3_dit_w4a8.c:6275-6277): pad to a multiple of 64, equal slices per rank.
-    Returns (seq_pad, seq_local, first_row, real_rows_of_this_rank)."""
-    seq_pad = (seq_real + align - 1) // align * align
-    seq_local = seq_pad // world
-    first = rank * seq_local
-    real = max(0, min(seq_local, seq_real - first))
-    return seq_pad, seq_local, first, real
-
-
 def gpu_arm(args):
     import torch
     import h3c_b200
@@ -257,13 +255,15 @@ def gpu_arm(args):
     cuda.set_quiet(True)
     geo = D.DitGeometry(dim=GEO["dim"], heads=GEO["heads"], head_dim=GEO["head_dim"], ffn=GEO["ffn"],
                         n_blocks=GEO["n_blocks"], mod_rows=1, t_dim=256, kind=D.BLOCK_CROSS_GELU, stream_dtype=D.BF16)
-    dit = D.build_synthetic(cuda, geo, seed=0)   # same seed on every rank: replicated weights
+    # same seed on every rank: replicated weights; host copies of the first two blocks' small tensors are kept for
+    # the checks that follow the timed region
+    dit, host_blocks = D.build_synthetic(cuda, geo, seed=0, keep_host=2)
     ulysses = big_workload(args)
     if world > 1 and not ulysses:
         raise SystemExit("--workload step6144 is a single-GPU workload")
     grid = GRID_ULYSSES if ulysses else GRID_1GPU
     seq_real, text_len = grid[0] * grid[1] * grid[2], GEO["text"]
-    seq_pad, seq_local, first_row, real_rows = shard_rows(seq_real, world, rank)
+    seq_pad, seq_local, first_row, real_rows = h3c_b200.ulysses_shard_rows(seq_real, world, rank)
     comm = None
     if world > 1:
         uid = torch.zeros(128, dtype=torch.uint8, device="cuda")
@@ -382,6 +382,15 @@ def gpu_arm(args):
     prof = profile_classes(cuda, dit, eager_step if (args.graph and world == 1) else step_resident)
     sync_all()
 
+    checks = {}
+    if not args.skip_checks:
+        if world > 1:
+            checks["ulysses_check"] = ulysses_check(cuda, dit, geo, host_blocks, world, rank, seq_real, seq_pad, seq_local,
+                                                    cos_d, sin_d, text_d, t_d, dist)
+        if rank == 0:
+            checks["parity_check"] = parity_check(cuda, dit, geo, host_blocks[0], grid, text_np, t_d)
+        sync_all()
+
     e2e_ms = None
     if not args.skip_e2e:
         for _ in range(max(1, min(args.warmup, 2))):
@@ -403,27 +412,14 @@ def gpu_arm(args):
         # algorithmic work of this rank: its rows through every linear, heads/U heads of the full attention
         lin_f, _ = block_flops(rows, text_len, geo.dim, geo.ffn)
         attn_f = (4.0 * seq_real * seq_real * geo.dim) / world + 4.0 * rows * text_len * geo.dim
-        roof = roofline(prof, lin_f, attn_f, geo.n_blocks, pk)
-        if roof and roof.get("kernel") == "attention" and world == 1 and seq_real == 50220:
-            roof["traffic"] = ATTN_DRAM_BYTES_PER_LAUNCH_50220
-            roof["traffic_note"] = ("dram__bytes_read.sum + dram__bytes_write.sum, mean of the self- and the "
-                                    "cross-attention launch of one block, one cold-cache ncu capture of this command")
-            v = ctypes.c_double(0)
-            from h3c_b200.lib import call
-            call("h3b_umma_peak_dev", cuda.h, 3, 1000000, ctypes.byref(v))   # bf16 128x128x16, about a second
-            roof["probe_peak"] = v.value
-            roof["frac_of_probe"] = roof["achieved"] / v.value
-        if roof and roof.get("kernel") == "gemm_i8":
-            if not ulysses and seq_real == 6144:
-                roof["traffic"] = GEMM_DRAM_BYTES_PER_LAUNCH_6144
-                roof["traffic_note"] = ("dram__bytes_read.sum + dram__bytes_write.sum, mean over the seven GEMM launches "
-                                        "of one block, one cold-cache ncu capture of this command")
-            # the int8 rate this GPU sustains on back-to-back MMAs with no loads (about a second of them)
-            v = ctypes.c_double(0)
-            from h3c_b200.lib import call
-            call("h3b_umma_peak_dev", cuda.h, 0, 1000000, ctypes.byref(v))
-            roof["probe_peak"] = v.value
-            roof["frac_of_probe"] = roof["achieved"] / v.value
+        # the rate this GPU sustains on about a second of back-to-back MMAs from a resident tile, measured now:
+        # the int8 denominator (the measured-peaks file has none) and a second opinion on the bf16 one
+        probe = {"int8": h3c_b200.tensor_pipe_rate(cuda, 0, 1000000), "bf16": h3c_b200.tensor_pipe_rate(cuda, 3, 1000000)}
+        roof = roofline(prof, lin_f, attn_f, geo.n_blocks, pk, probe)
+        if roof and roof.get("bound") == "tensor":
+            traffic = traffic_per_launch(roof["kernel"], seq_real if world == 1 else None)
+            if traffic:
+                roof["traffic"], roof["traffic_note"] = traffic
         lin_all, attn_all = block_flops(seq_real, text_len, geo.dim, geo.ffn)
         if args.skip_cpu_baseline or world > 1:
             cpu = None
@@ -446,6 +442,7 @@ def gpu_arm(args):
                         "d2h_bytes_per_step": int(d2h) * world},
                 "gpu_launches": int(launches) * world, "clocks": clocks, "roofline": roof, "cpu_baseline": cpu,
                 "step_tflops": (lin_all + attn_all) * geo.n_blocks / (ms_step * 1e-3) / 1e12, "kernel_classes": prof}
+        line.update(checks)
         OUT.emit(json.dumps(line))
     sync_all()
     dit.close()
@@ -454,6 +451,123 @@ def gpu_arm(args):
     cuda.close()
     if dist is not None:
         dist.destroy_process_group()
+
+
+def full_input_rows(world, seq_real, seq_pad, dim):
+    """The activations of the whole (padded) sequence as the ranks generate them: rank r seeds its own slice."""
+    seq_local = seq_pad // world
+    rows = seq_local if world > 1 else seq_real
+    parts = []
+    for r in range(world):
+        x = np.random.default_rng(1000 + r).normal(0, 1, (rows, dim)).astype(np.float32)
+        if world > 1:
+            x[max(0, min(seq_local, seq_real - r * seq_local)):] = 0.0
+        parts.append(x)
+    return np.concatenate(parts)
+
+
+def second_context(cuda, dit, geo, host_blocks, n_blocks):
+    """A context over the first `n_blocks` blocks of `dit` (same weight objects, borrowed) with no communicator
+    attached: the unsharded chain the sharded one is compared with."""
+    from dataclasses import replace
+    from h3c_b200 import dit as D
+    geo2 = replace(geo, n_blocks=n_blocks)
+    ctx = D.Dit(cuda, geo2)
+    per_block = 7 if geo.kind == D.BLOCK_CROSS_GELU else 4
+    for b in range(n_blocks):
+        for which, w in enumerate(dit._weights[b * per_block:(b + 1) * per_block]):
+            from h3c_b200.lib import call
+            call("h3b_dit_set_linear", ctx.h, b, which, w.h)      # borrowed: `dit` keeps ownership
+        h = host_blocks[b]
+        ctx.set_block_aux(b, h["norm1"], h["norm2"], h["q_norm"], h["k_norm"], h.get("norm_c"))
+        ctx.set_adaln(b, h["adaln_w"], h["adaln_b"])
+    return ctx
+
+
+def ulysses_check(cuda, dit, geo, host_blocks, world, rank, seq_real, seq_pad, seq_local, cos_d, sin_d, text_d, t_d, dist):
+    """Sharding self-check at the real size: the first two blocks run sequence-parallel (the exchange the timed
+    step used) and, on every rank, unsharded over the whole sequence; this rank's rows of both must agree bit for
+    bit.  Returns the largest absolute difference over all ranks (0.0 when the sharded path is exact)."""
+    import torch
+    x_full = torch.from_numpy(full_input_rows(world, seq_real, seq_pad, geo.dim)).cuda().to(torch.bfloat16)
+    mine = slice(rank * seq_local, (rank + 1) * seq_local)
+    rmap = torch.zeros(seq_pad, dtype=torch.int32, device="cuda")
+    dit.project_modulation(t_d)
+    y_sharded = dit.layers_forward_ulysses(x_full[mine].contiguous(), seq_real, cos_d, sin_d, n=2, row_map=rmap[:seq_local],
+                                           text=text_d)
+    solo = second_context(cuda, dit, geo, host_blocks, 2)
+    solo.project_modulation(t_d)
+    y_full = solo.layers_forward(x_full[:seq_real].contiguous(), cos_d[:seq_real].contiguous(), sin_d[:seq_real].contiguous(),
+                                 row_map=rmap[:seq_real], text=text_d)
+    cuda.check()
+    real = max(0, min(seq_local, seq_real - rank * seq_local))
+    diff = (y_sharded[:real].float() - y_full[mine][:real].float()).abs().max() if real else torch.zeros((), device="cuda")
+    d = diff.reshape(1).double()
+    dist.all_reduce(d, op=dist.ReduceOp.MAX)
+    solo.close_keep_weights()
+    return float(d.item())
+
+
+def parity_check(cuda, dit, geo, blk, grid, text_np, t_d, n_rows=8):
+    """Output rows of block 0 of the REAL workload (whole sequence on this GPU) against the CPU checker.  The GPU
+    runs the block; the checker recomputes `n_rows` of its output rows in f32 from the block's input: every
+    linear (the resident int8 weights are downloaded), QK-norm + RoPE, self-attention of those rows against the
+    keys and values of ALL tokens (taken from the GPU's own QKV projection, 16-bit), cross-attention, the FFN.
+    Bound: 2e-2 relative L2, the figure stated for the f32 CPU block (the GPU path keeps a bf16 residual stream)."""
+    import torch
+    import h3c_b200
+    from oracle.pyoracle import Oracle, Ref
+    impl = Ref() if Ref.available() else Oracle()
+    oracle = Oracle()
+    seq = grid[0] * grid[1] * grid[2]
+    heads, hd, dim = geo.heads, geo.head_dim, geo.dim
+    x = torch.from_numpy(full_input_rows(1, seq, seq, dim)).cuda().to(torch.bfloat16)
+    inv_freq = (1.0 / (10000.0 ** (np.arange(16) / 16.0))).astype(np.float32)
+    cos_h, sin_h = h3c_b200.video_rope_tables(inv_freq, GEO["text"], grid)
+    cos, sin = torch.from_numpy(cos_h).cuda(), torch.from_numpy(sin_h).cuda()
+    text = torch.from_numpy(text_np).cuda().to(torch.bfloat16)
+    rmap = torch.zeros(seq, dtype=torch.int32, device="cuda")
+    solo = second_context(cuda, dit, geo, [blk], 1)
+    solo.project_modulation(t_d)
+    y = solo.block_forward(0, x, cos, sin, row_map=rmap, text=text)
+    mod = solo.modulation(0).cpu().numpy()
+    # keys and values of all tokens: the block's own first two launches, repeated through the operator interface
+    w = {name: dit._weights[i] for i, name in enumerate(("qkv", "o", "up", "down", "cq", "ckv", "co"))}
+    q8 = torch.empty((seq, dim), dtype=torch.int8, device="cuda")
+    s8 = torch.empty(seq, dtype=torch.float32, device="cuda")
+    cuda.norm(x, norm_w=torch.from_numpy(blk["norm1"]).cuda(), modulation=solo.modulation(0), row_map=rmap, slots=6,
+              shift_slot=0, scale_slot=1, q=q8, scales=s8)
+    _, k_all, v_all = cuda.gemm_i8_qkv_rope(w["qkv"], q8, s8, torch.from_numpy(blk["q_norm"]).cuda(),
+                                            torch.from_numpy(blk["k_norm"]).cuda(), cos, sin, 48)
+    cuda.check()
+    rows = np.unique(np.concatenate([[0, 255, 256, seq - 1, (seq - 1) // 256 * 256],
+                                     np.random.default_rng(5).integers(0, seq, n_rows)]))[:max(n_rows, 8)]
+    idx = torch.from_numpy(rows).cuda()
+    k_h, v_h = k_all.float().cpu().numpy(), v_all.float().cpu().numpy()
+    W = {n_: (w_.download_int8(), w_.download_scales()) for n_, w_ in w.items()}
+    zero = np.zeros(len(rows), np.uint32)
+
+    def linear(a, name):
+        q, s = impl.quantize_act_int8(a)
+        return impl.gemm_i8_dequant(q, W[name][0], s, W[name][1])
+
+    xr = x[idx].float().cpu().numpy()
+    a = impl.adaln(xr, blk["norm1"], mod, zero, 6, 0, 1)
+    q_r, _, _ = impl.qkv_rope(linear(a, "qkv"), blk["q_norm"], blk["k_norm"], cos_h[rows], sin_h[rows], heads, hd, 48)
+    x1 = impl.gate(xr, linear(oracle.sdpa(q_r, k_h, v_h), "o"), mod, zero, 6, 2)
+    cq = linear(impl.rms_norm(x1, blk["norm_c"]), "cq").reshape(len(rows), heads, hd)
+    ckv = linear(text.float().cpu().numpy(), "ckv")
+    ck = np.ascontiguousarray(ckv[:, :dim]).reshape(-1, heads, hd)
+    cv = np.ascontiguousarray(ckv[:, dim:]).reshape(-1, heads, hd)
+    x2 = x1 + linear(oracle.sdpa(cq, ck, cv), "co")
+    up = linear(impl.adaln(x2, blk["norm2"], mod, zero, 6, 3, 4), "up")
+    h = (0.5 * up * (1.0 + np.tanh(0.7978845608028654 * (up + 0.044715 * up ** 3)))).astype(np.float32)
+    want = impl.gate(x2, linear(h, "down"), mod, zero, 6, 5)
+    got = y[idx].float().cpu().numpy()
+    rel = float(np.linalg.norm(got - want) / np.linalg.norm(want))
+    solo.close_keep_weights()
+    return {"rows": int(len(rows)), "of_rows": int(seq), "rel_l2": rel, "bound": 2e-2, "ok": bool(rel < 2e-2),
+            "checker": "reference CPU functions" if Ref.available() else "CPU restatement"}
 
 
 def ref_available():
@@ -476,38 +590,50 @@ def profile_classes(cuda, dit, step):
     return {names[i]: {"launches": int(cnt[i]), "ms": float(ms[i])} for i in range(min(n, len(names))) if cnt[i]}
 
 
-# DRAM bytes per int8 GEMM launch of the 6,144-token block (mean of its seven GEMMs): 894 MB per block / 7.
-# The algorithmic figure (codes + weights + outputs + residuals of the seven) is 857 MB per block.
-GEMM_DRAM_BYTES_PER_LAUNCH_6144 = 127.8e6
-# DRAM bytes per attention launch of the 50,220-token block on one GPU: self-attention 1277 MB (Q, K, V read
-# and O written once: 1234 MB algorithmic), cross-attention 576 MB (624 MB algorithmic); mean of the two.
-ATTN_DRAM_BYTES_PER_LAUNCH_50220 = 926.4e6
+def traffic_per_launch(kernel, tokens):
+    """DRAM bytes per launch of the dominant kernel class, read from the table of ncu captures committed under
+    profiles/ (rows `| class | tokens | MB per launch | ... |`); None when no capture covers this workload."""
+    table = ROOT / "profiles" / "dram_traffic_per_launch.md"
+    if tokens is None or not table.exists():
+        return None
+    for line in table.read_text().splitlines():
+        cells = [c.strip() for c in line.strip().strip("|").split("|")]
+        if len(cells) >= 4 and cells[0] == kernel and cells[1].replace(",", "") == str(tokens):
+            try:
+                return float(cells[2]) * 1e6, f"{cells[3]} (profiles/dram_traffic_per_launch.md)"
+            except ValueError:
+                return None
+    return None
 
 
-def roofline(prof, lin_flops_block, attn_flops_block, n_blocks, pk):
+def roofline(prof, lin_flops_block, attn_flops_block, n_blocks, pk, probe):
     """Roofline entry for the kernel class with the largest share of the step."""
     if not prof:
         return None
     top = max(prof, key=lambda k: prof[k]["ms"])
     p = prof[top]
     per_launch_ms = p["ms"] / p["launches"]
+    extra = {}
     if top == "gemm_i8":
         flops = lin_flops_block * n_blocks / p["launches"]
-        # int8 tensor peak is not in MEASURED_PEAKS.json; the dense int8 rate of the part is twice its bf16
-        # rate, so the denominator is 2 x the measured sustained bf16 figure
-        peak = 2.0 * pk["bf16_sustained"]
-        note = f"2 x {pk['src']} sustained bf16 ({pk['bf16_sustained']} TFLOP/s): int8 runs at twice the bf16 rate"
+        # no int8 figure exists among the measured peaks: the denominator is the int8 MMA rate measured live
+        peak = probe["int8"]
+        note = "int8 tcgen05.mma rate of this GPU over about a second of back-to-back MMAs from a resident tile, measured in this run"
     elif top == "attention":
         flops = attn_flops_block * n_blocks / p["launches"]
         peak = pk["bf16_sustained"]
         note = f"{pk['src']} sustained bf16"
+        extra = {"probe_peak": probe["bf16"], "probe_note": "bf16 128x128x16 tcgen05.mma rate measured in this run"}
     else:
         return {"bound": "hbm", "kernel": top, "achieved": None, "peak": pk["hbm"], "unit": "GB/s", "frac": None,
                 "traffic": None, "share_of_step": p["ms"] / sum(v["ms"] for v in prof.values())}
     achieved = flops / (per_launch_ms * 1e-3) / 1e12
-    return {"bound": "tensor", "kernel": top, "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
-            "frac": achieved / peak, "traffic": None, "peak_note": note,
-            "share_of_step": p["ms"] / sum(v["ms"] for v in prof.values())}
+    out = {"bound": "tensor", "kernel": top, "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
+           "frac": achieved / peak, "traffic": None, "peak_note": note,
+           "share_of_step": p["ms"] / sum(v["ms"] for v in prof.values())}
+    if extra:
+        out.update(extra, frac_of_probe=achieved / extra["probe_peak"])
+    return out
 
 
 # ------------------------------------------------------------------------- single kernels
@@ -557,14 +683,9 @@ def kernel_arm(a):
         ms = _time_kernel(lambda: cuda.gemm_i8(w, x, s, kind=kind, residual=res, out=y), a.iters)
         out.update(m=a.m, n=a.n, k=a.k, epi=a.epi, ms=ms, tops=2.0 * a.m * a.n * a.k / ms / 1e9)
     elif a.kernel == "peak":
-        import ctypes as C
-        from h3c_b200.lib import call
         for kind, name in ((0, "int8"), (1, "bf16"), (2, "nvfp4"), (3, "bf16_n128_ss"), (4, "bf16_n128_ts"), (5, "nvfp4_n128")):
-            v = C.c_double(0)
-            call("h3b_umma_peak_dev", cuda.h, kind, 20000, C.byref(v))     # ~10 ms of MMAs: burst clocks
-            out[name + "_burst_tops"] = v.value
-            call("h3b_umma_peak_dev", cuda.h, kind, 2000000, C.byref(v))   # ~1 s: under the power limit
-            out[name + "_sustained_tops"] = v.value
+            out[name + "_burst_tops"] = h3c_b200.tensor_pipe_rate(cuda, kind, 20000)         # ~10 ms of MMAs: burst clocks
+            out[name + "_sustained_tops"] = h3c_b200.tensor_pipe_rate(cuda, kind, 2000000)   # ~1 s: under the power limit
     elif a.kernel == "sides":   # patch embedding, final head and Euler update of a.m tokens (f32, hidden = a.n)
         lat = torch.randn((a.m, 96), generator=g, device="cuda")
         pw, pb = torch.randn((a.n, 96), generator=g, device="cuda"), torch.randn(a.n, generator=g, device="cuda")
@@ -646,6 +767,7 @@ def main():
     ap.add_argument("--graph", action="store_true", help="replay the resident step as one CUDA graph (N = 1)")
     ap.add_argument("--skip-cpu-baseline", action="store_true", help="omit the CPU sample (profiling runs)")
     ap.add_argument("--skip-e2e", action="store_true", help="omit the host-buffer measurement (profiling runs)")
+    ap.add_argument("--skip-checks", action="store_true", help="omit the parity / sharding self-checks (profiling runs)")
     ap.add_argument("--kernel", default=None,
                     choices=["gemm", "gemm_fp4", "attn", "norm", "rope", "peak", "sides"],
                     help="time ONE operator on synthetic data instead of the step (also the ncu capture commands)")

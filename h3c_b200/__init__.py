@@ -396,6 +396,23 @@ def ulysses_local_rows(seq_pad, ulysses, rank):
     return int(load().h3_ulysses_local_rows(seq_pad, ulysses, rank))
 
 
+def tensor_pipe_rate(cuda: "Cuda", kind: int, iters: int) -> float:
+    """Tera-operations per second this GPU sustains on back-to-back tcgen05.mma from a resident tile (no loads,
+    no epilogue): kind 0 int8 128x256x32, 1 bf16 128x256x16, 2 nvfp4 128x256x64, 3 bf16 128x128x16 from shared
+    memory, 4 bf16 128x128x16 with A in tensor memory, 5 nvfp4 128x128x64.  About a second of MMAs at
+    iters = 1,000,000.  Lives in libh3_b200_probe.so, a helper of the bench."""
+    from . import build as _b
+    if not _b.PROBE.exists():
+        raise H3Error(f"{_b.PROBE} is missing: run `python -m h3c_b200.build`")
+    lib = C.CDLL(str(_b.PROBE))
+    lib.h3b_umma_peak_dev.restype = C.c_int
+    lib.h3b_umma_peak_dev.argtypes = [C.c_void_p, C.c_int, C.c_int, C.POINTER(C.c_double), C.c_char_p, C.c_size_t]
+    v, err = C.c_double(0), C.create_string_buffer(_l.ERR_LEN)
+    if lib.h3b_umma_peak_dev(cuda.h, kind, iters, C.byref(v), err, _l.ERR_LEN) != 1:
+        raise H3Error(f"h3b_umma_peak_dev: {err.value.decode(errors='replace')}")
+    return v.value
+
+
 def plugin_value(name: str):
     """Value of a registered switch (environment, else its default); raises for an unregistered name."""
     v = load().h3b_plugin_value(name.encode())
@@ -457,6 +474,15 @@ def video_rope_tables(inv_freq, text_len, grid, spatial_scale=1.0, pad_rows=0):
 
 def t_row_from_sigma(sigma, t_table_rows):
     return int(load().h3_dit_w4a8_t_row_from_sigma(C.c_float(sigma), t_table_rows))
+
+
+def ulysses_shard_rows(seq_real, world, rank, align=64):
+    """Ulysses row split (h3_dit_w4a8.c:6275-6277): pad to a multiple of 64, equal slices per rank.
+    Returns (seq_pad, seq_local, first_row, real_rows_of_this_rank)."""
+    seq_pad = ulysses_pad_seq(seq_real, align)
+    seq_local = seq_pad // world
+    first = rank * seq_local
+    return seq_pad, seq_local, first, max(0, min(seq_local, seq_real - first))
 
 
 class UlyssesComm:

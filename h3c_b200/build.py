@@ -18,6 +18,7 @@ CSRC = HERE / "csrc"
 OBJ = HERE / "_obj"
 LIB = HERE / "libh3_b200.so"
 SDPA_PLUGIN = HERE / "libh3_b200_sdpa.so"   # the attention kernel behind the reference's dlopen plugin ABI
+PROBE = HERE / "libh3_b200_probe.so"        # tensor-pipe rate probe used by the bench (not part of the product)
 
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "-Xcompiler", "-fPIC"]
@@ -65,6 +66,13 @@ def build(force: bool = False) -> Path:
     if force or _stale(SDPA_PLUGIN, [plugin_src, LIB] + hdr):
         cmd = ["gcc"] + GCC_FLAGS + ["-shared", "-I/usr/local/cuda/include", str(plugin_src), "-o", str(SDPA_PLUGIN),
                                      f"-L{HERE}", "-lh3_b200", "-Wl,-rpath,$ORIGIN", "-L/usr/local/cuda/lib64", "-lcudart"]
+        res = subprocess.run(cmd, capture_output=True, text=True)
+        if res.returncode != 0:
+            raise RuntimeError(f"{' '.join(cmd)}\n{res.stdout}{res.stderr}")
+    probe_src = CSRC / "probe" / "h3b_peak.cu"
+    if force or _stale(PROBE, [probe_src, LIB] + hdr):
+        cmd = ["nvcc"] + NVCC_FLAGS + ["-shared", str(probe_src), "-o", str(PROBE), f"-L{HERE}", "-lh3_b200", "-Xlinker",
+                                       "-rpath=$ORIGIN"]
         res = subprocess.run(cmd, capture_output=True, text=True)
         if res.returncode != 0:
             raise RuntimeError(f"{' '.join(cmd)}\n{res.stdout}{res.stderr}")

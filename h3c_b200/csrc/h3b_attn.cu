@@ -219,6 +219,11 @@ __global__ void __launch_bounds__(attn::THREADS, 1) k_attn(const __grid_constant
             // S = Q K^T : both operands K-major in shared memory (d contiguous).
             // O += P V  : P from TMEM (row = lane, two bf16 keys per 32-bit column); V as stored
             //             ([key][d], d contiguous) is the N-major form of the B operand.
+            // EMU bit 31: one lane is elected once for the whole kernel and issues every tcgen05 instruction (the
+            // commits must come from the thread that issued the MMAs they track); otherwise elect.sync runs in
+            // front of every instruction
+            const bool fixed_leader = elect_one();
+            auto leader = [&]() -> bool { return (EMU >> 31) ? fixed_leader : elect_one(); };
             constexpr uint32_t idesc_s = umma_idesc(1, Elem<T>::FMT, Elem<T>::FMT, BQ, BKV, 0, 0);
             constexpr uint32_t idesc_o = umma_idesc(1, Elem<T>::FMT, Elem<T>::FMT, BQ, HD, 0, 1);
             const uint32_t q_base = smem_u32(sQ), k_base = smem_u32(sK), v_base = smem_u32(sV);
@@ -228,17 +233,17 @@ __global__ void __launch_bounds__(attn::THREADS, 1) k_attn(const __grid_constant
 #pragma unroll
                 for (int k = 0; k < HD / 16; k++) {
                     const uint32_t off = (uint32_t)(k >> 2) * SLAB + (uint32_t)(k & 3) * 32;
-                    if (elect_one())
+                    if (leader())
                         umma_f16_ss(d_tmem, umma_desc_k_sw128(q_addr + off), umma_desc_k_sw128(k_addr + off), idesc_s,
                                     (uint32_t)(k != 0));
                 }
-                if (elect_one()) tc_commit(&s_full[t]);
+                if (leader()) tc_commit(&s_full[t]);
             };
             auto issue_pv = [&](int t, int stage, int half, bool first) {
                 const uint32_t v_addr = v_base + stage * TILE;
 #pragma unroll
                 for (int k = half * (BKV / 32); k < (half + 1) * (BKV / 32); k++)
-                    if (elect_one())
+                    if (leader())
                         umma_f16_ts(tmem_base + O_COL + 128u * t, tmem_base + S_COL + 128u * t + (uint32_t)k * 8,
                                     umma_desc_mn_sw128(v_addr + (uint32_t)k * 2048, SLAB, 1024), idesc_o,
                                     (uint32_t)(!first || k != 0));
@@ -248,7 +253,7 @@ __global__ void __launch_bounds__(attn::THREADS, 1) k_attn(const __grid_constant
             if (ok) {
                 tc_fence_after();
                 for (int t = 0; t < n_tiles; t++) issue_s(t, 0);
-                if (elect_one()) tc_commit(&k_empty[0]);
+                if (leader()) tc_commit(&k_empty[0]);
                 ok = mbar_wait(&v_full[0], 0, abort_word, p.status, H3B_ST_TIMEOUT_FULL) &&
                      (n_kv < 2 || mbar_wait(&k_full[1], 0, abort_word, p.status, H3B_ST_TIMEOUT_FULL));
             }
@@ -268,10 +273,10 @@ __global__ void __launch_bounds__(attn::THREADS, 1) k_attn(const __grid_constant
                     if (!ok) break;
                     tc_fence_after();
                     issue_pv(t, st, 1, false);
-                    if (t == n_tiles - 1 && elect_one()) tc_commit(&v_empty[st]);
+                    if (t == n_tiles - 1 && leader()) tc_commit(&v_empty[st]);
                     if (more) {
                         issue_s(t, nx);   // overwrites the tile's scores / P, in order after the P V product
-                        if (t == n_tiles - 1 && elect_one()) tc_commit(&k_empty[nx]);
+                        if (t == n_tiles - 1 && leader()) tc_commit(&k_empty[nx]);
                     }
                 }
                 // stages of the next iteration: V(j+1) in stage nx, K(j+2) in stage st
@@ -286,7 +291,7 @@ __global__ void __launch_bounds__(attn::THREADS, 1) k_attn(const __grid_constant
                 step(j, std::integral_constant<int, 0>{});
                 if (ok && j + 1 < n_kv) step(j + 1, std::integral_constant<int, 1>{});
             }
-            if (elect_one()) tc_commit(o_done);
+            if (leader()) tc_commit(o_done);
         }
         __syncwarp();
     } else {
@@ -509,6 +514,11 @@ static int launch_sdpa_impl(h3_cuda *cuda, const void *q, size_t qs, const void 
     else if (emu == 2) kernel = k_attn<__nv_bfloat16, 0x11>;
     else if (emu == 3) kernel = k_attn<__nv_bfloat16, 0x49>;
     else if (emu == 4) kernel = k_attn<__nv_bfloat16, 0x55>;
+    else if (emu == 10) kernel = k_attn<__nv_bfloat16, 0x80000000u>;
+    else if (emu == 12) kernel = k_attn<__nv_bfloat16, 0x80000011u>;
+    else if (emu == 13) kernel = k_attn<__nv_bfloat16, 0x80000049u>;
+    else if (emu == 14) kernel = k_attn<__nv_bfloat16, 0x80000055u>;
+    else if (emu == 11) kernel = k_attn<__nv_bfloat16, 0x80000001u>;
     H3B_CUDA_OK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)attn::SMEM_BYTES),
                 "sdpa smem attribute");
     dim3 grid((unsigned)ceil_div(lq, 2 * attn::BQ), (unsigned)heads);

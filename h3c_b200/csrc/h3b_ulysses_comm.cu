@@ -346,15 +346,32 @@ void h3_ulysses_comm_destroy(h3_ulysses_cfg *cfg) {
     for (int i = 0; i < st->n_local; i++) {
         cudaSetDevice(st->device[i]);
         if (st->stream[i]) cudaStreamSynchronize(st->stream[i]);
-        if (api && st->comm[i]) api->CommDestroy(st->comm[i]);
         if (st->scratch[i]) cudaFree(st->scratch[i]);
         if (i == 0) {
             cudaDeviceSynchronize();
-            for (int pr = 0; pr < st->n_ranks; pr++)
-                if (st->peer_slab[pr] && st->peer_slab[pr] != st->slab) cudaIpcCloseMemHandle(st->peer_slab[pr]);
-            if (st->slab) cudaFree(st->slab);
-            if (st->d_barrier) cudaFree(st->d_barrier);
+            // Peers store into this rank's slab from their GEMM and attention epilogues.  Before the mappings go and
+            // the slab is freed, all ranks meet in one more (bounded) barrier, so that nobody's kernels are still in
+            // flight.  If the barrier gives up (a rank left early, or one of its own barriers ran out before), the
+            // slab and the mappings are deliberately left alone until the process exits: freeing memory a peer may
+            // still be writing would fault that peer's GPU.
+            int quiesced = 1;
+            if (st->direct_ready && st->n_local == 1 && st->d_barrier) {
+                h3_ulysses_cfg tmp = *cfg;
+                int status = 0;
+                quiesced = st->flag_barrier && h3b_ulysses_barrier(&tmp, NULL, 0) && h3b_ulysses_check(&tmp, &status, NULL, 0) &&
+                           status == 0;
+                if (!st->flag_barrier) {   // the all-reduce barrier: NCCL's own time-out bounds it
+                    quiesced = h3b_ulysses_barrier(&tmp, NULL, 0) && cudaStreamSynchronize(st->compute[0]) == cudaSuccess;
+                }
+            }
+            if (quiesced) {
+                for (int pr = 0; pr < st->n_ranks; pr++)
+                    if (st->peer_slab[pr] && st->peer_slab[pr] != st->slab) cudaIpcCloseMemHandle(st->peer_slab[pr]);
+                if (st->slab) cudaFree(st->slab);
+                if (st->d_barrier) cudaFree(st->d_barrier);
+            }
         }
+        if (api && st->comm[i]) api->CommDestroy(st->comm[i]);
         if (st->ev_compute[i]) cudaEventDestroy(st->ev_compute[i]);
         if (st->ev_comm[i]) cudaEventDestroy(st->ev_comm[i]);
         if (st->stream[i]) cudaStreamDestroy(st->stream[i]);
@@ -454,77 +471,156 @@ int h3_ulysses_a2a_attn_out(h3_ulysses_cfg *cfg, const void *d_in, void *d_out, 
 
 // ---------------------------------------------------------------- direct stores over peer memory
 
-int h3b_ulysses_direct_setup(h3_ulysses_cfg *cfg, size_t seq_local, size_t heads, size_t head_dim, char *err,
-                             size_t err_size) {
-    if (!cfg || !cfg->comm) return fail(err, err_size, "ulysses direct: not inited");
-    CommState *st = (CommState *)cfg->comm;
-    NcclApi *api = nccl_api(err, err_size);
-    if (!api) return 0;
-    if (st->n_local != 1) return fail(err, err_size, "ulysses direct: needs one process per GPU");
-    if (st->direct_ready) return fail(err, err_size, "ulysses direct: already set up");
-    if (!seq_local || !heads || !head_dim || heads % (size_t)st->n_ranks || (head_dim * 2) % 16)
-        return fail(err, err_size, "ulysses direct: bad geometry (seq_local %zu, heads %zu, head_dim %zu, U %d)", seq_local,
-                    heads, head_dim, st->n_ranks);
+// The set-up protocol as a function of its steps, so that its decision logic can run on a CPU with stand-in
+// steps (tests/test_ulysses_gloo.py drives it from two gloo ranks).  Both collectives are reached by EVERY rank
+// whatever happened locally before them: a rank that bailed out early would leave its peers blocked inside a
+// collective.  All ranks return the same value; on 0 every rank has rolled back.
+int h3b_ulysses_setup_protocol(const h3b_ulysses_setup_steps *s) {
+    if (!s || !s->prepare || !s->gather || !s->map_peers || !s->agree || !s->rollback) return 0;
+    int ok = s->prepare(s->ctx) != 0;           // local: allocate the buffers, make the handle
+    if (!s->gather(s->ctx, ok)) ok = 0;         // collective: exchange the handles (a rank without one still takes part)
+    if (ok) ok = s->map_peers(s->ctx) != 0;     // local: map the peers' buffers
+    int all_ok = 0;
+    if (!s->agree(s->ctx, ok, &all_ok)) all_ok = 0;   // collective: minimum over the ranks
+    if (!all_ok) {
+        s->rollback(s->ctx);                    // local: close mappings, free buffers
+        return 0;
+    }
+    return 1;
+}
+
+namespace {
+struct DirectSetup {
+    CommState *st;
+    NcclApi *api;
+    size_t part;
+    char *d_handles;
+    char *err;
+    size_t err_size;
+};
+
+int ds_prepare(void *ctx) {
+    DirectSetup *d = (DirectSetup *)ctx;
+    CommState *st = d->st;
     const int U = st->n_ranks, rank = st->local_rank[0];
-    if (cudaSetDevice(st->device[0]) != cudaSuccess) return fail(err, err_size, "ulysses direct: set device");
-    // the four buffers have the same size: U*seq_local rows of heads/U heads = seq_local rows of all heads
-    const size_t part = (seq_local * heads * head_dim * 2 + 255) & ~(size_t)255;
-    cudaError_t e = cudaMalloc(&st->slab, 4 * part + 256);   // + one row of arrival flags
-    if (e != cudaSuccess) return cuda_fail(e, "ulysses direct: slab allocation", err, err_size);
-    e = cudaMemset(st->slab, 0, 4 * part + 256);
-    char *d_handles = NULL;
-    if (e == cudaSuccess) e = cudaMalloc((void **)&d_handles, (size_t)U * sizeof(cudaIpcMemHandle_t));
+    // the exchange buffer and the barrier words come first: both collectives need them even when the slab fails
+    cudaError_t e = cudaMalloc((void **)&d->d_handles, (size_t)U * sizeof(cudaIpcMemHandle_t));
+    if (e == cudaSuccess) e = cudaMemset(d->d_handles, 0, (size_t)U * sizeof(cudaIpcMemHandle_t));
     if (e == cudaSuccess) e = cudaMalloc((void **)&st->d_barrier, 4 * sizeof(int));
     if (e == cudaSuccess) e = cudaMemset(st->d_barrier, 0, 4 * sizeof(int));
-    cudaIpcMemHandle_t mine, all[MAX_U];
+    if (e == cudaSuccess) e = cudaMalloc(&st->slab, 4 * d->part + 256);   // + one row of arrival flags
+    if (e == cudaSuccess) e = cudaMemset(st->slab, 0, 4 * d->part + 256);
+    cudaIpcMemHandle_t mine;
     if (e == cudaSuccess) e = cudaIpcGetMemHandle(&mine, st->slab);
-    if (e == cudaSuccess)
-        e = cudaMemcpy(d_handles + (size_t)rank * sizeof(mine), &mine, sizeof(mine), cudaMemcpyHostToDevice);
-    if (e != cudaSuccess) {
-        if (d_handles) cudaFree(d_handles);
-        return cuda_fail(e, "ulysses direct: IPC handle", err, err_size);
+    if (e == cudaSuccess) e = cudaMemcpy(d->d_handles + (size_t)rank * sizeof(mine), &mine, sizeof(mine), cudaMemcpyHostToDevice);
+    if (e != cudaSuccess) return cuda_fail(e, "ulysses direct: buffers / IPC handle", d->err, d->err_size);
+    return 1;
+}
+
+int ds_gather(void *ctx, int have_handle) {
+    DirectSetup *d = (DirectSetup *)ctx;
+    CommState *st = d->st;
+    (void)have_handle;   // a rank without a handle contributes the zeros its buffer was cleared to
+    if (!d->d_handles) {
+        // not even the exchange buffer exists: fall back to a scratch word so that the collective is still entered
+        if (cudaMalloc((void **)&d->d_handles, (size_t)st->n_ranks * sizeof(cudaIpcMemHandle_t)) != cudaSuccess)
+            return fail(d->err, d->err_size, "ulysses direct: no memory for the handle exchange");
+        cudaMemset(d->d_handles, 0, (size_t)st->n_ranks * sizeof(cudaIpcMemHandle_t));
     }
-    ncclResult_t rc = api->AllGather(d_handles + (size_t)rank * sizeof(mine), d_handles, sizeof(mine), ncclInt8, st->comm[0],
-                                     st->stream[0]);
-    if (rc != ncclSuccess) {
-        cudaFree(d_handles);
-        return fail(err, err_size, "ulysses direct: ncclAllGather failed: %s", api->GetErrorString ? api->GetErrorString(rc) : "error");
-    }
-    e = cudaStreamSynchronize(st->stream[0]);
-    if (e == cudaSuccess) e = cudaMemcpy(all, d_handles, (size_t)U * sizeof(mine), cudaMemcpyDeviceToHost);
-    cudaFree(d_handles);
-    if (e != cudaSuccess) return cuda_fail(e, "ulysses direct: handle exchange", err, err_size);
+    const size_t hb = sizeof(cudaIpcMemHandle_t);
+    ncclResult_t rc = d->api->AllGather(d->d_handles + (size_t)st->local_rank[0] * hb, d->d_handles, hb, ncclInt8, st->comm[0],
+                                        st->stream[0]);
+    if (rc != ncclSuccess)
+        return fail(d->err, d->err_size, "ulysses direct: ncclAllGather failed: %s",
+                    d->api->GetErrorString ? d->api->GetErrorString(rc) : "error");
+    if (cudaStreamSynchronize(st->stream[0]) != cudaSuccess) return fail(d->err, d->err_size, "ulysses direct: handle exchange");
+    return 1;
+}
+
+int ds_map_peers(void *ctx) {
+    DirectSetup *d = (DirectSetup *)ctx;
+    CommState *st = d->st;
+    const int U = st->n_ranks, rank = st->local_rank[0];
+    cudaIpcMemHandle_t all[MAX_U];
+    cudaError_t e = cudaMemcpy(all, d->d_handles, (size_t)U * sizeof(all[0]), cudaMemcpyDeviceToHost);
+    if (e != cudaSuccess) return cuda_fail(e, "ulysses direct: handle exchange", d->err, d->err_size);
+    const cudaIpcMemHandle_t zero = {};
     int mapped = 1;
     for (int pr = 0; pr < U; pr++) {
         if (pr == rank) {
             st->peer_slab[pr] = st->slab;
             continue;
         }
+        if (!memcmp(&all[pr], &zero, sizeof(zero))) {   // that rank could not allocate: nothing to map
+            fail(d->err, d->err_size, "ulysses direct: rank %d has no buffer to share", pr);
+            mapped = 0;
+            continue;
+        }
         e = cudaIpcOpenMemHandle(&st->peer_slab[pr], all[pr], cudaIpcMemLazyEnablePeerAccess);
         if (e != cudaSuccess) {
             st->peer_slab[pr] = NULL;
-            cuda_fail(e, "ulysses direct: cudaIpcOpenMemHandle (no peer access between the GPUs?)", err, err_size);
+            cuda_fail(e, "ulysses direct: cudaIpcOpenMemHandle (no peer access between the GPUs?)", d->err, d->err_size);
             mapped = 0;
         }
     }
-    // Every rank reaches this reduction whether or not its own mappings worked, and all of them take the
-    // same decision: a rank that returned early would leave the others waiting in the collective.
-    int agreed = 0;
-    e = cudaMemcpy(st->d_barrier, &mapped, sizeof(int), cudaMemcpyHostToDevice);
-    if (e == cudaSuccess) {
-        rc = api->AllReduce(st->d_barrier, st->d_barrier + 1, 1, ncclInt32, ncclMin, st->comm[0], st->stream[0]);
-        if (rc == ncclSuccess && cudaStreamSynchronize(st->stream[0]) == cudaSuccess)
-            cudaMemcpy(&agreed, st->d_barrier + 1, sizeof(int), cudaMemcpyDeviceToHost);
+    return mapped;
+}
+
+int ds_agree(void *ctx, int ok, int *all_ok) {
+    DirectSetup *d = (DirectSetup *)ctx;
+    CommState *st = d->st;
+    *all_ok = 0;
+    // the reduction needs two device words; if even the barrier words could not be allocated, borrow the
+    // front of the handle buffer (the exchange is over)
+    int *words = st->d_barrier ? st->d_barrier : (int *)d->d_handles;
+    if (!words) return fail(d->err, d->err_size, "ulysses direct: no device word for the agreement");
+    if (cudaMemcpy(words, &ok, sizeof(int), cudaMemcpyHostToDevice) != cudaSuccess) return 0;
+    ncclResult_t rc = d->api->AllReduce(words, words + 1, 1, ncclInt32, ncclMin, st->comm[0], st->stream[0]);
+    if (rc != ncclSuccess || cudaStreamSynchronize(st->stream[0]) != cudaSuccess) return 0;
+    if (cudaMemcpy(all_ok, words + 1, sizeof(int), cudaMemcpyDeviceToHost) != cudaSuccess) return 0;
+    if (st->d_barrier) cudaMemset(st->d_barrier, 0, 2 * sizeof(int));
+    if (ok && !*all_ok) fail(d->err, d->err_size, "ulysses direct: another rank could not set up its buffers");
+    return 1;
+}
+
+void ds_rollback(void *ctx) {
+    DirectSetup *d = (DirectSetup *)ctx;
+    CommState *st = d->st;
+    for (int pr = 0; pr < st->n_ranks; pr++) {
+        if (st->peer_slab[pr] && st->peer_slab[pr] != st->slab) cudaIpcCloseMemHandle(st->peer_slab[pr]);
+        st->peer_slab[pr] = NULL;
     }
-    cudaMemset(st->d_barrier, 0, 2 * sizeof(int));
-    if (!agreed) {
-        for (int pr = 0; pr < U; pr++) {
-            if (st->peer_slab[pr] && st->peer_slab[pr] != st->slab) cudaIpcCloseMemHandle(st->peer_slab[pr]);
-            st->peer_slab[pr] = NULL;
-        }
-        if (mapped) fail(err, err_size, "ulysses direct: another rank could not map the peers' buffers");
-        return 0;
-    }
+    // no peer has written here: all ranks roll back together (the agreement above) before anyone stores
+    if (st->slab) cudaFree(st->slab);
+    if (st->d_barrier) cudaFree(st->d_barrier);
+    st->slab = NULL;
+    st->d_barrier = NULL;
+}
+}  // namespace
+
+int h3b_ulysses_direct_setup(h3_ulysses_cfg *cfg, size_t seq_local, size_t heads, size_t head_dim, char *err,
+                             size_t err_size) {
+    if (!cfg || !cfg->comm) return fail(err, err_size, "ulysses direct: not inited");
+    CommState *st = (CommState *)cfg->comm;
+    NcclApi *api = nccl_api(err, err_size);
+    if (!api) return 0;
+    // argument errors are the same on every rank (all call with the same sizes), so returning here is collective
+    if (st->n_local != 1) return fail(err, err_size, "ulysses direct: needs one process per GPU");
+    if (st->direct_ready) return fail(err, err_size, "ulysses direct: already set up");
+    if (!seq_local || !heads || !head_dim || heads % (size_t)st->n_ranks || (head_dim * 2) % 16)
+        return fail(err, err_size, "ulysses direct: bad geometry (seq_local %zu, heads %zu, head_dim %zu, U %d)", seq_local,
+                    heads, head_dim, st->n_ranks);
+    const int U = st->n_ranks, rank = st->local_rank[0];
+    // a failing cudaSetDevice is local: it is folded into `prepare` failing, the collectives below still run
+    const int device_ok = cudaSetDevice(st->device[0]) == cudaSuccess;
+    // the four buffers have the same size: U*seq_local rows of heads/U heads = seq_local rows of all heads
+    DirectSetup ds = {st, api, (seq_local * heads * head_dim * 2 + 255) & ~(size_t)255, NULL, err, err_size};
+    h3b_ulysses_setup_steps steps = {&ds, ds_prepare, ds_gather, ds_map_peers, ds_agree, ds_rollback};
+    if (!device_ok) steps.prepare = [](void *c) { return fail(((DirectSetup *)c)->err, ((DirectSetup *)c)->err_size, "ulysses direct: set device"); };
+    const int ok = h3b_ulysses_setup_protocol(&steps);
+    if (ds.d_handles) cudaFree(ds.d_handles);
+    if (!ok) return 0;
+    const size_t part = ds.part;
     h3b_ulysses_direct *d = &st->direct;
     d->ulysses = U; d->rank = rank; d->seq_local = seq_local; d->heads = heads; d->head_dim = head_dim;
     for (int pr = 0; pr < U; pr++) {

@@ -56,6 +56,13 @@ class Dit:
             w.free()
         self._weights = []
 
+    def close_keep_weights(self):
+        """Frees the context only; for a context whose weight objects belong to another one."""
+        if self.h:
+            load().h3b_dit_free(self.h)
+            self.h = None
+        self._weights = []
+
     def set_linear(self, block, which, weight):
         call("h3b_dit_set_linear", self.h, block, which, weight.h)
         self._weights.append(weight)
@@ -173,7 +180,9 @@ def _rand_w4g_weight(cuda, gen, n, k, group=128, std=0.02):
 
 def build_synthetic(cuda, geo: DitGeometry, seed=0, keep_host=False):
     """Builds a `Dit` with seeded random W4 (group 128, f16 scales) weights.  With keep_host the
-    packed weights and aux tensors are also returned per block (for oracle comparisons)."""
+    packed weights and aux tensors are also returned per block (for oracle comparisons); an integer
+    keep_host keeps the aux tensors (not the packed weights) of that many leading blocks only."""
+    aux_only = 0 if isinstance(keep_host, bool) else int(keep_host)
     import torch
     gen = torch.Generator(device=cuda.device)
     gen.manual_seed(seed)
@@ -193,7 +202,7 @@ def build_synthetic(cuda, geo: DitGeometry, seed=0, keep_host=False):
         for name, (n, k) in shapes.items():
             w, packed, scales = _rand_w4g_weight(cuda, gen, n, k)
             dit.set_linear(b, names[name], w)
-            if keep_host:
+            if keep_host and not aux_only:
                 rec[name] = (packed, scales)
         aux = {"norm1": rng.normal(1, 0.1, D), "norm2": rng.normal(1, 0.1, D), "q_norm": rng.normal(1, 0.1, geo.head_dim),
                "k_norm": rng.normal(1, 0.1, geo.head_dim)}
@@ -204,7 +213,7 @@ def build_synthetic(cuda, geo: DitGeometry, seed=0, keep_host=False):
         ada_w = rng.normal(0, 0.02, (geo.mod_rows * 6 * D, geo.t_dim)).astype(np.float32)
         ada_b = rng.normal(0, 0.02, geo.mod_rows * 6 * D).astype(np.float32)
         dit.set_adaln(b, ada_w, ada_b)
-        if keep_host:
+        if keep_host and (not aux_only or b < aux_only):
             rec.update(aux)
             rec["adaln_w"], rec["adaln_b"] = ada_w, ada_b
             host.append(rec)

@@ -101,7 +101,6 @@ _SIGS = {
     "h3_cuda_host_alloc": (vp, (sz, C.POINTER(i32))),
     "h3_cuda_host_free": (None, (vp, i32)),
     "h3b_cuda_check": (i32, (vp, C.POINTER(i32)) + _ERR),
-    "h3b_umma_peak_dev": (i32, (vp, i32, i32, dbl_p) + _ERR),
     "h3b_cuda_launch_count": (C.c_ulonglong, (vp, i32)),
     "h3b_cuda_profile_begin": (None, (vp,)),
     "h3b_cuda_profile_end": (i32, (vp, dbl_p, C.POINTER(i32), i32)),
@@ -205,6 +204,7 @@ _SIGS = {
     "h3b_ulysses_comm_init_rank": (i32, (C.POINTER(UlyssesCfg), i32, i32, vp, i32) + _ERR),
     "h3b_dit_set_ulysses": (i32, (vp, C.POINTER(UlyssesCfg)) + _ERR),
     "h3b_ulysses_direct_setup": (i32, (C.POINTER(UlyssesCfg), sz, sz, sz) + _ERR),
+    "h3b_ulysses_setup_protocol": (i32, (vp,)),
     "h3b_ulysses_direct_get": (vp, (C.POINTER(UlyssesCfg),)),
     "h3b_ulysses_direct_enable": (None, (C.POINTER(UlyssesCfg), i32)),
     "h3b_ulysses_barrier": (i32, (C.POINTER(UlyssesCfg),) + _ERR),

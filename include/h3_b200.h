@@ -87,12 +87,6 @@ int h3b_cuda_check(h3_cuda *cuda, int *status_out, char *error, size_t error_siz
  * number of classes filled. */
 void h3b_cuda_profile_begin(h3_cuda *cuda);
 int h3b_cuda_profile_end(h3_cuda *cuda, double *ms_by_class, int *launches_by_class, int n_classes);
-/* Addition.  Sustained tensor-pipe rate of this GPU: every SM issues `iters` x 4 back-to-back
- * tcgen05.mma (kind 0 int8 128x256x32, 1 bf16 128x256x16, 2 nvfp4 128x256x64, 3 bf16 128x128x16 from
- * shared memory, 4 bf16 128x128x16 with A in tensor memory and B MN-major, 5 nvfp4 128x128x64) on a resident tile,
- * no loads or epilogue; returns tera-operations per second (2*M*N*K per MMA). */
-int h3b_umma_peak_dev(h3_cuda *cuda, int kind, int iters, double *tera_ops_per_s, char *error,
-                      size_t error_size);
 /* Addition.  Kernel launches issued through this handle since the last call. */
 unsigned long long h3b_cuda_launch_count(h3_cuda *cuda, int reset);
 
@@ -783,6 +777,21 @@ int h3b_ulysses_comm_init_rank(h3_ulysses_cfg *cfg, int rank, int world_size, co
  * one-word NCCL all-reduce instead.  _check synchronises the compute stream and reports whether a barrier gave up waiting. */
 int h3b_ulysses_direct_setup(h3_ulysses_cfg *cfg, size_t seq_local, size_t heads, size_t head_dim,
                              char *err, size_t err_size);
+/* Addition: the set-up protocol of _direct_setup with its five steps supplied by the caller (the library's own
+ * steps allocate, exchange IPC handles through NCCL, map, all-reduce the outcome, roll back).  Order: prepare
+ * (local) -> gather (collective, ALWAYS reached, told whether prepare worked) -> map_peers (local, only when all
+ * is well so far) -> agree (collective, ALWAYS reached: minimum of the ranks' outcomes) -> rollback on every
+ * rank unless all agreed.  Every step returns 1 = ok / 0 = failed.  Exported so that the decision logic can be
+ * exercised with stand-in steps on a CPU. */
+typedef struct h3b_ulysses_setup_steps {
+    void *ctx;
+    int (*prepare)(void *ctx);
+    int (*gather)(void *ctx, int have_handle);
+    int (*map_peers)(void *ctx);
+    int (*agree)(void *ctx, int ok, int *all_ok);
+    void (*rollback)(void *ctx);
+} h3b_ulysses_setup_steps;
+int h3b_ulysses_setup_protocol(const h3b_ulysses_setup_steps *steps);
 const h3b_ulysses_direct *h3b_ulysses_direct_get(const h3_ulysses_cfg *cfg);
 /* Switches the use of a set-up direct path off (0) or back on (1); the mappings stay.  For launchers that
  * found the set-up failing on some rank and fall back to the exchange on all of them. */

@@ -25,7 +25,7 @@ def _worker(rank, world, port, out_dir):
     import torch.distributed as dist
     import h3c_b200
     from h3c_b200 import dit as D
-    from bench import shard_rows
+    from h3c_b200 import ulysses_shard_rows as shard_rows
     from oracle.pyoracle import Oracle
     torch.cuda.set_device(rank)
     dist.init_process_group("gloo", rank=rank, world_size=world)   # plumbing only: distributes the NCCL id
