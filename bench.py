@@ -318,22 +318,21 @@ def gpu_arm(args):
             dit.layers_forward(x_d, cos_d, sin_d, row_map=rmap_d, text=text_d, out=y_d)
 
     if args.graph and world == 1:
-        # The resident step as one CUDA graph: the chain allocates nothing after `reserve` and syncs nowhere,
-        # so its ~800 launches can be captured once and replayed (removes the host launch gaps).
+        # The resident step with its block chain as one CUDA graph, captured and replayed by the C host
+        # (h3b_dit_layers_forward_graph_dev): removes the host launch gaps of the ~800 launches of a step.
         side = torch.cuda.Stream()
         side.wait_stream(torch.cuda.current_stream())
-        with torch.cuda.stream(side):
-            cuda.use_stream(side)
-            step_resident()   # first launches of every kernel happen outside the capture
-            side.synchronize()
-            graph = torch.cuda.CUDAGraph()
-            cuda.launch_count(reset=True)
-            with torch.cuda.graph(graph, stream=side):
-                step_resident()
-            graph_launches = cuda.launch_count(reset=True)   # kernel nodes of one replay
-        torch.cuda.current_stream().wait_stream(side)
-        cuda.use_stream(torch.cuda.current_stream())
-        eager_step, step_resident = step_resident, graph.replay
+        torch.cuda.set_stream(side)
+        cuda.use_stream(side)            # capture needs a real stream
+        eager_step = step_resident
+
+        def step_resident():
+            dit.project_modulation(t_d)
+            dit.layers_forward_graph(x_d, cos_d, sin_d, row_map=rmap_d, text=text_d, out=y_d)
+
+        step_resident()                  # eager pass + capture
+        side.synchronize()
+        graph_launches = dit.graph_nodes + geo.n_blocks   # nodes of one replay + the projection launches
 
     def step_e2e():
         if world > 1:
@@ -707,12 +706,18 @@ def kernel_arm(a):
         out.update(m=a.m, n=a.n, k=a.k, ms=ms, tflops=2.0 * a.m * a.n * a.k / ms / 1e9)
     elif a.kernel == "attn":
         lk = a.lk or a.lq
-        q = torch.randn((a.lq, a.heads, 128), generator=g, device="cuda").to(torch.bfloat16)
-        k = torch.randn((lk, a.heads, 128), generator=g, device="cuda").to(torch.bfloat16)
-        v = torch.randn((lk, a.heads, 128), generator=g, device="cuda").to(torch.bfloat16)
-        o = torch.empty((a.lq, a.heads * 128), dtype=torch.bfloat16, device="cuda")
-        ms = _time_kernel(lambda: cuda.sdpa_bf16(q, k, v, out=o), a.iters)
-        out.update(lq=a.lq, lk=lk, heads=a.heads, ms=ms, tflops=4.0 * a.lq * lk * a.heads * 128 / ms / 1e9)
+        dt = torch.float16 if a.f16 else torch.bfloat16
+        q = torch.randn((a.lq, a.heads, 128), generator=g, device="cuda").to(dt)
+        k = torch.randn((lk, a.heads, 128), generator=g, device="cuda").to(dt)
+        v = torch.randn((lk, a.heads, 128), generator=g, device="cuda").to(dt)
+        o = torch.empty((a.lq, a.heads * 128), dtype=dt, device="cuda")
+        ms = _time_kernel(lambda: cuda.sdpa(q, k, v, out=o), a.iters)
+        if a.check:   # relative L2 of the first rows against f64 softmax attention computed by torch on the GPU
+            rows = min(a.lq, 512)
+            s_ = torch.einsum("qhd,khd->hqk", q[:rows].double(), k.double()) * 128 ** -0.5
+            want = torch.einsum("hqk,khd->qhd", torch.softmax(s_, dim=-1), v.double()).reshape(rows, -1)
+            out["rel_l2"] = float((o[:rows].double() - want).norm() / want.norm())
+        out.update(lq=a.lq, lk=lk, heads=a.heads, dtype="f16" if a.f16 else "bf16", ms=ms, tflops=4.0 * a.lq * lk * a.heads * 128 / ms / 1e9)
     elif a.kernel == "norm":
         x = torch.randn((a.m, a.k), generator=g, device="cuda").to(torch.bfloat16)
         q = torch.empty((a.m, a.k), dtype=torch.int8, device="cuda")
@@ -779,6 +784,8 @@ def main():
     ap.add_argument("--heads", type=int, default=24)
     ap.add_argument("--epi", default="plain", choices=["plain", "gate", "gelu", "swiglu", "qkv"])
     ap.add_argument("--plain-quant", action="store_true")
+    ap.add_argument("--f16", action="store_true", help="--kernel attn: f16 tensors instead of bf16")
+    ap.add_argument("--check", action="store_true", help="--kernel attn: also report the error against f64 attention")
     ap.add_argument("--iters", type=int, default=20)
     args = ap.parse_args()
     if args.kernel:

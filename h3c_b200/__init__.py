@@ -307,6 +307,20 @@ class Cuda:
              hd, scale, ptr(out), out.stride(0))
         return out
 
+    def sdpa(self, q, k, v, scale=None, out=None):
+        """q [lq,H,128], k/v [lk,H,128], all bf16 or all f16, any row / head strides that are multiples of 8
+        elements -> [lq, H*128] of the same type (h3b_sdpa_strided_dev)."""
+        import torch
+        lq, heads, hd = q.shape
+        lk = k.shape[0]
+        scale = float(scale if scale is not None else hd ** -0.5)
+        if out is None:
+            out = torch.empty((lq, heads * hd), dtype=q.dtype, device=q.device)
+        dtype = {torch.bfloat16: 1, torch.float16: 2}[q.dtype]
+        call("h3b_sdpa_strided_dev", self.h, dtype, ptr(q), q.stride(0), q.stride(1), ptr(k), k.stride(0), k.stride(1),
+             ptr(v), v.stride(0), v.stride(1), lq, lk, heads, hd, scale, ptr(out), out.stride(0), hd)
+        return out
+
     def sdpa_f16_dev(self, q, k, v, scale=None):
         import torch
         seq, heads, hd = q.shape

@@ -21,6 +21,16 @@
 //               to the mapped buffer of the rank that owns the row.
 // TMEM (512 columns): S_A 0..127, S_B 128..255 (P overlays the first 64 columns of each),
 // O_A 256..383, O_B 384..511.
+//
+// Measured and rejected forms (B200 under its 1000 W limit, where a long run of this kernel is power-bound at
+// about 1.5 GHz, so extra instructions or operand traffic cost more than the pipeline bubbles they remove):
+//   - scores of the next key tile issued as two 64-key halves, the half that P does not overlay early: an
+//     M = 128, N = 64 product re-reads the whole Q operand from shared memory for half the work, -15 %;
+//   - two softmax threads per row (16 softmax warps, row maxima and sums exchanged through shared memory): equal
+//     without FMA-pipe exponentials, -10 % with them;
+//   - exponent offset taken from the previous key tile so that the row maximum leaves the path score ->
+//     probability: -6 %;
+//   - packed f16 exponentials (ex2.approx.f16x2) in the f16 form: -10 %.
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
@@ -320,15 +330,16 @@ __global__ void __launch_bounds__(attn::THREADS, 1) k_attn(const __grid_constant
                 for (int i = 0; i < BKV; i++)
                     if (i >= valid) sv[i] = 0xff800000u;   // -inf: exp2 gives 0
             }
-            float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
+            // eight independent chains of three-input maxima (eight dependent steps instead of sixteen)
+            float mxc[8];
 #pragma unroll
-            for (int i = 0; i < BKV; i += 8) {
-                mx0 = max3(mx0, __uint_as_float(sv[i]), __uint_as_float(sv[i + 1]));
-                mx1 = max3(mx1, __uint_as_float(sv[i + 2]), __uint_as_float(sv[i + 3]));
-                mx2 = max3(mx2, __uint_as_float(sv[i + 4]), __uint_as_float(sv[i + 5]));
-                mx3 = max3(mx3, __uint_as_float(sv[i + 6]), __uint_as_float(sv[i + 7]));
-            }
-            const float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
+            for (int c = 0; c < 8; c++) mxc[c] = -INFINITY;
+#pragma unroll
+            for (int i = 0; i < BKV; i += 16)
+#pragma unroll
+                for (int c = 0; c < 8; c++)
+                    mxc[c] = max3(mxc[c], __uint_as_float(sv[i + 2 * c]), __uint_as_float(sv[i + 2 * c + 1]));
+            const float mx = fmaxf(max3(mxc[0], mxc[1], mxc[2]), fmaxf(max3(mxc[3], mxc[4], mxc[5]), fmaxf(mxc[6], mxc[7])));
             const float m_new = fmaxf(m_run, mx * p.scale_log2);
             const bool grow_me = (m_new - m_run) > 8.0f;   // also true on the first tile (m_run = -inf)
             if (__any_sync(0xffffffffu, grow_me)) {
@@ -355,9 +366,8 @@ __global__ void __launch_bounds__(attn::THREADS, 1) k_attn(const __grid_constant
             // probabilities -> bf16 pairs -> TMEM, over the score columns (already in registers)
             float l0 = 0.0f, l1 = 0.0f, l2 = 0.0f, l3 = 0.0f;
             const float neg_m = -m_run;
-#pragma unroll
-            for (int ch = 0; ch < BKV / 32; ch++) {
-                uint32_t packed[16];
+            // 32 probabilities of chunk `ch` -> 16 packed words
+            auto chunk = [&](int ch, uint32_t (&packed)[16]) {
 #pragma unroll
                 for (int i = 0; i < 32; i += 4) {
                     float x0, x1, x2, x3;
@@ -375,14 +385,27 @@ __global__ void __launch_bounds__(attn::THREADS, 1) k_attn(const __grid_constant
                     packed[i >> 1] = Elem<T>::pack(p0, p1);
                     packed[(i >> 1) + 1] = Elem<T>::pack(p2, p3);
                 }
-                tmem_st_32x32b_x16(s_addr + ch * 16, packed);
-                if (ch & 1) {   // a half (64 keys) of P is complete: hand it to the MMA warp
-                    tmem_st_wait();
-                    tc_fence_before();
-                    __syncwarp();
-                    if (lane == 0) mbar_arrive(&p_full[2 * t + (ch >> 1)]);
-                }
-            }
+            };
+            // a half (64 keys) of P is in tensor memory: hand it to the MMA warp
+            auto hand_over = [&](int half) {
+                tmem_st_wait();
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&p_full[2 * t + half]);
+            };
+            // The stores of the first half are waited for only after the exponentials of the third chunk have
+            // been computed: the store latency hides behind arithmetic instead of stalling the warp twice per step.
+            uint32_t pk[16];
+            chunk(0, pk);
+            tmem_st_32x32b_x16(s_addr, pk);
+            chunk(1, pk);
+            tmem_st_32x32b_x16(s_addr + 16, pk);
+            chunk(2, pk);
+            hand_over(0);
+            tmem_st_32x32b_x16(s_addr + 32, pk);
+            chunk(3, pk);
+            tmem_st_32x32b_x16(s_addr + 48, pk);
+            hand_over(1);
             const float l_add = (l0 + l1) + (l2 + l3);
             l_run += l_add;
         }
@@ -506,19 +529,21 @@ static int launch_sdpa_impl(h3_cuda *cuda, const void *q, size_t qs, const void 
             p.sc_out[r] = sc->peer_att[r];
         }
     }
-    // share of the exponentials moved from the special-function unit to the FMA pipe: H3B_ATTN_EMU = 0, 2, 3, 4
-    // (eighths); the f16 form keeps the hardware exponential (its probabilities carry three more bits)
+    // Variant of the kernel (H3B_ATTN_EMU): 12 (default) = one lane elected once issues every tcgen05 instruction and
+    // two eighths of the exponentials run on the FMA pipe; 13 = three eighths; 10 = none; 0 = none, and a lane is
+    // elected in front of every instruction.
     static const int emu = atoi(h3_plugin_value("H3B_ATTN_EMU"));
-    void (*kernel)(const AttnParams) = k_attn<__nv_bfloat16, 0>;
-    if (f16) kernel = k_attn<__half, 0>;
-    else if (emu == 2) kernel = k_attn<__nv_bfloat16, 0x11>;
-    else if (emu == 3) kernel = k_attn<__nv_bfloat16, 0x49>;
-    else if (emu == 4) kernel = k_attn<__nv_bfloat16, 0x55>;
-    else if (emu == 10) kernel = k_attn<__nv_bfloat16, 0x80000000u>;
-    else if (emu == 12) kernel = k_attn<__nv_bfloat16, 0x80000011u>;
-    else if (emu == 13) kernel = k_attn<__nv_bfloat16, 0x80000049u>;
-    else if (emu == 14) kernel = k_attn<__nv_bfloat16, 0x80000055u>;
-    else if (emu == 11) kernel = k_attn<__nv_bfloat16, 0x80000001u>;
+    constexpr uint32_t LEAD = 0x80000000u;
+    void (*kernel)(const AttnParams) = nullptr;
+    if (f16) {
+        kernel = k_attn<__half, LEAD | 0x11>;
+        if (emu == 0) kernel = k_attn<__half, 0>;
+    } else {
+        kernel = k_attn<__nv_bfloat16, LEAD | 0x11>;
+        if (emu == 0) kernel = k_attn<__nv_bfloat16, 0>;
+        else if (emu == 10) kernel = k_attn<__nv_bfloat16, LEAD>;
+        else if (emu == 13) kernel = k_attn<__nv_bfloat16, LEAD | 0x49>;
+    }
     H3B_CUDA_OK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)attn::SMEM_BYTES),
                 "sdpa smem attribute");
     dim3 grid((unsigned)ceil_div(lq, 2 * attn::BQ), (unsigned)heads);

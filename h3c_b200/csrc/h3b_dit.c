@@ -51,6 +51,17 @@ struct h3b_dit {
     uint32_t *st_map;
     float *st_cos, *st_sin, *st_t;
     h3_ulysses_cfg *uly;    /* attached per-rank communicator, or NULL */
+    /* the chain captured as one CUDA graph (h3b_dit_layers_forward_graph_dev) and what it was captured for */
+    cudaGraph_t graph;
+    cudaGraphExec_t graph_exec;
+    struct {
+        unsigned first, n;
+        const void *x, *text;
+        void *y;
+        const uint32_t *row_map;
+        const float *cos, *sin;
+        size_t seq, text_seq;
+    } graph_key;
 };
 
 static int fail(char *error, size_t error_size, const char *fmt, ...) {
@@ -120,7 +131,15 @@ h3b_dit *h3b_dit_create(h3_cuda *cuda, const h3b_dit_config *cfg, char *error, s
     return d;
 }
 
+static void drop_graph(h3b_dit *d) {
+    if (d->graph_exec) cudaGraphExecDestroy(d->graph_exec);
+    if (d->graph) cudaGraphDestroy(d->graph);
+    d->graph_exec = NULL;
+    d->graph = NULL;
+}
+
 static void free_ws(h3b_dit *d) {
+    drop_graph(d);   /* a captured chain points into the workspace */
     void **p[] = {&d->xa, &d->xb, &d->io, &d->qkv, &d->wide, &d->q, &d->k, &d->v, &d->att, &d->cq, &d->ckv, (void **)&d->q8,
                   (void **)&d->s8, (void **)&d->tq8, (void **)&d->ts8, (void **)&d->st_x, (void **)&d->st_text,
                   &d->text_dev, (void **)&d->st_map, (void **)&d->st_cos, (void **)&d->st_sin, (void **)&d->st_t};
@@ -474,6 +493,63 @@ int h3b_dit_layers_forward_dev(h3b_dit *d, unsigned first, unsigned n, const voi
         cur = d_y;
     }
     return 1;
+}
+
+/* The block chain as ONE CUDA graph launch (the reference captures its step the same way,
+ * h3_dit_w4a8.c:4390 run_all_blocks_device under H3_DIT_W4A8_CUDA_GRAPH).  The first call for a set of arguments
+ * runs the chain once eagerly (every kernel gets loaded, the workspace gets its size), then captures the same
+ * launches on the handle's stream and instantiates the graph; later calls with the SAME arguments only replay it.
+ * Different arguments re-capture.  The chain reads the projected modulation through pointers that stay fixed, so
+ * h3b_dit_project_modulation between replays is honoured. */
+int h3b_dit_layers_forward_graph_dev(h3b_dit *d, unsigned first, unsigned n, const void *d_x, size_t seq,
+                                     const uint32_t *d_row_map, const float *d_cos, const float *d_sin, const void *d_text,
+                                     size_t text_seq, void *d_y, char *error, size_t error_size) {
+    cudaStream_t st;
+    cudaError_t e;
+    int ok;
+    if (!d || !n || first + n > d->cfg.n_blocks) return fail(error, error_size, "layers_forward_graph: bad block range");
+    if (d->uly && d->uly->comm) return fail(error, error_size, "layers_forward_graph: a Ulysses communicator is attached");
+    st = (cudaStream_t)h3_cuda_op_stream(d->cuda);
+    if (!st) return fail(error, error_size, "layers_forward_graph: set an op stream first (the legacy default stream cannot be captured)");
+    if (d->graph_exec && d->graph_key.first == first && d->graph_key.n == n && d->graph_key.x == d_x && d->graph_key.seq == seq &&
+        d->graph_key.row_map == d_row_map && d->graph_key.cos == d_cos && d->graph_key.sin == d_sin &&
+        d->graph_key.text == d_text && d->graph_key.text_seq == text_seq && d->graph_key.y == d_y) {
+        e = cudaGraphLaunch(d->graph_exec, st);
+        if (e != cudaSuccess) return fail(error, error_size, "cudaGraphLaunch: %s", cudaGetErrorString(e));
+        return 1;
+    }
+    drop_graph(d);
+    /* eager pass: loads the kernels, sizes the workspace, produces this call's result */
+    if (!h3b_dit_layers_forward_dev(d, first, n, d_x, seq, d_row_map, d_cos, d_sin, d_text, text_seq, d_y, error, error_size)) return 0;
+    e = cudaStreamSynchronize(st);
+    if (e != cudaSuccess) return fail(error, error_size, "layers_forward_graph: %s", cudaGetErrorString(e));
+    e = cudaStreamBeginCapture(st, cudaStreamCaptureModeThreadLocal);
+    if (e != cudaSuccess) return fail(error, error_size, "cudaStreamBeginCapture: %s", cudaGetErrorString(e));
+    h3_cuda_set_graph_capture(d->cuda, 1);   /* growth of scratch and event timing are off while capturing */
+    ok = h3b_dit_layers_forward_dev(d, first, n, d_x, seq, d_row_map, d_cos, d_sin, d_text, text_seq, d_y, error, error_size);
+    h3_cuda_set_graph_capture(d->cuda, 0);
+    e = cudaStreamEndCapture(st, &d->graph);
+    if (!ok || e != cudaSuccess || !d->graph) {
+        drop_graph(d);
+        if (ok) fail(error, error_size, "cudaStreamEndCapture: %s", cudaGetErrorString(e));
+        return 0;
+    }
+    e = cudaGraphInstantiate(&d->graph_exec, d->graph, 0);
+    if (e != cudaSuccess) {
+        drop_graph(d);
+        return fail(error, error_size, "cudaGraphInstantiate: %s", cudaGetErrorString(e));
+    }
+    d->graph_key.first = first; d->graph_key.n = n; d->graph_key.x = d_x; d->graph_key.seq = seq;
+    d->graph_key.row_map = d_row_map; d->graph_key.cos = d_cos; d->graph_key.sin = d_sin; d->graph_key.text = d_text;
+    d->graph_key.text_seq = text_seq; d->graph_key.y = d_y;
+    return 1;
+}
+
+/* Kernel nodes of the captured chain (0 when nothing is captured). */
+size_t h3b_dit_graph_nodes(const h3b_dit *d) {
+    size_t nodes = 0;
+    if (!d || !d->graph || cudaGraphGetNodes(d->graph, NULL, &nodes) != cudaSuccess) return 0;
+    return nodes;
 }
 
 static int layers_forward_host(h3b_dit *d, unsigned first, unsigned n, const float *t_feat, const float *x, size_t seq,

@@ -108,6 +108,20 @@ class Dit:
              ptr(text), 0 if text is None else text.shape[0], ptr(out))
         return out
 
+    def layers_forward_graph(self, x, cos, sin, *, first=0, n=None, row_map=None, text=None, out=None):
+        """The chain as one CUDA graph launch: captured by the C host on the first call for these tensors, replayed
+        on the following ones."""
+        import torch
+        n = self.geo.n_blocks - first if n is None else n
+        out = torch.empty_like(x) if out is None else out
+        call("h3b_dit_layers_forward_graph_dev", self.h, first, n, ptr(x), x.shape[0], ptr(row_map), ptr(cos), ptr(sin),
+             ptr(text), 0 if text is None else text.shape[0], ptr(out))
+        return out
+
+    @property
+    def graph_nodes(self):
+        return int(load().h3b_dit_graph_nodes(self.h))
+
     def layers_forward_f32(self, t_feat, x, cos, sin, *, first=0, n=None, row_map=None, text=None, out=None):
         """Host arrays in, host array out (pinned torch tensors or numpy arrays)."""
         n = self.geo.n_blocks - first if n is None else n

@@ -178,6 +178,8 @@ _SIGS = {
     "h3b_dit_reserve": (i32, (vp, sz, sz) + _ERR),
     "h3b_dit_block_forward_dev": (i32, (vp, C.c_uint, vp, sz, vp, vp, vp, vp, vp, sz, vp) + _ERR),
     "h3b_dit_layers_forward_dev": (i32, (vp, C.c_uint, C.c_uint, vp, sz, vp, vp, vp, vp, sz, vp) + _ERR),
+    "h3b_dit_layers_forward_graph_dev": (i32, (vp, C.c_uint, C.c_uint, vp, sz, vp, vp, vp, vp, sz, vp) + _ERR),
+    "h3b_dit_graph_nodes": (sz, (vp,)),
     "h3b_dit_layers_forward_f32": (i32, (vp, C.c_uint, C.c_uint, vp, vp, sz, vp, vp, vp, vp, sz, vp) + _ERR),
     "h3b_dit_launches_per_block": (i32, (vp,)),
     "h3_cuda_gemm_fp4_bs_dev": (i32, (vp, vp, vp, vp, vp, sz, sz, sz, vp, dbl_p) + _ERR),

@@ -675,6 +675,16 @@ int h3b_dit_layers_forward_dev(h3b_dit *dit, unsigned first_block, unsigned n_bl
                                size_t seq, const uint32_t *d_row_map, const float *d_rope_cos,
                                const float *d_rope_sin, const void *d_text, size_t text_seq, void *d_y,
                                char *error, size_t error_size);
+/* The same chain as ONE CUDA graph launch (the reference's whole-step graph, h3_dit_w4a8.c:4390 under
+ * H3_DIT_W4A8_CUDA_GRAPH).  The first call for a set of arguments runs the chain eagerly, then captures it on the
+ * handle's op stream (which must be a real stream, not the legacy default one) and instantiates the graph; later
+ * calls with the same arguments replay it; other arguments re-capture.  Not available with a communicator
+ * attached.  _graph_nodes: nodes of the captured graph, 0 if none. */
+int h3b_dit_layers_forward_graph_dev(h3b_dit *dit, unsigned first_block, unsigned n_blocks, const void *d_x,
+                                     size_t seq, const uint32_t *d_row_map, const float *d_rope_cos,
+                                     const float *d_rope_sin, const void *d_text, size_t text_seq, void *d_y,
+                                     char *error, size_t error_size);
+size_t h3b_dit_graph_nodes(const h3b_dit *dit);
 /* Host f32 in / host f32 out, like h3_dit_w4a8_layers_forward_f32: uploads x (and text), the
  * time feature, row map and rope tables, runs the chain, downloads y.  row_map NULL = all zeros. */
 int h3b_dit_layers_forward_f32(h3b_dit *dit, unsigned first_block, unsigned n_blocks,

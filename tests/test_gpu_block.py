@@ -102,6 +102,32 @@ def test_cross_gelu_block_bf16_stream(cuda, oracle):
     dit.close()
 
 
+def test_block_at_the_cpu_plumbing_config_shape(cuda, oracle):
+    """The benchmark's first configuration at its stated shape: hidden 3072, 24 x 128 heads, FFN 12288 with
+    tanh-GELU, 1,024 video tokens (16 x 16 patches x 4 latent frames) + 256 text tokens, seed 0.  The GPU block
+    (int4 group-128 weights, int8 activations, bf16 stream) against the CPU block at the same precision and against
+    the f32 CPU block; the f32 block's FNV-1a checksum (h3_dit_w4a8.c:8911) is printed for the record."""
+    geo, dit, host, x, text, t_feat, cos, sin = make_cross_case(cuda, oracle, 0, (4, 16, 16), 256, 3072, 24, 12288)
+    assert x.shape == (1024, 3072) and text.shape == (256, 3072)
+    dit.project_modulation(dev(t_feat))
+    xb, tb = dev(x, torch.bfloat16), dev(text, torch.bfloat16)
+    rmap = torch.zeros(x.shape[0], dtype=torch.int32, device="cuda")
+    y = dit.block_forward(0, xb, dev(cos), dev(sin), text=tb, row_map=rmap)
+    cuda.check()
+    xh, th = xb.float().cpu().numpy(), tb.float().cpu().numpy()
+    kw = dict(heads=24, head_dim=128, ffn=12288)
+    same = oracle.block_b(oracle_weights(oracle, host[0], t_feat, True), xh, th, cos, sin, quantised=True, bf16_stream=True, **kw)
+    full = oracle.block_b(oracle_weights(oracle, host[0], t_feat, False), xh, th, cos, sin, quantised=False, bf16_stream=False, **kw)
+    got = y.float().cpu().numpy()
+    e_same, e_full = rel_l2(got, same), rel_l2(got, full)
+    print(f"config 0 shape: rel-L2 {e_same:.2e} vs the same-precision CPU block, {e_full:.2e} vs the f32 CPU block; "
+          f"FNV-1a of the f32 CPU block output 0x{oracle.checksum_f32(full):016x}")
+    # the checker's "same precision" block keeps f32 attention probabilities where the kernel rounds them to bf16;
+    # over 1,024 + 256 keys and 24 heads that is 4e-3 here (2e-3 on the miniature shapes of the other tests)
+    assert e_same < 6e-3 and e_full < 2e-2
+    dit.close()
+
+
 def test_chain_host_entry_point_matches_device_chain(cuda, oracle):
     """h3b_dit_layers_forward_f32 (host buffers in/out) == cast + device chain, and two chained blocks
     agree with the oracle applied twice."""
@@ -119,6 +145,43 @@ def test_chain_host_entry_point_matches_device_chain(cuda, oracle):
                              ffn=512, quantised=True, bf16_stream=True)
     assert rel_l2(y_host, cur) < 3e-3
     assert dit.launches_per_block == 16
+    dit.close()
+
+
+def test_chain_as_cuda_graph_in_the_c_host(cuda, oracle):
+    """h3b_dit_layers_forward_graph_dev: the C host captures the chain on the first call and replays it afterwards;
+    replays follow a changed input, a re-projected modulation, and give the bits of the launched chain."""
+    geo, dit, host, x, text, t_feat, cos, sin = make_cross_case(cuda, oracle, 7, (2, 8, 8), 32, 256, 2, 512, n_blocks=2)
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        cuda.use_stream(side)            # capture needs a real stream
+        d_x, d_text = dev(x, torch.bfloat16), dev(text, torch.bfloat16)
+        d_cos, d_sin, d_t = dev(cos), dev(sin), dev(t_feat)
+        rmap = torch.zeros(x.shape[0], dtype=torch.int32, device="cuda")
+        out = torch.empty_like(d_x)
+        dit.project_modulation(d_t)
+        want = dit.layers_forward(d_x, d_cos, d_sin, text=d_text, row_map=rmap).clone()
+        assert dit.graph_nodes == 0
+        y1 = dit.layers_forward_graph(d_x, d_cos, d_sin, text=d_text, row_map=rmap, out=out).clone()     # eager + capture
+        nodes = dit.graph_nodes
+        assert nodes >= 2 * dit.launches_per_block
+        cuda.launch_count(reset=True)
+        y2 = dit.layers_forward_graph(d_x, d_cos, d_sin, text=d_text, row_map=rmap, out=out).clone()     # replay
+        assert cuda.launch_count() == 0 and dit.graph_nodes == nodes       # nothing launched by the host code
+        side.synchronize()
+        assert torch.equal(y1, want) and torch.equal(y2, want)
+        # same buffers, new contents and a new time feature: the replay must follow both
+        d_x.copy_(dev(np.random.default_rng(8).normal(0, 1, x.shape).astype(np.float32), torch.bfloat16))
+        d_t.copy_(dev((t_feat * 0.5).astype(np.float32)))
+        dit.project_modulation(d_t)
+        y3 = dit.layers_forward_graph(d_x, d_cos, d_sin, text=d_text, row_map=rmap, out=out).clone()
+        want3 = dit.layers_forward(d_x, d_cos, d_sin, text=d_text, row_map=rmap)
+        side.synchronize()
+        cuda.check()
+        assert torch.equal(y3, want3) and not torch.equal(y3, want)
+    torch.cuda.current_stream().wait_stream(side)
+    cuda.use_stream(torch.cuda.current_stream())
     dit.close()
 
 
