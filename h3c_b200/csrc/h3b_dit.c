@@ -138,17 +138,32 @@ static void drop_graph(h3b_dit *d) {
     d->graph = NULL;
 }
 
-static void free_ws(h3b_dit *d) {
-    drop_graph(d);   /* a captured chain points into the workspace */
-    void **p[] = {&d->xa, &d->xb, &d->io, &d->qkv, &d->wide, &d->q, &d->k, &d->v, &d->att, &d->cq, &d->ckv, (void **)&d->q8,
-                  (void **)&d->s8, (void **)&d->tq8, (void **)&d->ts8, (void **)&d->st_x, (void **)&d->st_text,
-                  &d->text_dev, (void **)&d->st_map, (void **)&d->st_cos, (void **)&d->st_sin, (void **)&d->st_t};
+/* The workspace is two groups of buffers that grow independently and never shrink: those sized by the token
+ * count (cq, the cross-attention queries, included) and those sized by the text length. */
+static void free_group(void ***p, size_t n) {
     size_t i;
-    for (i = 0; i < sizeof(p) / sizeof(p[0]); i++) {
+    for (i = 0; i < n; i++) {
         if (*p[i]) cudaFree(*p[i]);
         *p[i] = NULL;
     }
-    d->cap_seq = d->cap_text = 0;
+}
+static void free_seq_ws(h3b_dit *d) {
+    void **p[] = {&d->xa, &d->xb, &d->io, &d->qkv, &d->wide, &d->q, &d->k, &d->v, &d->att, &d->cq, (void **)&d->q8,
+                  (void **)&d->s8, (void **)&d->st_x, (void **)&d->st_map, (void **)&d->st_cos, (void **)&d->st_sin,
+                  (void **)&d->st_t};
+    drop_graph(d);   /* a captured chain points into the workspace */
+    free_group(p, sizeof(p) / sizeof(p[0]));
+    d->cap_seq = 0;
+}
+static void free_text_ws(h3b_dit *d) {
+    void **p[] = {&d->ckv, (void **)&d->tq8, (void **)&d->ts8, (void **)&d->st_text, &d->text_dev};
+    drop_graph(d);
+    free_group(p, sizeof(p) / sizeof(p[0]));
+    d->cap_text = 0;
+}
+static void free_ws(h3b_dit *d) {
+    free_seq_ws(d);
+    free_text_ws(d);
 }
 
 void h3b_dit_free(h3b_dit *d) {
@@ -232,39 +247,51 @@ const float *h3b_dit_modulation(h3b_dit *d, unsigned block) {
 
 int h3b_dit_reserve(h3b_dit *d, size_t seq, size_t text_seq, char *error, size_t error_size) {
     size_t D, I, F, widest, es, table_rows;
+    const int cross = d && d->cfg.kind == H3B_BLOCK_CROSS_GELU;
+    int grow_seq, grow_text;
     if (!d || !seq) return fail(error, error_size, "h3b_dit_reserve: invalid arguments");
-    if (seq <= d->cap_seq && text_seq <= d->cap_text) return 1;
+    grow_seq = seq > d->cap_seq;
+    grow_text = cross && (text_seq > d->cap_text || !d->ckv);
+    if (!grow_seq && !grow_text) return 1;
     if (h3_cuda_graph_capture(d->cuda)) return fail(error, error_size, "workspace growth is forbidden during graph capture");
     cudaStreamSynchronize((cudaStream_t)h3_cuda_op_stream(d->cuda));
-    free_ws(d);
     D = d->cfg.dim; I = inner(d); F = d->cfg.ffn; es = elem(d);
-    table_rows = seq * (size_t)((d->uly && d->uly->comm) ? d->uly->ulysses : 1);
-    widest = D > F ? D : F;
-    if (I > widest) widest = I;
-    if (!dmalloc(&d->xa, seq * D * es, error, error_size) || !dmalloc(&d->xb, seq * D * es, error, error_size) ||
-        !dmalloc(&d->io, seq * D * es, error, error_size) ||
-        !dmalloc(&d->qkv, seq * 3 * I * es, error, error_size) || !dmalloc(&d->wide, seq * F * es, error, error_size) ||
-        !dmalloc(&d->q, seq * I * 2, error, error_size) || !dmalloc(&d->k, seq * I * 2, error, error_size) ||
-        !dmalloc(&d->v, seq * I * 2, error, error_size) || !dmalloc(&d->att, seq * I * 2, error, error_size) ||
-        !dmalloc((void **)&d->q8, seq * widest, error, error_size) ||
-        !dmalloc((void **)&d->s8, seq * sizeof(float), error, error_size) ||
-        !dmalloc((void **)&d->st_x, seq * D * sizeof(float), error, error_size) ||
-        !dmalloc((void **)&d->st_map, seq * sizeof(uint32_t), error, error_size) ||
-        !dmalloc((void **)&d->st_cos, table_rows * (d->cfg.rope_half ? d->cfg.rope_half : 1) * sizeof(float), error, error_size) ||
-        !dmalloc((void **)&d->st_sin, table_rows * (d->cfg.rope_half ? d->cfg.rope_half : 1) * sizeof(float), error, error_size) ||
-        !dmalloc((void **)&d->st_t, (d->cfg.t_dim ? d->cfg.t_dim : 1) * sizeof(float), error, error_size))
-        return 0;
-    if (d->cfg.kind == H3B_BLOCK_CROSS_GELU) {
+    if (grow_seq) {
+        /* only the group that is too small is released and allocated again, at the size asked for */
+        free_seq_ws(d);
+        table_rows = seq * (size_t)((d->uly && d->uly->comm) ? d->uly->ulysses : 1);
+        widest = D > F ? D : F;
+        if (I > widest) widest = I;
+        if (!dmalloc(&d->xa, seq * D * es, error, error_size) || !dmalloc(&d->xb, seq * D * es, error, error_size) ||
+            !dmalloc(&d->io, seq * D * es, error, error_size) ||
+            !dmalloc(&d->qkv, seq * 3 * I * es, error, error_size) || !dmalloc(&d->wide, seq * F * es, error, error_size) ||
+            !dmalloc(&d->q, seq * I * 2, error, error_size) || !dmalloc(&d->k, seq * I * 2, error, error_size) ||
+            !dmalloc(&d->v, seq * I * 2, error, error_size) || !dmalloc(&d->att, seq * I * 2, error, error_size) ||
+            !dmalloc((void **)&d->q8, seq * widest, error, error_size) ||
+            !dmalloc((void **)&d->s8, seq * sizeof(float), error, error_size) ||
+            !dmalloc((void **)&d->st_x, seq * D * sizeof(float), error, error_size) ||
+            !dmalloc((void **)&d->st_map, seq * sizeof(uint32_t), error, error_size) ||
+            !dmalloc((void **)&d->st_cos, table_rows * (d->cfg.rope_half ? d->cfg.rope_half : 1) * sizeof(float), error, error_size) ||
+            !dmalloc((void **)&d->st_sin, table_rows * (d->cfg.rope_half ? d->cfg.rope_half : 1) * sizeof(float), error, error_size) ||
+            !dmalloc((void **)&d->st_t, (d->cfg.t_dim ? d->cfg.t_dim : 1) * sizeof(float), error, error_size) ||
+            (cross && !dmalloc(&d->cq, seq * I * 2, error, error_size))) {
+            free_seq_ws(d);   /* a half-built group must not pass for capacity */
+            return 0;
+        }
+        d->cap_seq = seq;
+    }
+    if (grow_text) {
         size_t t = text_seq ? text_seq : 1;
-        if (!dmalloc(&d->cq, seq * I * 2, error, error_size) || !dmalloc(&d->ckv, t * 2 * I * 2, error, error_size) ||
-            !dmalloc((void **)&d->tq8, t * D, error, error_size) ||
+        free_text_ws(d);
+        if (!dmalloc(&d->ckv, t * 2 * I * 2, error, error_size) || !dmalloc((void **)&d->tq8, t * D, error, error_size) ||
             !dmalloc((void **)&d->ts8, t * sizeof(float), error, error_size) ||
             !dmalloc((void **)&d->st_text, t * D * sizeof(float), error, error_size) ||
-            !dmalloc(&d->text_dev, t * D * es, error, error_size))
+            !dmalloc(&d->text_dev, t * D * es, error, error_size)) {
+            free_text_ws(d);
             return 0;
+        }
+        d->cap_text = text_seq;
     }
-    d->cap_seq = seq;
-    d->cap_text = text_seq;
     return 1;
 }
 
@@ -567,18 +594,25 @@ static int layers_forward_host(h3b_dit *d, unsigned first, unsigned n, const flo
     table_rows = uly ? seq * (size_t)d->uly->ulysses : seq;
     st = (cudaStream_t)h3_cuda_op_stream(d->cuda);
     D = d->cfg.dim; rh = d->cfg.rope_half;
-    cudaMemcpyAsync(d->st_x, x, seq * D * sizeof(float), cudaMemcpyHostToDevice, st);
-    cudaMemcpyAsync(d->st_t, t_feat, d->cfg.t_dim * sizeof(float), cudaMemcpyHostToDevice, st);
-    if (row_map) cudaMemcpyAsync(d->st_map, row_map, seq * sizeof(uint32_t), cudaMemcpyHostToDevice, st);
-    else cudaMemsetAsync(d->st_map, 0, seq * sizeof(uint32_t), st);
+    /* every staging copy is checked: a failed copy would otherwise run the chain on stale inputs */
+#define H3B_STAGE(call, what)                                                                              \
+    do {                                                                                                   \
+        e = (call);                                                                                        \
+        if (e != cudaSuccess) return fail(error, error_size, "layers_forward_f32: %s: %s", what, cudaGetErrorString(e)); \
+    } while (0)
+    H3B_STAGE(cudaMemcpyAsync(d->st_x, x, seq * D * sizeof(float), cudaMemcpyHostToDevice, st), "H2D(x)");
+    H3B_STAGE(cudaMemcpyAsync(d->st_t, t_feat, d->cfg.t_dim * sizeof(float), cudaMemcpyHostToDevice, st), "H2D(t_feat)");
+    if (row_map) H3B_STAGE(cudaMemcpyAsync(d->st_map, row_map, seq * sizeof(uint32_t), cudaMemcpyHostToDevice, st), "H2D(row_map)");
+    else H3B_STAGE(cudaMemsetAsync(d->st_map, 0, seq * sizeof(uint32_t), st), "memset(row_map)");
     if (rh) {
         if (!rope_cos || !rope_sin) return fail(error, error_size, "layers_forward_f32: rope tables missing");
-        cudaMemcpyAsync(d->st_cos, rope_cos, table_rows * rh * sizeof(float), cudaMemcpyHostToDevice, st);
-        cudaMemcpyAsync(d->st_sin, rope_sin, table_rows * rh * sizeof(float), cudaMemcpyHostToDevice, st);
+        H3B_STAGE(cudaMemcpyAsync(d->st_cos, rope_cos, table_rows * rh * sizeof(float), cudaMemcpyHostToDevice, st), "H2D(rope_cos)");
+        H3B_STAGE(cudaMemcpyAsync(d->st_sin, rope_sin, table_rows * rh * sizeof(float), cudaMemcpyHostToDevice, st), "H2D(rope_sin)");
     }
     if (d->cfg.kind == H3B_BLOCK_CROSS_GELU) {
         if (!text || !text_seq) return fail(error, error_size, "layers_forward_f32: text tokens missing");
-        cudaMemcpyAsync(d->st_text, text, text_seq * D * sizeof(float), cudaMemcpyHostToDevice, st);
+        H3B_STAGE(cudaMemcpyAsync(d->st_text, text, text_seq * D * sizeof(float), cudaMemcpyHostToDevice, st), "H2D(text)");
+#undef H3B_STAGE
         if (d->cfg.stream_dtype == H3B_F32) {
             dtext = d->st_text;
         } else {

@@ -20,16 +20,25 @@ constexpr size_t NOALLOC_MAX_ROWS = 16384;       // m <= 16384 rows (64 KiB of s
 static __device__ __align__(256) unsigned char g_noalloc_scratch[NOALLOC_MAX_CODES + NOALLOC_MAX_ROWS * sizeof(float)];
 
 // In host code `g_noalloc_scratch` is only a handle for the symbol, not an address a kernel can
-// use; the device address is looked up once per device and cached here.
+// use; the device address is looked up once per device and cached here.  The cache is written
+// without a lock: every writer of a slot stores the same value (the address of the symbol on that
+// device does not change), so racing first calls are harmless.
 static void *g_noalloc_ptr[64];
 
+// The handle's device must be the calling thread's current device: the kernels below are launched
+// on the current device with the scratch address of cuda->device.  A mismatch is refused on every
+// call rather than repaired, so that the caller's device binding is never changed behind its back
+// (h3_cuda_bind_device is the call that binds).
 static int noalloc_scratch(h3_cuda *cuda, void **out, char *error, size_t error_size) {
     const int dev = cuda->device;
     if (dev < 0 || dev >= 64) return fail(error, error_size, "no-alloc linear: device index %d out of range", dev);
+    int cur = -1;
+    H3B_CUDA_OK(cudaGetDevice(&cur), "cudaGetDevice");
+    if (cur != dev)
+        return fail(error, error_size,
+                    "no-alloc linear: the handle belongs to device %d but device %d is current; call h3_cuda_bind_device first",
+                    dev, cur);
     if (!g_noalloc_ptr[dev]) {
-        int cur = -1;
-        H3B_CUDA_OK(cudaGetDevice(&cur), "cudaGetDevice");
-        if (cur != dev) H3B_CUDA_OK(cudaSetDevice(dev), "cudaSetDevice");
         void *p = NULL;
         H3B_CUDA_OK(cudaGetSymbolAddress(&p, g_noalloc_scratch), "cudaGetSymbolAddress(no-alloc scratch)");
         if (!p) return fail(error, error_size, "no-alloc linear: scratch symbol has no device address");
@@ -60,6 +69,9 @@ int h3b_gemm_i8_dequant_f32_w_act_dev_noalloc(h3_cuda *cuda, const h3_cuda_w4a8_
                     "use h3_cuda_gemm_i8_dequant_f32_w_act_dev, which allocates",
                     m, k, NOALLOC_MAX_ROWS, NOALLOC_MAX_CODES);
     if (weight->pending) return fail(error, error_size, "no-alloc linear: weight upload still pending; call h3_cuda_w4a8_weight_ensure_ready first");
+    if (weight->device != cuda->device)   // before anything is enqueued
+        return fail(error, error_size, "no-alloc linear: the weight lives on device %d, the handle on device %d", weight->device,
+                    cuda->device);
     void *base = NULL;
     if (!noalloc_scratch(cuda, &base, error, error_size)) return 0;
     int8_t *codes = reinterpret_cast<int8_t *>(base);

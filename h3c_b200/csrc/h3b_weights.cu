@@ -143,11 +143,15 @@ int h3_cuda_w4a8_weight_create(h3_cuda *cuda, const int8_t *packed_host, size_t 
             break;
         }
         Timer th(cuda, h2d_ms);
-        cudaMemcpyAsync(d_packed, packed_host, n * k_half, cudaMemcpyHostToDevice, st);
-        cudaMemcpyAsync(d_srel, s_rel_f8, n * groups, cudaMemcpyHostToDevice, st);
-        cudaMemcpyAsync(d_cb, codebook16, 16 * sizeof(float), cudaMemcpyHostToDevice, st);
-        cudaMemcpyAsync(w->d_s, s_channel, n * sizeof(float), cudaMemcpyHostToDevice, st);
+        cudaError_t ec = cudaMemcpyAsync(d_packed, packed_host, n * k_half, cudaMemcpyHostToDevice, st);
+        if (ec == cudaSuccess) ec = cudaMemcpyAsync(d_srel, s_rel_f8, n * groups, cudaMemcpyHostToDevice, st);
+        if (ec == cudaSuccess) ec = cudaMemcpyAsync(d_cb, codebook16, 16 * sizeof(float), cudaMemcpyHostToDevice, st);
+        if (ec == cudaSuccess) ec = cudaMemcpyAsync(w->d_s, s_channel, n * sizeof(float), cudaMemcpyHostToDevice, st);
         th.stop();
+        if (ec != cudaSuccess) {
+            cuda_fail(ec, "w4a8 weight H2D", error, error_size);
+            break;
+        }
         Timer tu(cuda, unpack_ms);
         size_t total = n * k_half;
         unsigned grid = (unsigned)(ceil_div(total, 256) > (size_t)cuda->sm_count * 32 ? (size_t)cuda->sm_count * 32
@@ -191,8 +195,12 @@ int h3b_w4g_weight_create(h3_cuda *cuda, const uint8_t *packed_host, const uint1
             cuda_fail(cudaGetLastError(), "w4g staging allocation", error, error_size);
             break;
         }
-        cudaMemcpyAsync(d_packed, packed_host, n * k / 2, cudaMemcpyHostToDevice, st);
-        cudaMemcpyAsync(d_sc, scales_f16, n * groups * sizeof(__half), cudaMemcpyHostToDevice, st);
+        cudaError_t ec = cudaMemcpyAsync(d_packed, packed_host, n * k / 2, cudaMemcpyHostToDevice, st);
+        if (ec == cudaSuccess) ec = cudaMemcpyAsync(d_sc, scales_f16, n * groups * sizeof(__half), cudaMemcpyHostToDevice, st);
+        if (ec != cudaSuccess) {
+            cuda_fail(ec, "w4g weight H2D", error, error_size);
+            break;
+        }
         k_w4g_decode<<<(unsigned)n, 256, 0, st>>>(d_packed, d_sc, k, group, w->d_w, w->d_s);
         cuda->launches++;
         cudaError_t e = cudaStreamSynchronize(st);
@@ -419,8 +427,14 @@ int h3_cuda_gemm_i8_dequant_f32_w(h3_cuda *cuda, const h3_cuda_w4a8_weight *weig
         scales = tmp;
     }
     cudaStream_t st = cuda->op_stream;
-    cudaMemcpyAsync(dx.p, x_i8, m * k, cudaMemcpyHostToDevice, st);
-    cudaMemcpyAsync(da.p, scales, m * sizeof(float), cudaMemcpyHostToDevice, st);
+    {
+        cudaError_t ec = cudaMemcpyAsync(dx.p, x_i8, m * k, cudaMemcpyHostToDevice, st);
+        if (ec == cudaSuccess) ec = cudaMemcpyAsync(da.p, scales, m * sizeof(float), cudaMemcpyHostToDevice, st);
+        if (ec != cudaSuccess) {
+            free(tmp);
+            return cuda_fail(ec, "gemm_i8_w: H2D", error, error_size);
+        }
+    }
     h3b_gemm_epi e;
     memset(&e, 0, sizeof(e));
     e.kind = H3B_EPI_PLAIN; e.out_dtype = H3B_F32;
@@ -466,7 +480,7 @@ int h3_cuda_gemm_i8_dequant_f32_w_act(h3_cuda *cuda, const h3_cuda_w4a8_weight *
     if (!dx.alloc(m * k * sizeof(float), error, error_size) || !dy.alloc(m * n * sizeof(float), error, error_size))
         return 0;
     cudaStream_t st = cuda->op_stream;
-    cudaMemcpyAsync(dx.p, x_f32, m * k * sizeof(float), cudaMemcpyHostToDevice, st);
+    H3B_CUDA_OK(cudaMemcpyAsync(dx.p, x_f32, m * k * sizeof(float), cudaMemcpyHostToDevice, st), "gemm_i8_dequant_f32_w_act: H2D");
     int ok = h3_cuda_gemm_i8_dequant_f32_w_act_dev(cuda, weight, (const float *)dx.p, convrot_groupsize, m,
                                                    (float *)dy.p, prep_ms, gemm_ms, backend_out, backend_out_size,
                                                    error, error_size);

@@ -211,8 +211,12 @@ int h3_cuda_convrot_act_f32_dd(h3_cuda *cuda, const float *d_x, size_t m, size_t
  * or other allocating call.
  *   - limits: m <= h3b_linear_noalloc_max_rows() (16384) and m * K <= h3b_linear_noalloc_max_codes()
  *     (8 Mi); larger shapes are rejected with an error that names the limits
- *   - the first call on each device looks up the area's device address (that device is made
- *     current); make that first call before starting any stream capture
+ *   - the handle's device must be the calling thread's current device (h3_cuda_bind_device) and the
+ *     weight must live on it: both are checked on every call, before anything is enqueued, and a
+ *     mismatch is an error; the current device is never changed by this call
+ *   - the first call on each device looks up the area's device address; make that first call before
+ *     starting any stream capture.  The per-device cache of that address is written without a lock:
+ *     concurrent first calls store the same value
  *   - every call on a device shares the one area and leaves its codes behind; each call
  *     overwrites what it reads, so nothing needs clearing, but two calls whose kernels can run at
  *     the same time on one GPU (different streams, threads or handles) race on it: serialise them
