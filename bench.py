@@ -702,8 +702,8 @@ def kernel_arm(a):
         sfb = lambda rows: int(h3c_b200.load().h3_cuda_nvfp4_sf_bytes(rows, a.k))
         sfx = torch.full((sfb(a.m),), 0x38, device="cuda", dtype=torch.uint8)
         sfw = torch.full((sfb(a.n),), 0x38, device="cuda", dtype=torch.uint8)
-        ms = _time_kernel(lambda: cuda.gemm_fp4(w4, sfw, x4, sfx, out_dtype=torch.bfloat16), a.iters)
-        out.update(m=a.m, n=a.n, k=a.k, ms=ms, tflops=2.0 * a.m * a.n * a.k / ms / 1e9)
+        ms = _time_kernel(lambda: cuda.gemm_fp4(w4, sfw, x4, sfx, out_dtype=torch.bfloat16, swiglu=a.epi == "swiglu"), a.iters)
+        out.update(m=a.m, n=a.n, k=a.k, epi=a.epi, ms=ms, tflops=2.0 * a.m * a.n * a.k / ms / 1e9)
     elif a.kernel == "attn":
         lk = a.lk or a.lq
         dt = torch.float16 if a.f16 else torch.bfloat16

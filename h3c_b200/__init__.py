@@ -338,14 +338,15 @@ class Cuda:
         call("h3_cuda_quantize_act_nvfp4_dev", self.h, ptr(x), m, k, ptr(packed), ptr(sf))
         return packed, sf
 
-    def gemm_fp4(self, w_fp4, sf_w, x_fp4, sf_x, alpha=1.0, out_dtype=None):
-        """Block-scaled NVFP4 GEMM: packed E2M1 [n,k/2] x [m,k/2] with blocked UE4M3 scales -> [m,n]."""
+    def gemm_fp4(self, w_fp4, sf_w, x_fp4, sf_x, alpha=1.0, out_dtype=None, swiglu=False):
+        """Block-scaled NVFP4 GEMM: packed E2M1 [n,k/2] x [m,k/2] with blocked UE4M3 scales -> [m,n]
+        (swiglu: weight rows gate | up, -> [m, n/2] with SwiGLU on the f32 accumulators)."""
         import torch
         out_dtype = out_dtype or torch.float32
         n, m, k = w_fp4.shape[0], x_fp4.shape[0], x_fp4.shape[1] * 2
-        y = torch.empty((m, n), dtype=out_dtype, device=x_fp4.device)
-        call("h3b_gemm_fp4_dev", self.h, ptr(w_fp4), ptr(sf_w), ptr(x_fp4), ptr(sf_x), m, n, k, float(alpha), ptr(y),
-             _dt(y))
+        y = torch.empty((m, n // 2 if swiglu else n), dtype=out_dtype, device=x_fp4.device)
+        call("h3b_gemm_fp4_swiglu_dev" if swiglu else "h3b_gemm_fp4_dev", self.h, ptr(w_fp4), ptr(sf_w), ptr(x_fp4),
+             ptr(sf_x), m, n, k, float(alpha), ptr(y), _dt(y))
         return y
 
     def nvfp4_weight(self, packed, sf, scale2, n, k):

@@ -22,6 +22,7 @@
 
 typedef struct {
     const h3_cuda_w4a8_weight *lin[H3B_LIN_COUNT];
+    const h3_cuda_nvfp4_weight *fp4[4];                  /* NVFP4 form of QKV / OUT / FC1 / FC2; NULL = the INT8 weight */
     float *norm1, *norm2, *q_norm, *k_norm, *norm_cross; /* device */
     float *adaln_w, *adaln_b;                            /* device */
     float *modulation;                                   /* device [mod_rows, 6, dim] */
@@ -40,6 +41,8 @@ struct h3b_dit {
     void *q, *k, *v, *att;  /* bf16 [seq, inner] each */
     void *cq;               /* bf16 [seq, inner] cross-attention queries */
     void *ckv;              /* bf16 [text, 2*inner] */
+    float *rotf;            /* f32 [seq, max(dim, ffn, inner)]: activations of an NVFP4 linear (only when one is set) */
+    int any_fp4;
     int8_t *q8;             /* [seq, max(dim, ffn, inner)] activation codes */
     float *s8;              /* [seq] activation scales */
     int8_t *tq8;            /* [text, dim] */
@@ -149,7 +152,7 @@ static void free_group(void ***p, size_t n) {
 }
 static void free_seq_ws(h3b_dit *d) {
     void **p[] = {&d->xa, &d->xb, &d->io, &d->qkv, &d->wide, &d->q, &d->k, &d->v, &d->att, &d->cq, (void **)&d->q8,
-                  (void **)&d->s8, (void **)&d->st_x, (void **)&d->st_map, (void **)&d->st_cos, (void **)&d->st_sin,
+                  (void **)&d->rotf, (void **)&d->s8, (void **)&d->st_x, (void **)&d->st_map, (void **)&d->st_cos, (void **)&d->st_sin,
                   (void **)&d->st_t};
     drop_graph(d);   /* a captured chain points into the workspace */
     free_group(p, sizeof(p) / sizeof(p[0]));
@@ -199,6 +202,33 @@ int h3b_dit_set_linear(h3b_dit *d, unsigned block, int which, const h3_cuda_w4a8
                         want_n[which], want_k[which]);
     }
     d->blocks[block].lin[which] = w;
+    return 1;
+}
+
+/* Per-linear choice between the INT8 and the NVFP4 form of a weight, as the reference's nvfp4_gemm_dispatch makes it
+ * (h3_dit_w4a8.c:3519-3590, call sites :3623-3641): a linear with an NVFP4 weight set runs
+ * ConvRot -> NVFP4 activation quantisation -> block-scaled GEMM with the plain (QKV), SwiGLU (FC1) or gate (OUT, FC2)
+ * epilogue on f32 activations; the others keep their INT8 weight.  w == NULL returns the linear to INT8. */
+int h3b_dit_set_linear_nvfp4(h3b_dit *d, unsigned block, int which, const h3_cuda_nvfp4_weight *w, char *error,
+                             size_t error_size) {
+    size_t D, I, F;
+    if (!d || block >= d->cfg.n_blocks || which < H3B_LIN_QKV || which > H3B_LIN_FC2)
+        return fail(error, error_size, "h3b_dit_set_linear_nvfp4: invalid arguments");
+    if (d->cfg.kind != H3B_BLOCK_REFERENCE || d->cfg.stream_dtype != H3B_F32)
+        return fail(error, error_size, "h3b_dit_set_linear_nvfp4: NVFP4 linears go with the reference block on an f32 stream");
+    D = d->cfg.dim; I = inner(d); F = d->cfg.ffn;
+    if (w) {
+        const size_t want_n[4] = {3 * I, D, 2 * F, D}, want_k[4] = {D, I, D, F};
+        const size_t n = h3_cuda_nvfp4_weight_n(w), k = h3_cuda_nvfp4_weight_k(w);
+        if (n != want_n[which] || k != want_k[which])
+            return fail(error, error_size, "h3b_dit_set_linear_nvfp4: linear %d is [%zu,%zu], expected [%zu,%zu]", which, n, k,
+                        want_n[which], want_k[which]);
+        if (!d->any_fp4) {
+            d->any_fp4 = 1;
+            if (d->cap_seq) free_seq_ws(d);   /* the next reserve adds the f32 activation buffer */
+        }
+    }
+    d->blocks[block].fp4[which] = w;
     return 1;
 }
 
@@ -274,7 +304,8 @@ int h3b_dit_reserve(h3b_dit *d, size_t seq, size_t text_seq, char *error, size_t
             !dmalloc((void **)&d->st_cos, table_rows * (d->cfg.rope_half ? d->cfg.rope_half : 1) * sizeof(float), error, error_size) ||
             !dmalloc((void **)&d->st_sin, table_rows * (d->cfg.rope_half ? d->cfg.rope_half : 1) * sizeof(float), error, error_size) ||
             !dmalloc((void **)&d->st_t, (d->cfg.t_dim ? d->cfg.t_dim : 1) * sizeof(float), error, error_size) ||
-            (cross && !dmalloc(&d->cq, seq * I * 2, error, error_size))) {
+            (cross && !dmalloc(&d->cq, seq * I * 2, error, error_size)) ||
+            (d->any_fp4 && !dmalloc((void **)&d->rotf, seq * widest * sizeof(float), error, error_size))) {
             free_seq_ws(d);   /* a half-built group must not pass for capacity */
             return 0;
         }
@@ -323,6 +354,40 @@ static int gemm(h3b_dit *d, const h3_cuda_w4a8_weight *w, const int8_t *q, const
     return h3b_gemm_i8_dev(d->cuda, w, q, s, m, y, &e, error, error_size);
 }
 
+/* One NVFP4 linear of the reference block: rows of `x` (dtype `dt`) -> optional RMSNorm + modulation -> ConvRot -> f32
+ * in d->rotf -> the reference-named f32 entry point with the epilogue `epi` (0 plain, 1 SwiGLU, 2 gate). */
+static int fp4_linear(h3b_dit *d, const h3_cuda_nvfp4_weight *w, const void *x, int dt, size_t rows, size_t width,
+                      const float *norm_w, const float *mod, const uint32_t *row_map, size_t shift_slot,
+                      size_t scale_slot, int identity, int epi, const float *residual, size_t gate_slot, float *y,
+                      char *error, size_t error_size) {
+    const float *x_use;
+    if (!d->rotf) return fail(error, error_size, "NVFP4 linear: workspace not reserved");
+    if (d->cfg.convrot_gs > 0 || !identity) {
+        h3b_norm_args a;
+        memset(&a, 0, sizeof(a));
+        a.d_x = x; a.d_norm_w = norm_w; a.d_modulation = mod; a.d_row_map = row_map; a.rows = rows; a.width = width;
+        a.slots = 6; a.shift_slot = shift_slot; a.scale_slot = scale_slot; a.epsilon = d->cfg.eps; a.dtype = dt;
+        a.identity = identity; a.convrot_gs = d->cfg.convrot_gs;
+        if (d->cfg.convrot_gs > 0) a.d_rot = d->rotf;
+        else if (dt == H3B_F32) a.d_normed = d->rotf;
+        else return fail(error, error_size, "NVFP4 linear: normalised rows without ConvRot need an f32 input");
+        if (!h3b_norm_dev(d->cuda, &a, error, error_size)) return 0;
+        x_use = d->rotf;
+    } else if (dt == H3B_F32) {
+        x_use = (const float *)x;
+    } else {
+        if (!h3b_cast_dev(d->cuda, x, dt, d->rotf, H3B_F32, rows * width, error, error_size)) return 0;
+        x_use = d->rotf;
+    }
+    if (epi == 1)
+        return h3_cuda_gemm_fp4_w_act_dev_swiglu(d->cuda, w, x_use, 1.0f, rows, NULL, y, NULL, NULL, NULL, error, error_size,
+                                                 NULL);
+    if (epi == 2)
+        return h3_cuda_gemm_fp4_w_act_dev_gate(d->cuda, w, x_use, 1.0f, rows, residual, mod, row_map, 6, gate_slot, NULL, y,
+                                               NULL, NULL, NULL, error, error_size, NULL);
+    return h3_cuda_gemm_fp4_w_act_dev(d->cuda, w, x_use, 1.0f, rows, y, NULL, NULL, NULL, error, error_size, NULL);
+}
+
 static int block_forward(h3b_dit *d, unsigned block, const void *d_x, size_t seq, size_t seq_real,
                          const float *d_modulation, const uint32_t *d_row_map, const float *d_cos, const float *d_sin,
                          const void *d_text, size_t text_seq, void *d_y, char *error, size_t error_size) {
@@ -331,6 +396,7 @@ static int block_forward(h3b_dit *d, unsigned block, const void *d_x, size_t seq
     size_t D, I, F;
     int dt, i;
     float scale;
+    const void *att_src;   /* bf16 [seq, inner] attention output that feeds the out projection */
     if (!d || block >= d->cfg.n_blocks || !d_x || !d_y || !seq)
         return fail(error, error_size, "block forward: invalid arguments");
     b = &d->blocks[block];
@@ -338,20 +404,30 @@ static int block_forward(h3b_dit *d, unsigned block, const void *d_x, size_t seq
     if (!mod) return fail(error, error_size, "block %u: no modulation given or projected", block);
     if (!b->norm1) return fail(error, error_size, "block %u: aux tensors not set", block);
     for (i = 0; i < (d->cfg.kind == H3B_BLOCK_CROSS_GELU ? H3B_LIN_COUNT : 4); i++)
-        if (!b->lin[i]) return fail(error, error_size, "block %u: linear %d not set", block, i);
+        if (!b->lin[i] && !(i < 4 && b->fp4[i])) return fail(error, error_size, "block %u: linear %d not set", block, i);
     if (d->cfg.rope_half && (!d_cos || !d_sin)) return fail(error, error_size, "block %u: rope tables missing", block);
     if (d->cfg.kind == H3B_BLOCK_CROSS_GELU && (!d_text || !text_seq))
         return fail(error, error_size, "block %u: text tokens missing", block);
     if (!h3b_dit_reserve(d, seq, text_seq, error, error_size)) return 0;
     D = d->cfg.dim; I = inner(d); F = d->cfg.ffn; dt = d->cfg.stream_dtype;
     scale = 1.0f / 11.313708498984761f; /* 1/sqrt(128) */
+    att_src = d->att;
 
     /* ---- self-attention: adaLN(0,1) -> QKV -> QK-norm + RoPE -> SDPA -> out * gate(2) + x */
-    if (!norm_quant(d, d_x, dt, seq, D, b->norm1, mod, d_row_map, 0, 1, 0, d->q8, d->s8, error, error_size)) return 0;
+    if (!b->fp4[H3B_LIN_QKV] &&
+        !norm_quant(d, d_x, dt, seq, D, b->norm1, mod, d_row_map, 0, 1, 0, d->q8, d->s8, error, error_size))
+        return 0;
     if (!d->uly || !d->uly->comm) {
         /* QKV projection with the QK-norm and RoPE applied in the GEMM epilogue: Q, K, V leave the kernel
          * as bf16 [seq, heads, 128]; the [seq, 3*inner] intermediate is never written */
-        if (d->cfg.rope_half == 0 || d->cfg.rope_half == 48 || d->cfg.rope_half == 64) {
+        if (b->fp4[H3B_LIN_QKV]) {
+            if (!fp4_linear(d, b->fp4[H3B_LIN_QKV], d_x, dt, seq, D, b->norm1, mod, d_row_map, 0, 1, 0, 0, NULL, 0,
+                            (float *)d->qkv, error, error_size) ||
+                !h3b_qkv_rope_dev(d->cuda, d->qkv, dt, b->q_norm, b->k_norm, d_cos, d_sin, seq, d->cfg.heads,
+                                  d->cfg.head_dim, d->cfg.rope_half, d->cfg.eps, 0, 1, d->q, d->k, d->v, H3B_BF16, error,
+                                  error_size))
+                return 0;
+        } else if (d->cfg.rope_half == 0 || d->cfg.rope_half == 48 || d->cfg.rope_half == 64) {
             h3b_gemm_epi e;
             memset(&e, 0, sizeof(e));
             e.kind = H3B_EPI_QKV_ROPE; e.out_dtype = H3B_BF16; e.d_key = d->k; e.d_value = d->v;
@@ -377,7 +453,7 @@ static int block_forward(h3b_dit *d, unsigned block, const void *d_x, size_t seq
         const size_t es = dt == H3B_F32 ? 4 : 2;
         const h3b_ulysses_direct *dir = h3b_ulysses_direct_get(d->uly);
         if (dir && dir->seq_local == seq && dir->heads == d->cfg.heads && dir->head_dim == d->cfg.head_dim &&
-            d->cfg.head_dim == 128 && dt != H3B_F32 &&
+            d->cfg.head_dim == 128 && dt != H3B_F32 && !b->fp4[H3B_LIN_QKV] &&
             (d->cfg.rope_half == 0 || d->cfg.rope_half == 48 || d->cfg.rope_half == 64)) {
             /* Exchange-free form: the QKV epilogue (QK-norm and RoPE included: both are per row and head) stores
              * every head slice into the gathered buffer of the rank that attends that head, the attention
@@ -395,11 +471,15 @@ static int block_forward(h3b_dit *d, unsigned block, const void *d_x, size_t seq
             if (!h3b_ulysses_barrier(d->uly, error, error_size)) return 0;
             if (!h3b_sdpa_bf16_scatter_dev(d->cuda, dir, seq_real, scale, error, error_size)) return 0;
             if (!h3b_ulysses_barrier(d->uly, error, error_size)) return 0;
-            if (!norm_quant(d, dir->att, H3B_BF16, seq, I, NULL, NULL, NULL, 0, 0, 1, d->q8, d->s8, error, error_size)) return 0;
+            att_src = dir->att;
             goto attention_done;
         }
-        if (!gemm(d, b->lin[H3B_LIN_QKV], d->q8, d->s8, seq, d->qkv, H3B_EPI_PLAIN, dt, NULL, NULL, NULL, 0, error,
-                  error_size))
+        if (b->fp4[H3B_LIN_QKV]) {
+            if (!fp4_linear(d, b->fp4[H3B_LIN_QKV], d_x, dt, seq, D, b->norm1, mod, d_row_map, 0, 1, 0, 0, NULL, 0,
+                            (float *)d->qkv, error, error_size))
+                return 0;
+        } else if (!gemm(d, b->lin[H3B_LIN_QKV], d->q8, d->s8, seq, d->qkv, H3B_EPI_PLAIN, dt, NULL, NULL, NULL, 0, error,
+                         error_size))
             return 0;
         if (!h3_ulysses_a2a_qkv(d->uly, d->qkv, d->qkv, seq, d->cfg.heads, d->cfg.head_dim, (int)es, error, error_size))
             return 0;
@@ -416,19 +496,30 @@ static int block_forward(h3b_dit *d, unsigned block, const void *d_x, size_t seq
         if (!h3_ulysses_a2a_attn_out(d->uly, d->att, d->att, seq, d->cfg.heads, d->cfg.head_dim, 2, error, error_size))
             return 0;
     }
-    if (!norm_quant(d, d->att, H3B_BF16, seq, I, NULL, NULL, NULL, 0, 0, 1, d->q8, d->s8, error, error_size)) return 0;
 attention_done:
     /* x1 -> xa */
-    if (!gemm(d, b->lin[H3B_LIN_OUT], d->q8, d->s8, seq, d->xa, H3B_EPI_GATE, dt, d_x, mod, d_row_map, 2, error,
-              error_size))
+    if (b->fp4[H3B_LIN_OUT]) {
+        if (!fp4_linear(d, b->fp4[H3B_LIN_OUT], att_src, H3B_BF16, seq, I, NULL, mod, d_row_map, 0, 0, 1, 2, (const float *)d_x,
+                        2, (float *)d->xa, error, error_size))
+            return 0;
+    } else if (!norm_quant(d, att_src, H3B_BF16, seq, I, NULL, NULL, NULL, 0, 0, 1, d->q8, d->s8, error, error_size) ||
+               !gemm(d, b->lin[H3B_LIN_OUT], d->q8, d->s8, seq, d->xa, H3B_EPI_GATE, dt, d_x, mod, d_row_map, 2, error,
+                     error_size))
         return 0;
 
     if (d->cfg.kind == H3B_BLOCK_REFERENCE) {
         /* ---- MLP: adaLN(3,4) -> fc1 + SwiGLU -> fc2 * gate(5) + x1 */
-        if (!norm_quant(d, d->xa, dt, seq, D, b->norm2, mod, d_row_map, 3, 4, 0, d->q8, d->s8, error, error_size)) return 0;
-        if (!gemm(d, b->lin[H3B_LIN_FC1], d->q8, d->s8, seq, d->wide, H3B_EPI_SWIGLU, dt, NULL, NULL, NULL, 0, error,
-                  error_size))
+        if (b->fp4[H3B_LIN_FC1]) {
+            if (!fp4_linear(d, b->fp4[H3B_LIN_FC1], d->xa, dt, seq, D, b->norm2, mod, d_row_map, 3, 4, 0, 1, NULL, 0,
+                            (float *)d->wide, error, error_size))
+                return 0;
+        } else if (!norm_quant(d, d->xa, dt, seq, D, b->norm2, mod, d_row_map, 3, 4, 0, d->q8, d->s8, error, error_size) ||
+                   !gemm(d, b->lin[H3B_LIN_FC1], d->q8, d->s8, seq, d->wide, H3B_EPI_SWIGLU, dt, NULL, NULL, NULL, 0, error,
+                         error_size))
             return 0;
+        if (b->fp4[H3B_LIN_FC2])
+            return fp4_linear(d, b->fp4[H3B_LIN_FC2], d->wide, dt, seq, F, NULL, mod, d_row_map, 0, 0, 1, 2,
+                              (const float *)d->xa, 5, (float *)d_y, error, error_size);
         if (!norm_quant(d, d->wide, dt, seq, F, NULL, NULL, NULL, 0, 0, 1, d->q8, d->s8, error, error_size)) return 0;
         return gemm(d, b->lin[H3B_LIN_FC2], d->q8, d->s8, seq, d_y, H3B_EPI_GATE, dt, d->xa, mod, d_row_map, 5, error,
                     error_size);

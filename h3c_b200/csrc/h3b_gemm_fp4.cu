@@ -316,9 +316,14 @@ constexpr uint32_t SF_COL = 256;                                    // per stage
 constexpr size_t SMEM_BYTES = 1024 + (size_t)STAGES * STAGE_BYTES + 8 * OUT_STAGE_BYTES + 256;
 }  // namespace fp4w
 
-template <bool GATE, bool OUT_BF16>
+// MODE 0: y = alpha acc; 1: y = residual + alpha acc gate; 2: SwiGLU, y[:, c] = silu(alpha acc[:, c]) * alpha acc[:, N/2 + c]
+// in f32 straight from the accumulator (the reference's chain h3_cutlass_nvfp4_fc1_f32_run -> swiglu, h3_dit_nvfp4_chain.cu:
+// 201-277, 322-435, as one kernel).  For SwiGLU the tile's first 128 weight rows are gate rows nt*128.., the second
+// 128 the matching up rows N/2 + nt*128.., so gate and up of an output column sit 128 accumulator columns apart.
+template <int MODE, bool OUT_BF16>
 __global__ void __launch_bounds__(fp4w::THREADS, 1) k_gemm_nvfp4_wide(const __grid_constant__ Fp4Params p) {
     using namespace fp4w;
+    constexpr bool GATE = MODE == 1, SWIGLU = MODE == 2;
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     uint8_t *out_stage = smem + (size_t)STAGES * STAGE_BYTES;
@@ -360,7 +365,9 @@ __global__ void __launch_bounds__(fp4w::THREADS, 1) k_gemm_nvfp4_wide(const __gr
             uint32_t ph = 0;
             for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
                 const int mt = tile % p.m_tiles, nt = tile / p.m_tiles;
-                const int nb0 = 2 * nt, nb1 = min(2 * nt + 1, n_blocks - 1);   // a missing second block repeats the first
+                // weight rows of the tile's two halves and their scale row blocks
+                const int n0 = SWIGLU ? nt * 128 : nt * BN, n1 = SWIGLU ? p.N / 2 + nt * 128 : nt * BN + 128;
+                const int nb0 = n0 / 128, nb1 = min(n1 / 128, n_blocks - 1);   // a missing second block repeats the first
                 for (int kb = 0; kb < p.k_blocks; kb++) {
                     if (!mbar_wait(&empty[s], ph ^ 1, abort_word, p.status, H3B_ST_TIMEOUT_EMPTY)) break;
                     uint8_t *a_dst = smem + (size_t)s * STAGE_BYTES;
@@ -370,8 +377,8 @@ __global__ void __launch_bounds__(fp4w::THREADS, 1) k_gemm_nvfp4_wide(const __gr
                     const uint32_t sf_bytes = (uint32_t)nkt * 512;
                     mbar_expect_tx(&full[s], A_BYTES + B_BYTES + 3 * sf_bytes);
                     tma_load_2d(a_dst, &p.tmap_x, &full[s], kb * BK_BYTES, mt * BM);
-                    tma_load_2d(b_dst, &p.tmap_w, &full[s], kb * BK_BYTES, nt * BN);
-                    tma_load_2d(b_dst + B_BYTES / 2, &p.tmap_w, &full[s], kb * BK_BYTES, nt * BN + 128);
+                    tma_load_2d(b_dst, &p.tmap_w, &full[s], kb * BK_BYTES, n0);
+                    tma_load_2d(b_dst + B_BYTES / 2, &p.tmap_w, &full[s], kb * BK_BYTES, n1);
                     bulk_load(sfa_dst, p.sf_x + ((size_t)mt * p.sf_tiles_per_rowblock + kt0) * 512, sf_bytes, &full[s]);
                     bulk_load(sfb_dst, p.sf_w + ((size_t)nb0 * p.sf_tiles_per_rowblock + kt0) * 512, sf_bytes, &full[s]);
                     bulk_load(sfb_dst + 4 * 512, p.sf_w + ((size_t)nb1 * p.sf_tiles_per_rowblock + kt0) * 512, sf_bytes, &full[s]);
@@ -419,7 +426,8 @@ __global__ void __launch_bounds__(fp4w::THREADS, 1) k_gemm_nvfp4_wide(const __gr
         const int q = warp & 3, half = (warp - 2) >> 2;
         const uint32_t lane_base = (uint32_t)(q * 32) << 16;
         constexpr int CH_COLS = OUT_BF16 ? 64 : 32;   // 128 bytes of a row per copy
-        constexpr int NCH = 128 / CH_COLS;
+        constexpr int OUT_COLS = SWIGLU ? 64 : 128;   // output columns per thread
+        constexpr int NCH = OUT_COLS / CH_COLS;
         constexpr int UNIT = OUT_BF16 ? 8 : 4;        // values per 16-byte unit
         uint8_t *stg = out_stage + (size_t)(warp - 2) * OUT_STAGE_BYTES;
         uint64_t *rbar = &res_bar[warp - 2];
@@ -436,24 +444,28 @@ __global__ void __launch_bounds__(fp4w::THREADS, 1) k_gemm_nvfp4_wide(const __gr
             }
             bool ok = mbar_wait(tmem_full, it & 1, abort_word, p.status, H3B_ST_TIMEOUT_TMEM_FULL);
             tc_fence_after();
-            const uint32_t t_addr = tmem_base + lane_base + (uint32_t)half * 128;
+            // plain / gate: 128 accumulator columns per thread; SwiGLU: 64 gate columns in r[0..63] and the 64 up
+            // columns 128 further on in r[64..127]
+            const uint32_t t_addr = tmem_base + lane_base + (uint32_t)half * (SWIGLU ? 64 : 128);
             uint32_t r[128];
             if (ok) {
 #pragma unroll
                 for (int ch = 0; ch < 4; ch++)
-                    tmem_ld_32x32b_x32(t_addr + ch * 32, *reinterpret_cast<uint32_t(*)[32]>(&r[ch * 32]));
+                    tmem_ld_32x32b_x32(t_addr + (SWIGLU ? (ch >> 1) * 128 + (ch & 1) * 32 : ch * 32),
+                                       *reinterpret_cast<uint32_t(*)[32]>(&r[ch * 32]));
                 tmem_ld_wait();
             }
             // the values are in registers: the accumulator can take the next tile
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(tmem_empty);
-            const int col0 = nt * BN + half * 128;
+            const int col0 = SWIGLU ? nt * 128 + half * 64 : nt * BN + half * 128;
+            const int n_out = SWIGLU ? p.N / 2 : p.N;
             if (ok && row0 < p.M) {
 #pragma unroll
                 for (int ch = 0; ch < NCH; ch++) {
                     const int col = col0 + ch * CH_COLS;
-                    if (col >= p.N) break;
+                    if (col >= n_out) break;
                     if (lane == 0) tma_store_wait_read<0>();   // the previous copy has left the buffer
                     __syncwarp();
                     if (GATE) {
@@ -471,7 +483,15 @@ __global__ void __launch_bounds__(fp4w::THREADS, 1) k_gemm_nvfp4_wide(const __gr
                         const int v = ch * CH_COLS + u * UNIT;
                         float out[UNIT];
 #pragma unroll
-                        for (int e = 0; e < UNIT; e++) out[e] = __fmul_rn(p.alpha, __uint_as_float(r[v + e]));
+                        for (int e = 0; e < UNIT; e++) {
+                            out[e] = __fmul_rn(p.alpha, __uint_as_float(r[v + e]));
+                            if (SWIGLU) {
+                                const float u_ = __fmul_rn(p.alpha, __uint_as_float(r[64 + v + e]));
+                                // hardware exponential and reciprocal (about 2 ulp): the IEEE division and expf expand to
+                                // some forty instructions per element, 64 elements per thread
+                                out[e] = __fmul_rn(__fdividef(out[e], __fadd_rn(1.0f, __expf(-out[e]))), u_);
+                            }
+                        }
                         if (GATE) {
                             float resv[UNIT], g[UNIT];
                             const uint4 raw = *cell;
@@ -540,7 +560,9 @@ int launch_gemm_nvfp4(h3_cuda *cuda, const uint8_t *w_fp4, const uint8_t *sf_w, 
     if (out_dtype != H3B_F32 && out_dtype != H3B_BF16) return fail(error, error_size, "gemm_fp4: output must be f32 or bf16");
     if (((uintptr_t)w_fp4 | (uintptr_t)x_fp4 | (uintptr_t)sf_w | (uintptr_t)sf_x | (uintptr_t)y) & 15)
         return fail(error, error_size, "gemm_fp4: buffers must be 16-byte aligned");
-    if (gate && !residual) return fail(error, error_size, "gemm_fp4: gate epilogue needs a residual");
+    if (gate == 1 && !residual) return fail(error, error_size, "gemm_fp4: gate epilogue needs a residual");
+    if (gate == 2 && (n % 256 || !h3_plugin_enabled("H3B_FP4_WIDE")))
+        return fail(error, error_size, "gemm_fp4: the fused SwiGLU epilogue needs N %% 256 == 0 and the 128 x 256 tile form");
     if (m > 0x7fffff00u || n > 0x7fffff00u) return fail(error, error_size, "gemm_fp4: shape too large");
     Fp4Params p;
     memset(&p, 0, sizeof(p));
@@ -555,24 +577,25 @@ int launch_gemm_nvfp4(h3_cuda *cuda, const uint8_t *w_fp4, const uint8_t *sf_w, 
     p.sf_tiles_per_rowblock = (int)(k / 64);
     p.alpha = alpha; p.gate = gate; p.out_bf16 = out_dtype == H3B_BF16; p.y = y; p.residual = residual; p.mod = mod;
     p.row_map = row_map; p.slots = (int)slots; p.gate_slot = (int)gate_slot; p.status = cuda->d_status;
-    if (gate && (((uintptr_t)residual | (uintptr_t)mod) & 15)) return fail(error, error_size, "gemm_fp4: residual and modulation must be 16-byte aligned");
+    if (gate == 1 && (((uintptr_t)residual | (uintptr_t)mod) & 15)) return fail(error, error_size, "gemm_fp4: residual and modulation must be 16-byte aligned");
     // 128 x 256 tiles whenever N has two column blocks; H3B_FP4_WIDE=0 keeps the 128 x 128 form (A/B timing)
     static const bool wide_on = h3_plugin_enabled("H3B_FP4_WIDE") != 0;
     if (wide_on && n >= 256) {
         int rc2 = h3b_encode_tmap_2d(&p.tmap_w, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, w_fp4, k / 2, n, k / 2, BK_BYTES, 128,
                                      CU_TENSOR_MAP_SWIZZLE_128B);
         if (rc2 != 0) return fail(error, error_size, "gemm_fp4: cuTensorMapEncodeTiled failed (%d)", rc2);
-        p.n_tiles = (int)ceil_div(n, (size_t)fp4w::BN);
+        p.n_tiles = (int)ceil_div(n, (size_t)fp4w::BN);   // SwiGLU: N/2 output columns, 128 per tile: the same count
         const bool bf = out_dtype == H3B_BF16;
         const CUtensorMapDataType odt = bf ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32;
-        const size_t osz = bf ? 2 : 4;
-        rc2 = h3b_encode_tmap_2d(&p.tmap_y, odt, osz, y, n, m, n * osz, (uint32_t)(128 / osz), 32, CU_TENSOR_MAP_SWIZZLE_128B);
-        if (rc2 == 0 && gate)
+        const size_t osz = bf ? 2 : 4, n_y = gate == 2 ? n / 2 : n;
+        rc2 = h3b_encode_tmap_2d(&p.tmap_y, odt, osz, y, n_y, m, n_y * osz, (uint32_t)(128 / osz), 32, CU_TENSOR_MAP_SWIZZLE_128B);
+        if (rc2 == 0 && gate == 1)
             rc2 = h3b_encode_tmap_2d(&p.tmap_res, odt, osz, residual, n, m, n * osz, (uint32_t)(128 / osz), 32,
                                      CU_TENSOR_MAP_SWIZZLE_128B);
         if (rc2 != 0) return fail(error, error_size, "gemm_fp4: cuTensorMapEncodeTiled (outputs) failed (%d)", rc2);
-        auto kw = gate ? (p.out_bf16 ? k_gemm_nvfp4_wide<true, true> : k_gemm_nvfp4_wide<true, false>)
-                       : (p.out_bf16 ? k_gemm_nvfp4_wide<false, true> : k_gemm_nvfp4_wide<false, false>);
+        auto kw = gate == 2   ? (p.out_bf16 ? k_gemm_nvfp4_wide<2, true> : k_gemm_nvfp4_wide<2, false>)
+                  : gate == 1 ? (p.out_bf16 ? k_gemm_nvfp4_wide<1, true> : k_gemm_nvfp4_wide<1, false>)
+                              : (p.out_bf16 ? k_gemm_nvfp4_wide<0, true> : k_gemm_nvfp4_wide<0, false>);
         H3B_CUDA_OK(cudaFuncSetAttribute(kw, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)fp4w::SMEM_BYTES),
                     "gemm_fp4 smem attribute");
         const int tiles_w = p.m_tiles * p.n_tiles;
@@ -698,6 +721,13 @@ int h3b_gemm_fp4_dev(h3_cuda *cuda, const uint8_t *d_w_fp4, const uint8_t *d_sf_
                              0, error, error_size);
 }
 
+int h3b_gemm_fp4_swiglu_dev(h3_cuda *cuda, const uint8_t *d_w_fp4, const uint8_t *d_sf_w, const uint8_t *d_x_fp4,
+                            const uint8_t *d_sf_x, size_t m, size_t n, size_t k, float alpha, void *d_y, int out_dtype,
+                            char *error, size_t error_size) {
+    return launch_gemm_nvfp4(cuda, d_w_fp4, d_sf_w, d_x_fp4, d_sf_x, m, n, k, alpha, d_y, out_dtype, 2, NULL, NULL, NULL, 0,
+                             0, error, error_size);
+}
+
 // activation quantisation into the scratch area; returns pointers into it
 static int fp4_prepare(h3_cuda *cuda, const h3_cuda_nvfp4_weight *w, const float *d_x, size_t m, uint8_t *scratch,
                        uint8_t **x4, uint8_t **sfx, uint8_t **acc, double *prep_ms, char *error, size_t error_size) {
@@ -758,17 +788,25 @@ int h3_cuda_gemm_fp4_w_act_dev_swiglu(h3_cuda *cuda, const h3_cuda_nvfp4_weight 
     if (!d_y_f32 || (weight && (weight->n % 2))) return fail(error, error_size, "gemm_fp4_w_act_swiglu: invalid arguments");
     if (!fp4_prepare(cuda, weight, d_x, m, scratch, &x4, &sfx, &acc, prep_ms, error, error_size)) return 0;
     Timer t(cuda, gemm_ms);
-    // block-scaled GEMM to bf16 accumulators in the scratch area (as the reference does), then the SwiGLU epilogue
-    int ok = launch_gemm_nvfp4(cuda, weight->d_packed, weight->d_sf, x4, sfx, m, weight->n, weight->k, 1.0f, acc, H3B_BF16, 0,
+    int ok;
+    if (weight->n % 256 == 0 && h3_plugin_enabled("H3B_FP4_WIDE")) {
+        // SwiGLU in the GEMM epilogue, on the f32 accumulators
+        ok = launch_gemm_nvfp4(cuda, weight->d_packed, weight->d_sf, x4, sfx, m, weight->n, weight->k,
+                               weight->scale2 * act_scale, d_y_f32, H3B_F32, 2, NULL, NULL, NULL, 0, 0, error, error_size);
+    } else {
+        // odd widths: block-scaled GEMM to bf16 accumulators in the scratch area (as the reference does,
+        // h3_gpu_cuda.cu:757-808), then the SwiGLU kernel
+        ok = launch_gemm_nvfp4(cuda, weight->d_packed, weight->d_sf, x4, sfx, m, weight->n, weight->k, 1.0f, acc, H3B_BF16, 0,
                                NULL, NULL, NULL, 0, 0, error, error_size);
-    if (ok) {
-        const size_t width = weight->n / 2, total = m * width;
-        size_t grid = ceil_div(total, 256);
-        if (grid > (size_t)cuda->sm_count * 16) grid = (size_t)cuda->sm_count * 16;
-        k_fp4_swiglu<<<(unsigned)grid, 256, 0, cuda->op_stream>>>((const __nv_bfloat16 *)acc, weight->scale2 * act_scale, m,
-                                                                 (unsigned)width, d_y_f32);
-        cuda->launches++;
-        if (cudaGetLastError() != cudaSuccess) ok = fail(error, error_size, "k_fp4_swiglu launch failed");
+        if (ok) {
+            const size_t width = weight->n / 2, total = m * width;
+            size_t grid = ceil_div(total, 256);
+            if (grid > (size_t)cuda->sm_count * 16) grid = (size_t)cuda->sm_count * 16;
+            k_fp4_swiglu<<<(unsigned)grid, 256, 0, cuda->op_stream>>>((const __nv_bfloat16 *)acc, weight->scale2 * act_scale, m,
+                                                                     (unsigned)width, d_y_f32);
+            cuda->launches++;
+            if (cudaGetLastError() != cudaSuccess) ok = fail(error, error_size, "k_fp4_swiglu launch failed");
+        }
     }
     t.stop();
     return ok;

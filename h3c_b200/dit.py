@@ -67,6 +67,10 @@ class Dit:
         call("h3b_dit_set_linear", self.h, block, which, weight.h)
         self._weights.append(weight)
 
+    def set_linear_nvfp4(self, block, which, weight_handle):
+        """NVFP4 form of QKV / OUT / FC1 / FC2 (handle from Cuda.nvfp4_weight; None returns the linear to INT8)."""
+        call("h3b_dit_set_linear_nvfp4", self.h, block, which, weight_handle)
+
     def set_block_aux(self, block, norm1, norm2, q_norm, k_norm, norm_cross=None):
         f = lambda a: None if a is None else np.ascontiguousarray(a, np.float32)
         arrs = [f(a) for a in (norm1, norm2, q_norm, k_norm, norm_cross)]

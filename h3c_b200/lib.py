@@ -171,6 +171,7 @@ _SIGS = {
     "h3b_dit_create": (vp, (vp, C.POINTER(DitConfig)) + _ERR),
     "h3b_dit_free": (None, (vp,)),
     "h3b_dit_set_linear": (i32, (vp, C.c_uint, i32, vp) + _ERR),
+    "h3b_dit_set_linear_nvfp4": (i32, (vp, C.c_uint, i32, vp) + _ERR),
     "h3b_dit_set_block_aux": (i32, (vp, C.c_uint, vp, vp, vp, vp, vp) + _ERR),
     "h3b_dit_set_adaln": (i32, (vp, C.c_uint, vp, vp) + _ERR),
     "h3b_dit_project_modulation": (i32, (vp, vp) + _ERR),
@@ -184,6 +185,7 @@ _SIGS = {
     "h3b_dit_launches_per_block": (i32, (vp,)),
     "h3_cuda_gemm_fp4_bs_dev": (i32, (vp, vp, vp, vp, vp, sz, sz, sz, vp, dbl_p) + _ERR),
     "h3b_gemm_fp4_dev": (i32, (vp, vp, vp, vp, vp, sz, sz, sz, f32, vp, i32) + _ERR),
+    "h3b_gemm_fp4_swiglu_dev": (i32, (vp, vp, vp, vp, vp, sz, sz, sz, f32, vp, i32) + _ERR),
     "h3_cuda_nvfp4_weight_create": (i32, (vp, vp, vp, f32, sz, sz, C.POINTER(vp), dbl_p) + _ERR),
     "h3_cuda_nvfp4_weight_ensure_ready": (i32, (vp,) + _ERR),
     "h3_cuda_nvfp4_weight_free": (None, (vp, vp)),

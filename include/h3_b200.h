@@ -505,6 +505,13 @@ int h3b_gemm_fp4_dev(h3_cuda *cuda, const uint8_t *d_w_fp4, const uint8_t *d_sf_
                      const uint8_t *d_sf_x, size_t m, size_t n, size_t k, float alpha, void *d_y,
                      int out_dtype, char *error, size_t error_size);
 
+/* Addition: the same GEMM with SwiGLU on the f32 accumulators in the epilogue: weight rows [0, n/2) are the gate,
+ * [n/2, n) the up projection; d_y [m, n/2] = silu(alpha acc_gate) * (alpha acc_up).  n % 256 == 0.  This is the
+ * reference's chain FC1 (h3_cutlass_nvfp4_fc1_f32_run) + SwiGLU (h3_dit_nvfp4_chain.cu:201-277) as one kernel. */
+int h3b_gemm_fp4_swiglu_dev(h3_cuda *cuda, const uint8_t *d_w_fp4, const uint8_t *d_sf_w, const uint8_t *d_x_fp4,
+                            const uint8_t *d_sf_x, size_t m, size_t n, size_t k, float alpha, void *d_y,
+                            int out_dtype, char *error, size_t error_size);
+
 /* ------------------------------------------- the rest of the reference's operator surface
  * Everything below keeps the reference's name and signature (h3_gpu_cuda.h line cited per entry) so that the
  * reference's own DiT host (h3_dit_w4a8.c) links against this library without a change. */
@@ -652,6 +659,13 @@ void h3b_dit_free(h3b_dit *dit);
 /* The context borrows the weight object (the caller frees it after h3b_dit_free). */
 int h3b_dit_set_linear(h3b_dit *dit, unsigned block, int which, const h3_cuda_w4a8_weight *weight,
                        char *error, size_t error_size);
+/* Per-linear choice of the NVFP4 form of a weight (which = H3B_LIN_QKV, _OUT, _FC1 or _FC2), the decision the
+ * reference's nvfp4_gemm_dispatch takes per linear (h3_dit_w4a8.c:3519-3590, call sites :3623-3641): the linear then
+ * runs ConvRot -> NVFP4 activation quantisation -> block-scaled GEMM with the plain (QKV), SwiGLU (FC1) or
+ * gate (OUT, FC2) epilogue.  Reference block on an f32 stream only.  weight == NULL returns the linear to its INT8
+ * weight; a linear needs one of the two.  The weight object is borrowed. */
+int h3b_dit_set_linear_nvfp4(h3b_dit *dit, unsigned block, int which, const h3_cuda_nvfp4_weight *weight,
+                             char *error, size_t error_size);
 /* Host f32 vectors, copied to the device: norm1/norm2 [dim], q_norm/k_norm [head_dim],
  * norm_cross [dim] (cross block only, else NULL). */
 int h3b_dit_set_block_aux(h3b_dit *dit, unsigned block, const float *norm1, const float *norm2,

@@ -50,6 +50,66 @@ def test_reference_block_f32_stream_against_reference_vectors(cuda, oracle):
         dit.close()
 
 
+@pytest.mark.parametrize("fp4_linears,gs", [((0, 1, 2, 3), 0), ((0, 1, 2, 3), 256), ((2, 3), 256)])
+def test_reference_block_with_nvfp4_linears(cuda, oracle, fp4_linears, gs):
+    """Per-linear NVFP4 / INT8 choice in the reference block (the reference's nvfp4_gemm_dispatch,
+    h3_dit_w4a8.c:3519-3590): the chosen linears run ConvRot -> NVFP4 activation quantisation -> block-scaled GEMM with
+    the plain / SwiGLU / gate epilogue, the others stay INT8.  Checked against the same block put together from the
+    CPU checker's operators, with the NVFP4 linears as its quantiser + block-scaled product.  Bound 3e-2 (measured 0.9e-2 to
+    1.3e-2): the bf16 attention output differs from the checker's by 2e-3, and wherever that difference, carried along
+    the residual stream, moves an input of a later NVFP4 linear across a 4-bit code boundary, that input changes by up
+    to a sixth of its block maximum (the operator tests hold each NVFP4 linear to 1e-5 on identical inputs; the INT8
+    block, whose codes are 1/127 apart, holds 2e-3).  The NVFP4 block sits 3.7e-2 to 4e-2 from the INT8 block."""
+    from h3c_b200 import dit as D
+    g = np.load(GOLDEN / "block_r.npz")
+    dim, heads, hd, ffn, slots = 256, 2, 128, 512, 6
+    geo = D.DitGeometry(dim=dim, heads=heads, head_dim=hd, ffn=ffn, n_blocks=1, mod_rows=3, t_dim=8,
+                        kind=D.BLOCK_REFERENCE, stream_dtype=D.F32, convrot_gs=gs)
+    dit = D.Dit(cuda, geo)
+    names = ["qkv", "out", "fc1", "fc2"]
+    fp4, handles = {}, []
+    for i, name in enumerate(names):
+        dit.set_linear(0, D.LIN_NAMES_REF[name], cuda.weight_from_i8(g[f"w_{name}"], g[f"s_{name}"]))
+        if i in fp4_linears:
+            w = g[f"w_{name}"].astype(np.float32) * g[f"s_{name}"][:, None]
+            amax = float(np.abs(w).max())
+            scale2 = np.float32(amax / (6.0 * 448.0))              # per-tensor second-level scale of the sidecar
+            w4, sfw = oracle.quantize_nvfp4(w / scale2, rule=1)
+            h = cuda.nvfp4_weight(w4, sfw, float(scale2), *w.shape)
+            handles.append(h)
+            dit.set_linear_nvfp4(0, D.LIN_NAMES_REF[name], h)
+            fp4[name] = (w4, sfw, scale2)
+    dit.set_block_aux(0, g["norm1"], g["norm2"], g["q_norm"], g["k_norm"])
+    x, cos, sin, mod, rmap = g["x"], g["cos"], g["sin"], g["modulation"], g["row_map"]
+    y = dit.block_forward(0, dev(x), dev(cos), dev(sin), modulation=dev(mod), row_map=dev(rmap.view(np.int32)))
+    cuda.check()
+
+    def linear(name, a):
+        a = oracle.convrot(a, gs) if gs else a
+        if name in fp4:
+            w4, sfw, scale2 = fp4[name]
+            a4, sfa = oracle.quantize_nvfp4(a)
+            return oracle.gemm_nvfp4(a4, sfa, w4, sfw, scale2)
+        codes, scales = oracle.quantize_act_int8(a)
+        return oracle.gemm_i8_dequant(codes, g[f"w_{name}"], scales, g[f"s_{name}"])
+
+    a = oracle.adaln(x, g["norm1"], mod, rmap, slots, 0, 1)
+    q, k, v = oracle.qkv_rope(linear("qkv", a), g["q_norm"], g["k_norm"], cos, sin, heads, hd, 48)
+    att = oracle.bf16_round(oracle.sdpa(q, k, v))                   # the kernel hands the out projection bf16 rows
+    x1 = oracle.gate(x, linear("out", att.reshape(x.shape[0], -1)), mod, rmap, slots, 2)
+    h1 = oracle.swiglu(linear("fc1", oracle.adaln(x1, g["norm2"], mod, rmap, slots, 3, 4)))
+    want = oracle.gate(x1, linear("fc2", h1), mod, rmap, slots, 5)
+    err = rel_l2(y.cpu().numpy(), want)
+    far = rel_l2(y.cpu().numpy(), g[f"y_gs{gs}"])
+    print(f"NVFP4 linears {fp4_linears}, ConvRot {gs}: rel-L2 vs the checker's NVFP4 block {err:.2e}, vs the INT8 block {far:.2e}")
+    assert err < 3e-2, (fp4_linears, gs, err)
+    # it is the NVFP4 block that ran (4-bit weights and activations sit percents away from the INT8 block), not INT8
+    assert err < 0.5 * far < 0.2
+    dit.close()
+    for h in handles:
+        cuda.nvfp4_weight_free(h)
+
+
 def make_cross_case(cuda, oracle, seed, grid, text_len, dim, heads, ffn, n_blocks=1):
     from h3c_b200 import dit as D
     geo = D.DitGeometry(dim=dim, heads=heads, head_dim=128, ffn=ffn, n_blocks=n_blocks, mod_rows=1, t_dim=32,

@@ -416,6 +416,24 @@ def test_gemm_nvfp4(cuda, oracle, m, n, k):
     assert rel_l2(host(y), 0.5 * x @ w.T) < 0.2
 
 
+@pytest.mark.parametrize("m,n,k", [(150, 512, 512), (333, 1024, 256), (128, 256, 1024)])
+def test_gemm_nvfp4_swiglu_in_the_epilogue(cuda, oracle, m, n, k):
+    """SwiGLU on the f32 accumulators inside the GEMM (gate rows | up rows of the weight): the reference's chain
+    h3_cutlass_nvfp4_fc1_f32_run -> SwiGLU (h3_dit_nvfp4_chain.cu:201-277) as one kernel."""
+    rng = np.random.default_rng(71)
+    x = acts(rng, m, k)
+    w = rng.normal(0, 0.05, (n, k)).astype(np.float32)
+    w4, sfw = oracle.quantize_nvfp4(w, rule=1)
+    x4, sfx = cuda.quantize_act_nvfp4(dev(x))
+    want = oracle.swiglu(oracle.gemm_nvfp4(host(x4), host(sfx), w4, sfw, 0.5))
+    y = cuda.gemm_fp4(dev(w4), dev(sfw), x4, sfx, alpha=0.5, swiglu=True)
+    assert y.shape == (m, n // 2)
+    assert rel_l2(host(y), want) < 1e-5
+    yb = cuda.gemm_fp4(dev(w4), dev(sfw), x4, sfx, alpha=0.5, swiglu=True, out_dtype=torch.bfloat16)
+    assert rel_l2(host(yb), want) < 3e-3
+    cuda.check()
+
+
 @pytest.mark.parametrize("m,n,k", [(150, 256, 512), (300, 640, 1024), (90, 128, 256)])
 def test_reference_nvfp4_linear_entry_points(cuda, oracle, m, n, k):
     rng = np.random.default_rng(61)
@@ -435,8 +453,11 @@ def test_reference_nvfp4_linear_entry_points(cuda, oracle, m, n, k):
                                 row_map=dev(rmap.view(np.int32)), slots=slots, gate_slot=5)
     assert rel_l2(host(y), oracle.gate(res, base, mod, rmap, slots, 5)) < 1e-5
     y = cuda.gemm_fp4_w_act_dev(wh, dev(x), kind="swiglu")
-    fused = oracle.bf16_round(oracle.gemm_nvfp4(x4, sfx, w4, sfw, 1.0)) * np.float32(0.75)
-    assert rel_l2(host(y), oracle.swiglu(fused)) < 2e-3   # bf16 accumulators, as in the reference's fp4 path
+    if n % 256 == 0:   # SwiGLU on the f32 accumulators in the GEMM epilogue
+        assert rel_l2(host(y), oracle.swiglu(base)) < 1e-5
+    else:              # other widths: bf16 accumulators and a second kernel, as in the reference's fp4 path
+        fused = oracle.bf16_round(oracle.gemm_nvfp4(x4, sfx, w4, sfw, 1.0)) * np.float32(0.75)
+        assert rel_l2(host(y), oracle.swiglu(fused)) < 2e-3
     cuda.check()
     cuda.nvfp4_weight_free(wh)
 
