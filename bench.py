@@ -452,6 +452,107 @@ def gpu_arm(args):
         dist.destroy_process_group()
 
 
+def nvfp4_arm(args):
+    """`--weights nvfp4`: the 6,144-token step on the reference's own block (SwiGLU FFN, no cross-attention, f32
+    residual stream, 256-wide ConvRot) with all four linears per block as NVFP4 weights, the path the reference
+    takes through nvfp4_gemm_dispatch.  One GPU.  Roofline on the block-scaled GEMM."""
+    import torch
+    import h3c_b200
+    from h3c_b200 import dit as D
+    if int(os.environ.get("WORLD_SIZE", "1")) != 1 or args.gpus != 1:
+        raise SystemExit("--weights nvfp4 is a single-GPU workload")
+    torch.cuda.set_device(0)
+    cuda = h3c_b200.Cuda(0)
+    cuda.set_quiet(True)
+    geo = D.DitGeometry(dim=GEO["dim"], heads=GEO["heads"], head_dim=GEO["head_dim"], ffn=GEO["ffn"],
+                        n_blocks=GEO["n_blocks"], mod_rows=1, t_dim=256, kind=D.BLOCK_REFERENCE, stream_dtype=D.F32,
+                        convrot_gs=256)
+    dit = D.build_synthetic(cuda, geo, seed=0, nvfp4=True)
+    grid = GRID_1GPU
+    seq = grid[0] * grid[1] * grid[2]
+    inv_freq = (1.0 / (10000.0 ** (np.arange(16) / 16.0))).astype(np.float32)
+    cos_h, sin_h = h3c_b200.video_rope_tables(inv_freq, GEO["text"], grid, 1.0)
+    x_h = torch.from_numpy(np.random.default_rng(1000).normal(0, 1, (seq, geo.dim)).astype(np.float32)).pin_memory()
+    cos_p, sin_p = torch.from_numpy(cos_h).pin_memory(), torch.from_numpy(sin_h).pin_memory()
+    half = geo.t_dim // 2
+    freqs = np.exp(-np.log(10000.0) * np.arange(half) / half)
+    t_feat_h = torch.from_numpy(np.concatenate([np.cos(500.0 * freqs), np.sin(500.0 * freqs)]).astype(np.float32)).pin_memory()
+    y_h = torch.empty((seq, geo.dim), dtype=torch.float32).pin_memory()
+    x_d, cos_d, sin_d, t_d = x_h.cuda(), cos_p.cuda(), sin_p.cuda(), t_feat_h.cuda()
+    rmap_d = torch.zeros(seq, dtype=torch.int32, device="cuda")
+    y_d = torch.empty_like(x_d)
+    dit.reserve(seq, 0)
+
+    def step_resident():
+        dit.project_modulation(t_d)
+        dit.layers_forward(x_d, cos_d, sin_d, row_map=rmap_d, out=y_d)
+
+    def step_e2e():
+        dit.layers_forward_f32(t_feat_h, x_h, cos_p, sin_p, out=y_h)
+
+    for _ in range(args.warmup):
+        step_resident()
+    torch.cuda.synchronize()
+    cuda.check()
+    sampler = ClockSampler(0)
+    sampler.start()
+    time.sleep(0.3)
+    cuda.launch_count(reset=True)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        step_resident()
+    e1.record()
+    torch.cuda.synchronize()
+    launches = cuda.launch_count(reset=True)
+    ms_step = e0.elapsed_time(e1) / args.steps
+    clocks = sampler.stop()
+    cuda.check()
+    finite = bool(torch.isfinite(y_d).all().item())
+    prof = profile_classes(cuda, dit, step_resident)
+    if "gemm_i8" in prof:
+        prof["gemm_fp4"] = prof.pop("gemm_i8")   # the GEMM class of this workload is the block-scaled NVFP4 kernel
+    e2e_ms = None
+    if not args.skip_e2e:
+        step_e2e()
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        for _ in range(args.steps):
+            step_e2e()
+        torch.cuda.synchronize()
+        e2e_ms = (time.perf_counter() - t0) * 1e3 / args.steps
+    D_, F_ = geo.dim, geo.ffn
+    lin_f = 2.0 * seq * (D_ * 3 * D_ + D_ * D_ + D_ * 2 * F_ + F_ * D_)
+    attn_f = 4.0 * seq * seq * D_
+    g = prof.get("gemm_fp4")
+    roof = None
+    if g:
+        probe = h3c_b200.tensor_pipe_rate(cuda, 2, 1000000)
+        achieved = lin_f * geo.n_blocks / (g["ms"] * 1e-3) / 1e12
+        roof = {"bound": "tensor", "kernel": "gemm_fp4", "achieved": achieved, "peak": probe, "unit": "TFLOP/s",
+                "frac": achieved / probe, "traffic": None,
+                "peak_note": "NVFP4 block-scaled tcgen05.mma rate of this GPU over about a second of back-to-back MMAs from "
+                             "a resident tile, measured in this run",
+                "share_of_step": g["ms"] / sum(v["ms"] for v in prof.values())}
+    line = {"metric": METRIC, "value": ms_step, "unit": UNIT, "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": ms_step, "higher_is_better": False, "scaling": "weak", "vs_baseline": None,
+            "dtype": "nvfp4 (linears, f32 accumulate) + bf16 (attention, f32 accumulate)", "data": "synthetic",
+            "config": {"workload": "50 reference blocks (SwiGLU, no cross-attention), 6,144 tokens, every linear NVFP4",
+                       "tokens": seq, "patch_grid": list(grid), "dim": D_, "heads": geo.heads, "head_dim": geo.head_dim,
+                       "ffn": F_, "blocks": geo.n_blocks, "convrot": 256,
+                       "weights": "NVFP4 (E2M1, UE4M3 scale per 16, f32 second-level scale)",
+                       "activations": "ConvRot + NVFP4 per linear, f32 residual stream",
+                       "l2": "each step streams 3.8 GB of weights and >1 GB of activations, far above the 126 MB L2"},
+            "e2e": {"value": e2e_ms, "unit": UNIT, "h2d_bytes_per_step": int(x_h.numel() * 4 + cos_p.numel() * 8 + t_feat_h.numel() * 4),
+                    "d2h_bytes_per_step": int(y_h.numel() * 4)},
+            "gpu_launches": int(launches), "clocks": clocks, "roofline": roof, "cpu_baseline": None,
+            "step_tflops": (lin_f + attn_f) * geo.n_blocks / (ms_step * 1e-3) / 1e12, "kernel_classes": prof,
+            "output_finite": finite}
+    OUT.emit(json.dumps(line))
+    dit.close()
+    cuda.close()
+
+
 def full_input_rows(world, seq_real, seq_pad, dim):
     """The activations of the whole (padded) sequence as the ranks generate them: rank r seeds its own slice."""
     seq_local = seq_pad // world
@@ -769,6 +870,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="auto", choices=["auto", "ulysses", "step6144"],
                     help="auto / ulysses: the 50,220-token step at any N; step6144: the 6,144-token single-GPU step")
+    ap.add_argument("--weights", default="w4a8", choices=["w4a8", "nvfp4"],
+                    help="nvfp4: the 6,144-token step on the reference block with every linear NVFP4 (N = 1)")
     ap.add_argument("--graph", action="store_true", help="replay the resident step as one CUDA graph (N = 1)")
     ap.add_argument("--skip-cpu-baseline", action="store_true", help="omit the CPU sample (profiling runs)")
     ap.add_argument("--skip-e2e", action="store_true", help="omit the host-buffer measurement (profiling runs)")
@@ -792,6 +895,8 @@ def main():
         kernel_arm(args)
     elif args.impl == "reference":
         reference_arm(args)
+    elif args.weights == "nvfp4":
+        nvfp4_arm(args)
     else:
         gpu_arm(args)
 

@@ -655,7 +655,10 @@ __global__ void __launch_bounds__(gemm::THREADS, 1) k_gemm_i8(const __grid_const
                                     float u = __fmul_rn(__fmul_rn(a, sc2[v + e]), (float)(int32_t)r2[v + e]);
                                     if (lora_on && col + v + e < p.n_out)
                                         u = __fadd_rn(u, __ldg(p.lora + (size_t)row * p.N + p.n_out + col + v + e));
-                                    val = __fmul_rn(val / __fadd_rn(1.0f, expf(-val)), u);
+                                    // 16-bit outputs: hardware exponential and reciprocal (2 ulp, far below the output's
+                                    // rounding); f32 outputs keep the IEEE forms the CPU path uses
+                                    val = sizeof(OutT) == 2 ? __fmul_rn(__fdividef(val, __fadd_rn(1.0f, __expf(-val))), u)
+                                                            : __fmul_rn(val / __fadd_rn(1.0f, expf(-val)), u);
                                 }
                                 out[e] = val;
                             }

@@ -47,6 +47,7 @@ class Dit:
         if not self.h:
             raise H3Error(f"h3b_dit_create: {err.value.decode(errors='replace')}")
         self._weights = []  # keep the borrowed weight objects alive
+        self._fp4 = []      # NVFP4 weight handles this object owns (set_linear_nvfp4(..., own=True))
 
     def close(self):
         if self.h:
@@ -55,6 +56,9 @@ class Dit:
         for w in self._weights:
             w.free()
         self._weights = []
+        for h in self._fp4:
+            self.cuda.nvfp4_weight_free(h)
+        self._fp4 = []
 
     def close_keep_weights(self):
         """Frees the context only; for a context whose weight objects belong to another one."""
@@ -67,9 +71,12 @@ class Dit:
         call("h3b_dit_set_linear", self.h, block, which, weight.h)
         self._weights.append(weight)
 
-    def set_linear_nvfp4(self, block, which, weight_handle):
-        """NVFP4 form of QKV / OUT / FC1 / FC2 (handle from Cuda.nvfp4_weight; None returns the linear to INT8)."""
+    def set_linear_nvfp4(self, block, which, weight_handle, own=False):
+        """NVFP4 form of QKV / OUT / FC1 / FC2 (handle from Cuda.nvfp4_weight; None returns the linear to INT8).
+        own: the handle is freed by close()."""
         call("h3b_dit_set_linear_nvfp4", self.h, block, which, weight_handle)
+        if own and weight_handle:
+            self._fp4.append(weight_handle)
 
     def set_block_aux(self, block, norm1, norm2, q_norm, k_norm, norm_cross=None):
         f = lambda a: None if a is None else np.ascontiguousarray(a, np.float32)
@@ -196,10 +203,22 @@ def _rand_w4g_weight(cuda, gen, n, k, group=128, std=0.02):
     return cuda.weight_from_w4g(packed, scales, group), packed, scales
 
 
-def build_synthetic(cuda, geo: DitGeometry, seed=0, keep_host=False):
+def _rand_nvfp4_weight(cuda, gen, n, k, std=0.02):
+    """Handle of an NVFP4 weight: N(0, std^2) values scaled to the E2M1 range, quantised on the device by the
+    library's block quantiser (16-value blocks, UE4M3 scales in the 128 x 4 tile layout), second-level scale
+    undoing the range scaling."""
+    import torch
+    up = 6.0 * 448.0 / (4.0 * std)                      # a 4-sigma weight lands on the largest code x largest scale
+    w = torch.randn((n, k), generator=gen, device=cuda.device, dtype=torch.float32) * (std * up)
+    packed, sf = cuda.quantize_act_nvfp4(w)
+    return cuda.nvfp4_weight(packed.cpu().numpy(), sf.cpu().numpy(), 1.0 / up, n, k)
+
+
+def build_synthetic(cuda, geo: DitGeometry, seed=0, keep_host=False, nvfp4=False):
     """Builds a `Dit` with seeded random W4 (group 128, f16 scales) weights.  With keep_host the
     packed weights and aux tensors are also returned per block (for oracle comparisons); an integer
-    keep_host keeps the aux tensors (not the packed weights) of that many leading blocks only."""
+    keep_host keeps the aux tensors (not the packed weights) of that many leading blocks only.
+    nvfp4: the four linears of the reference block as NVFP4 weights instead (f32 stream)."""
     aux_only = 0 if isinstance(keep_host, bool) else int(keep_host)
     import torch
     gen = torch.Generator(device=cuda.device)
@@ -218,6 +237,9 @@ def build_synthetic(cuda, geo: DitGeometry, seed=0, keep_host=False):
     for b in range(geo.n_blocks):
         rec = {}
         for name, (n, k) in shapes.items():
+            if nvfp4:
+                dit.set_linear_nvfp4(b, names[name], _rand_nvfp4_weight(cuda, gen, n, k), own=True)
+                continue
             w, packed, scales = _rand_w4g_weight(cuda, gen, n, k)
             dit.set_linear(b, names[name], w)
             if keep_host and not aux_only:
