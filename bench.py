@@ -782,6 +782,21 @@ def kernel_arm(a):
         res = torch.zeros_like(y) if a.epi == "gate" else None
         ms = _time_kernel(lambda: cuda.gemm_i8(w, x, s, kind=kind, residual=res, out=y), a.iters)
         out.update(m=a.m, n=a.n, k=a.k, epi=a.epi, ms=ms, tops=2.0 * a.m * a.n * a.k / ms / 1e9)
+    elif a.kernel == "gemm_w4g":   # exact int4 group-128 product next to the resident-int8 form of the same weight
+        rng = np.random.default_rng(0)
+        packed = rng.integers(0, 256, (a.n, a.k // 2), dtype=np.uint8)
+        scales = np.full((a.n, a.k // 128), np.float16(0.003)).view(np.uint16)
+        x = torch.randint(-127, 128, (a.m, a.k), generator=g, device="cuda", dtype=torch.int8)
+        s = torch.full((a.m,), 0.01, device="cuda")
+        h = cuda.w4g_exact_weight(packed, scales)
+        y = torch.empty((a.m, a.n), dtype=torch.bfloat16, device="cuda")
+        from h3c_b200.lib import call as call_, ptr as ptr_
+        ms = _time_kernel(lambda: call_("h3b_gemm_w4g_exact_dev", cuda.h, h, ptr_(x), ptr_(s), a.m, ptr_(y), 1), a.iters)
+        w8 = cuda.weight_from_w4g(packed, scales, 128)
+        ms8 = _time_kernel(lambda: cuda.gemm_i8(w8, x, s, kind=h3c_b200.EPI_PLAIN, out=y), a.iters)
+        out.update(m=a.m, n=a.n, k=a.k, exact_ms=ms, exact_tops=2.0 * a.m * a.n * a.k / ms / 1e9, resident_int8_ms=ms8,
+                   resident_int8_tops=2.0 * a.m * a.n * a.k / ms8 / 1e9)
+        cuda.w4g_exact_weight_free(h)
     elif a.kernel == "peak":
         for kind, name in ((0, "int8"), (1, "bf16"), (2, "nvfp4"), (3, "bf16_n128_ss"), (4, "bf16_n128_ts"), (5, "nvfp4_n128")):
             out[name + "_burst_tops"] = h3c_b200.tensor_pipe_rate(cuda, kind, 20000)         # ~10 ms of MMAs: burst clocks
@@ -877,7 +892,7 @@ def main():
     ap.add_argument("--skip-e2e", action="store_true", help="omit the host-buffer measurement (profiling runs)")
     ap.add_argument("--skip-checks", action="store_true", help="omit the parity / sharding self-checks (profiling runs)")
     ap.add_argument("--kernel", default=None,
-                    choices=["gemm", "gemm_fp4", "attn", "norm", "rope", "peak", "sides"],
+                    choices=["gemm", "gemm_fp4", "gemm_w4g", "attn", "norm", "rope", "peak", "sides"],
                     help="time ONE operator on synthetic data instead of the step (also the ncu capture commands)")
     ap.add_argument("--m", type=int, default=6144)
     ap.add_argument("--n", type=int, default=9216)

@@ -307,6 +307,27 @@ class Cuda:
              hd, scale, ptr(out), out.stride(0))
         return out
 
+    # ---- int4 group-128 weights multiplied exactly (packed in HBM, expanded in registers)
+    def w4g_exact_weight(self, packed, scales_f16_bits):
+        """packed uint8 [n, k/2] (low nibble = even k), scales uint16 (f16 bits) [n, k/128] -> handle."""
+        import numpy as np
+        packed = np.ascontiguousarray(packed, np.uint8)
+        scales = np.ascontiguousarray(scales_f16_bits, np.uint16)
+        h = C.c_void_p()
+        call("h3b_w4g_exact_weight_create", self.h, packed.ctypes.data, scales.ctypes.data, packed.shape[0],
+             packed.shape[1] * 2, C.byref(h))
+        return h.value
+
+    def w4g_exact_weight_free(self, handle):
+        load().h3b_w4g_exact_weight_free(handle)
+
+    def gemm_w4g_exact(self, handle, n, x_i8, act_scales, out_dtype=None):
+        import torch
+        out_dtype = out_dtype or torch.float32
+        y = torch.empty((x_i8.shape[0], n), dtype=out_dtype, device=x_i8.device)
+        call("h3b_gemm_w4g_exact_dev", self.h, handle, ptr(x_i8), ptr(act_scales), x_i8.shape[0], ptr(y), _dt(y))
+        return y
+
     def sdpa(self, q, k, v, scale=None, out=None):
         """q [lq,H,128], k/v [lk,H,128], all bf16 or all f16, any row / head strides that are multiples of 8
         elements -> [lq, H*128] of the same type (h3b_sdpa_strided_dev)."""

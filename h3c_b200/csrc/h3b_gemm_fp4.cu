@@ -65,12 +65,6 @@ struct Fp4Params {
     int *status;
 };
 
-__device__ __forceinline__ void bulk_load(void *dst, const void *src, uint32_t bytes, uint64_t *bar) {
-    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
-                     smem_u32(dst)),
-                 "l"(src), "r"(bytes), "r"(smem_u32(bar))
-                 : "memory");
-}
 
 // Shared-memory descriptor of one 512-byte scale block, read as 32 rows of 16 bytes (rows 16 bytes
 // apart, 8-row groups 128 bytes apart, no swizzle); tcgen05.cp broadcasts it to the four lane quarters.

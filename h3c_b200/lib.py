@@ -184,6 +184,9 @@ _SIGS = {
     "h3b_dit_layers_forward_f32": (i32, (vp, C.c_uint, C.c_uint, vp, vp, sz, vp, vp, vp, vp, sz, vp) + _ERR),
     "h3b_dit_launches_per_block": (i32, (vp,)),
     "h3_cuda_gemm_fp4_bs_dev": (i32, (vp, vp, vp, vp, vp, sz, sz, sz, vp, dbl_p) + _ERR),
+    "h3b_w4g_exact_weight_create": (i32, (vp, vp, vp, sz, sz, C.POINTER(vp)) + _ERR),
+    "h3b_w4g_exact_weight_free": (None, (vp,)),
+    "h3b_gemm_w4g_exact_dev": (i32, (vp, vp, vp, vp, sz, vp, i32) + _ERR),
     "h3b_gemm_fp4_dev": (i32, (vp, vp, vp, vp, vp, sz, sz, sz, f32, vp, i32) + _ERR),
     "h3b_gemm_fp4_swiglu_dev": (i32, (vp, vp, vp, vp, vp, sz, sz, sz, f32, vp, i32) + _ERR),
     "h3_cuda_nvfp4_weight_create": (i32, (vp, vp, vp, f32, sz, sz, C.POINTER(vp), dbl_p) + _ERR),

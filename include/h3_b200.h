@@ -136,6 +136,19 @@ int h3_cuda_w4a8_weight_download_int8(const h3_cuda_w4a8_weight *weight, int8_t 
 int h3b_w4g_weight_create(h3_cuda *cuda, const uint8_t *packed_host, const uint16_t *scales_f16,
                           size_t n, size_t k, int group, h3_cuda_w4a8_weight **out,
                           char *error, size_t error_size);
+/* Addition: the same weight format kept PACKED on the device and multiplied exactly as the format defines it,
+ *   y[m,n] = a[m] * sum_g s[n,g] * (sum_{k in group g} x_i8[m,k] * q[n,k]),
+ * int32 partial sums per 128-K group, each scaled in f32 (one multiplication, one addition, in group order): the codes
+ * are expanded to int8 in registers on their way into the tile that tcgen05.mma reads.  Selectable next to the
+ * resident-int8 form above, which is the faster one.  K % 128 == 0, N % 4 == 0 (N % 8 for bf16 output);
+ * d_x_i8 [m, K] and d_act_scales [m] as produced by the activation quantiser; d_y [m, N] H3B_F32 or H3B_BF16. */
+typedef struct h3b_w4g_exact_weight h3b_w4g_exact_weight;
+int h3b_w4g_exact_weight_create(h3_cuda *cuda, const uint8_t *packed_host, const uint16_t *scales_f16_host, size_t n,
+                                size_t k, h3b_w4g_exact_weight **out, char *error, size_t error_size);
+void h3b_w4g_exact_weight_free(h3b_w4g_exact_weight *weight);
+int h3b_gemm_w4g_exact_dev(h3_cuda *cuda, const h3b_w4g_exact_weight *weight, const int8_t *d_x_i8,
+                           const float *d_act_scales, size_t m, void *d_y, int out_dtype, char *error,
+                           size_t error_size);
 /* Addition: device pointers of the resident tensors. */
 const int8_t *h3b_w4a8_weight_data(const h3_cuda_w4a8_weight *weight);
 const float *h3b_w4a8_weight_scales(const h3_cuda_w4a8_weight *weight);
