@@ -54,6 +54,8 @@ struct h3b_dit {
     uint32_t *st_map;
     float *st_cos, *st_sin, *st_t;
     h3_ulysses_cfg *uly;    /* attached per-rank communicator, or NULL */
+    h3_cuda_w4a8_weight **owned;   /* weights created by the checkpoint loader, freed with the context */
+    size_t n_owned, cap_owned;
     /* the chain captured as one CUDA graph (h3b_dit_layers_forward_graph_dev) and what it was captured for */
     cudaGraph_t graph;
     cudaGraphExec_t graph_exec;
@@ -181,6 +183,8 @@ void h3b_dit_free(h3b_dit *d) {
         for (i = 0; i < sizeof(p) / sizeof(p[0]); i++)
             if (p[i]) cudaFree(p[i]);
     }
+    for (b = 0; b < d->n_owned; b++) h3_cuda_w4a8_weight_free(d->owned[b]);
+    free(d->owned);
     free(d->blocks);
     free(d);
 }
@@ -255,6 +259,86 @@ int h3b_dit_set_adaln(h3b_dit *d, unsigned block, const float *w, const float *b
     if (!k->modulation && !dmalloc((void **)&k->modulation, mod_elems(d) * sizeof(float), error, error_size)) return 0;
     return upload(&k->adaln_w, w, mod_elems(d) * d->cfg.t_dim, error, error_size) &&
            upload(&k->adaln_b, b, mod_elems(d), error, error_size);
+}
+
+/* ---- INT8-ConvRot checkpoint block -> context (names of h3_dit_int8.h:37-40 and h3_dit_w4a8.c:2056-2117) */
+static const float *ckpt_f32(const h3b_ckpt *c, const char *name, size_t count, char *error, size_t error_size) {
+    h3b_ckpt_tensor t;
+    if (!h3b_ckpt_find(c, name, &t)) {
+        fail(error, error_size, "checkpoint: tensor %s missing", name);
+        return NULL;
+    }
+    if (strcmp(t.dtype, "F32") != 0 || t.bytes != count * sizeof(float)) {
+        fail(error, error_size, "checkpoint: %s is %s with %zu bytes, expected F32 x %zu", name, t.dtype, t.bytes, count);
+        return NULL;
+    }
+    return (const float *)t.data;
+}
+
+int h3b_dit_load_int8_convrot_block(h3b_dit *d, const h3b_ckpt *ckpt, unsigned src_block, unsigned dst_block,
+                                    char *error, size_t error_size) {
+    static const char *suffix[4] = {"attn.qkv_proj", "attn.out_proj", "mlp.fc1", "mlp.fc2"};
+    static const int slot[4] = {H3B_LIN_QKV, H3B_LIN_OUT, H3B_LIN_FC1, H3B_LIN_FC2};
+    char name[256];
+    const float *n1, *n2, *qn, *kn, *aw, *ab;
+    size_t D, I, F, mod;
+    int l;
+    if (!d || !ckpt || dst_block >= d->cfg.n_blocks) return fail(error, error_size, "load_int8_convrot_block: invalid arguments");
+    if (d->cfg.kind != H3B_BLOCK_REFERENCE)
+        return fail(error, error_size, "load_int8_convrot_block: the INT8-ConvRot checkpoint holds the reference block");
+    D = d->cfg.dim; I = inner(d); F = d->cfg.ffn; mod = d->cfg.mod_rows * 6 * D;
+    for (l = 0; l < 4; l++) {
+        const size_t want_n[4] = {3 * I, D, 2 * F, D}, want_k[4] = {D, I, D, F};
+        h3b_ckpt_tensor w, s;
+        h3_cuda_w4a8_weight *obj = NULL;
+        snprintf(name, sizeof(name), "blocks.%u.%s.weight", src_block, suffix[l]);
+        if (!h3b_ckpt_find(ckpt, name, &w)) return fail(error, error_size, "checkpoint: tensor %s missing", name);
+        if (strcmp(w.dtype, "I8") != 0 || w.rank != 2 || w.shape[0] != want_n[l] || w.shape[1] != want_k[l])
+            return fail(error, error_size, "checkpoint: %s is %s rank %d [%zu, %zu], expected I8 [%zu, %zu]", name, w.dtype,
+                        w.rank, w.shape[0], w.rank > 1 ? w.shape[1] : 0, want_n[l], want_k[l]);
+        snprintf(name, sizeof(name), "blocks.%u.%s.weight_scale", src_block, suffix[l]);
+        if (!h3b_ckpt_find(ckpt, name, &s)) return fail(error, error_size, "checkpoint: tensor %s missing", name);
+        if (strcmp(s.dtype, "F32") != 0 || s.bytes != want_n[l] * sizeof(float))
+            return fail(error, error_size, "checkpoint: %s must be F32 with one scale per output row", name);
+        /* the mapping is borrowed for the upload only: it has completed when ensure_ready returns, so the caller may
+         * close the checkpoint right after this call */
+        if (!h3_cuda_w4a8_weight_create_from_i8(d->cuda, (int8_t *)(uintptr_t)w.data, want_n[l], want_k[l],
+                                                (float *)(uintptr_t)s.data, &obj, NULL, 1, error, error_size))
+            return 0;
+        if (!h3_cuda_w4a8_weight_ensure_ready(obj, error, error_size)) {
+            h3_cuda_w4a8_weight_free(obj);
+            return 0;
+        }
+        if (d->n_owned == d->cap_owned) {
+            size_t ncap = d->cap_owned ? 2 * d->cap_owned : 16;
+            h3_cuda_w4a8_weight **no = (h3_cuda_w4a8_weight **)realloc(d->owned, ncap * sizeof(*no));
+            if (!no) {
+                h3_cuda_w4a8_weight_free(obj);
+                return fail(error, error_size, "load_int8_convrot_block: out of host memory");
+            }
+            d->owned = no;
+            d->cap_owned = ncap;
+        }
+        d->owned[d->n_owned++] = obj;
+        if (!h3b_dit_set_linear(d, dst_block, slot[l], obj, error, error_size)) return 0;
+    }
+    snprintf(name, sizeof(name), "blocks.%u.norm1.weight", src_block);
+    if (!(n1 = ckpt_f32(ckpt, name, D, error, error_size))) return 0;
+    snprintf(name, sizeof(name), "blocks.%u.norm2.weight", src_block);
+    if (!(n2 = ckpt_f32(ckpt, name, D, error, error_size))) return 0;
+    snprintf(name, sizeof(name), "blocks.%u.attn.q_norm.weight", src_block);
+    if (!(qn = ckpt_f32(ckpt, name, d->cfg.head_dim, error, error_size))) return 0;
+    snprintf(name, sizeof(name), "blocks.%u.attn.k_norm.weight", src_block);
+    if (!(kn = ckpt_f32(ckpt, name, d->cfg.head_dim, error, error_size))) return 0;
+    if (!h3b_dit_set_block_aux(d, dst_block, n1, n2, qn, kn, NULL, error, error_size)) return 0;
+    snprintf(name, sizeof(name), "blocks.%u.adaln_proj.linear.weight", src_block);
+    if (h3b_ckpt_find(ckpt, name, NULL)) {   /* optional: a caller may supply the modulation itself */
+        if (!(aw = ckpt_f32(ckpt, name, mod * d->cfg.t_dim, error, error_size))) return 0;
+        snprintf(name, sizeof(name), "blocks.%u.adaln_proj.linear.bias", src_block);
+        if (!(ab = ckpt_f32(ckpt, name, mod, error, error_size))) return 0;
+        if (!h3b_dit_set_adaln(d, dst_block, aw, ab, error, error_size)) return 0;
+    }
+    return 1;
 }
 
 int h3b_dit_project_modulation(h3b_dit *d, const float *d_t_feat, char *error, size_t error_size) {

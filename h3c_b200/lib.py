@@ -170,6 +170,12 @@ _SIGS = {
     "h3b_euler_step_f32_dev": (i32, (vp, vp, vp, sz, f32, f32) + _ERR),
     "h3b_dit_create": (vp, (vp, C.POINTER(DitConfig)) + _ERR),
     "h3b_dit_free": (None, (vp,)),
+    "h3b_ckpt_open": (vp, (C.c_char_p,) + _ERR),
+    "h3b_ckpt_close": (None, (vp,)),
+    "h3b_ckpt_count": (sz, (vp,)),
+    "h3b_ckpt_get": (i32, (vp, sz, vp)),
+    "h3b_ckpt_find": (i32, (vp, C.c_char_p, vp)),
+    "h3b_dit_load_int8_convrot_block": (i32, (vp, vp, C.c_uint, C.c_uint) + _ERR),
     "h3b_dit_set_linear": (i32, (vp, C.c_uint, i32, vp) + _ERR),
     "h3b_dit_set_linear_nvfp4": (i32, (vp, C.c_uint, i32, vp) + _ERR),
     "h3b_dit_set_block_aux": (i32, (vp, C.c_uint, vp, vp, vp, vp, vp) + _ERR),

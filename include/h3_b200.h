@@ -679,6 +679,29 @@ int h3b_dit_set_linear(h3b_dit *dit, unsigned block, int which, const h3_cuda_w4
  * weight; a linear needs one of the two.  The weight object is borrowed. */
 int h3b_dit_set_linear_nvfp4(h3b_dit *dit, unsigned block, int which, const h3_cuda_nvfp4_weight *weight,
                              char *error, size_t error_size);
+/* ---- checkpoints: the safetensors container (the reference's reader: h3_safetensors.c; its INT8-ConvRot DiT store:
+ * h3_dit_int8.c:120-206) -> device layouts.  The file is mapped read-only; a tensor is a view into the mapping. */
+typedef struct h3b_ckpt h3b_ckpt;
+typedef struct h3b_ckpt_tensor {
+    const char *name;     /* owned by the checkpoint */
+    char dtype[8];        /* "I8", "F32", "F16", "BF16", "U8", ... as written in the file */
+    int rank;
+    size_t shape[4];
+    const void *data;
+    size_t bytes;
+} h3b_ckpt_tensor;
+h3b_ckpt *h3b_ckpt_open(const char *path, char *error, size_t error_size);
+void h3b_ckpt_close(h3b_ckpt *ckpt);
+size_t h3b_ckpt_count(const h3b_ckpt *ckpt);
+int h3b_ckpt_get(const h3b_ckpt *ckpt, size_t index, h3b_ckpt_tensor *out);
+int h3b_ckpt_find(const h3b_ckpt *ckpt, const char *name, h3b_ckpt_tensor *out);
+/* Block `src_block` of an INT8-ConvRot DiT checkpoint -> block `dst_block` of a reference-kind context: the four
+ * linears blocks.N.{attn.qkv_proj, attn.out_proj, mlp.fc1, mlp.fc2}.weight (I8 [n, k]) + .weight_scale (F32 [n] or
+ * [n, 1]) become resident INT8 weights owned by the context (names: h3_dit_int8.h:37-40, h3_dit_int8.c:173);
+ * blocks.N.norm1/norm2.weight, blocks.N.attn.q_norm/k_norm.weight and blocks.N.adaln_proj.linear.weight/.bias (F32)
+ * are uploaded as h3_dit_w4a8_load_block_aux_hdr reads them (h3_dit_w4a8.c:2056-2117). */
+int h3b_dit_load_int8_convrot_block(h3b_dit *dit, const h3b_ckpt *ckpt, unsigned src_block, unsigned dst_block,
+                                    char *error, size_t error_size);
 /* Host f32 vectors, copied to the device: norm1/norm2 [dim], q_norm/k_norm [head_dim],
  * norm_cross [dim] (cross block only, else NULL). */
 int h3b_dit_set_block_aux(h3b_dit *dit, unsigned block, const float *norm1, const float *norm2,

@@ -136,3 +136,26 @@ def test_reference_host_runs_a_real_geometry_block_on_this_library(tmp_path, ora
     L.h3_dit_w4a8_free(C.c_void_p(ctx))
     L.h3_dit_int8_store_free(C.c_void_p(store))
     L.h3_cuda_free(C.c_void_p(cuda))
+
+    # ---- the same file through this library's own reader and block host (h3b_ckpt_open +
+    # h3b_dit_load_int8_convrot_block): same operators underneath, this library's orchestration
+    import h3c_b200
+    from h3c_b200 import dit as D
+    from h3c_b200.lib import call
+    cu = h3c_b200.Cuda(0)
+    geo = D.DitGeometry(dim=HIDDEN, heads=HEADS, head_dim=HD, ffn=FFN, n_blocks=1, mod_rows=MODS, t_dim=TFEAT,
+                        kind=D.BLOCK_REFERENCE, stream_dtype=D.F32, convrot_gs=256)
+    dit = D.Dit(cu, geo)
+    ck = h3c_b200.load().h3b_ckpt_open(str(path).encode(), err, ERR)
+    assert ck, err.value
+    call("h3b_dit_load_int8_convrot_block", dit.h, ck, 0, 0)
+    h3c_b200.load().h3b_ckpt_close(ck)          # the weights are resident: the mapping may go
+    dev = lambda a: torch.from_numpy(np.ascontiguousarray(a)).cuda()
+    y2 = dit.block_forward(0, dev(x), dev(cos), dev(sin), modulation=dev(mod), row_map=dev(row_map.view(np.int32)))
+    cu.check()
+    y2 = y2.cpu().numpy()
+    e_native, e_hosts = rel_l2(y2, want), rel_l2(y2, y)
+    print(f"native reader + h3b_dit block: rel-L2 vs the f32 CPU block {e_native:.2e}, vs the reference host's run {e_hosts:.2e}")
+    assert e_native < 2e-2 and e_hosts < 5e-3
+    dit.close()
+    cu.close()
