@@ -122,10 +122,10 @@ class Cuda:
     # ---- row-wise operators
     def norm(self, x, *, branch=None, norm_w=None, modulation=None, row_map=None, slots=0, gate_slot=0, shift_slot=0,
              scale_slot=0, eps=1e-5, identity=False, convrot_gs=0, gated=None, normed=None, rot=None, q=None,
-             scales=None):
+             scales=None, fp4=None, sf=None):
         a = _l.NormArgs(ptr(x), ptr(branch), ptr(norm_w), ptr(modulation), ptr(row_map), x.shape[0], x.shape[1],
                         slots, gate_slot, shift_slot, scale_slot, eps, _dt(x), int(identity), convrot_gs, ptr(gated),
-                        ptr(normed), ptr(rot), ptr(q), ptr(scales))
+                        ptr(normed), ptr(rot), ptr(q), ptr(scales), ptr(fp4), ptr(sf))
         call("h3b_norm_dev", self.h, C.byref(a))
 
     def quantize_act_int8(self, x):

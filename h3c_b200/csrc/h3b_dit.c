@@ -42,6 +42,7 @@ struct h3b_dit {
     void *cq;               /* bf16 [seq, inner] cross-attention queries */
     void *ckv;              /* bf16 [text, 2*inner] */
     float *rotf;            /* f32 [seq, max(dim, ffn, inner)]: activations of an NVFP4 linear (only when one is set) */
+    uint8_t *x4, *sfx;      /* NVFP4 codes [seq, max/2] and scale bytes of those activations (same condition) */
     int any_fp4;
     int8_t *q8;             /* [seq, max(dim, ffn, inner)] activation codes */
     float *s8;              /* [seq] activation scales */
@@ -154,7 +155,7 @@ static void free_group(void ***p, size_t n) {
 }
 static void free_seq_ws(h3b_dit *d) {
     void **p[] = {&d->xa, &d->xb, &d->io, &d->qkv, &d->wide, &d->q, &d->k, &d->v, &d->att, &d->cq, (void **)&d->q8,
-                  (void **)&d->rotf, (void **)&d->s8, (void **)&d->st_x, (void **)&d->st_map, (void **)&d->st_cos, (void **)&d->st_sin,
+                  (void **)&d->rotf, (void **)&d->x4, (void **)&d->sfx, (void **)&d->s8, (void **)&d->st_x, (void **)&d->st_map, (void **)&d->st_cos, (void **)&d->st_sin,
                   (void **)&d->st_t};
     drop_graph(d);   /* a captured chain points into the workspace */
     free_group(p, sizeof(p) / sizeof(p[0]));
@@ -389,7 +390,9 @@ int h3b_dit_reserve(h3b_dit *d, size_t seq, size_t text_seq, char *error, size_t
             !dmalloc((void **)&d->st_sin, table_rows * (d->cfg.rope_half ? d->cfg.rope_half : 1) * sizeof(float), error, error_size) ||
             !dmalloc((void **)&d->st_t, (d->cfg.t_dim ? d->cfg.t_dim : 1) * sizeof(float), error, error_size) ||
             (cross && !dmalloc(&d->cq, seq * I * 2, error, error_size)) ||
-            (d->any_fp4 && !dmalloc((void **)&d->rotf, seq * widest * sizeof(float), error, error_size))) {
+            (d->any_fp4 && (!dmalloc((void **)&d->rotf, seq * widest * sizeof(float), error, error_size) ||
+                            !dmalloc((void **)&d->x4, seq * widest / 2, error, error_size) ||
+                            !dmalloc((void **)&d->sfx, ((seq + 127) / 128) * ((widest + 63) / 64) * 512, error, error_size)))) {
             free_seq_ws(d);   /* a half-built group must not pass for capacity */
             return 0;
         }
@@ -446,6 +449,18 @@ static int fp4_linear(h3b_dit *d, const h3_cuda_nvfp4_weight *w, const void *x, 
                       char *error, size_t error_size) {
     const float *x_use;
     if (!d->rotf) return fail(error, error_size, "NVFP4 linear: workspace not reserved");
+    if (width % 64 == 0 && (epi != 1 || h3_cuda_nvfp4_weight_n(w) % 256 == 0)) {
+        /* one pass over the rows: (RMSNorm, modulation,) ConvRot and the NVFP4 quantisation in the row kernel, then the
+         * block-scaled GEMM on the codes */
+        h3b_norm_args a;
+        memset(&a, 0, sizeof(a));
+        a.d_x = x; a.d_norm_w = norm_w; a.d_modulation = identity ? NULL : mod; a.d_row_map = row_map; a.rows = rows;
+        a.width = width; a.slots = 6; a.shift_slot = shift_slot; a.scale_slot = scale_slot; a.epsilon = d->cfg.eps;
+        a.dtype = dt; a.identity = identity; a.convrot_gs = d->cfg.convrot_gs; a.d_fp4 = d->x4; a.d_sf = d->sfx;
+        if (!h3b_norm_dev(d->cuda, &a, error, error_size)) return 0;
+        return h3b_gemm_fp4_w_preq_dev(d->cuda, w, d->x4, d->sfx, rows, 1.0f, epi, residual, mod, row_map, 6, gate_slot, y,
+                                       H3B_F32, error, error_size);
+    }
     if (d->cfg.convrot_gs > 0 || !identity) {
         h3b_norm_args a;
         memset(&a, 0, sizeof(a));

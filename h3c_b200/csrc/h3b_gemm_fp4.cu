@@ -722,6 +722,19 @@ int h3b_gemm_fp4_swiglu_dev(h3_cuda *cuda, const uint8_t *d_w_fp4, const uint8_t
                              0, error, error_size);
 }
 
+int h3b_gemm_fp4_w_preq_dev(h3_cuda *cuda, const h3_cuda_nvfp4_weight *weight, const uint8_t *d_x_fp4,
+                            const uint8_t *d_sf_x, size_t m, float act_scale, int epi, const void *d_residual,
+                            const float *d_modulation, const uint32_t *d_row_map, size_t slots, size_t gate_slot,
+                            void *d_y, int out_dtype, char *error, size_t error_size) {
+    if (!cuda || !weight || !d_x_fp4 || !d_sf_x || !d_y || !m || epi < 0 || epi > 2)
+        return fail(error, error_size, "gemm_fp4_w_preq: invalid arguments");
+    if (epi == 2 && (!d_residual || !d_modulation || !slots)) return fail(error, error_size, "gemm_fp4_w_preq: gate epilogue needs residual and modulation");
+    return launch_gemm_nvfp4(cuda, weight->d_packed, weight->d_sf, d_x_fp4, d_sf_x, m, weight->n, weight->k,
+                             weight->scale2 * act_scale, d_y, out_dtype, epi == 2 ? 1 : epi == 1 ? 2 : 0,
+                             epi == 2 ? d_residual : NULL, epi == 2 ? d_modulation : NULL, epi == 2 ? d_row_map : NULL,
+                             epi == 2 ? slots : 0, epi == 2 ? gate_slot : 0, error, error_size);
+}
+
 // activation quantisation into the scratch area; returns pointers into it
 static int fp4_prepare(h3_cuda *cuda, const h3_cuda_nvfp4_weight *w, const float *d_x, size_t m, uint8_t *scratch,
                        uint8_t **x4, uint8_t **sfx, uint8_t **acc, double *prep_ms, char *error, size_t error_size) {

@@ -3,46 +3,9 @@
 // hardware cvt: E2M1 by a threshold table with ties going up in magnitude, scale = amax / 6
 // converted with frexpf + lroundf and clamped to at least byte 1.
 #include "h3b_internal.h"
+#include "h3b_nvfp4.cuh"
 
 namespace h3b {
-
-__device__ __forceinline__ uint8_t f32_to_ue4m3(float v) {   // h3_gpu_cuda.cu:4498-4513
-    int e, m, E;
-    if (!(v > 0.0f)) return 0;
-    const float f = frexpf(v, &e);
-    E = e + 6;
-    if (E <= 0) {
-        m = (int)lroundf(ldexpf(v, 6) * 8.0f);
-        return (uint8_t)(m > 7 ? 7 : m);
-    }
-    if (E >= 15) return 0x7E;
-    m = (int)lroundf((f * 2.0f - 1.0f) * 8.0f);
-    if (m == 8) {
-        E++;
-        m = 0;
-        if (E >= 15) return 0x7E;
-    }
-    return (uint8_t)((E << 3) | m);
-}
-
-__device__ __forceinline__ float ue4m3_to_f32(uint8_t b) {   // h3_gpu_cuda.cu:4515-4520
-    const int e = (b >> 3) & 15, m = b & 7;
-    if (e == 0) return ldexpf((float)m / 8.0f, -6);
-    if (e == 15 && m == 7) return __int_as_float(0x7fc00000);
-    return ldexpf(1.0f + (float)m / 8.0f, e - 7);
-}
-
-__device__ __forceinline__ uint32_t e2m1_nibble(float q) {   // h3_gpu_cuda.cu:4468-4496
-    const float a = fabsf(q);
-    uint32_t mag = (a >= 0.25f) + (a >= 0.75f) + (a >= 1.25f) + (a >= 1.75f) + (a >= 2.5f) + (a >= 3.5f) + (a >= 5.0f);
-    return ((q < 0.0f && mag != 0) ? 8u : 0u) | mag;
-}
-
-// byte offset of the scale of (row, 16-block) in the 128x4-blocked layout (h3_gpu_cuda.cu:4534-4552)
-__device__ __forceinline__ size_t sf_offset(size_t row, size_t blk, size_t ncb) {
-    const size_t r128 = row & 127u;
-    return ((row >> 7) * ncb + (blk >> 2)) * 512u + 16u * (r128 & 31u) + 4u * (r128 >> 5) + (blk & 3u);
-}
 
 // One thread per 16-element block; rows in [m, ceil128(m)) only clear their scale bytes.
 __global__ void k_quant_nvfp4(const float *x, size_t m, size_t m_pad, size_t k, uint8_t *packed, uint8_t *sf) {

@@ -9,6 +9,7 @@
 #include <cuda_fp16.h>
 
 #include "h3b_internal.h"
+#include "h3b_nvfp4.cuh"
 
 namespace h3b {
 
@@ -105,6 +106,7 @@ struct NormParams {
     float *rot;
     int8_t *q;
     float *scales;
+    uint8_t *fp4, *sf;   // NVFP4 codes [rows, width/2] and scale bytes (128 x 4 tile layout) of the final row values
 };
 
 // V = elements per vector access (4 when width % 4 == 0 and all pointers are
@@ -193,6 +195,23 @@ __global__ void __launch_bounds__(256) k_norm(NormParams p) {
             row[c] = v;
             amax = fmaxf(amax, fabsf(v));
             if (p.rot) p.rot[r * W + c] = v;
+        }
+    }
+
+    // ---- NVFP4 quantisation of the final row values (width % 16 == 0): four lanes per 16-element block
+    if (p.fp4) {
+        __syncthreads();   // the row is complete in shared memory, whichever stage wrote it last
+        uint8_t *dst = p.fp4 + r * (size_t)(W / 2);
+        for (unsigned base = 0; base < W; base += blockDim.x * 4) {
+            const unsigned c = base + threadIdx.x * 4;
+            const bool on = c < W;
+            const unsigned mask = __ballot_sync(0xffffffffu, on);
+            if (on) {
+                uint8_t sb;
+                const uint16_t codes = nvfp4_quad(*reinterpret_cast<const float4 *>(row + c), mask, &sb);
+                *reinterpret_cast<uint16_t *>(dst + c / 2) = codes;
+                if ((threadIdx.x & 3) == 0) p.sf[sf_offset(r, c / 16, W / 64)] = sb;
+            }
         }
     }
 
@@ -521,7 +540,7 @@ static int rowq_dispatch(h3_cuda *cuda, const NormParams &p, size_t rows, char *
     if constexpr (sizeof(T) != 2) {
         return -1;
     } else {
-    if (p.gs != 0 || p.rot || p.branch || p.gated) return -1;
+    if (p.gs != 0 || p.rot || p.branch || p.gated || p.fp4) return -1;
     auto al16 = [](const void *q_) { return !q_ || (reinterpret_cast<uintptr_t>(q_) & 15) == 0; };
     if (!al16(p.x) || !al16(p.normed) || !al16(p.norm_w) || !al16(p.mod) || (p.q && (reinterpret_cast<uintptr_t>(p.q) & 7)))
         return -1;
@@ -566,7 +585,7 @@ static int norm_reg_launch(h3_cuda *cuda, const NormParams &p, size_t rows, char
 // Picks the register-resident kernel when the shape allows it; returns -1 when it does not apply.
 template <typename T>
 static int norm_reg_dispatch(h3_cuda *cuda, const NormParams &p, size_t rows, char *error, size_t error_size) {
-    if (sizeof(T) != 2 || p.gs != 0 || p.rot || p.width % 1024) return -1;
+    if (sizeof(T) != 2 || p.gs != 0 || p.rot || p.fp4 || p.width % 1024) return -1;
     auto al16 = [](const void *q_) { return !q_ || (reinterpret_cast<uintptr_t>(q_) & 15) == 0; };
     if (!al16(p.x) || !al16(p.branch) || !al16(p.gated) || !al16(p.normed) || !al16(p.norm_w) || !al16(p.mod) ||
         (p.q && (reinterpret_cast<uintptr_t>(p.q) & 7)))
@@ -624,7 +643,18 @@ int launch_norm(h3_cuda *cuda, const h3b_norm_args *a, char *error, size_t error
     p.gate_slot = (unsigned)a->gate_slot; p.shift_slot = (unsigned)a->shift_slot;
     p.scale_slot = (unsigned)a->scale_slot; p.eps = a->epsilon; p.identity = a->identity;
     p.gs = a->convrot_gs; p.gated = a->d_gated; p.normed = a->d_normed; p.rot = a->d_rot; p.q = a->d_q;
-    p.scales = a->d_scales;
+    p.scales = a->d_scales; p.fp4 = a->d_fp4; p.sf = a->d_sf;
+    if (a->d_fp4) {
+        if (!a->d_sf) return fail(error, error_size, "norm: d_fp4 without d_sf");
+        if (a->width % 64) return fail(error, error_size, "norm: NVFP4 output needs a width that is a multiple of 64");
+        if (reinterpret_cast<uintptr_t>(a->d_fp4) & 1) return fail(error, error_size, "norm: misaligned d_fp4");
+        // scale bytes of the pad rows [rows, ceil128(rows)) are zero (h3_gpu_cuda.cu:4590-4596): they sit inside the
+        // last 128-row tile, which is cleared before the kernel writes the bytes of its real rows
+        if (a->rows % 128) {
+            const size_t tile = (a->width / 64) * 512;
+            H3B_CUDA_OK(cudaMemsetAsync(a->d_sf + (a->rows / 128) * tile, 0, tile, cuda->op_stream), "norm: clearing pad scales");
+        }
+    }
     // vector path: 4 elements per access (16 bytes of f32, 8 bytes of 16-bit types, 4 codes)
     const uintptr_t amask = 4 * dtype_bytes(a->dtype) - 1;
     auto al = [&](const void *q_, uintptr_t mask) { return !q_ || (reinterpret_cast<uintptr_t>(q_) & mask) == 0; };

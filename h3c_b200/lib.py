@@ -52,7 +52,8 @@ class NormArgs(C.Structure):  # h3b_norm_args
     _fields_ = [("d_x", vp), ("d_branch", vp), ("d_norm_w", vp), ("d_modulation", vp), ("d_row_map", vp),
                 ("rows", sz), ("width", sz), ("slots", sz), ("gate_slot", sz), ("shift_slot", sz),
                 ("scale_slot", sz), ("epsilon", f32), ("dtype", i32), ("identity", i32), ("convrot_gs", i32),
-                ("d_gated", vp), ("d_normed", vp), ("d_rot", vp), ("d_q", vp), ("d_scales", vp)]
+                ("d_gated", vp), ("d_normed", vp), ("d_rot", vp), ("d_q", vp), ("d_scales", vp), ("d_fp4", vp),
+                ("d_sf", vp)]
 
 
 class DitConfig(C.Structure):  # h3b_dit_config
@@ -194,6 +195,7 @@ _SIGS = {
     "h3b_w4g_exact_weight_free": (None, (vp,)),
     "h3b_gemm_w4g_exact_dev": (i32, (vp, vp, vp, vp, sz, vp, i32) + _ERR),
     "h3b_gemm_fp4_dev": (i32, (vp, vp, vp, vp, vp, sz, sz, sz, f32, vp, i32) + _ERR),
+    "h3b_gemm_fp4_w_preq_dev": (i32, (vp, vp, vp, vp, sz, f32, i32, vp, vp, vp, sz, sz, vp, i32) + _ERR),
     "h3b_gemm_fp4_swiglu_dev": (i32, (vp, vp, vp, vp, vp, sz, sz, sz, f32, vp, i32) + _ERR),
     "h3_cuda_nvfp4_weight_create": (i32, (vp, vp, vp, f32, sz, sz, C.POINTER(vp), dbl_p) + _ERR),
     "h3_cuda_nvfp4_weight_ensure_ready": (i32, (vp,) + _ERR),

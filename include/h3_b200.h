@@ -323,6 +323,8 @@ typedef struct h3b_norm_args {
     float *d_rot;                /* out: rotated row, f32 (h3_cuda_convrot_act_f32_dd) */
     int8_t *d_q;                 /* out: INT8 codes */
     float *d_scales;             /* out, with d_q: per-row scale */
+    uint8_t *d_fp4;              /* out: NVFP4 codes of the final row values [rows, width/2] (width % 64 == 0) */
+    uint8_t *d_sf;               /* out, with d_fp4: UE4M3 scales, layout and size of h3_cuda_nvfp4_sf_bytes */
 } h3b_norm_args;
 int h3b_norm_dev(h3_cuda *cuda, const h3b_norm_args *args, char *error, size_t error_size);
 
@@ -524,6 +526,15 @@ int h3b_gemm_fp4_dev(h3_cuda *cuda, const uint8_t *d_w_fp4, const uint8_t *d_sf_
 int h3b_gemm_fp4_swiglu_dev(h3_cuda *cuda, const uint8_t *d_w_fp4, const uint8_t *d_sf_w, const uint8_t *d_x_fp4,
                             const uint8_t *d_sf_x, size_t m, size_t n, size_t k, float alpha, void *d_y,
                             int out_dtype, char *error, size_t error_size);
+
+/* Addition: NVFP4 weight object x activations that are ALREADY NVFP4 codes + scales (for instance written by
+ * h3b_norm_dev's d_fp4 / d_sf outputs, which fuse RMSNorm, modulation, ConvRot and the quantisation into one pass
+ * over the row): epi 0 plain, 1 SwiGLU on the f32 accumulators (N % 256 == 0), 2 gate + residual.  The accumulator
+ * is scaled by weight scale2 * act_scale.  d_y H3B_F32 or H3B_BF16 (the residual has the same type). */
+int h3b_gemm_fp4_w_preq_dev(h3_cuda *cuda, const h3_cuda_nvfp4_weight *weight, const uint8_t *d_x_fp4,
+                            const uint8_t *d_sf_x, size_t m, float act_scale, int epi, const void *d_residual,
+                            const float *d_modulation, const uint32_t *d_row_map, size_t slots, size_t gate_slot,
+                            void *d_y, int out_dtype, char *error, size_t error_size);
 
 /* ------------------------------------------- the rest of the reference's operator surface
  * Everything below keeps the reference's name and signature (h3_gpu_cuda.h line cited per entry) so that the

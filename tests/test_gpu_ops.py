@@ -416,6 +416,29 @@ def test_gemm_nvfp4(cuda, oracle, m, n, k):
     assert rel_l2(host(y), 0.5 * x @ w.T) < 0.2
 
 
+@pytest.mark.parametrize("m,k,gs,dtype", [(300, 512, 256, "f32"), (128, 3072, 0, "f32"), (77, 1024, 64, "bf16")])
+def test_row_kernel_quantises_to_nvfp4_in_its_last_stage(cuda, oracle, m, k, gs, dtype):
+    """RMSNorm + modulation + ConvRot + NVFP4 quantisation in one pass over the row: codes and scale bytes equal the
+    stand-alone quantiser applied to the values the same launch writes out (bit for bit), pad rows' scale bytes are 0."""
+    rng = np.random.default_rng(83)
+    td = torch.float32 if dtype == "f32" else torch.bfloat16
+    x = dev(acts(rng, m, k)).to(td)
+    nw = dev(rng.normal(1, 0.1, k).astype(np.float32))
+    mod = dev(rng.normal(0, 0.3, (3, 6, k)).astype(np.float32))
+    rmap = dev((np.arange(m) % 3).astype(np.int32))
+    fp4 = torch.full((m, k // 2), 0xAB, dtype=torch.uint8, device="cuda")
+    sf = torch.full((int(oracle.nvfp4_sf_bytes(m, k)),), 0xCD, dtype=torch.uint8, device="cuda")
+    vals = torch.empty((m, k), dtype=torch.float32 if gs else td, device="cuda")
+    cuda.norm(x, norm_w=nw, modulation=mod, row_map=rmap, slots=6, shift_slot=3, scale_slot=4, convrot_gs=gs,
+              rot=vals if gs else None, normed=None if gs else vals, fp4=fp4, sf=sf)
+    cuda.check()
+    want4, wantsf = cuda.quantize_act_nvfp4(vals.float().contiguous())
+    assert torch.equal(fp4, want4)
+    assert torch.equal(sf, wantsf)
+    po, so = oracle.quantize_nvfp4(host(vals.float()))      # and the stand-alone quantiser is pinned to the checker
+    assert np.array_equal(host(fp4), po) and np.array_equal(host(sf), so)
+
+
 @pytest.mark.parametrize("m,n,k", [(150, 512, 512), (333, 1024, 256), (128, 256, 1024)])
 def test_gemm_nvfp4_swiglu_in_the_epilogue(cuda, oracle, m, n, k):
     """SwiGLU on the f32 accumulators inside the GEMM (gate rows | up rows of the weight): the reference's chain
