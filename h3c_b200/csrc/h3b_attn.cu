@@ -31,6 +31,10 @@
 //   - exponent offset taken from the previous key tile so that the row maximum leaves the path score ->
 //     probability: -6 %;
 //   - packed f16 exponentials (ex2.approx.f16x2) in the f16 form: -10 %.
+// The CTA-pair form further down (k_attn_pair: cta_group::2 MMAs, K and V tiles split over two SMs, three K/V stages)
+// is kept selectable (H3B_ATTN_EMU = 212 / 213).  It measures the same as this kernel (1273 / 1282 against 1296 / 1299
+// TFLOP/s at 6,144 / 24,576 keys, 1183 against 1191 sustained): halving the B-operand reads and the K/V traffic per SM
+// changes nothing, so shared-memory bandwidth is not what holds the score products back.
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
@@ -144,6 +148,168 @@ __device__ __forceinline__ void add2(float &d0, float &d1, float a0, float a1) {
         "add.rn.f32x2 rd, rd, ra;\n\tmov.b64 {%0, %1}, rd;\n\t}"
         : "+f"(d0), "+f"(d1)
         : "f"(a0), "f"(a1));
+}
+
+// The softmax role of one warp (see the head of the file): warps 2-5 serve the CTA's first query tile, 6-9 its
+// second.  row0 = first query row of the CTA's first tile, tile_stride = rows between its two tiles.  PAIR: the CTA is
+// one of a pair whose MMAs the CTA of cluster rank 0 issues, so "P is ready" is signalled on THAT CTA's barriers.
+template <typename T, uint32_t EMU, bool PAIR>
+__device__ __forceinline__ void softmax_role(const AttnParams &p, uint8_t *smem, uint32_t tmem_base, uint64_t *s_full,
+                                             uint64_t *p_full, uint64_t *o_done, volatile int *abort_word, int warp,
+                                             int lane, int n_kv, int n_tiles, int row0, int tile_stride, int head,
+                                             uint32_t rank) {
+    using namespace attn;
+    // ------------------------------------------------------------ softmax
+    const int t = (warp - 2) >> 2;                     // query tile of this warp group (warps 2-5: A, 6-9: B)
+    const int q = warp & 3;                            // TMEM lane quarter of this warp
+    const uint32_t lane_base = (uint32_t)(q * 32) << 16;
+    const uint32_t s_addr = tmem_base + lane_base + S_COL + 128u * t;
+    const uint32_t o_addr = tmem_base + lane_base + O_COL + 128u * t;
+    float m_run = -INFINITY, l_run = 0.0f;
+    bool ok = t < n_tiles;
+    for (int j = 0; j < n_kv && ok; j++) {
+        const int valid = min(BKV, p.lk - j * BKV);    // keys of this tile that exist
+        ok = mbar_wait(&s_full[t], j & 1, abort_word, p.status, H3B_ST_TIMEOUT_TMEM_FULL);
+        if (!ok) break;
+        tc_fence_after();
+        // all 128 scores of the row in registers (one TMEM round trip)
+        uint32_t sv[BKV];
+#pragma unroll
+        for (int ch = 0; ch < BKV / 32; ch++)
+            tmem_ld_32x32b_x32(s_addr + ch * 32, *reinterpret_cast<uint32_t(*)[32]>(&sv[ch * 32]));
+        tmem_ld_wait();
+        if (valid != BKV) {
+#pragma unroll
+            for (int i = 0; i < BKV; i++)
+                if (i >= valid) sv[i] = 0xff800000u;   // -inf: exp2 gives 0
+        }
+        // eight independent chains of three-input maxima (eight dependent steps instead of sixteen)
+        float mxc[8];
+#pragma unroll
+        for (int c = 0; c < 8; c++) mxc[c] = -INFINITY;
+#pragma unroll
+        for (int i = 0; i < BKV; i += 16)
+#pragma unroll
+            for (int c = 0; c < 8; c++)
+                mxc[c] = max3(mxc[c], __uint_as_float(sv[i + 2 * c]), __uint_as_float(sv[i + 2 * c + 1]));
+        const float mx = fmaxf(max3(mxc[0], mxc[1], mxc[2]), fmaxf(max3(mxc[3], mxc[4], mxc[5]), fmaxf(mxc[6], mxc[7])));
+        const float m_new = fmaxf(m_run, mx * p.scale_log2);
+        const bool grow_me = (m_new - m_run) > 8.0f;   // also true on the first tile (m_run = -inf)
+        if (__any_sync(0xffffffffu, grow_me)) {
+            float alpha = 1.0f;
+            if (grow_me) {
+                alpha = ex2_approx(m_run - m_new);     // 0 on the first tile
+                m_run = m_new;
+                l_run *= alpha;
+            }
+            // The score buffer of tile j became full only after the P V product of tile j-1 had
+            // completed (same issuing thread, in order), so the accumulator is at rest here.
+            if (j > 0) {
+#pragma unroll 1
+                for (int ch = 0; ch < HD / 16; ch++) {
+                    uint32_t o[16];
+                    tmem_ld_32x32b_x16(o_addr + ch * 16, o);
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int i = 0; i < 16; i++) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+                    tmem_st_32x32b_x16(o_addr + ch * 16, o);
+                }
+            }
+        }
+        // probabilities -> bf16 pairs -> TMEM, over the score columns (already in registers)
+        float l0 = 0.0f, l1 = 0.0f, l2 = 0.0f, l3 = 0.0f;
+        const float neg_m = -m_run;
+        // 32 probabilities of chunk `ch` -> 16 packed words
+        auto chunk = [&](int ch, uint32_t (&packed)[16]) {
+#pragma unroll
+            for (int i = 0; i < 32; i += 4) {
+                float x0, x1, x2, x3;
+                fma2(x0, x1, __uint_as_float(sv[ch * 32 + i]), __uint_as_float(sv[ch * 32 + i + 1]), p.scale_log2, neg_m);
+                fma2(x2, x3, __uint_as_float(sv[ch * 32 + i + 2]), __uint_as_float(sv[ch * 32 + i + 3]), p.scale_log2, neg_m);
+                float p0, p1, p2, p3;
+                if ((EMU >> (i >> 2)) & 1u) {
+                    ex2_emu2(p0, p1, x0, x1);
+                    ex2_emu2(p2, p3, x2, x3);
+                } else {
+                    p0 = ex2_approx(x0); p1 = ex2_approx(x1); p2 = ex2_approx(x2); p3 = ex2_approx(x3);
+                }
+                add2(l0, l1, p0, p1);
+                add2(l2, l3, p2, p3);
+                packed[i >> 1] = Elem<T>::pack(p0, p1);
+                packed[(i >> 1) + 1] = Elem<T>::pack(p2, p3);
+            }
+        };
+        // a half (64 keys) of P is in tensor memory: hand it to the MMA warp
+        auto hand_over = [&](int half) {
+            tmem_st_wait();
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) {
+            if (PAIR && rank != 0) mbar_arrive_cluster(mapa_shared(smem_u32(&p_full[2 * t + half]), 0));   // the issuing CTA's barrier
+            else mbar_arrive(&p_full[2 * t + half]);
+        }
+        };
+        // The stores of the first half are waited for only after the exponentials of the third chunk have
+        // been computed: the store latency hides behind arithmetic instead of stalling the warp twice per step.
+        uint32_t pk[16];
+        chunk(0, pk);
+        tmem_st_32x32b_x16(s_addr, pk);
+        chunk(1, pk);
+        tmem_st_32x32b_x16(s_addr + 16, pk);
+        chunk(2, pk);
+        hand_over(0);
+        tmem_st_32x32b_x16(s_addr + 32, pk);
+        chunk(3, pk);
+        tmem_st_32x32b_x16(s_addr + 48, pk);
+        hand_over(1);
+        const float l_add = (l0 + l1) + (l2 + l3);
+        l_run += l_add;
+    }
+    // ---- final: O / l -> bf16 -> global
+    if (t < n_tiles) {
+        if (ok) ok = mbar_wait(o_done, 0, abort_word, p.status, H3B_ST_TIMEOUT_OTHER);
+        tc_fence_after();
+        const float inv_l = 1.0f / l_run;
+        // All MMAs and loads of the CTA are done: its tile memory is free.  Lane = row here; the rows of
+        // the warp are parked in shared memory and written out sixteen lanes per 256-byte head slice,
+        // two rows per store instruction (whole slices matter when the owner of a row is another GPU).
+        constexpr int STG_ROW = 256 + 16;
+        uint8_t *stg = smem + (size_t)(warp - 2) * 32 * STG_ROW;
+#pragma unroll 1
+        for (int ch = 0; ch < HD / 32; ch++) {
+            uint32_t o[32];
+            tmem_ld_32x32b_x32(o_addr + ch * 32, o);
+            tmem_ld_wait();
+#pragma unroll
+            for (int i = 0; i < 32; i += 8) {
+                uint4 raw;
+                uint32_t *h = reinterpret_cast<uint32_t *>(&raw);
+#pragma unroll
+                for (int u = 0; u < 4; u++)
+                    h[u] = Elem<T>::pack(__uint_as_float(o[i + 2 * u]) * inv_l, __uint_as_float(o[i + 2 * u + 1]) * inv_l);
+                *reinterpret_cast<uint4 *>(stg + lane * STG_ROW + (ch * 32 + i) * 2) = raw;
+            }
+        }
+        __syncwarp();
+        const int row_first = row0 + t * tile_stride + q * 32;   // row of lane 0
+        const int sub = lane >> 4, chunk = lane & 15;
+#pragma unroll
+        for (int k2 = 0; k2 < 16; k2++) {
+            const int rr = 2 * k2 + sub, row = row_first + rr;
+            if (ok && row < p.lq) {
+                T *dst;
+                if (p.sc_rows) {
+                    const int owner = row / p.sc_rows;
+                    dst = reinterpret_cast<T *>(p.sc_out[owner < 8 ? owner : 0]) +
+                          ((size_t)(row - owner * p.sc_rows) * p.sc_heads + p.sc_head0 + head) * HD;
+                } else {
+                    dst = reinterpret_cast<T *>(p.out) + (size_t)row * p.o_stride + (size_t)head * p.o_head_stride;
+                }
+                *reinterpret_cast<uint4 *>(dst + chunk * 8) = *reinterpret_cast<const uint4 *>(stg + rr * STG_ROW + chunk * 16);
+            }
+        }
+    }
+
 }
 
 // EMU: bit q set = the q-th group of four probabilities of every 32 is computed by ex2_emu2 instead of ex2.approx
@@ -305,154 +471,8 @@ __global__ void __launch_bounds__(attn::THREADS, 1) k_attn(const __grid_constant
         }
         __syncwarp();
     } else {
-        // ------------------------------------------------------------ softmax
-        const int t = (warp - 2) >> 2;                     // query tile of this warp group (warps 2-5: A, 6-9: B)
-        const int q = warp & 3;                            // TMEM lane quarter of this warp
-        const int r = q * 32 + lane;                       // query row inside the tile
-        const uint32_t lane_base = (uint32_t)(q * 32) << 16;
-        const uint32_t s_addr = tmem_base + lane_base + S_COL + 128u * t;
-        const uint32_t o_addr = tmem_base + lane_base + O_COL + 128u * t;
-        float m_run = -INFINITY, l_run = 0.0f;
-        bool ok = t < n_tiles;
-        for (int j = 0; j < n_kv && ok; j++) {
-            const int valid = min(BKV, p.lk - j * BKV);    // keys of this tile that exist
-            ok = mbar_wait(&s_full[t], j & 1, abort_word, p.status, H3B_ST_TIMEOUT_TMEM_FULL);
-            if (!ok) break;
-            tc_fence_after();
-            // all 128 scores of the row in registers (one TMEM round trip)
-            uint32_t sv[BKV];
-#pragma unroll
-            for (int ch = 0; ch < BKV / 32; ch++)
-                tmem_ld_32x32b_x32(s_addr + ch * 32, *reinterpret_cast<uint32_t(*)[32]>(&sv[ch * 32]));
-            tmem_ld_wait();
-            if (valid != BKV) {
-#pragma unroll
-                for (int i = 0; i < BKV; i++)
-                    if (i >= valid) sv[i] = 0xff800000u;   // -inf: exp2 gives 0
-            }
-            // eight independent chains of three-input maxima (eight dependent steps instead of sixteen)
-            float mxc[8];
-#pragma unroll
-            for (int c = 0; c < 8; c++) mxc[c] = -INFINITY;
-#pragma unroll
-            for (int i = 0; i < BKV; i += 16)
-#pragma unroll
-                for (int c = 0; c < 8; c++)
-                    mxc[c] = max3(mxc[c], __uint_as_float(sv[i + 2 * c]), __uint_as_float(sv[i + 2 * c + 1]));
-            const float mx = fmaxf(max3(mxc[0], mxc[1], mxc[2]), fmaxf(max3(mxc[3], mxc[4], mxc[5]), fmaxf(mxc[6], mxc[7])));
-            const float m_new = fmaxf(m_run, mx * p.scale_log2);
-            const bool grow_me = (m_new - m_run) > 8.0f;   // also true on the first tile (m_run = -inf)
-            if (__any_sync(0xffffffffu, grow_me)) {
-                float alpha = 1.0f;
-                if (grow_me) {
-                    alpha = ex2_approx(m_run - m_new);     // 0 on the first tile
-                    m_run = m_new;
-                    l_run *= alpha;
-                }
-                // The score buffer of tile j became full only after the P V product of tile j-1 had
-                // completed (same issuing thread, in order), so the accumulator is at rest here.
-                if (j > 0) {
-#pragma unroll 1
-                    for (int ch = 0; ch < HD / 16; ch++) {
-                        uint32_t o[16];
-                        tmem_ld_32x32b_x16(o_addr + ch * 16, o);
-                        tmem_ld_wait();
-#pragma unroll
-                        for (int i = 0; i < 16; i++) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
-                        tmem_st_32x32b_x16(o_addr + ch * 16, o);
-                    }
-                }
-            }
-            // probabilities -> bf16 pairs -> TMEM, over the score columns (already in registers)
-            float l0 = 0.0f, l1 = 0.0f, l2 = 0.0f, l3 = 0.0f;
-            const float neg_m = -m_run;
-            // 32 probabilities of chunk `ch` -> 16 packed words
-            auto chunk = [&](int ch, uint32_t (&packed)[16]) {
-#pragma unroll
-                for (int i = 0; i < 32; i += 4) {
-                    float x0, x1, x2, x3;
-                    fma2(x0, x1, __uint_as_float(sv[ch * 32 + i]), __uint_as_float(sv[ch * 32 + i + 1]), p.scale_log2, neg_m);
-                    fma2(x2, x3, __uint_as_float(sv[ch * 32 + i + 2]), __uint_as_float(sv[ch * 32 + i + 3]), p.scale_log2, neg_m);
-                    float p0, p1, p2, p3;
-                    if ((EMU >> (i >> 2)) & 1u) {
-                        ex2_emu2(p0, p1, x0, x1);
-                        ex2_emu2(p2, p3, x2, x3);
-                    } else {
-                        p0 = ex2_approx(x0); p1 = ex2_approx(x1); p2 = ex2_approx(x2); p3 = ex2_approx(x3);
-                    }
-                    add2(l0, l1, p0, p1);
-                    add2(l2, l3, p2, p3);
-                    packed[i >> 1] = Elem<T>::pack(p0, p1);
-                    packed[(i >> 1) + 1] = Elem<T>::pack(p2, p3);
-                }
-            };
-            // a half (64 keys) of P is in tensor memory: hand it to the MMA warp
-            auto hand_over = [&](int half) {
-                tmem_st_wait();
-                tc_fence_before();
-                __syncwarp();
-                if (lane == 0) mbar_arrive(&p_full[2 * t + half]);
-            };
-            // The stores of the first half are waited for only after the exponentials of the third chunk have
-            // been computed: the store latency hides behind arithmetic instead of stalling the warp twice per step.
-            uint32_t pk[16];
-            chunk(0, pk);
-            tmem_st_32x32b_x16(s_addr, pk);
-            chunk(1, pk);
-            tmem_st_32x32b_x16(s_addr + 16, pk);
-            chunk(2, pk);
-            hand_over(0);
-            tmem_st_32x32b_x16(s_addr + 32, pk);
-            chunk(3, pk);
-            tmem_st_32x32b_x16(s_addr + 48, pk);
-            hand_over(1);
-            const float l_add = (l0 + l1) + (l2 + l3);
-            l_run += l_add;
-        }
-        // ---- final: O / l -> bf16 -> global
-        if (t < n_tiles) {
-            if (ok) ok = mbar_wait(o_done, 0, abort_word, p.status, H3B_ST_TIMEOUT_OTHER);
-            tc_fence_after();
-            const float inv_l = 1.0f / l_run;
-            // All MMAs and loads of the CTA are done: its tile memory is free.  Lane = row here; the rows of
-            // the warp are parked in shared memory and written out sixteen lanes per 256-byte head slice,
-            // two rows per store instruction (whole slices matter when the owner of a row is another GPU).
-            constexpr int STG_ROW = 256 + 16;
-            uint8_t *stg = smem + (size_t)(warp - 2) * 32 * STG_ROW;
-#pragma unroll 1
-            for (int ch = 0; ch < HD / 32; ch++) {
-                uint32_t o[32];
-                tmem_ld_32x32b_x32(o_addr + ch * 32, o);
-                tmem_ld_wait();
-#pragma unroll
-                for (int i = 0; i < 32; i += 8) {
-                    uint4 raw;
-                    uint32_t *h = reinterpret_cast<uint32_t *>(&raw);
-#pragma unroll
-                    for (int u = 0; u < 4; u++)
-                        h[u] = Elem<T>::pack(__uint_as_float(o[i + 2 * u]) * inv_l, __uint_as_float(o[i + 2 * u + 1]) * inv_l);
-                    *reinterpret_cast<uint4 *>(stg + lane * STG_ROW + (ch * 32 + i) * 2) = raw;
-                }
-            }
-            __syncwarp();
-            const int row_first = q0 + t * BQ + q * 32;   // row of lane 0
-            const int sub = lane >> 4, chunk = lane & 15;
-#pragma unroll
-            for (int k2 = 0; k2 < 16; k2++) {
-                const int rr = 2 * k2 + sub, row = row_first + rr;
-                if (ok && row < p.lq) {
-                    T *dst;
-                    if (p.sc_rows) {
-                        const int owner = row / p.sc_rows;
-                        dst = reinterpret_cast<T *>(p.sc_out[owner < 8 ? owner : 0]) +
-                              ((size_t)(row - owner * p.sc_rows) * p.sc_heads + p.sc_head0 + head) * HD;
-                    } else {
-                        dst = reinterpret_cast<T *>(p.out) + (size_t)row * p.o_stride + (size_t)head * p.o_head_stride;
-                    }
-                    *reinterpret_cast<uint4 *>(dst + chunk * 8) = *reinterpret_cast<const uint4 *>(stg + rr * STG_ROW + chunk * 16);
-                }
-            }
-        }
+        softmax_role<T, EMU, false>(p, smem, tmem_base, s_full, p_full, o_done, abort_word, warp, lane, n_kv, n_tiles, q0, BQ,
+                                    head, 0);
     }
 
     tc_fence_before();
@@ -463,11 +483,189 @@ __global__ void __launch_bounds__(attn::THREADS, 1) k_attn(const __grid_constant
     }
 }
 
+// ---------------------------------------------------------------------------------------------------------------
+// CTA-pair form.  A cluster of two CTAs serves 512 queries of one head: its two query tiles are 256 rows each, CTA r
+// of the pair holds rows [128 r, 128 r + 128) of both, and every MMA is a cta_group::2 instruction of M = 256 issued
+// by the CTA of rank 0.  The B operands are split along N: each CTA loads and holds HALF of every K tile (64 of its
+// 128 keys) and HALF of every V tile (64 of its 128 columns), so per SM the shared-memory reads of B, the TMA writes
+// and the L2 traffic of K and V are halved; the 64 KB that frees hold a third K/V stage.  Softmax and epilogue are
+// the single-CTA kernel's, per CTA; "P is ready" is signalled on the issuing CTA's barriers, commits are multicast
+// to both CTAs.  No TMA load is multicast: each CTA loads its own halves into its own shared memory.
+namespace attnp {
+constexpr int STAGES = 3;
+constexpr int KH = 64 * 128 * 2, KSLAB = 64 * 64 * 2;   // K half: 64 keys x 128 d as two 64-row slabs (8 KiB each)
+constexpr int VH = 128 * 64 * 2;                         // V half: 128 keys x 64 d, one slab (16 KiB)
+// shared memory: Q_A Q_B | K halves | V halves | barriers
+constexpr size_t SMEM_BYTES = 1024 + 2 * (size_t)attn::TILE + (size_t)STAGES * (KH + VH) + 256;
+}  // namespace attnp
+
+template <typename T, uint32_t EMU>
+__global__ void __launch_bounds__(attn::THREADS, 1) k_attn_pair(const __grid_constant__ AttnParams p) {
+    using namespace attn;
+    using namespace attnp;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    uint8_t *sQ = smem, *sK = smem + 2 * TILE, *sV = sK + STAGES * KH;
+    uint64_t *bars = reinterpret_cast<uint64_t *>(sV + STAGES * VH);
+    uint64_t *q_full = bars, *k_full = bars + 1, *v_full = k_full + STAGES, *k_empty = v_full + STAGES,
+             *v_empty = k_empty + STAGES, *s_full = v_empty + STAGES, *p_full = s_full + 2 /* [tile][half] */,
+             *o_done = p_full + 4;
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(o_done + 1);
+    volatile int *abort_word = reinterpret_cast<volatile int *>(tmem_slot + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t rank = cluster_ctarank();
+    const int q0_pair = (int)(blockIdx.x >> 1) * (4 * BQ), head = blockIdx.y;
+    const int row0 = q0_pair + (int)rank * BQ;          // this CTA's rows of the pair's first tile
+    const int n_kv = (p.lk + BKV - 1) / BKV;
+    const int n_tiles = (q0_pair + 2 * BQ < p.lq) ? 2 : 1;   // the same for both CTAs of the pair
+
+    if (threadIdx.x == 0) {
+        mbar_init(q_full, 1);
+        for (int i = 0; i < STAGES; i++) {
+            mbar_init(&k_full[i], 1);
+            mbar_init(&v_full[i], 1);
+            mbar_init(&k_empty[i], 1);
+            mbar_init(&v_empty[i], 1);
+        }
+        for (int i = 0; i < 2; i++) {
+            mbar_init(&s_full[i], 1);
+            mbar_init(&p_full[2 * i], 8);       // four softmax warps of each CTA
+            mbar_init(&p_full[2 * i + 1], 8);
+        }
+        mbar_init(o_done, 1);
+        *abort_word = 0;
+        mbar_fence_init();
+        tma_prefetch_desc(&p.tmap_q);
+        tma_prefetch_desc(&p.tmap_k);
+        tma_prefetch_desc(&p.tmap_v);
+    }
+    if (warp == 1) {
+        tmem_alloc_pair(tmem_slot, TMEM_COLS);
+        tmem_relinquish_pair();
+    }
+    tc_fence_before();
+    __syncthreads();
+    cluster_sync_all();   // the peer's barriers exist before anything signals them
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            // completion of both CTAs' loads is counted on the barriers of rank 0, which alone waits for them
+            const uint32_t qf = mapa_shared(smem_u32(q_full), 0);
+            if (rank == 0) mbar_expect_tx(q_full, 2 * n_tiles * TILE);
+            for (int t = 0; t < n_tiles; t++) {
+                tma_load_3d_pair(sQ + t * TILE, &p.tmap_q, qf, 0, head, row0 + t * 2 * BQ);
+                tma_load_3d_pair(sQ + t * TILE + SLAB, &p.tmap_q, qf, 64, head, row0 + t * 2 * BQ);
+            }
+            for (int j = 0; j < n_kv; j++) {
+                const int st = j % STAGES;
+                const uint32_t ph = ((j / STAGES) & 1) ^ 1;
+                if (!mbar_wait(&k_empty[st], ph, abort_word, p.status, H3B_ST_TIMEOUT_EMPTY)) break;
+                const uint32_t kf = mapa_shared(smem_u32(&k_full[st]), 0);
+                if (rank == 0) mbar_expect_tx(&k_full[st], 2 * KH);
+                tma_load_3d_pair(sK + st * KH, &p.tmap_k, kf, 0, head, j * BKV + (int)rank * 64);
+                tma_load_3d_pair(sK + st * KH + KSLAB, &p.tmap_k, kf, 64, head, j * BKV + (int)rank * 64);
+                if (!mbar_wait(&v_empty[st], ph, abort_word, p.status, H3B_ST_TIMEOUT_EMPTY)) break;
+                const uint32_t vf = mapa_shared(smem_u32(&v_full[st]), 0);
+                if (rank == 0) mbar_expect_tx(&v_full[st], 2 * VH);
+                tma_load_3d_pair(sV + st * VH, &p.tmap_v, vf, (int)rank * 64, head, j * BKV);
+            }
+        }
+        __syncwarp();
+    } else if (warp == 1) {
+        if (rank == 0) {
+            // ---- MMA issuer of the pair: the whole warp walks the loop, one lane elected once issues
+            const bool lead = elect_one();
+            constexpr uint32_t idesc_s = umma_idesc(1, Elem<T>::FMT, Elem<T>::FMT, 2 * BQ, BKV, 0, 0);
+            constexpr uint32_t idesc_o = umma_idesc(1, Elem<T>::FMT, Elem<T>::FMT, 2 * BQ, HD, 0, 1);
+            const uint32_t q_base = smem_u32(sQ), k_base = smem_u32(sK), v_base = smem_u32(sV);
+            auto issue_s = [&](int t, int stage) {
+                const uint32_t q_addr = q_base + t * TILE, k_addr = k_base + stage * KH;
+                const uint32_t d_tmem = tmem_base + S_COL + 128u * t;
+#pragma unroll
+                for (int k = 0; k < HD / 16; k++) {
+                    const uint32_t qo = (uint32_t)(k >> 2) * SLAB + (uint32_t)(k & 3) * 32;
+                    const uint32_t ko = (uint32_t)(k >> 2) * KSLAB + (uint32_t)(k & 3) * 32;
+                    if (lead)
+                        umma_f16_ss_pair(d_tmem, umma_desc_k_sw128(q_addr + qo), umma_desc_k_sw128(k_addr + ko), idesc_s,
+                                         (uint32_t)(k != 0));
+                }
+                if (lead) tc_commit_pair(&s_full[t], 3);
+            };
+            auto issue_pv = [&](int t, int stage, int half, bool first) {
+                const uint32_t v_addr = v_base + stage * VH;
+#pragma unroll
+                for (int k = half * (BKV / 32); k < (half + 1) * (BKV / 32); k++)
+                    if (lead)
+                        umma_f16_ts_pair(tmem_base + O_COL + 128u * t, tmem_base + S_COL + 128u * t + (uint32_t)k * 8,
+                                         umma_desc_mn_sw128(v_addr + (uint32_t)k * 2048, SLAB, 1024), idesc_o,
+                                         (uint32_t)(!first || k != 0));
+            };
+            bool ok = mbar_wait(q_full, 0, abort_word, p.status, H3B_ST_TIMEOUT_FULL) &&
+                      mbar_wait(&k_full[0], 0, abort_word, p.status, H3B_ST_TIMEOUT_FULL);
+            if (ok) {
+                tc_fence_after();
+                for (int t = 0; t < n_tiles; t++) issue_s(t, 0);
+                if (lead) tc_commit_pair(&k_empty[0], 3);
+                ok = mbar_wait(&v_full[0], 0, abort_word, p.status, H3B_ST_TIMEOUT_FULL) &&
+                     (n_kv < 2 || mbar_wait(&k_full[1 % STAGES], 0, abort_word, p.status, H3B_ST_TIMEOUT_FULL));
+            }
+            // one iteration with the K/V stage index as a compile-time constant: V(j) in stage st, K(j+1) in nx
+            auto step = [&](int j, auto stage_c) {
+                constexpr int st = decltype(stage_c)::value, nx = (st + 1) % STAGES, n2 = (st + 2) % STAGES;
+                const bool more = j + 1 < n_kv;
+                for (int t = 0; t < n_tiles && ok; t++) {
+                    ok = mbar_wait(&p_full[2 * t], j & 1, abort_word, p.status, H3B_ST_TIMEOUT_OTHER);
+                    if (!ok) break;
+                    tc_fence_after();
+                    issue_pv(t, st, 0, j == 0);
+                    ok = mbar_wait(&p_full[2 * t + 1], j & 1, abort_word, p.status, H3B_ST_TIMEOUT_OTHER);
+                    if (!ok) break;
+                    tc_fence_after();
+                    issue_pv(t, st, 1, false);
+                    if (t == n_tiles - 1 && lead) tc_commit_pair(&v_empty[st], 3);
+                    if (more) {
+                        issue_s(t, nx);
+                        if (t == n_tiles - 1 && lead) tc_commit_pair(&k_empty[nx], 3);
+                    }
+                }
+                if (ok && more) {
+                    ok = mbar_wait(&v_full[nx], ((j + 1) / STAGES) & 1, abort_word, p.status, H3B_ST_TIMEOUT_FULL);
+                    if (ok && j + 2 < n_kv)
+                        ok = mbar_wait(&k_full[n2], ((j + 2) / STAGES) & 1, abort_word, p.status, H3B_ST_TIMEOUT_FULL);
+                    tc_fence_after();
+                }
+            };
+            for (int j = 0; ok && j < n_kv; j += 3) {
+                step(j, std::integral_constant<int, 0>{});
+                if (ok && j + 1 < n_kv) step(j + 1, std::integral_constant<int, 1>{});
+                if (ok && j + 2 < n_kv) step(j + 2, std::integral_constant<int, 2>{});
+            }
+            if (lead) tc_commit_pair(o_done, 3);
+        }
+        __syncwarp();
+    } else {
+        softmax_role<T, EMU, true>(p, smem, tmem_base, s_full, p_full, o_done, abort_word, warp, lane, n_kv, n_tiles, row0,
+                                   2 * BQ, head, rank);
+    }
+
+    // a pair leaves together: neither CTA may exit while the other can still signal its barriers or read its tiles
+    tc_fence_before();
+    __syncthreads();
+    cluster_sync_all();
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc_pair(tmem_base, TMEM_COLS);
+    }
+}
+
 static int make_map(CUtensorMap *map, const void *base, size_t stride_elems, size_t head_stride_elems, size_t rows,
-                    size_t heads, int f16, char *error, size_t error_size, const char *what) {
+                    size_t heads, int f16, char *error, size_t error_size, const char *what, uint32_t box_rows = 128) {
     int rc = h3b_encode_tmap_3d(map, f16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, base,
                                 attn::HD, heads, rows,
-                                head_stride_elems * 2, stride_elems * 2, 64, 1, 128, CU_TENSOR_MAP_SWIZZLE_128B);
+                                head_stride_elems * 2, stride_elems * 2, 64, 1, box_rows, CU_TENSOR_MAP_SWIZZLE_128B);
     if (rc != 0) return fail(error, error_size, "sdpa: cuTensorMapEncodeTiled(%s) failed (%d)", what, rc);
     return 1;
 }
@@ -510,10 +708,13 @@ static int launch_sdpa_impl(h3_cuda *cuda, const void *q, size_t qs, const void 
     if ((hs.q | hs.k | hs.v | hs.o) % 8) return fail(error, error_size, "sdpa: head strides must be multiples of 8 elements");
     if (lq > 0x7fffff00u || lk > 0x7fffff00u || heads > 65535) return fail(error, error_size, "sdpa: shape too large");
     if (!(scale > 0.0f)) return fail(error, error_size, "sdpa: scale must be positive");
+    // H3B_ATTN_EMU = 212 / 213: the CTA-pair form of the kernel (two / three eighths of the exponentials on the FMA pipe)
+    static const int emu = atoi(h3_plugin_value("H3B_ATTN_EMU"));
+    const bool pair = emu == 212 || emu == 213;
     AttnParams p;
     memset(&p, 0, sizeof(p));
     if (!make_map(&p.tmap_q, q, qs, hs.q, lq, heads, f16, error, error_size, "Q") ||
-        !make_map(&p.tmap_k, k, ks, hs.k, lk, heads, f16, error, error_size, "K") ||
+        !make_map(&p.tmap_k, k, ks, hs.k, lk, heads, f16, error, error_size, "K", pair ? 64 : 128) ||
         !make_map(&p.tmap_v, v, vs, hs.v, lk, heads, f16, error, error_size, "V"))
         return 0;
     p.out = out; p.o_stride = os; p.o_head_stride = hs.o; p.lq = (int)lq; p.lk = (int)lk; p.heads = (int)heads;
@@ -532,8 +733,28 @@ static int launch_sdpa_impl(h3_cuda *cuda, const void *q, size_t qs, const void 
     // Variant of the kernel (H3B_ATTN_EMU): 12 (default) = one lane elected once issues every tcgen05 instruction and
     // two eighths of the exponentials run on the FMA pipe; 13 = three eighths; 10 = none; 0 = none, and a lane is
     // elected in front of every instruction.
-    static const int emu = atoi(h3_plugin_value("H3B_ATTN_EMU"));
     constexpr uint32_t LEAD = 0x80000000u;
+    if (pair) {
+        void (*kp)(const AttnParams) = f16 ? k_attn_pair<__half, 0x11> : (emu == 213 ? k_attn_pair<__nv_bfloat16, 0x49>
+                                                                                      : k_attn_pair<__nv_bfloat16, 0x11>);
+        H3B_CUDA_OK(cudaFuncSetAttribute(kp, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)attnp::SMEM_BYTES),
+                    "sdpa smem attribute");
+        cudaLaunchConfig_t cfg;
+        memset(&cfg, 0, sizeof(cfg));
+        cudaLaunchAttribute attr;
+        attr.id = cudaLaunchAttributeClusterDimension;
+        attr.val.clusterDim.x = 2; attr.val.clusterDim.y = 1; attr.val.clusterDim.z = 1;
+        cfg.gridDim = dim3((unsigned)(2 * ceil_div(lq, 4 * attn::BQ)), (unsigned)heads);
+        cfg.blockDim = dim3(attn::THREADS);
+        cfg.dynamicSmemBytes = attnp::SMEM_BYTES;
+        cfg.stream = cuda->op_stream;
+        cfg.attrs = &attr;
+        cfg.numAttrs = 1;
+        ProfScope prof(cuda, PROF_ATTN);
+        H3B_CUDA_OK(cudaLaunchKernelEx(&cfg, kp, p), "k_attn_pair launch");
+        cuda->launches++;
+        return 1;
+    }
     void (*kernel)(const AttnParams) = nullptr;
     if (f16) {
         kernel = k_attn<__half, LEAD | 0x11>;
