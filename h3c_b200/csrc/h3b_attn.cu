@@ -403,26 +403,28 @@ __global__ void __launch_bounds__(attn::THREADS, 1) k_attn(const __grid_constant
             constexpr uint32_t idesc_s = umma_idesc(1, Elem<T>::FMT, Elem<T>::FMT, BQ, BKV, 0, 0);
             constexpr uint32_t idesc_o = umma_idesc(1, Elem<T>::FMT, Elem<T>::FMT, BQ, HD, 0, 1);
             const uint32_t q_base = smem_u32(sQ), k_base = smem_u32(sK), v_base = smem_u32(sV);
+            // shared-memory descriptors as 32-bit halves (see umma_f16_ss_lh): one addition per operand and MMA
+            constexpr uint32_t DESC_HI = (1024u >> 4) | (1u << 14) | (2u << 29);   // SBO 1024, version 1, 128-byte swizzle
+            const uint32_t q_lo0 = ((q_base & 0x3ffffu) >> 4) | (1u << 16), q_lo1 = q_lo0 + (TILE >> 4);
+            const uint32_t k_lo0 = ((k_base & 0x3ffffu) >> 4) | (1u << 16);
+            const uint32_t v_lo0 = ((v_base & 0x3ffffu) >> 4) | ((uint32_t)((SLAB >> 4) & 0x3fff) << 16);   // LBO = slab
             auto issue_s = [&](int t, int stage) {   // scores of tile t against the K tile in `stage`
-                const uint32_t q_addr = q_base + t * TILE, k_addr = k_base + stage * TILE;
+                const uint32_t qa = t ? q_lo1 : q_lo0, kb = k_lo0 + (uint32_t)stage * (TILE >> 4);
                 const uint32_t d_tmem = tmem_base + S_COL + 128u * t;
 #pragma unroll
                 for (int k = 0; k < HD / 16; k++) {
-                    const uint32_t off = (uint32_t)(k >> 2) * SLAB + (uint32_t)(k & 3) * 32;
-                    if (leader())
-                        umma_f16_ss(d_tmem, umma_desc_k_sw128(q_addr + off), umma_desc_k_sw128(k_addr + off), idesc_s,
-                                    (uint32_t)(k != 0));
+                    const uint32_t c = (uint32_t)(k >> 2) * (SLAB >> 4) + (uint32_t)(k & 3) * 2;   // (slab, 32 bytes) >> 4
+                    if (leader()) umma_f16_ss_lh(d_tmem, qa + c, kb + c, DESC_HI, idesc_s, (uint32_t)(k != 0));
                 }
                 if (leader()) tc_commit(&s_full[t]);
             };
             auto issue_pv = [&](int t, int stage, int half, bool first) {
-                const uint32_t v_addr = v_base + stage * TILE;
+                const uint32_t vb = v_lo0 + (uint32_t)stage * (TILE >> 4);
 #pragma unroll
                 for (int k = half * (BKV / 32); k < (half + 1) * (BKV / 32); k++)
                     if (leader())
-                        umma_f16_ts(tmem_base + O_COL + 128u * t, tmem_base + S_COL + 128u * t + (uint32_t)k * 8,
-                                    umma_desc_mn_sw128(v_addr + (uint32_t)k * 2048, SLAB, 1024), idesc_o,
-                                    (uint32_t)(!first || k != 0));
+                        umma_f16_ts_lh(tmem_base + O_COL + 128u * t, tmem_base + S_COL + 128u * t + (uint32_t)k * 8,
+                                       vb + (uint32_t)k * (2048 >> 4), DESC_HI, idesc_o, (uint32_t)(!first || k != 0));
             };
             bool ok = mbar_wait(q_full, 0, abort_word, p.status, H3B_ST_TIMEOUT_FULL) &&
                       mbar_wait(&k_full[0], 0, abort_word, p.status, H3B_ST_TIMEOUT_FULL);
