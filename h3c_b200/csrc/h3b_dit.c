@@ -206,6 +206,7 @@ int h3b_dit_set_linear(h3b_dit *d, unsigned block, int which, const h3_cuda_w4a8
             return fail(error, error_size, "h3b_dit_set_linear: linear %d is [%zu,%zu], expected [%zu,%zu]", which, n, k,
                         want_n[which], want_k[which]);
     }
+    if (d->blocks[block].lin[which] != w) drop_graph(d);   /* a captured chain holds the old weight's pointers */
     d->blocks[block].lin[which] = w;
     return 1;
 }
@@ -233,6 +234,7 @@ int h3b_dit_set_linear_nvfp4(h3b_dit *d, unsigned block, int which, const h3_cud
             if (d->cap_seq) free_seq_ws(d);   /* the next reserve adds the f32 activation buffer */
         }
     }
+    if (d->blocks[block].fp4[which] != w) drop_graph(d);
     d->blocks[block].fp4[which] = w;
     return 1;
 }
