@@ -102,6 +102,7 @@ struct NormParams {
     unsigned width, slots, gate_slot, shift_slot, scale_slot;
     float eps;
     int identity, gs;
+    int sylvester;       // ConvRot by the Walsh-Hadamard matrix (radix-2 butterflies) instead of the regular one
     void *gated, *normed;
     float *rot;
     int8_t *q;
@@ -173,7 +174,28 @@ __global__ void __launch_bounds__(256) k_norm(NormParams p) {
 
     // ---- ConvRot: y = x * H per group, H = kron-power of the 4x4 regular Hadamard / sqrt(gs).
     // H is symmetric, so this is a radix-4 butterfly network with strides 1, 4, 16, 64.
-    if (p.gs > 0) {
+    if (p.gs > 0 && p.sylvester) {
+        // H3_CONVROT_SYLVESTER=1: the reference's in-place radix-2 transform, butterfly for butterfly, then one
+        // multiplication by 1/sqrt(gs) (h3_w4a8_dequant.c:241-258): bit-identical to it
+        for (int h = 1; h < p.gs; h <<= 1) {
+            __syncthreads();
+            for (unsigned b = threadIdx.x; b < W / 2; b += blockDim.x) {
+                const unsigned lo = b % h, base = (b / h) * h * 2 + lo;
+                const float u = row[base], v = row[base + h];
+                row[base] = __fadd_rn(u, v);
+                row[base + h] = __fsub_rn(u, v);
+            }
+        }
+        __syncthreads();
+        const float norm = 1.0f / sqrtf((float)p.gs);
+        amax = 0.0f;
+        for (unsigned c = threadIdx.x; c < W; c += blockDim.x) {
+            const float v = __fmul_rn(row[c], norm);
+            row[c] = v;
+            amax = fmaxf(amax, fabsf(v));
+            if (p.rot) p.rot[r * W + c] = v;
+        }
+    } else     if (p.gs > 0) {
         for (int stride = 1; stride < p.gs; stride <<= 2) {
             __syncthreads();
             for (unsigned b = threadIdx.x; b < W / 4; b += blockDim.x) {
@@ -631,8 +653,13 @@ int launch_norm(h3_cuda *cuda, const h3b_norm_args *a, char *error, size_t error
     if (!cuda || !a || !a->d_x || !a->rows || !a->width) return fail(error, error_size, "norm: invalid arguments");
     if (a->d_q && !a->d_scales) return fail(error, error_size, "norm: d_q without d_scales");
     if (a->d_modulation && a->slots == 0) return fail(error, error_size, "norm: slots must be > 0");
-    if (a->convrot_gs != 0 && a->convrot_gs != 4 && a->convrot_gs != 16 && a->convrot_gs != 64 &&
-        a->convrot_gs != 256)
+    // the reference's switch, read per call: Walsh-Hadamard groups of any power of two up to 256
+    const int sylvester = a->convrot_gs > 0 && strcmp(h3_plugin_value("H3_CONVROT_SYLVESTER"), "1") == 0;
+    if (sylvester) {
+        if (a->convrot_gs < 2 || a->convrot_gs > 256 || (a->convrot_gs & (a->convrot_gs - 1)))
+            return fail(error, error_size, "invalid fwht groupsize=%d K=%zu", a->convrot_gs, a->width);
+    } else if (a->convrot_gs != 0 && a->convrot_gs != 4 && a->convrot_gs != 16 && a->convrot_gs != 64 &&
+               a->convrot_gs != 256)
         return fail(error, error_size, "norm: ConvRot group size %d unsupported (0, 4, 16, 64, 256)", a->convrot_gs);
     if (a->convrot_gs && a->width % (size_t)a->convrot_gs)
         return fail(error, error_size, "K=%zu not divisible by convrot_groupsize=%d", a->width, a->convrot_gs);
@@ -642,6 +669,7 @@ int launch_norm(h3_cuda *cuda, const h3b_norm_args *a, char *error, size_t error
     p.row_map = a->d_row_map; p.width = (unsigned)a->width; p.slots = (unsigned)a->slots;
     p.gate_slot = (unsigned)a->gate_slot; p.shift_slot = (unsigned)a->shift_slot;
     p.scale_slot = (unsigned)a->scale_slot; p.eps = a->epsilon; p.identity = a->identity;
+    p.sylvester = sylvester;
     p.gs = a->convrot_gs; p.gated = a->d_gated; p.normed = a->d_normed; p.rot = a->d_rot; p.q = a->d_q;
     p.scales = a->d_scales; p.fp4 = a->d_fp4; p.sf = a->d_sf;
     if (a->d_fp4) {

@@ -27,6 +27,7 @@ extern "C" {
     X("H3B_ULYSSES_BARRIER", "STABLE", "SP", "flag") /* flag | nccl: barrier of the exchange-free form */       \
     X("H3B_ULYSSES_DIRECT", "STABLE", "SP", "1")     /* 0: NCCL exchange instead of direct peer stores (bench) */ \
     /* switches of the reference that this library honours with the reference's meaning */                     \
+    X("H3_CONVROT_SYLVESTER", "EXPERIMENTAL", "DIT", "0") /* 1: Walsh-Hadamard (radix-2) ConvRot, h3_w4a8_dequant.c:371 */ \
     X("H3_DIT_QKV_GROUPED", "EXPERIMENTAL", "DIT", "0")                                                        \
     X("H3_DIT_ROPE_HALF_OFFSET", "EXPERIMENTAL", "DIT", "0")                                                   \
     X("H3_DIT_ROPE_SPLIT_HALF", "EXPERIMENTAL", "DIT", "1")                                                    \

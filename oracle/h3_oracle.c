@@ -330,6 +330,31 @@ int ho_convrot_act_f32(const float *x, size_t m, size_t k, int gs, float *y) {
     return 1;
 }
 
+/* Walsh-Hadamard rotation of every `gs` group of a row by in-place radix-2 butterflies, then one multiplication by
+ * 1/sqrt(gs): what H3_CONVROT_SYLVESTER=1 selects instead of the regular-Hadamard product
+ * (h3_w4a8_dequant.c:241-284, switch at :371-375). */
+int ho_fwht_act_f32(const float *x, size_t m, size_t k, int gs, float *y) {
+    size_t row, g;
+    if (!x || !y || m == 0 || k == 0) return 0;
+    if (gs < 2 || (gs & (gs - 1)) || k % (size_t)gs) return 0;
+    if (x != y) memcpy(y, x, m * k * sizeof(float));
+    for (row = 0; row < m; row++)
+        for (g = 0; g < k / (size_t)gs; g++) {
+            float *a = y + row * k + g * (size_t)gs;
+            const float scale = 1.0f / sqrtf((float)gs);
+            int h, i, j;
+            for (h = 1; h < gs; h *= 2)
+                for (i = 0; i < gs; i += 2 * h)
+                    for (j = i; j < i + h; j++) {
+                        const float u = a[j], v = a[j + h];
+                        a[j] = u + v;
+                        a[j + h] = u - v;
+                    }
+            for (h = 0; h < gs; h++) a[h] *= scale;
+        }
+    return 1;
+}
+
 /* ------------------------------------------------ activation quant and GEMMs */
 
 /* h3_w4a8_dequant.c:671-688 */

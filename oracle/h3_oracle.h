@@ -58,6 +58,7 @@ int ho_quantize_weight_int8(const float *w, size_t n, size_t k, int8_t *w_i8,
 /* ---- ConvRot ---- */
 int ho_hadamard_normalized(int size, float *h);    /* h3_w4a8_dequant.c:139 */
 int ho_convrot_act_f32(const float *x, size_t m, size_t k, int gs, float *y); /* :286,:367 */
+int ho_fwht_act_f32(const float *x, size_t m, size_t k, int gs, float *y);    /* :241-284 (H3_CONVROT_SYLVESTER=1) */
 
 /* ---- INT8 activation quant + GEMM ---- */
 int ho_quantize_act_int8(const float *x, size_t m, size_t k, int8_t *q,

@@ -145,6 +145,13 @@ class Oracle:
                                            _p(y, c_f32p)) == 1
         return y
 
+    def fwht(self, x, gs):
+        """Sylvester (Walsh-Hadamard) rotation per group, the H3_CONVROT_SYLVESTER=1 form."""
+        x = f32(x)
+        y = np.empty_like(x)
+        assert self.lib.ho_fwht_act_f32(_p(x, c_f32p), sz(x.shape[0]), sz(x.shape[1]), C.c_int(gs), _p(y, c_f32p)) == 1
+        return y
+
     # ---- act quant + GEMM
     def quantize_act_int8(self, x):
         x = f32(x)
@@ -494,6 +501,14 @@ class Ref:
         y = np.empty_like(x)
         ok = self.lib.h3_w4a8_convrot_act_f32(_p(x, c_f32p), sz(x.shape[0]), sz(x.shape[1]), C.c_int(gs),
                                               _p(y, c_f32p), self._err, sz(ERR))
+        assert ok == 1, self._err.value
+        return y
+
+    def fwht(self, x, gs):
+        x = f32(x)
+        y = np.empty_like(x)
+        ok = self.lib.h3_w4a8_fwht_act_f32(_p(x, c_f32p), sz(x.shape[0]), sz(x.shape[1]), C.c_int(gs), _p(y, c_f32p),
+                                           self._err, sz(ERR))
         assert ok == 1, self._err.value
         return y
 

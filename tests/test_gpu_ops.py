@@ -144,6 +144,24 @@ def test_convrot(cuda, oracle, gs):
     assert np.array_equal(host(q), qo) and np.array_equal(host(s), so)
 
 
+@pytest.mark.parametrize("gs", [256, 64, 8, 2])
+def test_convrot_sylvester_switch(cuda, oracle, gs, monkeypatch):
+    """H3_CONVROT_SYLVESTER=1 (the reference's switch, h3_w4a8_dequant.c:371-375): Walsh-Hadamard groups by radix-2
+    butterflies, bit-identical to the reference's in-place transform; group sizes that are not powers of four exist
+    only under the switch."""
+    rng = np.random.default_rng(17)
+    x = acts(rng, 45, 1024)
+    monkeypatch.setenv("H3_CONVROT_SYLVESTER", "1")
+    y = host(cuda.convrot_act_f32_dd(dev(x), gs))
+    assert np.array_equal(y, oracle.fwht(x, gs))
+    monkeypatch.delenv("H3_CONVROT_SYLVESTER")
+    if gs in (8, 2):
+        with pytest.raises(Exception):
+            cuda.convrot_act_f32_dd(dev(x), gs)
+    else:
+        assert rel_l2(host(cuda.convrot_act_f32_dd(dev(x), gs)), oracle.convrot(x, gs)) < 1e-6
+
+
 def test_qkv_rope(cuda, oracle):
     rng = np.random.default_rng(16)
     heads, hd = 3, 128

@@ -21,6 +21,16 @@ def test_linear_chain_bit_exact(oracle, ref, seed):
     assert np.array_equal(oracle.gemm_f32(x, w), ref.gemm_f32(x, w))
 
 
+@pytest.mark.parametrize("gs", [2, 8, 64, 256])
+def test_sylvester_rotation_bit_exact(oracle, ref, gs):
+    """The Walsh-Hadamard form of ConvRot that H3_CONVROT_SYLVESTER=1 selects (h3_w4a8_dequant.c:241-284)."""
+    rng = np.random.default_rng(40 + gs)
+    x = rng.normal(0, 1, (19, 512)).astype(np.float32)
+    assert np.array_equal(oracle.fwht(x, gs), ref.fwht(x, gs))
+    # it is the product with the Sylvester matrix, an orthogonal map
+    assert np.allclose(np.linalg.norm(oracle.fwht(x, gs), axis=1), np.linalg.norm(x, axis=1), rtol=1e-5)
+
+
 def test_w4a8_decode_random(oracle, ref):
     rng = np.random.default_rng(3)
     n, k = 64, 256
