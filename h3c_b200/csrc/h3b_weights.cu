@@ -329,7 +329,15 @@ static int map_epi(const h3_cuda_dit_gemm_epi *in, h3b_gemm_epi *out, char *erro
     if (in->swiglu && in->gate) return fail(error, error_size, "gemm epilogue: swiglu and gate are mutually exclusive");
     out->d_lora = in->d_lora;
     out->lora_ready = in->d_lora ? in->lora_ready : NULL;
-    if (in->requant_mode) return fail(error, error_size, "gemm epilogue: fused requant (requant_mode=%d) is not supported", in->requant_mode);
+    // requant_mode 1 (SwiGLU output re-quantised per row for the next GEMM, the one mode the reference's host arms,
+    // h3_dit_w4a8.c:4058, 4077) is served after the GEMM by the entry points below; the gate forms (2, 3) are not
+    if (in->requant_mode < 0 || in->requant_mode > 1)
+        return fail(error, error_size, "gemm epilogue: fused requant of the gate output (requant_mode=%d) is not supported",
+                    in->requant_mode);
+    if (in->requant_mode == 1) {
+        if (!in->swiglu) return fail(error, error_size, "dit requant mode1 needs swiglu");
+        if (in->y_f16) return fail(error, error_size, "dit gemm y_f16 incompatible with gate/requant");
+    }
     if (in->swiglu) out->kind = H3B_EPI_SWIGLU;
     if (in->gate) {
         if (!in->d_residual || !in->d_modulation || !in->slots)
@@ -346,6 +354,40 @@ static int map_epi(const h3_cuda_dit_gemm_epi *in, h3b_gemm_epi *out, char *erro
     return 1;
 }
 
+// requant_mode 1 (h3_gpu_cuda.cu:562-612, 5544-5570): the SwiGLU output d_y [m, n/2] is quantised per row (absmax / 127,
+// round half away, no rotation) into library scratch, rows [m, ceil128(m)) zeroed, and the two pointers are handed
+// back through the caller's struct, as the reference does.  The reference does it inside its row-wise dequant
+// kernel; here the dequant lives in the tile-wise GEMM epilogue, so it is a second launch over rows that are still
+// in L2.  requant_gs must equal the row width.
+static int requant_swiglu_rows(h3_cuda *cuda, const h3_cuda_dit_gemm_epi *epi, const float *d_y, size_t m, size_t width,
+                               bool own_scratch, char *error, size_t error_size) {
+    if ((size_t)epi->requant_gs != width) return fail(error, error_size, "dit requant gs must equal act row width");
+    int8_t *q;
+    float *sc;
+    size_t rows_out;
+    if (own_scratch) {   // the f32-activation entry point: library scratch, pointers handed back (h3_gpu_cuda.cu:5544-5570)
+        rows_out = (m + 127) / 128 * 128;
+        const size_t act_off = (rows_out * width + 15) / 16 * 16;
+        if (!grow(cuda, &cuda->rq, &cuda->rq_bytes, act_off + rows_out * sizeof(float), error, error_size)) return 0;
+        q = (int8_t *)cuda->rq;
+        sc = (float *)((char *)cuda->rq + act_off);
+        h3_cuda_dit_gemm_epi *mut = const_cast<h3_cuda_dit_gemm_epi *>(epi);
+        mut->d_rq_x = q;
+        mut->d_rq_act = sc;
+        mut->requant_rows = rows_out;
+    } else {             // the pre-quantised entry point: the caller's buffers (h3_gpu_cuda.cu:5009-5012)
+        if (!epi->d_rq_x || !epi->d_rq_act || epi->requant_rows < m) return fail(error, error_size, "dit gemm epi requant args");
+        q = epi->d_rq_x;
+        sc = epi->d_rq_act;
+        rows_out = epi->requant_rows;
+    }
+    if (rows_out > m) {
+        H3B_CUDA_OK(cudaMemsetAsync(q + m * width, 0, (rows_out - m) * width, cuda->op_stream), "requant pad rows");
+        H3B_CUDA_OK(cudaMemsetAsync(sc + m, 0, (rows_out - m) * sizeof(float), cuda->op_stream), "requant pad scales");
+    }
+    return launch_quant(cuda, d_y, H3B_F32, m, width, q, sc, error, error_size);
+}
+
 int h3_cuda_gemm_i8_dequant_f32_dev_pre_q(h3_cuda *cuda, const h3_cuda_w4a8_weight *weight, const int8_t *d_x_i8,
                                           const float *d_act_in, size_t m, float *d_y_f32, double *prep_ms,
                                           double *gemm_ms, char *backend_out, size_t backend_out_size,
@@ -357,6 +399,8 @@ int h3_cuda_gemm_i8_dequant_f32_dev_pre_q(h3_cuda *cuda, const h3_cuda_w4a8_weig
     if (prep_ms) *prep_ms = 0.0;
     Timer t(cuda, gemm_ms);
     int ok = h3b_gemm_i8_dev(cuda, weight, d_x_i8, d_act_in, m, d_y_f32, &e, error, error_size);
+    if (ok && epi && epi->requant_mode == 1)
+        ok = requant_swiglu_rows(cuda, epi, d_y_f32, m, weight->n / 2, false, error, error_size);
     t.stop();
     backend_name(backend_out, backend_out_size);
     return ok;
@@ -384,6 +428,8 @@ int h3_cuda_gemm_i8_dequant_f32_w_act_dev_epi(h3_cuda *cuda, const h3_cuda_w4a8_
     Timer tg(cuda, gemm_ms);
     int ok = h3b_gemm_i8_dev(cuda, weight, (const int8_t *)cuda->act_q, (const float *)cuda->act_s, m, d_y_f32, &e,
                              error, error_size);
+    if (ok && epi && epi->requant_mode == 1)
+        ok = requant_swiglu_rows(cuda, epi, d_y_f32, m, weight->n / 2, true, error, error_size);
     tg.stop();
     backend_name(backend_out, backend_out_size);
     return ok;

@@ -45,9 +45,63 @@ def call(name, *args):
     return c(name, *args)
 
 
+def view_device(pointer, shape, typestr):
+    """A torch view of device memory the library handed back as a raw pointer."""
+    class Raw:
+        __cuda_array_interface__ = {"shape": tuple(shape), "typestr": typestr, "data": (int(pointer), False), "version": 2}
+    return torch.as_tensor(Raw(), device="cuda")
+
+
 def p(t):
     from h3c_b200.lib import ptr
     return ptr(t)
+
+
+# ------------------------------------------------------------------ fused requant of the SwiGLU output (requant_mode 1)
+
+def test_fc1_swiglu_requant_then_fc2_on_the_codes(cuda, oracle):
+    """The reference's E2 option (h3_gpu_cuda.h:386-397, armed at h3_dit_w4a8.c:4058): FC1 with SwiGLU also hands back
+    the int8 codes and row scales of its output (library scratch, rows padded to 128 with zeros), and FC2 runs on them
+    through the pre-quantised entry point.  Codes and scales are the activation quantiser's applied to the f32 output
+    the same call wrote, bit for bit; the gate forms of the option stay refused."""
+    import h3c_b200
+    from h3c_b200 import lib as L
+    rng = np.random.default_rng(91)
+    m, d, ffn = 300, 512, 768
+    x = acts(rng, m, d)
+    w1 = rng.integers(-127, 128, (2 * ffn, d), dtype=np.int8)
+    s1 = rng.uniform(5e-5, 2e-4, 2 * ffn).astype(np.float32)
+    w2 = rng.integers(-127, 128, (d, ffn), dtype=np.int8)
+    s2 = rng.uniform(5e-5, 2e-4, d).astype(np.float32)
+    W1, W2 = cuda.weight_from_i8(w1, s1), cuda.weight_from_i8(w2, s2)
+    epi = L.DitGemmEpi()
+    epi.swiglu, epi.requant_mode, epi.requant_gs = 1, 1, ffn
+    xd = dev(x)
+    y1 = torch.empty((m, ffn), dtype=torch.float32, device="cuda")
+    backend = C.create_string_buffer(32)
+    call("h3_cuda_gemm_i8_dequant_f32_w_act_dev_epi", cuda.h, W1.h, p(xd), 0, m, p(y1), None, None, backend, 32, C.byref(epi))
+    cuda.check()
+    assert epi.d_rq_x and epi.d_rq_act and epi.requant_rows == 384
+    codes = view_device(epi.d_rq_x, (384, ffn), "|i1").cpu().numpy()
+    scales = view_device(epi.d_rq_act, (384,), "<f4").cpu().numpy()
+    qo, so = oracle.quantize_act_int8(host(y1))
+    assert np.array_equal(codes[:m], qo) and np.array_equal(scales[:m], so)
+    assert not codes[m:].any() and not scales[m:].any()
+    # FC2 on those codes, plain epilogue
+    y2 = torch.empty((m, d), dtype=torch.float32, device="cuda")
+    call("h3_cuda_gemm_i8_dequant_f32_dev_pre_q", cuda.h, W2.h, epi.d_rq_x, epi.d_rq_act, m, p(y2), None, None, backend, 32, None)
+    cuda.check()
+    assert np.array_equal(host(y2), oracle.gemm_i8_dequant(qo, w2, so, s2))
+    # wrong group size, and the gate forms
+    bad = L.DitGemmEpi()
+    bad.swiglu, bad.requant_mode, bad.requant_gs = 1, 1, ffn // 2
+    with pytest.raises(h3c_b200.H3Error, match="requant gs"):
+        call("h3_cuda_gemm_i8_dequant_f32_w_act_dev_epi", cuda.h, W1.h, p(xd), 0, m, p(y1), None, None, backend, 32, C.byref(bad))
+    bad.requant_mode, bad.swiglu = 2, 0
+    with pytest.raises(h3c_b200.H3Error, match="not supported"):
+        call("h3_cuda_gemm_i8_dequant_f32_w_act_dev_epi", cuda.h, W1.h, p(xd), 0, m, p(y1), None, None, backend, 32, C.byref(bad))
+    W1.free()
+    W2.free()
 
 
 # ------------------------------------------------------------------ f32 GEMM forms, f16 ConvRot, requantise helper
