@@ -19,6 +19,7 @@
 #include <string.h>
 
 #include "../../include/h3_b200.h"
+#include "../../include/h3b_plugin.h"
 
 typedef struct {
     const h3_cuda_w4a8_weight *lin[H3B_LIN_COUNT];
@@ -451,7 +452,7 @@ static int fp4_linear(h3b_dit *d, const h3_cuda_nvfp4_weight *w, const void *x, 
                       char *error, size_t error_size) {
     const float *x_use;
     if (!d->rotf) return fail(error, error_size, "NVFP4 linear: workspace not reserved");
-    if (width % 64 == 0 && (epi != 1 || h3_cuda_nvfp4_weight_n(w) % 256 == 0)) {
+    if (width % 64 == 0 && (epi != 1 || (h3_cuda_nvfp4_weight_n(w) % 256 == 0 && h3_plugin_enabled("H3B_FP4_WIDE")))) {
         /* one pass over the rows: (RMSNorm, modulation,) ConvRot and the NVFP4 quantisation in the row kernel, then the
          * block-scaled GEMM on the codes */
         h3b_norm_args a;

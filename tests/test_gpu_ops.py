@@ -461,6 +461,9 @@ def test_row_kernel_quantises_to_nvfp4_in_its_last_stage(cuda, oracle, m, k, gs,
 def test_gemm_nvfp4_swiglu_in_the_epilogue(cuda, oracle, m, n, k):
     """SwiGLU on the f32 accumulators inside the GEMM (gate rows | up rows of the weight): the reference's chain
     h3_cutlass_nvfp4_fc1_f32_run -> SwiGLU (h3_dit_nvfp4_chain.cu:201-277) as one kernel."""
+    import h3c_b200
+    if not h3c_b200.plugin_enabled("H3B_FP4_WIDE"):
+        pytest.skip("the fused SwiGLU epilogue belongs to the 128 x 256 tile form (H3B_FP4_WIDE=0 is set)")
     rng = np.random.default_rng(71)
     x = acts(rng, m, k)
     w = rng.normal(0, 0.05, (n, k)).astype(np.float32)
@@ -494,7 +497,8 @@ def test_reference_nvfp4_linear_entry_points(cuda, oracle, m, n, k):
                                 row_map=dev(rmap.view(np.int32)), slots=slots, gate_slot=5)
     assert rel_l2(host(y), oracle.gate(res, base, mod, rmap, slots, 5)) < 1e-5
     y = cuda.gemm_fp4_w_act_dev(wh, dev(x), kind="swiglu")
-    if n % 256 == 0:   # SwiGLU on the f32 accumulators in the GEMM epilogue
+    import h3c_b200
+    if n % 256 == 0 and h3c_b200.plugin_enabled("H3B_FP4_WIDE"):   # SwiGLU on the f32 accumulators in the GEMM epilogue
         assert rel_l2(host(y), oracle.swiglu(base)) < 1e-5
     else:              # other widths: bf16 accumulators and a second kernel, as in the reference's fp4 path
         fused = oracle.bf16_round(oracle.gemm_nvfp4(x4, sfx, w4, sfw, 1.0)) * np.float32(0.75)
