@@ -10,44 +10,11 @@
 #include <string.h>
 
 #include "h3b_internal.h"
+#include "h3b_nvfp4.cuh"
 
 namespace h3b {
 
-// ------------------------------------------------------------------ NVFP4 rounding rules (h3_gpu_cuda.cu:4468-4520)
-
-__device__ __forceinline__ uint8_t rq_f32_to_ue4m3(float v) {
-    int e, m, E;
-    if (!(v > 0.0f)) return 0;
-    const float f = frexpf(v, &e);
-    E = e + 6;
-    if (E <= 0) {
-        m = (int)lroundf(ldexpf(v, 6) * 8.0f);
-        return (uint8_t)(m > 7 ? 7 : m);
-    }
-    if (E >= 15) return 0x7E;
-    m = (int)lroundf((f * 2.0f - 1.0f) * 8.0f);
-    if (m == 8) {
-        E++;
-        m = 0;
-        if (E >= 15) return 0x7E;
-    }
-    return (uint8_t)((E << 3) | m);
-}
-__device__ __forceinline__ float rq_ue4m3_to_f32(uint8_t b) {
-    const int e = (b >> 3) & 15, m = b & 7;
-    if (e == 0) return ldexpf((float)m / 8.0f, -6);
-    if (e == 15 && m == 7) return __int_as_float(0x7fc00000);
-    return ldexpf(1.0f + (float)m / 8.0f, e - 7);
-}
-__device__ __forceinline__ uint32_t rq_e2m1(float q) {
-    const float a = fabsf(q);
-    const uint32_t mag = (a >= 0.25f) + (a >= 0.75f) + (a >= 1.25f) + (a >= 1.75f) + (a >= 2.5f) + (a >= 3.5f) + (a >= 5.0f);
-    return ((q < 0.0f && mag != 0) ? 8u : 0u) | mag;
-}
-__device__ __forceinline__ size_t rq_sf_offset(size_t row, size_t blk, size_t ncb) {
-    const size_t r128 = row & 127u;
-    return ((row >> 7) * ncb + (blk >> 2)) * 512u + 16u * (r128 & 31u) + 4u * (r128 >> 5) + (blk & 3u);
-}
+// NVFP4 rounding rules and scale layout: h3b_nvfp4.cuh
 
 // FC1 accumulators [m, 2*ffn] f32 -> silu(gate) * up -> E2M1 codes + UE4M3 block scales of the FC2 input
 // (h3_dit_nvfp4_chain.cu:201-277).  One thread per 16-element block; rows in [m, ceil128(m)) clear their scale
@@ -59,7 +26,7 @@ __global__ void k_swiglu_requant_nvfp4(const float *acc, float acc_scale, const 
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
         const size_t row = i / nc, blk = i - row * nc;
         if (row >= m) {
-            sf[rq_sf_offset(row, blk, ncb)] = 0;
+            sf[sf_offset(row, blk, ncb)] = 0;
             continue;
         }
         const float *g = acc + row * 2 * ffn + blk * 16, *u = g + ffn;
@@ -83,14 +50,14 @@ __global__ void k_swiglu_requant_nvfp4(const float *acc, float acc_scale, const 
         // unlike the activation quantiser the chain keeps a zero scale byte (no clamp to byte 1): a block of
         // zeros gets scale 1.0, a tiny block may underflow to scale 0 and then divides by zero like the reference
         const float scale_f = amax > 0.0f ? amax / 6.0f : 1.0f;
-        const uint8_t sb = rq_f32_to_ue4m3(scale_f);
-        const float inv = 1.0f / rq_ue4m3_to_f32(sb);
-        sf[rq_sf_offset(row, blk, ncb)] = sb;
+        const uint8_t sb = f32_to_ue4m3(scale_f);
+        const float inv = 1.0f / ue4m3_to_f32(sb);
+        sf[sf_offset(row, blk, ncb)] = sb;
         uint32_t lo = 0, hi = 0;
 #pragma unroll
         for (int j = 0; j < 8; j += 2) {
-            lo |= ((rq_e2m1(__fmul_rn(v[j], inv)) << 4) | rq_e2m1(__fmul_rn(v[j + 1], inv))) << (4 * j);
-            hi |= ((rq_e2m1(__fmul_rn(v[8 + j], inv)) << 4) | rq_e2m1(__fmul_rn(v[9 + j], inv))) << (4 * j);
+            lo |= ((e2m1_nibble(__fmul_rn(v[j], inv)) << 4) | e2m1_nibble(__fmul_rn(v[j + 1], inv))) << (4 * j);
+            hi |= ((e2m1_nibble(__fmul_rn(v[8 + j], inv)) << 4) | e2m1_nibble(__fmul_rn(v[9 + j], inv))) << (4 * j);
         }
         *reinterpret_cast<uint2 *>(packed + row * (ffn / 2) + blk * 8) = make_uint2(lo, hi);
     }

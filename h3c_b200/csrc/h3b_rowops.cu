@@ -70,6 +70,21 @@ __device__ __forceinline__ void store_vec(T *p, const float (&in)[V]) {
     }
 }
 
+// V f32 values through the read-only path (one 16-byte load when V == 4); `fill` where the pointer is null
+template <int V>
+__device__ __forceinline__ void load_vec_ro(const float *p, float (&out)[V], float fill) {
+    if (!p) {
+#pragma unroll
+        for (int i = 0; i < V; i++) out[i] = fill;
+    } else if constexpr (V == 4) {
+        const float4 t = __ldg(reinterpret_cast<const float4 *>(p));
+        out[0] = t.x; out[1] = t.y; out[2] = t.z; out[3] = t.w;
+    } else {
+#pragma unroll
+        for (int i = 0; i < V; i++) out[i] = __ldg(p + i);
+    }
+}
+
 __device__ __forceinline__ float block_sum(float v, float *red) {
     for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
     __syncthreads();
@@ -151,14 +166,18 @@ __global__ void __launch_bounds__(256) k_norm(NormParams p) {
         ss = block_sum(ss, red);
         const float inv = 1.0f / sqrtf(ss / (float)W + p.eps);
         for (unsigned c = threadIdx.x * V; c < W; c += blockDim.x * V) {
+            // the weight and modulation values of the V columns are fetched first, as vectors through the read-only
+            // path: scalar loads between the shared-memory stores below are not reordered by the compiler and
+            // each exposed a round trip to L2
+            float wv[V], sc[V], sh[V];
+            load_vec_ro<V>(p.norm_w ? p.norm_w + c : nullptr, wv, 1.0f);
+            load_vec_ro<V>(mod ? mod + p.scale_slot * W + c : nullptr, sc, 0.0f);
+            load_vec_ro<V>(mod ? mod + p.shift_slot * W + c : nullptr, sh, 0.0f);
             float y[V];
 #pragma unroll
             for (int i = 0; i < V; i++) {
-                float w = p.norm_w ? p.norm_w[c + i] : 1.0f;
-                float n = __fmul_rn(__fmul_rn(row[c + i], inv), w);
-                if (mod)
-                    n = __fadd_rn(__fmul_rn(n, __fadd_rn(1.0f, mod[p.scale_slot * W + c + i])),
-                                  mod[p.shift_slot * W + c + i]);
+                float n = __fmul_rn(__fmul_rn(row[c + i], inv), wv[i]);
+                if (mod) n = __fadd_rn(__fmul_rn(n, __fadd_rn(1.0f, sc[i])), sh[i]);
                 y[i] = round_to<T>(n);
                 row[c + i] = y[i];
                 amax = fmaxf(amax, fabsf(y[i]));
@@ -177,10 +196,10 @@ __global__ void __launch_bounds__(256) k_norm(NormParams p) {
     if (p.gs > 0 && p.sylvester) {
         // H3_CONVROT_SYLVESTER=1: the reference's in-place radix-2 transform, butterfly for butterfly, then one
         // multiplication by 1/sqrt(gs) (h3_w4a8_dequant.c:241-258): bit-identical to it
-        for (int h = 1; h < p.gs; h <<= 1) {
+        for (int h = 1, sh = 0; h < p.gs; h <<= 1, sh++) {
             __syncthreads();
             for (unsigned b = threadIdx.x; b < W / 2; b += blockDim.x) {
-                const unsigned lo = b % h, base = (b / h) * h * 2 + lo;
+                const unsigned lo = b & (unsigned)(h - 1), base = (((b >> sh) << sh) << 1) + lo;
                 const float u = row[base], v = row[base + h];
                 row[base] = __fadd_rn(u, v);
                 row[base + h] = __fsub_rn(u, v);
@@ -196,11 +215,13 @@ __global__ void __launch_bounds__(256) k_norm(NormParams p) {
             if (p.rot) p.rot[r * W + c] = v;
         }
     } else     if (p.gs > 0) {
-        for (int stride = 1; stride < p.gs; stride <<= 2) {
+        for (int stride = 1, sh = 0; stride < p.gs; stride <<= 2, sh += 2) {
             __syncthreads();
             for (unsigned b = threadIdx.x; b < W / 4; b += blockDim.x) {
-                unsigned lo = b % stride, hi = b / stride;
-                unsigned base = hi * stride * 4 + lo;
+                // stride is a power of two: shifts and masks (a division by a run-time value costs some thirty
+                // instructions, and this loop runs once per four elements and stage)
+                const unsigned lo = b & (unsigned)(stride - 1), hi = b >> sh;
+                unsigned base = ((hi << sh) << 2) + lo;
                 float a0 = row[base], a1 = row[base + stride], a2 = row[base + 2 * stride], a3 = row[base + 3 * stride];
                 float s = (a0 + a1) + (a2 + a3);
                 row[base] = s - 2.0f * a3;
@@ -687,7 +708,7 @@ int launch_norm(h3_cuda *cuda, const h3b_norm_args *a, char *error, size_t error
     const uintptr_t amask = 4 * dtype_bytes(a->dtype) - 1;
     auto al = [&](const void *q_, uintptr_t mask) { return !q_ || (reinterpret_cast<uintptr_t>(q_) & mask) == 0; };
     bool vec = a->width % 4 == 0 && al(a->d_x, amask) && al(a->d_branch, amask) && al(a->d_gated, amask) &&
-               al(a->d_normed, amask) && al(a->d_q, 3);
+               al(a->d_normed, amask) && al(a->d_q, 3) && al(a->d_norm_w, 15) && al(a->d_modulation, 15);
     switch (a->dtype) {
     case H3B_F32: return norm_dispatch<float>(cuda, p, a->rows, vec, error, error_size);
     case H3B_BF16: return norm_dispatch<__nv_bfloat16>(cuda, p, a->rows, vec, error, error_size);
