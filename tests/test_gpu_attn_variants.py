@@ -22,10 +22,11 @@ def test_variant_matches_f64_attention(variant, f16):
     if f16 and variant in ("213", "13", "10"):
         pytest.skip("the f16 form has the default, the plain and the pair variant only")
     env = dict(os.environ, H3B_ATTN_EMU=variant)
-    for lq, lk, heads in SHAPES:
-        cmd = [sys.executable, str(ROOT / "bench.py"), "--kernel", "attn", "--lq", str(lq), "--lk", str(lk), "--heads",
-               str(heads), "--iters", "1", "--check"] + (["--f16"] if f16 else [])
-        out = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=300, cwd=ROOT)
-        assert out.returncode == 0, out.stderr[-2000:]
-        line = json.loads(out.stdout.strip().splitlines()[-1])
-        assert line["rel_l2"] < (1e-3 if f16 else 4e-3), (variant, f16, lq, lk, line["rel_l2"])
+    cmd = [sys.executable, str(ROOT / "tests" / "attn_variant_worker.py"), "f16" if f16 else "bf16"] + \
+          [f"{lq},{lk},{heads}" for lq, lk, heads in SHAPES]
+    out = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600, cwd=ROOT)
+    assert out.returncode == 0, out.stderr[-2000:]
+    errors = json.loads(out.stdout.strip().splitlines()[-1])
+    assert len(errors) == len(SHAPES)
+    for spec, err in errors.items():
+        assert err < (1e-3 if f16 else 4e-3), (variant, f16, spec, err)
