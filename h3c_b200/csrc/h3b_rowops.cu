@@ -191,6 +191,7 @@ __global__ void __launch_bounds__(256) k_norm(NormParams p) {
             for (int i = 0; i < V; i++) amax = fmaxf(amax, fabsf(row[c + i]));
     }
 
+    bool fp4_done = false;
     // ---- ConvRot: y = x * H per group, H = kron-power of the 4x4 regular Hadamard / sqrt(gs).
     // H is symmetric, so this is a radix-4 butterfly network with strides 1, 4, 16, 64.
     if (p.gs > 0 && p.sylvester) {
@@ -214,7 +215,90 @@ __global__ void __launch_bounds__(256) k_norm(NormParams p) {
             amax = fmaxf(amax, fabsf(v));
             if (p.rot) p.rot[r * W + c] = v;
         }
-    } else     if (p.gs > 0) {
+    } else if (p.gs > 0 && (W & 255u) == 0) {
+        // Warp-resident form (every width of the block path is a multiple of 256): a warp takes 256 consecutive
+        // elements, lane l holding [4l, 4l+4) and [128+4l, 128+4l+4), so that the stride-1 butterfly is inside a lane,
+        // strides 4 and 16 are lane exchanges (xor 1,2,3 and 4,8,12) and stride 64 pairs the two halves of lanes
+        // l and l^16.  Of a butterfly's four inputs a0..a3 (by position) the sum (a0+a1)+(a2+a3) is symmetric under
+        // the exchanges used, and output k is sum - 2 a(3-k), which for every lane is "sum - 2 x the value three
+        // strides away": the same arithmetic as the shared-memory network below, value for value, without its
+        // barriers and index arithmetic.  Scaling, the row maximum, the f32 output and the NVFP4 codes follow while
+        // the values are still in registers.
+        __syncthreads();   // the row is complete in shared memory
+        const float norm = 1.0f / sqrtf((float)p.gs);   // exact: gs is a power of four
+        const unsigned lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+        auto lane_bfly = [](float x, int d) {
+            const float x1 = __shfl_xor_sync(0xffffffffu, x, d), x2 = __shfl_xor_sync(0xffffffffu, x, 2 * d),
+                        x3 = __shfl_xor_sync(0xffffffffu, x, 3 * d);
+            const float sum = (x + x1) + (x2 + x3);
+            return sum - 2.0f * x3;
+        };
+        amax = 0.0f;
+        for (unsigned g = warp; g < W / 256; g += nw) {
+            float *grp = row + g * 256;
+            const float4 lo4 = *reinterpret_cast<const float4 *>(grp + 4 * lane);
+            const float4 hi4 = *reinterpret_cast<const float4 *>(grp + 128 + 4 * lane);
+            float a[4] = {lo4.x, lo4.y, lo4.z, lo4.w}, b[4] = {hi4.x, hi4.y, hi4.z, hi4.w};
+            {   // stride 1
+                float sa = (a[0] + a[1]) + (a[2] + a[3]), sb = (b[0] + b[1]) + (b[2] + b[3]);
+                const float t0 = sa - 2.0f * a[3], t1 = sa - 2.0f * a[2], t2 = sa - 2.0f * a[1], t3 = sa - 2.0f * a[0];
+                a[0] = t0; a[1] = t1; a[2] = t2; a[3] = t3;
+                const float u0 = sb - 2.0f * b[3], u1 = sb - 2.0f * b[2], u2 = sb - 2.0f * b[1], u3 = sb - 2.0f * b[0];
+                b[0] = u0; b[1] = u1; b[2] = u2; b[3] = u3;
+            }
+            if (p.gs >= 16) {
+#pragma unroll
+                for (int i = 0; i < 4; i++) { a[i] = lane_bfly(a[i], 1); b[i] = lane_bfly(b[i], 1); }
+            }
+            if (p.gs >= 64) {
+#pragma unroll
+                for (int i = 0; i < 4; i++) { a[i] = lane_bfly(a[i], 4); b[i] = lane_bfly(b[i], 4); }
+            }
+            if (p.gs >= 256) {   // positions: first half of lanes < 16, first half of lanes >= 16, second halves likewise
+#pragma unroll
+                for (int i = 0; i < 4; i++) {
+                    const float pa = __shfl_xor_sync(0xffffffffu, a[i], 16), pb = __shfl_xor_sync(0xffffffffu, b[i], 16);
+                    const float sum = (a[i] + pa) + (b[i] + pb);
+                    a[i] = sum - 2.0f * pb;
+                    b[i] = sum - 2.0f * pa;
+                }
+            }
+#pragma unroll
+            for (int i = 0; i < 4; i++) {
+                a[i] = a[i] * norm;
+                b[i] = b[i] * norm;
+                amax = fmaxf(amax, fmaxf(fabsf(a[i]), fabsf(b[i])));
+            }
+            const float4 ra = make_float4(a[0], a[1], a[2], a[3]), rb = make_float4(b[0], b[1], b[2], b[3]);
+            *reinterpret_cast<float4 *>(grp + 4 * lane) = ra;
+            *reinterpret_cast<float4 *>(grp + 128 + 4 * lane) = rb;
+            const unsigned c0 = g * 256 + 4 * lane, c1 = c0 + 128;
+            if (p.rot) {
+                float *ro = p.rot + r * W;
+                if ((reinterpret_cast<uintptr_t>(p.rot) & 15) == 0) {
+                    *reinterpret_cast<float4 *>(ro + c0) = ra;
+                    *reinterpret_cast<float4 *>(ro + c1) = rb;
+                } else {
+#pragma unroll
+                    for (int i = 0; i < 4; i++) {
+                        ro[c0 + i] = a[i];
+                        ro[c1 + i] = b[i];
+                    }
+                }
+            }
+            if (p.fp4) {   // four lanes = one 16-element block, in both halves
+                uint8_t s0, s1;
+                uint8_t *dst = p.fp4 + r * (size_t)(W / 2);
+                *reinterpret_cast<uint16_t *>(dst + c0 / 2) = nvfp4_quad(ra, 0xffffffffu, &s0);
+                *reinterpret_cast<uint16_t *>(dst + c1 / 2) = nvfp4_quad(rb, 0xffffffffu, &s1);
+                if ((lane & 3) == 0) {
+                    p.sf[sf_offset(r, c0 / 16, W / 64)] = s0;
+                    p.sf[sf_offset(r, c1 / 16, W / 64)] = s1;
+                }
+            }
+        }
+        fp4_done = p.fp4 != nullptr;
+    } else if (p.gs > 0) {
         for (int stride = 1, sh = 0; stride < p.gs; stride <<= 2, sh += 2) {
             __syncthreads();
             for (unsigned b = threadIdx.x; b < W / 4; b += blockDim.x) {
@@ -242,7 +326,7 @@ __global__ void __launch_bounds__(256) k_norm(NormParams p) {
     }
 
     // ---- NVFP4 quantisation of the final row values (width % 16 == 0): four lanes per 16-element block
-    if (p.fp4) {
+    if (p.fp4 && !fp4_done) {
         __syncthreads();   // the row is complete in shared memory, whichever stage wrote it last
         uint8_t *dst = p.fp4 + r * (size_t)(W / 2);
         for (unsigned base = 0; base < W; base += blockDim.x * 4) {
