@@ -140,9 +140,13 @@ __global__ void __launch_bounds__(256) k_norm(NormParams p) {
     T *gated = p.gated ? reinterpret_cast<T *>(p.gated) + r * W : nullptr;
     T *normed = p.normed ? reinterpret_cast<T *>(p.normed) + r * W : nullptr;
 
+    // Rotate-and-quantise of plain rows (the reference's quantised linear on f32 activations): the warp-resident
+    // rotation below reads the row straight from global memory, nothing is staged and nothing is reduced first.
+    const bool direct = V == 4 && p.identity && !br && p.gs > 0 && !p.sylvester && (W & 255u) == 0;
+
     // ---- stage the row (optionally residual + branch * gate), sum of squares
     float ss = 0.0f;
-    for (unsigned c = threadIdx.x * V; c < W; c += blockDim.x * V) {
+    for (unsigned c = threadIdx.x * V; c < W && !direct; c += blockDim.x * V) {
         float v[V];
         load_vec<T, V>(x + c, v);
         if (br) {
@@ -184,7 +188,7 @@ __global__ void __launch_bounds__(256) k_norm(NormParams p) {
             }
             if (normed) store_vec<T, V>(normed + c, y);
         }
-    } else {
+    } else if (p.gs == 0) {   // (with a rotation the maximum is taken after it)
         // same element ownership as the staging loop, so no barrier is needed here
         for (unsigned c = threadIdx.x * V; c < W; c += blockDim.x * V)
 #pragma unroll
@@ -224,7 +228,7 @@ __global__ void __launch_bounds__(256) k_norm(NormParams p) {
         // strides away": the same arithmetic as the shared-memory network below, value for value, without its
         // barriers and index arithmetic.  Scaling, the row maximum, the f32 output and the NVFP4 codes follow while
         // the values are still in registers.
-        __syncthreads();   // the row is complete in shared memory
+        if (!direct) __syncthreads();   // the row is complete in shared memory
         const float norm = 1.0f / sqrtf((float)p.gs);   // exact: gs is a power of four
         const unsigned lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
         auto lane_bfly = [](float x, int d) {
@@ -236,9 +240,18 @@ __global__ void __launch_bounds__(256) k_norm(NormParams p) {
         amax = 0.0f;
         for (unsigned g = warp; g < W / 256; g += nw) {
             float *grp = row + g * 256;
-            const float4 lo4 = *reinterpret_cast<const float4 *>(grp + 4 * lane);
-            const float4 hi4 = *reinterpret_cast<const float4 *>(grp + 128 + 4 * lane);
-            float a[4] = {lo4.x, lo4.y, lo4.z, lo4.w}, b[4] = {hi4.x, hi4.y, hi4.z, hi4.w};
+            float a[4], b[4];
+            if (direct) {
+                if constexpr (V == 4) {
+                    load_vec<T, 4>(x + g * 256 + 4 * lane, a);
+                    load_vec<T, 4>(x + g * 256 + 128 + 4 * lane, b);
+                }
+            } else {
+                const float4 lo4 = *reinterpret_cast<const float4 *>(grp + 4 * lane);
+                const float4 hi4 = *reinterpret_cast<const float4 *>(grp + 128 + 4 * lane);
+                a[0] = lo4.x; a[1] = lo4.y; a[2] = lo4.z; a[3] = lo4.w;
+                b[0] = hi4.x; b[1] = hi4.y; b[2] = hi4.z; b[3] = hi4.w;
+            }
             {   // stride 1
                 float sa = (a[0] + a[1]) + (a[2] + a[3]), sb = (b[0] + b[1]) + (b[2] + b[3]);
                 const float t0 = sa - 2.0f * a[3], t1 = sa - 2.0f * a[2], t2 = sa - 2.0f * a[1], t3 = sa - 2.0f * a[0];
