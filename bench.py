@@ -1,4 +1,4 @@
-"""Benchmark of the DiT denoiser step (BASELINE.json's metric) on N GPUs of one node.
+"""Benchmark of the DiT denoiser step (milliseconds per 50-block step) on N GPUs of one node.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
 
@@ -6,7 +6,8 @@ Workload at every N: the full 50-block W4A8 step at 50,220 video tokens (31x30x5
 tokens, D = 3072, 24 x 128 heads, FFN 12288, bf16 residual stream, t = 0.5 (the metric's headline workload).
 N = 1 runs it on one GPU; N > 1 (under torchrun, one rank per GPU) shards the rows across the ranks
 (Ulysses sequence parallelism), so the per-N values are the same work and compare directly.
-`--workload step6144` times the 6,144-token single-GPU step (6x32x32 grid) instead.
+`--workload step6144` times the 6,144-token single-GPU step (6x32x32 grid) instead; `--weights nvfp4` the same
+token count on the reference's own block with every linear as an NVFP4 weight.
 `--impl reference` times the reference's CPU implementation of the same block on the host cores.
 `--kernel NAME` times one operator on synthetic data (the commands behind the summaries under profiles/).
 

@@ -1,6 +1,6 @@
 // Tensor-pipe rate probe: every SM issues back-to-back tcgen05.mma on one resident shared-memory tile
 // (no loads, no epilogue), which gives the sustained MMA rate of the part under its power limit for
-// int8, bf16 and block-scaled fp4 -- the denominators the GEMM and attention kernels are judged by.
+// int8, bf16 and block-scaled fp4 -- the denominators the GEMM and attention kernels are measured against.
 // Built into libh3_b200_probe.so, a helper of the bench, not into the product library.
 #include "../h3b_internal.h"
 #include "../h3b_ptx.cuh"
