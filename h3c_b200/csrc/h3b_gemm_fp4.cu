@@ -50,10 +50,13 @@ struct Fp4Params {
     CUtensorMap tmap_w;   // [N, K/2] bytes, box 128 x 128
     CUtensorMap tmap_y;   // wide form: [M, N] outputs, box 128 bytes x 32 rows, 128-byte swizzle
     CUtensorMap tmap_res; // wide form, gate epilogue: the residual, same geometry
+    CUtensorMap tmap_sfx; // pair form: scale tiles of X as [tiles, 128] words, box of four tiles
+    CUtensorMap tmap_sfw; // pair form: scale tiles of W, same geometry
     const uint8_t *sf_x, *sf_w;
     int M, N, K;
     int m_tiles, n_tiles, k_blocks;
     int sf_tiles_per_rowblock;   // K / 64
+    int group_m;                 // wide form: row bands per rasterisation group
     float alpha;
     int gate;                    // 0 plain, 1 y = residual + alpha * acc * gate
     int out_bf16;                // 0 f32, 1 bf16
@@ -83,6 +86,20 @@ __device__ __forceinline__ void umma_nvfp4_ss(uint32_t d_tmem, uint64_t a_desc, 
     asm volatile(
         "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
         "tcgen05.mma.cta_group::1.kind::mxf4nvf4.block_scale.block16 [%0], %1, %2, %3, [%5], [%6], p;\n\t}"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(sfa), "r"(sfb)
+        : "memory");
+}
+
+// CTA-pair forms: one instruction, issued by the even CTA, runs in both CTAs of the pair, each on its own shared and
+// tensor memory at the same offsets.
+__device__ __forceinline__ void tmem_cp_32x128b_warpx4_pair(uint32_t taddr, uint64_t desc) {
+    asm volatile("tcgen05.cp.cta_group::2.32x128b.warpx4 [%0], %1;" ::"r"(taddr), "l"(desc) : "memory");
+}
+__device__ __forceinline__ void umma_nvfp4_ss_pair(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                                   uint32_t sfa, uint32_t sfb, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::mxf4nvf4.block_scale.block16 [%0], %1, %2, %3, [%5], [%6], p;\n\t}"
         ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(sfa), "r"(sfb)
         : "memory");
 }
@@ -308,16 +325,43 @@ constexpr int STAGE_BYTES = A_BYTES + B_BYTES + SFA_BYTES + SFB_BYTES;
 constexpr int THREADS = 320;
 constexpr uint32_t SF_COL = 256;                                    // per stage 16 SFA + 32 SFB columns
 constexpr size_t SMEM_BYTES = 1024 + (size_t)STAGES * STAGE_BYTES + 8 * OUT_STAGE_BYTES + 256;
+// CTA pair: tile 256 x 256 over two CTAs.  Each CTA holds its own 128 rows of X and their scales, HALF of the tile's
+// weight rows, and the scales of all 256 weight rows (its half of the accumulator spans all 256 columns).
+constexpr int PAIR_STAGES = 5;
+constexpr int PAIR_STAGE_BYTES = A_BYTES + B_BYTES / 2 + SFA_BYTES + SFB_BYTES;
+constexpr size_t PAIR_SMEM_BYTES = 1024 + (size_t)PAIR_STAGES * PAIR_STAGE_BYTES + 8 * OUT_STAGE_BYTES + 256;
+static_assert(SF_COL + PAIR_STAGES * 48 <= 512, "scale columns of every stage must fit tensor memory");
 }  // namespace fp4w
+
+// Tile order: row bands in groups that hold about 32 MB of X (64 bands of 256 rows at K = 4096); inside a group the
+// band index runs fastest.  A sweep over the column tiles then finds the group's bands in L2: a tall X (50,220 rows
+// x 2 KiB = 103 MB at K = 4096) comes from HBM once, not once per column tile.
+__device__ __forceinline__ void wide_tile_coords(int tile, int m_tiles, int n_tiles, int group, int &mt, int &nt) {
+    const int per_group = group * n_tiles;
+    const int g = tile / per_group;
+    const int first_m = g * group;
+    const int gm = min(group, m_tiles - first_m);
+    const int local = tile - g * per_group;
+    mt = first_m + local % gm;
+    nt = local / gm;
+}
 
 // MODE 0: y = alpha acc; 1: y = residual + alpha acc gate; 2: SwiGLU, y[:, c] = silu(alpha acc[:, c]) * alpha acc[:, N/2 + c]
 // in f32 straight from the accumulator (the reference's chain h3_cutlass_nvfp4_fc1_f32_run -> swiglu, h3_dit_nvfp4_chain.cu:
 // 201-277, 322-435, as one kernel).  For SwiGLU the tile's first 128 weight rows are gate rows nt*128.., the second
 // 128 the matching up rows N/2 + nt*128.., so gate and up of an output column sit 128 accumulator columns apart.
-template <int MODE, bool OUT_BF16>
+//
+// PAIR: two CTAs of a cluster share a 256 x 256 tile (instruction M = 256 over both).  Per MMA clock each CTA then
+// reads 16 KiB of X and 16 KiB of W instead of 16 + 32, and a tile hand-over covers twice the work.  Every load of
+// both CTAs completes on the even CTA's barrier; that CTA issues the scale copies and MMAs for both.
+template <int MODE, bool OUT_BF16, bool PAIR>
 __global__ void __launch_bounds__(fp4w::THREADS, 1) k_gemm_nvfp4_wide(const __grid_constant__ Fp4Params p) {
     using namespace fp4w;
     constexpr bool GATE = MODE == 1, SWIGLU = MODE == 2;
+    constexpr int STAGES = PAIR ? fp4w::PAIR_STAGES : fp4w::STAGES;
+    constexpr int B_BYTES = PAIR ? fp4w::B_BYTES / 2 : fp4w::B_BYTES;
+    constexpr int STAGE_BYTES = PAIR ? fp4w::PAIR_STAGE_BYTES : fp4w::STAGE_BYTES;
+    constexpr int TILE_M = PAIR ? 2 * BM : BM;
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     uint8_t *out_stage = smem + (size_t)STAGES * STAGE_BYTES;
@@ -329,6 +373,9 @@ __global__ void __launch_bounds__(fp4w::THREADS, 1) k_gemm_nvfp4_wide(const __gr
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int total_tiles = p.m_tiles * p.n_tiles;
     const int n_blocks = (p.N + 127) / 128;   // scale row blocks of W
+    const int cta_rank = PAIR ? (int)cluster_ctarank() : 0;
+    const int first_tile = PAIR ? (int)(blockIdx.x >> 1) : (int)blockIdx.x;
+    const int tile_step = PAIR ? (int)(gridDim.x >> 1) : (int)gridDim.x;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; s++) {
@@ -336,20 +383,30 @@ __global__ void __launch_bounds__(fp4w::THREADS, 1) k_gemm_nvfp4_wide(const __gr
             mbar_init(&empty[s], 1);
         }
         mbar_init(tmem_full, 1);
-        mbar_init(tmem_empty, 8);
+        mbar_init(tmem_empty, PAIR ? 16 : 8);   // one arrival per epilogue warp of every CTA of the pair
         for (int w = 0; w < 8; w++) mbar_init(&res_bar[w], 1);
         *abort_word = 0;
         mbar_fence_init();
         tma_prefetch_desc(&p.tmap_x);
         tma_prefetch_desc(&p.tmap_w);
         tma_prefetch_desc(&p.tmap_y);
+        if (PAIR) {
+            tma_prefetch_desc(&p.tmap_sfx);
+            tma_prefetch_desc(&p.tmap_sfw);
+        }
     }
     if (warp == 1) {
-        tmem_alloc(tmem_slot, 512);
-        tmem_relinquish();
+        if (PAIR) {
+            tmem_alloc_pair(tmem_slot, 512);
+            tmem_relinquish_pair();
+        } else {
+            tmem_alloc(tmem_slot, 512);
+            tmem_relinquish();
+        }
     }
     tc_fence_before();
-    __syncthreads();
+    if (PAIR) cluster_sync_all();   // the peer's barriers must exist before anything signals them
+    else __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
 
@@ -357,8 +414,9 @@ __global__ void __launch_bounds__(fp4w::THREADS, 1) k_gemm_nvfp4_wide(const __gr
         if (lane == 0) {
             int s = 0;
             uint32_t ph = 0;
-            for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
-                const int mt = tile % p.m_tiles, nt = tile / p.m_tiles;
+            for (int tile = first_tile; tile < total_tiles; tile += tile_step) {
+                int mt, nt;
+                wide_tile_coords(tile, p.m_tiles, p.n_tiles, p.group_m, mt, nt);
                 // weight rows of the tile's two halves and their scale row blocks
                 const int n0 = SWIGLU ? nt * 128 : nt * BN, n1 = SWIGLU ? p.N / 2 + nt * 128 : nt * BN + 128;
                 const int nb0 = n0 / 128, nb1 = min(n1 / 128, n_blocks - 1);   // a missing second block repeats the first
@@ -369,6 +427,19 @@ __global__ void __launch_bounds__(fp4w::THREADS, 1) k_gemm_nvfp4_wide(const __gr
                     const int kt0 = kb * 4;
                     const int nkt = min(4, p.sf_tiles_per_rowblock - kt0);
                     const uint32_t sf_bytes = (uint32_t)nkt * 512;
+                    if (PAIR) {
+                        // the scale boxes are always four tiles long: past the last tile of a row block they bring
+                        // tiles nobody reads (or zeros past the end of the array)
+                        const uint32_t bar = mapa_shared(smem_u32(&full[s]), 0);
+                        if (cta_rank == 0) mbar_expect_tx(&full[s], 2 * STAGE_BYTES);
+                        tma_load_2d_pair(a_dst, &p.tmap_x, bar, kb * BK_BYTES, mt * TILE_M + cta_rank * BM);
+                        tma_load_2d_pair(b_dst, &p.tmap_w, bar, kb * BK_BYTES, cta_rank == 0 ? n0 : n1);
+                        tma_load_2d_pair(sfa_dst, &p.tmap_sfx, bar, 0, (mt * 2 + cta_rank) * p.sf_tiles_per_rowblock + kt0);
+                        tma_load_2d_pair(sfb_dst, &p.tmap_sfw, bar, 0, nb0 * p.sf_tiles_per_rowblock + kt0);
+                        tma_load_2d_pair(sfb_dst + 4 * 512, &p.tmap_sfw, bar, 0, nb1 * p.sf_tiles_per_rowblock + kt0);
+                        if (++s == STAGES) { s = 0; ph ^= 1; }
+                        continue;
+                    }
                     mbar_expect_tx(&full[s], A_BYTES + B_BYTES + 3 * sf_bytes);
                     tma_load_2d(a_dst, &p.tmap_x, &full[s], kb * BK_BYTES, mt * BM);
                     tma_load_2d(b_dst, &p.tmap_w, &full[s], kb * BK_BYTES, n0);
@@ -383,10 +454,10 @@ __global__ void __launch_bounds__(fp4w::THREADS, 1) k_gemm_nvfp4_wide(const __gr
         }
         __syncwarp();
     } else if (warp == 1) {
-        constexpr uint32_t idesc = fp4_idesc(BM, BN);
+        constexpr uint32_t idesc = fp4_idesc(TILE_M, BN);
         int s = 0, it = 0;
         uint32_t ph = 0;
-        for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, it++) {
+        for (int tile = cta_rank == 0 ? first_tile : total_tiles; tile < total_tiles; tile += tile_step, it++) {
             if (!mbar_wait(tmem_empty, (it & 1) ^ 1, abort_word, p.status, H3B_ST_TIMEOUT_TMEM_EMPTY)) break;
             tc_fence_after();
             const uint32_t d_tmem = tmem_base;
@@ -398,21 +469,36 @@ __global__ void __launch_bounds__(fp4w::THREADS, 1) k_gemm_nvfp4_wide(const __gr
                 const int nkt = min(4, p.sf_tiles_per_rowblock - kb * 4);
                 const uint32_t sfa_t = tmem_base + SF_COL + (uint32_t)s * 48, sfb_t = sfa_t + 16;
                 if (elect_one()) {
-                    for (int j = 0; j < nkt; j++) {
-                        tmem_cp_32x128b_warpx4(sfa_t + j * 4, sf_desc(sfa_addr + j * 512));
-                        tmem_cp_32x128b_warpx4(sfb_t + j * 8, sf_desc(sfb_addr + j * 512));
-                        tmem_cp_32x128b_warpx4(sfb_t + j * 8 + 4, sf_desc(sfb_addr + (4 + j) * 512));
+                    if (PAIR) {
+                        for (int j = 0; j < nkt; j++) {
+                            tmem_cp_32x128b_warpx4_pair(sfa_t + j * 4, sf_desc(sfa_addr + j * 512));
+                            tmem_cp_32x128b_warpx4_pair(sfb_t + j * 8, sf_desc(sfb_addr + j * 512));
+                            tmem_cp_32x128b_warpx4_pair(sfb_t + j * 8 + 4, sf_desc(sfb_addr + (4 + j) * 512));
+                        }
+                        for (int j = 0; j < nkt; j++)
+                            umma_nvfp4_ss_pair(d_tmem, umma_desc_k_sw128(a_addr + j * 32), umma_desc_k_sw128(b_addr + j * 32),
+                                               idesc, sfa_t + j * 4, sfb_t + j * 8, (uint32_t)((kb | j) != 0));
+                        tc_commit_pair(&empty[s], 3);   // the stage is free in both CTAs once these have read it
+                    } else {
+                        for (int j = 0; j < nkt; j++) {
+                            tmem_cp_32x128b_warpx4(sfa_t + j * 4, sf_desc(sfa_addr + j * 512));
+                            tmem_cp_32x128b_warpx4(sfb_t + j * 8, sf_desc(sfb_addr + j * 512));
+                            tmem_cp_32x128b_warpx4(sfb_t + j * 8 + 4, sf_desc(sfb_addr + (4 + j) * 512));
+                        }
+                        for (int j = 0; j < nkt; j++)
+                            umma_nvfp4_ss(d_tmem, umma_desc_k_sw128(a_addr + j * 32), umma_desc_k_sw128(b_addr + j * 32), idesc,
+                                          sfa_t + j * 4, sfb_t + j * 8, (uint32_t)((kb | j) != 0));
+                        tc_commit(&empty[s]);
                     }
-                    for (int j = 0; j < nkt; j++)
-                        umma_nvfp4_ss(d_tmem, umma_desc_k_sw128(a_addr + j * 32), umma_desc_k_sw128(b_addr + j * 32), idesc,
-                                      sfa_t + j * 4, sfb_t + j * 8, (uint32_t)((kb | j) != 0));
-                    tc_commit(&empty[s]);
                 }
                 __syncwarp();
                 if (++s == STAGES) { s = 0; ph ^= 1; }
             }
             if (*abort_word) break;
-            if (elect_one()) tc_commit(tmem_full);
+            if (elect_one()) {
+                if (PAIR) tc_commit_pair(tmem_full, 3);
+                else tc_commit(tmem_full);
+            }
             __syncwarp();
         }
         __syncwarp();
@@ -427,9 +513,10 @@ __global__ void __launch_bounds__(fp4w::THREADS, 1) k_gemm_nvfp4_wide(const __gr
         uint64_t *rbar = &res_bar[warp - 2];
         uint32_t res_phase = 0;
         int it = 0;
-        for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, it++) {
-            const int mt = tile % p.m_tiles, nt = tile / p.m_tiles;
-            const int row0 = mt * BM + q * 32;
+        for (int tile = first_tile; tile < total_tiles; tile += tile_step, it++) {
+            int mt, nt;
+            wide_tile_coords(tile, p.m_tiles, p.n_tiles, p.group_m, mt, nt);
+            const int row0 = mt * TILE_M + cta_rank * BM + q * 32;
             const float *gate = nullptr;
             if (GATE && p.mod) {
                 const int row = min(row0 + lane, p.M - 1);   // rows past M are clipped by the store
@@ -452,7 +539,10 @@ __global__ void __launch_bounds__(fp4w::THREADS, 1) k_gemm_nvfp4_wide(const __gr
             // the values are in registers: the accumulator can take the next tile
             tc_fence_before();
             __syncwarp();
-            if (lane == 0) mbar_arrive(tmem_empty);
+            if (lane == 0) {
+                if (PAIR && cta_rank != 0) mbar_arrive_cluster(mapa_shared(smem_u32(tmem_empty), 0));
+                else mbar_arrive(tmem_empty);
+            }
             const int col0 = SWIGLU ? nt * 128 + half * 64 : nt * BN + half * 128;
             const int n_out = SWIGLU ? p.N / 2 : p.N;
             if (ok && row0 < p.M) {
@@ -535,10 +625,14 @@ __global__ void __launch_bounds__(fp4w::THREADS, 1) k_gemm_nvfp4_wide(const __gr
     }
 
     tc_fence_before();
-    __syncthreads();
+    // A pair leaves together: neither CTA may exit while the other can still signal its barriers, read its shared
+    // memory or write its tensor memory.
+    if (PAIR) cluster_sync_all();
+    else __syncthreads();
     if (warp == 1) {
         tc_fence_after();
-        tmem_dealloc(tmem_base, 512);
+        if (PAIR) tmem_dealloc_pair(tmem_base, 512);
+        else tmem_dealloc(tmem_base, 512);
     }
 }
 
@@ -578,6 +672,8 @@ int launch_gemm_nvfp4(h3_cuda *cuda, const uint8_t *w_fp4, const uint8_t *sf_w, 
         int rc2 = h3b_encode_tmap_2d(&p.tmap_w, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, w_fp4, k / 2, n, k / 2, BK_BYTES, 128,
                                      CU_TENSOR_MAP_SWIZZLE_128B);
         if (rc2 != 0) return fail(error, error_size, "gemm_fp4: cuTensorMapEncodeTiled failed (%d)", rc2);
+        p.group_m = (int)((32u << 20) / (256 * (k / 2)));
+        p.group_m = p.group_m < 8 ? 8 : p.group_m > 74 ? 74 : p.group_m;
         p.n_tiles = (int)ceil_div(n, (size_t)fp4w::BN);   // SwiGLU: N/2 output columns, 128 per tile: the same count
         const bool bf = out_dtype == H3B_BF16;
         const CUtensorMapDataType odt = bf ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32;
@@ -587,9 +683,52 @@ int launch_gemm_nvfp4(h3_cuda *cuda, const uint8_t *w_fp4, const uint8_t *sf_w, 
             rc2 = h3b_encode_tmap_2d(&p.tmap_res, odt, osz, residual, n, m, n * osz, (uint32_t)(128 / osz), 32,
                                      CU_TENSOR_MAP_SWIZZLE_128B);
         if (rc2 != 0) return fail(error, error_size, "gemm_fp4: cuTensorMapEncodeTiled (outputs) failed (%d)", rc2);
-        auto kw = gate == 2   ? (p.out_bf16 ? k_gemm_nvfp4_wide<2, true> : k_gemm_nvfp4_wide<2, false>)
-                  : gate == 1 ? (p.out_bf16 ? k_gemm_nvfp4_wide<1, true> : k_gemm_nvfp4_wide<1, false>)
-                              : (p.out_bf16 ? k_gemm_nvfp4_wide<0, true> : k_gemm_nvfp4_wide<0, false>);
+        // CTA pairs whenever there is more than one 128-row band (H3B_FP4_PAIRS=0 keeps single CTAs)
+        if (m > 128 && h3_plugin_enabled("H3B_FP4_PAIRS")) {
+            const uint64_t tiles_x = (uint64_t)ceil_div(m, 128) * (k / 64), tiles_wt = (uint64_t)ceil_div(n, 128) * (k / 64);
+            rc2 = h3b_encode_tmap_2d(&p.tmap_sfx, CU_TENSOR_MAP_DATA_TYPE_UINT32, 4, sf_x, 128, tiles_x, 512, 128, 4,
+                                     CU_TENSOR_MAP_SWIZZLE_NONE);
+            if (rc2 == 0)
+                rc2 = h3b_encode_tmap_2d(&p.tmap_sfw, CU_TENSOR_MAP_DATA_TYPE_UINT32, 4, sf_w, 128, tiles_wt, 512, 128, 4,
+                                         CU_TENSOR_MAP_SWIZZLE_NONE);
+            if (rc2 != 0) return fail(error, error_size, "gemm_fp4: cuTensorMapEncodeTiled (scales) failed (%d)", rc2);
+            auto kp = gate == 2   ? (p.out_bf16 ? k_gemm_nvfp4_wide<2, true, true> : k_gemm_nvfp4_wide<2, false, true>)
+                      : gate == 1 ? (p.out_bf16 ? k_gemm_nvfp4_wide<1, true, true> : k_gemm_nvfp4_wide<1, false, true>)
+                                  : (p.out_bf16 ? k_gemm_nvfp4_wide<0, true, true> : k_gemm_nvfp4_wide<0, false, true>);
+            H3B_CUDA_OK(cudaFuncSetAttribute(kp, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)fp4w::PAIR_SMEM_BYTES),
+                        "gemm_fp4 smem attribute");
+            cudaLaunchConfig_t cfg;
+            memset(&cfg, 0, sizeof(cfg));
+            cudaLaunchAttribute attr;
+            attr.id = cudaLaunchAttributeClusterDimension;
+            attr.val.clusterDim.x = 2; attr.val.clusterDim.y = 1; attr.val.clusterDim.z = 1;
+            cfg.blockDim = dim3(fp4w::THREADS);
+            cfg.dynamicSmemBytes = fp4w::PAIR_SMEM_BYTES;
+            cfg.stream = cuda->op_stream;
+            cfg.attrs = &attr;
+            cfg.numAttrs = 1;
+            // co-resident pairs on this device, asked once per kernel form and device
+            static int max_pairs[6][64];
+            const int dev = cuda->device & 63, form = gate * 2 + (p.out_bf16 ? 1 : 0);
+            if (max_pairs[form][dev] == 0) {
+                cfg.gridDim = dim3((unsigned)(cuda->sm_count & ~1));
+                int np = 0;
+                H3B_CUDA_OK(cudaOccupancyMaxActiveClusters(&np, kp, &cfg), "gemm_fp4 cluster occupancy");
+                if (np < 1) return fail(error, error_size, "gemm_fp4: no CTA pair fits on this device");
+                max_pairs[form][dev] = np;
+            }
+            p.m_tiles = (int)ceil_div(m, (size_t)256);
+            const int tiles_p = p.m_tiles * p.n_tiles;
+            const int n_pairs = tiles_p < max_pairs[form][dev] ? tiles_p : max_pairs[form][dev];
+            cfg.gridDim = dim3((unsigned)(2 * n_pairs));
+            ProfScope prof(cuda, PROF_GEMM);
+            H3B_CUDA_OK(cudaLaunchKernelEx(&cfg, kp, p), "k_gemm_nvfp4_wide pair launch");
+            cuda->launches++;
+            return 1;
+        }
+        auto kw = gate == 2   ? (p.out_bf16 ? k_gemm_nvfp4_wide<2, true, false> : k_gemm_nvfp4_wide<2, false, false>)
+                  : gate == 1 ? (p.out_bf16 ? k_gemm_nvfp4_wide<1, true, false> : k_gemm_nvfp4_wide<1, false, false>)
+                              : (p.out_bf16 ? k_gemm_nvfp4_wide<0, true, false> : k_gemm_nvfp4_wide<0, false, false>);
         H3B_CUDA_OK(cudaFuncSetAttribute(kw, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)fp4w::SMEM_BYTES),
                     "gemm_fp4 smem attribute");
         const int tiles_w = p.m_tiles * p.n_tiles;
