@@ -111,6 +111,23 @@ class Rt:
             out.append(ms.value)
         return float(np.median(out))
 
+    def time_ms_stream(self, fn, iters, warmup=2):
+        """Device time per call of `iters` calls queued back to back (one event pair around all of them)."""
+        for _ in range(warmup):
+            fn()
+        self.sync()
+        e0, e1 = vp(), vp()
+        self.rt.cudaEventCreate(C.byref(e0))
+        self.rt.cudaEventCreate(C.byref(e1))
+        self.rt.cudaEventRecord(e0, None)
+        for _ in range(iters):
+            fn()
+        self.rt.cudaEventRecord(e1, None)
+        self.rt.cudaEventSynchronize(e1)
+        ms = f32c()
+        self.rt.cudaEventElapsedTime(C.byref(ms), e0, e1)
+        return ms.value / iters
+
 
 class RefCuda:
     def __init__(self):
@@ -259,7 +276,7 @@ class RefCuda:
         run()
         self.rt.sync()
         self.lib.h3_cuda_set_quiet(vp(self.h), 1)
-        out[f"{tag}_ms"] = np.array([self.rt.time_ms(run, o.get("iters", 5))])
+        out[f"{tag}_ms"] = np.array([self.rt.time_ms(run, o.get("iters", 5)), self.rt.time_ms_stream(run, 3 * o.get("iters", 5))])
         self.lib.h3_cuda_set_quiet(vp(self.h), 0)
         self.rt.free_all()
 

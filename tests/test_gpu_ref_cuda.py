@@ -254,6 +254,7 @@ def test_timing_table_against_reference_cuda(cuda, tmp_path):
             if "f_ms" in ref:
                 row["ref_cublaslt_fp4_ms"] = float(ref["f_ms"][0])
                 row["tflops_ref"] = 2.0 * m * n * k / row["ref_cublaslt_fp4_ms"] / 1e9
+                row["ref_back_to_back_ms"] = float(ref["f_ms"][1])   # 30 calls queued behind one another
             else:
                 row["ref_failure"] = failures.get("f")
         except (AssertionError, subprocess.TimeoutExpired) as exc:
@@ -265,6 +266,15 @@ def test_timing_table_against_reference_cuda(cuda, tmp_path):
         sfw = torch.full((sfb(n),), 0x38, device="cuda", dtype=torch.uint8)
         row["ours_ms"] = _time(lambda: cuda.gemm_fp4(w4, sfw, x4, sfx, out_dtype=torch.bfloat16))
         row["tflops_ours"] = 2.0 * m * n * k / row["ours_ms"] / 1e9
+        fn = lambda: cuda.gemm_fp4(w4, sfw, x4, sfx, out_dtype=torch.bfloat16)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        e0.record()
+        for _ in range(30):
+            fn()
+        e1.record()
+        e1.synchronize()
+        row["ours_back_to_back_ms"] = e0.elapsed_time(e1) / 30
         table["fp4"].append(row)
     out_dir = ROOT / "gpurun_out"
     out_dir.mkdir(exist_ok=True)
