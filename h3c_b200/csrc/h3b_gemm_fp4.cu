@@ -9,8 +9,8 @@
 // its scale), and UE4M3 scales in the 128x4 blocked layout (h3_gpu_cuda.cu:4534), which is the
 // layout tcgen05.cp moves into tensor memory as it is: one 512-byte block = 128 rows x 64 k.
 //
-// Two kernels.  N >= 256 runs k_gemm_nvfp4_wide (tile 128 x 256, described at its definition below); narrower
-// outputs run k_gemm_nvfp4:
+// Two kernels.  N >= 256 runs k_gemm_nvfp4_wide (tile 128 x 256, or 256 x 256 over a CTA pair when M > 128; described
+// at its definition below); narrower outputs run k_gemm_nvfp4:
 // Persistent kernel, tile 128 x 128, 256 k (128 packed bytes) per stage.  A 128x128x64 fp4 MMA executes in
 // 64 cycles, while one stage costs its issuing warp a barrier poll (about 100 cycles), eight tcgen05.cp
 // scale copies, four MMAs and a commit: a single issuer kept the pipe a third busy.  So the CTA runs TWO
