@@ -195,13 +195,12 @@ __global__ void __launch_bounds__(fp4::THREADS, 1) k_gemm_nvfp4(const __grid_con
                     const int nkt = min(4, p.sf_tiles_per_rowblock - kb * 4);   // MMAs (64 k each) with data
                     const uint32_t sf_t = tmem_base + SF_COL + (uint32_t)pipe * 64 + (uint32_t)sfbuf * 32;
                     if (elect_one()) {
-                        for (int j = 0; j < nkt; j++) {
+                        for (int j = 0; j < nkt; j++) {   // copies of MMA j + 1 run while MMA j executes
                             tmem_cp_32x128b_warpx4(sf_t + j * 4, sf_desc(sfa_addr + j * 512));
                             tmem_cp_32x128b_warpx4(sf_t + 16 + j * 4, sf_desc(sfb_addr + j * 512));
-                        }
-                        for (int j = 0; j < nkt; j++)
                             umma_nvfp4_ss(d_tmem, umma_desc_k_sw128(a_addr + j * 32), umma_desc_k_sw128(b_addr + j * 32),
                                           idesc, sf_t + j * 4, sf_t + 16 + j * 4, (uint32_t)((kb | j) != 0));
+                        }
                         tc_commit(&empty[s]);
                     }
                     __syncwarp();
@@ -468,26 +467,27 @@ __global__ void __launch_bounds__(fp4w::THREADS, 1) k_gemm_nvfp4_wide(const __gr
                 const uint32_t b_addr = a_addr + A_BYTES, sfa_addr = b_addr + B_BYTES, sfb_addr = sfa_addr + SFA_BYTES;
                 const int nkt = min(4, p.sf_tiles_per_rowblock - kb * 4);
                 const uint32_t sfa_t = tmem_base + SF_COL + (uint32_t)s * 48, sfb_t = sfa_t + 16;
+                // The scale copies of MMA j + 1 follow MMA j in the queue and run while it executes.  All twelve
+                // copies of a stage ahead of its four MMAs cost 6 % (the pipe waits for the whole run of copies),
+                // two stages' copies ahead of eight MMAs 15 %.
                 if (elect_one()) {
                     if (PAIR) {
                         for (int j = 0; j < nkt; j++) {
                             tmem_cp_32x128b_warpx4_pair(sfa_t + j * 4, sf_desc(sfa_addr + j * 512));
                             tmem_cp_32x128b_warpx4_pair(sfb_t + j * 8, sf_desc(sfb_addr + j * 512));
                             tmem_cp_32x128b_warpx4_pair(sfb_t + j * 8 + 4, sf_desc(sfb_addr + (4 + j) * 512));
-                        }
-                        for (int j = 0; j < nkt; j++)
                             umma_nvfp4_ss_pair(d_tmem, umma_desc_k_sw128(a_addr + j * 32), umma_desc_k_sw128(b_addr + j * 32),
                                                idesc, sfa_t + j * 4, sfb_t + j * 8, (uint32_t)((kb | j) != 0));
+                        }
                         tc_commit_pair(&empty[s], 3);   // the stage is free in both CTAs once these have read it
                     } else {
                         for (int j = 0; j < nkt; j++) {
                             tmem_cp_32x128b_warpx4(sfa_t + j * 4, sf_desc(sfa_addr + j * 512));
                             tmem_cp_32x128b_warpx4(sfb_t + j * 8, sf_desc(sfb_addr + j * 512));
                             tmem_cp_32x128b_warpx4(sfb_t + j * 8 + 4, sf_desc(sfb_addr + (4 + j) * 512));
-                        }
-                        for (int j = 0; j < nkt; j++)
                             umma_nvfp4_ss(d_tmem, umma_desc_k_sw128(a_addr + j * 32), umma_desc_k_sw128(b_addr + j * 32), idesc,
                                           sfa_t + j * 4, sfb_t + j * 8, (uint32_t)((kb | j) != 0));
+                        }
                         tc_commit(&empty[s]);
                     }
                 }
