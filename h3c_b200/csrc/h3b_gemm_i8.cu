@@ -21,6 +21,7 @@
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
+#include <math.h>
 #include <stdlib.h>
 
 #include "h3b_internal.h"
@@ -35,6 +36,7 @@ constexpr int BK = 128;          // int8 elements (= bytes) of K per stage
 constexpr int A_BYTES = BM * BK;             // 16 KiB
 constexpr int THREADS = 320;
 constexpr int TMEM_COLS = 512;
+constexpr int SPLITK_CNT_BYTES = 1024;   // two counters per slot ahead of the slots' sums
 constexpr int GROUP_M_MIN = 8;   // rasterisation: at least 8 row bands share the weight tiles in L2
 // internal epilogue id: QKV + QK-norm + RoPE whose rows go to (peer) buffers selected by head group; the rows
 // are first transposed through shared memory so that every store instruction writes whole 256-byte head
@@ -75,6 +77,12 @@ struct GemmParams {
     int n_out;            // columns of Y (N, or N/2 for SwiGLU)
     int m_tiles, n_tiles, k_blocks;
     int group_m;   // row bands per rasterisation group
+    // Work items: items [0, tail_first) are whole tiles; with split_s > 1 the last tiles_total - tail_first tiles are cut
+    // into split_s slices of K each (item = tail_first + slot * split_s + slice), all of them in the last wave.
+    int items_total, tail_first, split_s;
+    int32_t *sk_acc;        // [slot][slice - 1][256 columns][256 rows] sums of the slices 1..
+    unsigned *sk_cnt;       // [slot][2]: slices' warps that have stored their sums; owner warps that have folded them
+                            // (zero between launches)
     int swiglu;
     const float *act_scale;   // [M]
     const float *s_channel;   // [N]
@@ -104,6 +112,23 @@ __device__ __forceinline__ void tile_coords(int tile, int m_tiles, int n_tiles, 
     const int local = tile - g * per_group;
     mt = first_m + local % gm;
     nt = local / gm;
+}
+
+struct GemmItem { int tile, kb0, kb1, slice, slot, parts; };
+__device__ __forceinline__ GemmItem gemm_item(const GemmParams &p, int item) {
+    GemmItem w;
+    if (item < p.tail_first) {
+        w.tile = item; w.kb0 = 0; w.kb1 = p.k_blocks; w.slice = 0; w.slot = 0; w.parts = 1;
+    } else {
+        const int idx = item - p.tail_first;
+        w.slot = idx / p.split_s;
+        w.slice = idx - w.slot * p.split_s;
+        w.tile = p.tail_first + w.slot;
+        w.parts = p.split_s;
+        w.kb0 = (int)((long long)w.slice * p.k_blocks / p.split_s);
+        w.kb1 = (int)((long long)(w.slice + 1) * p.k_blocks / p.split_s);
+    }
+    return w;
 }
 
 __device__ __forceinline__ float gelu_tanh_dev(float v) {   // h3_vision_cuda.c:365-371
@@ -273,7 +298,6 @@ __global__ void __launch_bounds__(gemm::THREADS, 1) k_gemm_i8(const __grid_const
     volatile int *abort_word = reinterpret_cast<volatile int *>(tmem_slot + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int total_tiles = p.m_tiles * p.n_tiles;
     // A pair walks the tile list together; cta_rank selects this CTA's rows of A, half of B and rows of Y.
     const int cta_rank = CTAS == 2 ? (int)cluster_ctarank() : 0;
     const int first_tile = CTAS == 2 ? (int)(blockIdx.x >> 1) : (int)blockIdx.x;
@@ -319,13 +343,14 @@ __global__ void __launch_bounds__(gemm::THREADS, 1) k_gemm_i8(const __grid_const
         if (lane == 0) {
             int s = 0;
             uint32_t ph = 0;
-            for (int tile = first_tile; tile < total_tiles; tile += tile_step) {
+            for (int item = first_tile; item < p.items_total; item += tile_step) {
+                const GemmItem w = gemm_item(p, item);
                 int mt, nt;
-                tile_coords(tile, p.m_tiles, p.n_tiles, p.group_m, mt, nt);
+                tile_coords(w.tile, p.m_tiles, p.n_tiles, p.group_m, mt, nt);
                 const int m0 = mt * TILE_M + cta_rank * BM;
                 const int n0 = p.swiglu ? nt * (BN / 2) : nt * BN;
                 const int n1 = p.swiglu ? p.N / 2 + n0 : n0 + BN / 2;
-                for (int kb = 0; kb < p.k_blocks; kb++) {
+                for (int kb = w.kb0; kb < w.kb1; kb++) {
                     if (!mbar_wait(&empty[s], ph ^ 1, abort_word, p.status, H3B_ST_TIMEOUT_EMPTY)) break;
                     uint8_t *a_dst = smem + (size_t)s * STAGE_BYTES;
                     uint8_t *b_dst = a_dst + A_BYTES;
@@ -358,13 +383,14 @@ __global__ void __launch_bounds__(gemm::THREADS, 1) k_gemm_i8(const __grid_const
             int s = 0;
             uint32_t ph = 0;
             int it = 0;
-            for (int tile = first_tile; tile < total_tiles; tile += tile_step, it++) {
+            for (int item = first_tile; item < p.items_total; item += tile_step, it++) {
+                const GemmItem w = gemm_item(p, item);
                 const int buf = it & 1;
                 if (!mbar_wait(&tmem_empty[buf], ((it >> 1) & 1) ^ 1, abort_word, p.status, H3B_ST_TIMEOUT_TMEM_EMPTY))
                     break;
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + (uint32_t)buf * BN;
-                for (int kb = 0; kb < p.k_blocks; kb++) {
+                for (int kb = w.kb0; kb < w.kb1; kb++) {
                     if (!mbar_wait(&full[s], ph, abort_word, p.status, H3B_ST_TIMEOUT_FULL)) break;
                     tc_fence_after();
                     const uint32_t a_addr = smem_u32(smem + (size_t)s * STAGE_BYTES);
@@ -375,10 +401,10 @@ __global__ void __launch_bounds__(gemm::THREADS, 1) k_gemm_i8(const __grid_const
                         for (int k = 0; k < BK / 32; k++) {
                             if (CTAS == 2)
                                 umma_i8_ss_pair(d_tmem, a_desc + (uint64_t)(k * 2), b_desc + (uint64_t)(k * 2), idesc,
-                                                (uint32_t)((kb | k) != 0));
+                                                (uint32_t)(kb != w.kb0 || k != 0));
                             else
                                 umma_i8_ss(d_tmem, a_desc + (uint64_t)(k * 2), b_desc + (uint64_t)(k * 2), idesc,
-                                           (uint32_t)((kb | k) != 0));
+                                           (uint32_t)(kb != w.kb0 || k != 0));
                         }
                         // the stage is free (in both CTAs) once these MMAs have read it
                         if (CTAS == 2) tc_commit_pair(&empty[s], 3);
@@ -411,9 +437,10 @@ __global__ void __launch_bounds__(gemm::THREADS, 1) k_gemm_i8(const __grid_const
         uint32_t res_phase = 0;
         int tab_it = 0;   // tiles of this CTA that used the cos / sin buffer so far
         int it = 0;
-        for (int tile = first_tile; tile < total_tiles; tile += tile_step, it++) {
+        for (int item = first_tile; item < p.items_total; item += tile_step, it++) {
+            const GemmItem w = gemm_item(p, item);
             int mt, nt;
-            tile_coords(tile, p.m_tiles, p.n_tiles, p.group_m, mt, nt);
+            tile_coords(w.tile, p.m_tiles, p.n_tiles, p.group_m, mt, nt);
             const int buf = it & 1;
             const int row0 = mt * TILE_M + cta_rank * BM + q * 32;
             const int row = row0 + lane;
@@ -430,7 +457,8 @@ __global__ void __launch_bounds__(gemm::THREADS, 1) k_gemm_i8(const __grid_const
             uint8_t *tab = tab_stage + (size_t)q * TAB_GROUP;
             if constexpr (QTMA) {
                 const int g0 = c0 >> 7;
-                tile_rope = p.rope_half != 0 && (g0 / p.heads < 2 || (c0 + 128 < p.N && (g0 + 1) / p.heads < 2));
+                // (a slice of a split tile that only adds its sums never rotates anything)
+                tile_rope = p.rope_half != 0 && w.slice == 0 && (g0 / p.heads < 2 || (c0 + 128 < p.N && (g0 + 1) / p.heads < 2));
                 if (tile_rope && half == 0 && lane == 0 &&
                     mbar_wait(&tab_empty[q], (tab_it & 1) ^ 1, abort_word, p.status, H3B_ST_TIMEOUT_EMPTY)) {
                     mbar_expect_tx(&tab_full[q], TAB_GROUP);
@@ -444,6 +472,97 @@ __global__ void __launch_bounds__(gemm::THREADS, 1) k_gemm_i8(const __grid_const
             bool ok = mbar_wait(&tmem_full[buf], (it >> 1) & 1, abort_word, p.status, H3B_ST_TIMEOUT_TMEM_FULL);
             tc_fence_after();
             const uint32_t t_addr = tmem_base + lane_base + (uint32_t)buf * BN;
+            if (w.parts > 1) {
+                // A tail tile cut along K.  Slices 1.. store their int32 sums to their own region of the tile's slot in
+                // global memory and are done; slice 0 waits for them, adds the regions to its accumulator in tensor
+                // memory (integer sums: exact in any order), and then runs the epilogue below as for a whole tile.
+                // Each warp touches exactly the columns its epilogue reads, so no other warp's fold is ever needed.
+                // Regions are [column][row]: a warp's 32 rows of one column are one 128-byte line.  (Adding into
+                // one region with red.global took 17 us per tile whatever the slice count: an SM retires about one
+                // 32-bit reduction per clock.)
+                constexpr unsigned WARPS = 8 * CTAS;
+                constexpr size_t REGION = (size_t)TILE_M * BN;
+                int32_t *slot_acc = p.sk_acc + (size_t)w.slot * (p.split_s - 1) * REGION + cta_rank * BM + q * 32 + lane;
+                unsigned *cnt = p.sk_cnt + 2 * w.slot;
+                if (w.slice != 0) {
+                    if (ok) {
+                        int32_t *mine = slot_acc + (size_t)(w.slice - 1) * REGION;
+#pragma unroll 1
+                        for (int j = 0; j < 4; j++) {
+                            const int col = (EPI == H3B_EPI_SWIGLU) ? (j >> 1) * (BN / 2) + half * 64 + (j & 1) * 32 : half * 128 + j * 32;
+                            uint32_t r[32];
+                            tmem_ld_32x32b_x32(t_addr + col, r);
+                            tmem_ld_wait();
+#pragma unroll
+                            for (int v = 0; v < 32; v++) __stcg(mine + (size_t)(col + v) * TILE_M, (int32_t)r[v]);
+                        }
+                        __threadfence();
+                    }
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) {
+                        if (CTAS == 2) mbar_arrive_cluster(mapa_shared(smem_u32(&tmem_empty[buf]), 0));
+                        else mbar_arrive(&tmem_empty[buf]);
+                        if (ok) atomicAdd(cnt, 1u);
+                    }
+                    if (*abort_word) break;
+                    continue;
+                }
+                if (ok && lane == 0) {
+                    const unsigned want = (unsigned)(w.parts - 1) * WARPS;
+                    const long long start = clock64();
+                    unsigned seen;
+                    while (true) {
+                        asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(seen) : "l"(cnt) : "memory");
+                        if (seen >= want || *abort_word) break;
+                        if (clock64() - start > H3B_WAIT_CYCLES) {
+                            *abort_word = H3B_ST_TIMEOUT_OTHER;
+                            if (p.status) atomicCAS(p.status, 0, H3B_ST_TIMEOUT_OTHER);
+                            break;
+                        }
+                        __nanosleep(100);
+                    }
+                    ok = seen >= want;
+                }
+                ok = __shfl_sync(0xffffffffu, (int)ok, 0) != 0;
+                if (ok) {
+#pragma unroll 1
+                    for (int j = 0; j < 4; j++) {
+                        const int col = (EPI == H3B_EPI_SWIGLU) ? (j >> 1) * (BN / 2) + half * 64 + (j & 1) * 32 : half * 128 + j * 32;
+                        uint32_t r[32];
+                        tmem_ld_32x32b_x32(t_addr + col, r);
+                        tmem_ld_wait();
+                        // three regions' loads are in flight together (96 per thread) before the first add needs one
+                        const int32_t *theirs = slot_acc + (size_t)col * TILE_M;
+                        int sl = 0;
+#pragma unroll 1
+                        for (; sl + 3 <= w.parts - 1; sl += 3) {
+                            int32_t t0[32], t1[32], t2[32];
+#pragma unroll
+                            for (int v = 0; v < 32; v++) {
+                                t0[v] = __ldcg(theirs + (size_t)sl * REGION + (size_t)v * TILE_M);
+                                t1[v] = __ldcg(theirs + (size_t)(sl + 1) * REGION + (size_t)v * TILE_M);
+                                t2[v] = __ldcg(theirs + (size_t)(sl + 2) * REGION + (size_t)v * TILE_M);
+                            }
+#pragma unroll
+                            for (int v = 0; v < 32; v++) r[v] += (uint32_t)(t0[v] + t1[v] + t2[v]);
+                        }
+#pragma unroll 1
+                        for (; sl < w.parts - 1; sl++) {
+#pragma unroll
+                            for (int v = 0; v < 32; v++) r[v] += (uint32_t)__ldcg(theirs + (size_t)sl * REGION + (size_t)v * TILE_M);
+                        }
+                        tmem_st_32x32b_x32(t_addr + col, r);
+                    }
+                    tmem_st_wait();
+                    __syncwarp();
+                    // the last of the owner's warps leaves the counters at zero for the next launch
+                    if (lane == 0 && atomicAdd(cnt + 1, 1u) == WARPS - 1) {
+                        cnt[0] = 0;
+                        cnt[1] = 0;
+                    }
+                }
+            }
             if constexpr (EPI == H3B_EPI_QKV_ROPE || EPI == EPI_QKV_ROPE_SCATTER) {
                 // This warp's 128 columns are exactly one head of Q, K or V; the thread holds its row of it.
                 const int col = c0 + half * 128;
@@ -775,6 +894,44 @@ static int gemm_launch_t(h3_cuda *cuda, GemmParams &p, char *error, size_t error
         const int tiles = p.m_tiles * p.n_tiles;
         const int n_pairs = tiles < max_pairs[dev] ? tiles : max_pairs[dev];
         cfg.gridDim = dim3((unsigned)(2 * n_pairs));
+        // A last wave that fills at most half of the pairs can be cut along K: its `rem` tiles become rem * S slices, one
+        // per pair; slices 1.. store their int32 sums to global memory, slice 0 adds them to its accumulator and runs the
+        // epilogue.  Storing, signalling, the fold and its extra pass through tensor memory cost about 10 us plus 2 us
+        // per region read; a k-block of MMAs saved is 0.39 us.  S minimises T/S + 2 (S - 1) for a tile of T us, and the
+        // tail is cut only where the estimate gains 8 us or more.  In the sharded step that is the K = 12288 projection
+        // (6,280 rows x 3,072 columns: 300 tiles on 74 pairs are 4 waves and 4 tiles): 172.2 -> 165.2 us with three or
+        // four slices, 320.3 -> 313.4 at 12,560 rows, 616.5 -> 607.7 at 25,110; forced on the K = 3072 projections it
+        // loses 6 us.  H3B_GEMM_SPLITK=0 keeps whole tiles, a value of 2 or more forces that many slices.  The slot
+        // memory belongs to the handle: one GEMM at a time per handle, as the op stream orders them.
+        p.items_total = tiles; p.tail_first = tiles; p.split_s = 1;
+        const int rem = tiles % n_pairs;
+        const int sk_mode = atoi(h3_plugin_value("H3B_GEMM_SPLITK"));
+        if (tiles > n_pairs && rem > 0 && 2 * rem <= n_pairs && sk_mode > 0) {
+            int split = sk_mode;
+            if (sk_mode == 1) {
+                const double t_tile = 0.39 * p.k_blocks, fold = 2.0;
+                split = (int)(sqrt(t_tile / fold) + 0.5);
+                if (split >= 2 && t_tile - t_tile / split - fold * (split - 1) < 8.0) split = 1;
+            }
+            if (split > n_pairs / rem) split = n_pairs / rem;
+            if (split > p.k_blocks / 2) split = p.k_blocks / 2;
+            if (split > 16) split = 16;
+            const size_t need = SPLITK_CNT_BYTES + (size_t)max_pairs[dev] * Shape<2, EPI>::TILE_M * BN * sizeof(int32_t);
+            if (split >= 2 && cuda->splitk_bytes < need && !cuda->graph_capture) {
+                if (cuda->splitk) cudaFree(cuda->splitk);
+                cuda->splitk = nullptr; cuda->splitk_bytes = 0;
+                H3B_CUDA_OK(cudaMalloc(&cuda->splitk, need), "cudaMalloc(split-K slots)");
+                cuda->splitk_bytes = need;
+                H3B_CUDA_OK(cudaMemsetAsync(cuda->splitk, 0, need, cuda->op_stream), "cudaMemsetAsync(split-K slots)");
+            }
+            if (split >= 2 && cuda->splitk_bytes >= need) {
+                p.split_s = split;
+                p.tail_first = tiles - rem;
+                p.items_total = p.tail_first + rem * split;
+                p.sk_cnt = reinterpret_cast<unsigned *>(cuda->splitk);
+                p.sk_acc = reinterpret_cast<int32_t *>(reinterpret_cast<uint8_t *>(cuda->splitk) + SPLITK_CNT_BYTES);
+            }
+        }
         ProfScope prof(cuda, PROF_GEMM);
         H3B_CUDA_OK(cudaLaunchKernelEx(&cfg, kern, p), "k_gemm_i8 pair launch");
         cuda->launches++;
@@ -785,6 +942,7 @@ static int gemm_launch_t(h3_cuda *cuda, GemmParams &p, char *error, size_t error
                 "gemm smem attribute");
     int tiles = p.m_tiles * p.n_tiles;
     int grid = tiles < cuda->sm_count ? tiles : cuda->sm_count;
+    p.items_total = tiles; p.tail_first = tiles; p.split_s = 1;
     ProfScope prof(cuda, PROF_GEMM);
     kern<<<grid, THREADS, Shape<1, EPI>::SMEM_BYTES, cuda->op_stream>>>(p);
     cuda->launches++;

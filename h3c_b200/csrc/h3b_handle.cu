@@ -201,10 +201,10 @@ void h3_cuda_release_heavy_workspace(h3_cuda *cuda) {
     if (!cuda) return;
     cudaSetDevice(cuda->device);
     cudaStreamSynchronize(cuda->op_stream);
-    void **slots[] = {&cuda->act_q, &cuda->act_s, &cuda->act_rot, &cuda->attn, &cuda->rq, &cuda->kvx, &cuda->wtmp};
+    void **slots[] = {&cuda->act_q, &cuda->act_s, &cuda->act_rot, &cuda->attn, &cuda->rq, &cuda->kvx, &cuda->wtmp, &cuda->splitk};
     size_t *sizes[] = {&cuda->act_q_bytes, &cuda->act_s_bytes, &cuda->act_rot_bytes, &cuda->attn_bytes, &cuda->rq_bytes,
-                       &cuda->kvx_bytes, &cuda->wtmp_bytes};
-    for (int i = 0; i < 7; i++) {
+                       &cuda->kvx_bytes, &cuda->wtmp_bytes, &cuda->splitk_bytes};
+    for (int i = 0; i < 8; i++) {
         if (*slots[i]) cudaFree(*slots[i]);
         *slots[i] = NULL;
         *sizes[i] = 0;

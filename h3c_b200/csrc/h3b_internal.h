@@ -29,6 +29,8 @@ struct h3_cuda {
     void *rq;      size_t rq_bytes;        // codes + scales handed out by h3_cuda_epi_fuse_ink_prep_fc2
     void *kvx;     size_t kvx_bytes;       // K/V with bound history appended (h3_cuda_sdpa_bind_kvcat)
     void *wtmp;    size_t wtmp_bytes;      // f32 copy of 16-bit weights (mixed-precision dense GEMM)
+    void *splitk;  size_t splitk_bytes;    // int32 sums + counters of the int8 GEMM's split tail tiles (the counters are
+                                           // zero between launches: the kernel that uses them resets them)
     int blas_side;                         // f32 GEMMs run on side[1] (h3_cuda_cublas_use_side)
     int pregrown;
     // optional per-launch timing (h3b_cuda_profile_begin / _end)

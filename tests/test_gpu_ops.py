@@ -250,6 +250,46 @@ def test_gemm_epilogues(cuda, oracle, m):
     cuda.check()
 
 
+@pytest.mark.parametrize("m,n,k", [(6280, 3072, 3072), (2560, 2048, 512), (6280, 9216, 512)])
+def test_gemm_split_tail_tiles(cuda, oracle, m, n, k, monkeypatch):
+    """A last wave that fills at most half of the CTA pairs can be cut along K (on 74 pairs: 300 tiles = 4 waves + 4 tiles;
+    80 tiles = 1 wave + 6; 900 tiles = 12 waves + 12).  Int32 sums are exact in any order, so every epilogue gives the
+    bits of the whole-tile form, call after call (the slots are left cleared)."""
+    import h3c_b200
+    rng = np.random.default_rng(m + n)
+    w, w_i8, s = make_weight(cuda, rng, n, k)
+    x = rng.integers(-127, 128, (m, k), dtype=np.int8)
+    xs = rng.uniform(0.005, 0.02, m).astype(np.float32)
+    dq, ds = dev(x), dev(xs)
+    res = dev(rng.normal(0, 1, (m, n)).astype(np.float32), torch.bfloat16)
+    heads = n // 384
+    qn = dev(rng.normal(1, 0.1, 128).astype(np.float32))
+    cos, sin = dev(rng.random((m, 64)).astype(np.float32)), dev(rng.random((m, 64)).astype(np.float32))
+
+    def run_all():
+        out = [cuda.gemm_i8(w, dq, torch.ones_like(ds), out_dtype=torch.int32),
+               cuda.gemm_i8(w, dq, ds, out_dtype=torch.bfloat16),
+               cuda.gemm_i8(w, dq, ds, kind=h3c_b200.EPI_GATE, residual=res, out_dtype=torch.bfloat16),
+               cuda.gemm_i8(w, dq, ds, kind=h3c_b200.EPI_GELU, out_dtype=torch.bfloat16),
+               cuda.gemm_i8(w, dq, ds, kind=h3c_b200.EPI_SWIGLU, out_dtype=torch.bfloat16),
+               cuda.gemm_i8(w, dq, ds, kind=h3c_b200.EPI_SWIGLU)]
+        if n == heads * 384:
+            out += list(cuda.gemm_i8_qkv_rope(w, dq, ds, qn, qn, cos, sin, 64))
+        cuda.check()
+        return out
+
+    monkeypatch.setenv("H3B_GEMM_SPLITK", "0")
+    whole = run_all()
+    for mode in ("1", "12", "3"):   # the library's own choice, and forced slice counts
+        monkeypatch.setenv("H3B_GEMM_SPLITK", mode)
+        for _ in range(2):
+            for a, b in zip(run_all(), whole):
+                assert torch.equal(a, b)
+    rows = np.unique(np.concatenate([[0, 127, 128, 255, 256, m - 1, m - 2, (m - 1) // 256 * 256], rng.integers(0, m, 8)]))
+    want = x[rows].astype(np.int32) @ w_i8.astype(np.int32).T
+    assert np.array_equal(host(whole[0][torch.from_numpy(rows).cuda()]), want)
+
+
 def test_gemm_qkv_rope_epilogue(cuda, oracle):
     """QKV projection with the QK-norm and split-half RoPE fused into the GEMM epilogue, against the oracle
     chain dequant -> (round to bf16) -> h3_dit_w4a8_qkv_rope_f32."""
