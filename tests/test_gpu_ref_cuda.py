@@ -192,7 +192,7 @@ def test_timing_table_against_reference_cuda(cuda, tmp_path):
     """Not a parity check: times the reference's cuBLASLt int8 linear, its cuBLASLt FP4 GEMM and its attention
     (in-tree flash, and cuDNN where the library is present) beside this library's kernels on the benchmark's
     shapes, same box, same process lifetime, CUDA events around whole calls (median of 10), and writes
-    gpurun_out/ref_cuda_timing.json.  The summary under profiles/ is made from that file."""
+    ref_cuda_timing.json into the run's output folder (H3_TIMING_OUT, default: the folder a GPU run brings back)."""
     import h3c_b200
     shapes = [(m, k, n) for m in (6144, 24576, 50220) for k, n in ((3072, 9216), (3072, 3072), (3072, 12288), (12288, 3072))]
     table = {"linear": [], "attention": [], "fp4": []}
@@ -276,7 +276,7 @@ def test_timing_table_against_reference_cuda(cuda, tmp_path):
         e1.synchronize()
         row["ours_back_to_back_ms"] = e0.elapsed_time(e1) / 30
         table["fp4"].append(row)
-    out_dir = ROOT / "gpurun_out"
+    out_dir = Path(os.environ.get("H3_TIMING_OUT", ROOT / "gpurun_out"))
     out_dir.mkdir(exist_ok=True)
     (out_dir / "ref_cuda_timing.json").write_text(json.dumps(table, indent=1))
     print(json.dumps(table, indent=1))
