@@ -374,9 +374,26 @@ class Cuda:
         import numpy as np
         packed = np.ascontiguousarray(packed, np.uint8)
         sf = np.ascontiguousarray(sf, np.uint8)
+        # The constructor owns its two host buffers once it has succeeded and releases them with free()
+        # (h3_gpu_cuda.h:437-444): it gets malloc'ed copies, never numpy's memory.
+        libc = C.CDLL(None)
+        libc.malloc.restype, libc.malloc.argtypes, libc.free.argtypes = C.c_void_p, [C.c_size_t], [C.c_void_p]
+        bufs = []
+        for a in (packed, sf):
+            ptr = libc.malloc(max(a.nbytes, 1))
+            if not ptr:
+                for b in bufs:
+                    libc.free(b)
+                raise MemoryError("nvfp4_weight: host staging")
+            C.memmove(ptr, a.ctypes.data, a.nbytes)
+            bufs.append(ptr)
         h = C.c_void_p()
-        call("h3_cuda_nvfp4_weight_create", self.h, packed.ctypes.data, sf.ctypes.data, float(scale2), n, k, C.byref(h),
-             None)
+        try:
+            call("h3_cuda_nvfp4_weight_create", self.h, bufs[0], bufs[1], float(scale2), n, k, C.byref(h), None)
+        except Exception:
+            for b in bufs:   # on failure the caller keeps them
+                libc.free(b)
+            raise
         return h.value
 
     def nvfp4_weight_free(self, handle):

@@ -56,8 +56,10 @@ struct h3b_dit {
     uint32_t *st_map;
     float *st_cos, *st_sin, *st_t;
     h3_ulysses_cfg *uly;    /* attached per-rank communicator, or NULL */
-    h3_cuda_w4a8_weight **owned;   /* weights created by the checkpoint loader, freed with the context */
+    h3_cuda_w4a8_weight **owned;   /* weights created by the checkpoint loaders, freed with the context */
     size_t n_owned, cap_owned;
+    h3_cuda_nvfp4_weight **owned_fp4;
+    size_t n_owned_fp4, cap_owned_fp4;
     /* the chain captured as one CUDA graph (h3b_dit_layers_forward_graph_dev) and what it was captured for */
     cudaGraph_t graph;
     cudaGraphExec_t graph_exec;
@@ -187,6 +189,8 @@ void h3b_dit_free(h3b_dit *d) {
     }
     for (b = 0; b < d->n_owned; b++) h3_cuda_w4a8_weight_free(d->owned[b]);
     free(d->owned);
+    for (b = 0; b < d->n_owned_fp4; b++) h3_cuda_nvfp4_weight_free(d->cuda, d->owned_fp4[b]);
+    free(d->owned_fp4);
     free(d->blocks);
     free(d);
 }
@@ -279,53 +283,40 @@ static const float *ckpt_f32(const h3b_ckpt *c, const char *name, size_t count, 
     return (const float *)t.data;
 }
 
-int h3b_dit_load_int8_convrot_block(h3b_dit *d, const h3b_ckpt *ckpt, unsigned src_block, unsigned dst_block,
-                                    char *error, size_t error_size) {
-    static const char *suffix[4] = {"attn.qkv_proj", "attn.out_proj", "mlp.fc1", "mlp.fc2"};
-    static const int slot[4] = {H3B_LIN_QKV, H3B_LIN_OUT, H3B_LIN_FC1, H3B_LIN_FC2};
+/* The four linears of a block under the reference's names, their slots and shapes [n, k]. */
+static const char *const ckpt_suffix[4] = {"attn.qkv_proj", "attn.out_proj", "mlp.fc1", "mlp.fc2"};
+static const int ckpt_slot[4] = {H3B_LIN_QKV, H3B_LIN_OUT, H3B_LIN_FC1, H3B_LIN_FC2};
+static void ckpt_linear_shapes(const h3b_dit *d, size_t n[4], size_t k[4]) {
+    const size_t D = d->cfg.dim, I = inner(d), F = d->cfg.ffn;
+    n[0] = 3 * I; k[0] = D;
+    n[1] = D;     k[1] = I;
+    n[2] = 2 * F; k[2] = D;
+    n[3] = D;     k[3] = F;
+}
+
+/* Keeps a weight the loader created until the context is freed; on failure the weight is freed here. */
+static int own_weight(h3b_dit *d, h3_cuda_w4a8_weight *obj, char *error, size_t error_size) {
+    if (d->n_owned == d->cap_owned) {
+        size_t ncap = d->cap_owned ? 2 * d->cap_owned : 16;
+        h3_cuda_w4a8_weight **no = (h3_cuda_w4a8_weight **)realloc(d->owned, ncap * sizeof(*no));
+        if (!no) {
+            h3_cuda_w4a8_weight_free(obj);
+            return fail(error, error_size, "checkpoint loader: out of host memory");
+        }
+        d->owned = no;
+        d->cap_owned = ncap;
+    }
+    d->owned[d->n_owned++] = obj;
+    return 1;
+}
+
+/* Norm weights, QK-norm weights and (optional) adaLN projection of a block: the same names in all three checkpoint
+ * formats (h3_dit_w4a8.c:2056-2104). */
+static int load_block_aux_from_ckpt(h3b_dit *d, const h3b_ckpt *ckpt, unsigned src_block, unsigned dst_block, char *error,
+                                    size_t error_size) {
     char name[256];
     const float *n1, *n2, *qn, *kn, *aw, *ab;
-    size_t D, I, F, mod;
-    int l;
-    if (!d || !ckpt || dst_block >= d->cfg.n_blocks) return fail(error, error_size, "load_int8_convrot_block: invalid arguments");
-    if (d->cfg.kind != H3B_BLOCK_REFERENCE)
-        return fail(error, error_size, "load_int8_convrot_block: the INT8-ConvRot checkpoint holds the reference block");
-    D = d->cfg.dim; I = inner(d); F = d->cfg.ffn; mod = d->cfg.mod_rows * 6 * D;
-    for (l = 0; l < 4; l++) {
-        const size_t want_n[4] = {3 * I, D, 2 * F, D}, want_k[4] = {D, I, D, F};
-        h3b_ckpt_tensor w, s;
-        h3_cuda_w4a8_weight *obj = NULL;
-        snprintf(name, sizeof(name), "blocks.%u.%s.weight", src_block, suffix[l]);
-        if (!h3b_ckpt_find(ckpt, name, &w)) return fail(error, error_size, "checkpoint: tensor %s missing", name);
-        if (strcmp(w.dtype, "I8") != 0 || w.rank != 2 || w.shape[0] != want_n[l] || w.shape[1] != want_k[l])
-            return fail(error, error_size, "checkpoint: %s is %s rank %d [%zu, %zu], expected I8 [%zu, %zu]", name, w.dtype,
-                        w.rank, w.shape[0], w.rank > 1 ? w.shape[1] : 0, want_n[l], want_k[l]);
-        snprintf(name, sizeof(name), "blocks.%u.%s.weight_scale", src_block, suffix[l]);
-        if (!h3b_ckpt_find(ckpt, name, &s)) return fail(error, error_size, "checkpoint: tensor %s missing", name);
-        if (strcmp(s.dtype, "F32") != 0 || s.bytes != want_n[l] * sizeof(float))
-            return fail(error, error_size, "checkpoint: %s must be F32 with one scale per output row", name);
-        /* the mapping is borrowed for the upload only: it has completed when ensure_ready returns, so the caller may
-         * close the checkpoint right after this call */
-        if (!h3_cuda_w4a8_weight_create_from_i8(d->cuda, (int8_t *)(uintptr_t)w.data, want_n[l], want_k[l],
-                                                (float *)(uintptr_t)s.data, &obj, NULL, 1, error, error_size))
-            return 0;
-        if (!h3_cuda_w4a8_weight_ensure_ready(obj, error, error_size)) {
-            h3_cuda_w4a8_weight_free(obj);
-            return 0;
-        }
-        if (d->n_owned == d->cap_owned) {
-            size_t ncap = d->cap_owned ? 2 * d->cap_owned : 16;
-            h3_cuda_w4a8_weight **no = (h3_cuda_w4a8_weight **)realloc(d->owned, ncap * sizeof(*no));
-            if (!no) {
-                h3_cuda_w4a8_weight_free(obj);
-                return fail(error, error_size, "load_int8_convrot_block: out of host memory");
-            }
-            d->owned = no;
-            d->cap_owned = ncap;
-        }
-        d->owned[d->n_owned++] = obj;
-        if (!h3b_dit_set_linear(d, dst_block, slot[l], obj, error, error_size)) return 0;
-    }
+    const size_t D = d->cfg.dim, mod = d->cfg.mod_rows * 6 * D;
     snprintf(name, sizeof(name), "blocks.%u.norm1.weight", src_block);
     if (!(n1 = ckpt_f32(ckpt, name, D, error, error_size))) return 0;
     snprintf(name, sizeof(name), "blocks.%u.norm2.weight", src_block);
@@ -341,6 +332,154 @@ int h3b_dit_load_int8_convrot_block(h3b_dit *d, const h3b_ckpt *ckpt, unsigned s
         snprintf(name, sizeof(name), "blocks.%u.adaln_proj.linear.bias", src_block);
         if (!(ab = ckpt_f32(ckpt, name, mod, error, error_size))) return 0;
         if (!h3b_dit_set_adaln(d, dst_block, aw, ab, error, error_size)) return 0;
+    }
+    return 1;
+}
+
+int h3b_dit_load_int8_convrot_block(h3b_dit *d, const h3b_ckpt *ckpt, unsigned src_block, unsigned dst_block,
+                                    char *error, size_t error_size) {
+    char name[256];
+    size_t want_n[4], want_k[4];
+    int l;
+    if (!d || !ckpt || dst_block >= d->cfg.n_blocks) return fail(error, error_size, "load_int8_convrot_block: invalid arguments");
+    if (d->cfg.kind != H3B_BLOCK_REFERENCE)
+        return fail(error, error_size, "load_int8_convrot_block: the INT8-ConvRot checkpoint holds the reference block");
+    ckpt_linear_shapes(d, want_n, want_k);
+    for (l = 0; l < 4; l++) {
+        h3b_ckpt_tensor w, s;
+        h3_cuda_w4a8_weight *obj = NULL;
+        snprintf(name, sizeof(name), "blocks.%u.%s.weight", src_block, ckpt_suffix[l]);
+        if (!h3b_ckpt_find(ckpt, name, &w)) return fail(error, error_size, "checkpoint: tensor %s missing", name);
+        if (strcmp(w.dtype, "I8") != 0 || w.rank != 2 || w.shape[0] != want_n[l] || w.shape[1] != want_k[l])
+            return fail(error, error_size, "checkpoint: %s is %s rank %d [%zu, %zu], expected I8 [%zu, %zu]", name, w.dtype,
+                        w.rank, w.shape[0], w.rank > 1 ? w.shape[1] : 0, want_n[l], want_k[l]);
+        snprintf(name, sizeof(name), "blocks.%u.%s.weight_scale", src_block, ckpt_suffix[l]);
+        if (!h3b_ckpt_find(ckpt, name, &s)) return fail(error, error_size, "checkpoint: tensor %s missing", name);
+        if (strcmp(s.dtype, "F32") != 0 || s.bytes != want_n[l] * sizeof(float))
+            return fail(error, error_size, "checkpoint: %s must be F32 with one scale per output row", name);
+        /* the mapping is borrowed for the upload only: it has completed when ensure_ready returns, so the caller may
+         * close the checkpoint right after this call */
+        if (!h3_cuda_w4a8_weight_create_from_i8(d->cuda, (int8_t *)(uintptr_t)w.data, want_n[l], want_k[l],
+                                                (float *)(uintptr_t)s.data, &obj, NULL, 1, error, error_size))
+            return 0;
+        if (!h3_cuda_w4a8_weight_ensure_ready(obj, error, error_size)) {
+            h3_cuda_w4a8_weight_free(obj);
+            return 0;
+        }
+        if (!own_weight(d, obj, error, error_size)) return 0;
+        if (!h3b_dit_set_linear(d, dst_block, ckpt_slot[l], obj, error, error_size)) return 0;
+    }
+    return load_block_aux_from_ckpt(d, ckpt, src_block, dst_block, error, error_size);
+}
+
+/* The reference's W4A8 checkpoint (h3_w4a8.c:75-115): per linear `weight` I8 [n, k/2] (two codes per byte, low
+ * nibble = even k), `weight_codebook` F32[16], `weight_s_rel` F8_E4M3 [n, k/16], `weight_s_channel` F32[n].  Decoded
+ * on the device to the resident INT8 form by the reference's own rule (h3_w4a8_dequant.c:65-118). */
+int h3b_dit_load_w4a8_block(h3b_dit *d, const h3b_ckpt *ckpt, unsigned src_block, unsigned dst_block, char *error,
+                            size_t error_size) {
+    char name[256];
+    size_t want_n[4], want_k[4];
+    int l;
+    if (!d || !ckpt || dst_block >= d->cfg.n_blocks) return fail(error, error_size, "load_w4a8_block: invalid arguments");
+    if (d->cfg.kind != H3B_BLOCK_REFERENCE)
+        return fail(error, error_size, "load_w4a8_block: the W4A8 checkpoint holds the reference block");
+    ckpt_linear_shapes(d, want_n, want_k);
+    for (l = 0; l < 4; l++) {
+        const size_t n = want_n[l], k = want_k[l];
+        h3b_ckpt_tensor w, cb, sr, sc;
+        h3_cuda_w4a8_weight *obj = NULL;
+        if (k % 16) return fail(error, error_size, "load_w4a8_block: K = %zu is not a multiple of the 16-wide scale group", k);
+        snprintf(name, sizeof(name), "blocks.%u.%s.weight", src_block, ckpt_suffix[l]);
+        if (!h3b_ckpt_find(ckpt, name, &w)) return fail(error, error_size, "checkpoint: tensor %s missing", name);
+        if (strcmp(w.dtype, "I8") != 0 || w.rank != 2 || w.shape[0] != n || w.shape[1] != k / 2)
+            return fail(error, error_size, "checkpoint: %s is %s rank %d [%zu, %zu], expected packed I8 [%zu, %zu]", name,
+                        w.dtype, w.rank, w.shape[0], w.rank > 1 ? w.shape[1] : 0, n, k / 2);
+        snprintf(name, sizeof(name), "blocks.%u.%s.weight_codebook", src_block, ckpt_suffix[l]);
+        if (!h3b_ckpt_find(ckpt, name, &cb)) return fail(error, error_size, "checkpoint: tensor %s missing", name);
+        if (strcmp(cb.dtype, "F32") != 0 || cb.rank != 1 || cb.shape[0] != 16)
+            return fail(error, error_size, "checkpoint: %s must be F32[16]", name);
+        snprintf(name, sizeof(name), "blocks.%u.%s.weight_s_rel", src_block, ckpt_suffix[l]);
+        if (!h3b_ckpt_find(ckpt, name, &sr)) return fail(error, error_size, "checkpoint: tensor %s missing", name);
+        if (strcmp(sr.dtype, "F8_E4M3") != 0 || sr.bytes != n * (k / 16))
+            return fail(error, error_size, "checkpoint: %s must be F8_E4M3 [%zu, %zu]", name, n, k / 16);
+        snprintf(name, sizeof(name), "blocks.%u.%s.weight_s_channel", src_block, ckpt_suffix[l]);
+        if (!h3b_ckpt_find(ckpt, name, &sc)) return fail(error, error_size, "checkpoint: tensor %s missing", name);
+        if (strcmp(sc.dtype, "F32") != 0 || sc.bytes != n * sizeof(float))
+            return fail(error, error_size, "checkpoint: %s must be F32 with one scale per output row", name);
+        /* the constructor copies from the mapping and returns with the decode queued behind the copies */
+        if (!h3_cuda_w4a8_weight_create(d->cuda, (const int8_t *)w.data, n, k / 2, (const float *)cb.data,
+                                        (const uint8_t *)sr.data, (const float *)sc.data, 16, &obj, NULL, NULL, error,
+                                        error_size))
+            return 0;
+        if (!h3_cuda_w4a8_weight_ensure_ready(obj, error, error_size)) {
+            h3_cuda_w4a8_weight_free(obj);
+            return 0;
+        }
+        if (!own_weight(d, obj, error, error_size)) return 0;
+        if (!h3b_dit_set_linear(d, dst_block, ckpt_slot[l], obj, error, error_size)) return 0;
+    }
+    return load_block_aux_from_ckpt(d, ckpt, src_block, dst_block, error, error_size);
+}
+
+/* The reference's NVFP4 sidecar (h3_dit_w4a8.c:3158-3274): per linear `weight_fp4` U8 [n, k/2], `weight_sf` U8 (the
+ * 128x4-blocked UE4M3 scales, h3_cuda_nvfp4_sf_bytes(n, k) bytes) and an optional F32 scalar `weight_scale2` (1 when
+ * absent).  `linears` is a mask of the linears to take from the sidecar (bit 0 QKV, 1 OUT, 2 FC1, 3 FC2: the
+ * reference's per-linear NVFP4 / INT8 choice); a linear that is absent from the file is an error if its bit is set.
+ * Norms and the adaLN projection are not part of a sidecar: load them from the checkpoint it accompanies. */
+int h3b_dit_load_nvfp4_block(h3b_dit *d, const h3b_ckpt *sidecar, unsigned src_block, unsigned dst_block, unsigned linears,
+                             char *error, size_t error_size) {
+    char name[256];
+    size_t want_n[4], want_k[4];
+    int l;
+    if (!d || !sidecar || dst_block >= d->cfg.n_blocks || !(linears & 15u))
+        return fail(error, error_size, "load_nvfp4_block: invalid arguments");
+    ckpt_linear_shapes(d, want_n, want_k);
+    for (l = 0; l < 4; l++) {
+        const size_t n = want_n[l], k = want_k[l], w_bytes = n * (k / 2), sf_bytes = h3_cuda_nvfp4_sf_bytes(n, k);
+        h3b_ckpt_tensor w, sf, s2;
+        h3_cuda_nvfp4_weight *obj = NULL;
+        uint8_t *h_w, *h_sf;
+        float scale2 = 1.0f;
+        if (!(linears & (1u << l))) continue;
+        snprintf(name, sizeof(name), "blocks.%u.%s.weight_fp4", src_block, ckpt_suffix[l]);
+        if (!h3b_ckpt_find(sidecar, name, &w)) return fail(error, error_size, "nvfp4 sidecar: tensor %s missing", name);
+        if (w.bytes != w_bytes) return fail(error, error_size, "nvfp4 sidecar %s size mismatch: %zu bytes, expected %zu", name, w.bytes, w_bytes);
+        snprintf(name, sizeof(name), "blocks.%u.%s.weight_sf", src_block, ckpt_suffix[l]);
+        if (!h3b_ckpt_find(sidecar, name, &sf)) return fail(error, error_size, "nvfp4 sidecar: tensor %s missing", name);
+        if (sf.bytes != sf_bytes) return fail(error, error_size, "nvfp4 sidecar %s size mismatch: %zu bytes, expected %zu", name, sf.bytes, sf_bytes);
+        snprintf(name, sizeof(name), "blocks.%u.%s.weight_scale2", src_block, ckpt_suffix[l]);
+        if (h3b_ckpt_find(sidecar, name, &s2)) {
+            if (strcmp(s2.dtype, "F32") != 0 || s2.bytes != sizeof(float))
+                return fail(error, error_size, "nvfp4 sidecar: %s must be one F32", name);
+            memcpy(&scale2, s2.data, sizeof(float));
+        }
+        /* the constructor owns its two host buffers once it has succeeded (h3_gpu_cuda.h:437-444): hand it copies */
+        h_w = (uint8_t *)malloc(w_bytes);
+        h_sf = (uint8_t *)malloc(sf_bytes);
+        if (!h_w || !h_sf) {
+            free(h_w);
+            free(h_sf);
+            return fail(error, error_size, "load_nvfp4_block: out of host memory");
+        }
+        memcpy(h_w, w.data, w_bytes);
+        memcpy(h_sf, sf.data, sf_bytes);
+        if (!h3_cuda_nvfp4_weight_create(d->cuda, h_w, h_sf, scale2, n, k, &obj, NULL, error, error_size)) {
+            free(h_w);
+            free(h_sf);
+            return 0;
+        }
+        if (d->n_owned_fp4 == d->cap_owned_fp4) {
+            size_t ncap = d->cap_owned_fp4 ? 2 * d->cap_owned_fp4 : 16;
+            h3_cuda_nvfp4_weight **no = (h3_cuda_nvfp4_weight **)realloc(d->owned_fp4, ncap * sizeof(*no));
+            if (!no) {
+                h3_cuda_nvfp4_weight_free(d->cuda, obj);
+                return fail(error, error_size, "load_nvfp4_block: out of host memory");
+            }
+            d->owned_fp4 = no;
+            d->cap_owned_fp4 = ncap;
+        }
+        d->owned_fp4[d->n_owned_fp4++] = obj;
+        if (!h3b_dit_set_linear_nvfp4(d, dst_block, ckpt_slot[l], obj, error, error_size)) return 0;
     }
     return 1;
 }

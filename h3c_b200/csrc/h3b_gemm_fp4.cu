@@ -804,13 +804,17 @@ int h3_cuda_nvfp4_weight_create(h3_cuda *cuda, const uint8_t *packed_host, const
     cudaMemcpyAsync(w->d_packed, packed_host, n * k / 2, cudaMemcpyHostToDevice, cuda->op_stream);
     cudaMemcpyAsync(w->d_sf, sf_swizzled_host, sfb, cudaMemcpyHostToDevice, cuda->op_stream);
     t.stop();
-    cudaError_t e = cudaStreamSynchronize(cuda->op_stream);   // host buffers may be released by the caller
+    cudaError_t e = cudaStreamSynchronize(cuda->op_stream);
     if (e != cudaSuccess) {
         cudaFree(w->d_packed);
         cudaFree(w->d_sf);
         free(w);
-        return cuda_fail(e, "nvfp4_weight_create: upload", error, error_size);
+        return cuda_fail(e, "nvfp4_weight_create: upload", error, error_size);   // the caller keeps its buffers
     }
+    // On success the two host buffers belong to the library (h3_gpu_cuda.h:437-444): the copies have completed, so
+    // they are released here; the reference's loaders malloc them and never free them after a successful call.
+    free(const_cast<uint8_t *>(packed_host));
+    free(const_cast<uint8_t *>(sf_swizzled_host));
     *out = w;
     return 1;
 }

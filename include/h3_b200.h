@@ -713,6 +713,19 @@ int h3b_ckpt_find(const h3b_ckpt *ckpt, const char *name, h3b_ckpt_tensor *out);
  * are uploaded as h3_dit_w4a8_load_block_aux_hdr reads them (h3_dit_w4a8.c:2056-2117). */
 int h3b_dit_load_int8_convrot_block(h3b_dit *dit, const h3b_ckpt *ckpt, unsigned src_block, unsigned dst_block,
                                     char *error, size_t error_size);
+/* The same for the reference's W4A8 checkpoint (h3_w4a8.c:75-115): per linear `weight` I8 [n, k/2] (two 4-bit codes per
+ * byte), `weight_codebook` F32[16], `weight_s_rel` F8_E4M3 [n, k/16] and `weight_s_channel` F32[n], decoded on the
+ * device by the reference's rule (h3_w4a8_dequant.c:65-118) into resident INT8 weights owned by the context; norms and
+ * adaLN projection as above. */
+int h3b_dit_load_w4a8_block(h3b_dit *dit, const h3b_ckpt *ckpt, unsigned src_block, unsigned dst_block, char *error,
+                            size_t error_size);
+/* The reference's NVFP4 sidecar (h3_dit_w4a8.c:3158-3274): per linear `weight_fp4` U8 [n, k/2], `weight_sf` (the
+ * 128x4-blocked UE4M3 scales, h3_cuda_nvfp4_sf_bytes(n, k) bytes) and an optional F32 scalar `weight_scale2`.
+ * `linears` is the mask of linears to take from it (bit 0 QKV, 1 OUT, 2 FC1, 3 FC2); they become NVFP4 weights owned
+ * by the context and are selected as h3b_dit_set_linear_nvfp4 does.  A sidecar carries no norms: load the block from
+ * the checkpoint it accompanies as well (first or afterwards). */
+int h3b_dit_load_nvfp4_block(h3b_dit *dit, const h3b_ckpt *sidecar, unsigned src_block, unsigned dst_block,
+                             unsigned linears, char *error, size_t error_size);
 /* Host f32 vectors, copied to the device: norm1/norm2 [dim], q_norm/k_norm [head_dim],
  * norm_cross [dim] (cross block only, else NULL). */
 int h3b_dit_set_block_aux(h3b_dit *dit, unsigned block, const float *norm1, const float *norm2,
