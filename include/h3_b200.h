@@ -487,6 +487,8 @@ int h3_cuda_quantize_act_nvfp4_dev(h3_cuda *cuda, const float *d_x, size_t m, si
 int h3_cuda_gemm_fp4_bs_dev(h3_cuda *cuda, const uint8_t *d_w_fp4, const uint8_t *d_sf_w,
                             const uint8_t *d_x_fp4, const uint8_t *d_sf_x, size_t m, size_t n, size_t k,
                             void *d_y_bf16, double *gemm_ms, char *error, size_t error_size);
+/* On success the library owns both host buffers (malloc'ed by the caller; copied, then released with free()); on failure
+ * the caller keeps them.  h3_gpu_cuda.h:437-444 */
 int h3_cuda_nvfp4_weight_create(h3_cuda *cuda, const uint8_t *packed_host,
                                 const uint8_t *sf_swizzled_host, float scale2, size_t n, size_t k,
                                 h3_cuda_nvfp4_weight **out, double *h2d_ms, char *error,
