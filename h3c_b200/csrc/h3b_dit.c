@@ -661,7 +661,22 @@ static int block_forward(h3b_dit *d, unsigned block, const void *d_x, size_t seq
     if (!d->uly || !d->uly->comm) {
         /* QKV projection with the QK-norm and RoPE applied in the GEMM epilogue: Q, K, V leave the kernel
          * as bf16 [seq, heads, 128]; the [seq, 3*inner] intermediate is never written */
-        if (b->fp4[H3B_LIN_QKV]) {
+        if (b->fp4[H3B_LIN_QKV] && D % 64 == 0 && d->cfg.head_dim == 128 && dt == H3B_F32 &&
+            (d->cfg.rope_half == 0 || d->cfg.rope_half == 48 || d->cfg.rope_half == 64) && 3 * I >= 256 &&
+            h3_plugin_enabled("H3B_FP4_WIDE") && h3_plugin_enabled("H3B_FP4_QKV_ROPE")) {
+            /* the same for an NVFP4 projection: adaLN, ConvRot and the NVFP4 quantisation in the row kernel, QK-norm and
+             * RoPE on the f32 accumulators in the GEMM epilogue (H3B_FP4_QKV_ROPE=0 keeps the two stand-alone steps) */
+            h3b_norm_args a;
+            memset(&a, 0, sizeof(a));
+            a.d_x = d_x; a.d_norm_w = b->norm1; a.d_modulation = mod; a.d_row_map = d_row_map; a.rows = seq; a.width = D;
+            a.slots = 6; a.shift_slot = 0; a.scale_slot = 1; a.epsilon = d->cfg.eps; a.dtype = dt;
+            a.convrot_gs = d->cfg.convrot_gs; a.d_fp4 = d->x4; a.d_sf = d->sfx;
+            if (!h3b_norm_dev(d->cuda, &a, error, error_size) ||
+                !h3b_gemm_fp4_w_preq_qkv_rope_dev(d->cuda, b->fp4[H3B_LIN_QKV], d->x4, d->sfx, seq, 1.0f, b->q_norm, b->k_norm,
+                                                  d_cos, d_sin, d->cfg.rope_half, d->cfg.heads, d->cfg.eps, d->q, d->k, d->v,
+                                                  error, error_size))
+                return 0;
+        } else if (b->fp4[H3B_LIN_QKV]) {
             if (!fp4_linear(d, b->fp4[H3B_LIN_QKV], d_x, dt, seq, D, b->norm1, mod, d_row_map, 0, 1, 0, 0, NULL, 0,
                             (float *)d->qkv, error, error_size) ||
                 !h3b_qkv_rope_dev(d->cuda, d->qkv, dt, b->q_norm, b->k_norm, d_cos, d_sin, seq, d->cfg.heads,

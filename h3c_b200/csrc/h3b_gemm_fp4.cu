@@ -26,6 +26,7 @@
 
 #include "h3b_internal.h"
 #include "h3b_ptx.cuh"
+#include "h3b_qkv_epi.cuh"
 
 namespace h3b {
 
@@ -52,6 +53,10 @@ struct Fp4Params {
     CUtensorMap tmap_res; // wide form, gate epilogue: the residual, same geometry
     CUtensorMap tmap_sfx; // pair form: scale tiles of X as [tiles, 128] words, box of four tiles
     CUtensorMap tmap_sfw; // pair form: scale tiles of W, same geometry
+    CUtensorMap tmap_yk, tmap_yv;   // QKV epilogue: K and V outputs [M, heads * 128] bf16 (Q is tmap_y)
+    const float *q_norm, *k_norm, *cosT, *sinT;   // QKV epilogue: QK-norm weights [128], RoPE tables [M, rope_half]
+    int rope_half, heads;
+    float eps;
     const uint8_t *sf_x, *sf_w;
     int M, N, K;
     int m_tiles, n_tiles, k_blocks;
@@ -345,6 +350,9 @@ __device__ __forceinline__ void wide_tile_coords(int tile, int m_tiles, int n_ti
     nt = local / gm;
 }
 
+// MODE 3: the QKV projection with QK-norm and split-half RoPE: a warp's 128 columns are one head of Q, K or V, the
+// thread holds its row of it; Q, K, V leave as bf16 [M, heads, 128] (h3_dit_w4a8_qkv_rope_f32, h3_dit_w4a8.c:2805-2890,
+// on the f32 accumulators; the [M, 3 heads 128] intermediate is never written).
 // MODE 0: y = alpha acc; 1: y = residual + alpha acc gate; 2: SwiGLU, y[:, c] = silu(alpha acc[:, c]) * alpha acc[:, N/2 + c]
 // in f32 straight from the accumulator (the reference's chain h3_cutlass_nvfp4_fc1_f32_run -> swiglu, h3_dit_nvfp4_chain.cu:
 // 201-277, 322-435, as one kernel).  For SwiGLU the tile's first 128 weight rows are gate rows nt*128.., the second
@@ -356,7 +364,8 @@ __device__ __forceinline__ void wide_tile_coords(int tile, int m_tiles, int n_ti
 template <int MODE, bool OUT_BF16, bool PAIR>
 __global__ void __launch_bounds__(fp4w::THREADS, 1) k_gemm_nvfp4_wide(const __grid_constant__ Fp4Params p) {
     using namespace fp4w;
-    constexpr bool GATE = MODE == 1, SWIGLU = MODE == 2;
+    constexpr bool GATE = MODE == 1, SWIGLU = MODE == 2, QKV = MODE == 3;
+    static_assert(!QKV || OUT_BF16, "the QKV epilogue writes bf16");
     constexpr int STAGES = PAIR ? fp4w::PAIR_STAGES : fp4w::STAGES;
     constexpr int B_BYTES = PAIR ? fp4w::B_BYTES / 2 : fp4w::B_BYTES;
     constexpr int STAGE_BYTES = PAIR ? fp4w::PAIR_STAGE_BYTES : fp4w::STAGE_BYTES;
@@ -392,6 +401,10 @@ __global__ void __launch_bounds__(fp4w::THREADS, 1) k_gemm_nvfp4_wide(const __gr
         if (PAIR) {
             tma_prefetch_desc(&p.tmap_sfx);
             tma_prefetch_desc(&p.tmap_sfw);
+        }
+        if (QKV) {
+            tma_prefetch_desc(&p.tmap_yk);
+            tma_prefetch_desc(&p.tmap_yv);
         }
     }
     if (warp == 1) {
@@ -545,6 +558,23 @@ __global__ void __launch_bounds__(fp4w::THREADS, 1) k_gemm_nvfp4_wide(const __gr
             }
             const int col0 = SWIGLU ? nt * 128 + half * 64 : nt * BN + half * 128;
             const int n_out = SWIGLU ? p.N / 2 : p.N;
+            float(&hv)[128] = reinterpret_cast<float(&)[128]>(r);   // QKV: the finished head, in the accumulator's registers
+            int which = 0, head = 0;
+            if (QKV && ok && row0 < p.M && col0 < p.N) {
+#pragma unroll
+                for (int i = 0; i < 128; i++) hv[i] = __fmul_rn(p.alpha, __uint_as_float(r[i]));
+                const int g = col0 >> 7;
+                which = g / p.heads;
+                head = g - which * p.heads;
+                if constexpr (QKV) {
+                    if (which < 2) {
+                        qk_norm_head(hv, which == 0 ? p.q_norm : p.k_norm, p.eps);
+                        const size_t trow = (size_t)min(row0 + lane, p.M - 1);   // rows past M are clipped by the store
+                        if (p.rope_half == 48) rope_split_half<48>(hv, p.cosT + trow * 48, p.sinT + trow * 48);
+                        else if (p.rope_half == 64) rope_split_half<64>(hv, p.cosT + trow * 64, p.sinT + trow * 64);
+                    }
+                }
+            }
             if (ok && row0 < p.M) {
 #pragma unroll
                 for (int ch = 0; ch < NCH; ch++) {
@@ -568,7 +598,7 @@ __global__ void __launch_bounds__(fp4w::THREADS, 1) k_gemm_nvfp4_wide(const __gr
                         float out[UNIT];
 #pragma unroll
                         for (int e = 0; e < UNIT; e++) {
-                            out[e] = __fmul_rn(p.alpha, __uint_as_float(r[v + e]));
+                            out[e] = QKV ? hv[v + e] : __fmul_rn(p.alpha, __uint_as_float(r[v + e]));
                             if (SWIGLU) {
                                 const float u_ = __fmul_rn(p.alpha, __uint_as_float(r[64 + v + e]));
                                 // hardware exponential and reciprocal (about 2 ulp): the IEEE division and expf expand to
@@ -614,7 +644,10 @@ __global__ void __launch_bounds__(fp4w::THREADS, 1) k_gemm_nvfp4_wide(const __gr
                     fence_proxy_async_smem();
                     __syncwarp();
                     if (lane == 0) {
-                        tma_store_2d(&p.tmap_y, stg, col, row0);
+                        if (QKV)
+                            tma_store_2d(which == 0 ? &p.tmap_y : which == 1 ? &p.tmap_yk : &p.tmap_yv, stg,
+                                         head * 128 + ch * CH_COLS, row0);
+                        else tma_store_2d(&p.tmap_y, stg, col, row0);
                         tma_store_commit();
                     }
                 }
@@ -639,7 +672,7 @@ __global__ void __launch_bounds__(fp4w::THREADS, 1) k_gemm_nvfp4_wide(const __gr
 int launch_gemm_nvfp4(h3_cuda *cuda, const uint8_t *w_fp4, const uint8_t *sf_w, const uint8_t *x_fp4, const uint8_t *sf_x,
                       size_t m, size_t n, size_t k, float alpha, void *y, int out_dtype, int gate, const void *residual,
                       const float *mod, const uint32_t *row_map, size_t slots, size_t gate_slot, char *error,
-                      size_t error_size) {
+                      size_t error_size, const Fp4QkvArgs *qkv) {
     using namespace fp4;
     if (!cuda || !w_fp4 || !sf_w || !x_fp4 || !sf_x || !y || !m || !n || !k)
         return fail(error, error_size, "gemm_fp4: invalid arguments");
@@ -649,6 +682,17 @@ int launch_gemm_nvfp4(h3_cuda *cuda, const uint8_t *w_fp4, const uint8_t *sf_w, 
     if (((uintptr_t)w_fp4 | (uintptr_t)x_fp4 | (uintptr_t)sf_w | (uintptr_t)sf_x | (uintptr_t)y) & 15)
         return fail(error, error_size, "gemm_fp4: buffers must be 16-byte aligned");
     if (gate == 1 && !residual) return fail(error, error_size, "gemm_fp4: gate epilogue needs a residual");
+    if (gate == 3) {
+        if (!qkv || !qkv->k || !qkv->v || !qkv->q_norm || !qkv->k_norm || !qkv->heads || n != 3 * qkv->heads * 128 ||
+            out_dtype != H3B_BF16 || n < 256 || !h3_plugin_enabled("H3B_FP4_WIDE"))
+            return fail(error, error_size, "gemm_fp4: the QKV epilogue needs N = 3 x heads x 128, bf16 outputs and the 128 x 256 tile form");
+        if (qkv->rope_half != 0 && qkv->rope_half != 48 && qkv->rope_half != 64)
+            return fail(error, error_size, "gemm_fp4: the QKV epilogue rotates 48 or 64 dimension pairs (or none)");
+        if (qkv->rope_half && (!qkv->cosT || !qkv->sinT)) return fail(error, error_size, "gemm_fp4: RoPE tables missing");
+        if (((uintptr_t)qkv->k | (uintptr_t)qkv->v | (uintptr_t)qkv->q_norm | (uintptr_t)qkv->k_norm | (uintptr_t)qkv->cosT |
+             (uintptr_t)qkv->sinT) & 15)
+            return fail(error, error_size, "gemm_fp4: QKV outputs, norm weights and tables must be 16-byte aligned");
+    }
     if (gate == 2 && (n % 256 || !h3_plugin_enabled("H3B_FP4_WIDE")))
         return fail(error, error_size, "gemm_fp4: the fused SwiGLU epilogue needs N %% 256 == 0 and the 128 x 256 tile form");
     if (m > 0x7fffff00u || n > 0x7fffff00u) return fail(error, error_size, "gemm_fp4: shape too large");
@@ -677,8 +721,15 @@ int launch_gemm_nvfp4(h3_cuda *cuda, const uint8_t *w_fp4, const uint8_t *sf_w, 
         p.n_tiles = (int)ceil_div(n, (size_t)fp4w::BN);   // SwiGLU: N/2 output columns, 128 per tile: the same count
         const bool bf = out_dtype == H3B_BF16;
         const CUtensorMapDataType odt = bf ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32;
-        const size_t osz = bf ? 2 : 4, n_y = gate == 2 ? n / 2 : n;
+        const size_t osz = bf ? 2 : 4, n_y = gate == 2 ? n / 2 : gate == 3 ? n / 3 : n;
         rc2 = h3b_encode_tmap_2d(&p.tmap_y, odt, osz, y, n_y, m, n_y * osz, (uint32_t)(128 / osz), 32, CU_TENSOR_MAP_SWIZZLE_128B);
+        if (rc2 == 0 && gate == 3) {
+            rc2 = h3b_encode_tmap_2d(&p.tmap_yk, odt, osz, qkv->k, n_y, m, n_y * osz, 64, 32, CU_TENSOR_MAP_SWIZZLE_128B);
+            if (rc2 == 0)
+                rc2 = h3b_encode_tmap_2d(&p.tmap_yv, odt, osz, qkv->v, n_y, m, n_y * osz, 64, 32, CU_TENSOR_MAP_SWIZZLE_128B);
+            p.q_norm = qkv->q_norm; p.k_norm = qkv->k_norm; p.cosT = qkv->cosT; p.sinT = qkv->sinT;
+            p.rope_half = qkv->rope_half; p.heads = (int)qkv->heads; p.eps = qkv->eps;
+        }
         if (rc2 == 0 && gate == 1)
             rc2 = h3b_encode_tmap_2d(&p.tmap_res, odt, osz, residual, n, m, n * osz, (uint32_t)(128 / osz), 32,
                                      CU_TENSOR_MAP_SWIZZLE_128B);
@@ -692,7 +743,8 @@ int launch_gemm_nvfp4(h3_cuda *cuda, const uint8_t *w_fp4, const uint8_t *sf_w, 
                 rc2 = h3b_encode_tmap_2d(&p.tmap_sfw, CU_TENSOR_MAP_DATA_TYPE_UINT32, 4, sf_w, 128, tiles_wt, 512, 128, 4,
                                          CU_TENSOR_MAP_SWIZZLE_NONE);
             if (rc2 != 0) return fail(error, error_size, "gemm_fp4: cuTensorMapEncodeTiled (scales) failed (%d)", rc2);
-            auto kp = gate == 2   ? (p.out_bf16 ? k_gemm_nvfp4_wide<2, true, true> : k_gemm_nvfp4_wide<2, false, true>)
+            auto kp = gate == 3   ? k_gemm_nvfp4_wide<3, true, true>
+                      : gate == 2 ? (p.out_bf16 ? k_gemm_nvfp4_wide<2, true, true> : k_gemm_nvfp4_wide<2, false, true>)
                       : gate == 1 ? (p.out_bf16 ? k_gemm_nvfp4_wide<1, true, true> : k_gemm_nvfp4_wide<1, false, true>)
                                   : (p.out_bf16 ? k_gemm_nvfp4_wide<0, true, true> : k_gemm_nvfp4_wide<0, false, true>);
             H3B_CUDA_OK(cudaFuncSetAttribute(kp, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)fp4w::PAIR_SMEM_BYTES),
@@ -708,7 +760,7 @@ int launch_gemm_nvfp4(h3_cuda *cuda, const uint8_t *w_fp4, const uint8_t *sf_w, 
             cfg.attrs = &attr;
             cfg.numAttrs = 1;
             // co-resident pairs on this device, asked once per kernel form and device
-            static int max_pairs[6][64];
+            static int max_pairs[8][64];
             const int dev = cuda->device & 63, form = gate * 2 + (p.out_bf16 ? 1 : 0);
             if (max_pairs[form][dev] == 0) {
                 cfg.gridDim = dim3((unsigned)(cuda->sm_count & ~1));
@@ -726,7 +778,8 @@ int launch_gemm_nvfp4(h3_cuda *cuda, const uint8_t *w_fp4, const uint8_t *sf_w, 
             cuda->launches++;
             return 1;
         }
-        auto kw = gate == 2   ? (p.out_bf16 ? k_gemm_nvfp4_wide<2, true, false> : k_gemm_nvfp4_wide<2, false, false>)
+        auto kw = gate == 3   ? k_gemm_nvfp4_wide<3, true, false>
+                  : gate == 2 ? (p.out_bf16 ? k_gemm_nvfp4_wide<2, true, false> : k_gemm_nvfp4_wide<2, false, false>)
                   : gate == 1 ? (p.out_bf16 ? k_gemm_nvfp4_wide<1, true, false> : k_gemm_nvfp4_wide<1, false, false>)
                               : (p.out_bf16 ? k_gemm_nvfp4_wide<0, true, false> : k_gemm_nvfp4_wide<0, false, false>);
         H3B_CUDA_OK(cudaFuncSetAttribute(kw, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)fp4w::SMEM_BYTES),
@@ -876,6 +929,19 @@ int h3b_gemm_fp4_w_preq_dev(h3_cuda *cuda, const h3_cuda_nvfp4_weight *weight, c
                              weight->scale2 * act_scale, d_y, out_dtype, epi == 2 ? 1 : epi == 1 ? 2 : 0,
                              epi == 2 ? d_residual : NULL, epi == 2 ? d_modulation : NULL, epi == 2 ? d_row_map : NULL,
                              epi == 2 ? slots : 0, epi == 2 ? gate_slot : 0, error, error_size);
+}
+
+int h3b_gemm_fp4_w_preq_qkv_rope_dev(h3_cuda *cuda, const h3_cuda_nvfp4_weight *weight, const uint8_t *d_x_fp4,
+                                     const uint8_t *d_sf_x, size_t m, float act_scale, const float *d_q_norm,
+                                     const float *d_k_norm, const float *d_cos, const float *d_sin, size_t rope_half,
+                                     size_t heads, float epsilon, void *d_q, void *d_k, void *d_v, char *error,
+                                     size_t error_size) {
+    if (!cuda || !weight || !d_x_fp4 || !d_sf_x || !d_q || !m) return fail(error, error_size, "gemm_fp4_w_preq_qkv_rope: invalid arguments");
+    Fp4QkvArgs a;
+    a.k = d_k; a.v = d_v; a.q_norm = d_q_norm; a.k_norm = d_k_norm; a.cosT = d_cos; a.sinT = d_sin;
+    a.rope_half = (int)rope_half; a.heads = heads; a.eps = epsilon;
+    return launch_gemm_nvfp4(cuda, weight->d_packed, weight->d_sf, d_x_fp4, d_sf_x, m, weight->n, weight->k,
+                             weight->scale2 * act_scale, d_q, H3B_BF16, 3, NULL, NULL, NULL, 0, 0, error, error_size, &a);
 }
 
 // activation quantisation into the scratch area; returns pointers into it

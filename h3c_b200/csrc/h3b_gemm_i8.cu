@@ -26,6 +26,7 @@
 
 #include "h3b_internal.h"
 #include "h3b_ptx.cuh"
+#include "h3b_qkv_epi.cuh"
 
 namespace h3b {
 
@@ -144,25 +145,6 @@ __device__ __forceinline__ float gelu_tanh_fast(float v) {
     float inner = 0.7978845608028654f * (v + 0.044715f * v * v * v), t;
     asm("tanh.approx.f32 %0, %1;" : "=f"(t) : "f"(inner));
     return 0.5f * v * (1.0f + t);
-}
-
-// split-half RoPE on one head held in registers: dimension d pairs with d + RH
-// (h3_dit_w4a8.c:2850-2883), cos/sin rows of RH floats
-template <int RH>
-__device__ __forceinline__ void rope_split_half(float (&v)[128], const float *cr, const float *sr) {
-#pragma unroll
-    for (int d4 = 0; d4 < RH / 4; d4++) {
-        const float4 c4 = __ldg(reinterpret_cast<const float4 *>(cr) + d4);
-        const float4 s4 = __ldg(reinterpret_cast<const float4 *>(sr) + d4);
-        const float cc[4] = {c4.x, c4.y, c4.z, c4.w}, sn[4] = {s4.x, s4.y, s4.z, s4.w};
-#pragma unroll
-        for (int e = 0; e < 4; e++) {
-            const int d = d4 * 4 + e;
-            const float lo = v[d], hi = v[d + RH];
-            v[d] = __fsub_rn(__fmul_rn(lo, cc[e]), __fmul_rn(hi, sn[e]));
-            v[d + RH] = __fadd_rn(__fmul_rn(hi, cc[e]), __fmul_rn(lo, sn[e]));
-        }
-    }
 }
 
 // The same with the cos / sin rows of the warp's 32 rows in shared memory, as TMA left them: per table two

@@ -100,10 +100,18 @@ int launch_convrot(h3_cuda *cuda, const float *x, size_t m, size_t k, int gs, fl
                    size_t error_size);
 int launch_gemm_i8(h3_cuda *cuda, const h3_cuda_w4a8_weight *w, const int8_t *x, const float *a, size_t m,
                    void *y, const h3b_gemm_epi *epi, char *error, size_t error_size);
+// gate: 0 plain, 1 residual + gate, 2 SwiGLU, 3 QKV with QK-norm and RoPE (y = Q, the rest in `qkv`)
+struct Fp4QkvArgs {
+    void *k, *v;
+    const float *q_norm, *k_norm, *cosT, *sinT;
+    int rope_half;
+    size_t heads;
+    float eps;
+};
 int launch_gemm_nvfp4(h3_cuda *cuda, const uint8_t *w_fp4, const uint8_t *sf_w, const uint8_t *x_fp4, const uint8_t *sf_x,
                       size_t m, size_t n, size_t k, float alpha, void *y, int out_dtype, int gate, const void *residual,
                       const float *mod, const uint32_t *row_map, size_t slots, size_t gate_slot, char *error,
-                      size_t error_size);
+                      size_t error_size, const Fp4QkvArgs *qkv = nullptr);
 // stream the f32 dense GEMMs run on: the op stream, or side stream 1 while h3_cuda_cublas_use_side is on
 static inline cudaStream_t dense_stream(const h3_cuda *c) { return c->blas_side ? c->side[1] : c->op_stream; }
 int launch_sdpa_bf16(h3_cuda *cuda, const void *q, size_t qs, const void *k, size_t ks, const void *v, size_t vs,

@@ -198,6 +198,7 @@ _SIGS = {
     "h3b_gemm_w4g_exact_dev": (i32, (vp, vp, vp, vp, sz, vp, i32) + _ERR),
     "h3b_gemm_fp4_dev": (i32, (vp, vp, vp, vp, vp, sz, sz, sz, f32, vp, i32) + _ERR),
     "h3b_gemm_fp4_w_preq_dev": (i32, (vp, vp, vp, vp, sz, f32, i32, vp, vp, vp, sz, sz, vp, i32) + _ERR),
+    "h3b_gemm_fp4_w_preq_qkv_rope_dev": (i32, (vp, vp, vp, vp, sz, f32, vp, vp, vp, vp, sz, sz, f32, vp, vp, vp) + _ERR),
     "h3b_gemm_fp4_swiglu_dev": (i32, (vp, vp, vp, vp, vp, sz, sz, sz, f32, vp, i32) + _ERR),
     "h3_cuda_nvfp4_weight_create": (i32, (vp, vp, vp, f32, sz, sz, C.POINTER(vp), dbl_p) + _ERR),
     "h3_cuda_nvfp4_weight_ensure_ready": (i32, (vp,) + _ERR),

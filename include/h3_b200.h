@@ -537,6 +537,14 @@ int h3b_gemm_fp4_w_preq_dev(h3_cuda *cuda, const h3_cuda_nvfp4_weight *weight, c
                             const uint8_t *d_sf_x, size_t m, float act_scale, int epi, const void *d_residual,
                             const float *d_modulation, const uint32_t *d_row_map, size_t slots, size_t gate_slot,
                             void *d_y, int out_dtype, char *error, size_t error_size);
+/* The QKV projection on pre-quantised activations with QK-norm and split-half RoPE in the epilogue, on the f32
+ * accumulators: Q, K, V bf16 [m, heads, 128]; N of the weight = 3 * heads * 128, rope_half 0, 48 or 64, tables
+ * [m, rope_half] f32 (h3_dit_w4a8_qkv_rope_f32, h3_dit_w4a8.c:2805-2890, fused behind nvfp4_gemm_dispatch, :3519). */
+int h3b_gemm_fp4_w_preq_qkv_rope_dev(h3_cuda *cuda, const h3_cuda_nvfp4_weight *weight, const uint8_t *d_x_fp4,
+                                     const uint8_t *d_sf_x, size_t m, float act_scale, const float *d_q_norm,
+                                     const float *d_k_norm, const float *d_cos, const float *d_sin, size_t rope_half,
+                                     size_t heads, float epsilon, void *d_q, void *d_k, void *d_v, char *error,
+                                     size_t error_size);
 
 /* ------------------------------------------- the rest of the reference's operator surface
  * Everything below keeps the reference's name and signature (h3_gpu_cuda.h line cited per entry) so that the

@@ -24,6 +24,7 @@ extern "C" {
     X("H3B_GEMM_PAIRS", "STABLE", "DIT", "1")        /* 0: int8 GEMM on single-CTA tiles instead of CTA pairs */ \
     X("H3B_GEMM_SPLITK", "STABLE", "DIT", "1")       /* 0: whole tiles only; n >= 2: n slices of K per tail tile */ \
     X("H3B_FP4_WIDE", "STABLE", "DIT", "1")          /* 0: NVFP4 GEMM on 128 x 128 tiles */                     \
+    X("H3B_FP4_QKV_ROPE", "STABLE", "DIT", "1")      /* 0: NVFP4 QKV projection, then stand-alone QK-norm + RoPE */ \
     X("H3B_FP4_PAIRS", "STABLE", "DIT", "1")         /* 0: NVFP4 GEMM on single CTAs, no 256 x 256 pair tiles */ \
     X("H3B_ATTN_EMU", "STABLE", "DIT", "12")         /* attention kernel variant: 12, 13, 10, 0; 212, 213 = CTA pairs */ \
     X("H3B_ULYSSES_BARRIER", "STABLE", "SP", "flag") /* flag | nccl: barrier of the exchange-free form */       \

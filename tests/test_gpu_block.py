@@ -1,4 +1,6 @@
 """Whole-block and block-chain parity through the C ABI (h3b_dit_*) against the CPU oracle."""
+import os
+
 import numpy as np
 import pytest
 
@@ -105,6 +107,15 @@ def test_reference_block_with_nvfp4_linears(cuda, oracle, fp4_linears, gs):
     assert err < 3e-2, (fp4_linears, gs, err)
     # it is the NVFP4 block that ran (4-bit weights and activations sit percents away from the INT8 block), not INT8
     assert err < 0.5 * far < 0.2
+    if 0 in fp4_linears:
+        # QK-norm and RoPE in the NVFP4 QKV epilogue (the default) and as a stand-alone kernel give the same bits
+        os.environ["H3B_FP4_QKV_ROPE"] = "0"
+        try:
+            y2 = dit.block_forward(0, dev(x), dev(cos), dev(sin), modulation=dev(mod), row_map=dev(rmap.view(np.int32)))
+            cuda.check()
+        finally:
+            del os.environ["H3B_FP4_QKV_ROPE"]
+        assert torch.equal(y, y2)
     dit.close()
     for h in handles:
         cuda.nvfp4_weight_free(h)

@@ -518,6 +518,34 @@ def test_gemm_nvfp4_swiglu_in_the_epilogue(cuda, oracle, m, n, k):
     cuda.check()
 
 
+@pytest.mark.parametrize("m,heads,k,rope_half", [(200, 2, 256, 48), (130, 3, 512, 64), (300, 2, 256, 0)])
+def test_gemm_nvfp4_qkv_rope_in_the_epilogue(cuda, oracle, m, heads, k, rope_half):
+    """NVFP4 QKV projection with QK-norm and split-half RoPE in its epilogue: the bits of the two-step route (GEMM to
+    f32, then the stand-alone QK-norm + RoPE kernel), which the checker's h3_dit_w4a8_qkv_rope_f32 holds to bf16
+    rounding.  Three heads: the last 256-column tile holds one head only."""
+    from h3c_b200.lib import call, ptr
+    rng = np.random.default_rng(90 + m)
+    n, hd = 3 * heads * 128, 128
+    w = rng.normal(0, 0.05, (n, k)).astype(np.float32)
+    w4, sfw = oracle.quantize_nvfp4(w, rule=1)
+    wh = cuda.nvfp4_weight(w4, sfw, 0.75, n, k)
+    x4, sfx = cuda.quantize_act_nvfp4(dev(acts(rng, m, k)))
+    qn, kn = dev(rng.normal(1, 0.1, hd).astype(np.float32)), dev(rng.normal(1, 0.1, hd).astype(np.float32))
+    ang = rng.uniform(0, 6.28, (m, max(rope_half, 1))).astype(np.float32)
+    cos, sin = dev(np.cos(ang)), dev(np.sin(ang))
+    q, kk, v = (torch.full((m, heads, hd), 7.0, dtype=torch.bfloat16, device="cuda") for _ in range(3))
+    call("h3b_gemm_fp4_w_preq_qkv_rope_dev", cuda.h, wh, ptr(x4), ptr(sfx), m, 1.0, ptr(qn), ptr(kn),
+         ptr(cos) if rope_half else None, ptr(sin) if rope_half else None, rope_half, heads, 1e-5, ptr(q), ptr(kk), ptr(v))
+    cuda.check()
+    qkv = cuda.gemm_fp4(dev(w4), dev(sfw), x4, sfx, alpha=0.75)
+    q2, k2, v2 = cuda.qkv_rope(qkv, qn, kn, cos, sin, heads, hd, rope_half, out_dtype=torch.bfloat16)
+    assert torch.equal(q, q2) and torch.equal(kk, k2) and torch.equal(v, v2)
+    qo, ko, vo = oracle.qkv_rope(host(qkv), host(qn), host(kn), host(cos) if rope_half else None,
+                                 host(sin) if rope_half else None, heads, hd, rope_half)
+    assert rel_l2(host(q), qo) < 3e-3 and rel_l2(host(kk), ko) < 3e-3 and np.array_equal(host(v), oracle.bf16_round(vo))
+    cuda.nvfp4_weight_free(wh)
+
+
 @pytest.mark.parametrize("m,n,k", [(150, 256, 512), (300, 640, 1024), (90, 128, 256)])
 def test_reference_nvfp4_linear_entry_points(cuda, oracle, m, n, k):
     rng = np.random.default_rng(61)
