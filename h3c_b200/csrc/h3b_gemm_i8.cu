@@ -26,6 +26,7 @@
 
 #include "h3b_internal.h"
 #include "h3b_ptx.cuh"
+#include "h3b_gemm_plan.h"
 #include "h3b_qkv_epi.cuh"
 
 namespace h3b {
@@ -115,21 +116,9 @@ __device__ __forceinline__ void tile_coords(int tile, int m_tiles, int n_tiles, 
     nt = local / gm;
 }
 
-struct GemmItem { int tile, kb0, kb1, slice, slot, parts; };
+typedef h3b_gemm_item GemmItem;
 __device__ __forceinline__ GemmItem gemm_item(const GemmParams &p, int item) {
-    GemmItem w;
-    if (item < p.tail_first) {
-        w.tile = item; w.kb0 = 0; w.kb1 = p.k_blocks; w.slice = 0; w.slot = 0; w.parts = 1;
-    } else {
-        const int idx = item - p.tail_first;
-        w.slot = idx / p.split_s;
-        w.slice = idx - w.slot * p.split_s;
-        w.tile = p.tail_first + w.slot;
-        w.parts = p.split_s;
-        w.kb0 = (int)((long long)w.slice * p.k_blocks / p.split_s);
-        w.kb1 = (int)((long long)(w.slice + 1) * p.k_blocks / p.split_s);
-    }
-    return w;
+    return h3b_gemm_get_item(p.tail_first, p.split_s, p.k_blocks, item);
 }
 
 __device__ __forceinline__ float gelu_tanh_dev(float v) {   // h3_vision_cuda.c:365-371
@@ -885,34 +874,22 @@ static int gemm_launch_t(h3_cuda *cuda, GemmParams &p, char *error, size_t error
         // four slices, 320.3 -> 313.4 at 12,560 rows, 616.5 -> 607.7 at 25,110; forced on the K = 3072 projections it
         // loses 6 us.  H3B_GEMM_SPLITK=0 keeps whole tiles, a value of 2 or more forces that many slices.  The slot
         // memory belongs to the handle: one GEMM at a time per handle, as the op stream orders them.
-        p.items_total = tiles; p.tail_first = tiles; p.split_s = 1;
-        const int rem = tiles % n_pairs;
-        const int sk_mode = atoi(h3_plugin_value("H3B_GEMM_SPLITK"));
-        if (tiles > n_pairs && rem > 0 && 2 * rem <= n_pairs && sk_mode > 0) {
-            int split = sk_mode;
-            if (sk_mode == 1) {
-                const double t_tile = 0.39 * p.k_blocks, fold = 2.0;
-                split = (int)(sqrt(t_tile / fold) + 0.5);
-                if (split >= 2 && t_tile - t_tile / split - fold * (split - 1) < 8.0) split = 1;
-            }
-            if (split > n_pairs / rem) split = n_pairs / rem;
-            if (split > p.k_blocks / 2) split = p.k_blocks / 2;
-            if (split > 16) split = 16;
+        h3b_gemm_plan plan = h3b_gemm_make_plan(tiles, n_pairs, p.k_blocks, atoi(h3_plugin_value("H3B_GEMM_SPLITK")));
+        if (plan.split_s > 1) {
             const size_t need = SPLITK_CNT_BYTES + (size_t)max_pairs[dev] * Shape<2, EPI>::TILE_M * BN * sizeof(int32_t);
-            if (split >= 2 && cuda->splitk_bytes < need && !cuda->graph_capture) {
+            if (cuda->splitk_bytes < need && !cuda->graph_capture) {
                 if (cuda->splitk) cudaFree(cuda->splitk);
                 cuda->splitk = nullptr; cuda->splitk_bytes = 0;
                 H3B_CUDA_OK(cudaMalloc(&cuda->splitk, need), "cudaMalloc(split-K slots)");
                 cuda->splitk_bytes = need;
                 H3B_CUDA_OK(cudaMemsetAsync(cuda->splitk, 0, need, cuda->op_stream), "cudaMemsetAsync(split-K slots)");
             }
-            if (split >= 2 && cuda->splitk_bytes >= need) {
-                p.split_s = split;
-                p.tail_first = tiles - rem;
-                p.items_total = p.tail_first + rem * split;
-                p.sk_cnt = reinterpret_cast<unsigned *>(cuda->splitk);
-                p.sk_acc = reinterpret_cast<int32_t *>(reinterpret_cast<uint8_t *>(cuda->splitk) + SPLITK_CNT_BYTES);
-            }
+            if (cuda->splitk_bytes < need) plan = h3b_gemm_make_plan(tiles, n_pairs, p.k_blocks, 0);   // no slots: whole tiles
+        }
+        p.items_total = plan.items_total; p.tail_first = plan.tail_first; p.split_s = plan.split_s;
+        if (plan.split_s > 1) {
+            p.sk_cnt = reinterpret_cast<unsigned *>(cuda->splitk);
+            p.sk_acc = reinterpret_cast<int32_t *>(reinterpret_cast<uint8_t *>(cuda->splitk) + SPLITK_CNT_BYTES);
         }
         ProfScope prof(cuda, PROF_GEMM);
         H3B_CUDA_OK(cudaLaunchKernelEx(&cfg, kern, p), "k_gemm_i8 pair launch");

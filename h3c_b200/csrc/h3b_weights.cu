@@ -5,6 +5,7 @@
 #include <string.h>
 
 #include "h3b_internal.h"
+#include "h3b_gemm_plan.h"
 #include "h3b_ptx.cuh"
 
 namespace h3b {
@@ -306,6 +307,22 @@ int h3b_w4a8_weight_download_scales(const h3_cuda_w4a8_weight *w, float *host_ou
 }
 
 // ---------------------------------------------------------------- linears
+
+int h3b_gemm_i8_plan(size_t tiles, size_t pairs, size_t k_blocks, int mode, size_t item, int *items_total, int *tail_first,
+                     int *split, int *tile, int *kb0, int *kb1, int *slice) {
+    if (tiles > 0x7fffffffu || pairs > 0x7fffffffu || k_blocks > 0x7fffffffu) return 0;
+    const h3b_gemm_plan pl = h3b_gemm_make_plan((int)tiles, (int)pairs, (int)k_blocks, mode);
+    if (items_total) *items_total = pl.items_total;
+    if (tail_first) *tail_first = pl.tail_first;
+    if (split) *split = pl.split_s;
+    if (item >= (size_t)pl.items_total) return tile || kb0 || kb1 || slice ? 0 : 1;
+    const h3b_gemm_item w = h3b_gemm_get_item(pl.tail_first, pl.split_s, (int)k_blocks, (int)item);
+    if (tile) *tile = w.tile;
+    if (kb0) *kb0 = w.kb0;
+    if (kb1) *kb1 = w.kb1;
+    if (slice) *slice = w.slice;
+    return 1;
+}
 
 int h3b_gemm_i8_dev(h3_cuda *cuda, const h3_cuda_w4a8_weight *weight, const int8_t *d_x_i8,
                     const float *d_act_scales, size_t m, void *d_y, const h3b_gemm_epi *epi, char *error,

@@ -177,6 +177,7 @@ _SIGS = {
     "h3b_ckpt_get": (i32, (vp, sz, vp)),
     "h3b_ckpt_find": (i32, (vp, C.c_char_p, vp)),
     "h3b_dit_load_int8_convrot_block": (i32, (vp, vp, C.c_uint, C.c_uint) + _ERR),
+    "h3b_gemm_i8_plan": (i32, (sz, sz, sz, i32, sz) + (C.POINTER(i32),) * 7),
     "h3b_dit_load_w4a8_block": (i32, (vp, vp, C.c_uint, C.c_uint) + _ERR),
     "h3b_dit_load_nvfp4_block": (i32, (vp, vp, C.c_uint, C.c_uint, C.c_uint) + _ERR),
     "h3b_dit_set_linear": (i32, (vp, C.c_uint, i32, vp) + _ERR),

@@ -294,6 +294,12 @@ typedef struct h3b_gemm_epi {
     const float *d_lora;
     void *lora_ready;
 } h3b_gemm_epi;
+/* Work decomposition of the persistent int8 GEMM (no GPU needed): `tiles` 256 x 256 tiles on `pairs` CTA pairs with
+ * `k_blocks` 128-byte blocks of K each; mode as H3B_GEMM_SPLITK (0 whole tiles, 1 the library's estimate, n >= 2 forced).
+ * Pair p runs items p, p + pairs, ...; item `item` covers k-blocks [kb0, kb1) of tile `tile`, slice 0 of a tile runs its
+ * epilogue after adding the other slices' sums.  Returns 0 if `item` is past the last item and item outputs are asked. */
+int h3b_gemm_i8_plan(size_t tiles, size_t pairs, size_t k_blocks, int mode, size_t item, int *items_total, int *tail_first,
+                     int *split, int *tile, int *kb0, int *kb1, int *slice);
 /* d_x_i8 [m,k] codes, d_act_scales [m]; d_y is [m,n] ([m,n/2] for swiglu). */
 int h3b_gemm_i8_dev(h3_cuda *cuda, const h3_cuda_w4a8_weight *weight, const int8_t *d_x_i8,
                     const float *d_act_scales, size_t m, void *d_y, const h3b_gemm_epi *epi,
