@@ -874,7 +874,9 @@ static int gemm_launch_t(h3_cuda *cuda, GemmParams &p, char *error, size_t error
         // four slices, 320.3 -> 313.4 at 12,560 rows, 616.5 -> 607.7 at 25,110; forced on the K = 3072 projections it
         // loses 6 us.  H3B_GEMM_SPLITK=0 keeps whole tiles, a value of 2 or more forces that many slices.  The slot
         // memory belongs to the handle: one GEMM at a time per handle, as the op stream orders them.
-        h3b_gemm_plan plan = h3b_gemm_make_plan(tiles, n_pairs, p.k_blocks, atoi(h3_plugin_value("H3B_GEMM_SPLITK")));
+        // (never inside a stream capture: a graph would keep the slots' address beyond h3_cuda_release_heavy_workspace)
+        h3b_gemm_plan plan = h3b_gemm_make_plan(tiles, n_pairs, p.k_blocks,
+                                                cuda->graph_capture ? 0 : atoi(h3_plugin_value("H3B_GEMM_SPLITK")));
         if (plan.split_s > 1) {
             const size_t need = SPLITK_CNT_BYTES + (size_t)max_pairs[dev] * Shape<2, EPI>::TILE_M * BN * sizeof(int32_t);
             if (cuda->splitk_bytes < need && !cuda->graph_capture) {
