@@ -347,6 +347,8 @@ int h3b_cuda_check(h3_cuda *cuda, int *status_out, char *error, size_t error_siz
     if (status_out) *status_out = st;
     if (st != 0) {
         cudaMemset(cuda->d_status, 0, sizeof(int));
+        // a GEMM that gave up may have left the counters of its split tail tiles mid-count: start them over
+        if (cuda->splitk) cudaMemset(cuda->splitk, 0, cuda->splitk_bytes < 1024 ? cuda->splitk_bytes : 1024);
         return fail(error, error_size, "a kernel gave up a bounded wait (status %d); its output is invalid", st);
     }
     return 1;
