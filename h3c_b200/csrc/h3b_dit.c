@@ -421,6 +421,12 @@ int h3b_dit_load_w4a8_block(h3b_dit *d, const h3b_ckpt *ckpt, unsigned src_block
     return load_block_aux_from_ckpt(d, ckpt, src_block, dst_block, error, error_size);
 }
 
+static void *heap_copy(const void *src, size_t bytes) {
+    void *p = malloc(bytes ? bytes : 1);
+    if (p) memcpy(p, src, bytes);
+    return p;
+}
+
 /* The reference's NVFP4 sidecar (h3_dit_w4a8.c:3158-3274): per linear `weight_fp4` U8 [n, k/2], `weight_sf` U8 (the
  * 128x4-blocked UE4M3 scales, h3_cuda_nvfp4_sf_bytes(n, k) bytes) and an optional F32 scalar `weight_scale2` (1 when
  * absent).  `linears` is a mask of the linears to take from the sidecar (bit 0 QKV, 1 OUT, 2 FC1, 3 FC2: the
@@ -438,7 +444,7 @@ int h3b_dit_load_nvfp4_block(h3b_dit *d, const h3b_ckpt *sidecar, unsigned src_b
         const size_t n = want_n[l], k = want_k[l], w_bytes = n * (k / 2), sf_bytes = h3_cuda_nvfp4_sf_bytes(n, k);
         h3b_ckpt_tensor w, sf, s2;
         h3_cuda_nvfp4_weight *obj = NULL;
-        uint8_t *h_w, *h_sf;
+        uint8_t *codes, *scales;
         float scale2 = 1.0f;
         if (!(linears & (1u << l))) continue;
         snprintf(name, sizeof(name), "blocks.%u.%s.weight_fp4", src_block, ckpt_suffix[l]);
@@ -453,20 +459,16 @@ int h3b_dit_load_nvfp4_block(h3b_dit *d, const h3b_ckpt *sidecar, unsigned src_b
                 return fail(error, error_size, "nvfp4 sidecar: %s must be one F32", name);
             memcpy(&scale2, s2.data, sizeof(float));
         }
-        /* the constructor owns its two host buffers once it has succeeded (h3_gpu_cuda.h:437-444): hand it copies */
-        h_w = (uint8_t *)malloc(w_bytes);
-        h_sf = (uint8_t *)malloc(sf_bytes);
-        if (!h_w || !h_sf) {
-            free(h_w);
-            free(h_sf);
-            return fail(error, error_size, "load_nvfp4_block: out of host memory");
-        }
-        memcpy(h_w, w.data, w_bytes);
-        memcpy(h_sf, sf.data, sf_bytes);
-        if (!h3_cuda_nvfp4_weight_create(d->cuda, h_w, h_sf, scale2, n, k, &obj, NULL, error, error_size)) {
-            free(h_w);
-            free(h_sf);
-            return 0;
+        /* the constructor owns its two host buffers once it has succeeded (h3_gpu_cuda.h:437-444): it gets heap copies
+         * of the mapped tensors, which are ours again only if it fails */
+        codes = (uint8_t *)heap_copy(w.data, w_bytes);
+        scales = (uint8_t *)heap_copy(sf.data, sf_bytes);
+        if (!codes || !scales ||
+            !h3_cuda_nvfp4_weight_create(d->cuda, codes, scales, scale2, n, k, &obj, NULL, error, error_size)) {
+            const int oom = !codes || !scales;
+            free(codes);
+            free(scales);
+            return oom ? fail(error, error_size, "load_nvfp4_block: out of host memory") : 0;
         }
         if (d->n_owned_fp4 == d->cap_owned_fp4) {
             size_t ncap = d->cap_owned_fp4 ? 2 * d->cap_owned_fp4 : 16;
